@@ -1,0 +1,163 @@
+/* nncase_b200 -- C ABI of the B200 (sm_100a) kernels behind nncase's `cuda` module.
+ *
+ * This is the thin extern "C" boundary that a runtime_module / custom-call plugin of the
+ * nncase native runtime (and its C# P/Invoke or Python ctypes callers) binds to. Plain
+ * pointers and sizes only. Every function returns 0 on success or a negative errno-style
+ * code, the convention of the reference's own C API (src/Native/src/api.cpp:25-49,
+ * managed side: src/Nncase.Simulator/Runtime/Interop/ErrorCode.cs:23-31):
+ *   -EINVAL  bad argument            -ENOMEM    device allocation failed
+ *   -ENOSYS  unsupported combination -EIO       a CUDA call or kernel failed
+ *   -ETIMEDOUT a kernel-internal wait ran out (the kernel returned, the context is usable)
+ * nncb_last_error() gives the text of the calling thread's last failure.
+ *
+ * Unless a function says "host", pointers are DEVICE pointers valid on the context's device.
+ * Calls enqueue work on the context's stream and return without synchronising; the *_host
+ * variants copy in, run, copy out and synchronise (the contract of the reference's
+ * synchronous kernels, src/Native/src/kernels/stackvm/tensor_ops.cpp).
+ *
+ * Quantized tensors: activations are u8, NHWC. Convolution weights are u8 or i8, OHWI
+ * ([oc][kh][kw][ic/groups]). Arithmetic of every quantized op is specified with the op and
+ * is bit-exact with the CPU oracle shipped in oracle/qoracle.c.
+ */
+#ifndef NNCASE_B200_H
+#define NNCASE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define NNCB_API __declspec(dllexport)
+#else
+#define NNCB_API __attribute__((visibility("default")))
+#endif
+
+typedef struct nncb_context nncb_context;
+typedef struct nncb_qconv2d nncb_qconv2d;
+
+/* element types, numbered like nncase's typecode_t for the types used here
+ * (src/Native/include/nncase/runtime/typecodes.def) */
+typedef enum nncb_dtype { NNCB_I8 = 2, NNCB_I16 = 3, NNCB_U8 = 6, NNCB_F16 = 10, NNCB_F32 = 11 } nncb_dtype;
+
+/* ---- context: device + stream (replaces kernels::kernel_context,
+ *      src/Native/include/nncase/kernels/kernel_context.h) ------------------------------ */
+/* stream: a cudaStream_t to launch on, or NULL to create an own non-blocking stream. */
+NNCB_API int nncb_context_create(int device, void *stream, nncb_context **out);
+NNCB_API int nncb_context_destroy(nncb_context *ctx);
+NNCB_API int nncb_context_set_stream(nncb_context *ctx, void *stream);
+NNCB_API void *nncb_context_stream(nncb_context *ctx);
+NNCB_API int nncb_synchronize(nncb_context *ctx);
+/* Number of kernels this context has launched so far. */
+NNCB_API uint64_t nncb_launch_count(nncb_context *ctx);
+/* Reads and clears the device-side status word kernels set when an internal wait ran out
+ * (0 = none). Synchronises the stream. */
+NNCB_API int nncb_check_device_status(nncb_context *ctx);
+NNCB_API const char *nncb_last_error(void);
+NNCB_API const char *nncb_version(void);
+
+/* ---- device memory (stands in for host_buffer, the only memory the reference has:
+ *      src/Native/include/nncase/runtime/host_buffer.h:46-84) ---------------------------- */
+NNCB_API int nncb_malloc(nncb_context *ctx, size_t bytes, void **dptr);
+NNCB_API int nncb_free(nncb_context *ctx, void *dptr);
+NNCB_API int nncb_memcpy_h2d(nncb_context *ctx, void *dst, const void *host_src, size_t bytes);
+NNCB_API int nncb_memcpy_d2h(nncb_context *ctx, void *host_dst, const void *src, size_t bytes);
+NNCB_API int nncb_memset(nncb_context *ctx, void *dst, int value, size_t bytes);
+
+/* ---- QuantParam math (host; replaces QuantUtility.GetQuantParam / FixupRange,
+ *      src/Nncase.Core/Utilities/QuantUtility.cs:41-97) ---------------------------------- */
+typedef enum nncb_quant_mode { NNCB_UNSIGNED = 0, NNCB_SIGNED_SYMMETRIC = 1, NNCB_SIGNED_ASYMMETRIC = 2 } nncb_quant_mode;
+NNCB_API int nncb_fixup_range(float *rmin, float *rmax, int symmetric);
+NNCB_API int nncb_get_quant_param(float rmin, float rmax, int bits, int mode, int32_t *zero_point, float *scale);
+
+/* ---- Quantize / Dequantize (replace kernels::stackvm::quantize / dequantize,
+ *      src/Native/src/kernels/stackvm/tensor_ops.cpp:681-695 and :268-283; arithmetic of
+ *      optimized/quantize.cpp:59-72 and optimized/dequantize.cpp:49-60) -------------------
+ *   q = clamp(rint(x / scale + zero_point), type_min, type_max)   (ties to even, true division)
+ *   y = ((float)q - (float)zero_point) * scale
+ * qtype: NNCB_U8, NNCB_I8 or NNCB_I16. Any n (n == 0 is a no-op). */
+NNCB_API int nncb_quantize(nncb_context *ctx, const float *in, void *out, size_t n, float scale, int32_t zero_point, int qtype);
+NNCB_API int nncb_dequantize(nncb_context *ctx, const void *in, float *out, size_t n, float scale, int32_t zero_point, int qtype);
+/* host-buffer forms: in/out are HOST pointers (synchronous). */
+NNCB_API int nncb_quantize_host(nncb_context *ctx, const float *in, void *out, size_t n, float scale, int32_t zero_point, int qtype);
+NNCB_API int nncb_dequantize_host(nncb_context *ctx, const void *in, float *out, size_t n, float scale, int32_t zero_point, int qtype);
+
+/* Module input/output stages: the reference's tensors are NCHW f32 at the module boundary;
+ * the kernels keep u8 NHWC inside. c_pad >= c pads the channel dimension with the zero point. */
+NNCB_API int nncb_quantize_nchw_to_nhwc_u8(nncb_context *ctx, const float *in, uint8_t *out, int n, int c, int h, int w, int c_pad, float scale, int32_t zero_point);
+NNCB_API int nncb_dequantize_nhwc_to_nchw_f32(nncb_context *ctx, const uint8_t *in, float *out, int n, int h, int w, int c, float scale, int32_t zero_point);
+/* u8 layout changes without arithmetic */
+NNCB_API int nncb_nchw_to_nhwc_u8(nncb_context *ctx, const uint8_t *in, uint8_t *out, int n, int c, int h, int w);
+NNCB_API int nncb_nhwc_to_nchw_u8(nncb_context *ctx, const uint8_t *in, uint8_t *out, int n, int h, int w, int c);
+
+/* ---- element-wise and pooling ops on u8 NHWC ------------------------------------------ */
+/* binary add (kernels::stackvm::binary, tensor_ops.cpp:70-89) between quantized tensors:
+ *   y = quantize(dequantize(a) + dequantize(b)) */
+NNCB_API int nncb_qadd_u8(nncb_context *ctx, const uint8_t *a, const uint8_t *b, uint8_t *y, size_t n, float sa, int32_t za, float sb, int32_t zb, float so, int32_t zo);
+/* y = quantize(clamp(dequantize(x), lo, hi)) -- clamp/relu/relu6 between quant params
+ * (kernels::stackvm::clamp / relu, reference/activation.cpp:32-55). Runs as a 256-entry table. */
+NNCB_API int nncb_requant_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, size_t n, float si, int32_t zi, float so, int32_t zo, float lo, float hi);
+/* y[i] = table[x[i]]; table: 256 bytes, HOST pointer. */
+NNCB_API int nncb_lut_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, size_t n, const uint8_t *host_table);
+/* reduce_window2d max (tensor_ops.cpp: reduce_window2d, reference/reduce_window.cpp:35-105):
+ * windows overlapping the padding also take the real value 0 (the zero point) into the max. */
+NNCB_API int nncb_maxpool_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, int n, int h, int w, int c, int kh, int kw, int stride_h, int stride_w, int pad_t, int pad_b, int pad_l, int pad_r, int32_t zero_point);
+/* reduce_window2d mean over the whole image:
+ *   mean = ((float)(sum q - cnt*zi) * si) / (float)cnt ; y = quantize(mean, so, zo) */
+NNCB_API int nncb_global_avgpool_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, int n, int h, int w, int c, float si, int32_t zi, float so, int32_t zo);
+
+/* ---- quantized Conv2D / MatMul (replace kernels::stackvm::conv2d, tensor_ops.cpp:181-220,
+ *      and kernels::stackvm::mat_mul, tensor_ops.cpp:553-565, for u8 x u8|i8 operands) ------
+ *   acc = sum over in-image taps of (xq - x_zp) * (wq - w_zp[oc])                 int32
+ *   v   = clamp((float)acc * mult[oc] + bias[oc], clamp_lo, clamp_hi)              f32, no fma
+ *   q   = clamp(rint(v / out_scale + out_zp), 0, 255) ; q = lut ? lut[q] : q
+ * optional fused residual add (res != NULL at run):  q = quantize(deq(q; out) + deq(res; res), add_out)
+ * optional second output y2 = quantize(clamp(deq(q'), y2_lo, y2_hi); y2_out) of the final q'.
+ * A MatMul [M,K]x[K,N] is the 1x1 case: n=1,h=1,w=M,c=K,oc=N with weights [N][K]. */
+typedef struct nncb_conv2d_desc {
+    int32_t n, h, w, c;
+    int32_t oc, kh, kw;
+    int32_t stride_h, stride_w;
+    int32_t pad_t, pad_b, pad_l, pad_r;
+    int32_t dil_h, dil_w;
+    int32_t groups;
+    int32_t w_signed;    /* 0: u8 weights, 1: i8 weights */
+    int32_t x_zp;
+    float out_scale;
+    int32_t out_zp;
+    float clamp_lo, clamp_hi;
+    /* fused residual add (used when has_residual != 0) */
+    int32_t has_residual;
+    float res_scale;
+    int32_t res_zp;
+    float add_out_scale;
+    int32_t add_out_zp;
+    /* second output (used when has_y2 != 0) */
+    int32_t has_y2;
+    float y2_scale;
+    int32_t y2_zp;
+    float y2_lo, y2_hi;
+    /* output as f32 real values (v above, no requantisation) instead of u8 */
+    int32_t f32_out;
+    /* 0: choose automatically; 1: force the CUDA-core kernel; 2: force the tcgen05 kernel */
+    int32_t force_path;
+} nncb_conv2d_desc;
+
+/* weights/w_zp/mult/bias/lut are HOST pointers, copied and repacked at creation.
+ * w_zp may be NULL (all zero); lut may be NULL. */
+NNCB_API int nncb_qconv2d_create(nncb_context *ctx, const nncb_conv2d_desc *desc, const void *weights, const int32_t *w_zp, const float *mult, const float *bias, const uint8_t *lut, nncb_qconv2d **out);
+NNCB_API int nncb_qconv2d_destroy(nncb_qconv2d *conv);
+/* 1 = CUDA-core kernel, 2 = tcgen05 tensor-core kernel */
+NNCB_API int nncb_qconv2d_path(const nncb_qconv2d *conv);
+NNCB_API int nncb_qconv2d_out_shape(const nncb_qconv2d *conv, int *oh, int *ow);
+/* y: u8 NHWC [n,oh,ow,oc] (or f32 when f32_out); res and y2 may be NULL when unused. */
+NNCB_API int nncb_qconv2d_run(nncb_context *ctx, nncb_qconv2d *conv, const uint8_t *x, const uint8_t *res, void *y, uint8_t *y2);
+/* One-shot with HOST buffers: x u8 NHWC in, y out; weights as in create. */
+NNCB_API int nncb_qconv2d_host(nncb_context *ctx, const nncb_conv2d_desc *desc, const void *weights, const int32_t *w_zp, const float *mult, const float *bias, const uint8_t *lut, const uint8_t *x, const uint8_t *res, void *y, uint8_t *y2);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NNCASE_B200_H */

@@ -1,0 +1,522 @@
+// extern "C" entry points declared in include/nncase_b200.h, the context object and the
+// host-side QuantParam math.
+#include "qconv.cuh"
+#include <cmath>
+#include <vector>
+
+namespace nncb {
+
+std::string &last_error() {
+    static thread_local std::string e;
+    return e;
+}
+
+int fail(int code, const char *fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    last_error() = buf;
+    return code;
+}
+
+int after_launch(nncb_context *ctx, const char *what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess)
+        return fail(-EIO, "launch of %s failed: %s", what, cudaGetErrorString(e));
+    ctx->launches++;
+    return 0;
+}
+
+// ---- host float arithmetic: one IEEE rounding per operation, like the device intrinsics ----
+// (host code of this library is compiled with floating-point contraction off)
+static inline int32_t host_quant_impl(float x, float scale, float zp, int32_t lo, int32_t hi) {
+    volatile float q = x / scale;
+    volatile float v = q + zp;
+    float r = nearbyintf(v);
+    // saturating conversion like the device's cvt.rni.s32.f32
+    int32_t i = r >= 2147483648.f ? INT32_MAX : (r <= -2147483648.f ? INT32_MIN : (std::isnan(r) ? 0 : (int32_t)r));
+    return i < lo ? lo : (i > hi ? hi : i);
+}
+
+void make_requant_table(float si, int32_t zi, float so, int32_t zo, float lo, float hi, uint8_t table[256]) {
+    for (int q = 0; q < 256; q++) {
+        volatile float d = (float)q - (float)zi;
+        volatile float f = d * si;
+        float t = f < hi ? f : hi;
+        float c = t > lo ? t : lo;
+        table[q] = (uint8_t)host_quant_impl(c, so, (float)zo, 0, 255);
+    }
+}
+
+EpiParams make_epi(const nncb_qconv2d *cv) {
+    const nncb_conv2d_desc &d = cv->d;
+    EpiParams p;
+    p.mult = cv->d_mult;
+    p.bias = cv->d_bias;
+    p.lut = cv->d_lut;
+    p.y2_lut = cv->d_y2lut;
+    p.out_scale = d.out_scale;
+    p.out_zp = (float)d.out_zp;
+    p.clamp_lo = d.clamp_lo;
+    p.clamp_hi = d.clamp_hi;
+    p.has_res = d.has_residual;
+    p.res_scale = d.res_scale;
+    p.res_zp = (float)d.res_zp;
+    p.add_scale = d.add_out_scale;
+    p.add_zp = (float)d.add_out_zp;
+    return p;
+}
+
+int quantize(nncb_context *, const float *, void *, size_t, float, int32_t, int);
+int dequantize(nncb_context *, const void *, float *, size_t, float, int32_t, int);
+int quantize_nchw_to_nhwc_u8(nncb_context *, const float *, uint8_t *, int, int, int, int, int, float, int32_t);
+int dequantize_nhwc_to_nchw_f32(nncb_context *, const uint8_t *, float *, int, int, int, int, float, int32_t);
+int nchw_to_nhwc_u8(nncb_context *, const uint8_t *, uint8_t *, int, int, int, int);
+int nhwc_to_nchw_u8(nncb_context *, const uint8_t *, uint8_t *, int, int, int, int);
+int qadd_u8(nncb_context *, const uint8_t *, const uint8_t *, uint8_t *, size_t, float, int32_t, float, int32_t, float, int32_t);
+int lut_u8(nncb_context *, const uint8_t *, uint8_t *, size_t, const uint8_t *);
+int maxpool_u8(nncb_context *, const uint8_t *, uint8_t *, int, int, int, int, int, int, int, int, int, int, int, int, int32_t);
+int global_avgpool_u8(nncb_context *, const uint8_t *, uint8_t *, int, int, int, int, float, int32_t, float, int32_t);
+
+static size_t qtype_size(int qtype) { return qtype == NNCB_I16 ? 2 : 1; }
+
+} // namespace nncb
+
+using namespace nncb;
+
+#define CHECK_CTX(ctx)                                                                          \
+    do {                                                                                        \
+        if (!(ctx))                                                                             \
+            return fail(-EINVAL, "null context");                                               \
+        cudaError_t e__ = cudaSetDevice((ctx)->device);                                         \
+        if (e__ != cudaSuccess)                                                                 \
+            return fail(-EIO, "cudaSetDevice(%d) failed: %s", (ctx)->device, cudaGetErrorString(e__)); \
+    } while (0)
+
+extern "C" {
+
+const char *nncb_version(void) { return "nncase_b200 0.1 (sm_100a)"; }
+const char *nncb_last_error(void) { return last_error().c_str(); }
+
+int nncb_context_create(int device, void *stream, nncb_context **out) {
+    if (!out)
+        return fail(-EINVAL, "nncb_context_create: null out");
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0)
+        return fail(-EIO, "no CUDA device available: %s", e == cudaSuccess ? "device count is 0" : cudaGetErrorString(e));
+    if (device < 0 || device >= count)
+        return fail(-EINVAL, "device %d out of range (0..%d)", device, count - 1);
+    NNCB_CUDA_TRY(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    NNCB_CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+        return fail(-ENOSYS, "device %d is sm_%d%d; this library contains sm_100a code only", device, prop.major, prop.minor);
+    nncb_context *ctx = new nncb_context();
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    if (stream) {
+        ctx->stream = (cudaStream_t)stream;
+    } else {
+        NNCB_CUDA_TRY(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
+        ctx->own_stream = true;
+    }
+    NNCB_CUDA_TRY(cudaMalloc(&ctx->d_status, sizeof(int)));
+    NNCB_CUDA_TRY(cudaMemset(ctx->d_status, 0, sizeof(int)));
+    *out = ctx;
+    return 0;
+}
+
+int nncb_context_destroy(nncb_context *ctx) {
+    if (!ctx)
+        return 0;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    cudaFree(ctx->d_status);
+    if (ctx->own_stream)
+        cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return 0;
+}
+
+int nncb_context_set_stream(nncb_context *ctx, void *stream) {
+    CHECK_CTX(ctx);
+    if (ctx->own_stream) {
+        cudaStreamSynchronize(ctx->stream);
+        cudaStreamDestroy(ctx->stream);
+        ctx->own_stream = false;
+    }
+    ctx->stream = (cudaStream_t)stream;
+    return 0;
+}
+
+void *nncb_context_stream(nncb_context *ctx) { return ctx ? (void *)ctx->stream : nullptr; }
+
+int nncb_synchronize(nncb_context *ctx) {
+    CHECK_CTX(ctx);
+    NNCB_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    return 0;
+}
+
+uint64_t nncb_launch_count(nncb_context *ctx) { return ctx ? ctx->launches : 0; }
+
+int nncb_check_device_status(nncb_context *ctx) {
+    CHECK_CTX(ctx);
+    int st = 0;
+    NNCB_CUDA_TRY(cudaMemcpyAsync(&st, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    NNCB_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    if (st != 0) {
+        NNCB_CUDA_TRY(cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream));
+        return fail(-ETIMEDOUT, "a kernel gave up waiting (role code %d) and returned early", st);
+    }
+    return 0;
+}
+
+int nncb_malloc(nncb_context *ctx, size_t bytes, void **dptr) {
+    CHECK_CTX(ctx);
+    if (!dptr)
+        return fail(-EINVAL, "nncb_malloc: null out");
+    *dptr = nullptr;
+    if (bytes == 0)
+        return 0;
+    cudaError_t e = cudaMalloc(dptr, bytes);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(-ENOMEM, "cudaMalloc(%zu) failed: %s", bytes, cudaGetErrorString(e));
+    }
+    return 0;
+}
+
+int nncb_free(nncb_context *ctx, void *dptr) {
+    CHECK_CTX(ctx);
+    if (dptr)
+        NNCB_CUDA_TRY(cudaFree(dptr));
+    return 0;
+}
+
+int nncb_memcpy_h2d(nncb_context *ctx, void *dst, const void *src, size_t bytes) {
+    CHECK_CTX(ctx);
+    if (bytes)
+        NNCB_CUDA_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    return 0;
+}
+
+int nncb_memcpy_d2h(nncb_context *ctx, void *dst, const void *src, size_t bytes) {
+    CHECK_CTX(ctx);
+    if (bytes) {
+        NNCB_CUDA_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+        NNCB_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    }
+    return 0;
+}
+
+int nncb_memset(nncb_context *ctx, void *dst, int value, size_t bytes) {
+    CHECK_CTX(ctx);
+    if (bytes)
+        NNCB_CUDA_TRY(cudaMemsetAsync(dst, value, bytes, ctx->stream));
+    return 0;
+}
+
+// ---- QuantParam math -----------------------------------------------------------------------
+int nncb_fixup_range(float *rmin, float *rmax, int symmetric) {
+    if (!rmin || !rmax)
+        return fail(-EINVAL, "nncb_fixup_range: null pointer");
+    if (symmetric) {
+        float r = std::fmax(std::fmax(std::fabs(*rmin), std::fabs(*rmax)), 0.01f);
+        *rmin = -r;
+        *rmax = r;
+        return 0;
+    }
+    float mx = std::fmax(0.f, *rmax), mn = std::fmin(0.f, *rmin);
+    volatile float r = mx - mn;
+    float rr = r;
+    if (rr == 0)
+        rr = 0.1f;
+    else if (rr < 0.01f)
+        rr = 0.01f;
+    volatile float nm = mn + rr;
+    *rmin = mn;
+    *rmax = nm;
+    return 0;
+}
+
+int nncb_get_quant_param(float rmin, float rmax, int bits, int mode, int32_t *zero_point, float *scale) {
+    if (!zero_point || !scale || bits < 2 || bits > 16)
+        return fail(-EINVAL, "nncb_get_quant_param: bad argument");
+    nncb_fixup_range(&rmin, &rmax, mode == NNCB_SIGNED_SYMMETRIC);
+    double qmin, qmax;
+    switch (mode) {
+    case NNCB_UNSIGNED:
+        qmin = 0, qmax = (double)((1 << bits) - 1);
+        break;
+    case NNCB_SIGNED_SYMMETRIC:
+        qmin = (double)(-(1 << (bits - 1)) + 1), qmax = (double)((1 << (bits - 1)) - 1);
+        break;
+    case NNCB_SIGNED_ASYMMETRIC:
+        qmin = (double)(-(1 << (bits - 1))), qmax = (double)((1 << (bits - 1)) - 1);
+        break;
+    default:
+        return fail(-EINVAL, "Invalid QuantMode");
+    }
+    volatile float spanf = rmax - rmin; // the reference subtracts in float, then divides in double
+    double span = (double)spanf;
+    double sc = span / (qmax - qmin);
+    double bias = std::nearbyint((double)rmin * (qmin - qmax) / span) + qmin; // banker's rounding
+    *zero_point = (int32_t)bias;
+    *scale = (float)sc;
+    return 0;
+}
+
+// ---- streaming ops -------------------------------------------------------------------------
+int nncb_quantize(nncb_context *ctx, const float *in, void *out, size_t n, float scale, int32_t zp, int qtype) {
+    CHECK_CTX(ctx);
+    return quantize(ctx, in, out, n, scale, zp, qtype);
+}
+int nncb_dequantize(nncb_context *ctx, const void *in, float *out, size_t n, float scale, int32_t zp, int qtype) {
+    CHECK_CTX(ctx);
+    return dequantize(ctx, in, out, n, scale, zp, qtype);
+}
+
+int nncb_quantize_host(nncb_context *ctx, const float *in, void *out, size_t n, float scale, int32_t zp, int qtype) {
+    CHECK_CTX(ctx);
+    if (n == 0)
+        return 0;
+    if (qtype != NNCB_U8 && qtype != NNCB_I8 && qtype != NNCB_I16)
+        return fail(-ENOSYS, "quantize: unsupported target type %d", qtype);
+    void *din = nullptr, *dout = nullptr;
+    NNCB_TRY(nncb_malloc(ctx, n * 4, &din));
+    int rc = nncb_malloc(ctx, n * qtype_size(qtype), &dout);
+    if (rc == 0)
+        rc = nncb_memcpy_h2d(ctx, din, in, n * 4);
+    if (rc == 0)
+        rc = quantize(ctx, (const float *)din, dout, n, scale, zp, qtype);
+    if (rc == 0)
+        rc = nncb_memcpy_d2h(ctx, out, dout, n * qtype_size(qtype));
+    cudaFree(din);
+    cudaFree(dout);
+    return rc;
+}
+
+int nncb_dequantize_host(nncb_context *ctx, const void *in, float *out, size_t n, float scale, int32_t zp, int qtype) {
+    CHECK_CTX(ctx);
+    if (n == 0)
+        return 0;
+    if (qtype != NNCB_U8 && qtype != NNCB_I8 && qtype != NNCB_I16)
+        return fail(-ENOSYS, "dequantize: unsupported source type %d", qtype);
+    void *din = nullptr, *dout = nullptr;
+    NNCB_TRY(nncb_malloc(ctx, n * qtype_size(qtype), &din));
+    int rc = nncb_malloc(ctx, n * 4, &dout);
+    if (rc == 0)
+        rc = nncb_memcpy_h2d(ctx, din, in, n * qtype_size(qtype));
+    if (rc == 0)
+        rc = dequantize(ctx, din, (float *)dout, n, scale, zp, qtype);
+    if (rc == 0)
+        rc = nncb_memcpy_d2h(ctx, out, dout, n * 4);
+    cudaFree(din);
+    cudaFree(dout);
+    return rc;
+}
+
+int nncb_quantize_nchw_to_nhwc_u8(nncb_context *ctx, const float *in, uint8_t *out, int n, int c, int h, int w, int c_pad, float scale, int32_t zp) {
+    CHECK_CTX(ctx);
+    return quantize_nchw_to_nhwc_u8(ctx, in, out, n, c, h, w, c_pad, scale, zp);
+}
+int nncb_dequantize_nhwc_to_nchw_f32(nncb_context *ctx, const uint8_t *in, float *out, int n, int h, int w, int c, float scale, int32_t zp) {
+    CHECK_CTX(ctx);
+    return dequantize_nhwc_to_nchw_f32(ctx, in, out, n, h, w, c, scale, zp);
+}
+int nncb_nchw_to_nhwc_u8(nncb_context *ctx, const uint8_t *in, uint8_t *out, int n, int c, int h, int w) {
+    CHECK_CTX(ctx);
+    return nchw_to_nhwc_u8(ctx, in, out, n, c, h, w);
+}
+int nncb_nhwc_to_nchw_u8(nncb_context *ctx, const uint8_t *in, uint8_t *out, int n, int h, int w, int c) {
+    CHECK_CTX(ctx);
+    return nhwc_to_nchw_u8(ctx, in, out, n, h, w, c);
+}
+int nncb_qadd_u8(nncb_context *ctx, const uint8_t *a, const uint8_t *b, uint8_t *y, size_t n, float sa, int32_t za, float sb, int32_t zb, float so, int32_t zo) {
+    CHECK_CTX(ctx);
+    return qadd_u8(ctx, a, b, y, n, sa, za, sb, zb, so, zo);
+}
+int nncb_requant_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, size_t n, float si, int32_t zi, float so, int32_t zo, float lo, float hi) {
+    CHECK_CTX(ctx);
+    uint8_t table[256];
+    make_requant_table(si, zi, so, zo, lo, hi, table);
+    return lut_u8(ctx, x, y, n, table);
+}
+int nncb_lut_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, size_t n, const uint8_t *host_table) {
+    CHECK_CTX(ctx);
+    return lut_u8(ctx, x, y, n, host_table);
+}
+int nncb_maxpool_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, int n, int h, int w, int c, int kh, int kw, int sh, int sw, int pt, int pb, int pl, int pr, int32_t zp) {
+    CHECK_CTX(ctx);
+    return maxpool_u8(ctx, x, y, n, h, w, c, kh, kw, sh, sw, pt, pb, pl, pr, zp);
+}
+int nncb_global_avgpool_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, int n, int h, int w, int c, float si, int32_t zi, float so, int32_t zo) {
+    CHECK_CTX(ctx);
+    return global_avgpool_u8(ctx, x, y, n, h, w, c, si, zi, so, zo);
+}
+
+// ---- quantized conv ------------------------------------------------------------------------
+int nncb_qconv2d_destroy(nncb_qconv2d *cv) {
+    if (!cv)
+        return 0;
+    cudaSetDevice(cv->device);
+    tc_conv_destroy(cv);
+    cudaFree(cv->d_w);
+    cudaFree(cv->d_wzp);
+    cudaFree(cv->d_mult);
+    cudaFree(cv->d_bias);
+    cudaFree(cv->d_lut);
+    cudaFree(cv->d_y2lut);
+    delete cv;
+    return 0;
+}
+
+static int upload(nncb_context *ctx, void **dst, const void *src, size_t bytes) {
+    NNCB_CUDA_TRY(cudaMalloc(dst, bytes));
+    NNCB_CUDA_TRY(cudaMemcpyAsync(*dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    return 0;
+}
+
+int nncb_qconv2d_create(nncb_context *ctx, const nncb_conv2d_desc *desc, const void *weights, const int32_t *w_zp,
+                        const float *mult, const float *bias, const uint8_t *lut, nncb_qconv2d **out) {
+    CHECK_CTX(ctx);
+    if (!desc || !weights || !mult || !bias || !out)
+        return fail(-EINVAL, "nncb_qconv2d_create: null argument");
+    const nncb_conv2d_desc &d = *desc;
+    if (d.n <= 0 || d.h <= 0 || d.w <= 0 || d.c <= 0 || d.oc <= 0 || d.kh <= 0 || d.kw <= 0 || d.stride_h <= 0 ||
+        d.stride_w <= 0 || d.dil_h <= 0 || d.dil_w <= 0 || d.groups <= 0 || d.pad_t < 0 || d.pad_b < 0 || d.pad_l < 0 ||
+        d.pad_r < 0)
+        return fail(-EINVAL, "nncb_qconv2d_create: non-positive dimension");
+    if (d.c % d.groups != 0 || d.oc % d.groups != 0)
+        return fail(-EINVAL, "nncb_qconv2d_create: channels not divisible by groups");
+    const int oh = conv_out_size(d.h, d.kh, d.stride_h, d.dil_h, d.pad_t, d.pad_b);
+    const int ow = conv_out_size(d.w, d.kw, d.stride_w, d.dil_w, d.pad_l, d.pad_r);
+    if (oh <= 0 || ow <= 0)
+        return fail(-EINVAL, "nncb_qconv2d_create: empty output");
+    if (!(d.out_scale > 0) && !d.f32_out)
+        return fail(-EINVAL, "nncb_qconv2d_create: output scale must be positive");
+    if (lut && (d.has_residual || d.f32_out))
+        return fail(-ENOSYS, "nncb_qconv2d_create: activation table cannot be combined with residual add or f32 output");
+    if (d.f32_out && (d.has_residual || d.has_y2))
+        return fail(-ENOSYS, "nncb_qconv2d_create: f32 output cannot be combined with residual add or a second output");
+
+    nncb_qconv2d *cv = new nncb_qconv2d();
+    cv->d = d;
+    cv->device = ctx->device;
+    cv->oh = oh;
+    cv->ow = ow;
+    const size_t wbytes = (size_t)d.oc * d.kh * d.kw * (d.c / d.groups);
+    std::vector<int32_t> wz(d.oc, 0);
+    if (w_zp)
+        memcpy(wz.data(), w_zp, sizeof(int32_t) * d.oc);
+    int rc = upload(ctx, &cv->d_w, weights, wbytes);
+    if (rc == 0)
+        rc = upload(ctx, (void **)&cv->d_wzp, wz.data(), sizeof(int32_t) * d.oc);
+    if (rc == 0)
+        rc = upload(ctx, (void **)&cv->d_mult, mult, sizeof(float) * d.oc);
+    if (rc == 0)
+        rc = upload(ctx, (void **)&cv->d_bias, bias, sizeof(float) * d.oc);
+    if (rc == 0 && lut)
+        rc = upload(ctx, (void **)&cv->d_lut, lut, 256);
+    uint8_t y2t[256];
+    if (rc == 0 && d.has_y2) {
+        const float fs = d.has_residual ? d.add_out_scale : d.out_scale;
+        const int32_t fz = d.has_residual ? d.add_out_zp : d.out_zp;
+        make_requant_table(fs, fz, d.y2_scale, d.y2_zp, d.y2_lo, d.y2_hi, y2t);
+        rc = upload(ctx, (void **)&cv->d_y2lut, y2t, 256);
+    }
+    if (rc == 0) {
+        cudaError_t e = cudaStreamSynchronize(ctx->stream);
+        if (e != cudaSuccess)
+            rc = fail(-EIO, "upload failed: %s", cudaGetErrorString(e));
+    }
+    if (rc == 0) {
+        std::string why;
+        const bool tc_ok = tc_conv_supported(d, &why);
+        if (d.force_path == PATH_TC && !tc_ok)
+            rc = fail(-ENOSYS, "tcgen05 path not available for this convolution: %s", why.c_str());
+        else if (d.force_path == PATH_SIMT || !tc_ok)
+            cv->path = PATH_SIMT;
+        else
+            cv->path = PATH_TC;
+    }
+    if (rc == 0 && cv->path == PATH_TC)
+        rc = tc_conv_create(ctx, cv, weights, w_zp);
+    if (rc != 0) {
+        nncb_qconv2d_destroy(cv);
+        return rc;
+    }
+    *out = cv;
+    return 0;
+}
+
+int nncb_qconv2d_path(const nncb_qconv2d *cv) { return cv ? cv->path : -EINVAL; }
+
+int nncb_qconv2d_out_shape(const nncb_qconv2d *cv, int *oh, int *ow) {
+    if (!cv || !oh || !ow)
+        return fail(-EINVAL, "nncb_qconv2d_out_shape: null argument");
+    *oh = cv->oh;
+    *ow = cv->ow;
+    return 0;
+}
+
+int nncb_qconv2d_run(nncb_context *ctx, nncb_qconv2d *cv, const uint8_t *x, const uint8_t *res, void *y, uint8_t *y2) {
+    CHECK_CTX(ctx);
+    if (!cv || !x || !y)
+        return fail(-EINVAL, "nncb_qconv2d_run: null argument");
+    if (cv->device != ctx->device)
+        return fail(-EINVAL, "nncb_qconv2d_run: plan belongs to device %d, context to %d", cv->device, ctx->device);
+    if (cv->d.has_residual && !res)
+        return fail(-EINVAL, "nncb_qconv2d_run: residual input missing");
+    if (cv->d.has_y2 && !y2)
+        return fail(-EINVAL, "nncb_qconv2d_run: second output missing");
+    if (!cv->d.has_residual)
+        res = nullptr;
+    if (!cv->d.has_y2)
+        y2 = nullptr;
+    if (cv->path == PATH_TC)
+        return tc_conv_run(ctx, cv, x, res, y, y2);
+    return simt_conv_run(ctx, cv, x, res, y, y2);
+}
+
+int nncb_qconv2d_host(nncb_context *ctx, const nncb_conv2d_desc *desc, const void *weights, const int32_t *w_zp,
+                      const float *mult, const float *bias, const uint8_t *lut, const uint8_t *x, const uint8_t *res,
+                      void *y, uint8_t *y2) {
+    CHECK_CTX(ctx);
+    nncb_qconv2d *cv = nullptr;
+    NNCB_TRY(nncb_qconv2d_create(ctx, desc, weights, w_zp, mult, bias, lut, &cv));
+    const size_t in_bytes = (size_t)desc->n * desc->h * desc->w * desc->c;
+    const size_t out_elems = (size_t)desc->n * cv->oh * cv->ow * desc->oc;
+    const size_t out_bytes = out_elems * (desc->f32_out ? 4 : 1);
+    void *dx = nullptr, *dr = nullptr, *dy = nullptr, *dy2 = nullptr;
+    int rc = nncb_malloc(ctx, in_bytes, &dx);
+    if (rc == 0)
+        rc = nncb_malloc(ctx, out_bytes, &dy);
+    if (rc == 0 && desc->has_residual)
+        rc = nncb_malloc(ctx, out_elems, &dr);
+    if (rc == 0 && desc->has_y2)
+        rc = nncb_malloc(ctx, out_elems, &dy2);
+    if (rc == 0)
+        rc = nncb_memcpy_h2d(ctx, dx, x, in_bytes);
+    if (rc == 0 && desc->has_residual)
+        rc = res ? nncb_memcpy_h2d(ctx, dr, res, out_elems) : fail(-EINVAL, "residual input missing");
+    if (rc == 0)
+        rc = nncb_qconv2d_run(ctx, cv, (const uint8_t *)dx, (const uint8_t *)dr, dy, (uint8_t *)dy2);
+    if (rc == 0)
+        rc = nncb_memcpy_d2h(ctx, y, dy, out_bytes);
+    if (rc == 0 && desc->has_y2)
+        rc = y2 ? nncb_memcpy_d2h(ctx, y2, dy2, out_elems) : fail(-EINVAL, "second output missing");
+    if (rc == 0)
+        rc = nncb_check_device_status(ctx);
+    cudaFree(dx);
+    cudaFree(dr);
+    cudaFree(dy);
+    cudaFree(dy2);
+    nncb_qconv2d_destroy(cv);
+    return rc;
+}
+
+} // extern "C"

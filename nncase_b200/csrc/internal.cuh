@@ -1,0 +1,72 @@
+// Shared declarations of the nncase_b200 CUDA library (host side + small device helpers).
+#pragma once
+#include <cerrno>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <cuda_runtime.h>
+#include <string>
+
+#include "../../include/nncase_b200.h"
+
+struct nncb_context {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    bool own_stream = false;
+    uint64_t launches = 0;
+    int sm_count = 148;
+    int *d_status = nullptr;  // device word: 0 ok, else code of the first bounded wait that gave up
+    uint8_t *d_lut = nullptr; // 256-byte scratch table for nncb_requant_u8 / nncb_lut_u8
+};
+
+namespace nncb {
+
+std::string &last_error();
+int fail(int code, const char *fmt, ...);
+
+#define NNCB_CUDA_TRY(expr)                                                                     \
+    do {                                                                                        \
+        cudaError_t e__ = (expr);                                                               \
+        if (e__ != cudaSuccess)                                                                 \
+            return nncb::fail(-EIO, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__),    \
+                              __FILE__, __LINE__);                                              \
+    } while (0)
+
+#define NNCB_TRY(expr)                                                                          \
+    do {                                                                                        \
+        int r__ = (expr);                                                                       \
+        if (r__ < 0)                                                                            \
+            return r__;                                                                         \
+    } while (0)
+
+// Checks the launch that was just enqueued and counts it.
+int after_launch(nncb_context *ctx, const char *what);
+
+inline int conv_out_size(int in, int k, int stride, int dil, int pad_before, int pad_after) {
+    return (in + pad_before + pad_after - ((k - 1) * dil + 1)) / stride + 1;
+}
+
+// Host float arithmetic identical to the device's IEEE operations (this file is compiled
+// with contraction off for host code): the quantize formula of the reference.
+inline int32_t host_quant(float x, float scale, float zp, int32_t lo, int32_t hi);
+
+// ---- device helpers -----------------------------------------------------------------------
+// q = clamp(rint(x / scale + zp), lo, hi): IEEE division, addition and round-half-even, the
+// same three roundings as `nearbyintf(x / scale + bias)` in the reference's quantize.
+__device__ __forceinline__ int quant_dev(float x, float scale, float zp, int lo, int hi) {
+    float v = __fadd_rn(__fdiv_rn(x, scale), zp);
+    int q = __float2int_rn(v);
+    return min(max(q, lo), hi);
+}
+// y = (q - zp) * scale with one rounding per operation.
+__device__ __forceinline__ float dequant_dev(float q, float zp, float scale) {
+    return __fmul_rn(__fsub_rn(q, zp), scale);
+}
+// kernels::detail::clamp = max(min(v, hi), lo)
+__device__ __forceinline__ float clamp_dev(float v, float lo, float hi) {
+    float t = v < hi ? v : hi;
+    return t > lo ? t : lo;
+}
+
+} // namespace nncb

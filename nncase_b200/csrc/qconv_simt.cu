@@ -1,0 +1,103 @@
+// CUDA-core quantized Conv2D: the general path (any stride, dilation, padding, groups --
+// depthwise included -- and channel counts the tensor-core kernel does not take, such as the
+// 3-channel stem). One thread per (output pixel, output channel); consecutive threads own
+// consecutive output channels, so activation loads broadcast within a warp and stores coalesce.
+#include "qconv.cuh"
+
+namespace nncb {
+
+struct SimtGeom {
+    int n, h, w, c, oc, kh, kw, sh, sw, pt, pl, dh, dw, groups, oh, ow, w_signed, x_zp, f32_out;
+};
+
+template <bool W_SIGNED>
+__device__ __forceinline__ int load_w(const void *w, size_t i) {
+    if (W_SIGNED)
+        return (int)reinterpret_cast<const int8_t *>(w)[i];
+    return (int)reinterpret_cast<const uint8_t *>(w)[i];
+}
+
+template <bool W_SIGNED>
+__global__ void __launch_bounds__(256)
+simt_conv_kernel(SimtGeom g, const uint8_t *__restrict__ x, const void *__restrict__ w,
+                 const int32_t *__restrict__ w_zp, EpiParams p, const uint8_t *__restrict__ res,
+                 void *__restrict__ y, uint8_t *__restrict__ y2) {
+    const int gic = g.c / g.groups, goc = g.oc / g.groups;
+    const size_t total = (size_t)g.n * g.oh * g.ow * g.oc;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const int oc = (int)(i % g.oc);
+        const size_t pix = i / g.oc;
+        const int ox = (int)(pix % g.ow);
+        const int oy = (int)((pix / g.ow) % g.oh);
+        const int b = (int)(pix / ((size_t)g.ow * g.oh));
+        const int grp = oc / goc;
+        const int zw = w_zp[oc];
+        const int iy0 = oy * g.sh - g.pt, ix0 = ox * g.sw - g.pl;
+        int acc = 0;
+        const bool vec4 = (gic % 4 == 0) && (g.c % 4 == 0);
+        for (int ky = 0; ky < g.kh; ky++) {
+            const int iy = iy0 + ky * g.dh;
+            if (iy < 0 || iy >= g.h)
+                continue;
+            for (int kx = 0; kx < g.kw; kx++) {
+                const int ix = ix0 + kx * g.dw;
+                if (ix < 0 || ix >= g.w)
+                    continue;
+                const uint8_t *xp = x + (((size_t)b * g.h + iy) * g.w + ix) * g.c + grp * gic;
+                const size_t wo = (((size_t)oc * g.kh + ky) * g.kw + kx) * gic;
+                if (vec4) {
+                    // sum (x - zx)(w - zw) = sum x*w - zx*sum w - zw*sum x + cnt*zx*zw, via dp4a
+                    const uint32_t *xv = reinterpret_cast<const uint32_t *>(xp);
+                    const uint32_t *wv = reinterpret_cast<const uint32_t *>(reinterpret_cast<const uint8_t *>(w) + wo);
+                    int sxw = 0, sx = 0, sw_ = 0;
+                    for (int k = 0; k < gic / 4; k++) {
+                        uint32_t xa = __ldg(xv + k), wa = __ldg(wv + k);
+                        if (W_SIGNED) {
+                            // x unsigned, w signed
+                            asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(sxw) : "r"(xa), "r"(wa), "r"(sxw));
+                            asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(sw_) : "r"(wa), "r"(0x01010101u), "r"(sw_));
+                        } else {
+                            sxw = (int)__dp4a(xa, wa, (unsigned)sxw);
+                            sw_ = (int)__dp4a(wa, 0x01010101u, (unsigned)sw_);
+                        }
+                        sx = (int)__dp4a(xa, 0x01010101u, (unsigned)sx);
+                    }
+                    acc += sxw - g.x_zp * sw_ - zw * sx + gic * g.x_zp * zw;
+                } else {
+                    int s = 0;
+                    for (int ic = 0; ic < gic; ic++)
+                        s += ((int)xp[ic] - g.x_zp) * (load_w<W_SIGNED>(w, wo + ic) - zw);
+                    acc += s;
+                }
+            }
+        }
+        const float mult = p.mult[oc], bias = p.bias[oc];
+        if (g.f32_out) {
+            reinterpret_cast<float *>(y)[i] = epi_real(acc, mult, bias, p.clamp_lo, p.clamp_hi);
+        } else {
+            int q = epi_u8(acc, mult, bias, p, p.has_res ? (int)res[i] : 0);
+            reinterpret_cast<uint8_t *>(y)[i] = (uint8_t)q;
+            if (y2)
+                y2[i] = p.y2_lut[q];
+        }
+    }
+}
+
+int simt_conv_run(nncb_context *ctx, nncb_qconv2d *cv, const uint8_t *x, const uint8_t *res, void *y, uint8_t *y2) {
+    const nncb_conv2d_desc &d = cv->d;
+    SimtGeom g{d.n, d.h, d.w, d.c, d.oc, d.kh, d.kw, d.stride_h, d.stride_w, d.pad_t, d.pad_l, d.dil_h,
+               d.dil_w, d.groups, cv->oh, cv->ow, d.w_signed, d.x_zp, d.f32_out};
+    EpiParams p = make_epi(cv);
+    size_t total = (size_t)d.n * cv->oh * cv->ow * d.oc;
+    size_t blocks = (total + 255) / 256;
+    size_t cap = (size_t)ctx->sm_count * 32;
+    int grid = (int)(blocks < cap ? blocks : cap);
+    if (d.w_signed)
+        simt_conv_kernel<true><<<grid, 256, 0, ctx->stream>>>(g, x, cv->d_w, cv->d_wzp, p, res, y, y2);
+    else
+        simt_conv_kernel<false><<<grid, 256, 0, ctx->stream>>>(g, x, cv->d_w, cv->d_wzp, p, res, y, y2);
+    return after_launch(ctx, "simt_conv");
+}
+
+} // namespace nncb

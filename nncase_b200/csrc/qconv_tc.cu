@@ -1,0 +1,736 @@
+// Quantized Conv2D / MatMul as an implicit GEMM on the 5th-generation tensor cores
+// (tcgen05.mma kind::i8, u8 activations x u8|i8 weights -> s32 in tensor memory).
+//
+//   GEMM view: M = n*oh*ow output pixels, N = output channels, K = kh*kw*c ordered (ky, kx, c).
+//   A (activations, NHWC) is never materialised: each K block of one filter tap is fetched by
+//   TMA -- a plain 2-D tile for 1x1/stride-1 convolutions and MatMul, the im2col tensor-map
+//   mode otherwise (the hardware walks 128 consecutive output pixels, applies the tap offset
+//   and zero-fills the padding). B (weights) is repacked once at plan creation into K-major
+//   rows per N tile.
+//
+//   One persistent CTA per SM, warp-specialised:
+//     warp 0      TMA producer   (one lane) fills a ring of shared-memory stages
+//     warp 1      MMA issuer     (one lane) tcgen05.mma into one of two TMEM accumulators
+//     warps 2..5  epilogue       tcgen05.ld the finished accumulator, requantise, store u8
+//   so the epilogue of tile i overlaps the main loop of tile i+1.
+//
+//   Zero points. The MMA accumulates raw sum(xq*wq); TMA fills padding with 0 (not with the
+//   zero point), so with "valid" = taps inside the image
+//     sum_valid (xq-zx)(wq-zw) = sum xq*wq - zx*sum_valid wq - zw*(sum_valid xq - cnt_valid*zx).
+//   sum_valid wq depends only on the output pixel's border class and the channel: a table
+//   corr[class][oc] built at plan creation. sum_valid xq is per pixel: it comes out of the same
+//   MMA through one extra all-ones weight row per N tile (present only if some zw != 0).
+//
+//   Every wait in the kernel is bounded: when a barrier does not complete within about a second
+//   the role records a code in the context's status word, raises a block-wide abort flag and
+//   all roles leave their loops, free tensor memory and return.
+#include "qconv.cuh"
+#include <vector>
+
+namespace nncb {
+
+// ------------------------------------------------------------------------------------------------
+// plan
+// ------------------------------------------------------------------------------------------------
+enum { MODE_GEMM = 0, MODE_IM2COL = 1 };
+
+struct TcGeom {
+    int mode;
+    int m_total;        // n*oh*ow
+    int oc;             // real output channels
+    int bn;             // output channels per N tile
+    int bn_mma;         // MMA N (bn + 16 when the row-sum column is present), multiple of 16
+    int n_tiles, m_tiles;
+    int kb;             // bytes (= int8 elements) per K block: 32, 64 or 128
+    int c_blocks;       // c / kb
+    int taps;           // kh*kw
+    int kw;
+    int oh, ow;
+    int stride_h, stride_w, pad_t, pad_l, dil_h, dil_w;
+    int has_xsum;       // row-sum column present
+    int x_zp;
+    int c;              // input channels
+    int n_cls_x;        // number of x border classes (corr index = ycls*n_cls_x + xcls)
+    int stages;
+    int tmem_cols;      // allocation (power of two >= 32)
+    int acc_stride;     // TMEM columns between the two accumulators
+    uint32_t idesc;
+    int f32_out;
+};
+
+struct TcPlan {
+    TcGeom g;
+    void *d_wpack = nullptr;       // [n_tiles][bn_mma][K] packed weights
+    int32_t *d_corr = nullptr;     // [n_cls][oc_pad] zx * sum_valid(wq)
+    int32_t *d_cnt = nullptr;      // [n_cls] valid taps * c
+    uint8_t *d_ycls = nullptr;     // [oh]
+    uint8_t *d_xcls = nullptr;     // [ow]
+    int oc_pad = 0;
+    CUtensorMap tmap_b;
+    // The A map depends on the activation pointer; it is rebuilt when the pointer changes.
+    CUtensorMap tmap_a;
+    const void *a_ptr = nullptr;
+    size_t smem_bytes = 0;
+};
+
+typedef CUresult (*PFN_encodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                    CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                    CUtensorMapFloatOOBfill);
+typedef CUresult (*PFN_encodeIm2col)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                     const cuuint64_t *, const int *, const int *, cuuint32_t, cuuint32_t,
+                                     const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static PFN_encodeTiled g_encode_tiled = nullptr;
+static PFN_encodeIm2col g_encode_im2col = nullptr;
+
+// The driver API is reached through the runtime so that the library has no link-time
+// dependency on libcuda and loads on machines without a driver.
+static int load_driver_entry_points() {
+    if (g_encode_tiled && g_encode_im2col)
+        return 0;
+    cudaDriverEntryPointQueryResult qres;
+    void *fn = nullptr;
+    NNCB_CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+    if (!fn || qres != cudaDriverEntryPointSuccess)
+        return fail(-EIO, "cuTensorMapEncodeTiled is not available from this driver");
+    g_encode_tiled = (PFN_encodeTiled)fn;
+    fn = nullptr;
+    NNCB_CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &qres));
+    if (!fn || qres != cudaDriverEntryPointSuccess)
+        return fail(-EIO, "cuTensorMapEncodeIm2col is not available from this driver");
+    g_encode_im2col = (PFN_encodeIm2col)fn;
+    return 0;
+}
+
+static CUtensorMapSwizzle swizzle_for(int kb) {
+    return kb == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (kb == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+}
+
+bool tc_conv_supported(const nncb_conv2d_desc &d, std::string *why) {
+    auto no = [&](const char *m) {
+        if (why)
+            *why = m;
+        return false;
+    };
+    if (d.groups != 1)
+        return no("grouped convolution");
+    if (d.c % 32 != 0)
+        return no("input channels not a multiple of 32");
+    if ((size_t)d.kh * d.kw * d.c > (1u << 20))
+        return no("K too large");
+    if (d.kh > 255 || d.kw > 255)
+        return no("filter too large");
+    const int oh = conv_out_size(d.h, d.kh, d.stride_h, d.dil_h, d.pad_t, d.pad_b);
+    const int ow = conv_out_size(d.w, d.kw, d.stride_w, d.dil_w, d.pad_l, d.pad_r);
+    if ((long long)d.n * oh * ow > 0x7fffffffLL)
+        return no("M too large");
+    // im2col tensor maps hold the corner offsets in 8 bits (4-D tensors).
+    const int upper_w = d.pad_r - (d.kw - 1) * d.dil_w, upper_h = d.pad_b - (d.kh - 1) * d.dil_h;
+    const bool gemm = d.kh == 1 && d.kw == 1 && d.stride_h == 1 && d.stride_w == 1 && d.pad_t == 0 && d.pad_b == 0 &&
+                      d.pad_l == 0 && d.pad_r == 0;
+    if (!gemm) {
+        if (d.pad_l > 128 || d.pad_t > 128 || upper_w < -128 || upper_w > 127 || upper_h < -128 || upper_h > 127)
+            return no("padding / dilation outside the im2col corner range");
+        if (d.stride_h > 8 || d.stride_w > 8)
+            return no("stride > 8");
+        if ((d.kw - 1) * d.dil_w > 255 || (d.kh - 1) * d.dil_h > 255)
+            return no("tap offset > 255");
+        // The hardware derives the output extent from the corners; it must agree with ours.
+        if ((d.w + upper_w + d.pad_l - 1) / d.stride_w + 1 != ow || (d.h + upper_h + d.pad_t - 1) / d.stride_h + 1 != oh)
+            return no("output extent not expressible by im2col corners");
+    }
+    return true;
+}
+
+static int make_tmap_a(TcPlan *tp, const nncb_conv2d_desc &d, const void *x) {
+    const TcGeom &g = tp->g;
+    CUresult r;
+    if (g.mode == MODE_GEMM) {
+        cuuint64_t dims[2] = {(cuuint64_t)d.c, (cuuint64_t)g.m_total};
+        cuuint64_t strides[1] = {(cuuint64_t)d.c};
+        cuuint32_t box[2] = {(cuuint32_t)g.kb, 128};
+        cuuint32_t estr[2] = {1, 1};
+        r = g_encode_tiled(&tp->tmap_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(x), dims, strides, box,
+                           estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(g.kb), CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else {
+        cuuint64_t dims[4] = {(cuuint64_t)d.c, (cuuint64_t)d.w, (cuuint64_t)d.h, (cuuint64_t)d.n};
+        cuuint64_t strides[3] = {(cuuint64_t)d.c, (cuuint64_t)d.c * d.w, (cuuint64_t)d.c * d.w * d.h};
+        int lower[2] = {-d.pad_l, -d.pad_t};
+        int upper[2] = {d.pad_r - (d.kw - 1) * d.dil_w, d.pad_b - (d.kh - 1) * d.dil_h};
+        cuuint32_t estr[4] = {1, (cuuint32_t)d.stride_w, (cuuint32_t)d.stride_h, 1};
+        r = g_encode_im2col(&tp->tmap_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void *>(x), dims, strides, lower,
+                            upper, (cuuint32_t)g.kb, 128, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(g.kb),
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        // Drivers up to CUDA 13.1 set a descriptor bit that misbehaves for tensors smaller than
+        // 128 KiB in im2col mode; clearing bit 21 of the second 64-bit word is the published
+        // remedy (CUTLASS does the same when it encodes im2col maps).
+        int drv = 0;
+        cudaDriverGetVersion(&drv);
+        if (r == CUDA_SUCCESS && drv <= 13010 && (size_t)d.c * d.w * d.h * d.n < 131072)
+            reinterpret_cast<uint64_t *>(&tp->tmap_a)[1] &= ~(1ull << 21);
+    }
+    if (r != CUDA_SUCCESS)
+        return fail(-EIO, "encoding the activation tensor map failed (CUresult %d)", (int)r);
+    tp->a_ptr = x;
+    return 0;
+}
+
+// ------------------------------------------------------------------------------------------------
+// device side
+// ------------------------------------------------------------------------------------------------
+namespace dev {
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok)
+                 : "r"(bar), "r"(parity)
+                 : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded wait. Returns false when the block is aborting or the wait ran out (about 1 s);
+// in the latter case it records `code` in the status word and raises the abort flag.
+__device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code) {
+    if (mbar_try(bar, parity))
+        return true;
+    const uint64_t t0 = globaltimer_ns();
+    for (uint32_t it = 1;; it++) {
+        if (mbar_try(bar, parity))
+            return true;
+        if ((it & 63) == 0) {
+            if (*abort_flag)
+                return false;
+            if (globaltimer_ns() - t0 > 1000000000ull) {
+                atomicCAS(status, 0, code);
+                *abort_flag = 1;
+                __threadfence_block();
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c, int w,
+                                                   int h, int n, uint16_t off_w, uint16_t off_h) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes"
+                 " [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h)
+                 : "memory");
+}
+
+// K-major shared-memory operand descriptor: rows of `kb` bytes, 8-row swizzle atoms `8*kb`
+// bytes apart (stride byte offset), swizzle mode matching the row length.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, int kb) {
+    const uint64_t layout = kb == 128 ? 2 : (kb == 64 ? 4 : 6);
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;                       // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)((8 * kb) >> 4) << 32;         // stride byte offset
+    d |= (uint64_t)1 << 46;                       // descriptor version of this architecture
+    d |= layout << 61;
+    return d;
+}
+
+__device__ __forceinline__ void mma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum)
+                 : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+                 "tcgen05.wait::ld.sync.aligned;"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr)
+                 : "memory");
+}
+// The wait is part of the same statement so that no use of the result can be scheduled before it.
+__device__ __forceinline__ void tmem_ld1(uint32_t taddr, int &r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];\ntcgen05.wait::ld.sync.aligned;"
+                 : "=r"(r)
+                 : "r"(taddr)
+                 : "memory");
+}
+
+} // namespace dev
+
+struct TcArgs {
+    TcGeom g;
+    EpiParams p;
+    const int32_t *corr;  // [n_cls][oc_pad]
+    const int32_t *cnt;   // [n_cls]
+    const uint8_t *ycls, *xcls;
+    const int32_t *w_zp;  // [oc]
+    int oc_pad;
+    const uint8_t *res;
+    void *y;
+    uint8_t *y2;
+    int *status;
+};
+
+enum { ERR_PRODUCER = 101, ERR_MMA_FULL = 102, ERR_MMA_ACC = 103, ERR_EPILOGUE = 104 };
+
+constexpr int TC_THREADS = 192;
+constexpr int MAX_STAGES = 8;
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
+tc_conv_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const TcArgs a) {
+    using namespace dev;
+    extern __shared__ uint8_t smem_raw[];
+    const TcGeom &g = a.g;
+    // stage ring, 1024-byte aligned (required by the 128-byte swizzle)
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t a_stage_bytes = 128u * g.kb;
+    const uint32_t b_stage_bytes = (uint32_t)g.bn_mma * g.kb;
+    // keep every stage's A and B tile 1024-byte aligned
+    const uint32_t b_stage_pitch = (b_stage_bytes + 1023u) & ~1023u;
+    const uint32_t stage_pitch = a_stage_bytes + b_stage_pitch; // a_stage_bytes is a multiple of 1024 for kb >= 8
+
+    __shared__ __align__(8) uint64_t bar_full[MAX_STAGES], bar_empty[MAX_STAGES], bar_acc_full[2], bar_acc_empty[2];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ volatile int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k_blocks = g.taps * g.c_blocks;
+    const int total_tiles = g.m_tiles * g.n_tiles;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < g.stages; s++) {
+            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_empty[s]), 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(smem_u32(&bar_acc_full[b]), 1);
+            mbar_init(smem_u32(&bar_acc_empty[b]), 4);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                     "r"((uint32_t)g.tmem_cols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp == 0) {
+        // ------------------------------- TMA producer -------------------------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int mt = tile % g.m_tiles, nt = tile / g.m_tiles;
+                const int m0 = mt * 128;
+                int cw = 0, chh = 0, cn = 0;
+                if (g.mode == MODE_IM2COL) {
+                    const int q = m0 % g.ow, pp = (m0 / g.ow) % g.oh;
+                    cn = m0 / (g.ow * g.oh);
+                    cw = q * g.stride_w - g.pad_l;
+                    chh = pp * g.stride_h - g.pad_t;
+                }
+                for (int kbi = 0; kbi < k_blocks; kbi++) {
+                    if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1, &abort_flag, a.status, ERR_PRODUCER)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t full = smem_u32(&bar_full[stage]);
+                    const uint32_t sa = smem_base + stage * stage_pitch, sb = sa + a_stage_bytes;
+                    mbar_expect_tx(full, a_stage_bytes + b_stage_bytes);
+                    const int tap = kbi / g.c_blocks, cb = kbi % g.c_blocks;
+                    if (g.mode == MODE_GEMM) {
+                        tma_load_2d(sa, &tmap_a, full, cb * g.kb, m0);
+                    } else {
+                        const int ky = tap / g.kw, kx = tap % g.kw;
+                        tma_load_im2col_4d(sa, &tmap_a, full, cb * g.kb, cw, chh, cn, (uint16_t)(kx * g.dil_w),
+                                           (uint16_t)(ky * g.dil_h));
+                    }
+                    tma_load_2d(sb, &tmap_b, full, kbi * g.kb, nt * g.bn_mma);
+                    if (++stage == (uint32_t)g.stages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------- MMA issuer ---------------------------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            uint32_t acc_phase[2] = {0, 0};
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, it++) {
+                const int buf = it & 1;
+                if (!mbar_wait(smem_u32(&bar_acc_empty[buf]), acc_phase[buf] ^ 1, &abort_flag, a.status, ERR_MMA_ACC)) {
+                    ok = false;
+                    break;
+                }
+                acc_phase[buf] ^= 1;
+                fence_after_sync();
+                const uint32_t tmem_d = tmem_base + buf * g.acc_stride;
+                for (int kbi = 0; kbi < k_blocks; kbi++) {
+                    if (!mbar_wait(smem_u32(&bar_full[stage]), phase, &abort_flag, a.status, ERR_MMA_FULL)) {
+                        ok = false;
+                        break;
+                    }
+                    fence_after_sync();
+                    const uint32_t sa = smem_base + stage * stage_pitch, sb = sa + a_stage_bytes;
+                    const uint64_t da = smem_desc(sa, g.kb), db = smem_desc(sb, g.kb);
+                    const int kk = g.kb / 32;
+                    for (int k = 0; k < kk; k++)
+                        mma_i8(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), g.idesc, (kbi | k) != 0);
+                    mma_commit(smem_u32(&bar_empty[stage])); // frees the stage when these MMAs retire
+                    if (++stage == (uint32_t)g.stages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (ok)
+                    mma_commit(smem_u32(&bar_acc_full[buf]));
+            }
+        }
+    } else {
+        // ------------------------------- epilogue -----------------------------------
+        const int lane_group = warp & 3; // TMEM lanes 32*lane_group .. +31 are this warp's
+        const int row = lane_group * 32 + lane;
+        uint32_t acc_phase[2] = {0, 0};
+        int it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, it++) {
+            const int buf = it & 1;
+            const int mt = tile % g.m_tiles, nt = tile / g.m_tiles;
+            const int m = mt * 128 + row;
+            const bool row_ok = m < g.m_total;
+            // border class of this output pixel
+            int cls = 0;
+            if (g.mode == MODE_IM2COL && row_ok) {
+                const int ox = m % g.ow, oy = (m / g.ow) % g.oh;
+                cls = (int)a.ycls[oy] * g.n_cls_x + (int)a.xcls[ox];
+            }
+            if (!mbar_wait(smem_u32(&bar_acc_full[buf]), acc_phase[buf], &abort_flag, a.status, ERR_EPILOGUE)) {
+                ok = false;
+                break;
+            }
+            acc_phase[buf] ^= 1;
+            fence_after_sync();
+            const uint32_t tbase = tmem_base + ((uint32_t)(lane_group * 32) << 16) + buf * g.acc_stride;
+            int rsum = 0; // sum_valid xq - cnt_valid * zx
+            if (g.has_xsum) {
+                int xs;
+                tmem_ld1(tbase + g.bn, xs);
+                rsum = xs - a.cnt[cls] * g.x_zp;
+            }
+            const int32_t *corr = a.corr + (size_t)cls * a.oc_pad;
+            const int oc0 = nt * g.bn;
+            for (int c0 = 0; c0 < g.bn; c0 += 16) {
+                int v[16];
+                __syncwarp();
+                tmem_ld16(tbase + c0, v);
+                if (!row_ok || oc0 + c0 >= g.oc)
+                    continue;
+                const size_t obase = (size_t)m * g.oc + oc0 + c0;
+                if (g.f32_out) {
+                    float *yo = reinterpret_cast<float *>(a.y) + obase;
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        const int oc = oc0 + c0 + j;
+                        if (oc < g.oc) {
+                            int acc = v[j] - corr[oc] - a.w_zp[oc] * rsum;
+                            yo[j] = epi_real(acc, a.p.mult[oc], a.p.bias[oc], a.p.clamp_lo, a.p.clamp_hi);
+                        }
+                    }
+                    continue;
+                }
+                uint32_t pk[4] = {0, 0, 0, 0}, pk2[4] = {0, 0, 0, 0};
+                const bool full16 = (oc0 + c0 + 16 <= g.oc) && ((obase & 15) == 0);
+                uint32_t rs[4] = {0, 0, 0, 0};
+                if (a.p.has_res) {
+                    if (full16) {
+                        uint4 r4 = *reinterpret_cast<const uint4 *>(a.res + obase);
+                        rs[0] = r4.x, rs[1] = r4.y, rs[2] = r4.z, rs[3] = r4.w;
+                    } else {
+                        for (int j = 0; j < 16; j++)
+                            if (oc0 + c0 + j < g.oc)
+                                rs[j >> 2] |= (uint32_t)a.res[obase + j] << (8 * (j & 3));
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    const int oc = oc0 + c0 + j;
+                    if (oc < g.oc) {
+                        int acc = v[j] - corr[oc] - a.w_zp[oc] * rsum;
+                        int q = epi_u8(acc, a.p.mult[oc], a.p.bias[oc], a.p, (int)((rs[j >> 2] >> (8 * (j & 3))) & 255));
+                        pk[j >> 2] |= (uint32_t)q << (8 * (j & 3));
+                        if (a.y2)
+                            pk2[j >> 2] |= (uint32_t)a.p.y2_lut[q] << (8 * (j & 3));
+                    }
+                }
+                uint8_t *yo = reinterpret_cast<uint8_t *>(a.y) + obase;
+                if (full16) {
+                    *reinterpret_cast<uint4 *>(yo) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    if (a.y2)
+                        *reinterpret_cast<uint4 *>(a.y2 + obase) = make_uint4(pk2[0], pk2[1], pk2[2], pk2[3]);
+                } else {
+                    for (int j = 0; j < 16; j++)
+                        if (oc0 + c0 + j < g.oc) {
+                            yo[j] = (uint8_t)(pk[j >> 2] >> (8 * (j & 3)));
+                            if (a.y2)
+                                a.y2[obase + j] = (uint8_t)(pk2[j >> 2] >> (8 * (j & 3)));
+                        }
+                }
+            }
+            // this accumulator may be overwritten once all four epilogue warps are done reading
+            fence_before_sync();
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(smem_u32(&bar_acc_empty[buf]));
+        }
+    }
+
+    // teardown: everyone arrives here, also after an abort
+    if (abort_flag) {
+        // give loads that are still in flight time to land before shared memory is released
+        const uint64_t t0 = dev::globaltimer_ns();
+        while (dev::globaltimer_ns() - t0 < 200000ull) {
+        }
+    }
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)g.tmem_cols)
+                     : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side: plan creation
+// ------------------------------------------------------------------------------------------------
+static int pick_bn(int oc, bool xsum) {
+    // N tile: as wide as the layer allows up to 128 (+16 for the row-sum column), multiple of 16
+    int bn = oc >= 128 ? 128 : ((oc + 15) / 16) * 16;
+    (void)xsum;
+    return bn;
+}
+
+int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, const int32_t *wzp_host) {
+    NNCB_TRY(load_driver_entry_points());
+    const nncb_conv2d_desc &d = cv->d;
+    TcPlan *tp = new TcPlan();
+    cv->tc = tp;
+    TcGeom &g = tp->g;
+    const bool gemm = d.kh == 1 && d.kw == 1 && d.stride_h == 1 && d.stride_w == 1 && d.pad_t == 0 && d.pad_b == 0 &&
+                      d.pad_l == 0 && d.pad_r == 0;
+    g.mode = gemm ? MODE_GEMM : MODE_IM2COL;
+    g.oh = cv->oh, g.ow = cv->ow;
+    g.m_total = d.n * cv->oh * cv->ow;
+    g.oc = d.oc;
+    bool any_zw = false;
+    for (int i = 0; i < d.oc && wzp_host; i++)
+        any_zw |= wzp_host[i] != 0;
+    g.has_xsum = any_zw ? 1 : 0;
+    g.bn = pick_bn(d.oc, any_zw);
+    g.bn_mma = g.bn + (any_zw ? 16 : 0);
+    g.n_tiles = (d.oc + g.bn - 1) / g.bn;
+    g.m_tiles = (g.m_total + 127) / 128;
+    g.kb = d.c % 128 == 0 ? 128 : (d.c % 64 == 0 ? 64 : 32);
+    g.c_blocks = d.c / g.kb;
+    g.taps = d.kh * d.kw;
+    g.kw = d.kw;
+    g.stride_h = d.stride_h, g.stride_w = d.stride_w, g.pad_t = d.pad_t, g.pad_l = d.pad_l;
+    g.dil_h = d.dil_h, g.dil_w = d.dil_w;
+    g.x_zp = d.x_zp;
+    g.c = d.c;
+    g.f32_out = d.f32_out;
+    g.acc_stride = g.bn_mma;
+    int cols = 32;
+    while (cols < 2 * g.acc_stride)
+        cols *= 2;
+    g.tmem_cols = cols;
+    g.idesc = (2u << 4) | (0u << 7) | ((d.w_signed ? 1u : 0u) << 10) | ((uint32_t)(g.bn_mma >> 3) << 17) |
+              ((uint32_t)(128 >> 4) << 24);
+    const uint32_t a_stage = 128u * g.kb, b_pitch = ((uint32_t)g.bn_mma * g.kb + 1023u) & ~1023u;
+    int stages = (int)((200u * 1024u) / (a_stage + b_pitch));
+    if (stages > MAX_STAGES)
+        stages = MAX_STAGES;
+    if (stages < 2)
+        return fail(-ENOSYS, "tcgen05 conv: tile does not fit shared memory");
+    g.stages = stages;
+    // More than half of an SM's shared memory, so exactly one CTA (and one TMEM allocation) per SM.
+    tp->smem_bytes = (size_t)stages * (a_stage + b_pitch) + 1024;
+    if (tp->smem_bytes < 120 * 1024)
+        tp->smem_bytes = 120 * 1024;
+
+    // ---- weights: [n_tiles][bn_mma][K], K ordered (ky, kx, c) = the OHWI row as given ----
+    const size_t K = (size_t)d.kh * d.kw * d.c;
+    std::vector<uint8_t> wp((size_t)g.n_tiles * g.bn_mma * K, 0);
+    const uint8_t *wsrc = reinterpret_cast<const uint8_t *>(w_host);
+    for (int nt = 0; nt < g.n_tiles; nt++) {
+        for (int r = 0; r < g.bn; r++) {
+            int oc = nt * g.bn + r;
+            if (oc < d.oc)
+                memcpy(&wp[((size_t)nt * g.bn_mma + r) * K], wsrc + (size_t)oc * K, K);
+        }
+        if (any_zw)
+            memset(&wp[((size_t)nt * g.bn_mma + g.bn) * K], 1, K); // all-ones row: per-pixel sum of xq
+    }
+    NNCB_CUDA_TRY(cudaMalloc(&tp->d_wpack, wp.size()));
+    NNCB_CUDA_TRY(cudaMemcpyAsync(tp->d_wpack, wp.data(), wp.size(), cudaMemcpyHostToDevice, ctx->stream));
+    NNCB_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    {
+        cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)g.n_tiles * g.bn_mma};
+        cuuint64_t strides[1] = {(cuuint64_t)K};
+        cuuint32_t box[2] = {(cuuint32_t)g.kb, (cuuint32_t)g.bn_mma};
+        cuuint32_t estr[2] = {1, 1};
+        CUresult r = g_encode_tiled(&tp->tmap_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, tp->d_wpack, dims, strides, box, estr,
+                                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(g.kb), CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS)
+            return fail(-EIO, "encoding the weight tensor map failed (CUresult %d)", (int)r);
+    }
+
+    // ---- border classes: distinct ranges of valid taps along y and along x ----
+    auto classes = [](int out, int in, int k, int stride, int pad, int dil, std::vector<uint8_t> &cls,
+                      std::vector<std::pair<int, int>> &ranges) -> bool {
+        cls.resize(out);
+        for (int o = 0; o < out; o++) {
+            int origin = o * stride - pad;
+            int lo = 0, hi = k;
+            while (lo < k && origin + lo * dil < 0)
+                lo++;
+            while (hi > lo && origin + (hi - 1) * dil >= in)
+                hi--;
+            std::pair<int, int> r(lo, hi);
+            size_t idx = 0;
+            for (; idx < ranges.size(); idx++)
+                if (ranges[idx] == r)
+                    break;
+            if (idx == ranges.size())
+                ranges.push_back(r);
+            if (idx > 255)
+                return false;
+            cls[o] = (uint8_t)idx;
+        }
+        return true;
+    };
+    std::vector<uint8_t> ycls, xcls;
+    std::vector<std::pair<int, int>> yr, xr;
+    if (!classes(cv->oh, d.h, d.kh, d.stride_h, d.pad_t, d.dil_h, ycls, yr) ||
+        !classes(cv->ow, d.w, d.kw, d.stride_w, d.pad_l, d.dil_w, xcls, xr))
+        return fail(-ENOSYS, "tcgen05 conv: too many border classes");
+    g.n_cls_x = (int)xr.size();
+    const int n_cls = (int)(yr.size() * xr.size());
+    tp->oc_pad = g.n_tiles * g.bn;
+    // per-tap weight sums, then per-class sums
+    std::vector<int64_t> tapsum((size_t)d.oc * g.taps, 0);
+    for (int oc = 0; oc < d.oc; oc++)
+        for (int t = 0; t < g.taps; t++) {
+            int64_t s = 0;
+            const uint8_t *p = wsrc + ((size_t)oc * g.taps + t) * d.c;
+            for (int c = 0; c < d.c; c++)
+                s += d.w_signed ? (int)(int8_t)p[c] : (int)p[c];
+            tapsum[(size_t)oc * g.taps + t] = s;
+        }
+    std::vector<int32_t> corr((size_t)n_cls * tp->oc_pad, 0), cnt(n_cls, 0);
+    for (size_t yc = 0; yc < yr.size(); yc++)
+        for (size_t xc = 0; xc < xr.size(); xc++) {
+            const int cls = (int)(yc * xr.size() + xc);
+            cnt[cls] = (yr[yc].second - yr[yc].first) * (xr[xc].second - xr[xc].first) * d.c;
+            for (int oc = 0; oc < d.oc; oc++) {
+                int64_t s = 0;
+                for (int ky = yr[yc].first; ky < yr[yc].second; ky++)
+                    for (int kx = xr[xc].first; kx < xr[xc].second; kx++)
+                        s += tapsum[(size_t)oc * g.taps + ky * d.kw + kx];
+                corr[(size_t)cls * tp->oc_pad + oc] = (int32_t)(s * d.x_zp);
+            }
+        }
+    NNCB_CUDA_TRY(cudaMalloc(&tp->d_corr, corr.size() * 4));
+    NNCB_CUDA_TRY(cudaMalloc(&tp->d_cnt, cnt.size() * 4));
+    NNCB_CUDA_TRY(cudaMalloc(&tp->d_ycls, ycls.size()));
+    NNCB_CUDA_TRY(cudaMalloc(&tp->d_xcls, xcls.size()));
+    NNCB_CUDA_TRY(cudaMemcpyAsync(tp->d_corr, corr.data(), corr.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+    NNCB_CUDA_TRY(cudaMemcpyAsync(tp->d_cnt, cnt.data(), cnt.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+    NNCB_CUDA_TRY(cudaMemcpyAsync(tp->d_ycls, ycls.data(), ycls.size(), cudaMemcpyHostToDevice, ctx->stream));
+    NNCB_CUDA_TRY(cudaMemcpyAsync(tp->d_xcls, xcls.data(), xcls.size(), cudaMemcpyHostToDevice, ctx->stream));
+    NNCB_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    NNCB_CUDA_TRY(cudaFuncSetAttribute(tc_conv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tp->smem_bytes));
+    return 0;
+}
+
+void tc_conv_destroy(nncb_qconv2d *cv) {
+    TcPlan *tp = cv->tc;
+    if (!tp)
+        return;
+    cudaFree(tp->d_wpack);
+    cudaFree(tp->d_corr);
+    cudaFree(tp->d_cnt);
+    cudaFree(tp->d_ycls);
+    cudaFree(tp->d_xcls);
+    delete tp;
+    cv->tc = nullptr;
+}
+
+int tc_conv_run(nncb_context *ctx, nncb_qconv2d *cv, const uint8_t *x, const uint8_t *res, void *y, uint8_t *y2) {
+    TcPlan *tp = cv->tc;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) != 0)
+        return fail(-EINVAL, "tcgen05 conv: activation pointer must be 16-byte aligned");
+    if (tp->a_ptr != x)
+        NNCB_TRY(make_tmap_a(tp, cv->d, x));
+    TcArgs a;
+    a.g = tp->g;
+    a.p = make_epi(cv);
+    a.corr = tp->d_corr;
+    a.cnt = tp->d_cnt;
+    a.ycls = tp->d_ycls;
+    a.xcls = tp->d_xcls;
+    a.w_zp = cv->d_wzp;
+    a.oc_pad = tp->oc_pad;
+    a.res = res;
+    a.y = y;
+    a.y2 = y2;
+    a.status = ctx->d_status;
+    const int tiles = tp->g.m_tiles * tp->g.n_tiles;
+    const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+    tc_conv_kernel<<<grid, TC_THREADS, tp->smem_bytes, ctx->stream>>>(tp->tmap_a, tp->tmap_b, a);
+    return after_launch(ctx, "tc_conv");
+}
+
+} // namespace nncb

@@ -1,0 +1,470 @@
+// HBM-streaming kernels: Quantize / Dequantize, layout changes, element-wise add, table
+// look-up, pooling. All are bandwidth-bound: 128-bit loads and stores, grid sized as a
+// multiple of the SM count with a grid-stride loop.
+#include "internal.cuh"
+
+namespace nncb {
+
+static inline int stream_grid(const nncb_context *ctx, size_t work_items, int threads) {
+    size_t blocks = (work_items + threads - 1) / threads;
+    size_t cap = (size_t)ctx->sm_count * 16;
+    if (blocks > cap)
+        blocks = cap;
+    if (blocks < 1)
+        blocks = 1;
+    return (int)blocks;
+}
+
+// ---- quantize -----------------------------------------------------------------------------
+template <typename Q> struct qlimits;
+template <> struct qlimits<uint8_t> { static constexpr int lo = 0, hi = 255; };
+template <> struct qlimits<int8_t> { static constexpr int lo = -128, hi = 127; };
+template <> struct qlimits<int16_t> { static constexpr int lo = -32768, hi = 32767; };
+
+// 16 elements per thread per iteration: four float4 loads, one 16-byte (8-bit types) or two
+// 16-byte (16-bit type) stores. `vec_ok` is false when a pointer is not 16-byte aligned.
+template <typename Q>
+__global__ void __launch_bounds__(256) quantize_kernel(const float *__restrict__ in, Q *__restrict__ out,
+                                                       size_t n, float scale, float zp, bool vec_ok) {
+    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t nthreads = (size_t)gridDim.x * blockDim.x;
+    const size_t nvec = vec_ok ? n / 16 : 0;
+    for (size_t v = tid; v < nvec; v += nthreads) {
+        const float4 *p = reinterpret_cast<const float4 *>(in) + v * 4;
+        float4 f[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+            f[i] = __ldcs(p + i);
+        alignas(16) Q q[16];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            q[i * 4 + 0] = (Q)quant_dev(f[i].x, scale, zp, qlimits<Q>::lo, qlimits<Q>::hi);
+            q[i * 4 + 1] = (Q)quant_dev(f[i].y, scale, zp, qlimits<Q>::lo, qlimits<Q>::hi);
+            q[i * 4 + 2] = (Q)quant_dev(f[i].z, scale, zp, qlimits<Q>::lo, qlimits<Q>::hi);
+            q[i * 4 + 3] = (Q)quant_dev(f[i].w, scale, zp, qlimits<Q>::lo, qlimits<Q>::hi);
+        }
+        uint4 *o = reinterpret_cast<uint4 *>(out + v * 16);
+        const uint4 *qs = reinterpret_cast<const uint4 *>(q);
+#pragma unroll
+        for (int i = 0; i < (int)(sizeof(Q) * 16 / 16); i++)
+            __stcs(o + i, qs[i]);
+    }
+    for (size_t i = nvec * 16 + tid; i < n; i += nthreads)
+        out[i] = (Q)quant_dev(in[i], scale, zp, qlimits<Q>::lo, qlimits<Q>::hi);
+}
+
+template <typename Q>
+__global__ void __launch_bounds__(256) dequantize_kernel(const Q *__restrict__ in, float *__restrict__ out,
+                                                         size_t n, float scale, float zp, bool vec_ok) {
+    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t nthreads = (size_t)gridDim.x * blockDim.x;
+    constexpr int PER = 16 / sizeof(Q); // elements per 16-byte load
+    const size_t nvec = vec_ok ? n / PER : 0;
+    for (size_t v = tid; v < nvec; v += nthreads) {
+        uint4 raw = __ldcs(reinterpret_cast<const uint4 *>(in) + v);
+        alignas(16) Q q[PER];
+        *reinterpret_cast<uint4 *>(q) = raw;
+        float4 *o = reinterpret_cast<float4 *>(out + v * PER);
+#pragma unroll
+        for (int i = 0; i < PER / 4; i++) {
+            float4 f;
+            f.x = dequant_dev((float)q[i * 4 + 0], zp, scale);
+            f.y = dequant_dev((float)q[i * 4 + 1], zp, scale);
+            f.z = dequant_dev((float)q[i * 4 + 2], zp, scale);
+            f.w = dequant_dev((float)q[i * 4 + 3], zp, scale);
+            __stcs(o + i, f);
+        }
+    }
+    for (size_t i = nvec * PER + tid; i < n; i += nthreads)
+        out[i] = dequant_dev((float)in[i], zp, scale);
+}
+
+static inline bool aligned16(const void *a, const void *b) {
+    return ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15) == 0;
+}
+
+int quantize(nncb_context *ctx, const float *in, void *out, size_t n, float scale, int32_t zp, int qtype) {
+    if (n == 0)
+        return 0;
+    if (!in || !out)
+        return fail(-EINVAL, "quantize: null pointer");
+    const int threads = 256;
+    const int grid = stream_grid(ctx, (n + 15) / 16, threads);
+    const bool v = aligned16(in, out);
+    switch (qtype) {
+    case NNCB_U8:
+        quantize_kernel<uint8_t><<<grid, threads, 0, ctx->stream>>>(in, (uint8_t *)out, n, scale, (float)zp, v);
+        break;
+    case NNCB_I8:
+        quantize_kernel<int8_t><<<grid, threads, 0, ctx->stream>>>(in, (int8_t *)out, n, scale, (float)zp, v);
+        break;
+    case NNCB_I16:
+        quantize_kernel<int16_t><<<grid, threads, 0, ctx->stream>>>(in, (int16_t *)out, n, scale, (float)zp, v);
+        break;
+    default:
+        return fail(-ENOSYS, "quantize: unsupported target type %d", qtype);
+    }
+    return after_launch(ctx, "quantize");
+}
+
+int dequantize(nncb_context *ctx, const void *in, float *out, size_t n, float scale, int32_t zp, int qtype) {
+    if (n == 0)
+        return 0;
+    if (!in || !out)
+        return fail(-EINVAL, "dequantize: null pointer");
+    const int threads = 256;
+    const bool v = aligned16(in, out);
+    switch (qtype) {
+    case NNCB_U8:
+        dequantize_kernel<uint8_t><<<stream_grid(ctx, (n + 15) / 16, threads), threads, 0, ctx->stream>>>(
+            (const uint8_t *)in, out, n, scale, (float)zp, v);
+        break;
+    case NNCB_I8:
+        dequantize_kernel<int8_t><<<stream_grid(ctx, (n + 15) / 16, threads), threads, 0, ctx->stream>>>(
+            (const int8_t *)in, out, n, scale, (float)zp, v);
+        break;
+    case NNCB_I16:
+        dequantize_kernel<int16_t><<<stream_grid(ctx, (n + 7) / 8, threads), threads, 0, ctx->stream>>>(
+            (const int16_t *)in, out, n, scale, (float)zp, v);
+        break;
+    default:
+        return fail(-ENOSYS, "dequantize: unsupported source type %d", qtype);
+    }
+    return after_launch(ctx, "dequantize");
+}
+
+// ---- NCHW f32 -> NHWC u8 (quantize + transpose) ----------------------------------------------
+// Tile of 32 channels x 64 pixels through shared memory: global reads run along pixels
+// (contiguous in NCHW), global writes along channels (contiguous in NHWC).
+template <bool QUANT>
+__global__ void __launch_bounds__(256)
+nchw_to_nhwc_kernel(const void *__restrict__ in_, uint8_t *__restrict__ out, int c, int hw, int c_pad,
+                    float scale, float zp) {
+    __shared__ uint8_t tile[64][33];
+    const int n = blockIdx.z;
+    const int p0 = blockIdx.x * 64, c0 = blockIdx.y * 32;
+    const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6; // 64 x 4
+    const uint8_t zq = (uint8_t)min(max(__float2int_rn(zp), 0), 255);
+    for (int cc = ty; cc < 32; cc += 4) {
+        int ch = c0 + cc, p = p0 + tx;
+        uint8_t q = zq;
+        if (ch < c && p < hw) {
+            size_t idx = ((size_t)n * c + ch) * hw + p;
+            if (QUANT)
+                q = (uint8_t)quant_dev(__ldcs(reinterpret_cast<const float *>(in_) + idx), scale, zp, 0, 255);
+            else
+                q = reinterpret_cast<const uint8_t *>(in_)[idx];
+        }
+        tile[tx][cc] = q;
+    }
+    __syncthreads();
+    const int wc = threadIdx.x & 31, wp = threadIdx.x >> 5; // 32 channels x 8 pixels
+    for (int pp = wp; pp < 64; pp += 8) {
+        int ch = c0 + wc, p = p0 + pp;
+        if (ch < c_pad && p < hw)
+            out[((size_t)n * hw + p) * c_pad + ch] = tile[pp][wc];
+    }
+}
+
+// Few channels (c_pad == 4, c <= 4): one thread per pixel, one 32-bit store.
+__global__ void __launch_bounds__(256)
+quantize_nchw_to_nhwc4_kernel(const float *__restrict__ in, uint32_t *__restrict__ out, int c, size_t hw,
+                              size_t total_pix, float scale, float zp) {
+    const uint32_t zq = (uint32_t)min(max(__float2int_rn(zp), 0), 255);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total_pix;
+         i += (size_t)gridDim.x * blockDim.x) {
+        size_t n = i / hw, p = i % hw;
+        uint32_t word = 0;
+#pragma unroll
+        for (int ch = 0; ch < 4; ch++) {
+            uint32_t q = zq;
+            if (ch < c)
+                q = (uint32_t)quant_dev(__ldcs(in + (n * c + ch) * hw + p), scale, zp, 0, 255);
+            word |= q << (8 * ch);
+        }
+        out[i] = word;
+    }
+}
+
+int quantize_nchw_to_nhwc_u8(nncb_context *ctx, const float *in, uint8_t *out, int n, int c, int h, int w,
+                             int c_pad, float scale, int32_t zp) {
+    if (n <= 0 || c <= 0 || h <= 0 || w <= 0 || c_pad < c)
+        return fail(-EINVAL, "quantize_nchw_to_nhwc_u8: bad shape");
+    const int hw = h * w;
+    if (c_pad == 4 && (reinterpret_cast<uintptr_t>(out) & 3) == 0) {
+        size_t total = (size_t)n * hw;
+        quantize_nchw_to_nhwc4_kernel<<<stream_grid(ctx, total, 256), 256, 0, ctx->stream>>>(
+            in, reinterpret_cast<uint32_t *>(out), c, (size_t)hw, total, scale, (float)zp);
+        return after_launch(ctx, "quantize_nchw_to_nhwc4");
+    }
+    dim3 grid((hw + 63) / 64, (c_pad + 31) / 32, n);
+    nchw_to_nhwc_kernel<true><<<grid, 256, 0, ctx->stream>>>(in, out, c, hw, c_pad, scale, (float)zp);
+    return after_launch(ctx, "quantize_nchw_to_nhwc");
+}
+
+int nchw_to_nhwc_u8(nncb_context *ctx, const uint8_t *in, uint8_t *out, int n, int c, int h, int w) {
+    if (n <= 0 || c <= 0 || h <= 0 || w <= 0)
+        return fail(-EINVAL, "nchw_to_nhwc_u8: bad shape");
+    const int hw = h * w;
+    dim3 grid((hw + 63) / 64, (c + 31) / 32, n);
+    nchw_to_nhwc_kernel<false><<<grid, 256, 0, ctx->stream>>>(in, out, c, hw, c, 1.f, 0.f);
+    return after_launch(ctx, "nchw_to_nhwc_u8");
+}
+
+// ---- NHWC u8 -> NCHW (f32 dequantized, or u8) ---------------------------------------------------
+template <bool DEQUANT>
+__global__ void __launch_bounds__(256)
+nhwc_to_nchw_kernel(const uint8_t *__restrict__ in, void *__restrict__ out_, int c, int hw, float scale, float zp) {
+    __shared__ uint8_t tile[64][33];
+    const int n = blockIdx.z;
+    const int p0 = blockIdx.x * 64, c0 = blockIdx.y * 32;
+    const int wc = threadIdx.x & 31, wp = threadIdx.x >> 5;
+    for (int pp = wp; pp < 64; pp += 8) {
+        int ch = c0 + wc, p = p0 + pp;
+        tile[pp][wc] = (ch < c && p < hw) ? in[((size_t)n * hw + p) * c + ch] : 0;
+    }
+    __syncthreads();
+    const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
+    for (int cc = ty; cc < 32; cc += 4) {
+        int ch = c0 + cc, p = p0 + tx;
+        if (ch < c && p < hw) {
+            size_t idx = ((size_t)n * c + ch) * hw + p;
+            if (DEQUANT)
+                __stcs(reinterpret_cast<float *>(out_) + idx, dequant_dev((float)tile[tx][cc], zp, scale));
+            else
+                reinterpret_cast<uint8_t *>(out_)[idx] = tile[tx][cc];
+        }
+    }
+}
+
+int dequantize_nhwc_to_nchw_f32(nncb_context *ctx, const uint8_t *in, float *out, int n, int h, int w, int c,
+                                float scale, int32_t zp) {
+    if (n <= 0 || c <= 0 || h <= 0 || w <= 0)
+        return fail(-EINVAL, "dequantize_nhwc_to_nchw_f32: bad shape");
+    const int hw = h * w;
+    dim3 grid((hw + 63) / 64, (c + 31) / 32, n);
+    nhwc_to_nchw_kernel<true><<<grid, 256, 0, ctx->stream>>>(in, out, c, hw, scale, (float)zp);
+    return after_launch(ctx, "dequantize_nhwc_to_nchw");
+}
+
+int nhwc_to_nchw_u8(nncb_context *ctx, const uint8_t *in, uint8_t *out, int n, int h, int w, int c) {
+    if (n <= 0 || c <= 0 || h <= 0 || w <= 0)
+        return fail(-EINVAL, "nhwc_to_nchw_u8: bad shape");
+    const int hw = h * w;
+    dim3 grid((hw + 63) / 64, (c + 31) / 32, n);
+    nhwc_to_nchw_kernel<false><<<grid, 256, 0, ctx->stream>>>(in, out, c, hw, 1.f, 0.f);
+    return after_launch(ctx, "nhwc_to_nchw_u8");
+}
+
+// ---- element-wise add between quantized tensors ------------------------------------------------
+__device__ __forceinline__ uint32_t qadd4(uint32_t a, uint32_t b, float sa, float za, float sb, float zb,
+                                          float so, float zo) {
+    uint32_t r = 0;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        float fa = dequant_dev((float)((a >> (8 * i)) & 255), za, sa);
+        float fb = dequant_dev((float)((b >> (8 * i)) & 255), zb, sb);
+        r |= (uint32_t)quant_dev(__fadd_rn(fa, fb), so, zo, 0, 255) << (8 * i);
+    }
+    return r;
+}
+
+__global__ void __launch_bounds__(256)
+qadd_kernel(const uint8_t *__restrict__ a, const uint8_t *__restrict__ b, uint8_t *__restrict__ y, size_t n,
+            float sa, float za, float sb, float zb, float so, float zo, bool vec_ok) {
+    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t nthreads = (size_t)gridDim.x * blockDim.x;
+    const size_t nvec = vec_ok ? n / 16 : 0;
+    for (size_t v = tid; v < nvec; v += nthreads) {
+        uint4 va = __ldcs(reinterpret_cast<const uint4 *>(a) + v);
+        uint4 vb = __ldcs(reinterpret_cast<const uint4 *>(b) + v);
+        uint4 r;
+        r.x = qadd4(va.x, vb.x, sa, za, sb, zb, so, zo);
+        r.y = qadd4(va.y, vb.y, sa, za, sb, zb, so, zo);
+        r.z = qadd4(va.z, vb.z, sa, za, sb, zb, so, zo);
+        r.w = qadd4(va.w, vb.w, sa, za, sb, zb, so, zo);
+        __stcs(reinterpret_cast<uint4 *>(y) + v, r);
+    }
+    for (size_t i = nvec * 16 + tid; i < n; i += nthreads) {
+        float fa = dequant_dev((float)a[i], za, sa), fb = dequant_dev((float)b[i], zb, sb);
+        y[i] = (uint8_t)quant_dev(__fadd_rn(fa, fb), so, zo, 0, 255);
+    }
+}
+
+int qadd_u8(nncb_context *ctx, const uint8_t *a, const uint8_t *b, uint8_t *y, size_t n, float sa, int32_t za,
+            float sb, int32_t zb, float so, int32_t zo) {
+    if (n == 0)
+        return 0;
+    if (!a || !b || !y)
+        return fail(-EINVAL, "qadd_u8: null pointer");
+    bool v = aligned16(a, b) && aligned16(y, y);
+    qadd_kernel<<<stream_grid(ctx, (n + 15) / 16, 256), 256, 0, ctx->stream>>>(a, b, y, n, sa, (float)za, sb,
+                                                                                  (float)zb, so, (float)zo, v);
+    return after_launch(ctx, "qadd_u8");
+}
+
+// ---- table look-up -------------------------------------------------------------------------------
+struct lut256 {
+    uint8_t t[256];
+};
+
+__global__ void __launch_bounds__(256)
+lut_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ y, size_t n, const lut256 table, bool vec_ok) {
+    __shared__ uint8_t s[256];
+    s[threadIdx.x] = table.t[threadIdx.x];
+    __syncthreads();
+    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t nthreads = (size_t)gridDim.x * blockDim.x;
+    const size_t nvec = vec_ok ? n / 16 : 0;
+    for (size_t v = tid; v < nvec; v += nthreads) {
+        uint4 in = __ldcs(reinterpret_cast<const uint4 *>(x) + v);
+        uint32_t w[4] = {in.x, in.y, in.z, in.w};
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            uint32_t r = 0;
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+                r |= (uint32_t)s[(w[k] >> (8 * i)) & 255] << (8 * i);
+            w[k] = r;
+        }
+        __stcs(reinterpret_cast<uint4 *>(y) + v, make_uint4(w[0], w[1], w[2], w[3]));
+    }
+    for (size_t i = nvec * 16 + tid; i < n; i += nthreads)
+        y[i] = s[x[i]];
+}
+
+int lut_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, size_t n, const uint8_t *host_table) {
+    if (n == 0)
+        return 0;
+    if (!x || !y || !host_table)
+        return fail(-EINVAL, "lut_u8: null pointer");
+    lut256 t;
+    memcpy(t.t, host_table, 256);
+    lut_kernel<<<stream_grid(ctx, (n + 15) / 16, 256), 256, 0, ctx->stream>>>(x, y, n, t, aligned16(x, y));
+    return after_launch(ctx, "lut_u8");
+}
+
+// ---- max pooling on u8 NHWC ----------------------------------------------------------------------
+// One thread per (output pixel, 16-channel group) when c % 16 == 0 (128-bit accesses, byte-wise
+// max via __vmaxu4), else one thread per element.
+__global__ void __launch_bounds__(256)
+maxpool_vec_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ y, int n, int h, int w, int c, int oh,
+                   int ow, int kh, int kw, int sh, int sw, int pt, int pl, uint32_t zp4) {
+    const int cg = c / 16;
+    const size_t total = (size_t)n * oh * ow * cg;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x) {
+        int g = (int)(i % cg);
+        size_t p = i / cg;
+        int ox = (int)(p % ow);
+        int oy = (int)((p / ow) % oh);
+        int b = (int)(p / ((size_t)ow * oh));
+        uint4 m = make_uint4(0, 0, 0, 0);
+        int cnt = 0;
+        for (int ky = 0; ky < kh; ky++) {
+            int iy = oy * sh - pt + ky;
+            if (iy < 0 || iy >= h)
+                continue;
+            for (int kx = 0; kx < kw; kx++) {
+                int ix = ox * sw - pl + kx;
+                if (ix < 0 || ix >= w)
+                    continue;
+                uint4 v = __ldg(reinterpret_cast<const uint4 *>(x + (((size_t)b * h + iy) * w + ix) * c) + g);
+                m.x = __vmaxu4(m.x, v.x);
+                m.y = __vmaxu4(m.y, v.y);
+                m.z = __vmaxu4(m.z, v.z);
+                m.w = __vmaxu4(m.w, v.w);
+                cnt++;
+            }
+        }
+        if (cnt < kh * kw) {
+            m.x = __vmaxu4(m.x, zp4);
+            m.y = __vmaxu4(m.y, zp4);
+            m.z = __vmaxu4(m.z, zp4);
+            m.w = __vmaxu4(m.w, zp4);
+        }
+        reinterpret_cast<uint4 *>(y + p * c)[g] = m;
+    }
+}
+
+__global__ void __launch_bounds__(256)
+maxpool_scalar_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ y, int n, int h, int w, int c,
+                      int oh, int ow, int kh, int kw, int sh, int sw, int pt, int pl, int zp) {
+    const size_t total = (size_t)n * oh * ow * c;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x) {
+        int ch = (int)(i % c);
+        size_t p = i / c;
+        int ox = (int)(p % ow);
+        int oy = (int)((p / ow) % oh);
+        int b = (int)(p / ((size_t)ow * oh));
+        int m = 0, cnt = 0;
+        for (int ky = 0; ky < kh; ky++) {
+            int iy = oy * sh - pt + ky;
+            if (iy < 0 || iy >= h)
+                continue;
+            for (int kx = 0; kx < kw; kx++) {
+                int ix = ox * sw - pl + kx;
+                if (ix < 0 || ix >= w)
+                    continue;
+                m = max(m, (int)x[(((size_t)b * h + iy) * w + ix) * c + ch]);
+                cnt++;
+            }
+        }
+        if (cnt < kh * kw)
+            m = max(m, zp);
+        y[i] = (uint8_t)m;
+    }
+}
+
+int maxpool_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, int n, int h, int w, int c, int kh, int kw,
+               int sh, int sw, int pt, int pb, int pl, int pr, int32_t zp) {
+    if (n <= 0 || h <= 0 || w <= 0 || c <= 0 || kh <= 0 || kw <= 0 || sh <= 0 || sw <= 0)
+        return fail(-EINVAL, "maxpool_u8: bad shape");
+    const int oh = conv_out_size(h, kh, sh, 1, pt, pb), ow = conv_out_size(w, kw, sw, 1, pl, pr);
+    if (oh <= 0 || ow <= 0)
+        return fail(-EINVAL, "maxpool_u8: empty output");
+    const int z = zp < 0 ? 0 : (zp > 255 ? 255 : zp);
+    if (c % 16 == 0 && aligned16(x, y)) {
+        size_t total = (size_t)n * oh * ow * (c / 16);
+        maxpool_vec_kernel<<<stream_grid(ctx, total, 256), 256, 0, ctx->stream>>>(
+            x, y, n, h, w, c, oh, ow, kh, kw, sh, sw, pt, pl, (uint32_t)z * 0x01010101u);
+    } else {
+        size_t total = (size_t)n * oh * ow * c;
+        maxpool_scalar_kernel<<<stream_grid(ctx, total, 256), 256, 0, ctx->stream>>>(x, y, n, h, w, c, oh, ow, kh,
+                                                                                      kw, sh, sw, pt, pl, z);
+    }
+    return after_launch(ctx, "maxpool_u8");
+}
+
+// ---- global mean over H x W ----------------------------------------------------------------------
+// One thread per (image, channel); consecutive threads read consecutive channels.
+__global__ void __launch_bounds__(256)
+global_avgpool_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ y, int n, int hw, int c, float si,
+                      int zi, float so, float zo) {
+    const size_t total = (size_t)n * c;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x) {
+        int ch = (int)(i % c);
+        size_t b = i / c;
+        const uint8_t *p = x + b * hw * c + ch;
+        int s = 0;
+        for (int k = 0; k < hw; k++)
+            s += p[(size_t)k * c];
+        s -= hw * zi;
+        float m = __fdiv_rn(__fmul_rn((float)s, si), (float)hw);
+        y[i] = (uint8_t)quant_dev(m, so, zo, 0, 255);
+    }
+}
+
+int global_avgpool_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, int n, int h, int w, int c, float si,
+                      int32_t zi, float so, int32_t zo) {
+    if (n <= 0 || h <= 0 || w <= 0 || c <= 0)
+        return fail(-EINVAL, "global_avgpool_u8: bad shape");
+    size_t total = (size_t)n * c;
+    global_avgpool_kernel<<<stream_grid(ctx, total, 256), 256, 0, ctx->stream>>>(x, y, n, h * w, c, si, zi, so,
+                                                                                 (float)zo);
+    return after_launch(ctx, "global_avgpool_u8");
+}
+
+} // namespace nncb

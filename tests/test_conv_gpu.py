@@ -1,0 +1,152 @@
+"""GPU parity of the quantized Conv2D / MatMul kernels against the C oracle: bit-exact u8,
+through the C ABI, on both the CUDA-core and the tcgen05 path."""
+import numpy as np
+import pytest
+import torch
+
+from nncase_b200 import lib as L
+from nncase_b200.kernels import QuantParam
+from oracle import quant_params as QP
+
+pytestmark = pytest.mark.gpu
+
+
+def make_case(seed, n, h, w, c, oc, kh, kw, groups=1, w_signed=False, sym_w=False):
+    """Seeded u8 activations / per-channel weights with realistic quant params."""
+    rng = np.random.default_rng(seed)
+    xq = rng.integers(0, 256, (n, h, w, c), dtype=np.uint8)
+    zx = int(rng.integers(0, 256))
+    sx = np.float32(0.02)
+    gic = c // groups
+    if w_signed:
+        wq = rng.integers(-127, 128, (oc, kh, kw, gic), dtype=np.int8)
+        zw = np.zeros(oc, np.int32) if sym_w else rng.integers(-20, 20, oc).astype(np.int32)
+    else:
+        wq = rng.integers(0, 256, (oc, kh, kw, gic), dtype=np.uint8)
+        zw = rng.integers(100, 156, oc).astype(np.int32)
+    sw = rng.uniform(0.001, 0.004, oc).astype(np.float32)
+    mult = (sx * sw).astype(np.float32)
+    k = kh * kw * gic
+    bias = rng.normal(0, 0.3, oc).astype(np.float32)
+    # output range ~ +-3 sigma of the accumulator
+    sigma = float(np.sqrt(k) * 74 * 74 * mult.mean())
+    zo, so = QP.get_quant_param(-2.5 * sigma, 2.5 * sigma)
+    return xq, zx, wq, zw, mult, bias, QuantParam(zo, float(so))
+
+
+def run_both(ctx, qo, case, path, stride=(1, 1), pad=(0, 0, 0, 0), dil=(1, 1), groups=1, clamp=(-np.inf, np.inf),
+             **extra):
+    xq, zx, wq, zw, mult, bias, oqp = case
+    want = qo.qconv2d_u8(xq, wq, zw, mult, bias, zx, oqp.scale, oqp.zero_point, stride, pad, dil, groups, clamp)
+    got = ctx.conv2d(torch.from_numpy(xq), wq, zw, mult, bias, zx, oqp, stride=stride, padding=pad, dilation=dil,
+                     groups=groups, fused_clamp=clamp, force_path=path, **extra)
+    ctx.check_status()
+    return got.cpu().numpy(), want
+
+
+SIMT_CASES = [
+    # n, h, w, c, oc, kh, kw, stride, pad, dil, groups
+    (1, 5, 5, 4, 8, 3, 3, 1, 1, 1, 1), (1, 16, 16, 4, 8, 3, 3, 2, 1, 2, 1), (2, 9, 7, 3, 5, 7, 7, 2, 3, 1, 1),
+    (1, 12, 12, 32, 32, 3, 3, 1, 1, 1, 32), (1, 10, 10, 24, 48, 1, 1, 1, 0, 1, 1), (1, 8, 8, 16, 16, 3, 3, 1, 1, 1, 4),
+]
+
+
+@pytest.mark.parametrize("cfg", SIMT_CASES)
+@pytest.mark.parametrize("w_signed", [False, True])
+def test_simt_conv(ctx, qo, cfg, w_signed):
+    n, h, w, c, oc, kh, kw, s, p, d, g = cfg
+    case = make_case(21, n, h, w, c, oc, kh, kw, g, w_signed)
+    got, want = run_both(ctx, qo, case, L.PATH_SIMT, (s, s), (p, p, p, p), (d, d), g, (0, 6))
+    assert np.array_equal(got, want)
+
+
+TC_CASES = [
+    # n, h, w, c, oc, kh, kw, stride, pad, dil        GEMM mode (1x1, stride 1)
+    (1, 1, 128, 128, 64, 1, 1, 1, 0, 1), (1, 1, 200, 64, 48, 1, 1, 1, 0, 1), (2, 14, 14, 256, 128, 1, 1, 1, 0, 1),
+    (1, 7, 7, 32, 16, 1, 1, 1, 0, 1), (1, 1, 300, 384, 1000, 1, 1, 1, 0, 1),
+    # im2col mode
+    (1, 56, 56, 64, 64, 3, 3, 1, 1, 1), (2, 14, 14, 128, 256, 3, 3, 1, 1, 1), (1, 28, 28, 64, 128, 3, 3, 2, 1, 1),
+    (3, 7, 7, 256, 64, 3, 3, 1, 1, 1), (1, 16, 16, 32, 32, 3, 3, 1, 2, 2), (2, 28, 28, 128, 64, 1, 1, 2, 0, 1),
+    (1, 1, 37, 64, 32, 1, 3, 1, 1, 1), (1, 20, 20, 32, 16, 5, 5, 1, 2, 1),
+]
+
+
+@pytest.mark.parametrize("cfg", TC_CASES)
+@pytest.mark.parametrize("wmode", ["u8_asym", "i8_sym"])
+def test_tc_conv(ctx, qo, cfg, wmode):
+    n, h, w, c, oc, kh, kw, s, p, d = cfg
+    ph, pw = (p if kh > 1 else 0), (p if kw > 1 else 0)
+    case = make_case(31, n, h, w, c, oc, kh, kw, 1, wmode == "i8_sym", sym_w=True)
+    got, want = run_both(ctx, qo, case, L.PATH_TC, (s, s), (ph, ph, pw, pw), (d, d), 1, (0, 6))
+    bad = np.argwhere(got != want)
+    assert bad.size == 0, f"{len(bad)} mismatches, first at {bad[:5].tolist()}"
+
+
+def test_tc_conv_residual_and_second_output(ctx, qo):
+    n, h, w, c, oc = 2, 14, 14, 64, 256
+    case = make_case(41, n, h, w, c, oc, 1, 1)
+    xq, zx, wq, zw, mult, bias, oqp = case
+    rng = np.random.default_rng(42)
+    res = rng.integers(0, 256, (n, h, w, oc), dtype=np.uint8)
+    rq, aq, yq2 = QuantParam(117, 0.05), QuantParam(125, 0.06), QuantParam(0, 0.03)
+    y1 = qo.qconv2d_u8(xq, wq, zw, mult, bias, zx, oqp.scale, oqp.zero_point)
+    want = qo.qadd_u8(y1, res, oqp.scale, oqp.zero_point, rq.scale, rq.zero_point, aq.scale, aq.zero_point)
+    want2 = qo.requant_u8(want, aq.scale, aq.zero_point, yq2.scale, yq2.zero_point, 0.0, np.inf)
+    for path in (L.PATH_SIMT, L.PATH_TC):
+        got, got2 = ctx.conv2d(torch.from_numpy(xq), wq, zw, mult, bias, zx, oqp, res=torch.from_numpy(res).cuda(),
+                               residual=(rq, aq), y2=(yq2, 0.0, float("inf")), force_path=path)
+        ctx.check_status()
+        assert np.array_equal(got.cpu().numpy(), want)
+        assert np.array_equal(got2.cpu().numpy(), want2)
+
+
+def test_tc_matmul_f32_logits(ctx, qo):
+    """FC layer: [M,K] x [N,K] with real-valued f32 output (classifier logits)."""
+    m, k, n = 70, 2048, 1000
+    case = make_case(51, 1, 1, m, k, n, 1, 1)
+    xq, zx, wq, zw, mult, bias, _ = case
+    want = qo.qconv2d_u8(xq, wq, zw, mult, bias, zx, 1.0, 0, f32_out=True).reshape(m, n)
+    for path in (L.PATH_SIMT, L.PATH_TC):
+        got = ctx.mat_mul(torch.from_numpy(xq.reshape(m, k)), wq.reshape(n, k), zw, mult, bias, zx, None,
+                          f32_out=True, force_path=path)
+        ctx.check_status()
+        assert np.array_equal(got.cpu().numpy(), want)
+
+
+def test_lut_activation(ctx, qo):
+    case = make_case(61, 1, 8, 8, 32, 32, 3, 3)
+    xq, zx, wq, zw, mult, bias, oqp = case
+    lut = np.random.default_rng(62).integers(0, 256, 256, dtype=np.uint8)
+    want = qo.qconv2d_u8(xq, wq, zw, mult, bias, zx, oqp.scale, oqp.zero_point, pad=(1, 1, 1, 1), lut=lut)
+    for path in (L.PATH_SIMT, L.PATH_TC):
+        got = ctx.conv2d(torch.from_numpy(xq), wq, zw, mult, bias, zx, oqp, padding=(1, 1, 1, 1), lut=lut,
+                         force_path=path)
+        assert np.array_equal(got.cpu().numpy(), want)
+
+
+def test_golden_conv_slice(ctx):
+    """The committed fixture generated from the reference's kernels (config-1 slice)."""
+    import os
+    c = np.load(os.path.join(os.path.dirname(__file__), "golden", "conv_config1_slice.npz"))
+    oqp = QuantParam(int(c["zo"]), float(c["so"]))
+    for path in (L.PATH_SIMT, L.PATH_TC):
+        got = ctx.conv2d(torch.from_numpy(c["xq"]), c["wq"], c["zw"], c["mult"], c["bias"], int(c["zx"]), oqp,
+                         padding=(1, 1, 1, 1), fused_clamp=(0.0, 6.0), force_path=path).cpu().numpy()
+        assert np.array_equal(got, c["y_integer"])
+        d = np.abs(got.astype(int) - c["y_ref_composite"].astype(int))
+        assert d.max() <= 1 and (d != 0).sum() <= int(c["allowed_mismatches"])
+
+
+def test_bad_arguments_are_rejected(ctx):
+    from nncase_b200.lib import NncbError
+    w = np.zeros((8, 3, 3, 5), np.uint8)
+    with pytest.raises(NncbError) as e:  # weights do not match channels
+        ctx.conv2d_plan((1, 8, 8, 4), w, None, np.ones(8), np.zeros(8), 0, QuantParam(0, 1.0))
+    assert e.value.code == -22
+    w = np.zeros((8, 3, 3, 4), np.uint8)
+    with pytest.raises(NncbError) as e:  # 4 channels cannot take the tensor-core path
+        ctx.conv2d_plan((1, 8, 8, 4), w, None, np.ones(8), np.zeros(8), 0, QuantParam(0, 1.0), force_path=L.PATH_TC)
+    assert e.value.code == -38
+    with pytest.raises(NncbError) as e:  # empty output
+        ctx.conv2d_plan((1, 2, 2, 4), w, None, np.ones(8), np.zeros(8), 0, QuantParam(0, 1.0))
+    assert e.value.code == -22

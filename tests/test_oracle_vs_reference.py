@@ -1,0 +1,130 @@
+"""Pins the C oracle against the reference's own compiled CPU kernels (oracle/_ref) and against
+the committed golden vectors (tests/golden, generated from those same kernels)."""
+import os
+
+import numpy as np
+import pytest
+
+from oracle import quant_params as QP
+
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def _edge_values(scale, zp):
+    # ties, clamp edges and denormals around every quantisation step
+    k = np.arange(-300, 300, dtype=np.float32)
+    half = (k + np.float32(0.5) - np.float32(zp)) * np.float32(scale)
+    return np.concatenate([half, np.nextafter(half, np.float32(np.inf)), np.nextafter(half, np.float32(-np.inf)),
+                           np.array([0.0, -0.0, 1e-40, -1e-40, 1e6, -1e6], np.float32)])
+
+
+@pytest.mark.parametrize("scale,zp", [(0.01, 127), (0.014035294, 88), (0.0078125, 0), (3.7e-3, 255)])
+def test_quantize_u8_matches_reference(qo, ref, scale, zp):
+    rng = np.random.default_rng(1)
+    x = np.concatenate([rng.normal(0, 1, 100000).astype(np.float32), _edge_values(scale, zp)])
+    a = qo.quantize_u8(x, scale, zp)
+    assert np.array_equal(a, ref.quantize_u8(x, scale, zp, optimized=True))
+    assert np.array_equal(a, ref.quantize_u8(x, scale, zp, optimized=False))
+
+
+@pytest.mark.parametrize("scale,zp", [(0.01, 0), (0.02, -5)])
+def test_quantize_i8_matches_reference(qo, ref, scale, zp):
+    rng = np.random.default_rng(2)
+    x = np.concatenate([rng.normal(0, 1, 50000).astype(np.float32), _edge_values(scale, zp)])
+    assert np.array_equal(qo.quantize_i8(x, scale, zp), ref.quantize_i8(x, scale, zp))
+
+
+def test_dequantize_matches_reference(qo, ref):
+    q = np.arange(256, dtype=np.uint8)
+    for scale, zp in [(0.01, 127), (0.014035294, 88), (1.5, 3)]:
+        assert np.array_equal(qo.dequantize_u8(q, scale, zp), ref.dequantize_u8(q, scale, zp))
+        assert np.array_equal(qo.dequantize_u8(q, scale, zp), ref.dequantize_u8(q, scale, zp, optimized=False))
+    qi = np.arange(-128, 128, dtype=np.int8)
+    assert np.array_equal(qo.dequantize_i8(qi, 0.02, -3), ref.dequantize_i8(qi, 0.02, -3))
+
+
+def _conv_case(seed, n, h, w, c, oc, k, stride, pad, dil=1, w_signed=False):
+    rng = np.random.default_rng(seed)
+    x = rng.uniform(-1, 1, (n, h, w, c)).astype(np.float32)
+    wt = rng.normal(0, 0.05, (oc, k, k, c)).astype(np.float32)
+    b = rng.normal(0, 0.01, oc).astype(np.float32)
+    zx, sx = QP.get_quant_param(*QP.get_min_max(x))
+    mode = QP.SIGNED_SYMMETRIC if w_signed else QP.UNSIGNED
+    zw, sw = QP.weights_quant_params(wt, oc, 8, mode)
+    return x, wt, b, zx, sx, zw, sw
+
+
+@pytest.mark.parametrize("shape", [
+    # n, h, w, c, oc, k, stride, pad, dil   (shapes of the reference's tests/kernels/test_conv2d.json plus config 1 scaled)
+    (1, 5, 5, 4, 8, 3, 1, 1, 1), (1, 16, 16, 4, 8, 3, 2, 1, 1), (1, 16, 16, 4, 8, 3, 1, 1, 2),
+    (1, 16, 16, 4, 8, 1, 1, 0, 1), (2, 14, 14, 64, 64, 3, 1, 1, 1), (1, 7, 9, 32, 16, 3, 2, 1, 1),
+])
+@pytest.mark.parametrize("w_signed", [False, True])
+def test_integer_conv_vs_reference_composite(qo, ref, shape, w_signed):
+    """The integer formulation against dequantize -> conv2d(f32, clamp) -> quantize run through the
+    reference's kernels: equal up to rare 1-LSB differences from f32 accumulation order."""
+    n, h, w, c, oc, k, stride, pad, dil = shape
+    x, wt, b, zx, sx, zw, sw = _conv_case(11, n, h, w, c, oc, k, stride, pad, dil, w_signed)
+    xq = qo.quantize_u8(x, sx, zx)
+    if w_signed:
+        wq = np.stack([qo.quantize_i8(wt[i], sw[i], zw[i]) for i in range(oc)])
+    else:
+        wq = np.stack([qo.quantize_u8(wt[i], sw[i], zw[i]) for i in range(oc)])
+    pads = (pad, pad, pad, pad)
+    yf = ref.conv2d_f32(x.transpose(0, 3, 1, 2), wt.transpose(0, 3, 1, 2), b, (stride, stride), pads, (dil, dil),
+                        clamp=(0, 6))
+    zo, so = QP.get_quant_param(*QP.get_min_max(yf))
+    mult = (np.float32(sx) * sw).astype(np.float32)
+    yq = qo.qconv2d_u8(xq, wq, zw, mult, b, zx, so, zo, (stride, stride), pads, (dil, dil), clamp=(0, 6))
+    yr = ref.qconv2d_composite_u8(xq, wq, zw, sw, b, sx, zx, so, zo, (stride, stride), pads, (dil, dil), clamp=(0, 6))
+    diff = np.abs(yq.astype(np.int32) - yr.astype(np.int32))
+    assert diff.max() <= 1
+    assert (diff != 0).mean() <= 1e-3
+
+
+def test_maxpool_padding_takes_zero_point(qo, ref):
+    """reduce_window2d max injects the real value 0 for padded taps (reference/reduce_window.cpp:86-90)."""
+    rng = np.random.default_rng(3)
+    scale, zp = 0.05, 140
+    q = rng.integers(0, 130, (1, 9, 9, 4), dtype=np.uint8)  # all real values negative
+    y = qo.maxpool_u8(q, (3, 3), (2, 2), (1, 1, 1, 1), zp)
+    xf = ref.dequantize_u8(np.ascontiguousarray(q.transpose(0, 3, 1, 2)), scale, zp)
+    yf = ref.reduce_window2d_f32("max", xf, (3, 3), (2, 2), (1, 1, 1, 1), init=float(np.finfo(np.float32).min))
+    yr = ref.quantize_u8(yf, scale, zp).transpose(0, 2, 3, 1)
+    assert np.array_equal(y, yr)
+    assert (y[0, 0, 0] == zp).all()  # corner window overlaps padding and all taps are below zero
+
+
+def test_qadd_vs_reference(qo, ref):
+    rng = np.random.default_rng(4)
+    a = rng.integers(0, 256, 10000, dtype=np.uint8)
+    b = rng.integers(0, 256, 10000, dtype=np.uint8)
+    sa, za, sb, zb, so, zo = 0.021, 120, 0.017, 131, 0.03, 125
+    y = qo.qadd_u8(a, b, sa, za, sb, zb, so, zo)
+    yr = ref.quantize_u8(ref.add_f32(ref.dequantize_u8(a, sa, za), ref.dequantize_u8(b, sb, zb)), so, zo)
+    assert np.array_equal(y, yr)
+
+
+def test_global_mean_vs_reference(qo, ref):
+    rng = np.random.default_rng(5)
+    q = rng.integers(0, 256, (2, 7, 7, 8), dtype=np.uint8)
+    si, zi, so, zo = 0.02, 10, 0.011, 3
+    y = qo.global_avgpool_u8(q, si, zi, so, zo)
+    xf = ref.dequantize_u8(np.ascontiguousarray(q.transpose(0, 3, 1, 2)), si, zi)
+    yf = ref.reduce_window2d_f32("mean", xf, (7, 7), (1, 1), (0, 0, 0, 0), init=0.0)
+    yr = ref.quantize_u8(yf, so, zo).transpose(0, 2, 3, 1)
+    d = np.abs(y.astype(int) - yr.astype(int))
+    assert d.max() <= 1 and (d != 0).mean() < 0.02  # float summation order of the reference differs
+
+
+def test_golden_vectors(qo):
+    """Committed fixtures produced by tests/golden/make_golden.py from the reference's kernels."""
+    g = np.load(os.path.join(GOLD, "quantize_dequantize.npz"))
+    assert np.array_equal(qo.quantize_u8(g["x"], float(g["scale"]), int(g["zp"])), g["q_u8"])
+    assert np.array_equal(qo.dequantize_u8(g["q_u8"], float(g["scale"]), int(g["zp"])), g["deq_f32"])
+    c = np.load(os.path.join(GOLD, "conv_config1_slice.npz"))
+    yq = qo.qconv2d_u8(c["xq"], c["wq"], c["zw"], c["mult"], c["bias"], int(c["zx"]), float(c["so"]), int(c["zo"]),
+                       (1, 1), (1, 1, 1, 1), (1, 1), clamp=(0, 6))
+    diff = np.abs(yq.astype(int) - c["y_ref_composite"].astype(int))
+    assert diff.max() <= 1 and (diff != 0).sum() <= int(c["allowed_mismatches"])
+    assert np.array_equal(yq, c["y_integer"])
