@@ -1,0 +1,369 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-inference hot path: u8/u8 ResNet-50 v2 images/s on B200.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--batch B]
+                  [--w-quant uint8|int8] [--layers]
+
+One step = one forward pass of the whole quantized network over one batch of synthetic images
+per GPU (seeded N(0,1) inputs standing in for ImageNet; random He-normal weights, BN folded).
+For N > 1 launch under torchrun, one rank per GPU; the batch is sharded by images with no
+collective on the data path (weak scaling: every GPU runs `--batch` images).
+
+Prints ONE JSON line (rank 0). `value` is device-resident throughput, `e2e` the same metric
+through the public host-buffer call (pinned f32 input -> H2D -> kernels -> D2H logits, copies
+double-buffered inside the timed region). `--impl reference` times the reference's own CPU
+kernels (dequantize -> conv2d f32 -> quantize, ...) on the host cores on a bounded sample.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CONFIG_ID = 3  # ResNet-50 v2 in the list of benchmark configurations
+SEED_W, SEED_X, SEED_CAL = 1000 + CONFIG_ID, 2000 + CONFIG_ID, 3000 + CONFIG_ID
+METRIC = "u8/u8 ResNet-50 images/s"
+UNIT = "images/s"
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_burst=d["bf16_tflops"], bf16_sustained=d["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16_burst=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], None, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = float(r[1])
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return dict(sm_mhz=float(np.median(sm)) if sm else None, sm_max_mhz=mx, reasons=sorted(reasons),
+                    samples=len(sm))
+
+
+def build_network(batch_for_calib_device, w_quant):
+    from nncase_b200 import builder, networks
+    graph = networks.resnet50v2(SEED_W)
+    cal = [np.random.default_rng(SEED_CAL + i).normal(0, 1, (1, 3, 224, 224)).astype(np.float32) for i in range(16)]
+    program = builder.build_program(graph, cal, w_quant, device=batch_for_calib_device)
+    macs, per_layer, _ = networks.graph_macs(graph)
+    return graph, program, macs, dict(per_layer)
+
+
+# ---------------------------------------------------------------------------------------------
+# reference arm: the reference's own CPU kernels on the host cores
+# ---------------------------------------------------------------------------------------------
+def cpu_reference_sample(graph, program, macs_total, seconds_target=20.0, threads=None):
+    """Times the reference's CPU implementation of the path on a bounded sample of the workload.
+
+    Sample: one image; the stem, the max-pool, every `stride`-th convolution layer (with its
+    residual add / ReLU requantisation) run through the reference's kernels exactly as its cpu
+    target executes a quantized convolution: dequantize -> conv2d(f32, fused clamp) -> quantize.
+    Layers are independent jobs spread over all host cores (the reference kernel itself is
+    single-threaded). images/s is extrapolated by the sample's share of the network's MACs.
+    """
+    from oracle import program as oprog
+    from oracle import qoracle, ref
+    threads = threads or os.cpu_count() or 1
+    x = np.random.default_rng(SEED_X).normal(0, 1, (1, 3, 224, 224)).astype(np.float32)
+    _, tens = oprog.run_program(program, x, threads=threads)  # inputs of every layer, from the oracle
+    convs = [op for op in program["ops"] if op["op"] == "conv" and not op.get("f32_out")]
+    use_ref = ref.available()
+    # reference f32 conv runs at ~0.3 GMAC/s per core: choose how many layers fit the time target
+    est_rate = 0.3e9 if use_ref else 3e9
+    layer_macs = []
+    for op in convs:
+        n, oh, ow, oc = tens[op["out"]].shape
+        layer_macs.append(oh * ow * oc * op["w"].shape[1] * op["w"].shape[2] * op["w"].shape[3])
+    budget = est_rate * seconds_target * threads
+    order = np.argsort(layer_macs)[::-1]
+    stride = max(1, int(np.ceil(sum(layer_macs) / budget)))
+    chosen = sorted(order[::stride].tolist())
+    T = program["tensors"]
+
+    job_seconds = []
+
+    def job(i):
+        t_job = time.perf_counter()
+        op = convs[i]
+        xq, xqp, cq = tens[op["in"]], T[op["in"]]["qp"], op["conv_qp"]
+        if use_ref:
+            sw = op["mult"] / np.float32(xqp.scale)
+            ref.qconv2d_composite_u8(xq, op["w"], op["w_zp"], sw, op["bias"], xqp.scale, xqp.zero_point, cq.scale,
+                                     cq.zero_point, op["stride"], op["pad"], op["dil"], op["groups"], op["clamp"])
+        else:
+            qoracle.qconv2d_u8(xq, op["w"], op["w_zp"], op["mult"], op["bias"], xqp.zero_point, cq.scale,
+                               cq.zero_point, op["stride"], op["pad"], op["dil"], op["groups"], op["clamp"])
+        job_seconds.append(time.perf_counter() - t_job)
+
+    if not use_ref:
+        qoracle.lib().qo_set_threads(1)
+    t0 = time.perf_counter()
+    from concurrent.futures import ThreadPoolExecutor
+    with ThreadPoolExecutor(threads) as ex:
+        list(ex.map(job, chosen))
+    dt = time.perf_counter() - t0
+    sample_macs = sum(layer_macs[i] for i in chosen)
+    macs_total = sum(layer_macs)  # same counting as the sample (the FC layer, 0.05 % of the MACs, is left out)
+    # core-seconds the sample took (each layer ran on one core) -> core-seconds per image at
+    # full-network MACs -> images/s with every core busy on its own image
+    core_seconds = sum(job_seconds)
+    img_per_s = threads / (core_seconds * macs_total / sample_macs)
+    return dict(value=img_per_s, unit=UNIT, cores=threads, kind="reference" if use_ref else "port",
+                sample=f"1 image, {len(chosen)} of {len(convs)} conv layers ({sample_macs / macs_total:.1%} of the "
+                       f"network's MACs) through dequantize->conv2d(f32)->quantize, {dt:.1f} s wall, "
+                       f"extrapolated by MACs"), dt
+
+
+def run_reference(args):
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    graph, program, macs, _ = build_network("cpu", args.w_quant)
+    vals, last = [], None
+    steps = max(1, args.steps)
+    per_step = max(3.0, min(20.0, 150.0 / (steps + args.warmup)))
+    for i in range(args.warmup + steps):
+        cb, dt = cpu_reference_sample(graph, program, macs, per_step)
+        if i >= args.warmup:
+            vals.append(cb["value"])
+            last = cb
+    v = float(np.mean(vals))
+    last["value"] = v
+    line = dict(metric=METRIC, value=v, unit=UNIT, n_gpus=args.gpus, steps=steps, warmup=args.warmup,
+                ms_per_step=1000.0 * args.batch / v, higher_is_better=True, scaling="weak", vs_baseline=None,
+                dtype="f32", data="synthetic", impl="reference",
+                config=dict(workload="resnet50v2_u8u8", batch_per_gpu=args.batch, w_quant=args.w_quant),
+                cpu_baseline=last, e2e=dict(value=v, unit=UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the hot path has no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from nncase_b200 import lib as L
+    from nncase_b200.kernels import Context
+    from nncase_b200.runtime import CudaFunction
+
+    dev = torch.device("cuda", local)
+    graph, program, macs, layer_macs = build_network(dev, args.w_quant)
+    ctx = Context(local)
+    fn = CudaFunction(program, args.batch, ctx)
+    B = args.batch
+    g = torch.Generator(device=dev).manual_seed(SEED_X + rank)
+    x = torch.randn((B, 3, 224, 224), device=dev, generator=g)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    # -------- device-resident throughput --------
+    for _ in range(max(3, args.warmup)):
+        fn.invoke(x)
+    ctx.check_status()
+    launches_per_step = fn.launches_per_call
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    l0 = ctx.launches
+    ev0.record()
+    for _ in range(args.steps):
+        fn.invoke(x)
+    ev1.record()
+    barrier()
+    ms = ev0.elapsed_time(ev1)
+    gpu_launches = ctx.launches - l0
+    ctx.check_status()
+
+    # -------- end to end through the host-buffer call --------
+    xh = [torch.empty((B, 3, 224, 224), dtype=torch.float32).pin_memory() for _ in range(2)]
+    for t in xh:
+        t.copy_(x)
+    oh = [torch.empty((B, 1, 1, 1000), dtype=torch.float32).pin_memory() for _ in range(2)]
+    copy_stream, comp_stream = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    xd = [torch.empty_like(x) for _ in range(2)]
+    e2e_steps = args.steps
+
+    def e2e_loop(steps):
+        # double buffered: the H2D copy of step i+1 overlaps the kernels of step i; every
+        # step's input copy and result read-back are inside the timed region
+        copied = [torch.cuda.Event() for _ in range(2)]
+        done = [torch.cuda.Event() for _ in range(2)]
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(copy_stream):
+            start.record()
+            xd[0].copy_(xh[0], non_blocking=True)
+            copied[0].record()
+        for i in range(steps):
+            b = i & 1
+            if i + 1 < steps:
+                with torch.cuda.stream(copy_stream):
+                    if i >= 1:
+                        copy_stream.wait_event(done[b ^ 1])
+                    xd[b ^ 1].copy_(xh[b ^ 1], non_blocking=True)
+                    copied[b ^ 1].record()
+            with torch.cuda.stream(comp_stream):
+                comp_stream.wait_event(copied[b])
+                out = fn.invoke(xd[b])
+                oh[b].copy_(out, non_blocking=True)
+                done[b].record()
+        with torch.cuda.stream(comp_stream):
+            comp_stream.wait_stream(copy_stream)
+            end.record()
+        comp_stream.synchronize()
+        copy_stream.synchronize()
+        return start.elapsed_time(end)
+
+    e2e_loop(3)
+    barrier()
+    e2e_ms = e2e_loop(e2e_steps)
+    barrier()
+    ctx.use_current_stream()
+    clocks = sampler.stop() if rank == 0 else None
+
+    # -------- per-layer timing of the dominant kernel (tcgen05 conv) for the roofline --------
+    tc_ops, tc_ms, rows = 0.0, 0.0, []
+    reps = 5
+    for st in fn.steps:
+        if st[0] != "conv":
+            continue
+        op, plan = st[1], st[2]
+        res = fn.buffers[op["res"]] if op.get("res") else None
+        y2 = fn.buffers[op["y2"]] if op.get("y2") else None
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        plan(fn.buffers[op["in"]], res, fn.buffers[op["out"]], y2)
+        torch.cuda.synchronize(dev)
+        a.record()
+        for _ in range(reps):
+            plan(fn.buffers[op["in"]], res, fn.buffers[op["out"]], y2)
+        b.record()
+        torch.cuda.synchronize(dev)
+        t = a.elapsed_time(b) / reps
+        ops = 2.0 * layer_macs[op["name"]] * B
+        rows.append((op["name"], plan.path, t, ops))
+        if plan.path == L.PATH_TC:
+            tc_ops += ops
+            tc_ms += t
+    ctx.check_status()
+
+    # max over ranks of the device-measured times
+    if world > 1:
+        tt = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(tt[0]), float(tt[1])
+        tl = torch.tensor([gpu_launches], device=dev, dtype=torch.int64)
+        dist.all_reduce(tl)
+        gpu_launches = int(tl[0])
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    pk = peaks()
+    value = world * B * args.steps / (ms / 1000.0)
+    e2e_value = world * B * e2e_steps / (e2e_ms / 1000.0)
+    int8_peak = 2.0 * pk["bf16_burst"]  # dense int8 = 2x the measured dense bf16 (int8 itself is not in the peaks file)
+    achieved = tc_ops / (tc_ms / 1000.0) / 1e12 if tc_ms > 0 else 0.0
+    line = dict(
+        metric=METRIC, value=value, unit=UNIT, n_gpus=world, steps=args.steps, warmup=max(3, args.warmup),
+        ms_per_step=ms / args.steps, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="u8",
+        data="synthetic", impl="ours",
+        config=dict(workload="resnet50v2_u8u8", batch_per_gpu=B, global_batch=B * world, w_quant=args.w_quant,
+                    input="f32 NCHW [B,3,224,224] N(0,1)", l2="inputs and activations larger than L2 (no flush)",
+                    parallelism=f"batch-sharded x{world}, no collective"),
+        e2e=dict(value=e2e_value, unit=UNIT, h2d_bytes_per_step=B * 3 * 224 * 224 * 4, d2h_bytes_per_step=B * 1000 * 4),
+        gpu_launches=gpu_launches, launches_per_step=launches_per_step,
+        clocks=clocks,
+        roofline=dict(bound="tensor", kernel="tc_conv_kernel", achieved=achieved, peak=int8_peak, unit="TFLOP/s",
+                      frac=achieved / int8_peak, traffic=None,
+                      peak_source=f"2 x bf16 burst of {pk['source']} peaks (int8 dense is twice bf16)",
+                      tc_ms_per_step=tc_ms, tc_share_of_step=tc_ms / (ms / args.steps),
+                      whole_step_tops=2.0 * macs * B / (ms / args.steps / 1000.0) / 1e12),
+    )
+    if world == 1 and not args.no_cpu_baseline:
+        cb, _ = cpu_reference_sample(graph, program, macs, 15.0)
+        line["cpu_baseline"] = cb
+    if args.layers:
+        for r in rows:
+            print(f"# {r[0]:10s} path={r[1]} {r[2] * 1000:9.1f} us  {r[3] / (r[2] / 1000) / 1e12:8.1f} TOP/s", file=sys.stderr)
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=512, help="images per GPU per step")
+    ap.add_argument("--w-quant", default="uint8", choices=["uint8", "int8"])
+    ap.add_argument("--layers", action="store_true", help="print per-layer timings to stderr")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -44,7 +44,7 @@ typedef enum nncb_dtype { NNCB_I8 = 2, NNCB_I16 = 3, NNCB_U8 = 6, NNCB_F16 = 10,
 
 /* ---- context: device + stream (replaces kernels::kernel_context,
  *      src/Native/include/nncase/kernels/kernel_context.h) ------------------------------ */
-/* stream: a cudaStream_t to launch on, or NULL to create an own non-blocking stream. */
+/* stream: the cudaStream_t to launch on; NULL is the CUDA default stream. The caller owns it. */
 NNCB_API int nncb_context_create(int device, void *stream, nncb_context **out);
 NNCB_API int nncb_context_destroy(nncb_context *ctx);
 NNCB_API int nncb_context_set_stream(nncb_context *ctx, void *stream);

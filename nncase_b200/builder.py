@@ -1,0 +1,214 @@
+"""Post-training quantization of a float layer graph into a program for the `cuda` module.
+
+This is the host-side stand-in for what the reference does in C# between import and codegen:
+  * calibration: run the float graph on the calibration samples and union per-tensor min/max
+    over finite values (Quantizer.GetRangesAsync / GetMinMax,
+    src/Nncase.Quantization/Quantization/Quantizer.cs:389-409, Quantizer.Algorithms.cs:14-30),
+    NoClip (no KLD refinement), then the calibration range fix-up (Quantizer.cs:358-387);
+  * QuantParams: activations asymmetric per-tensor u8, weights per output channel
+    (QuantUtility.GetQuantParam, Quantizer.cs:620-661), computed by the library's own host code;
+  * lowering of each marked Conv2D / MatMul into the integer kernel call with its fused
+    epilogue (what a `cuda` ITarget's RegisterQuantizePass would emit).
+The float forward used for calibration runs on torch (model preparation, not the hot path).
+"""
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+from . import kernels as K
+from . import lib as L
+
+INF = float("inf")
+_ACT_CLAMP = {None: (-INF, INF), "relu": (0.0, INF), "relu6": (0.0, 6.0)}
+
+
+# ---- float forward (calibration) -----------------------------------------------------------
+def float_forward(graph, x, device="cpu", record=None):
+    """Runs the float graph on x (torch f32 NCHW). `record(name, tensor)` sees every tensor."""
+    t = {}
+    rec = record or (lambda n, v: None)
+    out = None
+    for nd in graph:
+        op = nd["op"]
+        if op == "input":
+            t[nd["out"]] = x.to(device)
+            rec(nd["out"], t[nd["out"]])
+        elif op == "conv":
+            w = torch.from_numpy(nd["w"]).to(device)
+            b = torch.from_numpy(nd["b"]).to(device)
+            xin = t[nd["in"]]
+            pt, pb, pl, pr = nd["pad"]
+            if (pt, pl) != (pb, pr):
+                xin = F.pad(xin, (pl, pr, pt, pb))
+                padding = (0, 0)
+            else:
+                padding = (pt, pl)
+            y = F.conv2d(xin, w, b, nd["stride"], padding, nd["dil"], nd["groups"])
+            lo, hi = _ACT_CLAMP[nd["act"]]
+            if nd["act"] is not None:
+                y = y.clamp(lo, hi)
+            if nd.get("res"):
+                rec(nd["out"] + "@conv", y)
+                y = y + t[nd["res"]]
+            t[nd["out"]] = y
+            rec(nd["out"], y)
+            if nd.get("relu_out"):
+                t[nd["relu_out"]] = y.clamp_min(0)
+                rec(nd["relu_out"], t[nd["relu_out"]])
+        elif op == "maxpool":
+            xin = t[nd["in"]]
+            pt, pb, pl, pr = nd["pad"]
+            # the reference pads max windows with the value 0 (reduce_window.cpp:86-90)
+            xin = F.pad(xin, (pl, pr, pt, pb), value=0.0)
+            t[nd["out"]] = F.max_pool2d(xin, nd["k"], nd["stride"])
+            rec(nd["out"], t[nd["out"]])
+        elif op == "relu":
+            t[nd["out"]] = t[nd["in"]].clamp_min(0)
+            rec(nd["out"], t[nd["out"]])
+        elif op == "gap":
+            t[nd["out"]] = t[nd["in"]].mean(dim=(2, 3), keepdim=True)
+            rec(nd["out"], t[nd["out"]])
+        elif op == "fc":
+            w = torch.from_numpy(nd["w"]).to(device)
+            b = torch.from_numpy(nd["b"]).to(device)
+            t[nd["out"]] = t[nd["in"]].flatten(1) @ w.t() + b
+            rec(nd["out"], t[nd["out"]])
+        else:
+            raise ValueError(f"unknown node {op}")
+        out = nd["out"]
+    return t[out], t
+
+
+def calibrate(graph, samples, device="cpu"):
+    """Union of per-sample (min, max) over finite values for every tensor of the graph."""
+    ranges = {}
+
+    def rec(name, v):
+        v = v[torch.isfinite(v)]
+        if v.numel() == 0:
+            return
+        mn, mx = float(v.min()), float(v.max())
+        if name in ranges:
+            ranges[name] = (min(ranges[name][0], mn), max(ranges[name][1], mx))
+        else:
+            ranges[name] = (mn, mx)
+
+    with torch.no_grad():
+        for s in samples:
+            float_forward(graph, torch.as_tensor(s, dtype=torch.float32), device, rec)
+    return ranges
+
+
+def calib_fixup_range(mn, mx):
+    """Quantizer.FixUpRange, asymmetric branch (Quantizer.cs:358-387)."""
+    mn, mx = np.float32(mn), np.float32(mx)
+    if mx < 0:
+        mx = np.float32(0)
+    if mn > 0:
+        mn = np.float32(0)
+    r = np.float32(mx - mn)
+    if r < np.float32(1e-6):
+        r = np.float32(0.1)
+    return mn, np.float32(mn + r)
+
+
+def activation_qp(rng):
+    mn, mx = calib_fixup_range(*rng)
+    return K.get_quant_param(mn, mx, 8, L.UNSIGNED)
+
+
+def quantize_weights(w_oihw, w_quant_type="uint8", c_pad=None):
+    """Per-output-channel weight quantization -> (q OHWI, zero points int32[oc], scales f32[oc]).
+    'uint8': asymmetric unsigned; 'int8': symmetric signed (zero points all 0)."""
+    oc, ic = w_oihw.shape[:2]
+    flat = w_oihw.reshape(oc, -1)
+    zps = np.zeros(oc, np.int32)
+    scales = np.zeros(oc, np.float32)
+    mode = L.UNSIGNED if w_quant_type == "uint8" else L.SIGNED_SYMMETRIC
+    for ch in range(oc):
+        qp = K.get_quant_param(float(flat[ch].min()), float(flat[ch].max()), 8, mode)
+        zps[ch], scales[ch] = qp.zero_point, qp.scale
+    lo, hi = (0, 255) if w_quant_type == "uint8" else (-128, 127)
+    # q = clamp(rint(w / scale + zp)) in f32: the reference's quantize formula
+    q = np.rint(w_oihw / scales[:, None, None, None] + zps[:, None, None, None].astype(np.float32))
+    q = np.clip(q, lo, hi).astype(np.uint8 if w_quant_type == "uint8" else np.int8)
+    q = np.ascontiguousarray(q.transpose(0, 2, 3, 1))  # OHWI
+    if c_pad and c_pad > ic:
+        pad = np.empty(q.shape[:3] + (c_pad - ic,), q.dtype)
+        pad[...] = zps[:, None, None, None].astype(q.dtype)  # (w - zw) = 0 on padded channels
+        q = np.ascontiguousarray(np.concatenate([q, pad], axis=3))
+    return q, zps, scales
+
+
+def _pad_channels(c):
+    """Channel counts the tensor-core kernel accepts need no padding; tiny ones pad to 4."""
+    return 4 if c < 4 else c
+
+
+def build_program(graph, calib_samples, w_quant_type="uint8", device="cpu"):
+    """Calibrate and lower `graph` into a quantized program (a dict, see nncase_b200.runtime)."""
+    ranges = calibrate(graph, calib_samples, device)
+    qps = {name: activation_qp(r) for name, r in ranges.items()}
+    tensors, ops = {}, []
+    shapes = {}
+
+    def add_tensor(name, c, h, w, qp, dtype="u8"):
+        tensors[name] = dict(shape=(h, w, c), qp=qp, dtype=dtype)
+        shapes[name] = (c, h, w)
+
+    out_name = None
+    for nd in graph:
+        op = nd["op"]
+        if op == "input":
+            c, h, w = nd["shape"]
+            cp = _pad_channels(c)
+            add_tensor(nd["out"], cp, h, w, qps[nd["out"]])
+            ops.append(dict(op="quantize_input", out=nd["out"], c=c, c_pad=cp))
+            in_name = nd["out"]
+        elif op == "conv":
+            c, h, w = shapes[nd["in"]]
+            wq, zw, sw = quantize_weights(nd["w"], w_quant_type, c if nd["groups"] == 1 else None)
+            oc, kh, kw, _ = wq.shape
+            oh = (h + nd["pad"][0] + nd["pad"][1] - ((kh - 1) * nd["dil"][0] + 1)) // nd["stride"][0] + 1
+            ow = (w + nd["pad"][2] + nd["pad"][3] - ((kw - 1) * nd["dil"][1] + 1)) // nd["stride"][1] + 1
+            xqp = tensors[nd["in"]]["qp"]
+            mult = (np.float32(xqp.scale) * sw).astype(np.float32)
+            has_res = bool(nd.get("res"))
+            o = dict(op="conv", name=nd["name"], **{"in": nd["in"]}, out=nd["out"], w=wq,
+                     w_zp=zw if zw.any() else None, mult=mult, bias=nd["b"].astype(np.float32), stride=nd["stride"],
+                     pad=nd["pad"], dil=nd["dil"], groups=nd["groups"], clamp=_ACT_CLAMP[nd["act"]],
+                     res=nd.get("res"), y2=nd.get("relu_out"),
+                     conv_qp=qps[nd["out"] + "@conv"] if has_res else qps[nd["out"]])
+            add_tensor(nd["out"], oc, oh, ow, qps[nd["out"]])
+            if nd.get("relu_out"):
+                add_tensor(nd["relu_out"], oc, oh, ow, qps[nd["relu_out"]])
+            ops.append(o)
+        elif op == "maxpool":
+            c, h, w = shapes[nd["in"]]
+            oh = (h + nd["pad"][0] + nd["pad"][1] - nd["k"][0]) // nd["stride"][0] + 1
+            ow = (w + nd["pad"][2] + nd["pad"][3] - nd["k"][1]) // nd["stride"][1] + 1
+            add_tensor(nd["out"], c, oh, ow, tensors[nd["in"]]["qp"])  # max keeps the input's quant param
+            ops.append(dict(op="maxpool", **{"in": nd["in"]}, out=nd["out"], k=nd["k"], stride=nd["stride"],
+                            pad=nd["pad"]))
+        elif op == "relu":
+            c, h, w = shapes[nd["in"]]
+            add_tensor(nd["out"], c, h, w, qps[nd["out"]])
+            ops.append(dict(op="requant", **{"in": nd["in"]}, out=nd["out"], clamp=(0.0, INF)))
+        elif op == "gap":
+            c, h, w = shapes[nd["in"]]
+            add_tensor(nd["out"], c, 1, 1, qps[nd["out"]])
+            ops.append(dict(op="gap", **{"in": nd["in"]}, out=nd["out"]))
+        elif op == "fc":
+            c, h, w = shapes[nd["in"]]
+            wq, zw, sw = quantize_weights(nd["w"].reshape(nd["w"].shape[0], c, 1, 1), w_quant_type)
+            xqp = tensors[nd["in"]]["qp"]
+            mult = (np.float32(xqp.scale) * sw).astype(np.float32)
+            add_tensor(nd["out"], wq.shape[0], 1, 1, None, "f32")
+            ops.append(dict(op="conv", name=nd["name"], **{"in": nd["in"]}, out=nd["out"], w=wq,
+                            w_zp=zw if zw.any() else None, mult=mult, bias=nd["b"].astype(np.float32), stride=(1, 1),
+                            pad=(0, 0, 0, 0), dil=(1, 1), groups=1, clamp=(-INF, INF), res=None, y2=None,
+                            conv_qp=None, f32_out=True))
+        else:
+            raise ValueError(f"unknown node {op}")
+        out_name = nd["out"]
+    return dict(input=in_name, output=out_name, tensors=tensors, ops=ops, ranges=ranges)

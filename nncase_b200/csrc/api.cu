@@ -117,12 +117,7 @@ int nncb_context_create(int device, void *stream, nncb_context **out) {
     nncb_context *ctx = new nncb_context();
     ctx->device = device;
     ctx->sm_count = prop.multiProcessorCount;
-    if (stream) {
-        ctx->stream = (cudaStream_t)stream;
-    } else {
-        NNCB_CUDA_TRY(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
-        ctx->own_stream = true;
-    }
+    ctx->stream = (cudaStream_t)stream; // NULL is the CUDA default stream
     NNCB_CUDA_TRY(cudaMalloc(&ctx->d_status, sizeof(int)));
     NNCB_CUDA_TRY(cudaMemset(ctx->d_status, 0, sizeof(int)));
     *out = ctx;
@@ -135,19 +130,12 @@ int nncb_context_destroy(nncb_context *ctx) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     cudaFree(ctx->d_status);
-    if (ctx->own_stream)
-        cudaStreamDestroy(ctx->stream);
     delete ctx;
     return 0;
 }
 
 int nncb_context_set_stream(nncb_context *ctx, void *stream) {
     CHECK_CTX(ctx);
-    if (ctx->own_stream) {
-        cudaStreamSynchronize(ctx->stream);
-        cudaStreamDestroy(ctx->stream);
-        ctx->own_stream = false;
-    }
     ctx->stream = (cudaStream_t)stream;
     return 0;
 }

@@ -13,11 +13,9 @@
 struct nncb_context {
     int device = 0;
     cudaStream_t stream = nullptr;
-    bool own_stream = false;
     uint64_t launches = 0;
     int sm_count = 148;
     int *d_status = nullptr;  // device word: 0 ok, else code of the first bounded wait that gave up
-    uint8_t *d_lut = nullptr; // 256-byte scratch table for nncb_requant_u8 / nncb_lut_u8
 };
 
 namespace nncb {

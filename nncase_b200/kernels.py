@@ -41,15 +41,16 @@ def fixup_range(rmin, rmax, symmetric=False):
 
 
 class Context:
-    """One device + stream; the stand-in for ``kernel_context``. Uses torch's current stream of
-    the device unless ``own_stream`` is set."""
+    """One device + stream; the stand-in for ``kernel_context``. Launches on torch's current
+    stream of the device at construction (re-bind with ``use_current_stream``), so that torch
+    events, copies and CUDA-graph capture order correctly with the kernels."""
 
-    def __init__(self, device=0, own_stream=False):
+    def __init__(self, device=0):
         self._lib = L.load()
         if not torch.cuda.is_available():
             raise NncbError(-5, "no CUDA device: nncase_b200 has no CPU fallback")
         self.device = torch.device("cuda", device)
-        stream = None if own_stream else torch.cuda.current_stream(self.device).cuda_stream
+        stream = torch.cuda.current_stream(self.device).cuda_stream
         h = C.c_void_p()
         check(self._lib.nncb_context_create(device, C.c_void_p(stream), C.byref(h)))
         self._h = h

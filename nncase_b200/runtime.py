@@ -1,0 +1,155 @@
+"""The `cuda` module's runtime function: executes a quantized program on one B200.
+
+Mirrors what a ``runtime_function`` subclass does in the reference's native runtime
+(``initialize_core`` = upload weights and plan buffers once; ``invoke_core`` = run the kernels
+for one call, src/Native/include/nncase/runtime/runtime_function.h:59-63): tensors cross the
+boundary as f32 NCHW host or device arrays, stay u8 NHWC inside, and nothing is allocated or
+uploaded per call. The per-op host loop of the reference's StackVM
+(runtime_function.run.cpp:34-63) is replaced by a pre-planned launch list that can be captured
+into a CUDA graph.
+"""
+import numpy as np
+import torch
+
+from . import lib as L
+from .kernels import Context, NncbError, QuantParam
+
+INF = float("inf")
+
+
+class CudaFunction:
+    def __init__(self, program, batch, ctx=None, device=0, force_path=L.PATH_AUTO):
+        self.ctx = ctx or Context(device)
+        self.program = program
+        self.batch = batch
+        dev = self.ctx.device
+        self.buffers = {}
+        for name, t in program["tensors"].items():
+            h, w, c = t["shape"]
+            dt = torch.uint8 if t["dtype"] == "u8" else torch.float32
+            self.buffers[name] = torch.empty((batch, h, w, c), dtype=dt, device=dev)
+        self.steps = []
+        self.plans = []
+        for op in program["ops"]:
+            self.steps.append(self._plan(op, force_path))
+        in_t = program["tensors"][program["input"]]
+        self.in_qp = in_t["qp"]
+        self._graph = None
+        self._static_in = None
+        self.launches_per_call = None
+
+    # ---- planning --------------------------------------------------------------------------
+    def _plan(self, op, force_path):
+        ctx, buf, T = self.ctx, self.buffers, self.program["tensors"]
+        kind = op["op"]
+        if kind == "quantize_input":
+            return ("quantize_input", op)
+        if kind == "conv":
+            tin = T[op["in"]]
+            h, w, c = tin["shape"]
+            residual = y2 = None
+            out_qp = op["conv_qp"]
+            if op.get("res"):
+                residual = (T[op["res"]]["qp"], T[op["out"]]["qp"])
+            if op.get("y2"):
+                y2 = (T[op["y2"]]["qp"], 0.0, INF)
+            plan = ctx.conv2d_plan((self.batch, h, w, c), op["w"], op["w_zp"], op["mult"], op["bias"],
+                                   tin["qp"].zero_point, out_qp, stride=op["stride"], padding=op["pad"],
+                                   dilation=op["dil"], groups=op["groups"], fused_clamp=op["clamp"], residual=residual,
+                                   y2=y2, f32_out=bool(op.get("f32_out")), force_path=force_path)
+            self.plans.append(plan)
+            return ("conv", op, plan)
+        if kind in ("maxpool", "requant", "gap"):
+            return (kind, op)
+        raise NncbError(-38, f"unsupported program op {kind}")
+
+    @property
+    def conv_paths(self):
+        """{layer name: 1 (CUDA cores) | 2 (tcgen05)}"""
+        return {s[1]["name"]: s[2].path for s in self.steps if s[0] == "conv"}
+
+    # ---- execution -------------------------------------------------------------------------
+    def _run(self, x_dev):
+        """Enqueue all kernels of one call; x_dev: f32 NCHW device tensor of the planned batch."""
+        ctx, buf, T = self.ctx, self.buffers, self.program["tensors"]
+        lib, h_ = ctx._lib, ctx._h
+        for st in self.steps:
+            kind, op = st[0], st[1]
+            if kind == "quantize_input":
+                n, c, hh, ww = x_dev.shape
+                qp = T[op["out"]]["qp"]
+                L.check(lib.nncb_quantize_nchw_to_nhwc_u8(h_, x_dev.data_ptr(), buf[op["out"]].data_ptr(), n, c, hh, ww,
+                                                          op["c_pad"], qp.scale, qp.zero_point))
+            elif kind == "conv":
+                plan = st[2]
+                res = buf[op["res"]] if op.get("res") else None
+                y2 = buf[op["y2"]] if op.get("y2") else None
+                L.check(lib.nncb_qconv2d_run(h_, plan._h, buf[op["in"]].data_ptr(),
+                                             res.data_ptr() if res is not None else None, buf[op["out"]].data_ptr(),
+                                             y2.data_ptr() if y2 is not None else None))
+            elif kind == "maxpool":
+                hh, ww, c = T[op["in"]]["shape"]
+                L.check(lib.nncb_maxpool_u8(h_, buf[op["in"]].data_ptr(), buf[op["out"]].data_ptr(), self.batch, hh, ww, c,
+                                            op["k"][0], op["k"][1], op["stride"][0], op["stride"][1], *op["pad"],
+                                            T[op["in"]]["qp"].zero_point))
+            elif kind == "requant":
+                qi, qo = T[op["in"]]["qp"], T[op["out"]]["qp"]
+                L.check(lib.nncb_requant_u8(h_, buf[op["in"]].data_ptr(), buf[op["out"]].data_ptr(),
+                                            buf[op["in"]].numel(), qi.scale, qi.zero_point, qo.scale, qo.zero_point,
+                                            op["clamp"][0], op["clamp"][1]))
+            elif kind == "gap":
+                hh, ww, c = T[op["in"]]["shape"]
+                qi, qo = T[op["in"]]["qp"], T[op["out"]]["qp"]
+                L.check(lib.nncb_global_avgpool_u8(h_, buf[op["in"]].data_ptr(), buf[op["out"]].data_ptr(), self.batch,
+                                                   hh, ww, c, qi.scale, qi.zero_point, qo.scale, qo.zero_point))
+        return buf[self.program["output"]]
+
+    def invoke(self, x_dev):
+        """Device in (f32 NCHW [batch,c,h,w]), device out (the program's output buffer)."""
+        if x_dev.shape[0] != self.batch or x_dev.dtype != torch.float32 or not x_dev.is_contiguous():
+            raise NncbError(-22, "invoke: input must be a contiguous f32 NCHW tensor of the planned batch")
+        self.ctx.use_current_stream()
+        before = self.ctx.launches
+        out = self._run(x_dev)
+        self.launches_per_call = self.ctx.launches - before
+        return out
+
+    def capture(self, x_dev):
+        """Capture one call into a CUDA graph reading from a static copy of x_dev's storage."""
+        self._static_in = x_dev.clone()
+        self.invoke(self._static_in)  # warm-up outside capture (tensor maps, lazy init)
+        torch.cuda.synchronize(self.ctx.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.ctx.use_current_stream()
+            self._run(self._static_in)
+        self.ctx.use_current_stream()
+        self._graph = g
+        return g
+
+    def replay(self, x_dev=None):
+        if x_dev is not None:
+            self._static_in.copy_(x_dev, non_blocking=True)
+        self._graph.replay()
+        return self.buffers[self.program["output"]]
+
+    def invoke_host(self, x_host, out_host=None, pinned_in=None):
+        """Host in, host out (numpy or pinned torch tensors): H2D copy, kernels, D2H copy, sync."""
+        x = torch.as_tensor(x_host)
+        xd = x.to(self.ctx.device, non_blocking=True)
+        out = self.replay(xd) if self._graph is not None else self.invoke(xd)
+        if out_host is None:
+            res = out.to("cpu")
+        else:
+            out_host.copy_(out, non_blocking=True)
+            res = out_host
+        torch.cuda.current_stream(self.ctx.device).synchronize()
+        return res
+
+    def tensor(self, name):
+        return self.buffers[name]
+
+    def close(self):
+        for p in self.plans:
+            p.close()
+        self.plans = []

@@ -1,0 +1,54 @@
+"""Whole-program parity on the GPU: every tensor of the quantized networks bit-exact against the
+oracle's op-by-op replay, through the runtime function (C ABI underneath)."""
+import numpy as np
+import pytest
+import torch
+
+from nncase_b200 import builder, networks
+from nncase_b200 import lib as L
+from nncase_b200.runtime import CudaFunction
+from oracle import program as oprog
+
+pytestmark = pytest.mark.gpu
+
+
+def test_config1_single_conv(ctx):
+    """[1,64,56,56] f32 NCHW -> quantize -> 3x3 conv + ReLU6 -> u8, PTQ from 8 seeded samples."""
+    graph = networks.single_conv(1001)
+    cal = [np.random.default_rng(3001 + i).uniform(-1, 1, (1, 64, 56, 56)).astype(np.float32) for i in range(8)]
+    program = builder.build_program(graph, cal)
+    x = np.random.default_rng(2001).uniform(-1, 1, (1, 64, 56, 56)).astype(np.float32)
+    fn = CudaFunction(program, 1, ctx)
+    assert fn.conv_paths["conv"] == L.PATH_TC
+    got = fn.invoke(torch.from_numpy(x).cuda()).cpu().numpy()
+    ctx.check_status()
+    want, _ = oprog.run_program(program, x)
+    assert np.array_equal(got, want)
+    fn.close()
+
+
+@pytest.mark.parametrize("w_quant", ["uint8", "int8"])
+def test_resnet50v2_every_tensor(ctx, w_quant):
+    graph = networks.resnet50v2(1003)
+    cal = [np.random.default_rng(3003 + i).normal(0, 1, (1, 3, 224, 224)).astype(np.float32) for i in range(2)]
+    program = builder.build_program(graph, cal, w_quant)
+    n = 3
+    x = np.random.default_rng(2003).normal(0, 1, (n, 3, 224, 224)).astype(np.float32)
+    fn = CudaFunction(program, n, ctx)
+    paths = fn.conv_paths
+    assert paths["stem"] == L.PATH_SIMT and all(p == L.PATH_TC for k, p in paths.items() if k != "stem")
+    out = fn.invoke(torch.from_numpy(x).cuda())
+    ctx.check_status()
+    want, tens = oprog.run_program(program, x)
+    for name, ref_t in tens.items():
+        got = fn.tensor(name).cpu().numpy()
+        bad = int((got != ref_t).sum())
+        assert bad == 0, f"tensor {name}: {bad} of {ref_t.size} elements differ"
+    assert np.array_equal(out.cpu().numpy(), want)
+    # CUDA-graph replay and the host-buffer entry give the same logits
+    xd = torch.from_numpy(x).cuda()
+    fn.capture(xd)
+    assert torch.equal(fn.replay(xd), out)
+    host = fn.invoke_host(x)
+    assert np.array_equal(host.numpy(), want)
+    fn.close()
