@@ -691,7 +691,9 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
     NNCB_CUDA_TRY(cudaMemcpyAsync(tp->d_ycls, ycls.data(), ycls.size(), cudaMemcpyHostToDevice, ctx->stream));
     NNCB_CUDA_TRY(cudaMemcpyAsync(tp->d_xcls, xcls.data(), xcls.size(), cudaMemcpyHostToDevice, ctx->stream));
     NNCB_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
-    NNCB_CUDA_TRY(cudaFuncSetAttribute(tc_conv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tp->smem_bytes));
+    // The limit is a property of the function, not of the plan: raise it once to the most any
+    // plan can ask for (stages are sized to stay under 200 KiB + alignment slack).
+    NNCB_CUDA_TRY(cudaFuncSetAttribute(tc_conv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
     return 0;
 }
 
