@@ -87,6 +87,10 @@ NNCB_API int nncb_dequantize_host(nncb_context *ctx, const void *in, float *out,
 /* Module input/output stages: the reference's tensors are NCHW f32 at the module boundary;
  * the kernels keep u8 NHWC inside. c_pad >= c pads the channel dimension with the zero point. */
 NNCB_API int nncb_quantize_nchw_to_nhwc_u8(nncb_context *ctx, const float *in, uint8_t *out, int n, int c, int h, int w, int c_pad, float scale, int32_t zero_point);
+/* Quantize + space-to-depth(2): out[n][Y][X][(dy*2+dx)*c + ch] = quantize(in[n][ch][2Y+dy][2X+dx]),
+ * channels 4c..c_pad-1 = zero point (c_pad 16 or 32; h, w even). A stride-2 convolution over few
+ * input channels becomes a stride-1 convolution over c_pad channels with rearranged weights. */
+NNCB_API int nncb_quantize_nchw_to_s2d_u8(nncb_context *ctx, const float *in, uint8_t *out, int n, int c, int h, int w, int c_pad, float scale, int32_t zero_point);
 NNCB_API int nncb_dequantize_nhwc_to_nchw_f32(nncb_context *ctx, const uint8_t *in, float *out, int n, int h, int w, int c, float scale, int32_t zero_point);
 /* u8 layout changes without arithmetic */
 NNCB_API int nncb_nchw_to_nhwc_u8(nncb_context *ctx, const uint8_t *in, uint8_t *out, int n, int c, int h, int w);

@@ -140,6 +140,36 @@ def quantize_weights(w_oihw, w_quant_type="uint8", c_pad=None):
     return q, zps, scales
 
 
+def space_to_depth_conv(wq_ohwi, zw, pad, in_hw, c_pad=32):
+    """Rewrites a stride-2 convolution over few channels as a stride-1 convolution over the
+    space-to-depth(2) input [h/2, w/2, c_pad] (channel (dy*2+dx)*c + ch). Every product of the
+    original convolution appears exactly once; added taps and channels get the weight zero point
+    and contribute (w - zw) = 0. Returns (weights [oc][k2h][k2w][c_pad], pad (t, b, l, r))."""
+    oc, kh, kw, c = wq_ohwi.shape
+    h, w = in_hw
+    assert h % 2 == 0 and w % 2 == 0 and 4 * c <= c_pad
+
+    def dim(k, p_before, p_after, size):
+        off = p_before % 2                    # a leading dummy row keeps cells aligned to even rows
+        k2 = (k + off + 1) // 2
+        out = (size + p_before + p_after - k) // 2 + 1
+        pb = (p_before + off) // 2
+        pa = out - 1 + k2 - size // 2 - pb
+        assert pa >= 0
+        return off, k2, pb, pa
+
+    offy, k2h, pt, pb = dim(kh, pad[0], pad[1], h)
+    offx, k2w, pl, pr = dim(kw, pad[2], pad[3], w)
+    new = np.empty((oc, k2h, k2w, c_pad), wq_ohwi.dtype)
+    new[...] = np.asarray(zw).reshape(oc, 1, 1, 1).astype(wq_ohwi.dtype)
+    for ky in range(kh):
+        ty, dy = divmod(ky + offy, 2)
+        for kx in range(kw):
+            tx, dx = divmod(kx + offx, 2)
+            new[:, ty, tx, (dy * 2 + dx) * c:(dy * 2 + dx) * c + c] = wq_ohwi[:, ky, kx, :]
+    return np.ascontiguousarray(new), (pt, pb, pl, pr)
+
+
 def _pad_channels(c):
     """Channel counts the tensor-core kernel accepts need no padding; tiny ones pad to 4."""
     return 4 if c < 4 else c
@@ -161,22 +191,40 @@ def build_program(graph, calib_samples, w_quant_type="uint8", device="cpu"):
         op = nd["op"]
         if op == "input":
             c, h, w = nd["shape"]
-            cp = _pad_channels(c)
-            add_tensor(nd["out"], cp, h, w, qps[nd["out"]])
-            ops.append(dict(op="quantize_input", out=nd["out"], c=c, c_pad=cp))
+            users = [u for u in graph if u.get("in") == nd["out"] or u.get("res") == nd["out"]]
+            s2d = (len(users) == 1 and users[0]["op"] == "conv" and tuple(users[0]["stride"]) == (2, 2) and
+                   users[0]["groups"] == 1 and tuple(users[0]["dil"]) == (1, 1) and c <= 8 and h % 2 == 0 and
+                   w % 2 == 0)
+            if s2d:
+                # image stem: quantize straight into the space-to-depth layout (see space_to_depth_conv)
+                add_tensor(nd["out"], 32, h // 2, w // 2, qps[nd["out"]])
+                ops.append(dict(op="quantize_input", out=nd["out"], c=c, c_pad=32, s2d=True))
+                s2d_of = {nd["out"]: (c, h, w)}
+            else:
+                cp = _pad_channels(c)
+                add_tensor(nd["out"], cp, h, w, qps[nd["out"]])
+                ops.append(dict(op="quantize_input", out=nd["out"], c=c, c_pad=cp))
+                s2d_of = {}
             in_name = nd["out"]
         elif op == "conv":
             c, h, w = shapes[nd["in"]]
-            wq, zw, sw = quantize_weights(nd["w"], w_quant_type, c if nd["groups"] == 1 else None)
+            stride, pad = nd["stride"], nd["pad"]
+            if nd["in"] in s2d_of:
+                c0, h0, w0 = s2d_of[nd["in"]]
+                wq, zw, sw = quantize_weights(nd["w"], w_quant_type)
+                wq, pad = space_to_depth_conv(wq, zw, pad, (h0, w0), c)
+                stride = (1, 1)
+            else:
+                wq, zw, sw = quantize_weights(nd["w"], w_quant_type, c if nd["groups"] == 1 else None)
             oc, kh, kw, _ = wq.shape
-            oh = (h + nd["pad"][0] + nd["pad"][1] - ((kh - 1) * nd["dil"][0] + 1)) // nd["stride"][0] + 1
-            ow = (w + nd["pad"][2] + nd["pad"][3] - ((kw - 1) * nd["dil"][1] + 1)) // nd["stride"][1] + 1
+            oh = (h + pad[0] + pad[1] - ((kh - 1) * nd["dil"][0] + 1)) // stride[0] + 1
+            ow = (w + pad[2] + pad[3] - ((kw - 1) * nd["dil"][1] + 1)) // stride[1] + 1
             xqp = tensors[nd["in"]]["qp"]
             mult = (np.float32(xqp.scale) * sw).astype(np.float32)
             has_res = bool(nd.get("res"))
             o = dict(op="conv", name=nd["name"], **{"in": nd["in"]}, out=nd["out"], w=wq,
-                     w_zp=zw if zw.any() else None, mult=mult, bias=nd["b"].astype(np.float32), stride=nd["stride"],
-                     pad=nd["pad"], dil=nd["dil"], groups=nd["groups"], clamp=_ACT_CLAMP[nd["act"]],
+                     w_zp=zw if zw.any() else None, mult=mult, bias=nd["b"].astype(np.float32), stride=tuple(stride),
+                     pad=tuple(pad), dil=nd["dil"], groups=nd["groups"], clamp=_ACT_CLAMP[nd["act"]],
                      res=nd.get("res"), y2=nd.get("relu_out"),
                      conv_qp=qps[nd["out"] + "@conv"] if has_res else qps[nd["out"]])
             add_tensor(nd["out"], oc, oh, ow, qps[nd["out"]])

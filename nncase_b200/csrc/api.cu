@@ -72,6 +72,7 @@ EpiParams make_epi(const nncb_qconv2d *cv) {
 int quantize(nncb_context *, const float *, void *, size_t, float, int32_t, int);
 int dequantize(nncb_context *, const void *, float *, size_t, float, int32_t, int);
 int quantize_nchw_to_nhwc_u8(nncb_context *, const float *, uint8_t *, int, int, int, int, int, float, int32_t);
+int quantize_nchw_to_s2d_u8(nncb_context *, const float *, uint8_t *, int, int, int, int, int, float, int32_t);
 int dequantize_nhwc_to_nchw_f32(nncb_context *, const uint8_t *, float *, int, int, int, int, float, int32_t);
 int nchw_to_nhwc_u8(nncb_context *, const uint8_t *, uint8_t *, int, int, int, int);
 int nhwc_to_nchw_u8(nncb_context *, const uint8_t *, uint8_t *, int, int, int, int);
@@ -310,6 +311,10 @@ int nncb_dequantize_host(nncb_context *ctx, const void *in, float *out, size_t n
 int nncb_quantize_nchw_to_nhwc_u8(nncb_context *ctx, const float *in, uint8_t *out, int n, int c, int h, int w, int c_pad, float scale, int32_t zp) {
     CHECK_CTX(ctx);
     return quantize_nchw_to_nhwc_u8(ctx, in, out, n, c, h, w, c_pad, scale, zp);
+}
+int nncb_quantize_nchw_to_s2d_u8(nncb_context *ctx, const float *in, uint8_t *out, int n, int c, int h, int w, int c_pad, float scale, int32_t zp) {
+    CHECK_CTX(ctx);
+    return quantize_nchw_to_s2d_u8(ctx, in, out, n, c, h, w, c_pad, scale, zp);
 }
 int nncb_dequantize_nhwc_to_nchw_f32(nncb_context *ctx, const uint8_t *in, float *out, int n, int h, int w, int c, float scale, int32_t zp) {
     CHECK_CTX(ctx);

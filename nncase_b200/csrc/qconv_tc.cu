@@ -25,6 +25,7 @@
 //   the role records a code in the context's status word, raises a block-wide abort flag and
 //   all roles leave their loops, free tensor memory and return.
 #include "qconv.cuh"
+#include <cmath>
 #include <vector>
 
 namespace nncb {
@@ -58,6 +59,7 @@ struct TcGeom {
     int f32_out;
 };
 
+struct FastEpi;
 struct TcPlan {
     TcGeom g;
     void *d_wpack = nullptr;       // [n_tiles][bn_mma][K] packed weights
@@ -71,6 +73,13 @@ struct TcPlan {
     CUtensorMap tmap_a;
     const void *a_ptr = nullptr;
     size_t smem_bytes = 0;
+    // fast epilogue
+    bool fast = false;
+    FastEpi *f = nullptr;
+    float4 *d_cst = nullptr;
+    float2 *d_ex = nullptr;
+    CUtensorMap tmap_y, tmap_y2, tmap_res;
+    const void *y_ptr = nullptr, *y2_ptr = nullptr, *res_ptr = nullptr;
 };
 
 typedef CUresult (*PFN_encodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -287,9 +296,23 @@ __device__ __forceinline__ void tmem_ld1(uint32_t taddr, int &r) {
 
 } // namespace dev
 
+// Extra constants of the fast epilogue (see epilogue_fast below).
+struct FastEpi {
+    uint32_t off_out, off_y2, off_res, off_cst, off_ex, off_corr, off_lut2; // byte offsets from the aligned smem base
+    int corr_pitch;     // bn + 1: distinct border classes fall into distinct banks
+    int n_cls;
+    int out_sw;         // swizzle span of the staging tiles: 128, 64, 32 or 0
+    float thr1, thr2;   // 0.5 - error bound of the fast formulas (first stage, residual stage)
+    float qlo, qhi;     // fused clamp mapped into the quantized domain
+    float ca, cb, cc;   // residual stage: t2 = q*ca + r*cb + cc
+    const float4 *cst;  // [oc_pad] {A, B, bits(corr of class 0), bits(-zw)}
+    const float2 *ex;   // [oc_pad] {mult, bias} for the exact path
+};
+
 struct TcArgs {
     TcGeom g;
     EpiParams p;
+    FastEpi f;
     const int32_t *corr;  // [n_cls][oc_pad]
     const int32_t *cnt;   // [n_cls]
     const uint8_t *ycls, *xcls;
@@ -301,47 +324,51 @@ struct TcArgs {
     int *status;
 };
 
-enum { ERR_PRODUCER = 101, ERR_MMA_FULL = 102, ERR_MMA_ACC = 103, ERR_EPILOGUE = 104 };
+enum { ERR_PRODUCER = 101, ERR_MMA_FULL = 102, ERR_MMA_ACC = 103, ERR_EPILOGUE = 104, ERR_RESIDUAL = 105 };
 
-constexpr int TC_THREADS = 192;
+constexpr int EPI_WARPS = 8;
+constexpr int TC_THREADS = 64 + 32 * EPI_WARPS;
 constexpr int MAX_STAGES = 8;
+constexpr float MAGIC = 12582912.0f; // 1.5 * 2^23: adding it rounds a float to an integer in its low mantissa bits
 
-__global__ void __launch_bounds__(TC_THREADS, 1)
-tc_conv_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-               const TcArgs a) {
-    using namespace dev;
-    extern __shared__ uint8_t smem_raw[];
-    const TcGeom &g = a.g;
+struct TcShared {
+    uint64_t bar_full[MAX_STAGES], bar_empty[MAX_STAGES], bar_acc_full[2], bar_acc_empty[2], bar_res;
+    uint32_t tmem_base_slot;
+    volatile int abort_flag;
+};
+
+struct StageGeom {
+    uint32_t smem_base, a_stage_bytes, b_stage_bytes, stage_pitch;
+};
+
+__device__ __forceinline__ StageGeom stage_geom(const TcGeom &g, const uint8_t *smem_raw) {
+    StageGeom sg;
     // stage ring, 1024-byte aligned (required by the 128-byte swizzle)
-    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t a_stage_bytes = 128u * g.kb;
-    const uint32_t b_stage_bytes = (uint32_t)g.bn_mma * g.kb;
-    // keep every stage's A and B tile 1024-byte aligned
-    const uint32_t b_stage_pitch = (b_stage_bytes + 1023u) & ~1023u;
-    const uint32_t stage_pitch = a_stage_bytes + b_stage_pitch; // a_stage_bytes is a multiple of 1024 for kb >= 8
+    sg.smem_base = (dev::smem_u32(smem_raw) + 1023u) & ~1023u;
+    sg.a_stage_bytes = 128u * g.kb;
+    sg.b_stage_bytes = (uint32_t)g.bn_mma * g.kb;
+    // keep every stage's A and B tile 1024-byte aligned (a_stage_bytes is a multiple of 1024)
+    sg.stage_pitch = sg.a_stage_bytes + ((sg.b_stage_bytes + 1023u) & ~1023u);
+    return sg;
+}
 
-    __shared__ __align__(8) uint64_t bar_full[MAX_STAGES], bar_empty[MAX_STAGES], bar_acc_full[2], bar_acc_empty[2];
-    __shared__ uint32_t tmem_base_slot;
-    __shared__ volatile int abort_flag;
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int k_blocks = g.taps * g.c_blocks;
-    const int total_tiles = g.m_tiles * g.n_tiles;
-
+__device__ __forceinline__ void tc_setup(const TcGeom &g, TcShared &sh, int warp) {
+    using namespace dev;
     if (threadIdx.x == 0) {
-        abort_flag = 0;
+        sh.abort_flag = 0;
         for (int s = 0; s < g.stages; s++) {
-            mbar_init(smem_u32(&bar_full[s]), 1);
-            mbar_init(smem_u32(&bar_empty[s]), 1);
+            mbar_init(smem_u32(&sh.bar_full[s]), 1);
+            mbar_init(smem_u32(&sh.bar_empty[s]), 1);
         }
         for (int b = 0; b < 2; b++) {
-            mbar_init(smem_u32(&bar_acc_full[b]), 1);
-            mbar_init(smem_u32(&bar_acc_empty[b]), 4);
+            mbar_init(smem_u32(&sh.bar_acc_full[b]), 1);
+            mbar_init(smem_u32(&sh.bar_acc_empty[b]), EPI_WARPS);
         }
+        mbar_init(smem_u32(&sh.bar_res), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh.tmem_base_slot)),
                      "r"((uint32_t)g.tmem_cols)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -349,187 +376,14 @@ tc_conv_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     fence_before_sync();
     __syncthreads();
     fence_after_sync();
-    const uint32_t tmem_base = tmem_base_slot;
+}
 
-    if (warp == 0) {
-        // ------------------------------- TMA producer -------------------------------
-        if (lane == 0) {
-            uint32_t stage = 0, phase = 0;
-            bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int mt = tile % g.m_tiles, nt = tile / g.m_tiles;
-                const int m0 = mt * 128;
-                int cw = 0, chh = 0, cn = 0;
-                if (g.mode == MODE_IM2COL) {
-                    const int q = m0 % g.ow, pp = (m0 / g.ow) % g.oh;
-                    cn = m0 / (g.ow * g.oh);
-                    cw = q * g.stride_w - g.pad_l;
-                    chh = pp * g.stride_h - g.pad_t;
-                }
-                for (int kbi = 0; kbi < k_blocks; kbi++) {
-                    if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1, &abort_flag, a.status, ERR_PRODUCER)) {
-                        ok = false;
-                        break;
-                    }
-                    const uint32_t full = smem_u32(&bar_full[stage]);
-                    const uint32_t sa = smem_base + stage * stage_pitch, sb = sa + a_stage_bytes;
-                    mbar_expect_tx(full, a_stage_bytes + b_stage_bytes);
-                    const int tap = kbi / g.c_blocks, cb = kbi % g.c_blocks;
-                    if (g.mode == MODE_GEMM) {
-                        tma_load_2d(sa, &tmap_a, full, cb * g.kb, m0);
-                    } else {
-                        const int ky = tap / g.kw, kx = tap % g.kw;
-                        tma_load_im2col_4d(sa, &tmap_a, full, cb * g.kb, cw, chh, cn, (uint16_t)(kx * g.dil_w),
-                                           (uint16_t)(ky * g.dil_h));
-                    }
-                    tma_load_2d(sb, &tmap_b, full, kbi * g.kb, nt * g.bn_mma);
-                    if (++stage == (uint32_t)g.stages) {
-                        stage = 0;
-                        phase ^= 1;
-                    }
-                }
-            }
-        }
-    } else if (warp == 1) {
-        // ------------------------------- MMA issuer ---------------------------------
-        if (lane == 0) {
-            uint32_t stage = 0, phase = 0;
-            uint32_t acc_phase[2] = {0, 0};
-            int it = 0;
-            bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, it++) {
-                const int buf = it & 1;
-                if (!mbar_wait(smem_u32(&bar_acc_empty[buf]), acc_phase[buf] ^ 1, &abort_flag, a.status, ERR_MMA_ACC)) {
-                    ok = false;
-                    break;
-                }
-                acc_phase[buf] ^= 1;
-                fence_after_sync();
-                const uint32_t tmem_d = tmem_base + buf * g.acc_stride;
-                for (int kbi = 0; kbi < k_blocks; kbi++) {
-                    if (!mbar_wait(smem_u32(&bar_full[stage]), phase, &abort_flag, a.status, ERR_MMA_FULL)) {
-                        ok = false;
-                        break;
-                    }
-                    fence_after_sync();
-                    const uint32_t sa = smem_base + stage * stage_pitch, sb = sa + a_stage_bytes;
-                    const uint64_t da = smem_desc(sa, g.kb), db = smem_desc(sb, g.kb);
-                    const int kk = g.kb / 32;
-                    for (int k = 0; k < kk; k++)
-                        mma_i8(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), g.idesc, (kbi | k) != 0);
-                    mma_commit(smem_u32(&bar_empty[stage])); // frees the stage when these MMAs retire
-                    if (++stage == (uint32_t)g.stages) {
-                        stage = 0;
-                        phase ^= 1;
-                    }
-                }
-                if (ok)
-                    mma_commit(smem_u32(&bar_acc_full[buf]));
-            }
-        }
-    } else {
-        // ------------------------------- epilogue -----------------------------------
-        const int lane_group = warp & 3; // TMEM lanes 32*lane_group .. +31 are this warp's
-        const int row = lane_group * 32 + lane;
-        uint32_t acc_phase[2] = {0, 0};
-        int it = 0;
-        bool ok = true;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, it++) {
-            const int buf = it & 1;
-            const int mt = tile % g.m_tiles, nt = tile / g.m_tiles;
-            const int m = mt * 128 + row;
-            const bool row_ok = m < g.m_total;
-            // border class of this output pixel
-            int cls = 0;
-            if (g.mode == MODE_IM2COL && row_ok) {
-                const int ox = m % g.ow, oy = (m / g.ow) % g.oh;
-                cls = (int)a.ycls[oy] * g.n_cls_x + (int)a.xcls[ox];
-            }
-            if (!mbar_wait(smem_u32(&bar_acc_full[buf]), acc_phase[buf], &abort_flag, a.status, ERR_EPILOGUE)) {
-                ok = false;
-                break;
-            }
-            acc_phase[buf] ^= 1;
-            fence_after_sync();
-            const uint32_t tbase = tmem_base + ((uint32_t)(lane_group * 32) << 16) + buf * g.acc_stride;
-            int rsum = 0; // sum_valid xq - cnt_valid * zx
-            if (g.has_xsum) {
-                int xs;
-                tmem_ld1(tbase + g.bn, xs);
-                rsum = xs - a.cnt[cls] * g.x_zp;
-            }
-            const int32_t *corr = a.corr + (size_t)cls * a.oc_pad;
-            const int oc0 = nt * g.bn;
-            for (int c0 = 0; c0 < g.bn; c0 += 16) {
-                int v[16];
-                __syncwarp();
-                tmem_ld16(tbase + c0, v);
-                if (!row_ok || oc0 + c0 >= g.oc)
-                    continue;
-                const size_t obase = (size_t)m * g.oc + oc0 + c0;
-                if (g.f32_out) {
-                    float *yo = reinterpret_cast<float *>(a.y) + obase;
-#pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        const int oc = oc0 + c0 + j;
-                        if (oc < g.oc) {
-                            int acc = v[j] - corr[oc] - a.w_zp[oc] * rsum;
-                            yo[j] = epi_real(acc, a.p.mult[oc], a.p.bias[oc], a.p.clamp_lo, a.p.clamp_hi);
-                        }
-                    }
-                    continue;
-                }
-                uint32_t pk[4] = {0, 0, 0, 0}, pk2[4] = {0, 0, 0, 0};
-                const bool full16 = (oc0 + c0 + 16 <= g.oc) && ((obase & 15) == 0);
-                uint32_t rs[4] = {0, 0, 0, 0};
-                if (a.p.has_res) {
-                    if (full16) {
-                        uint4 r4 = *reinterpret_cast<const uint4 *>(a.res + obase);
-                        rs[0] = r4.x, rs[1] = r4.y, rs[2] = r4.z, rs[3] = r4.w;
-                    } else {
-                        for (int j = 0; j < 16; j++)
-                            if (oc0 + c0 + j < g.oc)
-                                rs[j >> 2] |= (uint32_t)a.res[obase + j] << (8 * (j & 3));
-                    }
-                }
-#pragma unroll
-                for (int j = 0; j < 16; j++) {
-                    const int oc = oc0 + c0 + j;
-                    if (oc < g.oc) {
-                        int acc = v[j] - corr[oc] - a.w_zp[oc] * rsum;
-                        int q = epi_u8(acc, a.p.mult[oc], a.p.bias[oc], a.p, (int)((rs[j >> 2] >> (8 * (j & 3))) & 255));
-                        pk[j >> 2] |= (uint32_t)q << (8 * (j & 3));
-                        if (a.y2)
-                            pk2[j >> 2] |= (uint32_t)a.p.y2_lut[q] << (8 * (j & 3));
-                    }
-                }
-                uint8_t *yo = reinterpret_cast<uint8_t *>(a.y) + obase;
-                if (full16) {
-                    *reinterpret_cast<uint4 *>(yo) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                    if (a.y2)
-                        *reinterpret_cast<uint4 *>(a.y2 + obase) = make_uint4(pk2[0], pk2[1], pk2[2], pk2[3]);
-                } else {
-                    for (int j = 0; j < 16; j++)
-                        if (oc0 + c0 + j < g.oc) {
-                            yo[j] = (uint8_t)(pk[j >> 2] >> (8 * (j & 3)));
-                            if (a.y2)
-                                a.y2[obase + j] = (uint8_t)(pk2[j >> 2] >> (8 * (j & 3)));
-                        }
-                }
-            }
-            // this accumulator may be overwritten once all four epilogue warps are done reading
-            fence_before_sync();
-            __syncwarp();
-            if (lane == 0)
-                mbar_arrive(smem_u32(&bar_acc_empty[buf]));
-        }
-    }
-
-    // teardown: everyone arrives here, also after an abort
-    if (abort_flag) {
+__device__ __forceinline__ void tc_teardown(const TcGeom &g, TcShared &sh, int warp, uint32_t tmem_base) {
+    using namespace dev;
+    if (sh.abort_flag) {
         // give loads that are still in flight time to land before shared memory is released
-        const uint64_t t0 = dev::globaltimer_ns();
-        while (dev::globaltimer_ns() - t0 < 200000ull) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) {
         }
     }
     fence_before_sync();
@@ -539,6 +393,474 @@ tc_conv_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)g.tmem_cols)
                      : "memory");
     }
+}
+
+// warp 0, one lane: fills the stage ring with the A (activation) and B (weight) tiles of every
+// K block of every tile this CTA owns.
+__device__ __forceinline__ void producer_loop(const TcGeom &g, const StageGeom &sg, TcShared &sh,
+                                              const CUtensorMap *tmap_a, const CUtensorMap *tmap_b, int *status) {
+    using namespace dev;
+    const int k_blocks = g.taps * g.c_blocks;
+    const int total_tiles = g.m_tiles * g.n_tiles;
+    uint32_t stage = 0, phase = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        const int mt = tile % g.m_tiles, nt = tile / g.m_tiles;
+        const int m0 = mt * 128;
+        int cw = 0, chh = 0, cn = 0;
+        if (g.mode == MODE_IM2COL) {
+            const int q = m0 % g.ow, pp = (m0 / g.ow) % g.oh;
+            cn = m0 / (g.ow * g.oh);
+            cw = q * g.stride_w - g.pad_l;
+            chh = pp * g.stride_h - g.pad_t;
+        }
+        for (int kbi = 0; kbi < k_blocks; kbi++) {
+            if (!mbar_wait(smem_u32(&sh.bar_empty[stage]), phase ^ 1, &sh.abort_flag, status, ERR_PRODUCER))
+                return;
+            const uint32_t full = smem_u32(&sh.bar_full[stage]);
+            const uint32_t sa = sg.smem_base + stage * sg.stage_pitch, sb = sa + sg.a_stage_bytes;
+            mbar_expect_tx(full, sg.a_stage_bytes + sg.b_stage_bytes);
+            const int tap = kbi / g.c_blocks, cb = kbi % g.c_blocks;
+            if (g.mode == MODE_GEMM) {
+                tma_load_2d(sa, tmap_a, full, cb * g.kb, m0);
+            } else {
+                const int ky = tap / g.kw, kx = tap % g.kw;
+                tma_load_im2col_4d(sa, tmap_a, full, cb * g.kb, cw, chh, cn, (uint16_t)(kx * g.dil_w),
+                                   (uint16_t)(ky * g.dil_h));
+            }
+            tma_load_2d(sb, tmap_b, full, kbi * g.kb, nt * g.bn_mma);
+            if (++stage == (uint32_t)g.stages) {
+                stage = 0;
+                phase ^= 1;
+            }
+        }
+    }
+}
+
+// warp 1, one lane: issues the MMAs of every K block into the tile's TMEM accumulator.
+__device__ __forceinline__ void mma_loop(const TcGeom &g, const StageGeom &sg, TcShared &sh, uint32_t tmem_base,
+                                         int *status) {
+    using namespace dev;
+    const int k_blocks = g.taps * g.c_blocks;
+    const int total_tiles = g.m_tiles * g.n_tiles;
+    uint32_t stage = 0, phase = 0;
+    uint32_t acc_phase0 = 0, acc_phase1 = 0;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, it++) {
+        const int buf = it & 1;
+        const uint32_t ph = buf ? acc_phase1 : acc_phase0;
+        if (!mbar_wait(smem_u32(&sh.bar_acc_empty[buf]), ph ^ 1, &sh.abort_flag, status, ERR_MMA_ACC))
+            return;
+        if (buf)
+            acc_phase1 ^= 1;
+        else
+            acc_phase0 ^= 1;
+        fence_after_sync();
+        const uint32_t tmem_d = tmem_base + buf * g.acc_stride;
+        for (int kbi = 0; kbi < k_blocks; kbi++) {
+            if (!mbar_wait(smem_u32(&sh.bar_full[stage]), phase, &sh.abort_flag, status, ERR_MMA_FULL))
+                return;
+            fence_after_sync();
+            const uint32_t sa = sg.smem_base + stage * sg.stage_pitch, sb = sa + sg.a_stage_bytes;
+            const uint64_t da = smem_desc(sa, g.kb), db = smem_desc(sb, g.kb);
+            const int kk = g.kb / 32;
+            for (int k = 0; k < kk; k++)
+                mma_i8(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), g.idesc, (kbi | k) != 0);
+            mma_commit(smem_u32(&sh.bar_empty[stage])); // frees the stage when these MMAs retire
+            if (++stage == (uint32_t)g.stages) {
+                stage = 0;
+                phase ^= 1;
+            }
+        }
+        mma_commit(smem_u32(&sh.bar_acc_full[buf]));
+    }
+}
+
+// -------------------------------------------------------------------------------------------------
+// generic epilogue: exact arithmetic per element, direct global stores. Takes every case
+// (f32 output, activation table, channel counts that are not a multiple of 16).
+// -------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void epilogue_generic(const TcArgs &a, TcShared &sh, uint32_t tmem_base, int warp, int lane) {
+    using namespace dev;
+    const TcGeom &g = a.g;
+    const int total_tiles = g.m_tiles * g.n_tiles;
+    const int ew = warp - 2;
+    const int lane_group = warp & 3; // TMEM lanes 32*lane_group .. +31 are this warp's
+    const int half = ew >> 2;        // two warps share a lane group and alternate 16-column chunks
+    const int row = lane_group * 32 + lane;
+    uint32_t acc_phase0 = 0, acc_phase1 = 0;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, it++) {
+        const int buf = it & 1;
+        const int mt = tile % g.m_tiles, nt = tile / g.m_tiles;
+        const int m = mt * 128 + row;
+        const bool row_ok = m < g.m_total;
+        int cls = 0; // border class of this output pixel
+        if (g.mode == MODE_IM2COL && row_ok) {
+            const int ox = m % g.ow, oy = (m / g.ow) % g.oh;
+            cls = (int)a.ycls[oy] * g.n_cls_x + (int)a.xcls[ox];
+        }
+        const uint32_t ph = buf ? acc_phase1 : acc_phase0;
+        if (!mbar_wait(smem_u32(&sh.bar_acc_full[buf]), ph, &sh.abort_flag, a.status, ERR_EPILOGUE))
+            return;
+        if (buf)
+            acc_phase1 ^= 1;
+        else
+            acc_phase0 ^= 1;
+        fence_after_sync();
+        const uint32_t tbase = tmem_base + ((uint32_t)(lane_group * 32) << 16) + buf * g.acc_stride;
+        int rsum = 0; // sum_valid xq - cnt_valid * zx
+        if (g.has_xsum) {
+            int xs;
+            tmem_ld1(tbase + g.bn, xs);
+            rsum = xs - a.cnt[cls] * g.x_zp;
+        }
+        const int32_t *corr = a.corr + (size_t)cls * a.oc_pad;
+        const int oc0 = nt * g.bn;
+        for (int c0 = half * 16; c0 < g.bn; c0 += 32) {
+            int v[16];
+            __syncwarp();
+            tmem_ld16(tbase + c0, v);
+            if (!row_ok || oc0 + c0 >= g.oc)
+                continue;
+            const size_t obase = (size_t)m * g.oc + oc0 + c0;
+            if (g.f32_out) {
+                float *yo = reinterpret_cast<float *>(a.y) + obase;
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    const int oc = oc0 + c0 + j;
+                    if (oc < g.oc) {
+                        int acc = v[j] - corr[oc] - a.w_zp[oc] * rsum;
+                        yo[j] = epi_real(acc, a.p.mult[oc], a.p.bias[oc], a.p.clamp_lo, a.p.clamp_hi);
+                    }
+                }
+                continue;
+            }
+            uint32_t pk[4] = {0, 0, 0, 0}, pk2[4] = {0, 0, 0, 0};
+            const bool full16 = (oc0 + c0 + 16 <= g.oc) && ((obase & 15) == 0);
+            uint32_t rs[4] = {0, 0, 0, 0};
+            if (a.p.has_res) {
+                if (full16) {
+                    uint4 r4 = *reinterpret_cast<const uint4 *>(a.res + obase);
+                    rs[0] = r4.x, rs[1] = r4.y, rs[2] = r4.z, rs[3] = r4.w;
+                } else {
+                    for (int j = 0; j < 16; j++)
+                        if (oc0 + c0 + j < g.oc)
+                            rs[j >> 2] |= (uint32_t)a.res[obase + j] << (8 * (j & 3));
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                const int oc = oc0 + c0 + j;
+                if (oc < g.oc) {
+                    int acc = v[j] - corr[oc] - a.w_zp[oc] * rsum;
+                    int q = epi_u8(acc, a.p.mult[oc], a.p.bias[oc], a.p, (int)((rs[j >> 2] >> (8 * (j & 3))) & 255));
+                    pk[j >> 2] |= (uint32_t)q << (8 * (j & 3));
+                    if (a.y2)
+                        pk2[j >> 2] |= (uint32_t)a.p.y2_lut[q] << (8 * (j & 3));
+                }
+            }
+            uint8_t *yo = reinterpret_cast<uint8_t *>(a.y) + obase;
+            if (full16) {
+                *reinterpret_cast<uint4 *>(yo) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                if (a.y2)
+                    *reinterpret_cast<uint4 *>(a.y2 + obase) = make_uint4(pk2[0], pk2[1], pk2[2], pk2[3]);
+            } else {
+                for (int j = 0; j < 16; j++)
+                    if (oc0 + c0 + j < g.oc) {
+                        yo[j] = (uint8_t)(pk[j >> 2] >> (8 * (j & 3)));
+                        if (a.y2)
+                            a.y2[obase + j] = (uint8_t)(pk2[j >> 2] >> (8 * (j & 3)));
+                    }
+            }
+        }
+        // this accumulator may be overwritten once all epilogue warps are done reading
+        fence_before_sync();
+        __syncwarp();
+        if (lane == 0)
+            mbar_arrive(smem_u32(&sh.bar_acc_empty[buf]));
+    }
+}
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
+tc_conv_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const TcArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) TcShared sh;
+    const TcGeom &g = a.g;
+    const StageGeom sg = stage_geom(g, smem_raw);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    tc_setup(g, sh, warp);
+    const uint32_t tmem_base = sh.tmem_base_slot;
+    if (warp == 0) {
+        if (lane == 0)
+            producer_loop(g, sg, sh, &tmap_a, &tmap_b, a.status);
+    } else if (warp == 1) {
+        if (lane == 0)
+            mma_loop(g, sg, sh, tmem_base, a.status);
+    } else {
+        epilogue_generic(a, sh, tmem_base, warp, lane);
+    }
+    tc_teardown(g, sh, warp, tmem_base);
+}
+
+// -------------------------------------------------------------------------------------------------
+// fast epilogue (u8 output, channel count a multiple of 16, no activation table).
+//
+// The exact requantisation  q = rint(clamp(fl(fl(acc)*mult) + bias) / so + zo)  costs four
+// dependent IEEE operations with a division per element. Because that map is monotone in acc, it
+// equals  clamp_q(rint(t))  with  t = acc*A + B  (A = mult/so, B = bias/so + zo, one fused
+// multiply-add) whenever t is not within `eps` of a rounding boundary, eps being a bound on the
+// accumulated rounding error of both formulas computed at plan creation. Elements inside the
+// guard band (a few per ten thousand) are recomputed with the exact formula, so results stay
+// bit-identical. Rounding uses the add-magic-constant trick, the clamp of the real value is
+// applied as a clamp of the quantized value, and the residual add gets the same treatment
+// (t2 = q*ca + r*cb + cc). Per-channel constants are staged in shared memory per N tile and
+// read as one broadcast 16-byte load per element; outputs (and the optional second output) are
+// staged in swizzled shared-memory tiles and written with TMA stores; the residual tile is
+// prefetched with a TMA load.
+// -------------------------------------------------------------------------------------------------
+namespace dev {
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(32 * EPI_WARPS) : "memory"); }
+__device__ __forceinline__ bool epi_bar_or(bool v) {
+    uint32_t out;
+    asm volatile("{\n.reg .pred p, q;\nsetp.ne.u32 q, %1, 0;\nbar.red.or.pred p, 1, %2, q;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(out)
+                 : "r"((uint32_t)v), "n"(32 * EPI_WARPS)
+                 : "memory");
+    return out != 0;
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src),
+                 "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds8(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float4 lds128f(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+// address of 16-byte chunk `chunk` of row `row` in a staging tile whose rows are `bn` bytes and
+// which TMA reads / writes with swizzle span `sw`
+__device__ __forceinline__ uint32_t stage_addr(uint32_t base, int row, int chunk, int bn, int sw) {
+    const int x = sw == 128 ? (row & 7) : (sw == 64 ? ((row >> 1) & 3) : (sw == 32 ? ((row >> 2) & 1) : 0));
+    return base + (uint32_t)(row * bn) + (uint32_t)((chunk ^ x) << 4);
+}
+} // namespace dev
+
+template <bool RES, bool Y2>
+__device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &sg, TcShared &sh, uint32_t tmem_base,
+                                              const CUtensorMap *tmap_y, const CUtensorMap *tmap_y2,
+                                              const CUtensorMap *tmap_res, int warp, int lane) {
+    using namespace dev;
+    const TcGeom &g = a.g;
+    const FastEpi &f = a.f;
+    const int total_tiles = g.m_tiles * g.n_tiles;
+    const int ew = warp - 2;
+    const int et = ew * 32 + lane;   // index among the epilogue threads
+    const int lane_group = warp & 3; // TMEM lanes 32*lane_group .. +31 are this warp's
+    const int half = ew >> 2;
+    const int row = lane_group * 32 + lane;
+    const bool leader = et == 0;
+    const uint32_t s_out = sg.smem_base + f.off_out, s_y2 = sg.smem_base + f.off_y2, s_res = sg.smem_base + f.off_res;
+    const uint32_t s_cst = sg.smem_base + f.off_cst, s_ex = sg.smem_base + f.off_ex, s_corr = sg.smem_base + f.off_corr;
+    const uint32_t s_lut2 = sg.smem_base + f.off_lut2;
+    const bool multi_cls = f.n_cls > 1;
+    const uint32_t res_bytes = 128u * g.bn;
+    if (Y2) {
+        // second-output table: 256 bytes
+        if (et < 64)
+            asm volatile("st.shared.u32 [%0], %1;" ::"r"(s_lut2 + et * 4),
+                         "r"(reinterpret_cast<const uint32_t *>(a.p.y2_lut)[et])
+                         : "memory");
+    }
+    if (RES && leader && (int)blockIdx.x < total_tiles) {
+        const int mt = blockIdx.x % g.m_tiles, nt = blockIdx.x / g.m_tiles;
+        mbar_expect_tx(smem_u32(&sh.bar_res), res_bytes);
+        tma_load_2d(s_res, tmap_res, smem_u32(&sh.bar_res), nt * g.bn, mt * 128);
+    }
+    uint32_t acc_phase0 = 0, acc_phase1 = 0, res_phase = 0;
+    int it = 0, cur_nt = -1;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, it++) {
+        const int buf = it & 1;
+        const int mt = tile % g.m_tiles, nt = tile / g.m_tiles;
+        const int m = mt * 128 + row;
+        const bool row_ok = m < g.m_total;
+        const int oc0 = nt * g.bn;
+        if (nt != cur_nt) {
+            // (re)load the per-channel constants of this N tile; happens once or twice per CTA
+            epi_bar_sync();
+            for (int c = et; c < g.bn; c += 32 * EPI_WARPS) {
+                const float4 k = f.cst[oc0 + c];
+                const float2 e = f.ex[oc0 + c];
+                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(s_cst + c * 16), "f"(k.x), "f"(k.y),
+                             "f"(k.z), "f"(k.w)
+                             : "memory");
+                asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(s_ex + c * 8), "f"(e.x), "f"(e.y) : "memory");
+            }
+            if (multi_cls)
+                for (int i = et; i < f.n_cls * g.bn; i += 32 * EPI_WARPS) {
+                    const int cl = i / g.bn, c = i % g.bn;
+                    asm volatile("st.shared.u32 [%0], %1;" ::"r"(s_corr + (cl * f.corr_pitch + c) * 4),
+                                 "r"(a.corr[(size_t)cl * a.oc_pad + oc0 + c])
+                                 : "memory");
+                }
+            cur_nt = nt;
+            epi_bar_sync();
+        }
+        int cls = 0;
+        if (g.mode == MODE_IM2COL && row_ok) {
+            const int ox = m % g.ow, oy = (m / g.ow) % g.oh;
+            cls = (int)a.ycls[oy] * g.n_cls_x + (int)a.xcls[ox];
+        }
+        const uint32_t ph = buf ? acc_phase1 : acc_phase0;
+        bool ok = mbar_wait(smem_u32(&sh.bar_acc_full[buf]), ph, &sh.abort_flag, a.status, ERR_EPILOGUE);
+        if (RES && ok)
+            ok = mbar_wait(smem_u32(&sh.bar_res), res_phase, &sh.abort_flag, a.status, ERR_RESIDUAL);
+        // the previous tile's TMA stores must have finished reading the staging tiles
+        if (leader)
+            tma_store_wait_read();
+        if (epi_bar_or(!ok))
+            return; // every epilogue warp leaves together
+        if (buf)
+            acc_phase1 ^= 1;
+        else
+            acc_phase0 ^= 1;
+        res_phase ^= 1;
+        fence_after_sync();
+        const uint32_t tbase = tmem_base + ((uint32_t)(lane_group * 32) << 16) + buf * g.acc_stride;
+        int rsum = 0;
+        if (g.has_xsum) {
+            int xs;
+            tmem_ld1(tbase + g.bn, xs);
+            rsum = xs - a.cnt[cls] * g.x_zp;
+        }
+        const uint32_t corr_row = s_corr + (uint32_t)(cls * f.corr_pitch) * 4;
+        for (int c0 = half * 16; c0 < g.bn; c0 += 32) {
+            int v[16];
+            __syncwarp();
+            tmem_ld16(tbase + c0, v);
+            uint4 rw = make_uint4(0, 0, 0, 0);
+            if (RES)
+                rw = lds128(stage_addr(s_res, row, c0 >> 4, g.bn, f.out_sw));
+            const uint32_t rwa[4] = {rw.x, rw.y, rw.z, rw.w};
+            int acc[16];
+            uint32_t bits[16];
+            uint32_t slow = 0; // bit j: element j lies inside the guard band
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                const float4 k = lds128f(s_cst + (c0 + j) * 16);
+                const int corr = multi_cls ? (int)lds32(corr_row + (c0 + j) * 4) : __float_as_int(k.z);
+                acc[j] = v[j] + __float_as_int(k.w) * rsum - corr;
+                const float t = __fmaf_rn((float)acc[j], k.x, k.y);
+                const float rf = __fadd_rn(__fadd_rn(t, MAGIC), -MAGIC);
+                bool bad = !(fabsf(__fadd_rn(t, -rf)) <= f.thr1);
+                float qf = fminf(fmaxf(rf, f.qlo), f.qhi);
+                if (RES) {
+                    const float rb = (float)((rwa[j >> 2] >> (8 * (j & 3))) & 255u);
+                    const float t2 = __fmaf_rn(qf, f.ca, __fmaf_rn(rb, f.cb, f.cc));
+                    const float rf2 = __fadd_rn(__fadd_rn(t2, MAGIC), -MAGIC);
+                    bad |= !(fabsf(__fadd_rn(t2, -rf2)) <= f.thr2);
+                    qf = fminf(fmaxf(rf2, 0.f), 255.f);
+                }
+                slow |= (uint32_t)bad << j;
+                bits[j] = __float_as_uint(__fadd_rn(qf, MAGIC)); // low byte = the quantized value
+            }
+            if (slow) {
+                // inside the guard band (or not finite): the exact formula decides, element by element
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    if (slow & (1u << j)) {
+                        float mult, bias;
+                        asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(mult), "=f"(bias) : "r"(s_ex + (c0 + j) * 8));
+                        bits[j] = (uint32_t)epi_u8(acc[j], mult, bias, a.p, (int)((rwa[j >> 2] >> (8 * (j & 3))) & 255u));
+                    }
+                }
+            }
+            uint4 o;
+            o.x = __byte_perm(__byte_perm(bits[0], bits[1], 0x0040), __byte_perm(bits[2], bits[3], 0x0040), 0x5410);
+            o.y = __byte_perm(__byte_perm(bits[4], bits[5], 0x0040), __byte_perm(bits[6], bits[7], 0x0040), 0x5410);
+            o.z = __byte_perm(__byte_perm(bits[8], bits[9], 0x0040), __byte_perm(bits[10], bits[11], 0x0040), 0x5410);
+            o.w = __byte_perm(__byte_perm(bits[12], bits[13], 0x0040), __byte_perm(bits[14], bits[15], 0x0040), 0x5410);
+            sts128(stage_addr(s_out, row, c0 >> 4, g.bn, f.out_sw), o);
+            if (Y2) {
+                uint32_t w2[4];
+                const uint32_t ow_[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    const uint32_t b0 = lds8(s_lut2 + (ow_[k] & 255u)), b1 = lds8(s_lut2 + ((ow_[k] >> 8) & 255u));
+                    const uint32_t b2 = lds8(s_lut2 + ((ow_[k] >> 16) & 255u)), b3 = lds8(s_lut2 + (ow_[k] >> 24));
+                    w2[k] = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+                }
+                sts128(stage_addr(s_y2, row, c0 >> 4, g.bn, f.out_sw), make_uint4(w2[0], w2[1], w2[2], w2[3]));
+            }
+        }
+        // accumulator and residual tile are consumed; staging tiles are written
+        fence_before_sync();
+        __syncwarp();
+        if (lane == 0)
+            mbar_arrive(smem_u32(&sh.bar_acc_empty[buf]));
+        fence_async_smem();
+        epi_bar_sync();
+        if (leader) {
+            tma_store_2d(tmap_y, s_out, oc0, mt * 128);
+            if (Y2)
+                tma_store_2d(tmap_y2, s_y2, oc0, mt * 128);
+            tma_store_commit();
+            const int next = tile + gridDim.x;
+            if (RES && next < total_tiles) {
+                mbar_expect_tx(smem_u32(&sh.bar_res), res_bytes);
+                tma_load_2d(s_res, tmap_res, smem_u32(&sh.bar_res), (next / g.m_tiles) * g.bn, (next % g.m_tiles) * 128);
+            }
+        }
+    }
+    if (leader)
+        tma_store_wait_all();
+}
+
+template <bool RES, bool Y2>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+tc_conv_fast_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const __grid_constant__ CUtensorMap tmap_y, const __grid_constant__ CUtensorMap tmap_y2,
+                    const __grid_constant__ CUtensorMap tmap_res, const TcArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) TcShared sh;
+    const TcGeom &g = a.g;
+    const StageGeom sg = stage_geom(g, smem_raw);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    tc_setup(g, sh, warp);
+    const uint32_t tmem_base = sh.tmem_base_slot;
+    if (warp == 0) {
+        if (lane == 0)
+            producer_loop(g, sg, sh, &tmap_a, &tmap_b, a.status);
+    } else if (warp == 1) {
+        if (lane == 0)
+            mma_loop(g, sg, sh, tmem_base, a.status);
+    } else {
+        epilogue_fast<RES, Y2>(a, sg, sh, tmem_base, &tmap_y, &tmap_y2, &tmap_res, warp, lane);
+    }
+    tc_teardown(g, sh, warp, tmem_base);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -587,18 +909,29 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
     g.tmem_cols = cols;
     g.idesc = (2u << 4) | (0u << 7) | ((d.w_signed ? 1u : 0u) << 10) | ((uint32_t)(g.bn_mma >> 3) << 17) |
               ((uint32_t)(128 >> 4) << 24);
+    // ---- fast epilogue: constants, error bounds and shared-memory layout ----
+    const bool fast_shape = !d.f32_out && cv->d_lut == nullptr && d.oc % 16 == 0;
+    tp->f = new FastEpi();
+    FastEpi &fe = *tp->f;
+    memset(&fe, 0, sizeof(fe));
     const uint32_t a_stage = 128u * g.kb, b_pitch = ((uint32_t)g.bn_mma * g.kb + 1023u) & ~1023u;
-    int stages = (int)((200u * 1024u) / (a_stage + b_pitch));
-    if (stages > MAX_STAGES)
-        stages = MAX_STAGES;
-    if (stages < 2)
-        return fail(-ENOSYS, "tcgen05 conv: tile does not fit shared memory");
-    g.stages = stages;
-    // More than half of an SM's shared memory, so exactly one CTA (and one TMEM allocation) per SM.
-    tp->smem_bytes = (size_t)stages * (a_stage + b_pitch) + 1024;
-    if (tp->smem_bytes < 120 * 1024)
-        tp->smem_bytes = 120 * 1024;
-
+    const uint32_t budget = 224u * 1024u - 1024u; // dynamic shared memory we may use, minus alignment slack
+    uint32_t extras = 0;
+    tp->fast = false;
+    if (fast_shape) {
+        const uint32_t tile_bytes = (128u * g.bn + 1023u) & ~1023u;
+        uint32_t off = 0;
+        fe.off_out = off, off += tile_bytes;
+        fe.off_y2 = off, off += d.has_y2 ? tile_bytes : 0;
+        fe.off_res = off, off += d.has_residual ? tile_bytes : 0;
+        fe.off_cst = off, off += (uint32_t)g.bn * 16;
+        fe.off_ex = off, off += (uint32_t)g.bn * 8;
+        fe.off_lut2 = off, off += 256;
+        fe.off_corr = off;
+        extras = off; // the per-class table is appended once the classes are known
+        fe.out_sw = g.bn == 128 ? 128 : (g.bn == 64 ? 64 : (g.bn == 32 ? 32 : 0));
+        tp->fast = true;
+    }
     // ---- weights: [n_tiles][bn_mma][K], K ordered (ky, kx, c) = the OHWI row as given ----
     const size_t K = (size_t)d.kh * d.kw * d.c;
     std::vector<uint8_t> wp((size_t)g.n_tiles * g.bn_mma * K, 0);
@@ -690,10 +1023,109 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
     NNCB_CUDA_TRY(cudaMemcpyAsync(tp->d_cnt, cnt.data(), cnt.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
     NNCB_CUDA_TRY(cudaMemcpyAsync(tp->d_ycls, ycls.data(), ycls.size(), cudaMemcpyHostToDevice, ctx->stream));
     NNCB_CUDA_TRY(cudaMemcpyAsync(tp->d_xcls, xcls.data(), xcls.size(), cudaMemcpyHostToDevice, ctx->stream));
+
+    if (tp->fast) {
+        fe.n_cls = n_cls;
+        fe.corr_pitch = g.bn + 1;
+        if (n_cls > 1)
+            extras += (uint32_t)n_cls * fe.corr_pitch * 4;
+        extras = (extras + 1023u) & ~1023u;
+        // Error bounds, in units of one quantization step. With u = 2^-24 the exact chain
+        // fl(fl(acc)*mult)+bias, /so, +zo and the fused t = fl(acc)*A + B each stay within
+        // u * (a few times the magnitudes involved) of the real-valued result; results that
+        // matter lie in [-1, 256], which bounds |acc*mult/so| by 512 + |bias/so|.
+        double max_b = 0;
+        std::vector<float> hm(d.oc), hb(d.oc);
+        NNCB_CUDA_TRY(cudaMemcpy(hm.data(), cv->d_mult, sizeof(float) * d.oc, cudaMemcpyDeviceToHost));
+        NNCB_CUDA_TRY(cudaMemcpy(hb.data(), cv->d_bias, sizeof(float) * d.oc, cudaMemcpyDeviceToHost));
+        const double so = d.out_scale, zo = d.out_zp;
+        std::vector<float4> cst(tp->oc_pad, make_float4(0, 0, 0, 0));
+        std::vector<float2> ex(tp->oc_pad, make_float2(0, 0));
+        bool finite = true;
+        for (int oc = 0; oc < d.oc; oc++) {
+            const double A = (double)hm[oc] / so, B = (double)hb[oc] / so + zo;
+            finite = finite && std::isfinite(A) && std::isfinite(B) && hm[oc] > 0;
+            max_b = std::fmax(max_b, std::fabs((double)hb[oc] / so));
+            const int32_t c0 = corr[oc], nzw = wzp_host ? -wzp_host[oc] : 0;
+            float4 k;
+            k.x = (float)A, k.y = (float)B;
+            memcpy(&k.z, &c0, 4);
+            memcpy(&k.w, &nzw, 4);
+            cst[oc] = k;
+            ex[oc] = make_float2(hm[oc], hb[oc]);
+        }
+        // Bound (derivation in units of a quantization step, u = 2^-24, X = acc*mult/so, Bq = bias/so,
+        // r = X + Bq + zo the real-valued result, |r| <= 256 and |zo| <= 255 for results that can
+        // change the output): exact chain within u*(|X| + 2|X+Bq| + |r|) of r, fused formula within
+        // u*(|X| + |Bq+zo| + |r|); with |X| <= 512 + |Bq| the sum is u*(2816 + 3|Bq|). Taken with a
+        // 1.5x margin for second-order terms and the rounding of the guard comparison itself.
+        const double u = 1.0 / 16777216.0;
+        const double eps1 = 1.5 * u * (2816.0 + 3.0 * max_b);
+        // quantize() is monotone, so clamping the real value equals clamping the quantized one
+        auto qexact = [&](float v) {
+            if (std::isinf(v))
+                return v > 0 ? 255.f : 0.f;
+            volatile float q1 = v / d.out_scale;
+            volatile float q2 = q1 + (float)d.out_zp;
+            float r = nearbyintf(q2);
+            return r < 0.f ? 0.f : (r > 255.f ? 255.f : r);
+        };
+        fe.qlo = qexact(d.clamp_lo);
+        fe.qhi = qexact(d.clamp_hi);
+        fe.thr1 = (float)(0.5 - eps1);
+        double eps2 = 0;
+        if (d.has_residual) {
+            const double sa = d.add_out_scale, ca = so / sa, cb = (double)d.res_scale / sa;
+            const double cc = (double)d.add_out_zp - zo * ca - (double)d.res_zp * cb;
+            fe.ca = (float)ca, fe.cb = (float)cb, fe.cc = (float)cc;
+            // exact: fl(fl((q-zo)*so) + fl((r-zr)*sr)) / sa + za, four roundings after the two products;
+            // fused: two fma. Magnitudes: |q-zo|*ca and |r-zr|*cb are at most 255*ca, 255*cb; the
+            // result of interest is at most 256 in magnitude, cc is a constant.
+            eps2 = 1.5 * u * (6.0 * 255.0 * (ca + cb) + 3.0 * std::fabs(cc) + 1024.0);
+            finite = finite && std::isfinite(ca) && std::isfinite(cb) && std::isfinite(cc);
+        }
+        fe.thr2 = (float)(0.5 - eps2);
+        if (!finite || !(eps1 < 0.125) || !(eps2 < 0.125) || std::isnan(d.clamp_lo) || std::isnan(d.clamp_hi))
+            tp->fast = false; // degenerate parameters: the generic (exact) epilogue takes the layer
+        if (tp->fast) {
+            NNCB_CUDA_TRY(cudaMalloc(&tp->d_cst, cst.size() * sizeof(float4)));
+            NNCB_CUDA_TRY(cudaMalloc(&tp->d_ex, ex.size() * sizeof(float2)));
+            NNCB_CUDA_TRY(cudaMemcpyAsync(tp->d_cst, cst.data(), cst.size() * sizeof(float4), cudaMemcpyHostToDevice, ctx->stream));
+            NNCB_CUDA_TRY(cudaMemcpyAsync(tp->d_ex, ex.data(), ex.size() * sizeof(float2), cudaMemcpyHostToDevice, ctx->stream));
+            fe.cst = tp->d_cst;
+            fe.ex = tp->d_ex;
+        }
+    }
     NNCB_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    if (!tp->fast)
+        extras = 0;
+    if (extras + 2 * (a_stage + b_pitch) > budget) {
+        tp->fast = false; // not enough room for the staging tiles next to two pipeline stages
+        extras = 0;
+    }
+    int stages = (int)((budget - extras) / (a_stage + b_pitch));
+    if (stages > MAX_STAGES)
+        stages = MAX_STAGES;
+    if (stages < 2)
+        return fail(-ENOSYS, "tcgen05 conv: tile does not fit shared memory");
+    g.stages = stages;
+    const uint32_t ring = (uint32_t)stages * (a_stage + b_pitch);
+    if (tp->fast) {
+        fe.off_out += ring, fe.off_y2 += ring, fe.off_res += ring, fe.off_cst += ring, fe.off_ex += ring;
+        fe.off_lut2 += ring, fe.off_corr += ring;
+    }
+    // More than half of an SM's shared memory, so exactly one CTA (and one TMEM allocation) per SM.
+    tp->smem_bytes = (size_t)ring + extras + 1024;
+    if (tp->smem_bytes < 120 * 1024)
+        tp->smem_bytes = 120 * 1024;
     // The limit is a property of the function, not of the plan: raise it once to the most any
-    // plan can ask for (stages are sized to stay under 200 KiB + alignment slack).
-    NNCB_CUDA_TRY(cudaFuncSetAttribute(tc_conv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+    // plan can ask for.
+    const int lim = 226 * 1024;
+    NNCB_CUDA_TRY(cudaFuncSetAttribute(tc_conv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+    NNCB_CUDA_TRY(cudaFuncSetAttribute(tc_conv_fast_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+    NNCB_CUDA_TRY(cudaFuncSetAttribute(tc_conv_fast_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+    NNCB_CUDA_TRY(cudaFuncSetAttribute(tc_conv_fast_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+    NNCB_CUDA_TRY(cudaFuncSetAttribute(tc_conv_fast_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
     return 0;
 }
 
@@ -706,8 +1138,29 @@ void tc_conv_destroy(nncb_qconv2d *cv) {
     cudaFree(tp->d_cnt);
     cudaFree(tp->d_ycls);
     cudaFree(tp->d_xcls);
+    cudaFree(tp->d_cst);
+    cudaFree(tp->d_ex);
+    delete tp->f;
     delete tp;
     cv->tc = nullptr;
+}
+
+static int make_tmap_out(CUtensorMap *map, const TcPlan *tp, const void *ptr) {
+    const TcGeom &g = tp->g;
+    cuuint64_t dims[2] = {(cuuint64_t)g.oc, (cuuint64_t)g.m_total};
+    cuuint64_t strides[1] = {(cuuint64_t)g.oc};
+    cuuint32_t box[2] = {(cuuint32_t)g.bn, 128};
+    cuuint32_t estr[2] = {1, 1};
+    const int sw = tp->f->out_sw;
+    CUtensorMapSwizzle swz = sw == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                       : (sw == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                                   : (sw == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE));
+    CUresult r = g_encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(ptr), dims, strides, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(-EIO, "encoding an output tensor map failed (CUresult %d)", (int)r);
+    return 0;
 }
 
 int tc_conv_run(nncb_context *ctx, nncb_qconv2d *cv, const uint8_t *x, const uint8_t *res, void *y, uint8_t *y2) {
@@ -719,6 +1172,7 @@ int tc_conv_run(nncb_context *ctx, nncb_qconv2d *cv, const uint8_t *x, const uin
     TcArgs a;
     a.g = tp->g;
     a.p = make_epi(cv);
+    a.f = *tp->f;
     a.corr = tp->d_corr;
     a.cnt = tp->d_cnt;
     a.ycls = tp->d_ycls;
@@ -731,6 +1185,31 @@ int tc_conv_run(nncb_context *ctx, nncb_qconv2d *cv, const uint8_t *x, const uin
     a.status = ctx->d_status;
     const int tiles = tp->g.m_tiles * tp->g.n_tiles;
     const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+    auto al16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    if (tp->fast && al16(y) && al16(y2) && al16(res)) {
+        if (tp->y_ptr != y) {
+            NNCB_TRY(make_tmap_out(&tp->tmap_y, tp, y));
+            tp->y_ptr = y;
+        }
+        if (y2 && tp->y2_ptr != y2) {
+            NNCB_TRY(make_tmap_out(&tp->tmap_y2, tp, y2));
+            tp->y2_ptr = y2;
+        }
+        if (res && tp->res_ptr != res) {
+            NNCB_TRY(make_tmap_out(&tp->tmap_res, tp, res));
+            tp->res_ptr = res;
+        }
+        const CUtensorMap &my2 = y2 ? tp->tmap_y2 : tp->tmap_y, &mres = res ? tp->tmap_res : tp->tmap_y;
+        if (res && y2)
+            tc_conv_fast_kernel<true, true><<<grid, TC_THREADS, tp->smem_bytes, ctx->stream>>>(tp->tmap_a, tp->tmap_b, tp->tmap_y, my2, mres, a);
+        else if (res)
+            tc_conv_fast_kernel<true, false><<<grid, TC_THREADS, tp->smem_bytes, ctx->stream>>>(tp->tmap_a, tp->tmap_b, tp->tmap_y, my2, mres, a);
+        else if (y2)
+            tc_conv_fast_kernel<false, true><<<grid, TC_THREADS, tp->smem_bytes, ctx->stream>>>(tp->tmap_a, tp->tmap_b, tp->tmap_y, my2, mres, a);
+        else
+            tc_conv_fast_kernel<false, false><<<grid, TC_THREADS, tp->smem_bytes, ctx->stream>>>(tp->tmap_a, tp->tmap_b, tp->tmap_y, my2, mres, a);
+        return after_launch(ctx, "tc_conv_fast");
+    }
     tc_conv_kernel<<<grid, TC_THREADS, tp->smem_bytes, ctx->stream>>>(tp->tmap_a, tp->tmap_b, a);
     return after_launch(ctx, "tc_conv");
 }

@@ -202,6 +202,66 @@ int quantize_nchw_to_nhwc_u8(nncb_context *ctx, const float *in, uint8_t *out, i
     return after_launch(ctx, "quantize_nchw_to_nhwc");
 }
 
+// ---- NCHW f32 -> space-to-depth(2) NHWC u8 ---------------------------------------------------
+// out[n][Y][X][(dy*2+dx)*c + ch] = quantize(in[n][ch][2Y+dy][2X+dx]); channels 4c..c_pad-1 hold the
+// zero point. Turns a stride-2 convolution over few channels (an image stem) into a stride-1
+// convolution over c_pad channels that the tensor-core kernel can take. One thread per cell.
+template <int CPAD>
+__global__ void __launch_bounds__(256)
+quantize_nchw_to_s2d_kernel(const float *__restrict__ in, uint8_t *__restrict__ out, int c, int h, int w,
+                            size_t total_cells, float scale, float zp) {
+    const int hc = h / 2, wc = w / 2;
+    const uint32_t zq = (uint32_t)min(max(__float2int_rn(zp), 0), 255);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total_cells;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const int X = (int)(i % wc);
+        const int Y = (int)((i / wc) % hc);
+        const size_t n = i / ((size_t)wc * hc);
+        uint32_t words[CPAD / 4];
+#pragma unroll
+        for (int k = 0; k < CPAD / 4; k++)
+            words[k] = zq * 0x01010101u;
+        for (int ch = 0; ch < c; ch++)
+#pragma unroll
+            for (int dy = 0; dy < 2; dy++) {
+                const float2 v = __ldcs(reinterpret_cast<const float2 *>(
+                    in + ((n * c + ch) * h + (2 * Y + dy)) * (size_t)w + 2 * X));
+                const uint32_t q0 = (uint32_t)quant_dev(v.x, scale, zp, 0, 255);
+                const uint32_t q1 = (uint32_t)quant_dev(v.y, scale, zp, 0, 255);
+                const int i0 = (dy * 2 + 0) * c + ch, i1 = (dy * 2 + 1) * c + ch;
+#pragma unroll
+                for (int k = 0; k < CPAD / 4; k++) {
+                    // constant-indexed update keeps `words` in registers
+                    if ((i0 >> 2) == k)
+                        words[k] = (words[k] & ~(0xFFu << (8 * (i0 & 3)))) | (q0 << (8 * (i0 & 3)));
+                    if ((i1 >> 2) == k)
+                        words[k] = (words[k] & ~(0xFFu << (8 * (i1 & 3)))) | (q1 << (8 * (i1 & 3)));
+                }
+            }
+        uint4 *o = reinterpret_cast<uint4 *>(out + i * CPAD);
+#pragma unroll
+        for (int k = 0; k < CPAD / 16; k++)
+            o[k] = make_uint4(words[4 * k], words[4 * k + 1], words[4 * k + 2], words[4 * k + 3]);
+    }
+}
+
+int quantize_nchw_to_s2d_u8(nncb_context *ctx, const float *in, uint8_t *out, int n, int c, int h, int w, int c_pad,
+                            float scale, int32_t zp) {
+    if (n <= 0 || c <= 0 || h <= 0 || w <= 0 || (h & 1) || (w & 1))
+        return fail(-EINVAL, "quantize_nchw_to_s2d_u8: height and width must be positive and even");
+    if (4 * c > c_pad || (c_pad != 16 && c_pad != 32))
+        return fail(-EINVAL, "quantize_nchw_to_s2d_u8: c_pad must be 16 or 32 and hold 4*c channels");
+    if ((reinterpret_cast<uintptr_t>(in) & 7) || (reinterpret_cast<uintptr_t>(out) & 15))
+        return fail(-EINVAL, "quantize_nchw_to_s2d_u8: pointers must be 8-byte (in) and 16-byte (out) aligned");
+    const size_t total = (size_t)n * (h / 2) * (w / 2);
+    const int grid = stream_grid(ctx, total, 256);
+    if (c_pad == 32)
+        quantize_nchw_to_s2d_kernel<32><<<grid, 256, 0, ctx->stream>>>(in, out, c, h, w, total, scale, (float)zp);
+    else
+        quantize_nchw_to_s2d_kernel<16><<<grid, 256, 0, ctx->stream>>>(in, out, c, h, w, total, scale, (float)zp);
+    return after_launch(ctx, "quantize_nchw_to_s2d");
+}
+
 int nchw_to_nhwc_u8(nncb_context *ctx, const uint8_t *in, uint8_t *out, int n, int c, int h, int w) {
     if (n <= 0 || c <= 0 || h <= 0 || w <= 0)
         return fail(-EINVAL, "nchw_to_nhwc_u8: bad shape");

@@ -121,6 +121,15 @@ class Context:
                                                       qp.scale, qp.zero_point))
         return y
 
+    def quantize_nchw_to_s2d(self, x, qp, c_pad=32):
+        """f32 NCHW -> u8 [n, h/2, w/2, c_pad], channel (dy*2+dx)*c + ch (space-to-depth by 2)."""
+        x = self._cuda(x, torch.float32)
+        n, c, h, w = x.shape
+        y = torch.empty((n, h // 2, w // 2, c_pad), dtype=torch.uint8, device=self.device)
+        check(self._lib.nncb_quantize_nchw_to_s2d_u8(self._h, x.data_ptr(), y.data_ptr(), n, c, h, w, c_pad,
+                                                     qp.scale, qp.zero_point))
+        return y
+
     def dequantize_nhwc_to_nchw(self, q, qp):
         q = self._cuda(q, torch.uint8)
         n, h, w, c = q.shape

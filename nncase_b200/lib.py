@@ -69,6 +69,7 @@ SIGNATURES = {
     "nncb_quantize_host": (_I, [_VP, _VP, _VP, _SZ, _F, _I32, _I]),
     "nncb_dequantize_host": (_I, [_VP, _VP, _VP, _SZ, _F, _I32, _I]),
     "nncb_quantize_nchw_to_nhwc_u8": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _F, _I32]),
+    "nncb_quantize_nchw_to_s2d_u8": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _F, _I32]),
     "nncb_dequantize_nhwc_to_nchw_f32": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _F, _I32]),
     "nncb_nchw_to_nhwc_u8": (_I, [_VP, _VP, _VP, _I, _I, _I, _I]),
     "nncb_nhwc_to_nchw_u8": (_I, [_VP, _VP, _VP, _I, _I, _I, _I]),

@@ -78,8 +78,9 @@ class CudaFunction:
             if kind == "quantize_input":
                 n, c, hh, ww = x_dev.shape
                 qp = T[op["out"]]["qp"]
-                L.check(lib.nncb_quantize_nchw_to_nhwc_u8(h_, x_dev.data_ptr(), buf[op["out"]].data_ptr(), n, c, hh, ww,
-                                                          op["c_pad"], qp.scale, qp.zero_point))
+                fn_q = lib.nncb_quantize_nchw_to_s2d_u8 if op.get("s2d") else lib.nncb_quantize_nchw_to_nhwc_u8
+                L.check(fn_q(h_, x_dev.data_ptr(), buf[op["out"]].data_ptr(), n, c, hh, ww, op["c_pad"], qp.scale,
+                             qp.zero_point))
             elif kind == "conv":
                 plan = st[2]
                 res = buf[op["res"]] if op.get("res") else None

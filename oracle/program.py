@@ -26,7 +26,10 @@ def run_program(program, x_nchw_f32, threads=8, feed=None, keep=None):
         k = op["op"]
         if k == "quantize_input":
             qp = T[op["out"]]["qp"]
-            t[op["out"]] = Q.quantize_nchw_to_nhwc_u8(x_nchw_f32, qp.scale, qp.zero_point, op["c_pad"])
+            if op.get("s2d"):
+                t[op["out"]] = Q.quantize_nchw_to_s2d_u8(x_nchw_f32, qp.scale, qp.zero_point, op["c_pad"])
+            else:
+                t[op["out"]] = Q.quantize_nchw_to_nhwc_u8(x_nchw_f32, qp.scale, qp.zero_point, op["c_pad"])
         elif k == "conv":
             xin = get(op["in"])
             xqp = T[op["in"]]["qp"]

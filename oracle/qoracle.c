@@ -126,6 +126,26 @@ void qo_quantize_nchw_to_nhwc_u8(const float *in, uint8_t *out, int n, int c, in
                 }
 }
 
+/* Fused input stage with space-to-depth(2): out[n][Y][X][(dy*2+dx)*c + ch] =
+ * quantize(in[n][ch][2Y+dy][2X+dx]); channels 4c..c_pad-1 hold the zero point. Element-wise it is
+ * qo_quantize_u8; only the arrangement differs. */
+void qo_quantize_nchw_to_s2d_u8(const float *in, uint8_t *out, int n, int c, int h, int w, int c_pad,
+                                float scale, int32_t zp) {
+    const int hc = h / 2, wc = w / 2;
+    for (int b = 0; b < n; b++)
+        for (int Y = 0; Y < hc; Y++)
+            for (int X = 0; X < wc; X++) {
+                uint8_t *o = out + (((size_t)b * hc + Y) * wc + X) * c_pad;
+                for (int k = 0; k < c_pad; k++)
+                    o[k] = (uint8_t)clampi(zp, 0, 255);
+                for (int dy = 0; dy < 2; dy++)
+                    for (int dx = 0; dx < 2; dx++)
+                        for (int ch = 0; ch < c; ch++)
+                            o[(dy * 2 + dx) * c + ch] = (uint8_t)quant1(
+                                in[(((size_t)b * c + ch) * h + 2 * Y + dy) * w + 2 * X + dx], scale, (float)zp, 0, 255);
+            }
+}
+
 /* Output size of a windowed op: kernels::detail::get_windowed_output_size
  * (include/nncase/kernels/kernel_utils.h). */
 static inline int out_size(int in, int k, int stride, int dil, int pad_before, int pad_after) {

@@ -25,7 +25,8 @@ def lib():
     global _LIB
     if _LIB is None:
         path = os.path.join(_HERE, "libqoracle.so")
-        if not os.path.exists(path):
+        src = os.path.join(_HERE, "qoracle.c")
+        if not os.path.exists(path) or (os.path.exists(src) and os.path.getmtime(src) > os.path.getmtime(path)):
             build()
         _LIB = C.CDLL(path)
     return _LIB
@@ -74,6 +75,14 @@ def quantize_nchw_to_nhwc_u8(x, scale, zp, c_pad=None):
     y = np.empty((n, h, w, c_pad), np.uint8)
     lib().qo_quantize_nchw_to_nhwc_u8(_p(x), _p(y), n, c, h, w, c_pad, C.c_float(scale),
                                       C.c_int32(zp))
+    return y
+
+
+def quantize_nchw_to_s2d_u8(x, scale, zp, c_pad=32):
+    x = np.ascontiguousarray(x, np.float32)
+    n, c, h, w = x.shape
+    y = np.empty((n, h // 2, w // 2, c_pad), np.uint8)
+    lib().qo_quantize_nchw_to_s2d_u8(_p(x), _p(y), n, c, h, w, c_pad, C.c_float(scale), C.c_int32(zp))
     return y
 
 

@@ -82,6 +82,41 @@ def test_tc_conv(ctx, qo, cfg, wmode):
     assert bad.size == 0, f"{len(bad)} mismatches, first at {bad[:5].tolist()}"
 
 
+@pytest.mark.parametrize("path", [L.PATH_SIMT, L.PATH_TC])
+def test_conv_rounding_ties(ctx, qo, path):
+    """Scales that are powers of two put half of all results exactly on a rounding boundary and
+    the rest exactly on integers: the fast epilogue's guard band must hand every tie to the
+    exact formula (round half to even), with and without the residual stage."""
+    rng = np.random.default_rng(77)
+    n, h, w, c, oc = 1, 16, 16, 64, 64
+    xq = rng.integers(0, 256, (n, h, w, c), dtype=np.uint8)
+    wq = rng.integers(0, 256, (oc, 3, 3, c), dtype=np.uint8)
+    zw = rng.integers(120, 136, oc).astype(np.int32)
+    mult = np.full(oc, 2.0 ** -13, np.float32)
+    bias = (rng.integers(-8, 8, oc) * 0.25).astype(np.float32)
+    oqp = QuantParam(128, 0.5)  # v / 0.5 is exact; acc * 2^-12 + k/2: ties wherever bit 11 of acc is set
+    want = qo.qconv2d_u8(xq, wq, zw, mult, bias, 131, oqp.scale, oqp.zero_point, pad=(1, 1, 1, 1))
+    got = ctx.conv2d(torch.from_numpy(xq), wq, zw, mult, bias, 131, oqp, padding=(1, 1, 1, 1), force_path=path)
+    ctx.check_status()
+    assert 5 < want.std() and np.array_equal(got.cpu().numpy(), want)
+    res = rng.integers(0, 256, want.shape, dtype=np.uint8)
+    rq, aq = QuantParam(100, 0.25), QuantParam(90, 0.5)  # (q-128)*0.5 + (r-100)*0.25 over 0.5: ties for odd r
+    want2 = qo.qadd_u8(want, res, oqp.scale, oqp.zero_point, rq.scale, rq.zero_point, aq.scale, aq.zero_point)
+    got2 = ctx.conv2d(torch.from_numpy(xq), wq, zw, mult, bias, 131, oqp, padding=(1, 1, 1, 1), force_path=path,
+                      res=torch.from_numpy(res).cuda(), residual=(rq, aq))
+    ctx.check_status()
+    assert np.array_equal(got2.cpu().numpy(), want2)
+
+
+@pytest.mark.parametrize("oc", [16, 48, 80, 192, 272])
+def test_tc_conv_channel_tiles(ctx, qo, oc):
+    """Output-channel counts that give every staging-tile width (swizzled and not) and a partial
+    last N tile."""
+    case = make_case(90 + oc, 2, 9, 9, 64, oc, 3, 3)
+    got, want = run_both(ctx, qo, case, L.PATH_TC, (1, 1), (1, 1, 1, 1), (1, 1), 1, (0, 6))
+    assert np.array_equal(got, want)
+
+
 def test_tc_conv_residual_and_second_output(ctx, qo):
     n, h, w, c, oc = 2, 14, 14, 64, 256
     case = make_case(41, n, h, w, c, oc, 1, 1)

@@ -36,7 +36,7 @@ def test_resnet50v2_every_tensor(ctx, w_quant):
     x = np.random.default_rng(2003).normal(0, 1, (n, 3, 224, 224)).astype(np.float32)
     fn = CudaFunction(program, n, ctx)
     paths = fn.conv_paths
-    assert paths["stem"] == L.PATH_SIMT and all(p == L.PATH_TC for k, p in paths.items() if k != "stem")
+    assert all(p == L.PATH_TC for p in paths.values()), paths
     out = fn.invoke(torch.from_numpy(x).cuda())
     ctx.check_status()
     want, tens = oprog.run_program(program, x)

@@ -128,3 +128,30 @@ def test_golden_vectors(qo):
     diff = np.abs(yq.astype(int) - c["y_ref_composite"].astype(int))
     assert diff.max() <= 1 and (diff != 0).sum() <= int(c["allowed_mismatches"])
     assert np.array_equal(yq, c["y_integer"])
+
+
+def test_space_to_depth_stem_is_the_same_convolution(qo):
+    """A 7x7 stride-2 pad-3 stem over 3 channels and its space-to-depth rewrite (4x4, stride 1 over
+    32 channels) give identical integer results -- the rewrite only rearranges the products."""
+    from nncase_b200.builder import space_to_depth_conv
+    rng = np.random.default_rng(12)
+    n, c, h, w, oc = 2, 3, 20, 16, 8
+    x = rng.normal(0, 1, (n, c, h, w)).astype(np.float32)
+    scale, zp = 0.03, 120
+    wq = rng.integers(0, 256, (oc, 7, 7, c), dtype=np.uint8)
+    zw = rng.integers(100, 150, oc).astype(np.int32)
+    mult = rng.uniform(1e-4, 3e-4, oc).astype(np.float32)
+    bias = rng.normal(0, 0.1, oc).astype(np.float32)
+    x_nhwc = qo.quantize_nchw_to_nhwc_u8(x, scale, zp)
+    want = qo.qconv2d_u8(x_nhwc, wq, zw, mult, bias, zp, 0.05, 10, (2, 2), (3, 3, 3, 3), clamp=(0, np.inf))
+    x_s2d = qo.quantize_nchw_to_s2d_u8(x, scale, zp, 32)
+    w2, pad2 = space_to_depth_conv(wq, zw, (3, 3, 3, 3), (h, w), 32)
+    assert w2.shape == (oc, 4, 4, 32) and pad2 == (2, 1, 2, 1)
+    got = qo.qconv2d_u8(x_s2d, w2, zw, mult, bias, zp, 0.05, 10, (1, 1), pad2, clamp=(0, np.inf))
+    assert np.array_equal(got, want)
+    # 3x3 stride 2 pad 1 (MobileNet / YOLO stems)
+    wq3 = rng.integers(0, 256, (oc, 3, 3, c), dtype=np.uint8)
+    want3 = qo.qconv2d_u8(x_nhwc, wq3, zw, mult, bias, zp, 0.05, 10, (2, 2), (1, 1, 1, 1))
+    w3, pad3 = space_to_depth_conv(wq3, zw, (1, 1, 1, 1), (h, w), 32)
+    got3 = qo.qconv2d_u8(x_s2d, w3, zw, mult, bias, zp, 0.05, 10, (1, 1), pad3)
+    assert w3.shape == (oc, 2, 2, 32) and np.array_equal(got3, want3)

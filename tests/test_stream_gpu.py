@@ -79,6 +79,13 @@ def test_quantize_nchw_to_nhwc(ctx, qo, shape, c_pad):
     assert np.array_equal(got, qo.quantize_nchw_to_nhwc_u8(x, 0.025, 120, c_pad))
 
 
+@pytest.mark.parametrize("shape,c_pad", [((2, 3, 18, 22), 32), ((1, 3, 224, 224), 32), ((2, 4, 8, 8), 16)])
+def test_quantize_nchw_to_s2d(ctx, qo, shape, c_pad):
+    x = np.random.default_rng(13).normal(0, 1, shape).astype(np.float32)
+    got = ctx.quantize_nchw_to_s2d(torch.from_numpy(x), QuantParam(117, 0.021), c_pad).cpu().numpy()
+    assert np.array_equal(got, qo.quantize_nchw_to_s2d_u8(x, 0.021, 117, c_pad))
+
+
 @pytest.mark.parametrize("shape", [(2, 7, 7, 40), (1, 1, 1, 1000), (3, 5, 6, 33)])
 def test_dequantize_nhwc_to_nchw_and_layout(ctx, qo, shape):
     q = np.random.default_rng(4).integers(0, 256, shape, dtype=np.uint8)
