@@ -348,6 +348,49 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_layer(args):
+    """Times one convolution layer of the network alone (for profiling): `--layer NAME`."""
+    import torch
+    from nncase_b200 import lib as L
+    from nncase_b200.kernels import Context
+    from nncase_b200.runtime import CudaFunction
+    dev = torch.device("cuda", 0)
+    graph, program, macs, layer_macs = build_network(dev, args.w_quant)
+    want = args.layer
+    keep = [op for op in program["ops"] if op["op"] == "conv" and op["name"] == want]
+    if not keep:
+        raise SystemExit(f"no conv layer named {want}; layers: {[o['name'] for o in program['ops'] if o['op'] == 'conv']}")
+    op = keep[0]
+    sub = dict(program, ops=[op])
+    ctx = Context(0)
+    fn = CudaFunction(sub, args.batch, ctx)
+    g = torch.Generator(device=dev).manual_seed(1)
+    for name in (op["in"], op.get("res")):
+        if name:
+            fn.buffers[name].copy_(torch.randint(0, 256, fn.buffers[name].shape, device=dev, generator=g, dtype=torch.uint8))
+    plan = fn.plans[0]
+    res = fn.buffers[op["res"]] if op.get("res") else None
+    y2 = fn.buffers[op["y2"]] if op.get("y2") else None
+    for _ in range(max(1, args.warmup)):
+        plan(fn.buffers[op["in"]], res, fn.buffers[op["out"]], y2)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.steps):
+        plan(fn.buffers[op["in"]], res, fn.buffers[op["out"]], y2)
+    b.record()
+    torch.cuda.synchronize()
+    ctx.check_status()
+    ms = a.elapsed_time(b) / args.steps
+    n, oh, ow, oc = plan.out_shape
+    in_bytes = fn.buffers[op["in"]].numel()
+    out_bytes = n * oh * ow * oc * (1 + (1 if res is not None else 0) + (1 if y2 is not None else 0))
+    print(json.dumps(dict(layer=want, batch=args.batch, path=plan.path, ms=ms,
+                          tops=2.0 * layer_macs[want] * args.batch / (ms / 1000) / 1e12,
+                          algorithmic_bytes=in_bytes + out_bytes + op["w"].size,
+                          gbs=(in_bytes + out_bytes + op["w"].size) / (ms / 1000) / 1e9)))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -358,8 +401,11 @@ def main():
     ap.add_argument("--w-quant", default="uint8", choices=["uint8", "int8"])
     ap.add_argument("--layers", action="store_true", help="print per-layer timings to stderr")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layer", default=None, help="time only this conv layer (profiling aid)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.layer:
+        run_layer(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

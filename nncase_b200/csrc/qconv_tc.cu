@@ -332,7 +332,7 @@ constexpr int MAX_STAGES = 8;
 constexpr float MAGIC = 12582912.0f; // 1.5 * 2^23: adding it rounds a float to an integer in its low mantissa bits
 
 struct TcShared {
-    uint64_t bar_full[MAX_STAGES], bar_empty[MAX_STAGES], bar_acc_full[2], bar_acc_empty[2], bar_res;
+    uint64_t bar_full[MAX_STAGES], bar_empty[MAX_STAGES], bar_acc_full[2], bar_acc_empty[2], bar_res[EPI_WARPS];
     uint32_t tmem_base_slot;
     volatile int abort_flag;
 };
@@ -364,7 +364,8 @@ __device__ __forceinline__ void tc_setup(const TcGeom &g, TcShared &sh, int warp
             mbar_init(smem_u32(&sh.bar_acc_full[b]), 1);
             mbar_init(smem_u32(&sh.bar_acc_empty[b]), EPI_WARPS);
         }
-        mbar_init(smem_u32(&sh.bar_res), 1);
+        for (int w = 0; w < EPI_WARPS; w++)
+            mbar_init(smem_u32(&sh.bar_res[w]), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -669,6 +670,18 @@ __device__ __forceinline__ uint32_t stage_addr(uint32_t base, int row, int chunk
 }
 } // namespace dev
 
+// Exact recomputation of one element, kept out of line: it runs for a few elements per ten
+// thousand, and inlining sixteen copies of it would push the hot loop out of the instruction cache.
+__device__ __noinline__ uint32_t epi_u8_exact(int acc, float mult, float bias, int res, float out_scale, float out_zp,
+                                              float lo, float hi, int has_res, float res_scale, float res_zp,
+                                              float add_scale, float add_zp) {
+    EpiParams p;
+    p.lut = nullptr;
+    p.out_scale = out_scale, p.out_zp = out_zp, p.clamp_lo = lo, p.clamp_hi = hi;
+    p.has_res = has_res, p.res_scale = res_scale, p.res_zp = res_zp, p.add_scale = add_scale, p.add_zp = add_zp;
+    return (uint32_t)epi_u8(acc, mult, bias, p, res);
+}
+
 template <bool RES, bool Y2>
 __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &sg, TcShared &sh, uint32_t tmem_base,
                                               const CUtensorMap *tmap_y, const CUtensorMap *tmap_y2,
@@ -680,28 +693,34 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
     const int ew = warp - 2;
     const int et = ew * 32 + lane;   // index among the epilogue threads
     const int lane_group = warp & 3; // TMEM lanes 32*lane_group .. +31 are this warp's
-    const int half = ew >> 2;
+    const int half = ew >> 2;        // which half of the tile's columns this warp owns
     const int row = lane_group * 32 + lane;
-    const bool leader = et == 0;
-    const uint32_t s_out = sg.smem_base + f.off_out, s_y2 = sg.smem_base + f.off_y2, s_res = sg.smem_base + f.off_res;
+    const int hw = g.bn >> 1;        // bytes per row of this warp's sub-tile (32 rows x hw columns)
+    // Every warp stages, stores and prefetches its own 32 x hw sub-tile: no block-wide barrier in
+    // the steady state.
+    const uint32_t sub = (uint32_t)ew * 32u * hw;
+    const uint32_t s_out = sg.smem_base + f.off_out + sub, s_y2 = sg.smem_base + f.off_y2 + sub;
+    const uint32_t s_res = sg.smem_base + f.off_res + sub;
     const uint32_t s_cst = sg.smem_base + f.off_cst, s_ex = sg.smem_base + f.off_ex, s_corr = sg.smem_base + f.off_corr;
     const uint32_t s_lut2 = sg.smem_base + f.off_lut2;
+    const uint32_t bar_res = smem_u32(&sh.bar_res[ew]);
     const bool multi_cls = f.n_cls > 1;
-    const uint32_t res_bytes = 128u * g.bn;
+    const uint32_t res_bytes = 32u * hw;
+    const int col_off = half * hw;
     if (Y2) {
-        // second-output table: 256 bytes
         if (et < 64)
             asm volatile("st.shared.u32 [%0], %1;" ::"r"(s_lut2 + et * 4),
                          "r"(reinterpret_cast<const uint32_t *>(a.p.y2_lut)[et])
                          : "memory");
     }
-    if (RES && leader && (int)blockIdx.x < total_tiles) {
+    if (RES && lane == 0 && (int)blockIdx.x < total_tiles) {
         const int mt = blockIdx.x % g.m_tiles, nt = blockIdx.x / g.m_tiles;
-        mbar_expect_tx(smem_u32(&sh.bar_res), res_bytes);
-        tma_load_2d(s_res, tmap_res, smem_u32(&sh.bar_res), nt * g.bn, mt * 128);
+        mbar_expect_tx(bar_res, res_bytes);
+        tma_load_2d(s_res, tmap_res, bar_res, nt * g.bn + col_off, mt * 128 + lane_group * 32);
     }
     uint32_t acc_phase0 = 0, acc_phase1 = 0, res_phase = 0;
     int it = 0, cur_nt = -1;
+    bool dead = false; // after a failed wait the warp only keeps the block-wide barriers company
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, it++) {
         const int buf = it & 1;
         const int mt = tile % g.m_tiles, nt = tile / g.m_tiles;
@@ -729,6 +748,8 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
             cur_nt = nt;
             epi_bar_sync();
         }
+        if (dead)
+            continue;
         int cls = 0;
         if (g.mode == MODE_IM2COL && row_ok) {
             const int ox = m % g.ow, oy = (m / g.ow) % g.oh;
@@ -737,12 +758,15 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
         const uint32_t ph = buf ? acc_phase1 : acc_phase0;
         bool ok = mbar_wait(smem_u32(&sh.bar_acc_full[buf]), ph, &sh.abort_flag, a.status, ERR_EPILOGUE);
         if (RES && ok)
-            ok = mbar_wait(smem_u32(&sh.bar_res), res_phase, &sh.abort_flag, a.status, ERR_RESIDUAL);
-        // the previous tile's TMA stores must have finished reading the staging tiles
-        if (leader)
+            ok = mbar_wait(bar_res, res_phase, &sh.abort_flag, a.status, ERR_RESIDUAL);
+        if (!ok) {
+            dead = true;
+            continue;
+        }
+        // this warp's previous TMA stores must have finished reading its staging sub-tiles
+        if (lane == 0)
             tma_store_wait_read();
-        if (epi_bar_or(!ok))
-            return; // every epilogue warp leaves together
+        __syncwarp();
         if (buf)
             acc_phase1 ^= 1;
         else
@@ -757,13 +781,14 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
             rsum = xs - a.cnt[cls] * g.x_zp;
         }
         const uint32_t corr_row = s_corr + (uint32_t)(cls * f.corr_pitch) * 4;
-        for (int c0 = half * 16; c0 < g.bn; c0 += 32) {
+        for (int cc = 0; cc < hw; cc += 16) {
+            const int c0 = col_off + cc; // column within the tile
             int v[16];
             __syncwarp();
             tmem_ld16(tbase + c0, v);
             uint4 rw = make_uint4(0, 0, 0, 0);
             if (RES)
-                rw = lds128(stage_addr(s_res, row, c0 >> 4, g.bn, f.out_sw));
+                rw = lds128(stage_addr(s_res, lane, cc >> 4, hw, f.out_sw));
             const uint32_t rwa[4] = {rw.x, rw.y, rw.z, rw.w};
             int acc[16];
             uint32_t bits[16];
@@ -774,13 +799,15 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
                 const int corr = multi_cls ? (int)lds32(corr_row + (c0 + j) * 4) : __float_as_int(k.z);
                 acc[j] = v[j] + __float_as_int(k.w) * rsum - corr;
                 const float t = __fmaf_rn((float)acc[j], k.x, k.y);
-                const float rf = __fadd_rn(__fadd_rn(t, MAGIC), -MAGIC);
+                const float rf = rintf(t);
                 bool bad = !(fabsf(__fadd_rn(t, -rf)) <= f.thr1);
                 float qf = fminf(fmaxf(rf, f.qlo), f.qhi);
                 if (RES) {
-                    const float rb = (float)((rwa[j >> 2] >> (8 * (j & 3))) & 255u);
+                    // byte j of the residual word as a float: 0x4B000000 | byte is 2^23 + byte
+                    const float rb = __fadd_rn(__uint_as_float(__byte_perm(rwa[j >> 2], 0x4B000000u, 0x7440 | (j & 3))),
+                                               -8388608.0f);
                     const float t2 = __fmaf_rn(qf, f.ca, __fmaf_rn(rb, f.cb, f.cc));
-                    const float rf2 = __fadd_rn(__fadd_rn(t2, MAGIC), -MAGIC);
+                    const float rf2 = rintf(t2);
                     bad |= !(fabsf(__fadd_rn(t2, -rf2)) <= f.thr2);
                     qf = fminf(fmaxf(rf2, 0.f), 255.f);
                 }
@@ -794,7 +821,9 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
                     if (slow & (1u << j)) {
                         float mult, bias;
                         asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(mult), "=f"(bias) : "r"(s_ex + (c0 + j) * 8));
-                        bits[j] = (uint32_t)epi_u8(acc[j], mult, bias, a.p, (int)((rwa[j >> 2] >> (8 * (j & 3))) & 255u));
+                        bits[j] = epi_u8_exact(acc[j], mult, bias, (int)((rwa[j >> 2] >> (8 * (j & 3))) & 255u),
+                                               a.p.out_scale, a.p.out_zp, a.p.clamp_lo, a.p.clamp_hi, RES ? 1 : 0,
+                                               a.p.res_scale, a.p.res_zp, a.p.add_scale, a.p.add_zp);
                     }
                 }
             }
@@ -803,39 +832,43 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
             o.y = __byte_perm(__byte_perm(bits[4], bits[5], 0x0040), __byte_perm(bits[6], bits[7], 0x0040), 0x5410);
             o.z = __byte_perm(__byte_perm(bits[8], bits[9], 0x0040), __byte_perm(bits[10], bits[11], 0x0040), 0x5410);
             o.w = __byte_perm(__byte_perm(bits[12], bits[13], 0x0040), __byte_perm(bits[14], bits[15], 0x0040), 0x5410);
-            sts128(stage_addr(s_out, row, c0 >> 4, g.bn, f.out_sw), o);
+            sts128(stage_addr(s_out, lane, cc >> 4, hw, f.out_sw), o);
             if (Y2) {
                 uint32_t w2[4];
                 const uint32_t ow_[4] = {o.x, o.y, o.z, o.w};
 #pragma unroll
                 for (int k = 0; k < 4; k++) {
-                    const uint32_t b0 = lds8(s_lut2 + (ow_[k] & 255u)), b1 = lds8(s_lut2 + ((ow_[k] >> 8) & 255u));
-                    const uint32_t b2 = lds8(s_lut2 + ((ow_[k] >> 16) & 255u)), b3 = lds8(s_lut2 + (ow_[k] >> 24));
-                    w2[k] = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+                    const uint32_t b0 = lds8(s_lut2 + __byte_perm(ow_[k], 0, 0x4440));
+                    const uint32_t b1 = lds8(s_lut2 + __byte_perm(ow_[k], 0, 0x4441));
+                    const uint32_t b2 = lds8(s_lut2 + __byte_perm(ow_[k], 0, 0x4442));
+                    const uint32_t b3 = lds8(s_lut2 + __byte_perm(ow_[k], 0, 0x4443));
+                    w2[k] = __byte_perm(__byte_perm(b0, b1, 0x0040), __byte_perm(b2, b3, 0x0040), 0x5410);
                 }
-                sts128(stage_addr(s_y2, row, c0 >> 4, g.bn, f.out_sw), make_uint4(w2[0], w2[1], w2[2], w2[3]));
+                sts128(stage_addr(s_y2, lane, cc >> 4, hw, f.out_sw), make_uint4(w2[0], w2[1], w2[2], w2[3]));
             }
         }
-        // accumulator and residual tile are consumed; staging tiles are written
+        // accumulator and residual sub-tile are consumed; staging sub-tiles are written
         fence_before_sync();
-        __syncwarp();
-        if (lane == 0)
-            mbar_arrive(smem_u32(&sh.bar_acc_empty[buf]));
         fence_async_smem();
-        epi_bar_sync();
-        if (leader) {
-            tma_store_2d(tmap_y, s_out, oc0, mt * 128);
-            if (Y2)
-                tma_store_2d(tmap_y2, s_y2, oc0, mt * 128);
+        __syncwarp();
+        if (lane == 0) {
+            mbar_arrive(smem_u32(&sh.bar_acc_empty[buf]));
+            const int gy = mt * 128 + lane_group * 32;
+            if (gy < g.m_total) {
+                tma_store_2d(tmap_y, s_out, oc0 + col_off, gy);
+                if (Y2)
+                    tma_store_2d(tmap_y2, s_y2, oc0 + col_off, gy);
+            }
             tma_store_commit();
             const int next = tile + gridDim.x;
             if (RES && next < total_tiles) {
-                mbar_expect_tx(smem_u32(&sh.bar_res), res_bytes);
-                tma_load_2d(s_res, tmap_res, smem_u32(&sh.bar_res), (next / g.m_tiles) * g.bn, (next % g.m_tiles) * 128);
+                mbar_expect_tx(bar_res, res_bytes);
+                tma_load_2d(s_res, tmap_res, bar_res, (next / g.m_tiles) * g.bn + col_off,
+                            (next % g.m_tiles) * 128 + lane_group * 32);
             }
         }
     }
-    if (leader)
+    if (lane == 0)
         tma_store_wait_all();
 }
 
@@ -867,10 +900,16 @@ tc_conv_fast_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 // host side: plan creation
 // ------------------------------------------------------------------------------------------------
 static int pick_bn(int oc, bool xsum) {
-    // N tile: as wide as the layer allows up to 128 (+16 for the row-sum column), multiple of 16
-    int bn = oc >= 128 ? 128 : ((oc + 15) / 16) * 16;
+    // N tile: as wide as the layer allows up to 128 (+16 for the row-sum column), multiple of 16.
+    // 128, 64 and 32 are the widths the fast epilogue stages; prefer them when nothing is wasted.
     (void)xsum;
-    return bn;
+    if (oc >= 128)
+        return 128;
+    if (oc % 64 == 0)
+        return 64;
+    if (oc % 32 == 0 && oc <= 96)
+        return 32;
+    return ((oc + 15) / 16) * 16;
 }
 
 int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, const int32_t *wzp_host) {
@@ -910,7 +949,8 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
     g.idesc = (2u << 4) | (0u << 7) | ((d.w_signed ? 1u : 0u) << 10) | ((uint32_t)(g.bn_mma >> 3) << 17) |
               ((uint32_t)(128 >> 4) << 24);
     // ---- fast epilogue: constants, error bounds and shared-memory layout ----
-    const bool fast_shape = !d.f32_out && cv->d_lut == nullptr && d.oc % 16 == 0;
+    const bool fast_shape = !d.f32_out && cv->d_lut == nullptr && d.oc % 16 == 0 &&
+                            (g.bn == 128 || g.bn == 64 || g.bn == 32);
     tp->f = new FastEpi();
     FastEpi &fe = *tp->f;
     memset(&fe, 0, sizeof(fe));
@@ -929,7 +969,8 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
         fe.off_lut2 = off, off += 256;
         fe.off_corr = off;
         extras = off; // the per-class table is appended once the classes are known
-        fe.out_sw = g.bn == 128 ? 128 : (g.bn == 64 ? 64 : (g.bn == 32 ? 32 : 0));
+        // each epilogue warp stages a 32-row x bn/2-byte sub-tile; its rows are the swizzle span
+        fe.out_sw = g.bn == 128 ? 64 : (g.bn == 64 ? 32 : 0);
         tp->fast = true;
     }
     // ---- weights: [n_tiles][bn_mma][K], K ordered (ky, kx, c) = the OHWI row as given ----
@@ -1149,7 +1190,7 @@ static int make_tmap_out(CUtensorMap *map, const TcPlan *tp, const void *ptr) {
     const TcGeom &g = tp->g;
     cuuint64_t dims[2] = {(cuuint64_t)g.oc, (cuuint64_t)g.m_total};
     cuuint64_t strides[1] = {(cuuint64_t)g.oc};
-    cuuint32_t box[2] = {(cuuint32_t)g.bn, 128};
+    cuuint32_t box[2] = {(cuuint32_t)(g.bn / 2), 32}; // one epilogue warp's sub-tile
     cuuint32_t estr[2] = {1, 1};
     const int sw = tp->f->out_sw;
     CUtensorMapSwizzle swz = sw == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
