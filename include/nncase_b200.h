@@ -161,6 +161,12 @@ NNCB_API int nncb_qconv2d_run(nncb_context *ctx, nncb_qconv2d *conv, const uint8
 /* One-shot with HOST buffers: x u8 NHWC in, y out; weights as in create. */
 NNCB_API int nncb_qconv2d_host(nncb_context *ctx, const nncb_conv2d_desc *desc, const void *weights, const int32_t *w_zp, const float *mult, const float *bias, const uint8_t *lut, const uint8_t *x, const uint8_t *res, void *y, uint8_t *y2);
 
+/* Diagnostic: the tensor-core kernel divides by a layer's output scale with a three-operation
+ * sequence around a correctly rounded reciprocal. This runs that sequence against the IEEE
+ * division for `count` pseudo-random operands on the device and returns how many differ
+ * (expected: 0). No counterpart in the reference. */
+NNCB_API int nncb_selftest_reciprocal_division(nncb_context *ctx, float scale, uint64_t count, uint64_t seed, uint64_t *mismatches);
+
 #ifdef __cplusplus
 }
 #endif

@@ -446,6 +446,16 @@ int nncb_qconv2d_create(nncb_context *ctx, const nncb_conv2d_desc *desc, const v
     return 0;
 }
 
+int nncb_selftest_reciprocal_division(nncb_context *ctx, float scale, uint64_t count, uint64_t seed, uint64_t *mismatches) {
+    CHECK_CTX(ctx);
+    if (!mismatches)
+        return fail(-EINVAL, "nncb_selftest_reciprocal_division: null out");
+    unsigned long long m = 0;
+    int rc = reciprocal_division_selftest(ctx, scale, count, seed, &m);
+    *mismatches = m;
+    return rc;
+}
+
 int nncb_qconv2d_path(const nncb_qconv2d *cv) { return cv ? cv->path : -EINVAL; }
 
 int nncb_qconv2d_out_shape(const nncb_qconv2d *cv, int *oh, int *ow) {

@@ -69,6 +69,8 @@ bool tc_conv_supported(const nncb_conv2d_desc &d, std::string *why);
 int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, const int32_t *wzp_host);
 void tc_conv_destroy(nncb_qconv2d *cv);
 int tc_conv_run(nncb_context *ctx, nncb_qconv2d *cv, const uint8_t *x, const uint8_t *res, void *y, uint8_t *y2);
+int reciprocal_division_selftest(nncb_context *ctx, float scale, unsigned long long count, unsigned long long seed,
+                                 unsigned long long *mismatches);
 // y = quantize(clamp(dequantize(x)))) for all 256 inputs, host arithmetic identical to the device's.
 void make_requant_table(float si, int32_t zi, float so, int32_t zo, float lo, float hi, uint8_t table[256]);
 } // namespace nncb

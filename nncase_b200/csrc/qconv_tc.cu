@@ -77,7 +77,6 @@ struct TcPlan {
     bool fast = false;
     FastEpi *f = nullptr;
     float4 *d_cst = nullptr;
-    float2 *d_ex = nullptr;
     CUtensorMap tmap_y, tmap_y2, tmap_res;
     const void *y_ptr = nullptr, *y2_ptr = nullptr, *res_ptr = nullptr;
 };
@@ -298,15 +297,16 @@ __device__ __forceinline__ void tmem_ld1(uint32_t taddr, int &r) {
 
 // Extra constants of the fast epilogue (see epilogue_fast below).
 struct FastEpi {
-    uint32_t off_out, off_y2, off_res, off_cst, off_ex, off_corr, off_lut2; // byte offsets from the aligned smem base
+    uint32_t off_out, off_y2, off_res, off_cst, off_corr, off_lut2; // byte offsets from the aligned smem base
     int corr_pitch;     // bn + 1: distinct border classes fall into distinct banks
     int n_cls;
-    int out_sw;         // swizzle span of the staging tiles: 128, 64, 32 or 0
-    float thr1, thr2;   // 0.5 - error bound of the fast formulas (first stage, residual stage)
-    float qlo, qhi;     // fused clamp mapped into the quantized domain
-    float ca, cb, cc;   // residual stage: t2 = q*ca + r*cb + cc
-    const float4 *cst;  // [oc_pad] {A, B, bits(corr of class 0), bits(-zw)}
-    const float2 *ex;   // [oc_pad] {mult, bias} for the exact path
+    int out_sw;         // swizzle span of the staging sub-tiles: 64, 32 or 0
+    int has_clamp;      // fused clamp on the real value is not (-inf, +inf)
+    float so, rso, zo;  // output scale, its correctly rounded reciprocal, zero point
+    float lo, hi;       // fused clamp
+    float sr, zr_m;     // residual scale; 2^23 + residual zero point
+    float sa, rsa, za;  // add-output scale, its correctly rounded reciprocal, zero point
+    const float4 *cst;  // [oc_pad] {mult, bias, bits(corr of class 0), bits(-zw)}
 };
 
 struct TcArgs {
@@ -329,7 +329,7 @@ enum { ERR_PRODUCER = 101, ERR_MMA_FULL = 102, ERR_MMA_ACC = 103, ERR_EPILOGUE =
 constexpr int EPI_WARPS = 8;
 constexpr int TC_THREADS = 64 + 32 * EPI_WARPS;
 constexpr int MAX_STAGES = 8;
-constexpr float MAGIC = 12582912.0f; // 1.5 * 2^23: adding it rounds a float to an integer in its low mantissa bits
+constexpr float MAGIC = 12582912.0f; // 1.5 * 2^23: x + MAGIC holds the integer x in its low mantissa bits
 
 struct TcShared {
     uint64_t bar_full[MAX_STAGES], bar_empty[MAX_STAGES], bar_acc_full[2], bar_acc_empty[2], bar_res[EPI_WARPS];
@@ -605,20 +605,18 @@ tc_conv_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 }
 
 // -------------------------------------------------------------------------------------------------
-// fast epilogue (u8 output, channel count a multiple of 16, no activation table).
-//
-// The exact requantisation  q = rint(clamp(fl(fl(acc)*mult) + bias) / so + zo)  costs four
-// dependent IEEE operations with a division per element. Because that map is monotone in acc, it
-// equals  clamp_q(rint(t))  with  t = acc*A + B  (A = mult/so, B = bias/so + zo, one fused
-// multiply-add) whenever t is not within `eps` of a rounding boundary, eps being a bound on the
-// accumulated rounding error of both formulas computed at plan creation. Elements inside the
-// guard band (a few per ten thousand) are recomputed with the exact formula, so results stay
-// bit-identical. Rounding uses the add-magic-constant trick, the clamp of the real value is
-// applied as a clamp of the quantized value, and the residual add gets the same treatment
-// (t2 = q*ca + r*cb + cc). Per-channel constants are staged in shared memory per N tile and
-// read as one broadcast 16-byte load per element; outputs (and the optional second output) are
-// staged in swizzled shared-memory tiles and written with TMA stores; the residual tile is
-// prefetched with a TMA load.
+// fast epilogue (u8 output, channel count a multiple of 16, N tile of 128, 64 or 32, no activation
+// table). Same arithmetic as epi_u8 -- every IEEE operation of the requantisation chain, in the
+// same order -- but organised for throughput:
+//   * the two divisions (by the output scale, by the add-output scale) use a reciprocal that was
+//     correctly rounded at plan creation: q0 = RN(x*r), rem = x - q0*s (exact, one fma),
+//     q = RN(q0 + rem*r). With r = RN(1/s) this sequence returns RN(x/s), the IEEE quotient
+//     (Markstein's theorem), in three fused operations instead of a division subroutine;
+//   * per-channel constants are staged in shared memory per N tile and read as one broadcast
+//     16-byte load per element;
+//   * every epilogue warp stages its 32 x bn/2 sub-tile of the output (and of the optional second
+//     output) in swizzled shared memory and writes it with its own TMA store; the residual
+//     sub-tile is prefetched with a TMA load. No block-wide barrier in the steady state.
 // -------------------------------------------------------------------------------------------------
 namespace dev {
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(32 * EPI_WARPS) : "memory"); }
@@ -670,19 +668,7 @@ __device__ __forceinline__ uint32_t stage_addr(uint32_t base, int row, int chunk
 }
 } // namespace dev
 
-// Exact recomputation of one element, kept out of line: it runs for a few elements per ten
-// thousand, and inlining sixteen copies of it would push the hot loop out of the instruction cache.
-__device__ __noinline__ uint32_t epi_u8_exact(int acc, float mult, float bias, int res, float out_scale, float out_zp,
-                                              float lo, float hi, int has_res, float res_scale, float res_zp,
-                                              float add_scale, float add_zp) {
-    EpiParams p;
-    p.lut = nullptr;
-    p.out_scale = out_scale, p.out_zp = out_zp, p.clamp_lo = lo, p.clamp_hi = hi;
-    p.has_res = has_res, p.res_scale = res_scale, p.res_zp = res_zp, p.add_scale = add_scale, p.add_zp = add_zp;
-    return (uint32_t)epi_u8(acc, mult, bias, p, res);
-}
-
-template <bool RES, bool Y2>
+template <bool RES, bool Y2, bool CLAMP>
 __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &sg, TcShared &sh, uint32_t tmem_base,
                                               const CUtensorMap *tmap_y, const CUtensorMap *tmap_y2,
                                               const CUtensorMap *tmap_res, int warp, int lane) {
@@ -701,7 +687,7 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
     const uint32_t sub = (uint32_t)ew * 32u * hw;
     const uint32_t s_out = sg.smem_base + f.off_out + sub, s_y2 = sg.smem_base + f.off_y2 + sub;
     const uint32_t s_res = sg.smem_base + f.off_res + sub;
-    const uint32_t s_cst = sg.smem_base + f.off_cst, s_ex = sg.smem_base + f.off_ex, s_corr = sg.smem_base + f.off_corr;
+    const uint32_t s_cst = sg.smem_base + f.off_cst, s_corr = sg.smem_base + f.off_corr;
     const uint32_t s_lut2 = sg.smem_base + f.off_lut2;
     const uint32_t bar_res = smem_u32(&sh.bar_res[ew]);
     const bool multi_cls = f.n_cls > 1;
@@ -732,11 +718,9 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
             epi_bar_sync();
             for (int c = et; c < g.bn; c += 32 * EPI_WARPS) {
                 const float4 k = f.cst[oc0 + c];
-                const float2 e = f.ex[oc0 + c];
                 asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(s_cst + c * 16), "f"(k.x), "f"(k.y),
                              "f"(k.z), "f"(k.w)
                              : "memory");
-                asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(s_ex + c * 8), "f"(e.x), "f"(e.y) : "memory");
             }
             if (multi_cls)
                 for (int i = et; i < f.n_cls * g.bn; i += 32 * EPI_WARPS) {
@@ -790,42 +774,31 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
             if (RES)
                 rw = lds128(stage_addr(s_res, lane, cc >> 4, hw, f.out_sw));
             const uint32_t rwa[4] = {rw.x, rw.y, rw.z, rw.w};
-            int acc[16];
             uint32_t bits[16];
-            uint32_t slow = 0; // bit j: element j lies inside the guard band
 #pragma unroll
             for (int j = 0; j < 16; j++) {
-                const float4 k = lds128f(s_cst + (c0 + j) * 16);
+                const float4 k = lds128f(s_cst + (c0 + j) * 16); // {mult, bias, corr, -zw}
                 const int corr = multi_cls ? (int)lds32(corr_row + (c0 + j) * 4) : __float_as_int(k.z);
-                acc[j] = v[j] + __float_as_int(k.w) * rsum - corr;
-                const float t = __fmaf_rn((float)acc[j], k.x, k.y);
-                const float rf = rintf(t);
-                bool bad = !(fabsf(__fadd_rn(t, -rf)) <= f.thr1);
-                float qf = fminf(fmaxf(rf, f.qlo), f.qhi);
+                const int acc = v[j] + __float_as_int(k.w) * rsum - corr;
+                float x = __fadd_rn(__fmul_rn((float)acc, k.x), k.y);
+                if (CLAMP)
+                    x = clamp_dev(x, f.lo, f.hi);
+                // x / so, correctly rounded
+                float q0 = __fmul_rn(x, f.rso);
+                q0 = __fmaf_rn(__fmaf_rn(-q0, f.so, x), f.rso, q0);
+                float qf = fminf(fmaxf(rintf(__fadd_rn(q0, f.zo)), 0.f), 255.f);
                 if (RES) {
+                    // dequantize both addends, add, requantise: same chain as the unfused binary add
+                    const float ya = __fmul_rn(__fadd_rn(qf, -f.zo), f.so);
                     // byte j of the residual word as a float: 0x4B000000 | byte is 2^23 + byte
-                    const float rb = __fadd_rn(__uint_as_float(__byte_perm(rwa[j >> 2], 0x4B000000u, 0x7440 | (j & 3))),
-                                               -8388608.0f);
-                    const float t2 = __fmaf_rn(qf, f.ca, __fmaf_rn(rb, f.cb, f.cc));
-                    const float rf2 = rintf(t2);
-                    bad |= !(fabsf(__fadd_rn(t2, -rf2)) <= f.thr2);
-                    qf = fminf(fmaxf(rf2, 0.f), 255.f);
+                    const float rb = __uint_as_float(__byte_perm(rwa[j >> 2], 0x4B000000u, 0x7440 | (j & 3)));
+                    const float yb = __fmul_rn(__fadd_rn(rb, -f.zr_m), f.sr);
+                    const float sum = __fadd_rn(ya, yb);
+                    float p0 = __fmul_rn(sum, f.rsa);
+                    p0 = __fmaf_rn(__fmaf_rn(-p0, f.sa, sum), f.rsa, p0);
+                    qf = fminf(fmaxf(rintf(__fadd_rn(p0, f.za)), 0.f), 255.f);
                 }
-                slow |= (uint32_t)bad << j;
                 bits[j] = __float_as_uint(__fadd_rn(qf, MAGIC)); // low byte = the quantized value
-            }
-            if (slow) {
-                // inside the guard band (or not finite): the exact formula decides, element by element
-#pragma unroll
-                for (int j = 0; j < 16; j++) {
-                    if (slow & (1u << j)) {
-                        float mult, bias;
-                        asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(mult), "=f"(bias) : "r"(s_ex + (c0 + j) * 8));
-                        bits[j] = epi_u8_exact(acc[j], mult, bias, (int)((rwa[j >> 2] >> (8 * (j & 3))) & 255u),
-                                               a.p.out_scale, a.p.out_zp, a.p.clamp_lo, a.p.clamp_hi, RES ? 1 : 0,
-                                               a.p.res_scale, a.p.res_zp, a.p.add_scale, a.p.add_zp);
-                    }
-                }
             }
             uint4 o;
             o.x = __byte_perm(__byte_perm(bits[0], bits[1], 0x0040), __byte_perm(bits[2], bits[3], 0x0040), 0x5410);
@@ -872,7 +845,7 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
         tma_store_wait_all();
 }
 
-template <bool RES, bool Y2>
+template <bool RES, bool Y2, bool CLAMP>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 tc_conv_fast_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_y, const __grid_constant__ CUtensorMap tmap_y2,
@@ -891,7 +864,7 @@ tc_conv_fast_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (lane == 0)
             mma_loop(g, sg, sh, tmem_base, a.status);
     } else {
-        epilogue_fast<RES, Y2>(a, sg, sh, tmem_base, &tmap_y, &tmap_y2, &tmap_res, warp, lane);
+        epilogue_fast<RES, Y2, CLAMP>(a, sg, sh, tmem_base, &tmap_y, &tmap_y2, &tmap_res, warp, lane);
     }
     tc_teardown(g, sh, warp, tmem_base);
 }
@@ -899,6 +872,77 @@ tc_conv_fast_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 // ------------------------------------------------------------------------------------------------
 // host side: plan creation
 // ------------------------------------------------------------------------------------------------
+// RN(1/b) as a float, verified against its neighbours in extended precision. The three-operation
+// division of the fast epilogue returns the IEEE quotient only with a correctly rounded
+// reciprocal; scales far from 1 (where intermediate products could leave the normal range) are
+// refused, and the generic epilogue takes the layer.
+static float rn_reciprocal(float b, bool *ok) {
+    if (!(b > 1e-18f && b < 1e18f)) {
+        *ok = false;
+        return 0.f;
+    }
+    const long double lb = (long double)b;
+    float best = (float)(1.0L / lb);
+    const float cand[3] = {best, nextafterf(best, 0.f), nextafterf(best, INFINITY)};
+    long double best_err = -1;
+    for (float c : cand) {
+        long double e = 1.0L - lb * (long double)c; // exact: 24 x 24 bit product, difference near 0
+        if (e < 0)
+            e = -e;
+        if (best_err < 0 || e < best_err) {
+            best_err = e;
+            best = c;
+        }
+    }
+    return best;
+}
+
+// Self-test of the reciprocal division: compares it with the IEEE division for `count` operands
+// (random sign and mantissa, exponents spread over [2^-32, 2^32) times the divisor) and counts
+// disagreements.
+__global__ void reciprocal_division_selftest_kernel(float s, float r, unsigned long long count, unsigned long long seed,
+                                                    unsigned long long *mismatches) {
+    unsigned long long bad = 0;
+    for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < count;
+         i += (unsigned long long)gridDim.x * blockDim.x) {
+        unsigned long long z = (i + seed) * 0x9E3779B97F4A7C15ull; // splitmix64
+        z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+        z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+        z ^= z >> 31;
+        const uint32_t mant = (uint32_t)z & 0x7FFFFFu, sign = (uint32_t)(z >> 23) & 1u;
+        const int e = (int)((z >> 24) & 63u) - 32;
+        const float x = __uint_as_float((sign << 31) | ((uint32_t)(127 + e) << 23) | mant) * s;
+        float q0 = __fmul_rn(x, r);
+        q0 = __fmaf_rn(__fmaf_rn(-q0, s, x), r, q0);
+        if (q0 != __fdiv_rn(x, s))
+            bad++;
+    }
+    if (bad)
+        atomicAdd(mismatches, bad);
+}
+
+int reciprocal_division_selftest(nncb_context *ctx, float scale, unsigned long long count, unsigned long long seed,
+                                 unsigned long long *mismatches) {
+    bool ok = true;
+    const float r = rn_reciprocal(scale, &ok);
+    if (!ok)
+        return fail(-EINVAL, "scale %g is outside the range the reciprocal division accepts", (double)scale);
+    unsigned long long *d = nullptr;
+    NNCB_CUDA_TRY(cudaMalloc(&d, sizeof(*d)));
+    NNCB_CUDA_TRY(cudaMemsetAsync(d, 0, sizeof(*d), ctx->stream));
+    reciprocal_division_selftest_kernel<<<ctx->sm_count * 8, 256, 0, ctx->stream>>>(scale, r, count, seed, d);
+    int rc = after_launch(ctx, "reciprocal_division_selftest");
+    if (rc == 0) {
+        cudaError_t e = cudaMemcpyAsync(mismatches, d, sizeof(*d), cudaMemcpyDeviceToHost, ctx->stream);
+        if (e == cudaSuccess)
+            e = cudaStreamSynchronize(ctx->stream);
+        if (e != cudaSuccess)
+            rc = fail(-EIO, "self-test copy failed: %s", cudaGetErrorString(e));
+    }
+    cudaFree(d);
+    return rc;
+}
+
 static int pick_bn(int oc, bool xsum) {
     // N tile: as wide as the layer allows up to 128 (+16 for the row-sum column), multiple of 16.
     // 128, 64 and 32 are the widths the fast epilogue stages; prefer them when nothing is wasted.
@@ -965,7 +1009,6 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
         fe.off_y2 = off, off += d.has_y2 ? tile_bytes : 0;
         fe.off_res = off, off += d.has_residual ? tile_bytes : 0;
         fe.off_cst = off, off += (uint32_t)g.bn * 16;
-        fe.off_ex = off, off += (uint32_t)g.bn * 8;
         fe.off_lut2 = off, off += 256;
         fe.off_corr = off;
         extras = off; // the per-class table is appended once the classes are known
@@ -1071,70 +1114,36 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
         if (n_cls > 1)
             extras += (uint32_t)n_cls * fe.corr_pitch * 4;
         extras = (extras + 1023u) & ~1023u;
-        // Error bounds, in units of one quantization step. With u = 2^-24 the exact chain
-        // fl(fl(acc)*mult)+bias, /so, +zo and the fused t = fl(acc)*A + B each stay within
-        // u * (a few times the magnitudes involved) of the real-valued result; results that
-        // matter lie in [-1, 256], which bounds |acc*mult/so| by 512 + |bias/so|.
-        double max_b = 0;
         std::vector<float> hm(d.oc), hb(d.oc);
         NNCB_CUDA_TRY(cudaMemcpy(hm.data(), cv->d_mult, sizeof(float) * d.oc, cudaMemcpyDeviceToHost));
         NNCB_CUDA_TRY(cudaMemcpy(hb.data(), cv->d_bias, sizeof(float) * d.oc, cudaMemcpyDeviceToHost));
-        const double so = d.out_scale, zo = d.out_zp;
         std::vector<float4> cst(tp->oc_pad, make_float4(0, 0, 0, 0));
-        std::vector<float2> ex(tp->oc_pad, make_float2(0, 0));
-        bool finite = true;
         for (int oc = 0; oc < d.oc; oc++) {
-            const double A = (double)hm[oc] / so, B = (double)hb[oc] / so + zo;
-            finite = finite && std::isfinite(A) && std::isfinite(B) && hm[oc] > 0;
-            max_b = std::fmax(max_b, std::fabs((double)hb[oc] / so));
             const int32_t c0 = corr[oc], nzw = wzp_host ? -wzp_host[oc] : 0;
             float4 k;
-            k.x = (float)A, k.y = (float)B;
+            k.x = hm[oc], k.y = hb[oc];
             memcpy(&k.z, &c0, 4);
             memcpy(&k.w, &nzw, 4);
             cst[oc] = k;
-            ex[oc] = make_float2(hm[oc], hb[oc]);
         }
-        // Bound (derivation in units of a quantization step, u = 2^-24, X = acc*mult/so, Bq = bias/so,
-        // r = X + Bq + zo the real-valued result, |r| <= 256 and |zo| <= 255 for results that can
-        // change the output): exact chain within u*(|X| + 2|X+Bq| + |r|) of r, fused formula within
-        // u*(|X| + |Bq+zo| + |r|); with |X| <= 512 + |Bq| the sum is u*(2816 + 3|Bq|). Taken with a
-        // 1.5x margin for second-order terms and the rounding of the guard comparison itself.
-        const double u = 1.0 / 16777216.0;
-        const double eps1 = 1.5 * u * (2816.0 + 3.0 * max_b);
-        // quantize() is monotone, so clamping the real value equals clamping the quantized one
-        auto qexact = [&](float v) {
-            if (std::isinf(v))
-                return v > 0 ? 255.f : 0.f;
-            volatile float q1 = v / d.out_scale;
-            volatile float q2 = q1 + (float)d.out_zp;
-            float r = nearbyintf(q2);
-            return r < 0.f ? 0.f : (r > 255.f ? 255.f : r);
-        };
-        fe.qlo = qexact(d.clamp_lo);
-        fe.qhi = qexact(d.clamp_hi);
-        fe.thr1 = (float)(0.5 - eps1);
-        double eps2 = 0;
+        bool ok = true;
+        fe.so = d.out_scale, fe.zo = (float)d.out_zp;
+        fe.rso = rn_reciprocal(d.out_scale, &ok);
+        fe.lo = d.clamp_lo, fe.hi = d.clamp_hi;
+        fe.has_clamp = !(std::isinf(d.clamp_lo) && d.clamp_lo < 0 && std::isinf(d.clamp_hi) && d.clamp_hi > 0);
         if (d.has_residual) {
-            const double sa = d.add_out_scale, ca = so / sa, cb = (double)d.res_scale / sa;
-            const double cc = (double)d.add_out_zp - zo * ca - (double)d.res_zp * cb;
-            fe.ca = (float)ca, fe.cb = (float)cb, fe.cc = (float)cc;
-            // exact: fl(fl((q-zo)*so) + fl((r-zr)*sr)) / sa + za, four roundings after the two products;
-            // fused: two fma. Magnitudes: |q-zo|*ca and |r-zr|*cb are at most 255*ca, 255*cb; the
-            // result of interest is at most 256 in magnitude, cc is a constant.
-            eps2 = 1.5 * u * (6.0 * 255.0 * (ca + cb) + 3.0 * std::fabs(cc) + 1024.0);
-            finite = finite && std::isfinite(ca) && std::isfinite(cb) && std::isfinite(cc);
+            fe.sr = d.res_scale;
+            fe.zr_m = 8388608.0f + (float)d.res_zp;
+            fe.sa = d.add_out_scale, fe.za = (float)d.add_out_zp;
+            fe.rsa = rn_reciprocal(d.add_out_scale, &ok);
+            ok = ok && d.res_zp >= 0 && d.res_zp <= 255;
         }
-        fe.thr2 = (float)(0.5 - eps2);
-        if (!finite || !(eps1 < 0.125) || !(eps2 < 0.125) || std::isnan(d.clamp_lo) || std::isnan(d.clamp_hi))
-            tp->fast = false; // degenerate parameters: the generic (exact) epilogue takes the layer
+        if (!ok || std::isnan(d.clamp_lo) || std::isnan(d.clamp_hi))
+            tp->fast = false; // scales outside the range the reciprocal division is proven for
         if (tp->fast) {
             NNCB_CUDA_TRY(cudaMalloc(&tp->d_cst, cst.size() * sizeof(float4)));
-            NNCB_CUDA_TRY(cudaMalloc(&tp->d_ex, ex.size() * sizeof(float2)));
             NNCB_CUDA_TRY(cudaMemcpyAsync(tp->d_cst, cst.data(), cst.size() * sizeof(float4), cudaMemcpyHostToDevice, ctx->stream));
-            NNCB_CUDA_TRY(cudaMemcpyAsync(tp->d_ex, ex.data(), ex.size() * sizeof(float2), cudaMemcpyHostToDevice, ctx->stream));
             fe.cst = tp->d_cst;
-            fe.ex = tp->d_ex;
         }
     }
     NNCB_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
@@ -1152,7 +1161,7 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
     g.stages = stages;
     const uint32_t ring = (uint32_t)stages * (a_stage + b_pitch);
     if (tp->fast) {
-        fe.off_out += ring, fe.off_y2 += ring, fe.off_res += ring, fe.off_cst += ring, fe.off_ex += ring;
+        fe.off_out += ring, fe.off_y2 += ring, fe.off_res += ring, fe.off_cst += ring;
         fe.off_lut2 += ring, fe.off_corr += ring;
     }
     // More than half of an SM's shared memory, so exactly one CTA (and one TMEM allocation) per SM.
@@ -1163,10 +1172,13 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
     // plan can ask for.
     const int lim = 226 * 1024;
     NNCB_CUDA_TRY(cudaFuncSetAttribute(tc_conv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
-    NNCB_CUDA_TRY(cudaFuncSetAttribute(tc_conv_fast_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
-    NNCB_CUDA_TRY(cudaFuncSetAttribute(tc_conv_fast_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
-    NNCB_CUDA_TRY(cudaFuncSetAttribute(tc_conv_fast_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
-    NNCB_CUDA_TRY(cudaFuncSetAttribute(tc_conv_fast_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+    const void *fast_kernels[8] = {
+        (const void *)tc_conv_fast_kernel<false, false, false>, (const void *)tc_conv_fast_kernel<false, false, true>,
+        (const void *)tc_conv_fast_kernel<false, true, false>,  (const void *)tc_conv_fast_kernel<false, true, true>,
+        (const void *)tc_conv_fast_kernel<true, false, false>,  (const void *)tc_conv_fast_kernel<true, false, true>,
+        (const void *)tc_conv_fast_kernel<true, true, false>,   (const void *)tc_conv_fast_kernel<true, true, true>};
+    for (const void *k : fast_kernels)
+        NNCB_CUDA_TRY(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
     return 0;
 }
 
@@ -1180,7 +1192,6 @@ void tc_conv_destroy(nncb_qconv2d *cv) {
     cudaFree(tp->d_ycls);
     cudaFree(tp->d_xcls);
     cudaFree(tp->d_cst);
-    cudaFree(tp->d_ex);
     delete tp->f;
     delete tp;
     cv->tc = nullptr;
@@ -1241,14 +1252,21 @@ int tc_conv_run(nncb_context *ctx, nncb_qconv2d *cv, const uint8_t *x, const uin
             tp->res_ptr = res;
         }
         const CUtensorMap &my2 = y2 ? tp->tmap_y2 : tp->tmap_y, &mres = res ? tp->tmap_res : tp->tmap_y;
-        if (res && y2)
-            tc_conv_fast_kernel<true, true><<<grid, TC_THREADS, tp->smem_bytes, ctx->stream>>>(tp->tmap_a, tp->tmap_b, tp->tmap_y, my2, mres, a);
-        else if (res)
-            tc_conv_fast_kernel<true, false><<<grid, TC_THREADS, tp->smem_bytes, ctx->stream>>>(tp->tmap_a, tp->tmap_b, tp->tmap_y, my2, mres, a);
-        else if (y2)
-            tc_conv_fast_kernel<false, true><<<grid, TC_THREADS, tp->smem_bytes, ctx->stream>>>(tp->tmap_a, tp->tmap_b, tp->tmap_y, my2, mres, a);
-        else
-            tc_conv_fast_kernel<false, false><<<grid, TC_THREADS, tp->smem_bytes, ctx->stream>>>(tp->tmap_a, tp->tmap_b, tp->tmap_y, my2, mres, a);
+        const int variant = (res ? 4 : 0) | (y2 ? 2 : 0) | (tp->f->has_clamp ? 1 : 0);
+#define NNCB_LAUNCH_FAST(R, Y, C)                                                                                     \
+    tc_conv_fast_kernel<R, Y, C><<<grid, TC_THREADS, tp->smem_bytes, ctx->stream>>>(tp->tmap_a, tp->tmap_b, tp->tmap_y, \
+                                                                                   my2, mres, a)
+        switch (variant) {
+        case 0: NNCB_LAUNCH_FAST(false, false, false); break;
+        case 1: NNCB_LAUNCH_FAST(false, false, true); break;
+        case 2: NNCB_LAUNCH_FAST(false, true, false); break;
+        case 3: NNCB_LAUNCH_FAST(false, true, true); break;
+        case 4: NNCB_LAUNCH_FAST(true, false, false); break;
+        case 5: NNCB_LAUNCH_FAST(true, false, true); break;
+        case 6: NNCB_LAUNCH_FAST(true, true, false); break;
+        default: NNCB_LAUNCH_FAST(true, true, true); break;
+        }
+#undef NNCB_LAUNCH_FAST
         return after_launch(ctx, "tc_conv_fast");
     }
     tc_conv_kernel<<<grid, TC_THREADS, tp->smem_bytes, ctx->stream>>>(tp->tmap_a, tp->tmap_b, a);

@@ -172,6 +172,17 @@ def test_golden_conv_slice(ctx):
         assert d.max() <= 1 and (d != 0).sum() <= int(c["allowed_mismatches"])
 
 
+@pytest.mark.parametrize("scale", [0.5, 0.014035294, 0.029455967, 0.3709820, 12.381763, 1.0 / 3.0, 7.955359,
+                                   1.1920929e-07 * 8388607, 3.4e-5, 1999.0])
+def test_reciprocal_division_matches_ieee(ctx, scale):
+    """The epilogue's division by a scale (reciprocal + two fused corrections) against the IEEE
+    division on 2^26 operands per scale."""
+    import ctypes
+    m = ctypes.c_uint64(123)
+    L.check(ctx._lib.nncb_selftest_reciprocal_division(ctx._h, scale, 1 << 26, 17, ctypes.byref(m)))
+    assert m.value == 0
+
+
 def test_bad_arguments_are_rejected(ctx):
     from nncase_b200.lib import NncbError
     w = np.zeros((8, 3, 3, 5), np.uint8)
