@@ -161,6 +161,20 @@ NNCB_API int nncb_qconv2d_run(nncb_context *ctx, nncb_qconv2d *conv, const uint8
 /* One-shot with HOST buffers: x u8 NHWC in, y out; weights as in create. */
 NNCB_API int nncb_qconv2d_host(nncb_context *ctx, const nncb_conv2d_desc *desc, const void *weights, const int32_t *w_zp, const float *mult, const float *bias, const uint8_t *lut, const uint8_t *x, const uint8_t *res, void *y, uint8_t *y2);
 
+/* ---- paged-attention decode ---------------------------------------------------------------
+ * The reference has no attention, KV-cache or softmax-over-pages operator (its native op list is
+ * src/Native/include/nncase/kernels/stackvm/tensor_ops.h:29-479); this entry point defines one.
+ * Math follows the reference's mat_mul and softmax kernels (reference/matmul.cpp:28-51,
+ * reference/softmax.cpp:30-80): f32 scores, max-subtracted softmax, f32 value sum.
+ *   q [batch][q_heads][head_dim] f16; k_pool, v_pool [num_pages][kv_heads][page_size][head_dim] f16;
+ *   block_table [batch][max_pages] int32 page ids; context_lens [batch] int32 (0 gives a zero row);
+ *   out [batch][q_heads][head_dim] f16.  Query head h reads kv head h / (q_heads / kv_heads).
+ * Built for head_dim 64, page_size 16, q_heads / kv_heads <= 8 (others: -ENOSYS).
+ * The context is split across CTAs; partial results go through `workspace` (device memory, size
+ * from nncb_paged_attention_workspace_size, may be 0). */
+NNCB_API int nncb_paged_attention_workspace_size(nncb_context *ctx, int batch, int q_heads, int kv_heads, int head_dim, int page_size, int max_pages, size_t *bytes);
+NNCB_API int nncb_paged_attention_decode(nncb_context *ctx, const void *q, const void *k_pool, const void *v_pool, const int32_t *block_table, const int32_t *context_lens, void *out, int batch, int q_heads, int kv_heads, int head_dim, int page_size, int max_pages, float scale, void *workspace, size_t workspace_bytes);
+
 /* Diagnostic: the tensor-core kernel divides by a layer's output scale with a three-operation
  * sequence around a correctly rounded reciprocal. This runs that sequence against the IEEE
  * division for `count` pseudo-random operands on the device and returns how many differ

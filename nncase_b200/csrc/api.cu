@@ -81,6 +81,13 @@ int lut_u8(nncb_context *, const uint8_t *, uint8_t *, size_t, const uint8_t *);
 int maxpool_u8(nncb_context *, const uint8_t *, uint8_t *, int, int, int, int, int, int, int, int, int, int, int, int, int32_t);
 int global_avgpool_u8(nncb_context *, const uint8_t *, uint8_t *, int, int, int, int, float, int32_t, float, int32_t);
 
+size_t paged_attention_scratch_bytes(int B, int Hq, int splits);
+int paged_attention_pick_splits(const nncb_context *ctx, int B, int Hkv, int max_ctx);
+int paged_attention_check(int B, int Hq, int Hkv, int head_dim, int page_size, int max_pages);
+int paged_attention_launch(nncb_context *ctx, const void *q, const void *k_pool, const void *v_pool,
+                           const int32_t *block_table, const int32_t *ctx_lens, void *out, int B, int Hq, int Hkv,
+                           int max_pages, float scale, int splits, void *scratch);
+
 static size_t qtype_size(int qtype) { return qtype == NNCB_I16 ? 2 : 1; }
 
 } // namespace nncb
@@ -349,6 +356,38 @@ int nncb_maxpool_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, int n, int 
 int nncb_global_avgpool_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, int n, int h, int w, int c, float si, int32_t zi, float so, int32_t zo) {
     CHECK_CTX(ctx);
     return global_avgpool_u8(ctx, x, y, n, h, w, c, si, zi, so, zo);
+}
+
+// ---- paged attention -----------------------------------------------------------------------
+int nncb_paged_attention_workspace_size(nncb_context *ctx, int batch, int q_heads, int kv_heads, int head_dim,
+                                        int page_size, int max_pages, size_t *bytes) {
+    CHECK_CTX(ctx);
+    if (!bytes)
+        return fail(-EINVAL, "nncb_paged_attention_workspace_size: null out");
+    NNCB_TRY(paged_attention_check(batch, q_heads, kv_heads, head_dim, page_size, max_pages));
+    const int splits = paged_attention_pick_splits(ctx, batch, kv_heads, max_pages * page_size);
+    *bytes = paged_attention_scratch_bytes(batch, q_heads, splits);
+    return 0;
+}
+
+int nncb_paged_attention_decode(nncb_context *ctx, const void *q, const void *k_pool, const void *v_pool,
+                                const int32_t *block_table, const int32_t *context_lens, void *out, int batch,
+                                int q_heads, int kv_heads, int head_dim, int page_size, int max_pages, float scale,
+                                void *workspace, size_t workspace_bytes) {
+    CHECK_CTX(ctx);
+    if (!q || !k_pool || !v_pool || !block_table || !context_lens || !out)
+        return fail(-EINVAL, "nncb_paged_attention_decode: null pointer");
+    NNCB_TRY(paged_attention_check(batch, q_heads, kv_heads, head_dim, page_size, max_pages));
+    if ((reinterpret_cast<uintptr_t>(k_pool) | reinterpret_cast<uintptr_t>(v_pool) | reinterpret_cast<uintptr_t>(q) |
+         reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(workspace)) & 15)
+        return fail(-EINVAL, "nncb_paged_attention_decode: pointers must be 16-byte aligned");
+    const int splits = paged_attention_pick_splits(ctx, batch, kv_heads, max_pages * page_size);
+    const size_t need = paged_attention_scratch_bytes(batch, q_heads, splits);
+    if (need > 0 && (!workspace || workspace_bytes < need))
+        return fail(-EINVAL, "nncb_paged_attention_decode: workspace of %zu bytes required, %zu given", need,
+                    workspace ? workspace_bytes : (size_t)0);
+    return paged_attention_launch(ctx, q, k_pool, v_pool, block_table, context_lens, out, batch, q_heads, kv_heads,
+                                  max_pages, scale, splits, workspace);
 }
 
 // ---- quantized conv ------------------------------------------------------------------------

@@ -197,6 +197,30 @@ class Context:
                                                qi.zero_point, qo.scale, qo.zero_point))
         return y
 
+    # ---- paged attention ----------------------------------------------------------------------
+    def paged_attention_decode(self, q, k_pool, v_pool, block_table, context_lens, scale=None, workspace=None):
+        """q [B,Hq,D] f16; k_pool/v_pool [pages,Hkv,page,D] f16; block_table [B,max_pages] i32;
+        context_lens [B] i32 -> out [B,Hq,D] f16."""
+        q = self._cuda(q, torch.float16)
+        k_pool, v_pool = self._cuda(k_pool, torch.float16), self._cuda(v_pool, torch.float16)
+        block_table = self._cuda(block_table, torch.int32)
+        context_lens = self._cuda(context_lens, torch.int32)
+        b, hq, d = q.shape
+        _, hkv, page, _ = k_pool.shape
+        max_pages = block_table.shape[1]
+        scale = float(scale) if scale is not None else 1.0 / float(np.sqrt(d))
+        need = C.c_size_t()
+        check(self._lib.nncb_paged_attention_workspace_size(self._h, b, hq, hkv, d, page, max_pages, C.byref(need)))
+        if workspace is None and need.value:
+            workspace = torch.empty(need.value, dtype=torch.uint8, device=self.device)
+        out = torch.empty_like(q)
+        check(self._lib.nncb_paged_attention_decode(
+            self._h, q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), block_table.data_ptr(),
+            context_lens.data_ptr(), out.data_ptr(), b, hq, hkv, d, page, max_pages, scale,
+            workspace.data_ptr() if workspace is not None else None,
+            workspace.numel() if workspace is not None else 0))
+        return out
+
     # ---- conv2d / mat_mul -------------------------------------------------------------------
     def conv2d_plan(self, in_shape, weights, w_zp, mult, bias, x_zp, out_qp, stride=(1, 1), padding=(0, 0, 0, 0),
                     dilation=(1, 1), groups=1, fused_clamp=(-float("inf"), float("inf")), lut=None,

@@ -1,0 +1,77 @@
+"""Paged-attention decode on the GPU against the numpy restatement: f32 math on f16 data,
+max-abs error <= 1e-3 of the output range."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import attention as OA
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3  # relative to the output range
+
+
+def make_cache(seed, b, hq, hkv, ctx_lens, d=64, page=16, extra_pages=5):
+    rng = np.random.default_rng(seed)
+    max_pages = max(1, (max(ctx_lens) + page - 1) // page)
+    total = b * max_pages + extra_pages
+    k_pool = rng.normal(0, 1, (total, hkv, page, d)).astype(np.float16)
+    v_pool = rng.normal(0, 1, (total, hkv, page, d)).astype(np.float16)
+    perm = rng.permutation(total)[: b * max_pages].astype(np.int32)  # random block-table permutation
+    table = perm.reshape(b, max_pages)
+    q = rng.normal(0, 1, (b, hq, d)).astype(np.float16)
+    return q, k_pool, v_pool, table, np.asarray(ctx_lens, np.int32)
+
+
+def check(ctx, case):
+    q, k, v, table, lens = case
+    want = OA.paged_attention_decode(q, k, v, table, lens).astype(np.float32)
+    got = ctx.paged_attention_decode(torch.from_numpy(q), torch.from_numpy(k), torch.from_numpy(v),
+                                     torch.from_numpy(table), torch.from_numpy(lens)).cpu().numpy().astype(np.float32)
+    rng_ = max(float(want.max() - want.min()), 1e-6)
+    err = float(np.abs(got - want).max())
+    assert err <= TOL * rng_, f"max abs err {err} vs range {rng_}"
+
+
+@pytest.mark.parametrize("hq,hkv", [(14, 2), (8, 8), (8, 1), (4, 2)])
+def test_ragged_contexts(ctx, hq, hkv):
+    lens = [1, 15, 16, 17, 33, 100, 511, 512, 513, 700, 0, 2048]
+    check(ctx, make_cache(5, len(lens), hq, hkv, lens))
+
+
+def test_single_token_and_empty(ctx):
+    check(ctx, make_cache(6, 3, 14, 2, [0, 1, 1]))
+
+
+def test_qwen2_shape_small_batch(ctx):
+    """Qwen2-0.5B shape (14 query / 2 kv heads, head_dim 64, 16-token pages) at context 2048."""
+    check(ctx, make_cache(7, 8, 14, 2, [2048] * 8))
+
+
+def test_large_scores_are_stable(ctx):
+    q, k, v, table, lens = make_cache(8, 2, 14, 2, [300, 64])
+    q = (q.astype(np.float32) * 6).astype(np.float16)  # sharp softmax
+    check(ctx, (q, k, v, table, lens))
+
+
+def test_softmax_rows_sum_to_one_full_size(ctx):
+    """Config size (batch 64, context 2048): with V = 1 everywhere every output must be 1 -- a
+    property of softmax that needs no oracle."""
+    b, hq, hkv, n = 64, 14, 2, 2048
+    g = torch.Generator(device="cuda").manual_seed(1)
+    pages = b * n // 16
+    k = torch.randn((pages, hkv, 16, 64), device="cuda", generator=g, dtype=torch.float16)
+    v = torch.ones((pages, hkv, 16, 64), device="cuda", dtype=torch.float16)
+    q = torch.randn((b, hq, 64), device="cuda", generator=g, dtype=torch.float16)
+    table = torch.randperm(pages, device="cuda", generator=g).to(torch.int32).reshape(b, n // 16)
+    lens = torch.full((b,), n, dtype=torch.int32, device="cuda")
+    out = ctx.paged_attention_decode(q, k, v, table, lens)
+    assert float((out.float() - 1.0).abs().max()) <= 1e-3
+
+
+def test_unsupported_shapes_are_rejected(ctx):
+    from nncase_b200.lib import NncbError
+    q = torch.zeros((1, 4, 128), dtype=torch.float16)
+    k = torch.zeros((2, 4, 16, 128), dtype=torch.float16)
+    with pytest.raises(NncbError) as e:
+        ctx.paged_attention_decode(q, k, k, torch.zeros((1, 2), dtype=torch.int32), torch.ones(1, dtype=torch.int32))
+    assert e.value.code == -38
