@@ -175,6 +175,26 @@ NNCB_API int nncb_qconv2d_host(nncb_context *ctx, const nncb_conv2d_desc *desc, 
 NNCB_API int nncb_paged_attention_workspace_size(nncb_context *ctx, int batch, int q_heads, int kv_heads, int head_dim, int page_size, int max_pages, size_t *bytes);
 NNCB_API int nncb_paged_attention_decode(nncb_context *ctx, const void *q, const void *k_pool, const void *v_pool, const int32_t *block_table, const int32_t *context_lens, void *out, int batch, int q_heads, int kv_heads, int head_dim, int page_size, int max_pages, float scale, void *workspace, size_t workspace_bytes);
 
+/* Paged-attention decode for callers that must not allocate. (No counterpart in the reference.)
+ *
+ * Some hosts of this library hand out all device memory up front and forbid the allocator
+ * afterwards: a runtime that plans every buffer when the model is loaded, an inference loop with a
+ * fixed memory budget owned by another framework, code running while a stream is being captured.
+ * They cannot provide (or size) the workspace that nncb_paged_attention_decode wants. This variant
+ * takes the same inputs and outputs and keeps the split partials in a 768 KiB array that is part of
+ * the library image on every GPU that loads it. It calls no cudaMalloc, cudaFree or other allocating
+ * routine.
+ *  - Limit: batch * q_heads * splits * 264 bytes must fit 768 KiB (the Qwen2-0.5B decode shape,
+ *    batch 64 x 14 heads x 3 context splits, uses 693 KiB); larger problems return -E2BIG with a
+ *    message that names both sizes.
+ *  - The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that
+ *    device current) and remembers it; make that first call before starting any stream capture.
+ *  - All calls on a device share the one array. Nothing in it has to be cleared between calls (every
+ *    entry that is read is written first by the same call), but two calls that overlap on the GPU
+ *    -- different streams, or different contexts -- race on it: serialise them.
+ * Results are identical to nncb_paged_attention_decode. */
+NNCB_API int nncb_paged_attention_decode_noalloc(nncb_context *ctx, const void *q, const void *k_pool, const void *v_pool, const int32_t *block_table, const int32_t *context_lens, void *out, int batch, int q_heads, int kv_heads, int head_dim, int page_size, int max_pages, float scale);
+
 /* Diagnostic: the tensor-core kernel divides by a layer's output scale with a three-operation
  * sequence around a correctly rounded reciprocal. This runs that sequence against the IEEE
  * division for `count` pseudo-random operands on the device and returns how many differ

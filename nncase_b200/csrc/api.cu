@@ -88,6 +88,9 @@ int paged_attention_launch(nncb_context *ctx, const void *q, const void *k_pool,
                            const int32_t *block_table, const int32_t *ctx_lens, void *out, int B, int Hq, int Hkv,
                            int max_pages, float scale, int splits, void *scratch);
 
+size_t paged_attention_static_capacity();
+int paged_attention_static_scratch(int device, void **ptr);
+
 static size_t qtype_size(int qtype) { return qtype == NNCB_I16 ? 2 : 1; }
 
 } // namespace nncb
@@ -388,6 +391,30 @@ int nncb_paged_attention_decode(nncb_context *ctx, const void *q, const void *k_
                     workspace ? workspace_bytes : (size_t)0);
     return paged_attention_launch(ctx, q, k_pool, v_pool, block_table, context_lens, out, batch, q_heads, kv_heads,
                                   max_pages, scale, splits, workspace);
+}
+
+int nncb_paged_attention_decode_noalloc(nncb_context *ctx, const void *q, const void *k_pool, const void *v_pool,
+                                        const int32_t *block_table, const int32_t *context_lens, void *out, int batch,
+                                        int q_heads, int kv_heads, int head_dim, int page_size, int max_pages,
+                                        float scale) {
+    CHECK_CTX(ctx);
+    if (!q || !k_pool || !v_pool || !block_table || !context_lens || !out)
+        return fail(-EINVAL, "nncb_paged_attention_decode_noalloc: null pointer");
+    NNCB_TRY(paged_attention_check(batch, q_heads, kv_heads, head_dim, page_size, max_pages));
+    if ((reinterpret_cast<uintptr_t>(k_pool) | reinterpret_cast<uintptr_t>(v_pool) | reinterpret_cast<uintptr_t>(q) |
+         reinterpret_cast<uintptr_t>(out)) & 15)
+        return fail(-EINVAL, "nncb_paged_attention_decode_noalloc: pointers must be 16-byte aligned");
+    const int splits = paged_attention_pick_splits(ctx, batch, kv_heads, max_pages * page_size);
+    const size_t need = paged_attention_scratch_bytes(batch, q_heads, splits);
+    if (need > paged_attention_static_capacity())
+        return fail(-E2BIG,
+                    "nncb_paged_attention_decode_noalloc: batch %d x %d heads x %d context splits needs %zu bytes of "
+                    "scratch, the built-in array holds %zu; use nncb_paged_attention_decode with a workspace",
+                    batch, q_heads, splits, need, paged_attention_static_capacity());
+    void *scratch = nullptr;
+    NNCB_TRY(paged_attention_static_scratch(ctx->device, &scratch));
+    return paged_attention_launch(ctx, q, k_pool, v_pool, block_table, context_lens, out, batch, q_heads, kv_heads,
+                                  max_pages, scale, splits, scratch);
 }
 
 // ---- quantized conv ------------------------------------------------------------------------

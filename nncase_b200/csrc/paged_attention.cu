@@ -335,4 +335,33 @@ int paged_attention_launch(nncb_context *ctx, const void *q, const void *k_pool,
     return 0;
 }
 
+// ---- variant that allocates nothing -----------------------------------------------------------
+// Scratch for the split partials lives in this fixed device array instead of caller memory. Every
+// GPU that loads the library holds it until the process exits.
+constexpr size_t PA_STATIC_SCRATCH_BYTES = 768u << 10; // 768 KiB
+static __device__ __align__(256) unsigned char pa_static_scratch[PA_STATIC_SCRATCH_BYTES];
+
+size_t paged_attention_static_capacity() { return PA_STATIC_SCRATCH_BYTES; }
+
+// Device address of the array on `device`. In host code the array's name is only a handle, not
+// a device pointer, so the address is asked from the runtime once per device, with that device
+// current, and remembered.
+int paged_attention_static_scratch(int device, void **ptr) {
+    constexpr int MAX_DEV = 64;
+    static void *cached[MAX_DEV] = {nullptr};
+    if (device < 0 || device >= MAX_DEV)
+        return fail(-EINVAL, "paged_attention (static scratch): device %d out of range", device);
+    if (!cached[device]) {
+        int cur = -1;
+        NNCB_CUDA_TRY(cudaGetDevice(&cur));
+        if (cur != device)
+            return fail(-EINVAL, "paged_attention (static scratch): device %d is not current", device);
+        void *p = nullptr;
+        NNCB_CUDA_TRY(cudaGetSymbolAddress(&p, pa_static_scratch));
+        cached[device] = p;
+    }
+    *ptr = cached[device];
+    return 0;
+}
+
 } // namespace nncb

@@ -85,6 +85,7 @@ SIGNATURES = {
     "nncb_qconv2d_run": (_I, [_VP, _VP, _VP, _VP, _VP, _VP]),
     "nncb_paged_attention_workspace_size": (_I, [_VP, _I, _I, _I, _I, _I, _I, C.POINTER(_SZ)]),
     "nncb_paged_attention_decode": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _F, _VP, _SZ]),
+    "nncb_paged_attention_decode_noalloc": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _F]),
     "nncb_selftest_reciprocal_division": (_I, [_VP, _F, C.c_uint64, C.c_uint64, C.POINTER(C.c_uint64)]),
     "nncb_qconv2d_host": (_I, [_VP, C.POINTER(Conv2dDesc), _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP]),
 }
