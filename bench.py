@@ -391,6 +391,62 @@ def run_layer(args):
                           gbs=(in_bytes + out_bytes + op["w"].size) / (ms / 1000) / 1e9)))
 
 
+def run_attention(args):
+    """Secondary measurement: paged-attention decode at the Qwen2-0.5B decode shape (batch 64, context
+    2048, 14 query / 2 kv heads, head_dim 64, 16-token f16 pages, random block-table permutation).
+    One step = the attention of all 24 layers, each over its own KV pool (1.61 GB of K/V per step,
+    larger than L2), reported as achieved HBM GB/s over the K/V bytes referenced."""
+    import torch
+    from nncase_b200.kernels import Context
+    dev = torch.device("cuda", 0)
+    ctx = Context(0)
+    B, Hq, Hkv, D, page, n_ctx, layers = 64, 14, 2, 64, 16, 2048, 24
+    pages = B * n_ctx // page
+    g = torch.Generator(device=dev).manual_seed(2005)
+    pools = [(torch.randn((pages, Hkv, page, D), device=dev, generator=g, dtype=torch.float16),
+              torch.randn((pages, Hkv, page, D), device=dev, generator=g, dtype=torch.float16)) for _ in range(layers)]
+    q = torch.randn((B, Hq, D), device=dev, generator=g, dtype=torch.float16)
+    table = torch.randperm(pages, device=dev, generator=g).to(torch.int32).reshape(B, n_ctx // page).contiguous()
+    lens = torch.full((B,), n_ctx, dtype=torch.int32, device=dev)
+    need = 1 << 22
+    ws = torch.empty(need, dtype=torch.uint8, device=dev)
+
+    def step():
+        for k, v in pools:
+            ctx.paged_attention_decode(q, k, v, table, lens, workspace=ws)
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    torch.cuda.synchronize()
+    # a decode step is launch-bound from Python (24 short kernels): replay it as one CUDA graph
+    l0 = ctx.launches
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        ctx.use_current_stream()
+        step()
+    ctx.use_current_stream()
+    launches_per_step = ctx.launches - l0
+    graph.replay()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.steps):
+        graph.replay()
+    b.record()
+    torch.cuda.synchronize()
+    ctx.check_status()
+    ms = a.elapsed_time(b) / args.steps
+    kv_bytes = layers * B * n_ctx * Hkv * D * 2 * 2
+    pk = peaks()
+    gbs = kv_bytes / (ms / 1000) / 1e9
+    print(json.dumps(dict(metric="paged-attention decode HBM GB/s", value=gbs, unit="GB/s", ms_per_step=ms,
+                          steps=args.steps, kv_bytes_per_step=kv_bytes, gpu_launches=launches_per_step * args.steps,
+                          config=dict(workload="qwen2_0.5b_decode_attention", batch=B, context=n_ctx, q_heads=Hq,
+                                      kv_heads=Hkv, head_dim=D, page=page, layers=layers),
+                          roofline=dict(bound="hbm", achieved=gbs, peak=pk["hbm_gbs"], unit="GB/s",
+                                        frac=gbs / pk["hbm_gbs"], peak_source=pk["source"]))))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -402,8 +458,11 @@ def main():
     ap.add_argument("--layers", action="store_true", help="print per-layer timings to stderr")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layer", default=None, help="time only this conv layer (profiling aid)")
+    ap.add_argument("--attention", action="store_true", help="secondary metric: paged-attention decode GB/s")
     args = ap.parse_args()
-    if args.layer:
+    if args.attention:
+        run_attention(args)
+    elif args.layer:
         run_layer(args)
     elif args.impl == "reference":
         run_reference(args)

@@ -23,6 +23,7 @@
 // With `splits` > 1 partial (max, sum, unnormalised output) triples go to a scratch buffer and a
 // second small kernel merges them.
 #include "internal.cuh"
+#include <cstdlib>
 #include <cuda_fp16.h>
 
 namespace nncb {
@@ -286,15 +287,19 @@ size_t paged_attention_scratch_bytes(int B, int Hq, int splits) {
 }
 
 int paged_attention_pick_splits(const nncb_context *ctx, int B, int Hkv, int max_ctx) {
-    // enough CTAs for two per SM, but at least 8 pages (4 units) per CTA
-    const int ctas = B * Hkv;
-    int s = (2 * ctx->sm_count + ctas - 1) / ctas;
+    // Two CTAs fit an SM (96 KB of shared memory each). Split the context so that the grid fills
+    // those slots in ONE wave -- a second, partly filled wave costs a full pass -- but keep at
+    // least 8 pages (4 units) per CTA.
+    const int ctas = B * Hkv, slots = 2 * ctx->sm_count;
+    int s = slots / ctas;
     const int pages = (max_ctx + PA_PAGE - 1) / PA_PAGE;
     const int cap = pages / 8 > 1 ? pages / 8 : 1;
     if (s > cap)
         s = cap;
     if (s > 16)
         s = 16;
+    if (const char *e = getenv("NNCB_PA_SPLITS")) // tuning aid: force the split count
+        s = atoi(e);
     return s < 1 ? 1 : s;
 }
 
