@@ -303,14 +303,10 @@ def run_ours(args):
             tc_ms += t
     ctx.check_status()
 
-    # max over ranks of the device-measured times
-    if world > 1:
-        tt = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = float(tt[0]), float(tt[1])
-        tl = torch.tensor([gpu_launches], device=dev, dtype=torch.int64)
-        dist.all_reduce(tl)
-        gpu_launches = int(tl[0])
+    # max over ranks of the device-measured times, sum of the launch counters
+    from nncase_b200 import sharding
+    ms, e2e_ms = sharding.max_over_ranks([ms, e2e_ms], dev)
+    gpu_launches = sharding.sum_over_ranks([gpu_launches], dev)[0]
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
