@@ -1,11 +1,13 @@
 // Minimal stand-in for the gsl-lite header that the nncase native sources include.
 //
-// TEST INFRASTRUCTURE ONLY. The nncase native runtime depends on gsl-lite 0.37
-// (a Conan package that is not vendored in its tree). This file provides just the
-// surface those sources use -- gsl::span, gsl::byte, gsl::cstring_span, make_span
-// and four configuration macros -- written from scratch on top of the C++20
-// standard library so that the reference kernels can be compiled where they lie
-// into oracle/_ref/ and used as the parity checker / CPU baseline.
+// BUILD SHIM. The nncase native runtime depends on gsl-lite 0.37 (a Conan package that
+// is not vendored in its tree). This file provides just the surface its headers and
+// sources use -- gsl::span, gsl::byte, gsl::cstring_span, make_span and four
+// configuration macros -- written from scratch on top of the C++20 standard library,
+// so that code can be compiled against the reference's headers where the package is
+// not installed: the runtime plugin in this directory, and the CPU checker that
+// compiles the reference's own kernels. With the real gsl-lite on the include path
+// this file is not needed.
 #pragma once
 #include <algorithm>
 #include <array>
