@@ -103,6 +103,19 @@ NNCB_API int nncb_qadd_u8(nncb_context *ctx, const uint8_t *a, const uint8_t *b,
 /* y = quantize(clamp(dequantize(x), lo, hi)) -- clamp/relu/relu6 between quant params
  * (kernels::stackvm::clamp / relu, reference/activation.cpp:32-55). Runs as a 256-entry table. */
 NNCB_API int nncb_requant_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, size_t n, float si, int32_t zi, float so, int32_t zo, float lo, float hi);
+/* Unary activations on u8 (kernels::stackvm::relu / sigmoid / swish / hard_swish,
+ * src/Native/src/kernels/stackvm/reference/activation.cpp:32-38, evaluated in double like the
+ * reference's UNARY_TEMPLATE, kernel_template.h:19-50):
+ *   y = quantize((float)f((double)dequantize(x)))   as a 256-entry table.
+ * nncb_make_activation_table / nncb_make_requant_table (host) give the tables themselves, e.g. to
+ * fuse an activation into a convolution through its `lut` argument. */
+typedef enum nncb_activation { NNCB_ACT_RELU = 0, NNCB_ACT_SIGMOID = 1, NNCB_ACT_SWISH = 2, NNCB_ACT_HARD_SWISH = 3 } nncb_activation;
+NNCB_API int nncb_activation_u8(nncb_context *ctx, int kind, const uint8_t *x, uint8_t *y, size_t n, float si, int32_t zi, float so, int32_t zo);
+NNCB_API int nncb_make_activation_table(int kind, float si, int32_t zi, float so, int32_t zo, uint8_t *table);
+NNCB_API int nncb_make_requant_table(float si, int32_t zi, float so, int32_t zo, float lo, float hi, uint8_t *table);
+/* softmax over the last axis of a [rows, cols] f32 tensor (kernels::stackvm::softmax,
+ * tensor_ops.cpp:1054-1071; reference/softmax.cpp:30-80): exp((x - max) * beta) / sum. */
+NNCB_API int nncb_softmax_f32(nncb_context *ctx, const float *in, float *out, size_t rows, int cols, float beta);
 /* y[i] = table[x[i]]; table: 256 bytes, HOST pointer. */
 NNCB_API int nncb_lut_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, size_t n, const uint8_t *host_table);
 /* reduce_window2d max (tensor_ops.cpp: reduce_window2d, reference/reduce_window.cpp:35-105):

@@ -1,6 +1,7 @@
 // extern "C" entry points declared in include/nncase_b200.h, the context object and the
 // host-side QuantParam math.
 #include "qconv.cuh"
+#include <algorithm>
 #include <cmath>
 #include <vector>
 
@@ -50,6 +51,37 @@ void make_requant_table(float si, int32_t zi, float so, int32_t zo, float lo, fl
     }
 }
 
+// Unary activations of the reference are evaluated in double and cast back to float
+// (UNARY_TEMPLATE, src/Native/src/kernels/stackvm/reference/kernel_template.h:19-50 with the formulas
+// of reference/activation.cpp:32-38). On a u8 tensor the op is a function of 256 values:
+//   table[q] = quantize((float)f((double)dequantize(q)), out)
+int make_activation_table(int kind, float si, int32_t zi, float so, int32_t zo, uint8_t table[256]) {
+    for (int q = 0; q < 256; q++) {
+        volatile float d = (float)q - (float)zi;
+        volatile float xf = d * si;
+        const double x = (double)xf;
+        double y;
+        switch (kind) {
+        case NNCB_ACT_RELU:
+            y = std::max((double)0, x);
+            break;
+        case NNCB_ACT_SIGMOID:
+            y = 1 / (1 + std::exp(-x));
+            break;
+        case NNCB_ACT_SWISH:
+            y = x / (1 + std::exp(-x));
+            break;
+        case NNCB_ACT_HARD_SWISH:
+            y = x * std::max((double)0.f, std::min((double)1.f, (double)(1.f / 6 * x + 0.5)));
+            break;
+        default:
+            return fail(-EINVAL, "unknown activation kind %d", kind);
+        }
+        table[q] = (uint8_t)host_quant_impl((float)y, so, (float)zo, 0, 255);
+    }
+    return 0;
+}
+
 EpiParams make_epi(const nncb_qconv2d *cv) {
     const nncb_conv2d_desc &d = cv->d;
     EpiParams p;
@@ -80,6 +112,7 @@ int qadd_u8(nncb_context *, const uint8_t *, const uint8_t *, uint8_t *, size_t,
 int lut_u8(nncb_context *, const uint8_t *, uint8_t *, size_t, const uint8_t *);
 int maxpool_u8(nncb_context *, const uint8_t *, uint8_t *, int, int, int, int, int, int, int, int, int, int, int, int, int32_t);
 int global_avgpool_u8(nncb_context *, const uint8_t *, uint8_t *, int, int, int, int, float, int32_t, float, int32_t);
+int softmax_f32(nncb_context *, const float *, float *, size_t, int, float);
 
 size_t paged_attention_scratch_bytes(int B, int Hq, int splits);
 int paged_attention_pick_splits(const nncb_context *ctx, int B, int Hkv, int max_ctx);
@@ -347,6 +380,27 @@ int nncb_requant_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, size_t n, f
     uint8_t table[256];
     make_requant_table(si, zi, so, zo, lo, hi, table);
     return lut_u8(ctx, x, y, n, table);
+}
+int nncb_make_activation_table(int kind, float si, int32_t zi, float so, int32_t zo, uint8_t *table) {
+    if (!table)
+        return fail(-EINVAL, "nncb_make_activation_table: null table");
+    return make_activation_table(kind, si, zi, so, zo, table);
+}
+int nncb_make_requant_table(float si, int32_t zi, float so, int32_t zo, float lo, float hi, uint8_t *table) {
+    if (!table)
+        return fail(-EINVAL, "nncb_make_requant_table: null table");
+    make_requant_table(si, zi, so, zo, lo, hi, table);
+    return 0;
+}
+int nncb_activation_u8(nncb_context *ctx, int kind, const uint8_t *x, uint8_t *y, size_t n, float si, int32_t zi, float so, int32_t zo) {
+    CHECK_CTX(ctx);
+    uint8_t table[256];
+    NNCB_TRY(make_activation_table(kind, si, zi, so, zo, table));
+    return lut_u8(ctx, x, y, n, table);
+}
+int nncb_softmax_f32(nncb_context *ctx, const float *in, float *out, size_t rows, int cols, float beta) {
+    CHECK_CTX(ctx);
+    return softmax_f32(ctx, in, out, rows, cols, beta);
 }
 int nncb_lut_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, size_t n, const uint8_t *host_table) {
     CHECK_CTX(ctx);

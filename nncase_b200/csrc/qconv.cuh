@@ -72,5 +72,6 @@ int tc_conv_run(nncb_context *ctx, nncb_qconv2d *cv, const uint8_t *x, const uin
 int reciprocal_division_selftest(nncb_context *ctx, float scale, unsigned long long count, unsigned long long seed,
                                  unsigned long long *mismatches);
 // y = quantize(clamp(dequantize(x)))) for all 256 inputs, host arithmetic identical to the device's.
+int make_activation_table(int kind, float si, int32_t zi, float so, int32_t zo, uint8_t table[256]);
 void make_requant_table(float si, int32_t zi, float so, int32_t zo, float lo, float hi, uint8_t table[256]);
 } // namespace nncb

@@ -527,4 +527,44 @@ int global_avgpool_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, int n, in
     return after_launch(ctx, "global_avgpool_u8");
 }
 
+// ---- softmax over the last axis (f32) -----------------------------------------------------------
+// reference::softmax (src/Native/src/kernels/stackvm/reference/softmax.cpp:30-80): subtract the
+// row maximum, scale by beta, expf, sum, multiply by 1/sum. One warp per row, shuffle reductions.
+__global__ void __launch_bounds__(256)
+softmax_rows_kernel(const float *__restrict__ in, float *__restrict__ out, size_t rows, int cols, float beta) {
+    const int lane = threadIdx.x & 31;
+    const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
+    for (size_t r = warp; r < rows; r += nwarps) {
+        const float *x = in + r * cols;
+        float *y = out + r * cols;
+        float mx = -INFINITY;
+        for (int j = lane; j < cols; j += 32)
+            mx = fmaxf(mx, x[j]);
+        for (int o = 16; o > 0; o >>= 1)
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        float sum = 0.f;
+        for (int j = lane; j < cols; j += 32) {
+            const float e = expf(__fmul_rn(__fsub_rn(x[j], mx), beta));
+            y[j] = e;
+            sum += e;
+        }
+        for (int o = 16; o > 0; o >>= 1)
+            sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        const float inv = __fdiv_rn(1.0f, sum);
+        for (int j = lane; j < cols; j += 32)
+            y[j] = __fmul_rn(y[j], inv);
+    }
+}
+
+int softmax_f32(nncb_context *ctx, const float *in, float *out, size_t rows, int cols, float beta) {
+    if (rows == 0)
+        return 0;
+    if (!in || !out || cols <= 0)
+        return fail(-EINVAL, "softmax_f32: bad argument");
+    const int grid = stream_grid(ctx, rows * 32, 256);
+    softmax_rows_kernel<<<grid, 256, 0, ctx->stream>>>(in, out, rows, cols, beta);
+    return after_launch(ctx, "softmax_f32");
+}
+
 } // namespace nncb

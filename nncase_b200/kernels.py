@@ -33,6 +33,14 @@ def get_quant_param(rmin, rmax, bits=8, mode=L.UNSIGNED):
     return QuantParam(zp.value, sc.value)
 
 
+def activation_table(kind, qi, qo):
+    """256-entry table of a unary activation between two quant params (host)."""
+    t = np.empty(256, np.uint8)
+    check(L.load().nncb_make_activation_table(kind, qi.scale, qi.zero_point, qo.scale, qo.zero_point,
+                                              t.ctypes.data))
+    return t
+
+
 def fixup_range(rmin, rmax, symmetric=False):
     """QuantUtility.FixupRange (QuantUtility.cs:72-97)."""
     a, b = C.c_float(rmin), C.c_float(rmax)
@@ -167,6 +175,22 @@ class Context:
         y = torch.empty_like(x)
         check(self._lib.nncb_requant_u8(self._h, x.data_ptr(), y.data_ptr(), x.numel(), qi.scale, qi.zero_point,
                                         qo.scale, qo.zero_point, lo, hi))
+        return y
+
+    def activation(self, kind, x, qi, qo):
+        """relu / sigmoid / swish / hard_swish (L.ACT_*) on a u8 tensor between quant params."""
+        x = self._cuda(x, torch.uint8)
+        y = torch.empty_like(x)
+        check(self._lib.nncb_activation_u8(self._h, kind, x.data_ptr(), y.data_ptr(), x.numel(), qi.scale,
+                                           qi.zero_point, qo.scale, qo.zero_point))
+        return y
+
+    def softmax(self, x, beta=1.0):
+        """softmax over the last axis of an f32 tensor."""
+        x = self._cuda(x, torch.float32)
+        y = torch.empty_like(x)
+        cols = x.shape[-1]
+        check(self._lib.nncb_softmax_f32(self._h, x.data_ptr(), y.data_ptr(), x.numel() // cols, cols, beta))
         return y
 
     def lut(self, x, table):

@@ -12,6 +12,7 @@ I8, I16, U8, F16, F32 = 2, 3, 6, 10, 11
 # nncb_quant_mode
 UNSIGNED, SIGNED_SYMMETRIC, SIGNED_ASYMMETRIC = 0, 1, 2
 PATH_AUTO, PATH_SIMT, PATH_TC = 0, 1, 2
+ACT_RELU, ACT_SIGMOID, ACT_SWISH, ACT_HARD_SWISH = 0, 1, 2, 3
 
 
 class NncbError(RuntimeError):
@@ -75,6 +76,10 @@ SIGNATURES = {
     "nncb_nhwc_to_nchw_u8": (_I, [_VP, _VP, _VP, _I, _I, _I, _I]),
     "nncb_qadd_u8": (_I, [_VP, _VP, _VP, _VP, _SZ, _F, _I32, _F, _I32, _F, _I32]),
     "nncb_requant_u8": (_I, [_VP, _VP, _VP, _SZ, _F, _I32, _F, _I32, _F, _F]),
+    "nncb_activation_u8": (_I, [_VP, _I, _VP, _VP, _SZ, _F, _I32, _F, _I32]),
+    "nncb_make_activation_table": (_I, [_I, _F, _I32, _F, _I32, _VP]),
+    "nncb_make_requant_table": (_I, [_F, _I32, _F, _I32, _F, _F, _VP]),
+    "nncb_softmax_f32": (_I, [_VP, _VP, _VP, _SZ, _I, _F]),
     "nncb_lut_u8": (_I, [_VP, _VP, _VP, _SZ, _VP]),
     "nncb_maxpool_u8": (_I, [_VP, _VP, _VP] + [_I] * 12 + [_I32]),
     "nncb_global_avgpool_u8": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _F, _I32, _F, _I32]),

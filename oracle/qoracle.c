@@ -293,6 +293,65 @@ void qo_requant_u8(const uint8_t *x, uint8_t *y, size_t n, float si, int32_t zi,
     }
 }
 
+/* Unary activations between quant params as a 256-entry table:
+ *   table[q] = quantize((float)f((double)dequantize(q)))
+ * f evaluated in double and cast to float like the reference's UNARY_TEMPLATE
+ * (reference/kernel_template.h:19-50) with the formulas of reference/activation.cpp:32-38.
+ * kind: 0 relu, 1 sigmoid, 2 swish, 3 hard_swish. */
+int qo_activation_table(int kind, float si, int32_t zi, float so, int32_t zo, uint8_t *table) {
+    for (int q = 0; q < 256; q++) {
+        float xf = ((float)q - (float)zi) * si;
+        double x = (double)xf, y;
+        switch (kind) {
+        case 0:
+            y = x > 0 ? x : 0;
+            break;
+        case 1:
+            y = 1 / (1 + exp(-x));
+            break;
+        case 2:
+            y = x / (1 + exp(-x));
+            break;
+        case 3: {
+            double t = (double)(1.f / 6 * x + 0.5);
+            t = t < 1.0 ? t : 1.0;
+            t = t > 0.0 ? t : 0.0;
+            y = x * t;
+            break;
+        }
+        default:
+            return -1;
+        }
+        table[q] = (uint8_t)quant1((float)y, so, (float)zo, 0, 255);
+    }
+    return 0;
+}
+
+void qo_lut_u8(const uint8_t *x, uint8_t *y, size_t n, const uint8_t *table) {
+    for (size_t i = 0; i < n; i++)
+        y[i] = table[x[i]];
+}
+
+/* softmax over the last axis, f32 (reference/softmax.cpp:30-80): max, (x - max) * beta, expf,
+ * sequential sum, multiply by 1/sum. */
+void qo_softmax_f32(const float *in, float *out, size_t rows, int cols, float beta) {
+    for (size_t r = 0; r < rows; r++) {
+        const float *x = in + r * cols;
+        float *y = out + r * cols;
+        float mx = x[0];
+        for (int j = 0; j < cols; j++)
+            mx = x[j] > mx ? x[j] : mx;
+        float sum = 0;
+        for (int j = 0; j < cols; j++) {
+            y[j] = expf((x[j] - mx) * beta);
+            sum += y[j];
+        }
+        float inv = 1.0f / sum;
+        for (int j = 0; j < cols; j++)
+            y[j] *= inv;
+    }
+}
+
 /* Max pooling on u8 NHWC with input and output sharing one quant param (max commutes with
  * the monotone dequantize/quantize pair). A window that overlaps the padding also takes the
  * real value 0, i.e. the zero point, into the max: reduce_window2d applies

@@ -160,3 +160,25 @@ def dequantize_nhwc_to_nchw_f32(q, scale, zp):
     lib().qo_dequantize_nhwc_to_nchw_f32(_p(q), _p(y), n, h, w, c, C.c_float(scale),
                                          C.c_int32(zp))
     return y
+
+
+def activation_table(kind, si, zi, so, zo):
+    t = np.empty(256, np.uint8)
+    assert lib().qo_activation_table(kind, C.c_float(si), C.c_int32(zi), C.c_float(so), C.c_int32(zo), _p(t)) == 0
+    return t
+
+
+def lut_u8(x, table):
+    x = np.ascontiguousarray(x, np.uint8)
+    y = np.empty(x.shape, np.uint8)
+    t = np.ascontiguousarray(table, np.uint8)
+    lib().qo_lut_u8(_p(x), _p(y), C.c_size_t(x.size), _p(t))
+    return y
+
+
+def softmax_f32(x, beta=1.0):
+    x = np.ascontiguousarray(x, np.float32)
+    y = np.empty(x.shape, np.float32)
+    cols = x.shape[-1]
+    lib().qo_softmax_f32(_p(x), _p(y), C.c_size_t(x.size // cols), cols, C.c_float(beta))
+    return y

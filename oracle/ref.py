@@ -157,3 +157,11 @@ def qconv2d_composite_u8(xq_nhwc, wq_ohwi, w_zp, w_scale, bias, x_scale, x_zp, o
     yf = conv2d_f32(xf, wf, bias, stride, pad, dilation, groups, clamp)
     yq = quantize_u8(yf, out_scale, out_zp)
     return np.ascontiguousarray(yq.transpose(0, 2, 3, 1))
+
+
+def unary_f32(kind, x):
+    """kind: 0 relu, 1 sigmoid, 2 swish, 3 hard_swish -- the reference's kernels::stackvm functions."""
+    x = np.ascontiguousarray(x, np.float32)
+    y = np.empty(x.shape, np.float32)
+    _chk(lib().nncase_ref_unary_f32(kind, _p(x), _p(y), C.c_size_t(x.size)))
+    return y

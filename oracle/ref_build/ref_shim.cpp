@@ -14,6 +14,8 @@
 #include "opt_ops.h"
 #include "ref_ops.h"
 #include <nncase/runtime/datatypes.h>
+#include <nncase/kernels/stackvm/tensor_ops.h>
+#include <nncase/runtime/runtime_tensor.h>
 #include <nncase/runtime/util.h>
 
 using namespace nncase;
@@ -164,6 +166,29 @@ int nncase_ref_reduce_window2d_f32(int op, const float *in, float init_value, fl
                                    ph, pw, fh, fw, stride_h, stride_w, 1, 1,
                                    value_range<float>::full(), count_include_pad != 0,
                                    default_kernel_context()));
+}
+
+// kernels::stackvm::{relu, sigmoid, swish, hard_swish}(value_t) on a flat f32 tensor
+// (reference/activation.cpp:32-38 through the value_t dispatch of kernel_template.h:52-65).
+// kind: 0 relu, 1 sigmoid, 2 swish, 3 hard_swish.
+int nncase_ref_unary_f32(int kind, const float *in, float *out, size_t n) {
+    using namespace nncase::runtime;
+    auto run = [&]() -> result<void> {
+        try_var(t, hrt::create(dt_float32, dims_t{n}, {(gsl::byte *)in, n * 4}, true, hrt::pool_cpu_only));
+        value_t x = t.impl(), y;
+        switch (kind) {
+        case 0: { try_set(y, nncase::kernels::stackvm::relu(x)); break; }
+        case 1: { try_set(y, nncase::kernels::stackvm::sigmoid(x)); break; }
+        case 2: { try_set(y, nncase::kernels::stackvm::swish(x)); break; }
+        case 3: { try_set(y, nncase::kernels::stackvm::hard_swish(x)); break; }
+        default: return err(std::errc::invalid_argument);
+        }
+        try_var(yt, y.as<tensor>());
+        try_var(src, get_input_data(yt));
+        std::memcpy(out, src, n * 4);
+        return ok();
+    };
+    return rc(run());
 }
 
 int nncase_ref_binary_op_add(void) { return (int)binary_op_t::add; }

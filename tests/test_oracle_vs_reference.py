@@ -155,3 +155,26 @@ def test_space_to_depth_stem_is_the_same_convolution(qo):
     w3, pad3 = space_to_depth_conv(wq3, zw, (1, 1, 1, 1), (h, w), 32)
     got3 = qo.qconv2d_u8(x_s2d, w3, zw, mult, bias, zp, 0.05, 10, (1, 1), pad3)
     assert w3.shape == (oc, 2, 2, 32) and np.array_equal(got3, want3)
+
+
+@pytest.mark.parametrize("kind", [0, 1, 2, 3])
+def test_activation_tables_vs_reference_kernels(qo, ref, kind):
+    """relu / sigmoid / swish / hard_swish tables against the reference's own kernels run on the
+    dequantized values and requantised with the reference's quantize."""
+    si, zi, so, zo = 0.0471, 131, 0.0312, 9
+    q = np.arange(256, dtype=np.uint8)
+    want = ref.quantize_u8(ref.unary_f32(kind, ref.dequantize_u8(q, si, zi)), so, zo)
+    assert np.array_equal(qo.activation_table(kind, si, zi, so, zo), want)
+
+
+def test_library_activation_tables_match_oracle(qo):
+    from nncase_b200 import kernels as K
+    for kind in range(4):
+        for (si, zi, so, zo) in [(0.0471, 131, 0.0312, 9), (0.1, 0, 0.004, 0), (0.02, 255, 0.02, 128)]:
+            t = K.activation_table(kind, K.QuantParam(zi, si), K.QuantParam(zo, so))
+            assert np.array_equal(t, qo.activation_table(kind, si, zi, so, zo))
+
+
+def test_softmax_vs_reference(qo, ref):
+    x = np.random.default_rng(6).normal(0, 3, (37, 1000)).astype(np.float32)
+    assert np.array_equal(qo.softmax_f32(x), ref.softmax_f32(x))

@@ -153,3 +153,21 @@ def test_size_independent_properties_full_size(ctx):
     qs = ctx.quantize(xs, qp)
     assert bool((qs[1:] >= qs[:-1]).all())
     ctx.check_status()
+
+
+@pytest.mark.parametrize("kind", [0, 1, 2, 3])
+def test_activation(ctx, qo, kind):
+    x = np.random.default_rng(20 + kind).integers(0, 256, 100003, dtype=np.uint8)
+    qi, qo_ = QuantParam(131, 0.0471), QuantParam(9, 0.0312)
+    got = ctx.activation(kind, torch.from_numpy(x), qi, qo_).cpu().numpy()
+    assert np.array_equal(got, qo.lut_u8(x, qo.activation_table(kind, 0.0471, 131, 0.0312, 9)))
+
+
+@pytest.mark.parametrize("shape", [(1, 1000), (512, 1000), (7, 33), (3, 1)])
+def test_softmax(ctx, qo, shape):
+    """f32 result within 1e-3 of the output range (the exp and the summation order differ)."""
+    x = np.random.default_rng(30).normal(0, 4, shape).astype(np.float32)
+    got = ctx.softmax(torch.from_numpy(x)).cpu().numpy()
+    want = qo.softmax_f32(x)
+    assert np.abs(got - want).max() <= 1e-3 * max(float(want.max() - want.min()), 1e-6)
+    assert np.allclose(got.sum(-1), 1.0, atol=1e-5)
