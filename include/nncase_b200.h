@@ -174,6 +174,25 @@ NNCB_API int nncb_qconv2d_run(nncb_context *ctx, nncb_qconv2d *conv, const uint8
 /* One-shot with HOST buffers: x u8 NHWC in, y out; weights as in create. */
 NNCB_API int nncb_qconv2d_host(nncb_context *ctx, const nncb_conv2d_desc *desc, const void *weights, const int32_t *w_zp, const float *mult, const float *bias, const uint8_t *lut, const uint8_t *x, const uint8_t *res, void *y, uint8_t *y2);
 
+/* ---- decode-step operators of a transformer with i8 weights and f16 activations -----------
+ * None of these has a reference operator; they extend kernels::stackvm::mat_mul's convention
+ * (f32 accumulation, reference/matmul.cpp:28-51) to weight-only quantization, with f16 storage
+ * between operators. All pointers are device pointers.
+ *   gemv_w8a16:  y[m][n] = f16( (sum_k x[m][k]*w[n][k]) * scale[n] + bias[n] + residual[m][n] )
+ *                x f16 [m<=64][k], w i8 [n][k], scale f16 [n]; bias, residual may be NULL; k % 64 == 0.
+ *   add_rmsnorm: if delta: x <- f16(x + delta) in place;  h = f16(x * rsqrt(mean(x^2) + eps) * weight)
+ *   rope_kv_append: rotary embedding ("rotate half", cos/sin table [max_pos][32] f32) of the q and k
+ *                parts of qkv [batch][(q_heads + 2 kv_heads) * 64]; rotated q to q_out [batch][q_heads][64],
+ *                rotated k and v to page block_table[b][pos/16], slot pos%16 of the pools (the layouts
+ *                nncb_paged_attention_decode reads).
+ *   swiglu:      out[m][j] = f16( silu(gate_up[m][j]) * gate_up[m][inter + j] )
+ *   embedding:   out[m][:] = table[ids[m]][:] */
+NNCB_API int nncb_gemv_w8a16(nncb_context *ctx, const void *x, const int8_t *w, const void *scale, const void *bias, const void *residual, void *y, int m, int n, int k);
+NNCB_API int nncb_add_rmsnorm_f16(nncb_context *ctx, void *x, const void *delta, const void *weight, void *h, int rows, int cols, float eps);
+NNCB_API int nncb_rope_kv_append_f16(nncb_context *ctx, const void *qkv, void *q_out, const float *cos_table, const float *sin_table, const int32_t *positions, const int32_t *block_table, void *k_pool, void *v_pool, int batch, int q_heads, int kv_heads, int head_dim, int page_size, int max_pages);
+NNCB_API int nncb_swiglu_f16(nncb_context *ctx, const void *gate_up, void *out, int rows, int inter);
+NNCB_API int nncb_embedding_f16(nncb_context *ctx, const void *table, const int32_t *ids, void *out, int rows, int cols, int vocab);
+
 /* ---- paged-attention decode ---------------------------------------------------------------
  * The reference has no attention, KV-cache or softmax-over-pages operator (its native op list is
  * src/Native/include/nncase/kernels/stackvm/tensor_ops.h:29-479); this entry point defines one.

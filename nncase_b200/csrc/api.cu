@@ -121,6 +121,12 @@ int paged_attention_launch(nncb_context *ctx, const void *q, const void *k_pool,
                            const int32_t *block_table, const int32_t *ctx_lens, void *out, int B, int Hq, int Hkv,
                            int max_pages, float scale, int splits, void *scratch);
 
+int gemv_w8a16(nncb_context *, const void *, const int8_t *, const void *, const void *, const void *, void *, int, int, int);
+int add_rmsnorm_f16(nncb_context *, void *, const void *, const void *, void *, int, int, float);
+int rope_kv_append_f16(nncb_context *, const void *, void *, const float *, const float *, const int32_t *,
+                       const int32_t *, void *, void *, int, int, int, int, int, int);
+int swiglu_f16(nncb_context *, const void *, void *, int, int);
+int embedding_f16(nncb_context *, const void *, const int32_t *, void *, int, int, int);
 size_t paged_attention_static_capacity();
 int paged_attention_static_scratch(int device, void **ptr);
 
@@ -413,6 +419,42 @@ int nncb_maxpool_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, int n, int 
 int nncb_global_avgpool_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, int n, int h, int w, int c, float si, int32_t zi, float so, int32_t zo) {
     CHECK_CTX(ctx);
     return global_avgpool_u8(ctx, x, y, n, h, w, c, si, zi, so, zo);
+}
+
+// ---- decode-step operators -----------------------------------------------------------------
+int nncb_gemv_w8a16(nncb_context *ctx, const void *x, const int8_t *w, const void *scale, const void *bias,
+                    const void *residual, void *y, int m, int n, int k) {
+    CHECK_CTX(ctx);
+    if (!x || !w || !scale || !y)
+        return fail(-EINVAL, "nncb_gemv_w8a16: null pointer");
+    return gemv_w8a16(ctx, x, w, scale, bias, residual, y, m, n, k);
+}
+int nncb_add_rmsnorm_f16(nncb_context *ctx, void *x, const void *delta, const void *weight, void *h, int rows, int cols, float eps) {
+    CHECK_CTX(ctx);
+    if (!x || !weight || !h)
+        return fail(-EINVAL, "nncb_add_rmsnorm_f16: null pointer");
+    return add_rmsnorm_f16(ctx, x, delta, weight, h, rows, cols, eps);
+}
+int nncb_rope_kv_append_f16(nncb_context *ctx, const void *qkv, void *q_out, const float *cos_table, const float *sin_table,
+                            const int32_t *positions, const int32_t *block_table, void *k_pool, void *v_pool, int batch,
+                            int q_heads, int kv_heads, int head_dim, int page_size, int max_pages) {
+    CHECK_CTX(ctx);
+    if (!qkv || !q_out || !cos_table || !sin_table || !positions || !block_table || !k_pool || !v_pool)
+        return fail(-EINVAL, "nncb_rope_kv_append_f16: null pointer");
+    return rope_kv_append_f16(ctx, qkv, q_out, cos_table, sin_table, positions, block_table, k_pool, v_pool, batch, q_heads,
+                              kv_heads, head_dim, page_size, max_pages);
+}
+int nncb_swiglu_f16(nncb_context *ctx, const void *gate_up, void *out, int rows, int inter) {
+    CHECK_CTX(ctx);
+    if (!gate_up || !out)
+        return fail(-EINVAL, "nncb_swiglu_f16: null pointer");
+    return swiglu_f16(ctx, gate_up, out, rows, inter);
+}
+int nncb_embedding_f16(nncb_context *ctx, const void *table, const int32_t *ids, void *out, int rows, int cols, int vocab) {
+    CHECK_CTX(ctx);
+    if (!table || !ids || !out)
+        return fail(-EINVAL, "nncb_embedding_f16: null pointer");
+    return embedding_f16(ctx, table, ids, out, rows, cols, vocab);
 }
 
 // ---- paged attention -----------------------------------------------------------------------

@@ -1,0 +1,252 @@
+// Decode-step kernels of a Qwen2-shaped transformer with i8 weights and f16 activations:
+// small-M weight-only-quantized MatMul, RMSNorm (optionally fused with the residual add), rotary
+// embedding + KV-page append, SwiGLU, embedding gather. The reference has none of these
+// operators (its op list is src/Native/include/nncase/kernels/stackvm/tensor_ops.h:29-479);
+// arithmetic follows its mat_mul convention (f32 accumulation, reference/matmul.cpp:28-51) with
+// f16 storage between operators.
+//
+// At batch 64 every one of these is tiny next to the KV-cache read of the attention kernel: a
+// layer's weights are 15 MB (2.3 us of HBM time), so the design goal here is few, simple,
+// latency-tolerant launches that capture into one CUDA graph, not peak tensor throughput.
+#include "internal.cuh"
+#include <cuda_fp16.h>
+
+namespace nncb {
+
+// ---- y[m][n] = (sum_k x[m][k] * w[n][k]) * scale[n] (+ bias[n]) (+ residual[m][n]) ---------------
+// x f16 [M<=64][K], w i8 [N][K] (per-output-channel symmetric), scale f16 [N], y f16 [M][N].
+// One CTA per 16 output channels; its 8 warps split K in chunks of 64 and reduce through shared
+// memory. Tensor-core math: mma.sync m16n8k16 f16 with the weights as A (converted i8 -> f16 in
+// registers) and x^T as B. Inside a 64-wide K chunk the k index is permuted (lane t of a row owns
+// bytes 16t..16t+15) so that every lane fetches its weights with one 16-byte load per row and its
+// activations with 8-byte loads; a dot product does not care about the order of k.
+constexpr int GEMV_WARPS = 8;
+
+__device__ __forceinline__ void mma16816_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                             uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+                 "{%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// two signed bytes (byte 2i, 2i+1 of w, i = 0 or 1) -> half2, exactly
+__device__ __forceinline__ uint32_t i8x2_to_half2(uint32_t w, int pair) {
+    // (b ^ 0x80) | 0x6400 is the half 1024 + (b + 128); subtracting 1152 gives b
+    const uint32_t sel = pair == 0 ? 0x4140u : 0x4342u; // bytes {b0, 0x64, b1, 0x64} / {b2, 0x64, b3, 0x64}
+    const uint32_t h = __byte_perm(w ^ 0x80808080u, 0x64646464u, sel);
+    const __half2 v = __hsub2(*reinterpret_cast<const __half2 *>(&h), __half2half2(__ushort_as_half(0x6480)));
+    return *reinterpret_cast<const uint32_t *>(&v);
+}
+
+template <int MT> // token tiles of 8
+__global__ void __launch_bounds__(GEMV_WARPS * 32)
+gemv_w8a16_kernel(const __half *__restrict__ x, const int8_t *__restrict__ w, const __half *__restrict__ scale,
+                  const __half *__restrict__ bias, const __half *__restrict__ residual, __half *__restrict__ y, int M,
+                  int N, int K) {
+    __shared__ float red[GEMV_WARPS][16][MT * 8 + 1];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int n0 = blockIdx.x * 16;
+    float acc[MT][4];
+#pragma unroll
+    for (int i = 0; i < MT; i++)
+        acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    const int r0 = min(n0 + g, N - 1), r1 = min(n0 + g + 8, N - 1); // clamped rows of a partial last block
+    const int chunks = K / 64;
+    for (int ch = warp; ch < chunks; ch += GEMV_WARPS) {
+        const int k0 = ch * 64 + 16 * t;
+        const uint4 wa = __ldg(reinterpret_cast<const uint4 *>(w + (size_t)r0 * K + k0));
+        const uint4 wb = __ldg(reinterpret_cast<const uint4 *>(w + (size_t)r1 * K + k0));
+        const uint32_t wav[4] = {wa.x, wa.y, wa.z, wa.w}, wbv[4] = {wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const uint32_t a0 = i8x2_to_half2(wav[j], 0), a2 = i8x2_to_half2(wav[j], 1);
+            const uint32_t a1 = i8x2_to_half2(wbv[j], 0), a3 = i8x2_to_half2(wbv[j], 1);
+#pragma unroll
+            for (int i = 0; i < MT; i++) {
+                const int tok = min(8 * i + g, M - 1);
+                const uint2 b = __ldg(reinterpret_cast<const uint2 *>(x + (size_t)tok * K + k0 + 4 * j));
+                mma16816_f16(acc[i], a0, a1, a2, a3, b.x, b.y);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < MT; i++) {
+        red[warp][g][8 * i + 2 * t] = acc[i][0];
+        red[warp][g][8 * i + 2 * t + 1] = acc[i][1];
+        red[warp][g + 8][8 * i + 2 * t] = acc[i][2];
+        red[warp][g + 8][8 * i + 2 * t + 1] = acc[i][3];
+    }
+    __syncthreads();
+    // 256 threads: thread -> (token, 16 channels as 4 groups of 4)
+    for (int idx = threadIdx.x; idx < MT * 8 * 16; idx += GEMV_WARPS * 32) {
+        const int tok = idx / 16, r = idx % 16;
+        const int n = n0 + r;
+        if (tok >= M || n >= N)
+            continue;
+        float s = 0.f;
+#pragma unroll
+        for (int wv = 0; wv < GEMV_WARPS; wv++)
+            s += red[wv][r][tok];
+        float v = s * __half2float(scale[n]);
+        if (bias)
+            v += __half2float(bias[n]);
+        if (residual)
+            v += __half2float(residual[(size_t)tok * N + n]);
+        y[(size_t)tok * N + n] = __float2half_rn(v);
+    }
+}
+
+int gemv_w8a16(nncb_context *ctx, const void *x, const int8_t *w, const void *scale, const void *bias,
+               const void *residual, void *y, int M, int N, int K) {
+    if (M <= 0 || N <= 0 || K <= 0)
+        return fail(-EINVAL, "gemv_w8a16: non-positive dimension");
+    if (M > 64)
+        return fail(-ENOSYS, "gemv_w8a16: built for at most 64 rows of activations (decode batches)");
+    if (K % 64 != 0)
+        return fail(-ENOSYS, "gemv_w8a16: K must be a multiple of 64");
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15)
+        return fail(-EINVAL, "gemv_w8a16: x and w must be 16-byte aligned");
+    const int grid = (N + 15) / 16;
+    const __half *xs = (const __half *)x, *sc = (const __half *)scale, *bi = (const __half *)bias,
+                 *re = (const __half *)residual;
+    __half *ys = (__half *)y;
+    const int mt = (M + 7) / 8;
+    switch (mt) {
+    case 1: gemv_w8a16_kernel<1><<<grid, GEMV_WARPS * 32, 0, ctx->stream>>>(xs, w, sc, bi, re, ys, M, N, K); break;
+    case 2: gemv_w8a16_kernel<2><<<grid, GEMV_WARPS * 32, 0, ctx->stream>>>(xs, w, sc, bi, re, ys, M, N, K); break;
+    case 3:
+    case 4: gemv_w8a16_kernel<4><<<grid, GEMV_WARPS * 32, 0, ctx->stream>>>(xs, w, sc, bi, re, ys, M, N, K); break;
+    default: gemv_w8a16_kernel<8><<<grid, GEMV_WARPS * 32, 0, ctx->stream>>>(xs, w, sc, bi, re, ys, M, N, K); break;
+    }
+    return after_launch(ctx, "gemv_w8a16");
+}
+
+// ---- RMSNorm, optionally fused with the residual add ---------------------------------------------
+//   if delta: x <- f16(x + delta)  (written back);  h = f16( x * rsqrt(mean(x^2) + eps) * w )
+// one CTA of 128 threads per row; f32 statistics.
+__global__ void __launch_bounds__(128)
+add_rmsnorm_kernel(__half *__restrict__ x, const __half *__restrict__ delta, const __half *__restrict__ w,
+                   __half *__restrict__ h, int cols, float eps) {
+    __shared__ float part[4];
+    const size_t row = blockIdx.x;
+    __half *xr = x + row * cols;
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < cols; j += 128) {
+        float v = __half2float(xr[j]);
+        if (delta) {
+            v = __half2float(__float2half_rn(v + __half2float(delta[row * cols + j])));
+            xr[j] = __float2half_rn(v);
+        }
+        ss += v * v;
+    }
+    for (int o = 16; o > 0; o >>= 1)
+        ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0)
+        part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    const float tot = part[0] + part[1] + part[2] + part[3];
+    const float inv = rsqrtf(tot / (float)cols + eps);
+    for (int j = threadIdx.x; j < cols; j += 128)
+        h[row * cols + j] = __float2half_rn(__half2float(xr[j]) * inv * __half2float(w[j]));
+}
+
+int add_rmsnorm_f16(nncb_context *ctx, void *x, const void *delta, const void *w, void *h, int rows, int cols, float eps) {
+    if (rows <= 0 || cols <= 0)
+        return fail(-EINVAL, "rmsnorm: non-positive dimension");
+    add_rmsnorm_kernel<<<rows, 128, 0, ctx->stream>>>((__half *)x, (const __half *)delta, (const __half *)w, (__half *)h,
+                                                       cols, eps);
+    return after_launch(ctx, "add_rmsnorm");
+}
+
+// ---- rotary embedding of q and k, and append of k, v to the paged cache --------------------------
+// qkv [B][(Hq + 2 Hkv) * 64] f16 (q heads, then k heads, then v heads). Rotation pairs dimension i
+// with i + 32 ("rotate half"): out[i] = x[i] cos - x[i+32] sin, out[i+32] = x[i+32] cos + x[i] sin,
+// cos/sin from a host table [max_pos][32] f32. Rotated q goes to q_out [B][Hq][64] (dense, the layout
+// the attention kernel reads); k (rotated) and v go to page block_table[b][pos / 16], slot pos % 16.
+__global__ void __launch_bounds__(64)
+rope_kv_append_kernel(const __half *__restrict__ qkv, __half *__restrict__ q_out, const float *__restrict__ cos_t,
+                      const float *__restrict__ sin_t,
+                      const int *__restrict__ positions, const int *__restrict__ block_table, __half *__restrict__ k_pool,
+                      __half *__restrict__ v_pool, int Hq, int Hkv, int max_pages) {
+    const int b = blockIdx.y, head = blockIdx.x; // heads 0..Hq-1: q; Hq..Hq+Hkv-1: k; then v
+    const int d = threadIdx.x;                   // 0..63
+    const int pos = positions[b];
+    const __half *row = qkv + (size_t)b * (Hq + 2 * Hkv) * 64 + (size_t)head * 64;
+    const bool is_v = head >= Hq + Hkv;
+    float out;
+    const float xv = __half2float(row[d]);
+    if (is_v) {
+        out = xv;
+    } else {
+        const int i = d & 31;
+        const float c = cos_t[(size_t)pos * 32 + i], s = sin_t[(size_t)pos * 32 + i];
+        const float other = __half2float(row[d < 32 ? d + 32 : d - 32]);
+        out = d < 32 ? xv * c - other * s : xv * c + other * s;
+    }
+    const __half ho = __float2half_rn(out);
+    if (head < Hq) {
+        q_out[((size_t)b * Hq + head) * 64 + d] = ho;
+    } else {
+        const int kvh = is_v ? head - Hq - Hkv : head - Hq;
+        const int page = block_table[(size_t)b * max_pages + pos / 16];
+        __half *dst = (is_v ? v_pool : k_pool) + (((size_t)page * Hkv + kvh) * 16 + (pos % 16)) * 64;
+        dst[d] = ho;
+    }
+}
+
+int rope_kv_append_f16(nncb_context *ctx, const void *qkv, void *q_out, const float *cos_t, const float *sin_t, const int32_t *positions,
+                       const int32_t *block_table, void *k_pool, void *v_pool, int B, int Hq, int Hkv, int head_dim,
+                       int page_size, int max_pages) {
+    if (B <= 0 || Hq <= 0 || Hkv <= 0 || max_pages <= 0)
+        return fail(-EINVAL, "rope_kv_append: non-positive dimension");
+    if (head_dim != 64 || page_size != 16)
+        return fail(-ENOSYS, "rope_kv_append: only head_dim 64 and 16-token pages are built");
+    dim3 grid(Hq + 2 * Hkv, B);
+    rope_kv_append_kernel<<<grid, 64, 0, ctx->stream>>>((const __half *)qkv, (__half *)q_out, cos_t, sin_t, positions, block_table,
+                                                       (__half *)k_pool, (__half *)v_pool, Hq, Hkv, max_pages);
+    return after_launch(ctx, "rope_kv_append");
+}
+
+// ---- SwiGLU: out[m][j] = silu(gu[m][j]) * gu[m][inter + j], f32 math -------------------------------
+__global__ void __launch_bounds__(256)
+swiglu_kernel(const __half *__restrict__ gu, __half *__restrict__ out, size_t rows, int inter) {
+    const size_t total = rows * inter;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / inter, j = i % inter;
+        const float g = __half2float(gu[r * 2 * inter + j]), u = __half2float(gu[r * 2 * inter + inter + j]);
+        out[i] = __float2half_rn(g / (1.0f + expf(-g)) * u);
+    }
+}
+
+int swiglu_f16(nncb_context *ctx, const void *gu, void *out, int rows, int inter) {
+    if (rows <= 0 || inter <= 0)
+        return fail(-EINVAL, "swiglu: non-positive dimension");
+    const size_t total = (size_t)rows * inter;
+    int grid = (int)((total + 255) / 256);
+    if (grid > ctx->sm_count * 8)
+        grid = ctx->sm_count * 8;
+    swiglu_kernel<<<grid, 256, 0, ctx->stream>>>((const __half *)gu, (__half *)out, (size_t)rows, inter);
+    return after_launch(ctx, "swiglu");
+}
+
+// ---- embedding gather: out[m][:] = table[ids[m]][:] -----------------------------------------------
+__global__ void __launch_bounds__(128)
+embedding_kernel(const __half *__restrict__ table, const int *__restrict__ ids, __half *__restrict__ out, int cols,
+                 int vocab) {
+    const int id = min(max(ids[blockIdx.x], 0), vocab - 1);
+    const uint32_t *src = reinterpret_cast<const uint32_t *>(table + (size_t)id * cols);
+    uint32_t *dst = reinterpret_cast<uint32_t *>(out + (size_t)blockIdx.x * cols);
+    for (int j = threadIdx.x; j < cols / 2; j += 128)
+        dst[j] = src[j];
+}
+
+int embedding_f16(nncb_context *ctx, const void *table, const int32_t *ids, void *out, int rows, int cols, int vocab) {
+    if (rows <= 0 || cols <= 0 || vocab <= 0 || (cols & 1))
+        return fail(-EINVAL, "embedding: bad dimension");
+    embedding_kernel<<<rows, 128, 0, ctx->stream>>>((const __half *)table, ids, (__half *)out, cols, vocab);
+    return after_launch(ctx, "embedding");
+}
+
+} // namespace nncb

@@ -1,0 +1,189 @@
+"""Decode step of a Qwen2-shaped transformer on the `cuda` module's kernels.
+
+i8 weights (per output channel, symmetric, f16 scales), f16 activations, paged f16 KV cache with
+16-token pages. One call = one new token for every sequence of the batch. Tensor parallel over the
+GPUs of one node: qkv / gate-up projections split by output channel (whole heads), o / down
+projections split by input channel, so each rank produces a partial [batch, hidden] sum that is
+all-reduced with NCCL (torch.distributed) after the attention-output and the down projection; KV
+pages are rank-local. The reference has no transformer operators and no multi-device runtime; the
+operator semantics are those of include/nncase_b200.h.
+"""
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from . import lib as L
+from .kernels import Context, NncbError, check
+
+
+@dataclass(frozen=True)
+class DecoderConfig:
+    layers: int = 24
+    hidden: int = 896
+    q_heads: int = 14
+    kv_heads: int = 2
+    head_dim: int = 64
+    inter: int = 4864
+    vocab: int = 151936
+    eps: float = 1e-6
+    rope_theta: float = 1e6
+    max_pos: int = 4096
+    page: int = 16
+
+
+def quantize_per_channel_i8(w):
+    """[N, K] f32 -> (i8 [N, K], f16 scales [N]): symmetric, scale = max|w| / 127 rounded to f16."""
+    amax = np.abs(w).max(axis=1)
+    scale = np.maximum(amax / 127.0, 1e-8).astype(np.float16)
+    q = np.clip(np.rint(w / scale.astype(np.float32)[:, None]), -127, 127).astype(np.int8)
+    return q, scale
+
+
+def make_weights(cfg, seed=1005):
+    """Seeded N(0, 0.02) weights of the given shape, quantized; norm weights 1 + N(0, 0.02)."""
+    rng = np.random.default_rng(seed)
+    H, D = cfg.hidden, cfg.head_dim
+    nq, nkv = cfg.q_heads * D, cfg.kv_heads * D
+
+    def lin(n, k):
+        return quantize_per_channel_i8(rng.normal(0, 0.02, (n, k)).astype(np.float32))
+
+    layers = []
+    for _ in range(cfg.layers):
+        layers.append(dict(
+            ln1=(1 + rng.normal(0, 0.02, H)).astype(np.float16), ln2=(1 + rng.normal(0, 0.02, H)).astype(np.float16),
+            qkv=lin(nq + 2 * nkv, H), qkv_bias=rng.normal(0, 0.02, nq + 2 * nkv).astype(np.float16),
+            o=lin(H, nq), gate_up=lin(2 * cfg.inter, H), down=lin(H, cfg.inter)))
+    return dict(embed=rng.normal(0, 0.02, (cfg.vocab, H)).astype(np.float16), layers=layers,
+                ln_f=(1 + rng.normal(0, 0.02, H)).astype(np.float16), lm_head=lin(cfg.vocab, H))
+
+
+def rope_tables(cfg):
+    """cos/sin [max_pos][head_dim/2] f32, angles computed in double."""
+    half = cfg.head_dim // 2
+    inv = cfg.rope_theta ** (-np.arange(half, dtype=np.float64) * 2.0 / cfg.head_dim)
+    ang = np.arange(cfg.max_pos, dtype=np.float64)[:, None] * inv[None, :]
+    return np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+
+
+def shard_weights(cfg, w, world, rank):
+    """The slice of every projection that tensor-parallel rank `rank` of `world` owns."""
+    if world == 1:
+        return w
+    if cfg.q_heads % world or cfg.kv_heads % world or cfg.inter % (world * 64) or cfg.vocab % world:
+        raise NncbError(-38, f"tensor parallel degree {world} does not divide the heads / widths of this shape")
+    D = cfg.head_dim
+    hq, hkv = cfg.q_heads // world, cfg.kv_heads // world
+    nq, nkv = cfg.q_heads * D, cfg.kv_heads * D
+    qs = slice(rank * hq * D, (rank + 1) * hq * D)
+    ks = slice(nq + rank * hkv * D, nq + (rank + 1) * hkv * D)
+    vs = slice(nq + nkv + rank * hkv * D, nq + nkv + (rank + 1) * hkv * D)
+    ii = cfg.inter // world
+    gs = slice(rank * ii, (rank + 1) * ii)
+    us = slice(cfg.inter + rank * ii, cfg.inter + (rank + 1) * ii)
+    vv = cfg.vocab // world
+
+    def rows(t, *sl):
+        return np.concatenate([t[0][s] for s in sl]), np.concatenate([t[1][s] for s in sl])
+
+    def cols(t, s):
+        return np.ascontiguousarray(t[0][:, s]), t[1]
+
+    layers = []
+    for lw in w["layers"]:
+        layers.append(dict(ln1=lw["ln1"], ln2=lw["ln2"], qkv=rows(lw["qkv"], qs, ks, vs),
+                           qkv_bias=np.concatenate([lw["qkv_bias"][s] for s in (qs, ks, vs)]),
+                           o=cols(lw["o"], qs), gate_up=rows(lw["gate_up"], gs, us), down=cols(lw["down"], gs)))
+    return dict(embed=w["embed"], layers=layers, ln_f=w["ln_f"],
+                lm_head=rows(w["lm_head"], slice(rank * vv, (rank + 1) * vv)))
+
+
+class Decoder:
+    """One tensor-parallel rank of the decoder (world 1 = the whole model)."""
+
+    def __init__(self, cfg, weights, max_batch, num_pages, ctx=None, device=0, world=1, rank=0, group=None):
+        self.cfg, self.world, self.rank, self.group = cfg, world, rank, group
+        self.ctx = ctx or Context(device)
+        dev = self.ctx.device
+        w = shard_weights(cfg, weights, world, rank)
+        t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+        self.embed, self.ln_f = t(w["embed"]), t(w["ln_f"])
+        self.lm_w, self.lm_s = t(w["lm_head"][0]), t(w["lm_head"][1])
+        self.layers = []
+        self.hq, self.hkv = cfg.q_heads // world, cfg.kv_heads // world
+        self.inter = cfg.inter // world
+        for lw in w["layers"]:
+            self.layers.append(dict(
+                ln1=t(lw["ln1"]), ln2=t(lw["ln2"]), qkv_w=t(lw["qkv"][0]), qkv_s=t(lw["qkv"][1]), qkv_b=t(lw["qkv_bias"]),
+                o_w=t(lw["o"][0]), o_s=t(lw["o"][1]), gu_w=t(lw["gate_up"][0]), gu_s=t(lw["gate_up"][1]),
+                d_w=t(lw["down"][0]), d_s=t(lw["down"][1]),
+                k_pool=torch.zeros((num_pages, self.hkv, cfg.page, cfg.head_dim), dtype=torch.float16, device=dev),
+                v_pool=torch.zeros((num_pages, self.hkv, cfg.page, cfg.head_dim), dtype=torch.float16, device=dev)))
+        cos, sin = rope_tables(cfg)
+        self.cos, self.sin = t(cos), t(sin)
+        B, H, D = max_batch, cfg.hidden, cfg.head_dim
+        f16 = dict(dtype=torch.float16, device=dev)
+        self.x, self.h = torch.empty((B, H), **f16), torch.empty((B, H), **f16)
+        self.qkv = torch.empty((B, (self.hq + 2 * self.hkv) * D), **f16)
+        self.q = torch.empty((B, self.hq * D), **f16)
+        self.attn = torch.empty((B, self.hq * D), **f16)
+        self.proj = torch.empty((B, H), **f16)
+        self.gu = torch.empty((B, 2 * self.inter), **f16)
+        self.act = torch.empty((B, self.inter), **f16)
+        self.logits = torch.empty((B, cfg.vocab // world), **f16)
+        self.ws = torch.empty(4 << 20, dtype=torch.uint8, device=dev)
+        self.max_batch = B
+
+    # thin wrappers over the C ABI (device pointers of preallocated tensors)
+    def _gemv(self, x, w, s, b, y):
+        lib, h = self.ctx._lib, self.ctx._h
+        check(lib.nncb_gemv_w8a16(h, x.data_ptr(), w.data_ptr(), s.data_ptr(), b.data_ptr() if b is not None else None,
+                                  None, y.data_ptr(), x.shape[0], w.shape[0], w.shape[1]))
+
+    def _norm(self, x, delta, w, out):
+        check(self.ctx._lib.nncb_add_rmsnorm_f16(self.ctx._h, x.data_ptr(), delta.data_ptr() if delta is not None else None,
+                                                 w.data_ptr(), out.data_ptr(), x.shape[0], x.shape[1], self.cfg.eps))
+
+    def _all_reduce(self, t):
+        if self.world > 1:
+            dist.all_reduce(t, group=self.group)
+
+    def step(self, token_ids, positions, block_table):
+        """token_ids, positions [B] int32 (position = number of tokens already cached), block_table
+        [B, max_pages] int32 (device tensors). Appends this token's K/V and returns this rank's slice of
+        the logits [B, vocab / world] f16."""
+        cfg, lib, h = self.cfg, self.ctx._lib, self.ctx._h
+        B = token_ids.shape[0]
+        if B > self.max_batch:
+            raise NncbError(-22, "batch larger than planned")
+        x, hh, qkv, q, attn, proj, gu, act = (self.x[:B], self.h[:B], self.qkv[:B], self.q[:B], self.attn[:B],
+                                              self.proj[:B], self.gu[:B], self.act[:B])
+        ctx_lens = positions + 1
+        check(lib.nncb_embedding_f16(h, self.embed.data_ptr(), token_ids.data_ptr(), x.data_ptr(), B, cfg.hidden, cfg.vocab))
+        delta = None
+        for lw in self.layers:
+            self._norm(x, delta, lw["ln1"], hh)
+            self._gemv(hh, lw["qkv_w"], lw["qkv_s"], lw["qkv_b"], qkv)
+            check(lib.nncb_rope_kv_append_f16(h, qkv.data_ptr(), q.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(),
+                                              positions.data_ptr(), block_table.data_ptr(), lw["k_pool"].data_ptr(),
+                                              lw["v_pool"].data_ptr(), B, self.hq, self.hkv, cfg.head_dim, cfg.page,
+                                              block_table.shape[1]))
+            check(lib.nncb_paged_attention_decode(h, q.data_ptr(), lw["k_pool"].data_ptr(), lw["v_pool"].data_ptr(),
+                                                  block_table.data_ptr(), ctx_lens.data_ptr(), attn.data_ptr(), B,
+                                                  self.hq, self.hkv, cfg.head_dim, cfg.page, block_table.shape[1],
+                                                  C.c_float(1.0 / np.sqrt(cfg.head_dim)), self.ws.data_ptr(),
+                                                  self.ws.numel()))
+            self._gemv(attn, lw["o_w"], lw["o_s"], None, proj)
+            self._all_reduce(proj)
+            self._norm(x, proj, lw["ln2"], hh)
+            self._gemv(hh, lw["gu_w"], lw["gu_s"], None, gu)
+            check(lib.nncb_swiglu_f16(h, gu.data_ptr(), act.data_ptr(), B, self.inter))
+            self._gemv(act, lw["d_w"], lw["d_s"], None, proj)
+            self._all_reduce(proj)
+            delta = proj
+        self._norm(x, delta, self.ln_f, hh)
+        self._gemv(hh, self.lm_w, self.lm_s, None, self.logits[:B])
+        return self.logits[:B]

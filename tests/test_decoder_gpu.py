@@ -1,0 +1,116 @@
+"""Decode-step operators and the whole decode step against the numpy restatement (f16 storage, f32
+math; tolerance relative to each output's range)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from nncase_b200 import decoder as D
+from nncase_b200 import lib as L
+from oracle import decoder as OD
+
+pytestmark = pytest.mark.gpu
+
+
+def close(got, want, tol=1e-3):
+    got, want = np.asarray(got, np.float32), np.asarray(want, np.float32)
+    rng = max(float(want.max() - want.min()), 1e-6)
+    err = float(np.abs(got - want).max())
+    assert err <= tol * rng, f"max abs err {err} vs range {rng}"
+
+
+@pytest.mark.parametrize("m,n,k", [(64, 1152, 896), (64, 896, 4864), (5, 1000, 128), (1, 16, 64), (33, 9728, 896)])
+def test_gemv_w8a16(ctx, m, n, k):
+    rng = np.random.default_rng(m + n)
+    x = rng.normal(0, 1, (m, k)).astype(np.float16)
+    wq, s = D.quantize_per_channel_i8(rng.normal(0, 0.02, (n, k)).astype(np.float32))
+    bias = rng.normal(0, 0.1, n).astype(np.float16)
+    res = rng.normal(0, 1, (m, n)).astype(np.float16)
+    t = lambda a: torch.from_numpy(a).cuda()
+    xd, wd, sd, bd, rd = t(x), t(wq), t(s), t(bias), t(res)
+    y = torch.empty((m, n), dtype=torch.float16, device="cuda")
+    L.check(ctx._lib.nncb_gemv_w8a16(ctx._h, xd.data_ptr(), wd.data_ptr(), sd.data_ptr(), bd.data_ptr(), rd.data_ptr(),
+                                     y.data_ptr(), m, n, k))
+    close(y.cpu().numpy(), OD.gemv_w8a16(x, wq, s, bias, res))
+    L.check(ctx._lib.nncb_gemv_w8a16(ctx._h, xd.data_ptr(), wd.data_ptr(), sd.data_ptr(), None, None, y.data_ptr(), m, n, k))
+    close(y.cpu().numpy(), OD.gemv_w8a16(x, wq, s))
+
+
+def test_gemv_rejects_unsupported(ctx):
+    z = torch.zeros(1 << 16, dtype=torch.float16, device="cuda")
+    w = torch.zeros(1 << 16, dtype=torch.int8, device="cuda")
+    assert ctx._lib.nncb_gemv_w8a16(ctx._h, z.data_ptr(), w.data_ptr(), z.data_ptr(), None, None, z.data_ptr(), 65, 16, 64) == -38
+    assert ctx._lib.nncb_gemv_w8a16(ctx._h, z.data_ptr(), w.data_ptr(), z.data_ptr(), None, None, z.data_ptr(), 4, 16, 70) == -38
+
+
+def test_add_rmsnorm_swiglu_embedding(ctx):
+    rng = np.random.default_rng(9)
+    x = rng.normal(0, 1, (7, 896)).astype(np.float16)
+    dl = rng.normal(0, 1, (7, 896)).astype(np.float16)
+    w = (1 + rng.normal(0, 0.02, 896)).astype(np.float16)
+    xd, dd, wd = torch.from_numpy(x).cuda(), torch.from_numpy(dl).cuda(), torch.from_numpy(w).cuda()
+    h = torch.empty_like(xd)
+    L.check(ctx._lib.nncb_add_rmsnorm_f16(ctx._h, xd.data_ptr(), dd.data_ptr(), wd.data_ptr(), h.data_ptr(), 7, 896, 1e-6))
+    xn, hn = OD.add_rmsnorm(x, dl, w, 1e-6)
+    assert np.array_equal(xd.cpu().numpy(), xn)  # the residual add itself is exact in f16
+    close(h.cpu().numpy(), hn)
+    gu = rng.normal(0, 2, (7, 2 * 608)).astype(np.float16)
+    gd = torch.from_numpy(gu).cuda()
+    out = torch.empty((7, 608), dtype=torch.float16, device="cuda")
+    L.check(ctx._lib.nncb_swiglu_f16(ctx._h, gd.data_ptr(), out.data_ptr(), 7, 608))
+    close(out.cpu().numpy(), OD.swiglu(gu, 608))
+    table = rng.normal(0, 1, (50, 896)).astype(np.float16)
+    ids = np.array([3, 49, 0, 17], np.int32)
+    td, idd = torch.from_numpy(table).cuda(), torch.from_numpy(ids).cuda()
+    e = torch.empty((4, 896), dtype=torch.float16, device="cuda")
+    L.check(ctx._lib.nncb_embedding_f16(ctx._h, td.data_ptr(), idd.data_ptr(), e.data_ptr(), 4, 896, 50))
+    assert np.array_equal(e.cpu().numpy(), table[ids])
+
+
+def _run_steps(ctx, cfg, weights, B, start_lens, steps, seed):
+    """Prefill the caches with random K/V, then decode `steps` tokens on both sides."""
+    rng = np.random.default_rng(seed)
+    max_pages = (max(start_lens) + steps + cfg.page - 1) // cfg.page
+    num_pages = B * max_pages + 2
+    table = rng.permutation(num_pages)[: B * max_pages].astype(np.int32).reshape(B, max_pages)
+    cos, sin = D.rope_tables(cfg)
+    ref = OD.Decoder(cfg, weights, cos, sin, num_pages)
+    dec = D.Decoder(cfg, weights, B, num_pages, ctx=ctx)
+    for li in range(cfg.layers):
+        k = rng.normal(0, 1, ref.k_pools[li].shape).astype(np.float16)
+        v = rng.normal(0, 1, ref.v_pools[li].shape).astype(np.float16)
+        ref.k_pools[li][...], ref.v_pools[li][...] = k, v
+        dec.layers[li]["k_pool"].copy_(torch.from_numpy(k))
+        dec.layers[li]["v_pool"].copy_(torch.from_numpy(v))
+    pos = np.asarray(start_lens, np.int32)
+    td = torch.from_numpy(table).cuda()
+    outs = []
+    for s in range(steps):
+        ids = rng.integers(0, cfg.vocab, B).astype(np.int32)
+        want = ref.step(ids, pos, table)
+        got = dec.step(torch.from_numpy(ids).cuda(), torch.from_numpy(pos).cuda(), td)
+        ctx.check_status()
+        outs.append((got.cpu().numpy(), want))
+        pos = pos + 1
+    return outs, dec, ref
+
+
+def test_decode_steps_small_model(ctx):
+    cfg = D.DecoderConfig(layers=3, hidden=256, q_heads=4, kv_heads=2, inter=512, vocab=1000, max_pos=256)
+    weights = D.make_weights(cfg, 7)
+    outs, dec, ref = _run_steps(ctx, cfg, weights, 5, [0, 1, 15, 16, 40], 3, 1)
+    for got, want in outs:
+        close(got, want, 5e-3)
+    # the appended K/V pages agree bit for bit up to f16 rounding of the rope
+    for li in range(cfg.layers):
+        close(dec.layers[li]["k_pool"].cpu().numpy(), ref.k_pools[li], 2e-3)
+
+
+def test_decode_step_qwen2_shape_two_layers(ctx):
+    """Full widths of the Qwen2-0.5B shape (hidden 896, 14/2 heads, inter 4864), two layers, a small
+    vocabulary, batch 64."""
+    cfg = D.DecoderConfig(layers=2, vocab=2048, max_pos=512)
+    weights = D.make_weights(cfg, 8)
+    outs, _, _ = _run_steps(ctx, cfg, weights, 64, list(np.random.default_rng(2).integers(1, 300, 64)), 1, 2)
+    close(outs[0][0], outs[0][1], 5e-3)
