@@ -443,6 +443,91 @@ def run_attention(args):
                                         frac=gbs / pk["hbm_gbs"], peak_source=pk["source"]))))
 
 
+def run_decode(args):
+    """Secondary measurement: one decode step of the Qwen2-0.5B-shaped model (24 layers, hidden 896,
+    14/2 heads, SwiGLU 4864, vocabulary 151936, i8 weights, f16 activations, paged f16 KV cache) at
+    batch 64 and context 2048, tensor parallel over the launched ranks (NCCL all-reduce after the o
+    and down projections). The step is replayed as one CUDA graph. Reports tokens/s and the HBM
+    bytes a step must read (KV pages referenced + weights) over the measured time."""
+    import torch
+    import torch.distributed as dist
+    from nncase_b200 import decoder as D
+    from nncase_b200 import sharding
+    from nncase_b200.kernels import Context
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = D.DecoderConfig()
+    B, n_ctx = 64, 2048
+    weights = D.make_weights(cfg, 1005)
+    max_pages = n_ctx // cfg.page + 1
+    num_pages = B * max_pages
+    ctx = Context(local)
+    dec = D.Decoder(cfg, weights, B, num_pages, ctx=ctx, world=world, rank=rank)
+    g = torch.Generator(device=dev).manual_seed(2005)
+    for lw in dec.layers:
+        lw["k_pool"].normal_(generator=g)
+        lw["v_pool"].normal_(generator=g)
+    table = torch.randperm(num_pages, device=dev, generator=g).to(torch.int32).reshape(B, max_pages).contiguous()
+    ids = torch.randint(0, cfg.vocab, (B,), device=dev, generator=g, dtype=torch.int32)
+    pos = torch.full((B,), n_ctx - 1, dtype=torch.int32, device=dev)
+    for _ in range(max(3, args.warmup)):
+        dec.step(ids, pos, table)
+    torch.cuda.synchronize()
+    l0 = ctx.launches
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph):
+            ctx.use_current_stream()
+            dec.step(ids, pos, table)
+    ctx.use_current_stream()
+    launches_per_step = ctx.launches - l0
+    graph.replay()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.steps):
+        graph.replay()
+    b.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms = sharding.max_over_ranks([a.elapsed_time(b) / args.steps], dev)[0]
+    ctx.check_status()
+    if rank == 0:
+        kv = cfg.layers * B * n_ctx * cfg.kv_heads * cfg.head_dim * 2 * 2
+        H, nq, nkv = cfg.hidden, cfg.q_heads * cfg.head_dim, cfg.kv_heads * cfg.head_dim
+        wbytes = cfg.layers * ((nq + 2 * nkv) * H + H * nq + 2 * cfg.inter * H + H * cfg.inter) + cfg.vocab * H
+        pk = peaks()
+        gbs = (kv + wbytes) / world / (ms / 1000) / 1e9  # per GPU: each rank reads its share
+        print(json.dumps(dict(metric="Qwen2-0.5B-shape decode tokens/s", value=B / (ms / 1000), unit="tokens/s",
+                              n_gpus=world, ms_per_step=ms, steps=args.steps, launches_per_step=launches_per_step,
+                              config=dict(workload="qwen2_0.5b_decode", batch=B, context=n_ctx, layers=cfg.layers,
+                                          parallelism=f"tp{world}", weights="i8 per-channel, f16 scales",
+                                          kv="f16, 16-token pages"),
+                              bytes_per_step=dict(kv=kv, weights=wbytes),
+                              roofline=dict(bound="hbm", achieved=gbs, peak=pk["hbm_gbs"], unit="GB/s per GPU",
+                                            frac=gbs / pk["hbm_gbs"], peak_source=pk["source"]))))
+    # A CUDA graph that holds captured NCCL kernels keeps the communicator busy: tearing the process
+    # group down while it is alive can block forever. Drop the graph, drain the device, line the ranks
+    # up and leave without the NCCL teardown.
+    sys.stdout.flush()
+    del graph
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+        os._exit(0)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -455,8 +540,11 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layer", default=None, help="time only this conv layer (profiling aid)")
     ap.add_argument("--attention", action="store_true", help="secondary metric: paged-attention decode GB/s")
+    ap.add_argument("--decode", action="store_true", help="secondary metric: decoder step tokens/s (tensor parallel under torchrun)")
     args = ap.parse_args()
-    if args.attention:
+    if args.decode:
+        run_decode(args)
+    elif args.attention:
         run_attention(args)
     elif args.layer:
         run_layer(args)
