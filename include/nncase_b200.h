@@ -91,6 +91,8 @@ NNCB_API int nncb_quantize_nchw_to_nhwc_u8(nncb_context *ctx, const float *in, u
  * channels 4c..c_pad-1 = zero point (c_pad 16 or 32; h, w even). A stride-2 convolution over few
  * input channels becomes a stride-1 convolution over c_pad channels with rearranged weights. */
 NNCB_API int nncb_quantize_nchw_to_s2d_u8(nncb_context *ctx, const float *in, uint8_t *out, int n, int c, int h, int w, int c_pad, float scale, int32_t zero_point);
+/* the same from an NHWC f32 input [n][h][w][c] */
+NNCB_API int nncb_quantize_nhwc_to_s2d_u8(nncb_context *ctx, const float *in, uint8_t *out, int n, int h, int w, int c, int c_pad, float scale, int32_t zero_point);
 NNCB_API int nncb_dequantize_nhwc_to_nchw_f32(nncb_context *ctx, const uint8_t *in, float *out, int n, int h, int w, int c, float scale, int32_t zero_point);
 /* u8 layout changes without arithmetic */
 NNCB_API int nncb_nchw_to_nhwc_u8(nncb_context *ctx, const uint8_t *in, uint8_t *out, int n, int c, int h, int w);
@@ -116,6 +118,14 @@ NNCB_API int nncb_make_requant_table(float si, int32_t zi, float so, int32_t zo,
 /* softmax over the last axis of a [rows, cols] f32 tensor (kernels::stackvm::softmax,
  * tensor_ops.cpp:1054-1071; reference/softmax.cpp:30-80): exp((x - max) * beta) / sum. */
 NNCB_API int nncb_softmax_f32(nncb_context *ctx, const float *in, float *out, size_t rows, int cols, float beta);
+/* Channel-block copy between NHWC u8 tensors, optionally through a 256-entry table (HOST pointer or
+ * NULL): dst[p][dst_off + j] = table[src[p][src_off + j]], j < len, p < pixels. This is
+ * kernels::stackvm::concat (tensor_ops.cpp: concat) on the channel axis between quant params -- one
+ * call per input, the table requantising it into the output's param -- and split / slice without one. */
+NNCB_API int nncb_copy_channels_u8(nncb_context *ctx, const uint8_t *src, int src_c, int src_off, uint8_t *dst, int dst_c, int dst_off, int len, size_t pixels, const uint8_t *host_table);
+/* kernels::stackvm::resize_image, nearest neighbour with asymmetric coordinates and floor rounding,
+ * for integer factors: y[n][oy][ox] = x[n][oy / fy][ox / fx]  (NHWC u8). */
+NNCB_API int nncb_resize_nearest_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, int n, int h, int w, int c, int fy, int fx);
 /* y[i] = table[x[i]]; table: 256 bytes, HOST pointer. */
 NNCB_API int nncb_lut_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, size_t n, const uint8_t *host_table);
 /* reduce_window2d max (tensor_ops.cpp: reduce_window2d, reference/reduce_window.cpp:35-105):

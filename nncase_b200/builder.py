@@ -31,7 +31,10 @@ def float_forward(graph, x, device="cpu", record=None):
     for nd in graph:
         op = nd["op"]
         if op == "input":
-            t[nd["out"]] = x.to(device)
+            xin = x.to(device)
+            if nd.get("layout") == "nhwc":
+                xin = xin.permute(0, 3, 1, 2).contiguous()  # the float graph itself runs NCHW
+            t[nd["out"]] = xin
             rec(nd["out"], t[nd["out"]])
         elif op == "conv":
             w = torch.from_numpy(nd["w"]).to(device)
@@ -44,8 +47,11 @@ def float_forward(graph, x, device="cpu", record=None):
             else:
                 padding = (pt, pl)
             y = F.conv2d(xin, w, b, nd["stride"], padding, nd["dil"], nd["groups"])
-            lo, hi = _ACT_CLAMP[nd["act"]]
-            if nd["act"] is not None:
+            if nd["act"] == "silu":
+                rec(nd["out"] + "@pre", y)
+                y = y * torch.sigmoid(y)
+            elif nd["act"] is not None:
+                lo, hi = _ACT_CLAMP[nd["act"]]
                 y = y.clamp(lo, hi)
             if nd.get("res"):
                 rec(nd["out"] + "@conv", y)
@@ -73,6 +79,17 @@ def float_forward(graph, x, device="cpu", record=None):
             b = torch.from_numpy(nd["b"]).to(device)
             t[nd["out"]] = t[nd["in"]].flatten(1) @ w.t() + b
             rec(nd["out"], t[nd["out"]])
+        elif op == "slice":
+            t[nd["out"]] = t[nd["in"]][:, nd["begin"]:nd["end"]]
+            rec(nd["out"], t[nd["out"]])
+        elif op == "concat":
+            t[nd["out"]] = torch.cat([t[i] for i in nd["ins"]], 1)
+            rec(nd["out"], t[nd["out"]])
+        elif op == "upsample":
+            t[nd["out"]] = t[nd["in"]].repeat_interleave(nd["factor"], 2).repeat_interleave(nd["factor"], 3)
+            rec(nd["out"], t[nd["out"]])
+        elif op == "output":
+            return [t[i] for i in nd["ins"]], t
         else:
             raise ValueError(f"unknown node {op}")
         out = nd["out"]
@@ -186,24 +203,26 @@ def build_program(graph, calib_samples, w_quant_type="uint8", device="cpu"):
         tensors[name] = dict(shape=(h, w, c), qp=qp, dtype=dtype)
         shapes[name] = (c, h, w)
 
-    out_name = None
+    out_name, outputs = None, None
     for nd in graph:
         op = nd["op"]
         if op == "input":
             c, h, w = nd["shape"]
-            users = [u for u in graph if u.get("in") == nd["out"] or u.get("res") == nd["out"]]
+            users = [u for u in graph if u.get("in") == nd["out"] or u.get("res") == nd["out"] or
+                     nd["out"] in u.get("ins", ())]
+            nhwc = nd.get("layout") == "nhwc"
             s2d = (len(users) == 1 and users[0]["op"] == "conv" and tuple(users[0]["stride"]) == (2, 2) and
                    users[0]["groups"] == 1 and tuple(users[0]["dil"]) == (1, 1) and c <= 8 and h % 2 == 0 and
                    w % 2 == 0)
             if s2d:
                 # image stem: quantize straight into the space-to-depth layout (see space_to_depth_conv)
                 add_tensor(nd["out"], 32, h // 2, w // 2, qps[nd["out"]])
-                ops.append(dict(op="quantize_input", out=nd["out"], c=c, c_pad=32, s2d=True))
+                ops.append(dict(op="quantize_input", out=nd["out"], c=c, c_pad=32, s2d=True, nhwc=nhwc))
                 s2d_of = {nd["out"]: (c, h, w)}
             else:
                 cp = _pad_channels(c)
                 add_tensor(nd["out"], cp, h, w, qps[nd["out"]])
-                ops.append(dict(op="quantize_input", out=nd["out"], c=c, c_pad=cp))
+                ops.append(dict(op="quantize_input", out=nd["out"], c=c, c_pad=cp, nhwc=nhwc))
                 s2d_of = {}
             in_name = nd["out"]
         elif op == "conv":
@@ -222,15 +241,31 @@ def build_program(graph, calib_samples, w_quant_type="uint8", device="cpu"):
             xqp = tensors[nd["in"]]["qp"]
             mult = (np.float32(xqp.scale) * sw).astype(np.float32)
             has_res = bool(nd.get("res"))
-            o = dict(op="conv", name=nd["name"], **{"in": nd["in"]}, out=nd["out"], w=wq,
+            silu = nd["act"] == "silu"
+            lut = None
+            if silu:
+                # conv output quantized with the pre-activation range, then SiLU as a table into the
+                # activation's own quant param (quantize -> swish on the dequantized value -> quantize)
+                conv_qp = qps[nd["out"] + "@pre"]
+                act_qp = qps[nd["out"] + "@conv"] if has_res else qps[nd["out"]]
+                lut = K.activation_table(L.ACT_SWISH, conv_qp, act_qp)
+                clamp = (-INF, INF)
+            else:
+                conv_qp = qps[nd["out"] + "@conv"] if has_res else qps[nd["out"]]
+                clamp = _ACT_CLAMP[nd["act"]]
+            fuse_res = has_res and not silu  # a table and a fused add do not combine: emit a separate add
+            conv_out = nd["out"] if (fuse_res or not has_res) else nd["out"] + "@conv"
+            o = dict(op="conv", name=nd["name"], **{"in": nd["in"]}, out=conv_out, w=wq,
                      w_zp=zw if zw.any() else None, mult=mult, bias=nd["b"].astype(np.float32), stride=tuple(stride),
-                     pad=tuple(pad), dil=nd["dil"], groups=nd["groups"], clamp=_ACT_CLAMP[nd["act"]],
-                     res=nd.get("res"), y2=nd.get("relu_out"),
-                     conv_qp=qps[nd["out"] + "@conv"] if has_res else qps[nd["out"]])
+                     pad=tuple(pad), dil=nd["dil"], groups=nd["groups"], clamp=clamp,
+                     res=nd.get("res") if fuse_res else None, y2=nd.get("relu_out"), conv_qp=conv_qp, lut=lut)
+            ops.append(o)
+            if has_res and not fuse_res:
+                add_tensor(conv_out, oc, oh, ow, qps[nd["out"] + "@conv"])
+                ops.append(dict(op="add", a=conv_out, b=nd["res"], out=nd["out"]))
             add_tensor(nd["out"], oc, oh, ow, qps[nd["out"]])
             if nd.get("relu_out"):
                 add_tensor(nd["relu_out"], oc, oh, ow, qps[nd["relu_out"]])
-            ops.append(o)
         elif op == "maxpool":
             c, h, w = shapes[nd["in"]]
             oh = (h + nd["pad"][0] + nd["pad"][1] - nd["k"][0]) // nd["stride"][0] + 1
@@ -256,7 +291,22 @@ def build_program(graph, calib_samples, w_quant_type="uint8", device="cpu"):
                             w_zp=zw if zw.any() else None, mult=mult, bias=nd["b"].astype(np.float32), stride=(1, 1),
                             pad=(0, 0, 0, 0), dil=(1, 1), groups=1, clamp=(-INF, INF), res=None, y2=None,
                             conv_qp=None, f32_out=True))
+        elif op == "slice":
+            c, h, w = shapes[nd["in"]]
+            add_tensor(nd["out"], nd["end"] - nd["begin"], h, w, tensors[nd["in"]]["qp"])  # same quant param
+            ops.append(dict(op="slice", **{"in": nd["in"]}, out=nd["out"], begin=nd["begin"], end=nd["end"]))
+        elif op == "concat":
+            c0, h, w = shapes[nd["ins"][0]]
+            add_tensor(nd["out"], sum(shapes[i][0] for i in nd["ins"]), h, w, qps[nd["out"]])
+            ops.append(dict(op="concat", ins=list(nd["ins"]), out=nd["out"]))
+        elif op == "upsample":
+            c, h, w = shapes[nd["in"]]
+            add_tensor(nd["out"], c, h * nd["factor"], w * nd["factor"], tensors[nd["in"]]["qp"])
+            ops.append(dict(op="upsample", **{"in": nd["in"]}, out=nd["out"], factor=nd["factor"]))
+        elif op == "output":
+            outputs = list(nd["ins"])
+            continue
         else:
             raise ValueError(f"unknown node {op}")
         out_name = nd["out"]
-    return dict(input=in_name, output=out_name, tensors=tensors, ops=ops, ranges=ranges)
+    return dict(input=in_name, output=out_name, outputs=outputs or [out_name], tensors=tensors, ops=ops, ranges=ranges)

@@ -206,7 +206,7 @@ int quantize_nchw_to_nhwc_u8(nncb_context *ctx, const float *in, uint8_t *out, i
 // out[n][Y][X][(dy*2+dx)*c + ch] = quantize(in[n][ch][2Y+dy][2X+dx]); channels 4c..c_pad-1 hold the
 // zero point. Turns a stride-2 convolution over few channels (an image stem) into a stride-1
 // convolution over c_pad channels that the tensor-core kernel can take. One thread per cell.
-template <int CPAD>
+template <int CPAD, bool IN_NHWC>
 __global__ void __launch_bounds__(256)
 quantize_nchw_to_s2d_kernel(const float *__restrict__ in, uint8_t *__restrict__ out, int c, int h, int w,
                             size_t total_cells, float scale, float zp) {
@@ -224,8 +224,13 @@ quantize_nchw_to_s2d_kernel(const float *__restrict__ in, uint8_t *__restrict__ 
         for (int ch = 0; ch < c; ch++)
 #pragma unroll
             for (int dy = 0; dy < 2; dy++) {
-                const float2 v = __ldcs(reinterpret_cast<const float2 *>(
-                    in + ((n * c + ch) * h + (2 * Y + dy)) * (size_t)w + 2 * X));
+                float2 v;
+                if (IN_NHWC) {
+                    const float *px = in + ((n * h + (2 * Y + dy)) * (size_t)w + 2 * X) * c + ch;
+                    v = make_float2(__ldcs(px), __ldcs(px + c));
+                } else {
+                    v = __ldcs(reinterpret_cast<const float2 *>(in + ((n * c + ch) * h + (2 * Y + dy)) * (size_t)w + 2 * X));
+                }
                 const uint32_t q0 = (uint32_t)quant_dev(v.x, scale, zp, 0, 255);
                 const uint32_t q1 = (uint32_t)quant_dev(v.y, scale, zp, 0, 255);
                 const int i0 = (dy * 2 + 0) * c + ch, i1 = (dy * 2 + 1) * c + ch;
@@ -246,7 +251,7 @@ quantize_nchw_to_s2d_kernel(const float *__restrict__ in, uint8_t *__restrict__ 
 }
 
 int quantize_nchw_to_s2d_u8(nncb_context *ctx, const float *in, uint8_t *out, int n, int c, int h, int w, int c_pad,
-                            float scale, int32_t zp) {
+                            float scale, int32_t zp, bool in_nhwc) {
     if (n <= 0 || c <= 0 || h <= 0 || w <= 0 || (h & 1) || (w & 1))
         return fail(-EINVAL, "quantize_nchw_to_s2d_u8: height and width must be positive and even");
     if (4 * c > c_pad || (c_pad != 16 && c_pad != 32))
@@ -255,10 +260,14 @@ int quantize_nchw_to_s2d_u8(nncb_context *ctx, const float *in, uint8_t *out, in
         return fail(-EINVAL, "quantize_nchw_to_s2d_u8: pointers must be 8-byte (in) and 16-byte (out) aligned");
     const size_t total = (size_t)n * (h / 2) * (w / 2);
     const int grid = stream_grid(ctx, total, 256);
-    if (c_pad == 32)
-        quantize_nchw_to_s2d_kernel<32><<<grid, 256, 0, ctx->stream>>>(in, out, c, h, w, total, scale, (float)zp);
+    if (c_pad == 32 && in_nhwc)
+        quantize_nchw_to_s2d_kernel<32, true><<<grid, 256, 0, ctx->stream>>>(in, out, c, h, w, total, scale, (float)zp);
+    else if (c_pad == 32)
+        quantize_nchw_to_s2d_kernel<32, false><<<grid, 256, 0, ctx->stream>>>(in, out, c, h, w, total, scale, (float)zp);
+    else if (in_nhwc)
+        quantize_nchw_to_s2d_kernel<16, true><<<grid, 256, 0, ctx->stream>>>(in, out, c, h, w, total, scale, (float)zp);
     else
-        quantize_nchw_to_s2d_kernel<16><<<grid, 256, 0, ctx->stream>>>(in, out, c, h, w, total, scale, (float)zp);
+        quantize_nchw_to_s2d_kernel<16, false><<<grid, 256, 0, ctx->stream>>>(in, out, c, h, w, total, scale, (float)zp);
     return after_launch(ctx, "quantize_nchw_to_s2d");
 }
 
@@ -525,6 +534,95 @@ int global_avgpool_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, int n, in
     global_avgpool_kernel<<<stream_grid(ctx, total, 256), 256, 0, ctx->stream>>>(x, y, n, h * w, c, si, zi, so,
                                                                                  (float)zo);
     return after_launch(ctx, "global_avgpool_u8");
+}
+
+// ---- channel-block copy with optional table (concat / split of NHWC tensors) ---------------------
+// dst[p][dst_off + j] = table ? table[src[p][src_off + j]] : src[p][src_off + j],  j < len, p < pixels.
+// Concat requantises every input into the output's quant param (a 256-entry table per input); a
+// split is the same copy without a table. 16-byte accesses when offsets and widths allow.
+__global__ void __launch_bounds__(256)
+copy_channels_kernel(const uint8_t *__restrict__ src, int src_c, int src_off, uint8_t *__restrict__ dst, int dst_c,
+                     int dst_off, int len, size_t pixels, const lut256 table, bool use_table, bool vec_ok) {
+    __shared__ uint8_t s[256];
+    s[threadIdx.x] = table.t[threadIdx.x];
+    __syncthreads();
+    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
+    if (vec_ok) {
+        const int vpp = len / 16; // 16-byte vectors per pixel
+        const size_t total = pixels * vpp;
+        for (size_t i = tid; i < total; i += nth) {
+            const size_t p = i / vpp;
+            const int v = (int)(i % vpp);
+            uint4 in = __ldg(reinterpret_cast<const uint4 *>(src + p * src_c + src_off) + v);
+            if (use_table) {
+                uint32_t w[4] = {in.x, in.y, in.z, in.w};
+#pragma unroll
+                for (int k = 0; k < 4; k++)
+                    w[k] = (uint32_t)s[w[k] & 255] | ((uint32_t)s[(w[k] >> 8) & 255] << 8) |
+                           ((uint32_t)s[(w[k] >> 16) & 255] << 16) | ((uint32_t)s[w[k] >> 24] << 24);
+                in = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            reinterpret_cast<uint4 *>(dst + p * dst_c + dst_off)[v] = in;
+        }
+    } else {
+        const size_t total = pixels * len;
+        for (size_t i = tid; i < total; i += nth) {
+            const size_t p = i / len;
+            const int j = (int)(i % len);
+            const uint8_t q = src[p * src_c + src_off + j];
+            dst[p * dst_c + dst_off + j] = use_table ? s[q] : q;
+        }
+    }
+}
+
+int copy_channels_u8(nncb_context *ctx, const uint8_t *src, int src_c, int src_off, uint8_t *dst, int dst_c, int dst_off,
+                     int len, size_t pixels, const uint8_t *host_table) {
+    if (pixels == 0 || len == 0)
+        return 0;
+    if (!src || !dst || src_c <= 0 || dst_c <= 0 || src_off < 0 || dst_off < 0 || len < 0 || src_off + len > src_c ||
+        dst_off + len > dst_c)
+        return fail(-EINVAL, "copy_channels_u8: channel block out of range");
+    lut256 t;
+    if (host_table)
+        memcpy(t.t, host_table, 256);
+    else
+        memset(t.t, 0, 256);
+    const bool vec = aligned16(src, dst) && ((src_c | src_off | dst_c | dst_off | len) % 16 == 0);
+    const size_t items = vec ? pixels * (len / 16) : pixels * len;
+    copy_channels_kernel<<<stream_grid(ctx, items, 256), 256, 0, ctx->stream>>>(src, src_c, src_off, dst, dst_c, dst_off,
+                                                                                len, pixels, t, host_table != nullptr, vec);
+    return after_launch(ctx, "copy_channels_u8");
+}
+
+// ---- nearest-neighbour resize by an integer factor (NHWC u8) --------------------------------------
+// out[n][y][x][:] = in[n][y / fy][x / fx][:]  (resize_image nearest with asymmetric coordinates and
+// floor rounding, reference/resize_image.cpp, for integer scale factors).
+__global__ void __launch_bounds__(256)
+resize_nearest_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ y, int n, int h, int w, int c, int fy, int fx,
+                      bool vec_ok) {
+    const int oh = h * fy, ow = w * fx;
+    const int per = vec_ok ? c / 16 : c;
+    const size_t total = (size_t)n * oh * ow * per;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int j = (int)(i % per);
+        const size_t p = i / per;
+        const int ox = (int)(p % ow), oy = (int)((p / ow) % oh);
+        const size_t b = p / ((size_t)ow * oh);
+        const size_t sp = (b * h + oy / fy) * w + ox / fx;
+        if (vec_ok)
+            reinterpret_cast<uint4 *>(y + p * c)[j] = __ldg(reinterpret_cast<const uint4 *>(x + sp * c) + j);
+        else
+            y[p * c + j] = x[sp * c + j];
+    }
+}
+
+int resize_nearest_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, int n, int h, int w, int c, int fy, int fx) {
+    if (n <= 0 || h <= 0 || w <= 0 || c <= 0 || fy <= 0 || fx <= 0)
+        return fail(-EINVAL, "resize_nearest_u8: bad shape");
+    const bool vec = c % 16 == 0 && aligned16(x, y);
+    const size_t total = (size_t)n * h * fy * w * fx * (vec ? c / 16 : c);
+    resize_nearest_kernel<<<stream_grid(ctx, total, 256), 256, 0, ctx->stream>>>(x, y, n, h, w, c, fy, fx, vec);
+    return after_launch(ctx, "resize_nearest_u8");
 }
 
 // ---- softmax over the last axis (f32) -----------------------------------------------------------

@@ -138,6 +138,34 @@ class Context:
                                                      qp.scale, qp.zero_point))
         return y
 
+    def quantize_nhwc_to_s2d(self, x, qp, c_pad=32):
+        """f32 NHWC -> u8 [n, h/2, w/2, c_pad] with the same channel order as quantize_nchw_to_s2d."""
+        x = self._cuda(x, torch.float32)
+        n, h, w, c = x.shape
+        y = torch.empty((n, h // 2, w // 2, c_pad), dtype=torch.uint8, device=self.device)
+        check(self._lib.nncb_quantize_nhwc_to_s2d_u8(self._h, x.data_ptr(), y.data_ptr(), n, h, w, c, c_pad,
+                                                     qp.scale, qp.zero_point))
+        return y
+
+    def copy_channels(self, src, src_off, dst, dst_off, length, table=None):
+        """dst[..., dst_off:dst_off+length] = table[src[..., src_off:src_off+length]] on NHWC u8 tensors, in place
+        on dst (Slice and one input of Concat; table None copies)."""
+        src, dst = self._cuda(src, torch.uint8), self._cuda(dst, torch.uint8)
+        pixels = src.numel() // src.shape[-1] if src.shape[-1] else 0
+        t = None if table is None else np.ascontiguousarray(table, np.uint8)
+        check(self._lib.nncb_copy_channels_u8(self._h, src.data_ptr(), src.shape[-1], src_off, dst.data_ptr(),
+                                              dst.shape[-1], dst_off, length, pixels,
+                                              t.ctypes.data if t is not None else None))
+        return dst
+
+    def resize_nearest(self, x, fy, fx):
+        """NHWC u8 nearest-neighbour upsampling by integer factors."""
+        x = self._cuda(x, torch.uint8)
+        n, h, w, c = x.shape
+        y = torch.empty((n, h * fy, w * fx, c), dtype=torch.uint8, device=self.device)
+        check(self._lib.nncb_resize_nearest_u8(self._h, x.data_ptr(), y.data_ptr(), n, h, w, c, fy, fx))
+        return y
+
     def dequantize_nhwc_to_nchw(self, q, qp):
         q = self._cuda(q, torch.uint8)
         n, h, w, c = q.shape

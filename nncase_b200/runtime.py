@@ -56,10 +56,23 @@ class CudaFunction:
             plan = ctx.conv2d_plan((self.batch, h, w, c), op["w"], op["w_zp"], op["mult"], op["bias"],
                                    tin["qp"].zero_point, out_qp, stride=op["stride"], padding=op["pad"],
                                    dilation=op["dil"], groups=op["groups"], fused_clamp=op["clamp"], residual=residual,
-                                   y2=y2, f32_out=bool(op.get("f32_out")), force_path=force_path)
+                                   y2=y2, f32_out=bool(op.get("f32_out")), force_path=force_path, lut=op.get("lut"))
             self.plans.append(plan)
             return ("conv", op, plan)
-        if kind in ("maxpool", "requant", "gap"):
+        if kind == "concat":
+            # one requantising table per input: into the concat's quant param
+            tables, off = [], 0
+            oq = T[op["out"]]["qp"]
+            for name in op["ins"]:
+                iq = T[name]["qp"]
+                t = np.empty(256, np.uint8)
+                L.check(ctx._lib.nncb_make_requant_table(iq.scale, iq.zero_point, oq.scale, oq.zero_point,
+                                                         -INF, INF, t.ctypes.data))
+                identity = (iq.scale, iq.zero_point) == (oq.scale, oq.zero_point)
+                tables.append((name, off, T[name]["shape"][2], None if identity else t))
+                off += T[name]["shape"][2]
+            return ("concat", op, tables)
+        if kind in ("maxpool", "requant", "gap", "add", "slice", "upsample"):
             return (kind, op)
         raise NncbError(-38, f"unsupported program op {kind}")
 
@@ -78,9 +91,20 @@ class CudaFunction:
             if kind == "quantize_input":
                 n, c, hh, ww = x_dev.shape
                 qp = T[op["out"]]["qp"]
-                fn_q = lib.nncb_quantize_nchw_to_s2d_u8 if op.get("s2d") else lib.nncb_quantize_nchw_to_nhwc_u8
-                L.check(fn_q(h_, x_dev.data_ptr(), buf[op["out"]].data_ptr(), n, c, hh, ww, op["c_pad"], qp.scale,
-                             qp.zero_point))
+                if op.get("nhwc"):
+                    n, hh, ww, c = x_dev.shape
+                    if op.get("s2d"):
+                        L.check(lib.nncb_quantize_nhwc_to_s2d_u8(h_, x_dev.data_ptr(), buf[op["out"]].data_ptr(), n, hh, ww,
+                                                                 c, op["c_pad"], qp.scale, qp.zero_point))
+                    elif op["c_pad"] == c:
+                        L.check(lib.nncb_quantize(h_, x_dev.data_ptr(), buf[op["out"]].data_ptr(), x_dev.numel(),
+                                                  qp.scale, qp.zero_point, L.U8))
+                    else:
+                        raise NncbError(-38, "NHWC input with channel padding is only built for stride-2 stems")
+                else:
+                    fn_q = lib.nncb_quantize_nchw_to_s2d_u8 if op.get("s2d") else lib.nncb_quantize_nchw_to_nhwc_u8
+                    L.check(fn_q(h_, x_dev.data_ptr(), buf[op["out"]].data_ptr(), n, c, hh, ww, op["c_pad"], qp.scale,
+                                 qp.zero_point))
             elif kind == "conv":
                 plan = st[2]
                 res = buf[op["res"]] if op.get("res") else None
@@ -98,6 +122,26 @@ class CudaFunction:
                 L.check(lib.nncb_requant_u8(h_, buf[op["in"]].data_ptr(), buf[op["out"]].data_ptr(),
                                             buf[op["in"]].numel(), qi.scale, qi.zero_point, qo.scale, qo.zero_point,
                                             op["clamp"][0], op["clamp"][1]))
+            elif kind == "add":
+                qa, qb, qo = T[op["a"]]["qp"], T[op["b"]]["qp"], T[op["out"]]["qp"]
+                L.check(lib.nncb_qadd_u8(h_, buf[op["a"]].data_ptr(), buf[op["b"]].data_ptr(), buf[op["out"]].data_ptr(),
+                                         buf[op["out"]].numel(), qa.scale, qa.zero_point, qb.scale, qb.zero_point,
+                                         qo.scale, qo.zero_point))
+            elif kind == "slice":
+                hh, ww, c = T[op["in"]]["shape"]
+                L.check(lib.nncb_copy_channels_u8(h_, buf[op["in"]].data_ptr(), c, op["begin"], buf[op["out"]].data_ptr(),
+                                                  op["end"] - op["begin"], 0, op["end"] - op["begin"],
+                                                  self.batch * hh * ww, None))
+            elif kind == "concat":
+                hh, ww, ctot = T[op["out"]]["shape"]
+                for name, off, ci, table in st[2]:
+                    L.check(lib.nncb_copy_channels_u8(h_, buf[name].data_ptr(), ci, 0, buf[op["out"]].data_ptr(), ctot, off,
+                                                      ci, self.batch * hh * ww,
+                                                      table.ctypes.data if table is not None else None))
+            elif kind == "upsample":
+                hh, ww, c = T[op["in"]]["shape"]
+                L.check(lib.nncb_resize_nearest_u8(h_, buf[op["in"]].data_ptr(), buf[op["out"]].data_ptr(), self.batch, hh,
+                                                   ww, c, op["factor"], op["factor"]))
             elif kind == "gap":
                 hh, ww, c = T[op["in"]]["shape"]
                 qi, qo = T[op["in"]]["qp"], T[op["out"]]["qp"]
@@ -108,7 +152,7 @@ class CudaFunction:
     def invoke(self, x_dev):
         """Device in (f32 NCHW [batch,c,h,w]), device out (the program's output buffer)."""
         if x_dev.shape[0] != self.batch or x_dev.dtype != torch.float32 or not x_dev.is_contiguous():
-            raise NncbError(-22, "invoke: input must be a contiguous f32 NCHW tensor of the planned batch")
+            raise NncbError(-22, "invoke: input must be a contiguous f32 tensor of the planned batch")
         self.ctx.use_current_stream()
         before = self.ctx.launches
         out = self._run(x_dev)
@@ -149,6 +193,10 @@ class CudaFunction:
 
     def tensor(self, name):
         return self.buffers[name]
+
+    def outputs(self):
+        """The program's output tensors, in order (u8 NHWC, or f32 for a MatMul classifier)."""
+        return [self.buffers[n] for n in self.program.get("outputs", [self.program["output"]])]
 
     def close(self):
         for p in self.plans:

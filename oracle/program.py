@@ -26,10 +26,13 @@ def run_program(program, x_nchw_f32, threads=8, feed=None, keep=None):
         k = op["op"]
         if k == "quantize_input":
             qp = T[op["out"]]["qp"]
+            xin = x_nchw_f32
+            if op.get("nhwc"):  # element-wise identical: bring the NHWC input to the NCHW form the helpers take
+                xin = np.ascontiguousarray(np.transpose(x_nchw_f32, (0, 3, 1, 2)))
             if op.get("s2d"):
-                t[op["out"]] = Q.quantize_nchw_to_s2d_u8(x_nchw_f32, qp.scale, qp.zero_point, op["c_pad"])
+                t[op["out"]] = Q.quantize_nchw_to_s2d_u8(xin, qp.scale, qp.zero_point, op["c_pad"])
             else:
-                t[op["out"]] = Q.quantize_nchw_to_nhwc_u8(x_nchw_f32, qp.scale, qp.zero_point, op["c_pad"])
+                t[op["out"]] = Q.quantize_nchw_to_nhwc_u8(xin, qp.scale, qp.zero_point, op["c_pad"])
         elif k == "conv":
             xin = get(op["in"])
             xqp = T[op["in"]]["qp"]
@@ -40,7 +43,8 @@ def run_program(program, x_nchw_f32, threads=8, feed=None, keep=None):
                 continue
             cq = op["conv_qp"]
             y = Q.qconv2d_u8(xin, op["w"], op["w_zp"], op["mult"], op["bias"], xqp.zero_point, cq.scale,
-                             cq.zero_point, op["stride"], op["pad"], op["dil"], op["groups"], op["clamp"])
+                             cq.zero_point, op["stride"], op["pad"], op["dil"], op["groups"], op["clamp"],
+                             lut=op.get("lut"))
             if op.get("res"):
                 rq, oq = T[op["res"]]["qp"], T[op["out"]]["qp"]
                 y = Q.qadd_u8(y, get(op["res"]), cq.scale, cq.zero_point, rq.scale, rq.zero_point, oq.scale,
@@ -54,6 +58,21 @@ def run_program(program, x_nchw_f32, threads=8, feed=None, keep=None):
         elif k == "requant":
             qi, qo = T[op["in"]]["qp"], T[op["out"]]["qp"]
             t[op["out"]] = Q.requant_u8(get(op["in"]), qi.scale, qi.zero_point, qo.scale, qo.zero_point, *op["clamp"])
+        elif k == "add":
+            qa, qb, qo = T[op["a"]]["qp"], T[op["b"]]["qp"], T[op["out"]]["qp"]
+            t[op["out"]] = Q.qadd_u8(get(op["a"]), get(op["b"]), qa.scale, qa.zero_point, qb.scale, qb.zero_point,
+                                     qo.scale, qo.zero_point)
+        elif k == "slice":
+            t[op["out"]] = np.ascontiguousarray(get(op["in"])[..., op["begin"]:op["end"]])
+        elif k == "concat":
+            oq = T[op["out"]]["qp"]
+            parts = []
+            for name in op["ins"]:
+                iq = T[name]["qp"]
+                parts.append(Q.requant_u8(get(name), iq.scale, iq.zero_point, oq.scale, oq.zero_point))
+            t[op["out"]] = np.ascontiguousarray(np.concatenate(parts, axis=-1))
+        elif k == "upsample":
+            t[op["out"]] = Q.resize_nearest_u8(get(op["in"]), op["factor"], op["factor"])
         elif k == "gap":
             qi, qo = T[op["in"]]["qp"], T[op["out"]]["qp"]
             t[op["out"]] = Q.global_avgpool_u8(get(op["in"]), qi.scale, qi.zero_point, qo.scale, qo.zero_point)

@@ -332,6 +332,25 @@ void qo_lut_u8(const uint8_t *x, uint8_t *y, size_t n, const uint8_t *table) {
         y[i] = table[x[i]];
 }
 
+/* Channel-block copy through an optional table: concat (per-input requantisation) and split. */
+void qo_copy_channels_u8(const uint8_t *src, int src_c, int src_off, uint8_t *dst, int dst_c, int dst_off, int len,
+                         size_t pixels, const uint8_t *table) {
+    for (size_t p = 0; p < pixels; p++)
+        for (int j = 0; j < len; j++) {
+            uint8_t q = src[p * src_c + src_off + j];
+            dst[p * dst_c + dst_off + j] = table ? table[q] : q;
+        }
+}
+
+/* Nearest-neighbour resize by integer factors, asymmetric coordinates, floor (NHWC). */
+void qo_resize_nearest_u8(const uint8_t *x, uint8_t *y, int n, int h, int w, int c, int fy, int fx) {
+    const int oh = h * fy, ow = w * fx;
+    for (int b = 0; b < n; b++)
+        for (int oy = 0; oy < oh; oy++)
+            for (int ox = 0; ox < ow; ox++)
+                memcpy(y + (((size_t)b * oh + oy) * ow + ox) * c, x + (((size_t)b * h + oy / fy) * w + ox / fx) * c, c);
+}
+
 /* softmax over the last axis, f32 (reference/softmax.cpp:30-80): max, (x - max) * beta, expf,
  * sequential sum, multiply by 1/sum. */
 void qo_softmax_f32(const float *in, float *out, size_t rows, int cols, float beta) {

@@ -182,3 +182,24 @@ def softmax_f32(x, beta=1.0):
     cols = x.shape[-1]
     lib().qo_softmax_f32(_p(x), _p(y), C.c_size_t(x.size // cols), cols, C.c_float(beta))
     return y
+
+
+def copy_channels_u8(src, src_off, dst, dst_off, length, table=None):
+    """In place on dst (NHWC arrays): dst[..., dst_off:dst_off+length] = table[src[..., src_off:...]]."""
+    assert src.flags.c_contiguous and dst.flags.c_contiguous
+    pixels = src.size // src.shape[-1]
+    t = None if table is None else np.ascontiguousarray(table, np.uint8)
+    lib().qo_copy_channels_u8(_p(src), src.shape[-1], src_off, _p(dst), dst.shape[-1], dst_off, length,
+                              C.c_size_t(pixels), _p(t))
+
+
+def resize_nearest_u8(x, fy, fx):
+    x = np.ascontiguousarray(x, np.uint8)
+    n, h, w, c = x.shape
+    y = np.empty((n, h * fy, w * fx, c), np.uint8)
+    lib().qo_resize_nearest_u8(_p(x), _p(y), n, h, w, c, fy, fx)
+    return y
+
+
+def requant_table(si, zi, so, zo, lo=-np.inf, hi=np.inf):
+    return requant_u8(np.arange(256, dtype=np.uint8), si, zi, so, zo, lo, hi)

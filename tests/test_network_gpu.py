@@ -52,3 +52,50 @@ def test_resnet50v2_every_tensor(ctx, w_quant):
     host = fn.invoke_host(x)
     assert np.array_equal(host.numpy(), want)
     fn.close()
+
+
+def _check_every_tensor(fn, program, x, ctx):
+    fn.invoke(torch.from_numpy(x).cuda())
+    ctx.check_status()
+    _, tens = oprog.run_program(program, x)
+    for name, ref_t in tens.items():
+        got = fn.tensor(name).cpu().numpy()
+        bad = int((got != ref_t).sum())
+        assert bad == 0, f"tensor {name}: {bad} of {ref_t.size} elements differ"
+    return tens
+
+
+def test_mobilenetv2_every_tensor(ctx):
+    """NHWC f32 input, depthwise 3x3 (direct kernel) between 1x1 tensor-core layers, ReLU6, residual adds."""
+    graph = networks.mobilenetv2(1005)
+    cal = [np.random.default_rng(3005 + i).uniform(0, 1, (1, 224, 224, 3)).astype(np.float32) for i in range(2)]
+    program = builder.build_program(graph, cal)
+    n = 2
+    x = np.random.default_rng(2005).uniform(0, 1, (n, 224, 224, 3)).astype(np.float32)
+    fn = CudaFunction(program, n, ctx)
+    ops = {o["name"]: o for o in program["ops"] if o["op"] == "conv"}
+    for name, path in fn.conv_paths.items():
+        assert path == (L.PATH_TC if ops[name]["groups"] == 1 else L.PATH_SIMT), (name, path)
+    _check_every_tensor(fn, program, x, ctx)
+    xd = torch.from_numpy(x).cuda()
+    out = fn.invoke(xd).clone()
+    fn.capture(xd)
+    assert torch.equal(fn.replay(xd), out)
+    fn.close()
+
+
+def test_yolov8s_every_tensor(ctx):
+    """SiLU tables in the convolution epilogue, Slice/Concat/Upsample, 5x5 max pooling, six u8 outputs."""
+    graph = networks.yolov8s(1007, image=320)
+    cal = [np.random.default_rng(3007 + i).uniform(0, 1, (1, 3, 320, 320)).astype(np.float32) for i in range(2)]
+    program = builder.build_program(graph, cal)
+    n = 2
+    x = np.random.default_rng(2007).uniform(0, 1, (n, 3, 320, 320)).astype(np.float32)
+    fn = CudaFunction(program, n, ctx)
+    assert all(p == L.PATH_TC for p in fn.conv_paths.values()), fn.conv_paths
+    tens = _check_every_tensor(fn, program, x, ctx)
+    outs = fn.outputs()
+    assert len(outs) == 6
+    for name, t in zip(program["outputs"], outs):
+        assert np.array_equal(t.cpu().numpy(), tens[name])
+    fn.close()

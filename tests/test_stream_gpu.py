@@ -171,3 +171,41 @@ def test_softmax(ctx, qo, shape):
     want = qo.softmax_f32(x)
     assert np.abs(got - want).max() <= 1e-3 * max(float(want.max() - want.min()), 1e-6)
     assert np.allclose(got.sum(-1), 1.0, atol=1e-5)
+
+
+@pytest.mark.parametrize("shape,c_pad", [((2, 18, 22, 3), 32), ((1, 224, 224, 3), 32), ((2, 8, 8, 4), 16)])
+def test_quantize_nhwc_to_s2d(ctx, qo, shape, c_pad):
+    """The NHWC-input form gives the bytes of the NCHW form on the transposed input."""
+    x = np.random.default_rng(14).normal(0, 1, shape).astype(np.float32)
+    got = ctx.quantize_nhwc_to_s2d(torch.from_numpy(x), QuantParam(117, 0.021), c_pad).cpu().numpy()
+    want = qo.quantize_nchw_to_s2d_u8(np.ascontiguousarray(x.transpose(0, 3, 1, 2)), 0.021, 117, c_pad)
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("src_c,src_off,dst_c,dst_off,length", [(64, 0, 192, 64, 64), (64, 32, 32, 0, 32),
+                                                               (40, 3, 51, 7, 29), (16, 0, 16, 0, 0)])
+@pytest.mark.parametrize("with_table", [False, True])
+def test_copy_channels(ctx, qo, src_c, src_off, dst_c, dst_off, length, with_table):
+    rng = np.random.default_rng(15)
+    src = rng.integers(0, 256, (2, 9, 11, src_c), dtype=np.uint8)
+    dst0 = rng.integers(0, 256, (2, 9, 11, dst_c), dtype=np.uint8)
+    table = qo.requant_table(0.031, 120, 0.047, 99) if with_table else None
+    got = ctx.copy_channels(torch.from_numpy(src), src_off, torch.from_numpy(dst0.copy()), dst_off, length, table)
+    want = dst0.copy()
+    qo.copy_channels_u8(src, src_off, want, dst_off, length, table)
+    assert np.array_equal(got.cpu().numpy(), want)
+
+
+def test_copy_channels_rejects_out_of_range(ctx):
+    from nncase_b200.kernels import NncbError
+    a = torch.zeros((1, 2, 2, 16), dtype=torch.uint8)
+    with pytest.raises(NncbError):
+        ctx.copy_channels(a, 8, a.clone(), 0, 16)
+
+
+@pytest.mark.parametrize("shape,f", [((2, 10, 10, 256), 2), ((1, 7, 5, 33), 3), ((3, 20, 20, 128), 2)])
+def test_resize_nearest(ctx, qo, shape, f):
+    x = np.random.default_rng(16).integers(0, 256, shape, dtype=np.uint8)
+    got = ctx.resize_nearest(torch.from_numpy(x), f, f).cpu().numpy()
+    assert np.array_equal(got, qo.resize_nearest_u8(x, f, f))
+    assert np.array_equal(got, x.repeat(f, 1).repeat(f, 2))
