@@ -204,6 +204,11 @@ def build_program(graph, calib_samples, w_quant_type="uint8", device="cpu"):
         shapes[name] = (c, h, w)
 
     out_name, outputs = None, None
+    # Tensors between layers are stored with their channel count rounded up to the tensor-core
+    # kernel's K granule (32); added channels carry weight zero points / zero multipliers and
+    # contribute nothing. Program outputs keep their own channel count.
+    final = set(graph[-1]["ins"]) if graph[-1]["op"] == "output" else {graph[-1]["out"]}
+    logical = {}
     for nd in graph:
         op = nd["op"]
         if op == "input":
@@ -235,6 +240,22 @@ def build_program(graph, calib_samples, w_quant_type="uint8", device="cpu"):
                 stride = (1, 1)
             else:
                 wq, zw, sw = quantize_weights(nd["w"], w_quant_type, c if nd["groups"] == 1 else None)
+            bias = nd["b"].astype(np.float32)
+            groups = nd["groups"]
+            logical[nd["out"]] = wq.shape[0]
+            oc_p = wq.shape[0]
+            if groups != 1:
+                if groups != wq.shape[0] or wq.shape[3] != 1:
+                    raise ValueError("grouped convolutions other than depthwise are not lowered")
+                oc_p = groups = c  # depthwise over the stored (padded) channels
+            elif nd["out"] not in final and nd.get("relu_out") not in final:
+                oc_p = -(-wq.shape[0] // 32) * 32
+            extra = oc_p - wq.shape[0]
+            if extra:
+                wq = np.ascontiguousarray(np.concatenate([wq, np.zeros((extra,) + wq.shape[1:], wq.dtype)]))
+                zw = np.concatenate([zw, np.zeros(extra, np.int32)])
+                sw = np.concatenate([sw, np.zeros(extra, np.float32)])  # multiplier 0: the channel holds q(0)
+                bias = np.concatenate([bias, np.zeros(extra, np.float32)])
             oc, kh, kw, _ = wq.shape
             oh = (h + pad[0] + pad[1] - ((kh - 1) * nd["dil"][0] + 1)) // stride[0] + 1
             ow = (w + pad[2] + pad[3] - ((kw - 1) * nd["dil"][1] + 1)) // stride[1] + 1
@@ -256,8 +277,8 @@ def build_program(graph, calib_samples, w_quant_type="uint8", device="cpu"):
             fuse_res = has_res and not silu  # a table and a fused add do not combine: emit a separate add
             conv_out = nd["out"] if (fuse_res or not has_res) else nd["out"] + "@conv"
             o = dict(op="conv", name=nd["name"], **{"in": nd["in"]}, out=conv_out, w=wq,
-                     w_zp=zw if zw.any() else None, mult=mult, bias=nd["b"].astype(np.float32), stride=tuple(stride),
-                     pad=tuple(pad), dil=nd["dil"], groups=nd["groups"], clamp=clamp,
+                     w_zp=zw if zw.any() else None, mult=mult, bias=bias, stride=tuple(stride),
+                     pad=tuple(pad), dil=nd["dil"], groups=groups, clamp=clamp,
                      res=nd.get("res") if fuse_res else None, y2=nd.get("relu_out"), conv_qp=conv_qp, lut=lut)
             ops.append(o)
             if has_res and not fuse_res:
@@ -283,7 +304,7 @@ def build_program(graph, calib_samples, w_quant_type="uint8", device="cpu"):
             ops.append(dict(op="gap", **{"in": nd["in"]}, out=nd["out"]))
         elif op == "fc":
             c, h, w = shapes[nd["in"]]
-            wq, zw, sw = quantize_weights(nd["w"].reshape(nd["w"].shape[0], c, 1, 1), w_quant_type)
+            wq, zw, sw = quantize_weights(nd["w"].reshape(nd["w"].shape[0], -1, 1, 1), w_quant_type, c)
             xqp = tensors[nd["in"]]["qp"]
             mult = (np.float32(xqp.scale) * sw).astype(np.float32)
             add_tensor(nd["out"], wq.shape[0], 1, 1, None, "f32")
@@ -293,10 +314,14 @@ def build_program(graph, calib_samples, w_quant_type="uint8", device="cpu"):
                             conv_qp=None, f32_out=True))
         elif op == "slice":
             c, h, w = shapes[nd["in"]]
+            if logical.get(nd["in"], c) != c:
+                raise ValueError("slice of a channel-padded tensor is not lowered")
             add_tensor(nd["out"], nd["end"] - nd["begin"], h, w, tensors[nd["in"]]["qp"])  # same quant param
             ops.append(dict(op="slice", **{"in": nd["in"]}, out=nd["out"], begin=nd["begin"], end=nd["end"]))
         elif op == "concat":
             c0, h, w = shapes[nd["ins"][0]]
+            if any(logical.get(i, shapes[i][0]) != shapes[i][0] for i in nd["ins"]):
+                raise ValueError("concat of channel-padded tensors is not lowered")
             add_tensor(nd["out"], sum(shapes[i][0] for i in nd["ins"]), h, w, qps[nd["out"]])
             ops.append(dict(op="concat", ins=list(nd["ins"]), out=nd["out"]))
         elif op == "upsample":

@@ -298,6 +298,7 @@ __device__ __forceinline__ void tmem_ld1(uint32_t taddr, int &r) {
 // Extra constants of the fast epilogue (see epilogue_fast below).
 struct FastEpi {
     uint32_t off_out, off_y2, off_res, off_cst, off_corr, off_lut2; // byte offsets from the aligned smem base
+    int lut_only; // the table maps the convolution's own output: only the mapped tile is stored
     int corr_pitch;     // bn + 1: distinct border classes fall into distinct banks
     int n_cls;
     int out_sw;         // swizzle span of the staging sub-tiles: 64, 32 or 0
@@ -828,7 +829,8 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
             mbar_arrive(smem_u32(&sh.bar_acc_empty[buf]));
             const int gy = mt * 128 + lane_group * 32;
             if (gy < g.m_total) {
-                tma_store_2d(tmap_y, s_out, oc0 + col_off, gy);
+                if (!Y2 || !f.lut_only)
+                    tma_store_2d(tmap_y, s_out, oc0 + col_off, gy);
                 if (Y2)
                     tma_store_2d(tmap_y2, s_y2, oc0 + col_off, gy);
             }
@@ -993,7 +995,10 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
     g.idesc = (2u << 4) | (0u << 7) | ((d.w_signed ? 1u : 0u) << 10) | ((uint32_t)(g.bn_mma >> 3) << 17) |
               ((uint32_t)(128 >> 4) << 24);
     // ---- fast epilogue: constants, error bounds and shared-memory layout ----
-    const bool fast_shape = !d.f32_out && cv->d_lut == nullptr && d.oc % 16 == 0 &&
+    // An activation table on the output runs through the second-output machinery (table in shared
+    // memory, mapped tile staged and stored), with the unmapped tile left unstored.
+    const bool lut_only = cv->d_lut != nullptr && !d.has_y2 && !d.has_residual;
+    const bool fast_shape = !d.f32_out && (cv->d_lut == nullptr || lut_only) && d.oc % 16 == 0 &&
                             (g.bn == 128 || g.bn == 64 || g.bn == 32);
     tp->f = new FastEpi();
     FastEpi &fe = *tp->f;
@@ -1006,7 +1011,8 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
         const uint32_t tile_bytes = (128u * g.bn + 1023u) & ~1023u;
         uint32_t off = 0;
         fe.off_out = off, off += tile_bytes;
-        fe.off_y2 = off, off += d.has_y2 ? tile_bytes : 0;
+        fe.off_y2 = off, off += (d.has_y2 || lut_only) ? tile_bytes : 0;
+        fe.lut_only = lut_only ? 1 : 0;
         fe.off_res = off, off += d.has_residual ? tile_bytes : 0;
         fe.off_cst = off, off += (uint32_t)g.bn * 16;
         fe.off_lut2 = off, off += 256;
@@ -1239,6 +1245,10 @@ int tc_conv_run(nncb_context *ctx, nncb_qconv2d *cv, const uint8_t *x, const uin
     const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
     auto al16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
     if (tp->fast && al16(y) && al16(y2) && al16(res)) {
+        if (tp->f->lut_only) {
+            a.p.y2_lut = cv->d_lut;
+            y2 = static_cast<uint8_t *>(y);
+        }
         if (tp->y_ptr != y) {
             NNCB_TRY(make_tmap_out(&tp->tmap_y, tp, y));
             tp->y_ptr = y;
