@@ -218,9 +218,10 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 
 // Bounded wait. Returns false when the block is aborting or the wait ran out (about 1 s);
 // in the latter case it records `code` in the status word and raises the abort flag.
-__device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code) {
-    if (mbar_try(bar, parity))
-        return true;
+// The first probe is inlined at the call site: the one-thread producer and MMA loops run one
+// dependent instruction at a time, so a call and a timer read per K block would cost more than
+// the K block's loads and MMAs.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code) {
     const uint64_t t0 = globaltimer_ns();
     for (uint32_t it = 1;; it++) {
         if (mbar_try(bar, parity))
@@ -236,6 +237,11 @@ __device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile i
             }
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code) {
+    if (mbar_try(bar, parity))
+        return true;
+    return mbar_wait_slow(bar, parity, abort_flag, status, code);
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y) {
@@ -404,33 +410,47 @@ __device__ __forceinline__ void producer_loop(const TcGeom &g, const StageGeom &
     using namespace dev;
     const int k_blocks = g.taps * g.c_blocks;
     const int total_tiles = g.m_tiles * g.n_tiles;
+    const bool gemm = g.mode == MODE_GEMM;
+    const int kb = g.kb, c_blocks = g.c_blocks, kw_ = g.kw;
+    const uint32_t dil_w = g.dil_w, dil_h = g.dil_h, stages = g.stages;
+    const uint32_t stage_bytes = sg.a_stage_bytes + sg.b_stage_bytes;
+    const uint32_t bar_full0 = smem_u32(&sh.bar_full[0]), bar_empty0 = smem_u32(&sh.bar_empty[0]);
     uint32_t stage = 0, phase = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
         const int mt = tile % g.m_tiles, nt = tile / g.m_tiles;
-        const int m0 = mt * 128;
+        const int m0 = mt * 128, n0 = nt * g.bn_mma;
         int cw = 0, chh = 0, cn = 0;
-        if (g.mode == MODE_IM2COL) {
+        if (!gemm) {
             const int q = m0 % g.ow, pp = (m0 / g.ow) % g.oh;
             cn = m0 / (g.ow * g.oh);
             cw = q * g.stride_w - g.pad_l;
             chh = pp * g.stride_h - g.pad_t;
         }
+        // K blocks in (tap row, tap column, channel block) order; all indices advance by
+        // increments -- this loop is one thread's dependent instruction stream
+        int cb = 0, c_off = 0, k_off = 0;
+        uint32_t off_w = 0, off_h = 0;
+        int kx = 0;
         for (int kbi = 0; kbi < k_blocks; kbi++) {
-            if (!mbar_wait(smem_u32(&sh.bar_empty[stage]), phase ^ 1, &sh.abort_flag, status, ERR_PRODUCER))
+            if (!mbar_wait(bar_empty0 + stage * 8, phase ^ 1, &sh.abort_flag, status, ERR_PRODUCER))
                 return;
-            const uint32_t full = smem_u32(&sh.bar_full[stage]);
+            const uint32_t full = bar_full0 + stage * 8;
             const uint32_t sa = sg.smem_base + stage * sg.stage_pitch, sb = sa + sg.a_stage_bytes;
-            mbar_expect_tx(full, sg.a_stage_bytes + sg.b_stage_bytes);
-            const int tap = kbi / g.c_blocks, cb = kbi % g.c_blocks;
-            if (g.mode == MODE_GEMM) {
-                tma_load_2d(sa, tmap_a, full, cb * g.kb, m0);
-            } else {
-                const int ky = tap / g.kw, kx = tap % g.kw;
-                tma_load_im2col_4d(sa, tmap_a, full, cb * g.kb, cw, chh, cn, (uint16_t)(kx * g.dil_w),
-                                   (uint16_t)(ky * g.dil_h));
+            mbar_expect_tx(full, stage_bytes);
+            if (gemm)
+                tma_load_2d(sa, tmap_a, full, c_off, m0);
+            else
+                tma_load_im2col_4d(sa, tmap_a, full, c_off, cw, chh, cn, (uint16_t)off_w, (uint16_t)off_h);
+            tma_load_2d(sb, tmap_b, full, k_off, n0);
+            k_off += kb;
+            c_off += kb;
+            if (++cb == c_blocks) {
+                cb = 0, c_off = 0;
+                off_w += dil_w;
+                if (++kx == kw_)
+                    kx = 0, off_w = 0, off_h += dil_h;
             }
-            tma_load_2d(sb, tmap_b, full, kbi * g.kb, nt * g.bn_mma);
-            if (++stage == (uint32_t)g.stages) {
+            if (++stage == stages) {
                 stage = 0;
                 phase ^= 1;
             }
@@ -447,6 +467,12 @@ __device__ __forceinline__ void mma_loop(const TcGeom &g, const StageGeom &sg, T
     uint32_t stage = 0, phase = 0;
     uint32_t acc_phase0 = 0, acc_phase1 = 0;
     int it = 0;
+    // descriptors of stage 0; a stage further on adds its byte offset >> 4 to the address field
+    // (the ring stays below the field's 256 KB range, so the sum never carries out of it)
+    const uint64_t desc_a0 = smem_desc(sg.smem_base, g.kb), desc_b0 = smem_desc(sg.smem_base + sg.a_stage_bytes, g.kb);
+    const uint32_t pitch16 = sg.stage_pitch >> 4, stages = g.stages, idesc = g.idesc;
+    const int kk = g.kb / 32; // 1, 2 or 4 MMAs of K = 32 per K block
+    const uint32_t bar_full0 = smem_u32(&sh.bar_full[0]), bar_empty0 = smem_u32(&sh.bar_empty[0]);
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, it++) {
         const int buf = it & 1;
         const uint32_t ph = buf ? acc_phase1 : acc_phase0;
@@ -459,16 +485,19 @@ __device__ __forceinline__ void mma_loop(const TcGeom &g, const StageGeom &sg, T
         fence_after_sync();
         const uint32_t tmem_d = tmem_base + buf * g.acc_stride;
         for (int kbi = 0; kbi < k_blocks; kbi++) {
-            if (!mbar_wait(smem_u32(&sh.bar_full[stage]), phase, &sh.abort_flag, status, ERR_MMA_FULL))
+            if (!mbar_wait(bar_full0 + stage * 8, phase, &sh.abort_flag, status, ERR_MMA_FULL))
                 return;
             fence_after_sync();
-            const uint32_t sa = sg.smem_base + stage * sg.stage_pitch, sb = sa + sg.a_stage_bytes;
-            const uint64_t da = smem_desc(sa, g.kb), db = smem_desc(sb, g.kb);
-            const int kk = g.kb / 32;
-            for (int k = 0; k < kk; k++)
-                mma_i8(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), g.idesc, (kbi | k) != 0);
-            mma_commit(smem_u32(&sh.bar_empty[stage])); // frees the stage when these MMAs retire
-            if (++stage == (uint32_t)g.stages) {
+            const uint64_t da = desc_a0 + (uint64_t)(stage * pitch16), db = desc_b0 + (uint64_t)(stage * pitch16);
+            mma_i8(tmem_d, da, db, idesc, kbi != 0);
+            if (kk > 1)
+                mma_i8(tmem_d, da + 2, db + 2, idesc, 1);
+            if (kk > 2) {
+                mma_i8(tmem_d, da + 4, db + 4, idesc, 1);
+                mma_i8(tmem_d, da + 6, db + 6, idesc, 1);
+            }
+            mma_commit(bar_empty0 + stage * 8); // frees the stage when these MMAs retire
+            if (++stage == stages) {
                 stage = 0;
                 phase ^= 1;
             }
