@@ -77,6 +77,7 @@ struct TcPlan {
     bool fast = false;
     FastEpi *f = nullptr;
     float4 *d_cst = nullptr;
+    uint8_t *d_addtab = nullptr;   // [256][256] residual-add table
     CUtensorMap tmap_y, tmap_y2, tmap_res;
     const void *y_ptr = nullptr, *y2_ptr = nullptr, *res_ptr = nullptr;
 };
@@ -291,6 +292,18 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&r)[16]) {
                  : "r"(taddr)
                  : "memory");
 }
+// Split form: the load is issued early; the registers hold the data only after tmem_ld_wait().
+// Both are volatile statements with a memory clobber, which keeps them in program order; every
+// use of the registers is written after the wait.
+__device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, int (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // The wait is part of the same statement so that no use of the result can be scheduled before it.
 __device__ __forceinline__ void tmem_ld1(uint32_t taddr, int &r) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];\ntcgen05.wait::ld.sync.aligned;"
@@ -303,17 +316,16 @@ __device__ __forceinline__ void tmem_ld1(uint32_t taddr, int &r) {
 
 // Extra constants of the fast epilogue (see epilogue_fast below).
 struct FastEpi {
-    uint32_t off_out, off_y2, off_res, off_cst, off_corr, off_lut2; // byte offsets from the aligned smem base
+    uint32_t off_out, off_y2, off_res, off_cst, off_corr, off_lut2, off_tab; // byte offsets from the aligned smem base
+    uint32_t res_pitch; // bytes between the residual staging buffers
     int lut_only; // the table maps the convolution's own output: only the mapped tile is stored
     int corr_pitch;     // bn + 1: distinct border classes fall into distinct banks
     int n_cls;
     int out_sw;         // swizzle span of the staging sub-tiles: 64, 32 or 0
-    int has_clamp;      // fused clamp on the real value is not (-inf, +inf)
     float so, rso, zo;  // output scale, its correctly rounded reciprocal, zero point
-    float lo, hi;       // fused clamp
-    float sr, zr_m;     // residual scale; 2^23 + residual zero point
-    float sa, rsa, za;  // add-output scale, its correctly rounded reciprocal, zero point
+    float qlo, qhi;     // the fused clamp's bounds after quantization, within [0, 255]
     const float4 *cst;  // [oc_pad] {mult, bias, bits(corr of class 0), bits(-zw)}
+    const uint8_t *add_table; // [256][256] quantized sum of (convolution output, residual), or null
 };
 
 struct TcArgs {
@@ -336,10 +348,11 @@ enum { ERR_PRODUCER = 101, ERR_MMA_FULL = 102, ERR_MMA_ACC = 103, ERR_EPILOGUE =
 constexpr int EPI_WARPS = 8;
 constexpr int TC_THREADS = 64 + 32 * EPI_WARPS;
 constexpr int MAX_STAGES = 8;
-constexpr float MAGIC = 12582912.0f; // 1.5 * 2^23: x + MAGIC holds the integer x in its low mantissa bits
+constexpr int RES_BUFS = 3; // residual sub-tiles in flight per epilogue warp: the fetch of tile i+3 starts when tile i is done
+constexpr float MAGIC = 8388608.0f; // 2^23: for 0 <= x <= 255, x + MAGIC has bits 0x4B0000qq with qq = rint(x)
 
 struct TcShared {
-    uint64_t bar_full[MAX_STAGES], bar_empty[MAX_STAGES], bar_acc_full[2], bar_acc_empty[2], bar_res[EPI_WARPS];
+    uint64_t bar_full[MAX_STAGES], bar_empty[MAX_STAGES], bar_acc_full[2], bar_acc_empty[2], bar_res[EPI_WARPS * RES_BUFS];
     uint32_t tmem_base_slot;
     volatile int abort_flag;
 };
@@ -371,7 +384,7 @@ __device__ __forceinline__ void tc_setup(const TcGeom &g, TcShared &sh, int warp
             mbar_init(smem_u32(&sh.bar_acc_full[b]), 1);
             mbar_init(smem_u32(&sh.bar_acc_empty[b]), EPI_WARPS);
         }
-        for (int w = 0; w < EPI_WARPS; w++)
+        for (int w = 0; w < EPI_WARPS * RES_BUFS; w++)
             mbar_init(smem_u32(&sh.bar_res[w]), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -698,7 +711,7 @@ __device__ __forceinline__ uint32_t stage_addr(uint32_t base, int row, int chunk
 }
 } // namespace dev
 
-template <bool RES, bool Y2, bool CLAMP>
+template <bool RES, bool Y2, bool XSUM>
 __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &sg, TcShared &sh, uint32_t tmem_base,
                                               const CUtensorMap *tmap_y, const CUtensorMap *tmap_y2,
                                               const CUtensorMap *tmap_res, int warp, int lane) {
@@ -718,23 +731,34 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
     const uint32_t s_out = sg.smem_base + f.off_out + sub, s_y2 = sg.smem_base + f.off_y2 + sub;
     const uint32_t s_res = sg.smem_base + f.off_res + sub;
     const uint32_t s_cst = sg.smem_base + f.off_cst, s_corr = sg.smem_base + f.off_corr;
-    const uint32_t s_lut2 = sg.smem_base + f.off_lut2;
-    const uint32_t bar_res = smem_u32(&sh.bar_res[ew]);
+    const uint32_t s_lut2 = sg.smem_base + f.off_lut2, s_tab = sg.smem_base + f.off_tab;
+    const uint32_t bar_res = smem_u32(&sh.bar_res[ew * RES_BUFS]);
     const bool multi_cls = f.n_cls > 1;
     const uint32_t res_bytes = 32u * hw;
     const int col_off = half * hw;
+    if (RES) {
+        // the add table: 64 KB, copied once per CTA
+        const uint4 *src = reinterpret_cast<const uint4 *>(f.add_table);
+        for (int i = et; i < 4096; i += 32 * EPI_WARPS)
+            sts128(s_tab + i * 16, __ldg(src + i));
+    }
     if (Y2) {
         if (et < 64)
             asm volatile("st.shared.u32 [%0], %1;" ::"r"(s_lut2 + et * 4),
                          "r"(reinterpret_cast<const uint32_t *>(a.p.y2_lut)[et])
                          : "memory");
     }
-    if (RES && lane == 0 && (int)blockIdx.x < total_tiles) {
-        const int mt = blockIdx.x % g.m_tiles, nt = blockIdx.x / g.m_tiles;
-        mbar_expect_tx(bar_res, res_bytes);
-        tma_load_2d(s_res, tmap_res, bar_res, nt * g.bn + col_off, mt * 128 + lane_group * 32);
+    // residual sub-tiles of this warp's next RES_BUFS tiles are always in flight
+    if (RES && lane == 0) {
+        int t = blockIdx.x;
+        for (int b = 0; b < RES_BUFS && t < total_tiles; b++, t += gridDim.x) {
+            mbar_expect_tx(bar_res + b * 8, res_bytes);
+            tma_load_2d(s_res + b * f.res_pitch, tmap_res, bar_res + b * 8, (t / g.m_tiles) * g.bn + col_off,
+                        (t % g.m_tiles) * 128 + lane_group * 32);
+        }
     }
-    uint32_t acc_phase0 = 0, acc_phase1 = 0, res_phase = 0;
+    uint32_t acc_phase0 = 0, acc_phase1 = 0, res_phase = 0; // res_phase: one parity bit per buffer
+    int rb = 0;                                             // residual buffer of the current tile
     int it = 0, cur_nt = -1;
     bool dead = false; // after a failed wait the warp only keeps the block-wide barriers company
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, it++) {
@@ -772,7 +796,7 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
         const uint32_t ph = buf ? acc_phase1 : acc_phase0;
         bool ok = mbar_wait(smem_u32(&sh.bar_acc_full[buf]), ph, &sh.abort_flag, a.status, ERR_EPILOGUE);
         if (RES && ok)
-            ok = mbar_wait(bar_res, res_phase, &sh.abort_flag, a.status, ERR_RESIDUAL);
+            ok = mbar_wait(bar_res + rb * 8, (res_phase >> rb) & 1, &sh.abort_flag, a.status, ERR_RESIDUAL);
         if (!ok) {
             dead = true;
             continue;
@@ -785,50 +809,45 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
             acc_phase1 ^= 1;
         else
             acc_phase0 ^= 1;
-        res_phase ^= 1;
+        res_phase ^= 1u << rb;
+        const uint32_t s_res_cur = s_res + rb * f.res_pitch;
         fence_after_sync();
         const uint32_t tbase = tmem_base + ((uint32_t)(lane_group * 32) << 16) + buf * g.acc_stride;
         int rsum = 0;
-        if (g.has_xsum) {
+        if (XSUM) {
             int xs;
             tmem_ld1(tbase + g.bn, xs);
             rsum = xs - a.cnt[cls] * g.x_zp;
         }
         const uint32_t corr_row = s_corr + (uint32_t)(cls * f.corr_pitch) * 4;
-        for (int cc = 0; cc < hw; cc += 16) {
+        auto chunk = [&](const int (&v)[16], const int cc) {
             const int c0 = col_off + cc; // column within the tile
-            int v[16];
-            __syncwarp();
-            tmem_ld16(tbase + c0, v);
             uint4 rw = make_uint4(0, 0, 0, 0);
             if (RES)
-                rw = lds128(stage_addr(s_res, lane, cc >> 4, hw, f.out_sw));
+                rw = lds128(stage_addr(s_res_cur, lane, cc >> 4, hw, f.out_sw));
             const uint32_t rwa[4] = {rw.x, rw.y, rw.z, rw.w};
             uint32_t bits[16];
 #pragma unroll
             for (int j = 0; j < 16; j++) {
                 const float4 k = lds128f(s_cst + (c0 + j) * 16); // {mult, bias, corr, -zw}
                 const int corr = multi_cls ? (int)lds32(corr_row + (c0 + j) * 4) : __float_as_int(k.z);
-                const int acc = v[j] + __float_as_int(k.w) * rsum - corr;
-                float x = __fadd_rn(__fmul_rn((float)acc, k.x), k.y);
-                if (CLAMP)
-                    x = clamp_dev(x, f.lo, f.hi);
+                int acc = v[j] - corr;
+                if (XSUM)
+                    acc += __float_as_int(k.w) * rsum;
+                const float x = __fadd_rn(__fmul_rn((float)acc, k.x), k.y);
                 // x / so, correctly rounded
                 float q0 = __fmul_rn(x, f.rso);
                 q0 = __fmaf_rn(__fmaf_rn(-q0, f.so, x), f.rso, q0);
-                float qf = fminf(fmaxf(rintf(__fadd_rn(q0, f.zo)), 0.f), 255.f);
+                // Quantization is monotone, so the fused clamp on the real value is a clamp of the
+                // quantized value to the quantized bounds; clamping before rounding to an integer is
+                // the same as after, and adding 2^23 rounds to nearest-even like rint.
+                const float t = fminf(fmaxf(__fadd_rn(q0, f.zo), f.qlo), f.qhi);
+                bits[j] = __float_as_uint(__fadd_rn(t, MAGIC)); // 0x4B0000qq: low byte = the quantized value
                 if (RES) {
-                    // dequantize both addends, add, requantise: same chain as the unfused binary add
-                    const float ya = __fmul_rn(__fadd_rn(qf, -f.zo), f.so);
-                    // byte j of the residual word as a float: 0x4B000000 | byte is 2^23 + byte
-                    const float rb = __uint_as_float(__byte_perm(rwa[j >> 2], 0x4B000000u, 0x7440 | (j & 3)));
-                    const float yb = __fmul_rn(__fadd_rn(rb, -f.zr_m), f.sr);
-                    const float sum = __fadd_rn(ya, yb);
-                    float p0 = __fmul_rn(sum, f.rsa);
-                    p0 = __fmaf_rn(__fmaf_rn(-p0, f.sa, sum), f.rsa, p0);
-                    qf = fminf(fmaxf(rintf(__fadd_rn(p0, f.za)), 0.f), 255.f);
+                    // dequantize both addends, add, requantise -- as a 64 K-entry table of all byte pairs
+                    const uint32_t idx = __byte_perm(rwa[j >> 2], bits[j], 0x6540 | (j & 3)); // (q << 8) | r
+                    bits[j] = lds8(s_tab + idx);
                 }
-                bits[j] = __float_as_uint(__fadd_rn(qf, MAGIC)); // low byte = the quantized value
             }
             uint4 o;
             o.x = __byte_perm(__byte_perm(bits[0], bits[1], 0x0040), __byte_perm(bits[2], bits[3], 0x0040), 0x5410);
@@ -837,17 +856,33 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
             o.w = __byte_perm(__byte_perm(bits[12], bits[13], 0x0040), __byte_perm(bits[14], bits[15], 0x0040), 0x5410);
             sts128(stage_addr(s_out, lane, cc >> 4, hw, f.out_sw), o);
             if (Y2) {
-                uint32_t w2[4];
-                const uint32_t ow_[4] = {o.x, o.y, o.z, o.w};
+                uint32_t b2[16];
 #pragma unroll
-                for (int k = 0; k < 4; k++) {
-                    const uint32_t b0 = lds8(s_lut2 + __byte_perm(ow_[k], 0, 0x4440));
-                    const uint32_t b1 = lds8(s_lut2 + __byte_perm(ow_[k], 0, 0x4441));
-                    const uint32_t b2 = lds8(s_lut2 + __byte_perm(ow_[k], 0, 0x4442));
-                    const uint32_t b3 = lds8(s_lut2 + __byte_perm(ow_[k], 0, 0x4443));
-                    w2[k] = __byte_perm(__byte_perm(b0, b1, 0x0040), __byte_perm(b2, b3, 0x0040), 0x5410);
-                }
-                sts128(stage_addr(s_y2, lane, cc >> 4, hw, f.out_sw), make_uint4(w2[0], w2[1], w2[2], w2[3]));
+                for (int j = 0; j < 16; j++)
+                    b2[j] = lds8(s_lut2 + (RES ? bits[j] : (bits[j] & 255u)));
+                uint4 o2;
+                o2.x = __byte_perm(__byte_perm(b2[0], b2[1], 0x0040), __byte_perm(b2[2], b2[3], 0x0040), 0x5410);
+                o2.y = __byte_perm(__byte_perm(b2[4], b2[5], 0x0040), __byte_perm(b2[6], b2[7], 0x0040), 0x5410);
+                o2.z = __byte_perm(__byte_perm(b2[8], b2[9], 0x0040), __byte_perm(b2[10], b2[11], 0x0040), 0x5410);
+                o2.w = __byte_perm(__byte_perm(b2[12], b2[13], 0x0040), __byte_perm(b2[14], b2[15], 0x0040), 0x5410);
+                sts128(stage_addr(s_y2, lane, cc >> 4, hw, f.out_sw), o2);
+            }
+        };
+        // the TMEM load of the next 16 columns is in flight while the current ones are requantised
+        int va[16], vb[16];
+        __syncwarp();
+        tmem_ld16_issue(tbase + col_off, va);
+        for (int cc = 0; cc < hw; cc += 32) {
+            tmem_ld_wait();
+            const bool more = cc + 16 < hw; // warp-uniform
+            if (more)
+                tmem_ld16_issue(tbase + col_off + cc + 16, vb);
+            chunk(va, cc);
+            if (more) {
+                tmem_ld_wait();
+                if (cc + 32 < hw)
+                    tmem_ld16_issue(tbase + col_off + cc + 32, va);
+                chunk(vb, cc + 16);
             }
         }
         // accumulator and residual sub-tile are consumed; staging sub-tiles are written
@@ -864,19 +899,21 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
                     tma_store_2d(tmap_y2, s_y2, oc0 + col_off, gy);
             }
             tma_store_commit();
-            const int next = tile + gridDim.x;
+            const int next = tile + RES_BUFS * (int)gridDim.x;
             if (RES && next < total_tiles) {
-                mbar_expect_tx(bar_res, res_bytes);
-                tma_load_2d(s_res, tmap_res, bar_res, (next / g.m_tiles) * g.bn + col_off,
+                mbar_expect_tx(bar_res + rb * 8, res_bytes);
+                tma_load_2d(s_res_cur, tmap_res, bar_res + rb * 8, (next / g.m_tiles) * g.bn + col_off,
                             (next % g.m_tiles) * 128 + lane_group * 32);
             }
         }
+        if (++rb == RES_BUFS)
+            rb = 0;
     }
     if (lane == 0)
         tma_store_wait_all();
 }
 
-template <bool RES, bool Y2, bool CLAMP>
+template <bool RES, bool Y2, bool XSUM>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 tc_conv_fast_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_y, const __grid_constant__ CUtensorMap tmap_y2,
@@ -895,7 +932,7 @@ tc_conv_fast_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (lane == 0)
             mma_loop(g, sg, sh, tmem_base, a.status);
     } else {
-        epilogue_fast<RES, Y2, CLAMP>(a, sg, sh, tmem_base, &tmap_y, &tmap_y2, &tmap_res, warp, lane);
+        epilogue_fast<RES, Y2, XSUM>(a, sg, sh, tmem_base, &tmap_y, &tmap_y2, &tmap_res, warp, lane);
     }
     tc_teardown(g, sh, warp, tmem_base);
 }
@@ -1042,9 +1079,11 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
         fe.off_out = off, off += tile_bytes;
         fe.off_y2 = off, off += (d.has_y2 || lut_only) ? tile_bytes : 0;
         fe.lut_only = lut_only ? 1 : 0;
-        fe.off_res = off, off += d.has_residual ? tile_bytes : 0;
+        fe.off_res = off, off += d.has_residual ? RES_BUFS * tile_bytes : 0;
+        fe.res_pitch = tile_bytes;
         fe.off_cst = off, off += (uint32_t)g.bn * 16;
         fe.off_lut2 = off, off += 256;
+        fe.off_tab = off, off += d.has_residual ? 65536 : 0;
         fe.off_corr = off;
         extras = off; // the per-class table is appended once the classes are known
         // each epilogue warp stages a 32-row x bn/2-byte sub-tile; its rows are the swizzle span
@@ -1164,14 +1203,35 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
         bool ok = true;
         fe.so = d.out_scale, fe.zo = (float)d.out_zp;
         fe.rso = rn_reciprocal(d.out_scale, &ok);
-        fe.lo = d.clamp_lo, fe.hi = d.clamp_hi;
-        fe.has_clamp = !(std::isinf(d.clamp_lo) && d.clamp_lo < 0 && std::isinf(d.clamp_hi) && d.clamp_hi > 0);
+        // quantized clamp bounds: q(clamp(v, lo, hi)) == clamp(q(v), q(lo), q(hi)) for the monotone q
+        auto quant = [&](float v) {
+            if (std::isinf(v))
+                return v < 0 ? 0.f : 255.f;
+            const float t = v / d.out_scale;
+            const float u = t + (float)d.out_zp;
+            return std::fmin(std::fmax(rintf(u), 0.f), 255.f);
+        };
+        fe.qlo = quant(d.clamp_lo), fe.qhi = quant(d.clamp_hi);
+        std::vector<uint8_t> addtab;
         if (d.has_residual) {
-            fe.sr = d.res_scale;
-            fe.zr_m = 8388608.0f + (float)d.res_zp;
-            fe.sa = d.add_out_scale, fe.za = (float)d.add_out_zp;
-            fe.rsa = rn_reciprocal(d.add_out_scale, &ok);
+            // every (convolution output byte, residual byte) pair through the unfused chain:
+            // dequantize both, add, divide by the output scale, add the zero point, round, clamp
             ok = ok && d.res_zp >= 0 && d.res_zp <= 255;
+            addtab.resize(65536);
+            const float so = d.out_scale, zo = (float)d.out_zp, sr = d.res_scale, zr = (float)d.res_zp;
+            const float sa = d.add_out_scale, za = (float)d.add_out_zp;
+            for (int qa = 0; qa < 256; qa++) {
+                const float da = (float)qa - zo;
+                const float ya = da * so;
+                for (int r = 0; r < 256; r++) {
+                    const float dr = (float)r - zr;
+                    const float yb = dr * sr;
+                    const float sum = ya + yb;
+                    const float p = sum / sa;
+                    const float u = p + za;
+                    addtab[qa * 256 + r] = (uint8_t)std::fmin(std::fmax(rintf(u), 0.f), 255.f);
+                }
+            }
         }
         if (!ok || std::isnan(d.clamp_lo) || std::isnan(d.clamp_hi))
             tp->fast = false; // scales outside the range the reciprocal division is proven for
@@ -1179,6 +1239,11 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
             NNCB_CUDA_TRY(cudaMalloc(&tp->d_cst, cst.size() * sizeof(float4)));
             NNCB_CUDA_TRY(cudaMemcpyAsync(tp->d_cst, cst.data(), cst.size() * sizeof(float4), cudaMemcpyHostToDevice, ctx->stream));
             fe.cst = tp->d_cst;
+            if (!addtab.empty()) {
+                NNCB_CUDA_TRY(cudaMalloc(&tp->d_addtab, addtab.size()));
+                NNCB_CUDA_TRY(cudaMemcpyAsync(tp->d_addtab, addtab.data(), addtab.size(), cudaMemcpyHostToDevice, ctx->stream));
+                fe.add_table = tp->d_addtab;
+            }
         }
     }
     NNCB_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
@@ -1197,7 +1262,7 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
     const uint32_t ring = (uint32_t)stages * (a_stage + b_pitch);
     if (tp->fast) {
         fe.off_out += ring, fe.off_y2 += ring, fe.off_res += ring, fe.off_cst += ring;
-        fe.off_lut2 += ring, fe.off_corr += ring;
+        fe.off_lut2 += ring, fe.off_corr += ring, fe.off_tab += ring;
     }
     // More than half of an SM's shared memory, so exactly one CTA (and one TMEM allocation) per SM.
     tp->smem_bytes = (size_t)ring + extras + 1024;
@@ -1227,6 +1292,7 @@ void tc_conv_destroy(nncb_qconv2d *cv) {
     cudaFree(tp->d_ycls);
     cudaFree(tp->d_xcls);
     cudaFree(tp->d_cst);
+    cudaFree(tp->d_addtab);
     delete tp->f;
     delete tp;
     cv->tc = nullptr;
@@ -1291,7 +1357,7 @@ int tc_conv_run(nncb_context *ctx, nncb_qconv2d *cv, const uint8_t *x, const uin
             tp->res_ptr = res;
         }
         const CUtensorMap &my2 = y2 ? tp->tmap_y2 : tp->tmap_y, &mres = res ? tp->tmap_res : tp->tmap_y;
-        const int variant = (res ? 4 : 0) | (y2 ? 2 : 0) | (tp->f->has_clamp ? 1 : 0);
+        const int variant = (res ? 4 : 0) | (y2 ? 2 : 0) | (tp->g.has_xsum ? 1 : 0);
 #define NNCB_LAUNCH_FAST(R, Y, C)                                                                                     \
     tc_conv_fast_kernel<R, Y, C><<<grid, TC_THREADS, tp->smem_bytes, ctx->stream>>>(tp->tmap_a, tp->tmap_b, tp->tmap_y, \
                                                                                    my2, mres, a)
