@@ -26,6 +26,7 @@
 //   all roles leave their loops, free tensor memory and return.
 #include "qconv.cuh"
 #include <cmath>
+#include <type_traits>
 #include <vector>
 
 namespace nncb {
@@ -57,6 +58,7 @@ struct TcGeom {
     int acc_stride;     // TMEM columns between the two accumulators
     uint32_t idesc;
     int f32_out;
+    int acc_arrivals;   // epilogue warps that release an accumulator buffer
 };
 
 struct FastEpi;
@@ -227,6 +229,9 @@ __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volat
     for (uint32_t it = 1;; it++) {
         if (mbar_try(bar, parity))
             return true;
+        // a role that is ahead of the others backs off instead of spending issue slots on probes
+        if (it > 4)
+            __nanosleep(it > 32 ? 256 : 64);
         if ((it & 63) == 0) {
             if (*abort_flag)
                 return false;
@@ -321,7 +326,8 @@ struct FastEpi {
     int lut_only; // the table maps the convolution's own output: only the mapped tile is stored
     int corr_pitch;     // bn + 1: distinct border classes fall into distinct banks
     int n_cls;
-    int out_sw;         // swizzle span of the staging sub-tiles: 64, 32 or 0
+    int out_sw;         // swizzle span of the staging sub-tiles: 32 or 0
+    int ncg, wcols;     // column groups per tile (4 or 2) and columns per epilogue warp (32 or 16)
     float so, rso, zo;  // output scale, its correctly rounded reciprocal, zero point
     float qlo, qhi;     // the fused clamp's bounds after quantization, within [0, 255]
     const float4 *cst;  // [oc_pad] {mult, bias, bits(corr of class 0), bits(-zw)}
@@ -345,7 +351,7 @@ struct TcArgs {
 
 enum { ERR_PRODUCER = 101, ERR_MMA_FULL = 102, ERR_MMA_ACC = 103, ERR_EPILOGUE = 104, ERR_RESIDUAL = 105 };
 
-constexpr int EPI_WARPS = 8;
+constexpr int EPI_WARPS = 16; // four per TMEM lane quadrant: enough warps per scheduler to hide TMEM and shared-memory latency
 constexpr int TC_THREADS = 64 + 32 * EPI_WARPS;
 constexpr int MAX_STAGES = 8;
 constexpr int RES_BUFS = 3; // residual sub-tiles in flight per epilogue warp: the fetch of tile i+3 starts when tile i is done
@@ -382,7 +388,7 @@ __device__ __forceinline__ void tc_setup(const TcGeom &g, TcShared &sh, int warp
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(smem_u32(&sh.bar_acc_full[b]), 1);
-            mbar_init(smem_u32(&sh.bar_acc_empty[b]), EPI_WARPS);
+            mbar_init(smem_u32(&sh.bar_acc_empty[b]), g.acc_arrivals);
         }
         for (int w = 0; w < EPI_WARPS * RES_BUFS; w++)
             mbar_init(smem_u32(&sh.bar_res[w]), 1);
@@ -529,7 +535,7 @@ __device__ __forceinline__ void epilogue_generic(const TcArgs &a, TcShared &sh, 
     const int total_tiles = g.m_tiles * g.n_tiles;
     const int ew = warp - 2;
     const int lane_group = warp & 3; // TMEM lanes 32*lane_group .. +31 are this warp's
-    const int half = ew >> 2;        // two warps share a lane group and alternate 16-column chunks
+    const int grp = ew >> 2;         // the warps of a lane group take 16-column chunks in turn
     const int row = lane_group * 32 + lane;
     uint32_t acc_phase0 = 0, acc_phase1 = 0;
     int it = 0;
@@ -560,7 +566,7 @@ __device__ __forceinline__ void epilogue_generic(const TcArgs &a, TcShared &sh, 
         }
         const int32_t *corr = a.corr + (size_t)cls * a.oc_pad;
         const int oc0 = nt * g.bn;
-        for (int c0 = half * 16; c0 < g.bn; c0 += 32) {
+        for (int c0 = grp * 16; c0 < g.bn; c0 += 16 * (EPI_WARPS / 4)) {
             int v[16];
             __syncwarp();
             tmem_ld16(tbase + c0, v);
@@ -722,9 +728,10 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
     const int ew = warp - 2;
     const int et = ew * 32 + lane;   // index among the epilogue threads
     const int lane_group = warp & 3; // TMEM lanes 32*lane_group .. +31 are this warp's
-    const int half = ew >> 2;        // which half of the tile's columns this warp owns
+    const int grp = ew >> 2;         // which group of the tile's columns this warp owns
+    const bool active = grp < f.ncg; // narrow tiles leave the last warps without columns
     const int row = lane_group * 32 + lane;
-    const int hw = g.bn >> 1;        // bytes per row of this warp's sub-tile (32 rows x hw columns)
+    const int hw = f.wcols;          // bytes per row of this warp's sub-tile (32 rows x hw columns)
     // Every warp stages, stores and prefetches its own 32 x hw sub-tile: no block-wide barrier in
     // the steady state.
     const uint32_t sub = (uint32_t)ew * 32u * hw;
@@ -735,7 +742,7 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
     const uint32_t bar_res = smem_u32(&sh.bar_res[ew * RES_BUFS]);
     const bool multi_cls = f.n_cls > 1;
     const uint32_t res_bytes = 32u * hw;
-    const int col_off = half * hw;
+    const int col_off = grp * hw;
     if (RES) {
         // the add table: 64 KB, copied once per CTA
         const uint4 *src = reinterpret_cast<const uint4 *>(f.add_table);
@@ -749,7 +756,7 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
                          : "memory");
     }
     // residual sub-tiles of this warp's next RES_BUFS tiles are always in flight
-    if (RES && lane == 0) {
+    if (RES && lane == 0 && active) {
         int t = blockIdx.x;
         for (int b = 0; b < RES_BUFS && t < total_tiles; b++, t += gridDim.x) {
             mbar_expect_tx(bar_res + b * 8, res_bytes);
@@ -786,7 +793,7 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
             cur_nt = nt;
             epi_bar_sync();
         }
-        if (dead)
+        if (dead || !active)
             continue;
         int cls = 0;
         if (g.mode == MODE_IM2COL && row_ok) {
@@ -820,7 +827,8 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
             rsum = xs - a.cnt[cls] * g.x_zp;
         }
         const uint32_t corr_row = s_corr + (uint32_t)(cls * f.corr_pitch) * 4;
-        auto chunk = [&](const int (&v)[16], const int cc) {
+        auto chunk = [&](const int (&v)[16], const int cc, auto multi_tag) {
+            constexpr bool MULTI = decltype(multi_tag)::value;
             const int c0 = col_off + cc; // column within the tile
             uint4 rw = make_uint4(0, 0, 0, 0);
             if (RES)
@@ -830,7 +838,7 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
 #pragma unroll
             for (int j = 0; j < 16; j++) {
                 const float4 k = lds128f(s_cst + (c0 + j) * 16); // {mult, bias, corr, -zw}
-                const int corr = multi_cls ? (int)lds32(corr_row + (c0 + j) * 4) : __float_as_int(k.z);
+                const int corr = MULTI ? (int)lds32(corr_row + (c0 + j) * 4) : __float_as_int(k.z);
                 int acc = v[j] - corr;
                 if (XSUM)
                     acc += __float_as_int(k.w) * rsum;
@@ -845,7 +853,10 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
                 bits[j] = __float_as_uint(__fadd_rn(t, MAGIC)); // 0x4B0000qq: low byte = the quantized value
                 if (RES) {
                     // dequantize both addends, add, requantise -- as a 64 K-entry table of all byte pairs
-                    const uint32_t idx = __byte_perm(rwa[j >> 2], bits[j], 0x6540 | (j & 3)); // (q << 8) | r
+                    // index (q << 8) | r, with q's low bits folded into the bank bits of r: pixels of one
+                    // channel have similar q and similar r, which would otherwise share few banks
+                    uint32_t idx = __byte_perm(rwa[j >> 2], bits[j], 0x6540 | (j & 3));
+                    idx ^= (idx >> 6) & 0x7Cu;
                     bits[j] = lds8(s_tab + idx);
                 }
             }
@@ -869,22 +880,28 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
             }
         };
         // the TMEM load of the next 16 columns is in flight while the current ones are requantised
-        int va[16], vb[16];
-        __syncwarp();
-        tmem_ld16_issue(tbase + col_off, va);
-        for (int cc = 0; cc < hw; cc += 32) {
-            tmem_ld_wait();
-            const bool more = cc + 16 < hw; // warp-uniform
-            if (more)
-                tmem_ld16_issue(tbase + col_off + cc + 16, vb);
-            chunk(va, cc);
-            if (more) {
+        auto columns = [&](auto multi_tag) {
+            int va[16], vb[16];
+            __syncwarp();
+            tmem_ld16_issue(tbase + col_off, va);
+            for (int cc = 0; cc < hw; cc += 32) {
                 tmem_ld_wait();
-                if (cc + 32 < hw)
-                    tmem_ld16_issue(tbase + col_off + cc + 32, va);
-                chunk(vb, cc + 16);
+                const bool more = cc + 16 < hw; // warp-uniform
+                if (more)
+                    tmem_ld16_issue(tbase + col_off + cc + 16, vb);
+                chunk(va, cc, multi_tag);
+                if (more) {
+                    tmem_ld_wait();
+                    if (cc + 32 < hw)
+                        tmem_ld16_issue(tbase + col_off + cc + 32, va);
+                    chunk(vb, cc + 16, multi_tag);
+                }
             }
-        }
+        };
+        if (multi_cls)
+            columns(std::true_type{});
+        else
+            columns(std::false_type{});
         // accumulator and residual sub-tile are consumed; staging sub-tiles are written
         fence_before_sync();
         fence_async_smem();
@@ -1086,8 +1103,10 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
         fe.off_tab = off, off += d.has_residual ? 65536 : 0;
         fe.off_corr = off;
         extras = off; // the per-class table is appended once the classes are known
-        // each epilogue warp stages a 32-row x bn/2-byte sub-tile; its rows are the swizzle span
-        fe.out_sw = g.bn == 128 ? 64 : (g.bn == 64 ? 32 : 0);
+        // each epilogue warp stages a 32-row x wcols-byte sub-tile; 32-byte rows are the swizzle span
+        fe.ncg = g.bn >= 64 ? 4 : 2;
+        fe.wcols = g.bn / fe.ncg;
+        fe.out_sw = fe.wcols == 32 ? 32 : 0;
         tp->fast = true;
     }
     // ---- weights: [n_tiles][bn_mma][K], K ordered (ky, kx, c) = the OHWI row as given ----
@@ -1229,7 +1248,7 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
                     const float sum = ya + yb;
                     const float p = sum / sa;
                     const float u = p + za;
-                    addtab[qa * 256 + r] = (uint8_t)std::fmin(std::fmax(rintf(u), 0.f), 255.f);
+                    addtab[qa * 256 + (r ^ ((qa << 2) & 0x7C))] = (uint8_t)std::fmin(std::fmax(rintf(u), 0.f), 255.f);
                 }
             }
         }
@@ -1259,6 +1278,7 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
     if (stages < 2)
         return fail(-ENOSYS, "tcgen05 conv: tile does not fit shared memory");
     g.stages = stages;
+    g.acc_arrivals = tp->fast ? 4 * fe.ncg : EPI_WARPS;
     const uint32_t ring = (uint32_t)stages * (a_stage + b_pitch);
     if (tp->fast) {
         fe.off_out += ring, fe.off_y2 += ring, fe.off_res += ring, fe.off_cst += ring;
@@ -1302,7 +1322,7 @@ static int make_tmap_out(CUtensorMap *map, const TcPlan *tp, const void *ptr) {
     const TcGeom &g = tp->g;
     cuuint64_t dims[2] = {(cuuint64_t)g.oc, (cuuint64_t)g.m_total};
     cuuint64_t strides[1] = {(cuuint64_t)g.oc};
-    cuuint32_t box[2] = {(cuuint32_t)(g.bn / 2), 32}; // one epilogue warp's sub-tile
+    cuuint32_t box[2] = {(cuuint32_t)tp->f->wcols, 32}; // one epilogue warp's sub-tile
     cuuint32_t estr[2] = {1, 1};
     const int sw = tp->f->out_sw;
     CUtensorMapSwizzle swz = sw == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
