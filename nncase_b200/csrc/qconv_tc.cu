@@ -34,7 +34,11 @@ namespace nncb {
 // ------------------------------------------------------------------------------------------------
 // plan
 // ------------------------------------------------------------------------------------------------
-enum { MODE_GEMM = 0, MODE_IM2COL = 1 };
+// MODE_ROWS: an unpadded stride-1 convolution over few channels whose kw taps of one kernel row are
+// contiguous in memory (kw * c is 32, 64 or 128 bytes): a plain tiled tensor map whose pixel stride
+// is smaller than its row extent delivers the overlapping windows, one K block per kernel row, and
+// the M tile is a bx x by patch of output pixels instead of 128 consecutive ones.
+enum { MODE_GEMM = 0, MODE_IM2COL = 1, MODE_ROWS = 2 };
 
 struct TcGeom {
     int mode;
@@ -59,6 +63,7 @@ struct TcGeom {
     uint32_t idesc;
     int f32_out;
     int acc_arrivals;   // epilogue warps that release an accumulator buffer
+    int bx_log2, tiles_x, tiles_y; // MODE_ROWS: patch width 2^bx_log2 (height 128 >> bx_log2), patches per image
 };
 
 struct FastEpi;
@@ -119,6 +124,13 @@ static CUtensorMapSwizzle swizzle_for(int kb) {
     return kb == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (kb == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
 }
 
+static bool rows_mode_applies(const nncb_conv2d_desc &d) {
+    const int rb = d.kw * d.c;
+    return d.groups == 1 && d.kw > 1 && d.stride_h == 1 && d.stride_w == 1 && d.dil_h == 1 && d.dil_w == 1 &&
+           d.pad_t == 0 && d.pad_b == 0 && d.pad_l == 0 && d.pad_r == 0 && d.c % 16 == 0 &&
+           (rb == 32 || rb == 64 || rb == 128) && d.h >= d.kh && d.w >= d.kw;
+}
+
 bool tc_conv_supported(const nncb_conv2d_desc &d, std::string *why) {
     auto no = [&](const char *m) {
         if (why)
@@ -127,7 +139,7 @@ bool tc_conv_supported(const nncb_conv2d_desc &d, std::string *why) {
     };
     if (d.groups != 1)
         return no("grouped convolution");
-    if (d.c % 32 != 0)
+    if (d.c % 32 != 0 && !rows_mode_applies(d))
         return no("input channels not a multiple of 32");
     if ((size_t)d.kh * d.kw * d.c > (1u << 20))
         return no("K too large");
@@ -158,7 +170,16 @@ bool tc_conv_supported(const nncb_conv2d_desc &d, std::string *why) {
 static int make_tmap_a(TcPlan *tp, const nncb_conv2d_desc &d, const void *x) {
     const TcGeom &g = tp->g;
     CUresult r;
-    if (g.mode == MODE_GEMM) {
+    if (g.mode == MODE_ROWS) {
+        // dimension 1 steps one pixel (c bytes) while dimension 0 spans kw pixels: overlapping windows
+        cuuint64_t dims[4] = {(cuuint64_t)(d.kw * d.c), (cuuint64_t)g.ow, (cuuint64_t)d.h, (cuuint64_t)d.n};
+        cuuint64_t strides[3] = {(cuuint64_t)d.c, (cuuint64_t)d.c * d.w, (cuuint64_t)d.c * d.w * d.h};
+        cuuint32_t box[4] = {(cuuint32_t)g.kb, 1u << g.bx_log2, 128u >> g.bx_log2, 1};
+        cuuint32_t estr[4] = {1, 1, 1, 1};
+        r = g_encode_tiled(&tp->tmap_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void *>(x), dims, strides, box,
+                           estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(g.kb), CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else if (g.mode == MODE_GEMM) {
         cuuint64_t dims[2] = {(cuuint64_t)d.c, (cuuint64_t)g.m_total};
         cuuint64_t strides[1] = {(cuuint64_t)d.c};
         cuuint32_t box[2] = {(cuuint32_t)g.kb, 128};
@@ -253,6 +274,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2,
+                                            int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
                  : "memory");
 }
 __device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c, int w,
@@ -429,7 +456,7 @@ __device__ __forceinline__ void producer_loop(const TcGeom &g, const StageGeom &
     using namespace dev;
     const int k_blocks = g.taps * g.c_blocks;
     const int total_tiles = g.m_tiles * g.n_tiles;
-    const bool gemm = g.mode == MODE_GEMM;
+    const bool gemm = g.mode == MODE_GEMM, rows = g.mode == MODE_ROWS;
     const int kb = g.kb, c_blocks = g.c_blocks, kw_ = g.kw;
     const uint32_t dil_w = g.dil_w, dil_h = g.dil_h, stages = g.stages;
     const uint32_t stage_bytes = sg.a_stage_bytes + sg.b_stage_bytes;
@@ -439,7 +466,12 @@ __device__ __forceinline__ void producer_loop(const TcGeom &g, const StageGeom &
         const int mt = tile % g.m_tiles, nt = tile / g.m_tiles;
         const int m0 = mt * 128, n0 = nt * g.bn_mma;
         int cw = 0, chh = 0, cn = 0;
-        if (!gemm) {
+        if (rows) {
+            const int txi = mt % g.tiles_x, r = mt / g.tiles_x;
+            cw = txi << g.bx_log2;
+            chh = (r % g.tiles_y) * (128 >> g.bx_log2);
+            cn = r / g.tiles_y;
+        } else if (!gemm) {
             const int q = m0 % g.ow, pp = (m0 / g.ow) % g.oh;
             cn = m0 / (g.ow * g.oh);
             cw = q * g.stride_w - g.pad_l;
@@ -458,6 +490,8 @@ __device__ __forceinline__ void producer_loop(const TcGeom &g, const StageGeom &
             mbar_expect_tx(full, stage_bytes);
             if (gemm)
                 tma_load_2d(sa, tmap_a, full, c_off, m0);
+            else if (rows)
+                tma_load_4d(sa, tmap_a, full, 0, cw, chh + (int)off_h, cn); // kw = 1 here: off_h counts kernel rows
             else
                 tma_load_im2col_4d(sa, tmap_a, full, c_off, cw, chh, cn, (uint16_t)off_w, (uint16_t)off_h);
             tma_load_2d(sb, tmap_b, full, k_off, n0);
@@ -542,8 +576,16 @@ __device__ __forceinline__ void epilogue_generic(const TcArgs &a, TcShared &sh, 
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, it++) {
         const int buf = it & 1;
         const int mt = tile % g.m_tiles, nt = tile / g.m_tiles;
-        const int m = mt * 128 + row;
-        const bool row_ok = m < g.m_total;
+        int m = mt * 128 + row;
+        bool row_ok = m < g.m_total;
+        if (g.mode == MODE_ROWS) {
+            // the tile is a patch of output pixels: row -> (patch row, patch column)
+            const int txi = mt % g.tiles_x, r2 = mt / g.tiles_x;
+            const int ox = (txi << g.bx_log2) + (row & ((1 << g.bx_log2) - 1));
+            const int oy = (r2 % g.tiles_y) * (128 >> g.bx_log2) + (row >> g.bx_log2);
+            row_ok = ox < g.ow && oy < g.oh;
+            m = ((r2 / g.tiles_y) * g.oh + oy) * g.ow + ox;
+        }
         int cls = 0; // border class of this output pixel
         if (g.mode == MODE_IM2COL && row_ok) {
             const int ox = m % g.ow, oy = (m / g.ow) % g.oh;
@@ -682,6 +724,11 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t sr
                  "r"(x), "r"(y)
                  : "memory");
 }
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap *map, uint32_t src, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(map),
+                 "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
@@ -743,6 +790,34 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
     const bool multi_cls = f.n_cls > 1;
     const uint32_t res_bytes = 32u * hw;
     const int col_off = grp * hw;
+    const bool rows = g.mode == MODE_ROWS;
+    // Tensor-map coordinates of this warp's 32-row sub-tile of tile (mt, nt): 2-D {channel, pixel} in
+    // general, 4-D {channel, x, y, image} when the tile is a patch of pixels. False when the sub-tile
+    // lies wholly outside the output.
+    auto sub_coords = [&](int mt, int nt, int (&c)[4]) {
+        c[0] = nt * g.bn + col_off;
+        if (!rows) {
+            c[1] = mt * 128 + lane_group * 32;
+            return c[1] < g.m_total;
+        }
+        const int txi = mt % g.tiles_x, r2 = mt / g.tiles_x, r0 = lane_group * 32;
+        c[1] = (txi << g.bx_log2) + (r0 & ((1 << g.bx_log2) - 1));
+        c[2] = (r2 % g.tiles_y) * (128 >> g.bx_log2) + (r0 >> g.bx_log2);
+        c[3] = r2 / g.tiles_y;
+        return c[1] < g.ow && c[2] < g.oh;
+    };
+    auto load_sub = [&](uint32_t dst, const CUtensorMap *map, uint32_t bar, const int (&c)[4]) {
+        if (rows)
+            tma_load_4d(dst, map, bar, c[0], c[1], c[2], c[3]);
+        else
+            tma_load_2d(dst, map, bar, c[0], c[1]);
+    };
+    auto store_sub = [&](const CUtensorMap *map, uint32_t src, const int (&c)[4]) {
+        if (rows)
+            tma_store_4d(map, src, c[0], c[1], c[2], c[3]);
+        else
+            tma_store_2d(map, src, c[0], c[1]);
+    };
     if (RES) {
         // the add table: 64 KB, copied once per CTA
         const uint4 *src = reinterpret_cast<const uint4 *>(f.add_table);
@@ -759,9 +834,10 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
     if (RES && lane == 0 && active) {
         int t = blockIdx.x;
         for (int b = 0; b < RES_BUFS && t < total_tiles; b++, t += gridDim.x) {
+            int c[4];
+            sub_coords(t % g.m_tiles, t / g.m_tiles, c); // a load outside the tensor still completes, with fill
             mbar_expect_tx(bar_res + b * 8, res_bytes);
-            tma_load_2d(s_res + b * f.res_pitch, tmap_res, bar_res + b * 8, (t / g.m_tiles) * g.bn + col_off,
-                        (t % g.m_tiles) * 128 + lane_group * 32);
+            load_sub(s_res + b * f.res_pitch, tmap_res, bar_res + b * 8, c);
         }
     }
     uint32_t acc_phase0 = 0, acc_phase1 = 0, res_phase = 0; // res_phase: one parity bit per buffer
@@ -908,19 +984,19 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
         __syncwarp();
         if (lane == 0) {
             mbar_arrive(smem_u32(&sh.bar_acc_empty[buf]));
-            const int gy = mt * 128 + lane_group * 32;
-            if (gy < g.m_total) {
+            int c[4];
+            if (sub_coords(mt, nt, c)) {
                 if (!Y2 || !f.lut_only)
-                    tma_store_2d(tmap_y, s_out, oc0 + col_off, gy);
+                    store_sub(tmap_y, s_out, c);
                 if (Y2)
-                    tma_store_2d(tmap_y2, s_y2, oc0 + col_off, gy);
+                    store_sub(tmap_y2, s_y2, c);
             }
             tma_store_commit();
             const int next = tile + RES_BUFS * (int)gridDim.x;
             if (RES && next < total_tiles) {
+                sub_coords(next % g.m_tiles, next / g.m_tiles, c);
                 mbar_expect_tx(bar_res + rb * 8, res_bytes);
-                tma_load_2d(s_res_cur, tmap_res, bar_res + rb * 8, (next / g.m_tiles) * g.bn + col_off,
-                            (next % g.m_tiles) * 128 + lane_group * 32);
+                load_sub(s_res_cur, tmap_res, bar_res + rb * 8, c);
             }
         }
         if (++rb == RES_BUFS)
@@ -1049,7 +1125,7 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
     TcGeom &g = tp->g;
     const bool gemm = d.kh == 1 && d.kw == 1 && d.stride_h == 1 && d.stride_w == 1 && d.pad_t == 0 && d.pad_b == 0 &&
                       d.pad_l == 0 && d.pad_r == 0;
-    g.mode = gemm ? MODE_GEMM : MODE_IM2COL;
+    g.mode = gemm ? MODE_GEMM : (rows_mode_applies(d) ? MODE_ROWS : MODE_IM2COL);
     g.oh = cv->oh, g.ow = cv->ow;
     g.m_total = d.n * cv->oh * cv->ow;
     g.oc = d.oc;
@@ -1065,6 +1141,23 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
     g.c_blocks = d.c / g.kb;
     g.taps = d.kh * d.kw;
     g.kw = d.kw;
+    if (g.mode == MODE_ROWS) {
+        // patch shape: the one that covers the output with the fewest wasted rows; wider on a tie
+        long long best = -1;
+        for (int l = 7; l >= 3; l--) {
+            const int bx = 1 << l, by = 128 >> l;
+            const long long area = (long long)((g.ow + bx - 1) / bx) * bx * ((g.oh + by - 1) / by) * by;
+            if (best < 0 || area < best)
+                best = area, g.bx_log2 = l;
+        }
+        const int bx = 1 << g.bx_log2, by = 128 >> g.bx_log2;
+        g.tiles_x = (g.ow + bx - 1) / bx, g.tiles_y = (g.oh + by - 1) / by;
+        g.m_tiles = d.n * g.tiles_x * g.tiles_y;
+        g.kb = d.kw * d.c; // one K block per kernel row
+        g.c_blocks = 1;
+        g.taps = d.kh;
+        g.kw = 1;
+    }
     g.stride_h = d.stride_h, g.stride_w = d.stride_w, g.pad_t = d.pad_t, g.pad_l = d.pad_l;
     g.dil_h = d.dil_h, g.dil_w = d.dil_w;
     g.x_zp = d.x_zp;
@@ -1170,14 +1263,15 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
     const int n_cls = (int)(yr.size() * xr.size());
     tp->oc_pad = g.n_tiles * g.bn;
     // per-tap weight sums, then per-class sums
-    std::vector<int64_t> tapsum((size_t)d.oc * g.taps, 0);
+    const int all_taps = d.kh * d.kw; // g.taps counts K blocks per channel block, which MODE_ROWS merges
+    std::vector<int64_t> tapsum((size_t)d.oc * all_taps, 0);
     for (int oc = 0; oc < d.oc; oc++)
-        for (int t = 0; t < g.taps; t++) {
+        for (int t = 0; t < all_taps; t++) {
             int64_t s = 0;
-            const uint8_t *p = wsrc + ((size_t)oc * g.taps + t) * d.c;
+            const uint8_t *p = wsrc + ((size_t)oc * all_taps + t) * d.c;
             for (int c = 0; c < d.c; c++)
                 s += d.w_signed ? (int)(int8_t)p[c] : (int)p[c];
-            tapsum[(size_t)oc * g.taps + t] = s;
+            tapsum[(size_t)oc * all_taps + t] = s;
         }
     std::vector<int32_t> corr((size_t)n_cls * tp->oc_pad, 0), cnt(n_cls, 0);
     for (size_t yc = 0; yc < yr.size(); yc++)
@@ -1188,7 +1282,7 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
                 int64_t s = 0;
                 for (int ky = yr[yc].first; ky < yr[yc].second; ky++)
                     for (int kx = xr[xc].first; kx < xr[xc].second; kx++)
-                        s += tapsum[(size_t)oc * g.taps + ky * d.kw + kx];
+                        s += tapsum[(size_t)oc * all_taps + ky * d.kw + kx];
                 corr[(size_t)cls * tp->oc_pad + oc] = (int32_t)(s * d.x_zp);
             }
         }
@@ -1320,17 +1414,31 @@ void tc_conv_destroy(nncb_qconv2d *cv) {
 
 static int make_tmap_out(CUtensorMap *map, const TcPlan *tp, const void *ptr) {
     const TcGeom &g = tp->g;
-    cuuint64_t dims[2] = {(cuuint64_t)g.oc, (cuuint64_t)g.m_total};
-    cuuint64_t strides[1] = {(cuuint64_t)g.oc};
-    cuuint32_t box[2] = {(cuuint32_t)tp->f->wcols, 32}; // one epilogue warp's sub-tile
-    cuuint32_t estr[2] = {1, 1};
     const int sw = tp->f->out_sw;
     CUtensorMapSwizzle swz = sw == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
                                        : (sw == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
                                                    : (sw == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE));
-    CUresult r = g_encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(ptr), dims, strides, box, estr,
-                                CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r;
+    if (g.mode == MODE_ROWS) {
+        // a warp's 32 rows are sx x sy pixels of the patch
+        const int bx = 1 << g.bx_log2, sx = bx < 32 ? bx : 32;
+        const int n_img = g.m_total / (g.oh * g.ow);
+        cuuint64_t dims[4] = {(cuuint64_t)g.oc, (cuuint64_t)g.ow, (cuuint64_t)g.oh, (cuuint64_t)n_img};
+        cuuint64_t strides[3] = {(cuuint64_t)g.oc, (cuuint64_t)g.oc * g.ow, (cuuint64_t)g.oc * g.ow * g.oh};
+        cuuint32_t box[4] = {(cuuint32_t)tp->f->wcols, (cuuint32_t)sx, (cuuint32_t)(32 / sx), 1};
+        cuuint32_t estr[4] = {1, 1, 1, 1};
+        r = g_encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void *>(ptr), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else {
+        cuuint64_t dims[2] = {(cuuint64_t)g.oc, (cuuint64_t)g.m_total};
+        cuuint64_t strides[1] = {(cuuint64_t)g.oc};
+        cuuint32_t box[2] = {(cuuint32_t)tp->f->wcols, 32}; // one epilogue warp's sub-tile
+        cuuint32_t estr[2] = {1, 1};
+        r = g_encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(ptr), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
     if (r != CUDA_SUCCESS)
         return fail(-EIO, "encoding an output tensor map failed (CUresult %d)", (int)r);
     return 0;

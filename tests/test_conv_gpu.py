@@ -196,3 +196,40 @@ def test_bad_arguments_are_rejected(ctx):
     with pytest.raises(NncbError) as e:  # empty output
         ctx.conv2d_plan((1, 2, 2, 4), w, None, np.ones(8), np.zeros(8), 0, QuantParam(0, 1.0))
     assert e.value.code == -22
+
+
+ROWS_CASES = [
+    # n, h, w, c, oc, kh, kw: unpadded stride-1 convolutions whose kernel row is 32, 64 or 128 contiguous bytes
+    (2, 19, 19, 16, 64, 4, 4), (1, 115, 115, 16, 64, 4, 4), (2, 15, 16, 32, 32, 3, 2), (1, 9, 21, 16, 48, 2, 2),
+    (3, 10, 37, 32, 128, 3, 4), (1, 6, 6, 16, 24, 4, 4), (1, 40, 11, 64, 16, 5, 2),
+]
+
+
+@pytest.mark.parametrize("cfg", ROWS_CASES)
+@pytest.mark.parametrize("wmode", ["u8_asym", "i8_sym"])
+def test_tc_conv_kernel_rows(ctx, qo, cfg, wmode):
+    """The merged-kernel-row form (one K block per kernel row, pixel-patch tiles): patch shapes that
+    divide the output and ones that overhang it, both epilogues (oc = 24 takes the general one)."""
+    n, h, w, c, oc, kh, kw = cfg
+    case = make_case(51, n, h, w, c, oc, kh, kw, 1, wmode == "i8_sym", sym_w=True)
+    got, want = run_both(ctx, qo, case, L.PATH_TC, clamp=(0, 6))
+    bad = np.argwhere(got != want)
+    assert bad.size == 0, f"{len(bad)} mismatches, first at {bad[:5].tolist()}"
+
+
+def test_tc_conv_kernel_rows_residual_second_output(ctx, qo):
+    n, h, w, c, oc, kh, kw = 2, 22, 27, 16, 128, 3, 4
+    case = make_case(52, n, h, w, c, oc, kh, kw)
+    xq, zx, wq, zw, mult, bias, oqp = case
+    rng = np.random.default_rng(53)
+    oh, ow = h - kh + 1, w - kw + 1
+    res = rng.integers(0, 256, (n, oh, ow, oc), dtype=np.uint8)
+    rq, aq, yq2 = QuantParam(117, 0.05), QuantParam(125, 0.06), QuantParam(0, 0.03)
+    conv = qo.qconv2d_u8(xq, wq, zw, mult, bias, zx, oqp.scale, oqp.zero_point)
+    want = qo.qadd_u8(conv, res, oqp.scale, oqp.zero_point, rq.scale, rq.zero_point, aq.scale, aq.zero_point)
+    want2 = qo.requant_u8(want, aq.scale, aq.zero_point, yq2.scale, yq2.zero_point, 0.0, np.inf)
+    got, got2 = ctx.conv2d(torch.from_numpy(xq), wq, zw, mult, bias, zx, oqp, force_path=L.PATH_TC,
+                           res=torch.from_numpy(res).cuda(), residual=(rq, aq), y2=(yq2, 0.0, float("inf")))
+    ctx.check_status()
+    assert np.array_equal(got.cpu().numpy(), want)
+    assert np.array_equal(got2.cpu().numpy(), want2)
