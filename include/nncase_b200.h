@@ -93,6 +93,11 @@ NNCB_API int nncb_quantize_nchw_to_nhwc_u8(nncb_context *ctx, const float *in, u
 NNCB_API int nncb_quantize_nchw_to_s2d_u8(nncb_context *ctx, const float *in, uint8_t *out, int n, int c, int h, int w, int c_pad, float scale, int32_t zero_point);
 /* the same from an NHWC f32 input [n][h][w][c] */
 NNCB_API int nncb_quantize_nhwc_to_s2d_u8(nncb_context *ctx, const float *in, uint8_t *out, int n, int h, int w, int c, int c_pad, float scale, int32_t zero_point);
+/* the same with the convolution's padding materialised: out is [n][h/2+pad_t+pad_b][w/2+pad_l+pad_r][c_pad]
+ * and the border cells hold the zero point, so that the consumer is an unpadded convolution
+ * (Conv2D's zero padding, src/Native/src/kernels/stackvm/reference/convolution.cpp:56-66, as data).
+ * in_nhwc != 0: the f32 input is [n][h][w][c], else [n][c][h][w]. */
+NNCB_API int nncb_quantize_to_s2d_padded_u8(nncb_context *ctx, const float *in, int in_nhwc, uint8_t *out, int n, int c, int h, int w, int c_pad, int pad_t, int pad_b, int pad_l, int pad_r, float scale, int32_t zero_point);
 NNCB_API int nncb_dequantize_nhwc_to_nchw_f32(nncb_context *ctx, const uint8_t *in, float *out, int n, int h, int w, int c, float scale, int32_t zero_point);
 /* u8 layout changes without arithmetic */
 NNCB_API int nncb_nchw_to_nhwc_u8(nncb_context *ctx, const uint8_t *in, uint8_t *out, int n, int c, int h, int w);

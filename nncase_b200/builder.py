@@ -220,10 +220,18 @@ def build_program(graph, calib_samples, w_quant_type="uint8", device="cpu"):
                    users[0]["groups"] == 1 and tuple(users[0]["dil"]) == (1, 1) and c <= 8 and h % 2 == 0 and
                    w % 2 == 0)
             if s2d:
-                # image stem: quantize straight into the space-to-depth layout (see space_to_depth_conv)
-                add_tensor(nd["out"], 32, h // 2, w // 2, qps[nd["out"]])
-                ops.append(dict(op="quantize_input", out=nd["out"], c=c, c_pad=32, s2d=True, nhwc=nhwc))
-                s2d_of = {nd["out"]: (c, h, w)}
+                # image stem: quantize straight into the space-to-depth layout (see space_to_depth_conv).
+                # With 16-byte cells and the padding written as zero-point cells, the stem is an unpadded
+                # stride-1 convolution whose kernel rows are contiguous bytes (the kernel's row mode).
+                cp = 16 if 4 * c <= 16 else 32
+                _, pad2 = space_to_depth_conv(np.zeros((1,) + tuple(users[0]["w"].shape[2:]) + (c,), np.uint8), [0],
+                                              users[0]["pad"], (h, w), cp)
+                k2w = (users[0]["w"].shape[3] + users[0]["pad"][2] % 2 + 1) // 2
+                pre_pad = pad2 if k2w * cp in (32, 64, 128) else (0, 0, 0, 0)
+                add_tensor(nd["out"], cp, h // 2 + pre_pad[0] + pre_pad[1], w // 2 + pre_pad[2] + pre_pad[3],
+                           qps[nd["out"]])
+                ops.append(dict(op="quantize_input", out=nd["out"], c=c, c_pad=cp, s2d=True, nhwc=nhwc, pad=pre_pad))
+                s2d_of = {nd["out"]: (c, h, w, pre_pad)}
             else:
                 cp = _pad_channels(c)
                 add_tensor(nd["out"], cp, h, w, qps[nd["out"]])
@@ -234,9 +242,12 @@ def build_program(graph, calib_samples, w_quant_type="uint8", device="cpu"):
             c, h, w = shapes[nd["in"]]
             stride, pad = nd["stride"], nd["pad"]
             if nd["in"] in s2d_of:
-                c0, h0, w0 = s2d_of[nd["in"]]
+                c0, h0, w0, pre_pad = s2d_of[nd["in"]]
                 wq, zw, sw = quantize_weights(nd["w"], w_quant_type)
                 wq, pad = space_to_depth_conv(wq, zw, pad, (h0, w0), c)
+                if any(pre_pad):
+                    assert tuple(pad) == tuple(pre_pad)
+                    pad = (0, 0, 0, 0)  # already in the data
                 stride = (1, 1)
             else:
                 wq, zw, sw = quantize_weights(nd["w"], w_quant_type, c if nd["groups"] == 1 else None)

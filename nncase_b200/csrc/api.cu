@@ -104,7 +104,8 @@ EpiParams make_epi(const nncb_qconv2d *cv) {
 int quantize(nncb_context *, const float *, void *, size_t, float, int32_t, int);
 int dequantize(nncb_context *, const void *, float *, size_t, float, int32_t, int);
 int quantize_nchw_to_nhwc_u8(nncb_context *, const float *, uint8_t *, int, int, int, int, int, float, int32_t);
-int quantize_nchw_to_s2d_u8(nncb_context *, const float *, uint8_t *, int, int, int, int, int, float, int32_t, bool);
+int quantize_nchw_to_s2d_u8(nncb_context *, const float *, uint8_t *, int, int, int, int, int, float, int32_t, bool, int, int,
+                            int, int);
 int copy_channels_u8(nncb_context *, const uint8_t *, int, int, uint8_t *, int, int, int, size_t, const uint8_t *);
 int resize_nearest_u8(nncb_context *, const uint8_t *, uint8_t *, int, int, int, int, int, int);
 int dequantize_nhwc_to_nchw_f32(nncb_context *, const uint8_t *, float *, int, int, int, int, float, int32_t);
@@ -365,11 +366,16 @@ int nncb_quantize_nchw_to_nhwc_u8(nncb_context *ctx, const float *in, uint8_t *o
 }
 int nncb_quantize_nchw_to_s2d_u8(nncb_context *ctx, const float *in, uint8_t *out, int n, int c, int h, int w, int c_pad, float scale, int32_t zp) {
     CHECK_CTX(ctx);
-    return quantize_nchw_to_s2d_u8(ctx, in, out, n, c, h, w, c_pad, scale, zp, false);
+    return quantize_nchw_to_s2d_u8(ctx, in, out, n, c, h, w, c_pad, scale, zp, false, 0, 0, 0, 0);
 }
 int nncb_quantize_nhwc_to_s2d_u8(nncb_context *ctx, const float *in, uint8_t *out, int n, int h, int w, int c, int c_pad, float scale, int32_t zp) {
     CHECK_CTX(ctx);
-    return quantize_nchw_to_s2d_u8(ctx, in, out, n, c, h, w, c_pad, scale, zp, true);
+    return quantize_nchw_to_s2d_u8(ctx, in, out, n, c, h, w, c_pad, scale, zp, true, 0, 0, 0, 0);
+}
+int nncb_quantize_to_s2d_padded_u8(nncb_context *ctx, const float *in, int in_nhwc, uint8_t *out, int n, int c, int h, int w,
+                                   int c_pad, int pad_t, int pad_b, int pad_l, int pad_r, float scale, int32_t zp) {
+    CHECK_CTX(ctx);
+    return quantize_nchw_to_s2d_u8(ctx, in, out, n, c, h, w, c_pad, scale, zp, in_nhwc != 0, pad_t, pad_b, pad_l, pad_r);
 }
 int nncb_copy_channels_u8(nncb_context *ctx, const uint8_t *src, int src_c, int src_off, uint8_t *dst, int dst_c, int dst_off, int len, size_t pixels, const uint8_t *host_table) {
     CHECK_CTX(ctx);

@@ -335,6 +335,12 @@ __device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, int (&r)[16]) {
                  : "r"(taddr)
                  : "memory");
 }
+__device__ __forceinline__ void tmem_ld8_issue(uint32_t taddr, int (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // The wait is part of the same statement so that no use of the result can be scheduled before it.
 __device__ __forceinline__ void tmem_ld1(uint32_t taddr, int &r) {
@@ -753,6 +759,14 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
     return v;
 }
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts64(uint32_t addr, uint2 v) {
+    asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(addr), "r"(v.x), "r"(v.y) : "memory");
+}
 __device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
     asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
@@ -764,7 +778,7 @@ __device__ __forceinline__ uint32_t stage_addr(uint32_t base, int row, int chunk
 }
 } // namespace dev
 
-template <bool RES, bool Y2, bool XSUM>
+template <bool RES, bool Y2, bool XSUM, bool ROWS>
 __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &sg, TcShared &sh, uint32_t tmem_base,
                                               const CUtensorMap *tmap_y, const CUtensorMap *tmap_y2,
                                               const CUtensorMap *tmap_res, int warp, int lane) {
@@ -790,7 +804,7 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
     const bool multi_cls = f.n_cls > 1;
     const uint32_t res_bytes = 32u * hw;
     const int col_off = grp * hw;
-    const bool rows = g.mode == MODE_ROWS;
+    constexpr bool rows = ROWS; // the tile is a patch of pixels (MODE_ROWS)
     // Tensor-map coordinates of this warp's 32-row sub-tile of tile (mt, nt): 2-D {channel, pixel} in
     // general, 4-D {channel, x, y, image} when the tile is a patch of pixels. False when the sub-tile
     // lies wholly outside the output.
@@ -903,16 +917,18 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
             rsum = xs - a.cnt[cls] * g.x_zp;
         }
         const uint32_t corr_row = s_corr + (uint32_t)(cls * f.corr_pitch) * 4;
-        auto chunk = [&](const int (&v)[16], const int cc, auto multi_tag) {
+        // eight columns at a time: short live ranges keep the 16 epilogue warps within the register file
+        auto chunk = [&](const int (&v)[8], const int cc, auto multi_tag) {
             constexpr bool MULTI = decltype(multi_tag)::value;
             const int c0 = col_off + cc; // column within the tile
-            uint4 rw = make_uint4(0, 0, 0, 0);
+            const uint32_t half16 = stage_addr(0, lane, cc >> 4, hw, f.out_sw) + (cc & 8); // offset in a sub-tile
+            uint2 rw = make_uint2(0, 0);
             if (RES)
-                rw = lds128(stage_addr(s_res_cur, lane, cc >> 4, hw, f.out_sw));
-            const uint32_t rwa[4] = {rw.x, rw.y, rw.z, rw.w};
-            uint32_t bits[16];
+                rw = lds64(s_res_cur + half16);
+            const uint32_t rwa[2] = {rw.x, rw.y};
+            uint32_t bits[8];
 #pragma unroll
-            for (int j = 0; j < 16; j++) {
+            for (int j = 0; j < 8; j++) {
                 const float4 k = lds128f(s_cst + (c0 + j) * 16); // {mult, bias, corr, -zw}
                 const int corr = MULTI ? (int)lds32(corr_row + (c0 + j) * 4) : __float_as_int(k.z);
                 int acc = v[j] - corr;
@@ -928,50 +944,40 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
                 const float t = fminf(fmaxf(__fadd_rn(q0, f.zo), f.qlo), f.qhi);
                 bits[j] = __float_as_uint(__fadd_rn(t, MAGIC)); // 0x4B0000qq: low byte = the quantized value
                 if (RES) {
-                    // dequantize both addends, add, requantise -- as a 64 K-entry table of all byte pairs
-                    // index (q << 8) | r, with q's low bits folded into the bank bits of r: pixels of one
-                    // channel have similar q and similar r, which would otherwise share few banks
+                    // dequantize both addends, add, requantise -- as a 64 K-entry table of all byte pairs.
+                    // Index (q << 8) | r, with q's low bits folded into the bank bits of r: pixels of one
+                    // channel have similar q and similar r, which would otherwise share few banks.
                     uint32_t idx = __byte_perm(rwa[j >> 2], bits[j], 0x6540 | (j & 3));
                     idx ^= (idx >> 6) & 0x7Cu;
                     bits[j] = lds8(s_tab + idx);
                 }
             }
-            uint4 o;
+            uint2 o;
             o.x = __byte_perm(__byte_perm(bits[0], bits[1], 0x0040), __byte_perm(bits[2], bits[3], 0x0040), 0x5410);
             o.y = __byte_perm(__byte_perm(bits[4], bits[5], 0x0040), __byte_perm(bits[6], bits[7], 0x0040), 0x5410);
-            o.z = __byte_perm(__byte_perm(bits[8], bits[9], 0x0040), __byte_perm(bits[10], bits[11], 0x0040), 0x5410);
-            o.w = __byte_perm(__byte_perm(bits[12], bits[13], 0x0040), __byte_perm(bits[14], bits[15], 0x0040), 0x5410);
-            sts128(stage_addr(s_out, lane, cc >> 4, hw, f.out_sw), o);
+            sts64(s_out + half16, o);
             if (Y2) {
-                uint32_t b2[16];
 #pragma unroll
-                for (int j = 0; j < 16; j++)
-                    b2[j] = lds8(s_lut2 + (RES ? bits[j] : (bits[j] & 255u)));
-                uint4 o2;
-                o2.x = __byte_perm(__byte_perm(b2[0], b2[1], 0x0040), __byte_perm(b2[2], b2[3], 0x0040), 0x5410);
-                o2.y = __byte_perm(__byte_perm(b2[4], b2[5], 0x0040), __byte_perm(b2[6], b2[7], 0x0040), 0x5410);
-                o2.z = __byte_perm(__byte_perm(b2[8], b2[9], 0x0040), __byte_perm(b2[10], b2[11], 0x0040), 0x5410);
-                o2.w = __byte_perm(__byte_perm(b2[12], b2[13], 0x0040), __byte_perm(b2[14], b2[15], 0x0040), 0x5410);
-                sts128(stage_addr(s_y2, lane, cc >> 4, hw, f.out_sw), o2);
+                for (int j = 0; j < 8; j++)
+                    bits[j] = lds8(s_lut2 + (RES ? bits[j] : (bits[j] & 255u)));
+                o.x = __byte_perm(__byte_perm(bits[0], bits[1], 0x0040), __byte_perm(bits[2], bits[3], 0x0040), 0x5410);
+                o.y = __byte_perm(__byte_perm(bits[4], bits[5], 0x0040), __byte_perm(bits[6], bits[7], 0x0040), 0x5410);
+                sts64(s_y2 + half16, o);
             }
         };
-        // the TMEM load of the next 16 columns is in flight while the current ones are requantised
+        // the TMEM load of the next eight columns is in flight while the current ones are requantised
         auto columns = [&](auto multi_tag) {
-            int va[16], vb[16];
+            int va[8], vb[8];
             __syncwarp();
-            tmem_ld16_issue(tbase + col_off, va);
-            for (int cc = 0; cc < hw; cc += 32) {
+            tmem_ld8_issue(tbase + col_off, va);
+            for (int cc = 0; cc < hw; cc += 16) { // hw is 16 or 32
                 tmem_ld_wait();
-                const bool more = cc + 16 < hw; // warp-uniform
-                if (more)
-                    tmem_ld16_issue(tbase + col_off + cc + 16, vb);
+                tmem_ld8_issue(tbase + col_off + cc + 8, vb);
                 chunk(va, cc, multi_tag);
-                if (more) {
-                    tmem_ld_wait();
-                    if (cc + 32 < hw)
-                        tmem_ld16_issue(tbase + col_off + cc + 32, va);
-                    chunk(vb, cc + 16, multi_tag);
-                }
+                tmem_ld_wait();
+                if (cc + 16 < hw)
+                    tmem_ld8_issue(tbase + col_off + cc + 16, va);
+                chunk(vb, cc + 8, multi_tag);
             }
         };
         if (multi_cls)
@@ -1006,7 +1012,7 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
         tma_store_wait_all();
 }
 
-template <bool RES, bool Y2, bool XSUM>
+template <bool RES, bool Y2, bool XSUM, bool ROWS>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 tc_conv_fast_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_y, const __grid_constant__ CUtensorMap tmap_y2,
@@ -1025,7 +1031,7 @@ tc_conv_fast_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (lane == 0)
             mma_loop(g, sg, sh, tmem_base, a.status);
     } else {
-        epilogue_fast<RES, Y2, XSUM>(a, sg, sh, tmem_base, &tmap_y, &tmap_y2, &tmap_res, warp, lane);
+        epilogue_fast<RES, Y2, XSUM, ROWS>(a, sg, sh, tmem_base, &tmap_y, &tmap_y2, &tmap_res, warp, lane);
     }
     tc_teardown(g, sh, warp, tmem_base);
 }
@@ -1386,11 +1392,12 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
     // plan can ask for.
     const int lim = 226 * 1024;
     NNCB_CUDA_TRY(cudaFuncSetAttribute(tc_conv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
-    const void *fast_kernels[8] = {
-        (const void *)tc_conv_fast_kernel<false, false, false>, (const void *)tc_conv_fast_kernel<false, false, true>,
-        (const void *)tc_conv_fast_kernel<false, true, false>,  (const void *)tc_conv_fast_kernel<false, true, true>,
-        (const void *)tc_conv_fast_kernel<true, false, false>,  (const void *)tc_conv_fast_kernel<true, false, true>,
-        (const void *)tc_conv_fast_kernel<true, true, false>,   (const void *)tc_conv_fast_kernel<true, true, true>};
+    const void *fast_kernels[16] = {
+#define NNCB_K(R, Y, X) (const void *)tc_conv_fast_kernel<R, Y, X, false>, (const void *)tc_conv_fast_kernel<R, Y, X, true>
+        NNCB_K(false, false, false), NNCB_K(false, false, true), NNCB_K(false, true, false), NNCB_K(false, true, true),
+        NNCB_K(true, false, false),  NNCB_K(true, false, true),  NNCB_K(true, true, false),  NNCB_K(true, true, true)
+#undef NNCB_K
+    };
     for (const void *k : fast_kernels)
         NNCB_CUDA_TRY(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
     return 0;
@@ -1487,8 +1494,14 @@ int tc_conv_run(nncb_context *ctx, nncb_qconv2d *cv, const uint8_t *x, const uin
         const CUtensorMap &my2 = y2 ? tp->tmap_y2 : tp->tmap_y, &mres = res ? tp->tmap_res : tp->tmap_y;
         const int variant = (res ? 4 : 0) | (y2 ? 2 : 0) | (tp->g.has_xsum ? 1 : 0);
 #define NNCB_LAUNCH_FAST(R, Y, C)                                                                                     \
-    tc_conv_fast_kernel<R, Y, C><<<grid, TC_THREADS, tp->smem_bytes, ctx->stream>>>(tp->tmap_a, tp->tmap_b, tp->tmap_y, \
-                                                                                   my2, mres, a)
+    do {                                                                                                              \
+        if (tp->g.mode == MODE_ROWS)                                                                                  \
+            tc_conv_fast_kernel<R, Y, C, true><<<grid, TC_THREADS, tp->smem_bytes, ctx->stream>>>(                    \
+                tp->tmap_a, tp->tmap_b, tp->tmap_y, my2, mres, a);                                                    \
+        else                                                                                                          \
+            tc_conv_fast_kernel<R, Y, C, false><<<grid, TC_THREADS, tp->smem_bytes, ctx->stream>>>(                   \
+                tp->tmap_a, tp->tmap_b, tp->tmap_y, my2, mres, a);                                                    \
+    } while (0)
         switch (variant) {
         case 0: NNCB_LAUNCH_FAST(false, false, false); break;
         case 1: NNCB_LAUNCH_FAST(false, false, true); break;

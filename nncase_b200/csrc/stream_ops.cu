@@ -209,19 +209,21 @@ int quantize_nchw_to_nhwc_u8(nncb_context *ctx, const float *in, uint8_t *out, i
 template <int CPAD, bool IN_NHWC>
 __global__ void __launch_bounds__(256)
 quantize_nchw_to_s2d_kernel(const float *__restrict__ in, uint8_t *__restrict__ out, int c, int h, int w,
-                            size_t total_cells, float scale, float zp) {
-    const int hc = h / 2, wc = w / 2;
+                            size_t total_cells, float scale, float zp, int pad_t, int pad_b, int pad_l, int pad_r) {
+    // output cells include a border of pad_* cells that hold the zero point in every channel
+    const int hc = h / 2 + pad_t + pad_b, wc = w / 2 + pad_l + pad_r;
     const uint32_t zq = (uint32_t)min(max(__float2int_rn(zp), 0), 255);
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total_cells;
          i += (size_t)gridDim.x * blockDim.x) {
-        const int X = (int)(i % wc);
-        const int Y = (int)((i / wc) % hc);
+        const int X = (int)(i % wc) - pad_l;
+        const int Y = (int)((i / wc) % hc) - pad_t;
         const size_t n = i / ((size_t)wc * hc);
         uint32_t words[CPAD / 4];
 #pragma unroll
         for (int k = 0; k < CPAD / 4; k++)
             words[k] = zq * 0x01010101u;
-        for (int ch = 0; ch < c; ch++)
+        const bool inside = X >= 0 && Y >= 0 && X < w / 2 && Y < h / 2;
+        for (int ch = 0; inside && ch < c; ch++)
 #pragma unroll
             for (int dy = 0; dy < 2; dy++) {
                 float2 v;
@@ -251,23 +253,29 @@ quantize_nchw_to_s2d_kernel(const float *__restrict__ in, uint8_t *__restrict__ 
 }
 
 int quantize_nchw_to_s2d_u8(nncb_context *ctx, const float *in, uint8_t *out, int n, int c, int h, int w, int c_pad,
-                            float scale, int32_t zp, bool in_nhwc) {
+                            float scale, int32_t zp, bool in_nhwc, int pad_t, int pad_b, int pad_l, int pad_r) {
     if (n <= 0 || c <= 0 || h <= 0 || w <= 0 || (h & 1) || (w & 1))
         return fail(-EINVAL, "quantize_nchw_to_s2d_u8: height and width must be positive and even");
+    if (pad_t < 0 || pad_b < 0 || pad_l < 0 || pad_r < 0)
+        return fail(-EINVAL, "quantize_nchw_to_s2d_u8: negative padding");
     if (4 * c > c_pad || (c_pad != 16 && c_pad != 32))
         return fail(-EINVAL, "quantize_nchw_to_s2d_u8: c_pad must be 16 or 32 and hold 4*c channels");
     if ((reinterpret_cast<uintptr_t>(in) & 7) || (reinterpret_cast<uintptr_t>(out) & 15))
         return fail(-EINVAL, "quantize_nchw_to_s2d_u8: pointers must be 8-byte (in) and 16-byte (out) aligned");
-    const size_t total = (size_t)n * (h / 2) * (w / 2);
+    const size_t total = (size_t)n * (h / 2 + pad_t + pad_b) * (w / 2 + pad_l + pad_r);
     const int grid = stream_grid(ctx, total, 256);
     if (c_pad == 32 && in_nhwc)
-        quantize_nchw_to_s2d_kernel<32, true><<<grid, 256, 0, ctx->stream>>>(in, out, c, h, w, total, scale, (float)zp);
+        quantize_nchw_to_s2d_kernel<32, true><<<grid, 256, 0, ctx->stream>>>(in, out, c, h, w, total, scale, (float)zp, pad_t, pad_b,
+                                                                              pad_l, pad_r);
     else if (c_pad == 32)
-        quantize_nchw_to_s2d_kernel<32, false><<<grid, 256, 0, ctx->stream>>>(in, out, c, h, w, total, scale, (float)zp);
+        quantize_nchw_to_s2d_kernel<32, false><<<grid, 256, 0, ctx->stream>>>(in, out, c, h, w, total, scale, (float)zp, pad_t, pad_b,
+                                                                              pad_l, pad_r);
     else if (in_nhwc)
-        quantize_nchw_to_s2d_kernel<16, true><<<grid, 256, 0, ctx->stream>>>(in, out, c, h, w, total, scale, (float)zp);
+        quantize_nchw_to_s2d_kernel<16, true><<<grid, 256, 0, ctx->stream>>>(in, out, c, h, w, total, scale, (float)zp, pad_t, pad_b,
+                                                                              pad_l, pad_r);
     else
-        quantize_nchw_to_s2d_kernel<16, false><<<grid, 256, 0, ctx->stream>>>(in, out, c, h, w, total, scale, (float)zp);
+        quantize_nchw_to_s2d_kernel<16, false><<<grid, 256, 0, ctx->stream>>>(in, out, c, h, w, total, scale, (float)zp, pad_t, pad_b,
+                                                                              pad_l, pad_r);
     return after_launch(ctx, "quantize_nchw_to_s2d");
 }
 

@@ -138,6 +138,20 @@ class Context:
                                                      qp.scale, qp.zero_point))
         return y
 
+    def quantize_to_s2d_padded(self, x, qp, c_pad, pad, nhwc=False):
+        """f32 NCHW (or NHWC) -> u8 [n, h/2+pt+pb, w/2+pl+pr, c_pad]: space-to-depth cells inside a border of
+        zero-point cells; pad = (top, bottom, left, right) in cells."""
+        x = self._cuda(x, torch.float32)
+        if nhwc:
+            n, h, w, c = x.shape
+        else:
+            n, c, h, w = x.shape
+        pt, pb, pl, pr = pad
+        y = torch.empty((n, h // 2 + pt + pb, w // 2 + pl + pr, c_pad), dtype=torch.uint8, device=self.device)
+        check(self._lib.nncb_quantize_to_s2d_padded_u8(self._h, x.data_ptr(), int(nhwc), y.data_ptr(), n, c, h, w, c_pad,
+                                                       pt, pb, pl, pr, qp.scale, qp.zero_point))
+        return y
+
     def quantize_nhwc_to_s2d(self, x, qp, c_pad=32):
         """f32 NHWC -> u8 [n, h/2, w/2, c_pad] with the same channel order as quantize_nchw_to_s2d."""
         x = self._cuda(x, torch.float32)

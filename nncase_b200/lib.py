@@ -81,6 +81,7 @@ SIGNATURES = {
     "nncb_make_requant_table": (_I, [_F, _I32, _F, _I32, _F, _F, _VP]),
     "nncb_softmax_f32": (_I, [_VP, _VP, _VP, _SZ, _I, _F]),
     "nncb_quantize_nhwc_to_s2d_u8": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _F, _I32]),
+    "nncb_quantize_to_s2d_padded_u8": (_I, [_VP, _VP, _I, _VP, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I32]),
     "nncb_copy_channels_u8": (_I, [_VP, _VP, _I, _I, _VP, _I, _I, _I, _SZ, _VP]),
     "nncb_resize_nearest_u8": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _I]),
     "nncb_lut_u8": (_I, [_VP, _VP, _VP, _SZ, _VP]),

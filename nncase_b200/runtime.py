@@ -91,7 +91,16 @@ class CudaFunction:
             if kind == "quantize_input":
                 n, c, hh, ww = x_dev.shape
                 qp = T[op["out"]]["qp"]
-                if op.get("nhwc"):
+                if op.get("s2d") and any(op.get("pad", ())):
+                    if op.get("nhwc"):
+                        n, hh, ww, c = x_dev.shape
+                    else:
+                        n, c, hh, ww = x_dev.shape
+                    pt, pb, pl, pr = op["pad"]
+                    L.check(lib.nncb_quantize_to_s2d_padded_u8(h_, x_dev.data_ptr(), int(bool(op.get("nhwc"))),
+                                                               buf[op["out"]].data_ptr(), n, c, hh, ww, op["c_pad"], pt, pb,
+                                                               pl, pr, qp.scale, qp.zero_point))
+                elif op.get("nhwc"):
                     n, hh, ww, c = x_dev.shape
                     if op.get("s2d"):
                         L.check(lib.nncb_quantize_nhwc_to_s2d_u8(h_, x_dev.data_ptr(), buf[op["out"]].data_ptr(), n, hh, ww,

@@ -30,7 +30,8 @@ def run_program(program, x_nchw_f32, threads=8, feed=None, keep=None):
             if op.get("nhwc"):  # element-wise identical: bring the NHWC input to the NCHW form the helpers take
                 xin = np.ascontiguousarray(np.transpose(x_nchw_f32, (0, 3, 1, 2)))
             if op.get("s2d"):
-                t[op["out"]] = Q.quantize_nchw_to_s2d_u8(xin, qp.scale, qp.zero_point, op["c_pad"])
+                t[op["out"]] = Q.quantize_nchw_to_s2d_u8(xin, qp.scale, qp.zero_point, op["c_pad"],
+                                                         op.get("pad", (0, 0, 0, 0)))
             else:
                 t[op["out"]] = Q.quantize_nchw_to_nhwc_u8(xin, qp.scale, qp.zero_point, op["c_pad"])
         elif k == "conv":

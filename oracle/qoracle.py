@@ -78,12 +78,16 @@ def quantize_nchw_to_nhwc_u8(x, scale, zp, c_pad=None):
     return y
 
 
-def quantize_nchw_to_s2d_u8(x, scale, zp, c_pad=32):
+def quantize_nchw_to_s2d_u8(x, scale, zp, c_pad=32, pad=(0, 0, 0, 0)):
+    """pad = (top, bottom, left, right) cells of zero point around the space-to-depth cells."""
     x = np.ascontiguousarray(x, np.float32)
     n, c, h, w = x.shape
     y = np.empty((n, h // 2, w // 2, c_pad), np.uint8)
     lib().qo_quantize_nchw_to_s2d_u8(_p(x), _p(y), n, c, h, w, c_pad, C.c_float(scale), C.c_int32(zp))
-    return y
+    if any(pad):
+        q0 = np.uint8(min(max(int(zp), 0), 255))
+        y = np.pad(y, ((0, 0), (pad[0], pad[1]), (pad[2], pad[3]), (0, 0)), constant_values=q0)
+    return np.ascontiguousarray(y)
 
 
 def qconv2d_u8(x, w, w_zp, mult, bias, x_zp, out_scale, out_zp, stride=(1, 1),

@@ -209,3 +209,14 @@ def test_resize_nearest(ctx, qo, shape, f):
     got = ctx.resize_nearest(torch.from_numpy(x), f, f).cpu().numpy()
     assert np.array_equal(got, qo.resize_nearest_u8(x, f, f))
     assert np.array_equal(got, x.repeat(f, 1).repeat(f, 2))
+
+
+@pytest.mark.parametrize("nhwc", [False, True])
+@pytest.mark.parametrize("shape,c_pad,pad", [((2, 3, 18, 22), 16, (2, 1, 2, 1)), ((1, 3, 224, 224), 16, (2, 1, 2, 1)),
+                                             ((2, 4, 8, 8), 32, (1, 0, 1, 0)), ((1, 3, 6, 4), 16, (0, 0, 0, 3))])
+def test_quantize_to_s2d_padded(ctx, qo, shape, c_pad, pad, nhwc):
+    """Space-to-depth cells inside a border of zero-point cells (the stem convolution's padding as data)."""
+    x = np.random.default_rng(17).normal(0, 1, shape).astype(np.float32)
+    xin = np.ascontiguousarray(x.transpose(0, 2, 3, 1)) if nhwc else x
+    got = ctx.quantize_to_s2d_padded(torch.from_numpy(xin), QuantParam(117, 0.021), c_pad, pad, nhwc=nhwc).cpu().numpy()
+    assert np.array_equal(got, qo.quantize_nchw_to_s2d_u8(x, 0.021, 117, c_pad, pad))
