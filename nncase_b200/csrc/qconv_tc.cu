@@ -63,6 +63,7 @@ struct TcGeom {
     uint32_t idesc;
     int f32_out;
     int acc_arrivals;   // epilogue warps that release an accumulator buffer
+    int b_resident;     // the whole weight matrix stays in shared memory (one N tile, small K): loaded once per CTA
     int bx_log2, tiles_x, tiles_y; // MODE_ROWS: patch width 2^bx_log2 (height 128 >> bx_log2), patches per image
 };
 
@@ -391,13 +392,15 @@ constexpr int RES_BUFS = 3; // residual sub-tiles in flight per epilogue warp: t
 constexpr float MAGIC = 8388608.0f; // 2^23: for 0 <= x <= 255, x + MAGIC has bits 0x4B0000qq with qq = rint(x)
 
 struct TcShared {
-    uint64_t bar_full[MAX_STAGES], bar_empty[MAX_STAGES], bar_acc_full[2], bar_acc_empty[2], bar_res[EPI_WARPS * RES_BUFS];
+    uint64_t bar_full[MAX_STAGES], bar_empty[MAX_STAGES], bar_acc_full[2], bar_acc_empty[2], bar_b, bar_res[EPI_WARPS * RES_BUFS];
     uint32_t tmem_base_slot;
     volatile int abort_flag;
 };
 
 struct StageGeom {
     uint32_t smem_base, a_stage_bytes, b_stage_bytes, stage_pitch;
+    uint32_t b_pitch;    // bytes between the K blocks of a resident weight matrix
+    uint32_t b_resident; // its address (after the stage ring), or 0 when weights travel with the stages
 };
 
 __device__ __forceinline__ StageGeom stage_geom(const TcGeom &g, const uint8_t *smem_raw) {
@@ -407,7 +410,9 @@ __device__ __forceinline__ StageGeom stage_geom(const TcGeom &g, const uint8_t *
     sg.a_stage_bytes = 128u * g.kb;
     sg.b_stage_bytes = (uint32_t)g.bn_mma * g.kb;
     // keep every stage's A and B tile 1024-byte aligned (a_stage_bytes is a multiple of 1024)
-    sg.stage_pitch = sg.a_stage_bytes + ((sg.b_stage_bytes + 1023u) & ~1023u);
+    sg.b_pitch = (sg.b_stage_bytes + 1023u) & ~1023u;
+    sg.stage_pitch = sg.a_stage_bytes + (g.b_resident ? 0u : sg.b_pitch);
+    sg.b_resident = g.b_resident ? sg.smem_base + (uint32_t)g.stages * sg.stage_pitch : 0u;
     return sg;
 }
 
@@ -419,6 +424,7 @@ __device__ __forceinline__ void tc_setup(const TcGeom &g, TcShared &sh, int warp
             mbar_init(smem_u32(&sh.bar_full[s]), 1);
             mbar_init(smem_u32(&sh.bar_empty[s]), 1);
         }
+        mbar_init(smem_u32(&sh.bar_b), 1);
         for (int b = 0; b < 2; b++) {
             mbar_init(smem_u32(&sh.bar_acc_full[b]), 1);
             mbar_init(smem_u32(&sh.bar_acc_empty[b]), g.acc_arrivals);
@@ -465,9 +471,17 @@ __device__ __forceinline__ void producer_loop(const TcGeom &g, const StageGeom &
     const bool gemm = g.mode == MODE_GEMM, rows = g.mode == MODE_ROWS;
     const int kb = g.kb, c_blocks = g.c_blocks, kw_ = g.kw;
     const uint32_t dil_w = g.dil_w, dil_h = g.dil_h, stages = g.stages;
-    const uint32_t stage_bytes = sg.a_stage_bytes + sg.b_stage_bytes;
+    const bool b_res = sg.b_resident != 0;
+    const uint32_t stage_bytes = sg.a_stage_bytes + (b_res ? 0u : sg.b_stage_bytes);
     const uint32_t bar_full0 = smem_u32(&sh.bar_full[0]), bar_empty0 = smem_u32(&sh.bar_empty[0]);
     uint32_t stage = 0, phase = 0;
+    if (b_res && (int)blockIdx.x < total_tiles) {
+        // the whole weight matrix, once
+        const uint32_t bar_b = smem_u32(&sh.bar_b);
+        mbar_expect_tx(bar_b, (uint32_t)k_blocks * sg.b_stage_bytes);
+        for (int kbi = 0; kbi < k_blocks; kbi++)
+            tma_load_2d(sg.b_resident + kbi * sg.b_pitch, tmap_b, bar_b, kbi * kb, 0);
+    }
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
         const int mt = tile % g.m_tiles, nt = tile / g.m_tiles;
         const int m0 = mt * 128, n0 = nt * g.bn_mma;
@@ -500,7 +514,8 @@ __device__ __forceinline__ void producer_loop(const TcGeom &g, const StageGeom &
                 tma_load_4d(sa, tmap_a, full, 0, cw, chh + (int)off_h, cn); // kw = 1 here: off_h counts kernel rows
             else
                 tma_load_im2col_4d(sa, tmap_a, full, c_off, cw, chh, cn, (uint16_t)off_w, (uint16_t)off_h);
-            tma_load_2d(sb, tmap_b, full, k_off, n0);
+            if (!b_res)
+                tma_load_2d(sb, tmap_b, full, k_off, n0);
             k_off += kb;
             c_off += kb;
             if (++cb == c_blocks) {
@@ -532,6 +547,13 @@ __device__ __forceinline__ void mma_loop(const TcGeom &g, const StageGeom &sg, T
     const uint32_t pitch16 = sg.stage_pitch >> 4, stages = g.stages, idesc = g.idesc;
     const int kk = g.kb / 32; // 1, 2 or 4 MMAs of K = 32 per K block
     const uint32_t bar_full0 = smem_u32(&sh.bar_full[0]), bar_empty0 = smem_u32(&sh.bar_empty[0]);
+    const bool b_res = sg.b_resident != 0;
+    const uint64_t desc_bres = smem_desc(sg.b_resident, g.kb);
+    const uint32_t bres_pitch16 = sg.b_pitch >> 4;
+    if (b_res && (int)blockIdx.x < total_tiles) {
+        if (!mbar_wait(smem_u32(&sh.bar_b), 0, &sh.abort_flag, status, ERR_MMA_FULL))
+            return;
+    }
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, it++) {
         const int buf = it & 1;
         const uint32_t ph = buf ? acc_phase1 : acc_phase0;
@@ -547,7 +569,8 @@ __device__ __forceinline__ void mma_loop(const TcGeom &g, const StageGeom &sg, T
             if (!mbar_wait(bar_full0 + stage * 8, phase, &sh.abort_flag, status, ERR_MMA_FULL))
                 return;
             fence_after_sync();
-            const uint64_t da = desc_a0 + (uint64_t)(stage * pitch16), db = desc_b0 + (uint64_t)(stage * pitch16);
+            const uint64_t da = desc_a0 + (uint64_t)(stage * pitch16);
+            const uint64_t db = b_res ? desc_bres + (uint64_t)(kbi * bres_pitch16) : desc_b0 + (uint64_t)(stage * pitch16);
             mma_i8(tmem_d, da, db, idesc, kbi != 0);
             if (kk > 1)
                 mma_i8(tmem_d, da + 2, db + 2, idesc, 1);
@@ -1372,14 +1395,20 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
         tp->fast = false; // not enough room for the staging tiles next to two pipeline stages
         extras = 0;
     }
-    int stages = (int)((budget - extras) / (a_stage + b_pitch));
+    // A weight matrix of one N tile that fits beside four activation stages stays resident: the
+    // loads are bound by rows moved per clock, and weights are 40 % of the rows of a 64-channel layer.
+    const uint32_t k_blocks = (uint32_t)(g.taps * g.c_blocks);
+    const uint32_t b_all = k_blocks * b_pitch;
+    g.b_resident = g.n_tiles == 1 && b_all <= 64u * 1024u && extras + b_all + 4 * a_stage <= budget;
+    const uint32_t per_stage = a_stage + (g.b_resident ? 0u : b_pitch);
+    int stages = (int)((budget - extras - (g.b_resident ? b_all : 0u)) / per_stage);
     if (stages > MAX_STAGES)
         stages = MAX_STAGES;
     if (stages < 2)
         return fail(-ENOSYS, "tcgen05 conv: tile does not fit shared memory");
     g.stages = stages;
     g.acc_arrivals = tp->fast ? 4 * fe.ncg : EPI_WARPS;
-    const uint32_t ring = (uint32_t)stages * (a_stage + b_pitch);
+    const uint32_t ring = (uint32_t)stages * per_stage + (g.b_resident ? b_all : 0u);
     if (tp->fast) {
         fe.off_out += ring, fe.off_y2 += ring, fe.off_res += ring, fe.off_cst += ring;
         fe.off_lut2 += ring, fe.off_corr += ring, fe.off_tab += ring;
