@@ -63,6 +63,7 @@ struct TcGeom {
     uint32_t idesc;
     int f32_out;
     int acc_arrivals;   // epilogue warps that release an accumulator buffer
+    int kgroup;         // K blocks per pipeline stage (one barrier round trip and one commit for all of them)
     int b_resident;     // the whole weight matrix stays in shared memory (one N tile, small K): loaded once per CTA
     int bx_log2, tiles_x, tiles_y; // MODE_ROWS: patch width 2^bx_log2 (height 128 >> bx_log2), patches per image
 };
@@ -399,6 +400,7 @@ struct TcShared {
 
 struct StageGeom {
     uint32_t smem_base, a_stage_bytes, b_stage_bytes, stage_pitch;
+    uint32_t kblock_pitch; // bytes between the K blocks of one stage
     uint32_t b_pitch;    // bytes between the K blocks of a resident weight matrix
     uint32_t b_resident; // its address (after the stage ring), or 0 when weights travel with the stages
 };
@@ -411,7 +413,8 @@ __device__ __forceinline__ StageGeom stage_geom(const TcGeom &g, const uint8_t *
     sg.b_stage_bytes = (uint32_t)g.bn_mma * g.kb;
     // keep every stage's A and B tile 1024-byte aligned (a_stage_bytes is a multiple of 1024)
     sg.b_pitch = (sg.b_stage_bytes + 1023u) & ~1023u;
-    sg.stage_pitch = sg.a_stage_bytes + (g.b_resident ? 0u : sg.b_pitch);
+    sg.kblock_pitch = sg.a_stage_bytes + (g.b_resident ? 0u : sg.b_pitch);
+    sg.stage_pitch = (uint32_t)g.kgroup * sg.kblock_pitch;
     sg.b_resident = g.b_resident ? sg.smem_base + (uint32_t)g.stages * sg.stage_pitch : 0u;
     return sg;
 }
@@ -472,7 +475,8 @@ __device__ __forceinline__ void producer_loop(const TcGeom &g, const StageGeom &
     const int kb = g.kb, c_blocks = g.c_blocks, kw_ = g.kw;
     const uint32_t dil_w = g.dil_w, dil_h = g.dil_h, stages = g.stages;
     const bool b_res = sg.b_resident != 0;
-    const uint32_t stage_bytes = sg.a_stage_bytes + (b_res ? 0u : sg.b_stage_bytes);
+    const uint32_t kblock_bytes = sg.a_stage_bytes + (b_res ? 0u : sg.b_stage_bytes);
+    const int kgroup = g.kgroup;
     const uint32_t bar_full0 = smem_u32(&sh.bar_full[0]), bar_empty0 = smem_u32(&sh.bar_empty[0]);
     uint32_t stage = 0, phase = 0;
     if (b_res && (int)blockIdx.x < total_tiles) {
@@ -502,27 +506,61 @@ __device__ __forceinline__ void producer_loop(const TcGeom &g, const StageGeom &
         int cb = 0, c_off = 0, k_off = 0;
         uint32_t off_w = 0, off_h = 0;
         int kx = 0;
-        for (int kbi = 0; kbi < k_blocks; kbi++) {
+        if (kgroup == 1) {
+            // one K block per stage: the shortest instruction stream per block
+            for (int kbi = 0; kbi < k_blocks; kbi++) {
+                if (!mbar_wait(bar_empty0 + stage * 8, phase ^ 1, &sh.abort_flag, status, ERR_PRODUCER))
+                    return;
+                const uint32_t full = bar_full0 + stage * 8;
+                const uint32_t sa = sg.smem_base + stage * sg.stage_pitch;
+                mbar_expect_tx(full, kblock_bytes);
+                if (gemm)
+                    tma_load_2d(sa, tmap_a, full, c_off, m0);
+                else if (rows)
+                    tma_load_4d(sa, tmap_a, full, 0, cw, chh + (int)off_h, cn);
+                else
+                    tma_load_im2col_4d(sa, tmap_a, full, c_off, cw, chh, cn, (uint16_t)off_w, (uint16_t)off_h);
+                if (!b_res)
+                    tma_load_2d(sa + sg.a_stage_bytes, tmap_b, full, k_off, n0);
+                k_off += kb;
+                c_off += kb;
+                if (++cb == c_blocks) {
+                    cb = 0, c_off = 0;
+                    off_w += dil_w;
+                    if (++kx == kw_)
+                        kx = 0, off_w = 0, off_h += dil_h;
+                }
+                if (++stage == stages) {
+                    stage = 0;
+                    phase ^= 1;
+                }
+            }
+            continue;
+        }
+        for (int kb0 = 0; kb0 < k_blocks; kb0 += kgroup) {
             if (!mbar_wait(bar_empty0 + stage * 8, phase ^ 1, &sh.abort_flag, status, ERR_PRODUCER))
                 return;
             const uint32_t full = bar_full0 + stage * 8;
-            const uint32_t sa = sg.smem_base + stage * sg.stage_pitch, sb = sa + sg.a_stage_bytes;
-            mbar_expect_tx(full, stage_bytes);
-            if (gemm)
-                tma_load_2d(sa, tmap_a, full, c_off, m0);
-            else if (rows)
-                tma_load_4d(sa, tmap_a, full, 0, cw, chh + (int)off_h, cn); // kw = 1 here: off_h counts kernel rows
-            else
-                tma_load_im2col_4d(sa, tmap_a, full, c_off, cw, chh, cn, (uint16_t)off_w, (uint16_t)off_h);
-            if (!b_res)
-                tma_load_2d(sb, tmap_b, full, k_off, n0);
-            k_off += kb;
-            c_off += kb;
-            if (++cb == c_blocks) {
-                cb = 0, c_off = 0;
-                off_w += dil_w;
-                if (++kx == kw_)
-                    kx = 0, off_w = 0, off_h += dil_h;
+            const int cnt = min(kgroup, k_blocks - kb0); // K blocks of this stage
+            mbar_expect_tx(full, (uint32_t)cnt * kblock_bytes);
+            uint32_t sa = sg.smem_base + stage * sg.stage_pitch;
+            for (int i = 0; i < cnt; i++, sa += sg.kblock_pitch) {
+                if (gemm)
+                    tma_load_2d(sa, tmap_a, full, c_off, m0);
+                else if (rows)
+                    tma_load_4d(sa, tmap_a, full, 0, cw, chh + (int)off_h, cn); // kw = 1 here: off_h counts kernel rows
+                else
+                    tma_load_im2col_4d(sa, tmap_a, full, c_off, cw, chh, cn, (uint16_t)off_w, (uint16_t)off_h);
+                if (!b_res)
+                    tma_load_2d(sa + sg.a_stage_bytes, tmap_b, full, k_off, n0);
+                k_off += kb;
+                c_off += kb;
+                if (++cb == c_blocks) {
+                    cb = 0, c_off = 0;
+                    off_w += dil_w;
+                    if (++kx == kw_)
+                        kx = 0, off_w = 0, off_h += dil_h;
+                }
             }
             if (++stage == stages) {
                 stage = 0;
@@ -549,7 +587,9 @@ __device__ __forceinline__ void mma_loop(const TcGeom &g, const StageGeom &sg, T
     const uint32_t bar_full0 = smem_u32(&sh.bar_full[0]), bar_empty0 = smem_u32(&sh.bar_empty[0]);
     const bool b_res = sg.b_resident != 0;
     const uint64_t desc_bres = smem_desc(sg.b_resident, g.kb);
-    const uint32_t bres_pitch16 = sg.b_pitch >> 4;
+    const uint32_t bres_pitch16 = sg.b_pitch >> 4, kblock_pitch16 = sg.kblock_pitch >> 4;
+    const uint32_t b_step16 = b_res ? bres_pitch16 : kblock_pitch16; // from one K block's weights to the next
+    const int kgroup = g.kgroup;
     if (b_res && (int)blockIdx.x < total_tiles) {
         if (!mbar_wait(smem_u32(&sh.bar_b), 0, &sh.abort_flag, status, ERR_MMA_FULL))
             return;
@@ -565,18 +605,44 @@ __device__ __forceinline__ void mma_loop(const TcGeom &g, const StageGeom &sg, T
             acc_phase0 ^= 1;
         fence_after_sync();
         const uint32_t tmem_d = tmem_base + buf * g.acc_stride;
-        for (int kbi = 0; kbi < k_blocks; kbi++) {
+        if (kgroup == 1) {
+            for (int kbi = 0; kbi < k_blocks; kbi++) {
+                if (!mbar_wait(bar_full0 + stage * 8, phase, &sh.abort_flag, status, ERR_MMA_FULL))
+                    return;
+                fence_after_sync();
+                const uint64_t da = desc_a0 + (uint64_t)(stage * pitch16);
+                const uint64_t db = b_res ? desc_bres + (uint64_t)(kbi * bres_pitch16) : desc_b0 + (uint64_t)(stage * pitch16);
+                mma_i8(tmem_d, da, db, idesc, kbi != 0);
+                if (kk > 1)
+                    mma_i8(tmem_d, da + 2, db + 2, idesc, 1);
+                if (kk > 2) {
+                    mma_i8(tmem_d, da + 4, db + 4, idesc, 1);
+                    mma_i8(tmem_d, da + 6, db + 6, idesc, 1);
+                }
+                mma_commit(bar_empty0 + stage * 8); // frees the stage when these MMAs retire
+                if (++stage == stages) {
+                    stage = 0;
+                    phase ^= 1;
+                }
+            }
+            mma_commit(smem_u32(&sh.bar_acc_full[buf]));
+            continue;
+        }
+        for (int kb0 = 0; kb0 < k_blocks; kb0 += kgroup) {
             if (!mbar_wait(bar_full0 + stage * 8, phase, &sh.abort_flag, status, ERR_MMA_FULL))
                 return;
             fence_after_sync();
-            const uint64_t da = desc_a0 + (uint64_t)(stage * pitch16);
-            const uint64_t db = b_res ? desc_bres + (uint64_t)(kbi * bres_pitch16) : desc_b0 + (uint64_t)(stage * pitch16);
-            mma_i8(tmem_d, da, db, idesc, kbi != 0);
-            if (kk > 1)
-                mma_i8(tmem_d, da + 2, db + 2, idesc, 1);
-            if (kk > 2) {
-                mma_i8(tmem_d, da + 4, db + 4, idesc, 1);
-                mma_i8(tmem_d, da + 6, db + 6, idesc, 1);
+            const int cnt = min(kgroup, k_blocks - kb0);
+            uint64_t da = desc_a0 + (uint64_t)(stage * pitch16);
+            uint64_t db = b_res ? desc_bres + (uint64_t)(kb0 * bres_pitch16) : desc_b0 + (uint64_t)(stage * pitch16);
+            for (int i = 0; i < cnt; i++, da += kblock_pitch16, db += b_step16) {
+                mma_i8(tmem_d, da, db, idesc, (kb0 | i) != 0);
+                if (kk > 1)
+                    mma_i8(tmem_d, da + 2, db + 2, idesc, 1);
+                if (kk > 2) {
+                    mma_i8(tmem_d, da + 4, db + 4, idesc, 1);
+                    mma_i8(tmem_d, da + 6, db + 6, idesc, 1);
+                }
             }
             mma_commit(bar_empty0 + stage * 8); // frees the stage when these MMAs retire
             if (++stage == stages) {
@@ -1400,8 +1466,27 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
     const uint32_t k_blocks = (uint32_t)(g.taps * g.c_blocks);
     const uint32_t b_all = k_blocks * b_pitch;
     g.b_resident = g.n_tiles == 1 && b_all <= 64u * 1024u && extras + b_all + 4 * a_stage <= budget;
-    const uint32_t per_stage = a_stage + (g.b_resident ? 0u : b_pitch);
-    int stages = (int)((budget - extras - (g.b_resident ? b_all : 0u)) / per_stage);
+    const uint32_t per_kblock = a_stage + (g.b_resident ? 0u : b_pitch);
+    // Several small K blocks share a stage: the barrier round trip and the commit cost a few hundred
+    // cycles per stage whatever its size. Stages of up to 32 KB (larger K blocks already carry enough
+    // MMA work each), a count that divides the K blocks if there is one, and at least three stages.
+    const uint32_t room = budget - extras - (g.b_resident ? b_all : 0u);
+    g.kgroup = 1;
+    int fallback = 1;
+    for (uint32_t k = 4; k >= 2; k--) {
+        if (k > k_blocks || k * per_kblock > 32u * 1024u || 3 * k * per_kblock > room)
+            continue;
+        if (k_blocks % k == 0) {
+            g.kgroup = (int)k;
+            break;
+        }
+        if (fallback == 1)
+            fallback = (int)k;
+    }
+    if (g.kgroup == 1)
+        g.kgroup = fallback;
+    const uint32_t per_stage = (uint32_t)g.kgroup * per_kblock;
+    int stages = (int)(room / per_stage);
     if (stages > MAX_STAGES)
         stages = MAX_STAGES;
     if (stages < 2)
