@@ -28,7 +28,10 @@
 
 namespace nncb {
 
-constexpr int PA_D = 64, PA_PAGE = 16, PA_WARPS = 4, PA_STAGES = 3, PA_TOK = 32; // tokens per stage
+#ifndef NNCB_PA_WARPS
+#define NNCB_PA_WARPS 4
+#endif
+constexpr int PA_D = 64, PA_PAGE = 16, PA_WARPS = NNCB_PA_WARPS, PA_STAGES = 3, PA_TOK = 32; // tokens per stage
 constexpr int PA_STAGE_BYTES = PA_TOK * PA_D * 2;                                  // K or V of one stage
 
 struct PaArgs {
@@ -232,9 +235,11 @@ paged_attention_decode_kernel(const PaArgs a) {
         mrg_o[(warp * 8 + g) * PA_D + 8 * n + 2 * t + 1] = o[n][1];
     }
     __syncthreads();
-    // 128 threads: head = tid / 16, dims 4 * (tid % 16) ..
-    const int h = threadIdx.x >> 4, d0 = (threadIdx.x & 15) * 4;
-    if (h < group) {
+    // item = (head, four dims): head = item / 16, dims 4 * (item % 16) ..
+    for (int item = threadIdx.x; item < 8 * 16; item += PA_WARPS * 32) {
+        const int h = item >> 4, d0 = (item & 15) * 4;
+        if (h >= group)
+            continue;
         float M = -INFINITY;
         for (int w = 0; w < PA_WARPS; w++)
             M = fmaxf(M, mrg_m[w * 8 + h]);
@@ -255,7 +260,7 @@ paged_attention_decode_kernel(const PaArgs a) {
         } else {
             const size_t pi = ((size_t)b * a.Hq + hq) * a.splits + split;
             *reinterpret_cast<float4 *>(a.part_o + pi * PA_D + d0) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-            if ((threadIdx.x & 15) == 0) {
+            if ((item & 15) == 0) {
                 a.part_ml[pi * 2] = M;
                 a.part_ml[pi * 2 + 1] = L;
             }
@@ -290,7 +295,8 @@ int paged_attention_pick_splits(const nncb_context *ctx, int B, int Hkv, int max
     // Two CTAs fit an SM (96 KB of shared memory each). Split the context so that the grid fills
     // those slots in ONE wave -- a second, partly filled wave costs a full pass -- but keep at
     // least 8 pages (4 units) per CTA.
-    const int ctas = B * Hkv, slots = 2 * ctx->sm_count;
+    const int per_sm = (int)((227u * 1024u) / ((size_t)PA_WARPS * PA_STAGES * 2 * PA_STAGE_BYTES + 1024));
+    const int ctas = B * Hkv, slots = (per_sm > 16 ? 16 : per_sm) * ctx->sm_count;
     int s = slots / ctas;
     const int pages = (max_ctx + PA_PAGE - 1) / PA_PAGE;
     const int cap = pages / 8 > 1 ? pages / 8 : 1;
