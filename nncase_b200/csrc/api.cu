@@ -173,6 +173,11 @@ int nncb_context_create(int device, void *stream, nncb_context **out) {
     ctx->stream = (cudaStream_t)stream; // NULL is the CUDA default stream
     NNCB_CUDA_TRY(cudaMalloc(&ctx->d_status, sizeof(int)));
     NNCB_CUDA_TRY(cudaMemset(ctx->d_status, 0, sizeof(int)));
+    {
+        const size_t bytes = (size_t)nncb::GEMV_SPLIT_SLOTS * (16 * 64 * sizeof(float) + sizeof(int));
+        NNCB_CUDA_TRY(cudaMalloc(&ctx->d_gemv_ws, bytes));
+        NNCB_CUDA_TRY(cudaMemset(ctx->d_gemv_ws, 0, bytes));
+    }
     *out = ctx;
     return 0;
 }
@@ -183,6 +188,7 @@ int nncb_context_destroy(nncb_context *ctx) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     cudaFree(ctx->d_status);
+    cudaFree(ctx->d_gemv_ws);
     delete ctx;
     return 0;
 }

@@ -15,11 +15,18 @@ namespace nncb {
 
 // ---- y[m][n] = (sum_k x[m][k] * w[n][k]) * scale[n] (+ bias[n]) (+ residual[m][n]) ---------------
 // x f16 [M<=64][K], w i8 [N][K] (per-output-channel symmetric), scale f16 [N], y f16 [M][N].
-// One CTA per 16 output channels; its 8 warps split K in chunks of 64 and reduce through shared
-// memory. Tensor-core math: mma.sync m16n8k16 f16 with the weights as A (converted i8 -> f16 in
-// registers) and x^T as B. Inside a 64-wide K chunk the k index is permuted (lane t of a row owns
-// bytes 16t..16t+15) so that every lane fetches its weights with one 16-byte load per row and its
-// activations with 8-byte loads; a dot product does not care about the order of k.
+// Weight-bandwidth bound: every weight byte is read once, the activations (at most 64 x K f16) are
+// staged in shared memory once per CTA and reused for all the output channels the CTA walks
+// (persistent loop over channel blocks; K beyond the shared-memory chunk is streamed chunk by chunk).
+// Tensor-core math: mma.sync m16n8k16 f16 with the weights as A (converted i8 -> f16 in registers) and
+// x^T as B. Inside a 64-wide K chunk the k index is permuted (lane t of a row owns bytes 16t..16t+15)
+// so that every lane fetches its weights with one 16-byte load per row and its activations with
+// 8-byte shared-memory loads (row pitch = 8 mod 128 bytes: conflict-free); a dot product does not
+// care about the order of k. The next chunk's weights are in flight while the current one is
+// multiplied. Two warp arrangements: G = 8, every warp owns 16 channels of a 128-channel block and
+// walks all of K (no reduction; layers with many output channels); G = 1, the eight warps share 16
+// channels and split K, reducing through shared memory (few output channels: more CTAs, more loads
+// in flight).
 constexpr int GEMV_WARPS = 8;
 
 __device__ __forceinline__ void mma16816_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -39,62 +46,177 @@ __device__ __forceinline__ uint32_t i8x2_to_half2(uint32_t w, int pair) {
     return *reinterpret_cast<const uint32_t *>(&v);
 }
 
-template <int MT> // token tiles of 8
+constexpr int GEMV_KC_MAX = 1280; // largest K chunk of activations held in shared memory (64 x 1280 f16 = 160 KB)
+
+template <int MT, int G> // MT token tiles of 8; G channel groups per CTA (8 or 1)
 __global__ void __launch_bounds__(GEMV_WARPS * 32)
 gemv_w8a16_kernel(const __half *__restrict__ x, const int8_t *__restrict__ w, const __half *__restrict__ scale,
                   const __half *__restrict__ bias, const __half *__restrict__ residual, __half *__restrict__ y, int M,
-                  int N, int K) {
-    __shared__ float red[GEMV_WARPS][16][MT * 8 + 1];
+                  int N, int K, int KC, float *__restrict__ split_ws, int *__restrict__ split_cnt) {
+    // split_ws != null (G == 1 only): gridDim.y CTAs share a channel block, each taking one K chunk of KC;
+    // partial sums meet in split_ws ([block][K chunk][16][64] f32) and the CTA that arrives last (split_cnt,
+    // zero between launches) adds them in chunk order, finishes the block and clears the counter.
+    extern __shared__ __align__(16) uint8_t gemv_smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int n0 = blockIdx.x * 16;
-    float acc[MT][4];
+    const int pitch = KC * 2 + 8; // bytes per token row
+    float(*red)[16][MT * 8 + 1] = reinterpret_cast<float(*)[16][MT * 8 + 1]>(gemv_smem + (size_t)MT * 8 * pitch);
+    const int nblk = (N + 16 * G - 1) / (16 * G);
+    const bool split = G == 1 && split_ws != nullptr;
+    const int k_begin = split ? (int)blockIdx.y * KC : 0, k_end = split ? min(K, k_begin + KC) : K;
+    const bool resident = split || K <= KC;
+
+    auto stage_x = [&](int kc0, int len) {
+        const int per_row = len / 8; // 16-byte pieces
+        for (int idx = threadIdx.x; idx < MT * 8 * per_row; idx += GEMV_WARPS * 32) {
+            const int tok = idx / per_row, c8 = idx % per_row;
+            const uint4 v = __ldg(reinterpret_cast<const uint4 *>(x + (size_t)min(tok, M - 1) * K + kc0) + c8);
+            uint2 *dst = reinterpret_cast<uint2 *>(gemv_smem + (size_t)tok * pitch + c8 * 16);
+            dst[0] = make_uint2(v.x, v.y);
+            dst[1] = make_uint2(v.z, v.w);
+        }
+    };
+    if (resident) {
+        stage_x(k_begin, k_end - k_begin);
+        __syncthreads();
+    }
+    for (int blk = blockIdx.x; blk < nblk; blk += gridDim.x) {
+        float acc[MT][4];
 #pragma unroll
-    for (int i = 0; i < MT; i++)
-        acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-    const int r0 = min(n0 + g, N - 1), r1 = min(n0 + g + 8, N - 1); // clamped rows of a partial last block
-    const int chunks = K / 64;
-    for (int ch = warp; ch < chunks; ch += GEMV_WARPS) {
-        const int k0 = ch * 64 + 16 * t;
-        const uint4 wa = __ldg(reinterpret_cast<const uint4 *>(w + (size_t)r0 * K + k0));
-        const uint4 wb = __ldg(reinterpret_cast<const uint4 *>(w + (size_t)r1 * K + k0));
-        const uint32_t wav[4] = {wa.x, wa.y, wa.z, wa.w}, wbv[4] = {wb.x, wb.y, wb.z, wb.w};
+        for (int i = 0; i < MT; i++)
+            acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+        const int n0 = blk * 16 * G + (G == 1 ? 0 : warp * 16);
+        const int r0 = min(n0 + g, N - 1), r1 = min(n0 + g + 8, N - 1); // clamped rows of a partial last block
+        const int8_t *w0 = w + (size_t)r0 * K + 16 * t, *w1 = w + (size_t)r1 * K + 16 * t;
+        for (int kc0 = k_begin; kc0 < k_end; kc0 += KC) {
+            const int len = min(KC, k_end - kc0);
+            if (!resident) {
+                __syncthreads(); // the previous chunk has been consumed
+                stage_x(kc0, len);
+                __syncthreads();
+            }
+            const int chunks = len / 64;
+            const int c_first = G == 1 ? warp : 0, c_step = G == 1 ? GEMV_WARPS : 1;
+            // PF chunks of weights are in flight per warp (1 KB each): the loop is a stream of dependent
+            // loads otherwise, one memory latency per chunk
+            constexpr int PF = 4;
+            uint4 pa[PF], pb[PF];
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const uint32_t a0 = i8x2_to_half2(wav[j], 0), a2 = i8x2_to_half2(wav[j], 1);
-            const uint32_t a1 = i8x2_to_half2(wbv[j], 0), a3 = i8x2_to_half2(wbv[j], 1);
+            for (int p = 0; p < PF; p++) {
+                const int c = c_first + p * c_step;
+                pa[p] = pb[p] = make_uint4(0, 0, 0, 0);
+                if (c < chunks) {
+                    pa[p] = __ldg(reinterpret_cast<const uint4 *>(w0 + kc0 + c * 64));
+                    pb[p] = __ldg(reinterpret_cast<const uint4 *>(w1 + kc0 + c * 64));
+                }
+            }
+            for (int ch0 = c_first; ch0 < chunks; ch0 += PF * c_step) {
 #pragma unroll
-            for (int i = 0; i < MT; i++) {
-                const int tok = min(8 * i + g, M - 1);
-                const uint2 b = __ldg(reinterpret_cast<const uint2 *>(x + (size_t)tok * K + k0 + 4 * j));
-                mma16816_f16(acc[i], a0, a1, a2, a3, b.x, b.y);
+                for (int p = 0; p < PF; p++) {
+                    const int ch = ch0 + p * c_step;
+                    if (ch >= chunks)
+                        break;
+                    const uint4 wa = pa[p], wb = pb[p];
+                    const int nxt = ch + PF * c_step;
+                    if (nxt < chunks) {
+                        pa[p] = __ldg(reinterpret_cast<const uint4 *>(w0 + kc0 + nxt * 64));
+                        pb[p] = __ldg(reinterpret_cast<const uint4 *>(w1 + kc0 + nxt * 64));
+                    }
+                    const uint32_t wav[4] = {wa.x, wa.y, wa.z, wa.w}, wbv[4] = {wb.x, wb.y, wb.z, wb.w};
+                    const uint8_t *xrow = gemv_smem + (size_t)g * pitch + (ch * 64 + 16 * t) * 2;
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const uint32_t a0 = i8x2_to_half2(wav[j], 0), a2 = i8x2_to_half2(wav[j], 1);
+                        const uint32_t a1 = i8x2_to_half2(wbv[j], 0), a3 = i8x2_to_half2(wbv[j], 1);
+#pragma unroll
+                        for (int i = 0; i < MT; i++) {
+                            const uint2 bfrag = *reinterpret_cast<const uint2 *>(xrow + (size_t)(8 * i) * pitch + 8 * j);
+                            mma16816_f16(acc[i], a0, a1, a2, a3, bfrag.x, bfrag.y);
+                        }
+                    }
+                }
             }
         }
-    }
+        if (G == 1) {
 #pragma unroll
-    for (int i = 0; i < MT; i++) {
-        red[warp][g][8 * i + 2 * t] = acc[i][0];
-        red[warp][g][8 * i + 2 * t + 1] = acc[i][1];
-        red[warp][g + 8][8 * i + 2 * t] = acc[i][2];
-        red[warp][g + 8][8 * i + 2 * t + 1] = acc[i][3];
-    }
-    __syncthreads();
-    // 256 threads: thread -> (token, 16 channels as 4 groups of 4)
-    for (int idx = threadIdx.x; idx < MT * 8 * 16; idx += GEMV_WARPS * 32) {
-        const int tok = idx / 16, r = idx % 16;
-        const int n = n0 + r;
-        if (tok >= M || n >= N)
-            continue;
-        float s = 0.f;
+            for (int i = 0; i < MT; i++) {
+                red[warp][g][8 * i + 2 * t] = acc[i][0];
+                red[warp][g][8 * i + 2 * t + 1] = acc[i][1];
+                red[warp][g + 8][8 * i + 2 * t] = acc[i][2];
+                red[warp][g + 8][8 * i + 2 * t + 1] = acc[i][3];
+            }
+            __syncthreads();
+            bool finish = true;
+            if (split) {
+                // publish this CTA's K slice in its own slot, then see whether every slice of the block has
+                // arrived (slots instead of atomic adds: the sum below has a fixed order)
+                float *ws = split_ws + ((size_t)blk * gridDim.y + blockIdx.y) * 16 * 64;
+                for (int idx = threadIdx.x; idx < MT * 8 * 16; idx += GEMV_WARPS * 32) {
+                    const int tok = idx / 16, r = idx % 16;
+                    float s = 0.f;
 #pragma unroll
-        for (int wv = 0; wv < GEMV_WARPS; wv++)
-            s += red[wv][r][tok];
-        float v = s * __half2float(scale[n]);
-        if (bias)
-            v += __half2float(bias[n]);
-        if (residual)
-            v += __half2float(residual[(size_t)tok * N + n]);
-        y[(size_t)tok * N + n] = __float2half_rn(v);
+                    for (int wv = 0; wv < GEMV_WARPS; wv++)
+                        s += red[wv][r][tok];
+                    ws[r * 64 + tok] = s;
+                }
+                __shared__ int s_last;
+                __threadfence();
+                __syncthreads();
+                if (threadIdx.x == 0)
+                    s_last = atomicAdd(split_cnt + blk, 1) == (int)gridDim.y - 1;
+                __syncthreads();
+                finish = s_last != 0;
+                if (finish)
+                    __threadfence();
+            }
+            // thread -> (token, channel)
+            for (int idx = threadIdx.x; finish && idx < MT * 8 * 16; idx += GEMV_WARPS * 32) {
+                const int tok = idx / 16, r = idx % 16;
+                const int n = n0 + r;
+                float s = 0.f;
+                if (split) {
+                    const float *cell = split_ws + (size_t)blk * gridDim.y * 16 * 64 + r * 64 + tok;
+                    for (int ks = 0; ks < (int)gridDim.y; ks++)
+                        s += __ldcg(cell + (size_t)ks * 16 * 64);
+                } else {
+#pragma unroll
+                    for (int wv = 0; wv < GEMV_WARPS; wv++)
+                        s += red[wv][r][tok];
+                }
+                if (tok >= M || n >= N)
+                    continue;
+                float v = s * __half2float(scale[n]);
+                if (bias)
+                    v += __half2float(bias[n]);
+                if (residual)
+                    v += __half2float(residual[(size_t)tok * N + n]);
+                y[(size_t)tok * N + n] = __float2half_rn(v);
+            }
+            if (split && finish && threadIdx.x == 0)
+                split_cnt[blk] = 0;
+            __syncthreads(); // red is reused by the next block
+        } else {
+            // this warp's 16 channels x all tokens: accumulator (row = channel g / g + 8, column = token 2t, 2t + 1)
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int n = n0 + g + 8 * h;
+                if (n >= N)
+                    continue;
+                const float sc = __half2float(scale[n]), bi = bias ? __half2float(bias[n]) : 0.f;
+#pragma unroll
+                for (int i = 0; i < MT; i++)
+#pragma unroll
+                    for (int e = 0; e < 2; e++) {
+                        const int tok = 8 * i + 2 * t + e;
+                        if (tok >= M)
+                            continue;
+                        float v = acc[i][2 * h + e] * sc + bi;
+                        if (residual)
+                            v += __half2float(residual[(size_t)tok * N + n]);
+                        y[(size_t)tok * N + n] = __float2half_rn(v);
+                    }
+            }
+        }
     }
 }
 
@@ -108,18 +230,52 @@ int gemv_w8a16(nncb_context *ctx, const void *x, const int8_t *w, const void *sc
         return fail(-ENOSYS, "gemv_w8a16: K must be a multiple of 64");
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15)
         return fail(-EINVAL, "gemv_w8a16: x and w must be 16-byte aligned");
-    const int grid = (N + 15) / 16;
     const __half *xs = (const __half *)x, *sc = (const __half *)scale, *bi = (const __half *)bias,
                  *re = (const __half *)residual;
     __half *ys = (__half *)y;
-    const int mt = (M + 7) / 8;
-    switch (mt) {
-    case 1: gemv_w8a16_kernel<1><<<grid, GEMV_WARPS * 32, 0, ctx->stream>>>(xs, w, sc, bi, re, ys, M, N, K); break;
-    case 2: gemv_w8a16_kernel<2><<<grid, GEMV_WARPS * 32, 0, ctx->stream>>>(xs, w, sc, bi, re, ys, M, N, K); break;
-    case 3:
-    case 4: gemv_w8a16_kernel<4><<<grid, GEMV_WARPS * 32, 0, ctx->stream>>>(xs, w, sc, bi, re, ys, M, N, K); break;
-    default: gemv_w8a16_kernel<8><<<grid, GEMV_WARPS * 32, 0, ctx->stream>>>(xs, w, sc, bi, re, ys, M, N, K); break;
+    const int mt = (M + 7) / 8, mtt = mt <= 1 ? 1 : (mt <= 2 ? 2 : (mt <= 4 ? 4 : 8));
+    const int KC = K <= GEMV_KC_MAX ? K : 1024;
+    // many output channels: each warp owns 16 of them; few: the warps split K so that more CTAs carry loads
+    const bool wide = N >= 2048;
+    const int nblk = (N + (wide ? 127 : 15)) / (wide ? 128 : 16);
+    size_t smem = (size_t)mtt * 8 * (KC * 2 + 8);
+    if (!wide)
+        smem += sizeof(float) * GEMV_WARPS * 16 * (mtt * 8 + 1);
+    const int per_sm = (int)((227u * 1024u) / (smem + 1024));
+    const int slots = (per_sm < 1 ? 1 : (per_sm > 4 ? 4 : per_sm)) * ctx->sm_count;
+    // A long K with few output channels (the down projection): the K chunks go to different CTAs, which
+    // meet in the context's f32 workspace; otherwise one CTA per channel block walks K itself.
+    const int k_splits = (K + KC - 1) / KC;
+    const bool split = !wide && k_splits > 1 && nblk * k_splits <= GEMV_SPLIT_SLOTS && ctx->d_gemv_ws != nullptr;
+    dim3 grid(nblk < slots ? nblk : slots, 1, 1);
+    float *ws = nullptr;
+    int *cnt = nullptr;
+    if (split) {
+        grid = dim3(nblk, k_splits, 1);
+        ws = ctx->d_gemv_ws;
+        cnt = reinterpret_cast<int *>(ctx->d_gemv_ws + (size_t)GEMV_SPLIT_SLOTS * 16 * 64);
     }
+#define NNCB_GEMV(MT_, G_)                                                                                            \
+    do {                                                                                                              \
+        static bool attr_done = false;                                                                                \
+        if (!attr_done) {                                                                                             \
+            NNCB_CUDA_TRY(cudaFuncSetAttribute(gemv_w8a16_kernel<MT_, G_>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                               226 * 1024));                                                          \
+            attr_done = true;                                                                                         \
+        }                                                                                                             \
+        gemv_w8a16_kernel<MT_, G_><<<grid, GEMV_WARPS * 32, smem, ctx->stream>>>(xs, w, sc, bi, re, ys, M, N, K, KC, ws, cnt);  \
+    } while (0)
+    switch (mtt * 2 + (wide ? 1 : 0)) {
+    case 2: NNCB_GEMV(1, 1); break;
+    case 3: NNCB_GEMV(1, 8); break;
+    case 4: NNCB_GEMV(2, 1); break;
+    case 5: NNCB_GEMV(2, 8); break;
+    case 8: NNCB_GEMV(4, 1); break;
+    case 9: NNCB_GEMV(4, 8); break;
+    case 16: NNCB_GEMV(8, 1); break;
+    default: NNCB_GEMV(8, 8); break;
+    }
+#undef NNCB_GEMV
     return after_launch(ctx, "gemv_w8a16");
 }
 

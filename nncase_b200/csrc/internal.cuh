@@ -16,9 +16,12 @@ struct nncb_context {
     uint64_t launches = 0;
     int sm_count = 148;
     int *d_status = nullptr;  // device word: 0 ok, else code of the first bounded wait that gave up
+    float *d_gemv_ws = nullptr; // split-K meeting place of gemv_w8a16: GEMV_SPLIT_SLOTS x 16 x 64 f32 + one counter per slot, counters zero between launches
 };
 
 namespace nncb {
+
+constexpr int GEMV_SPLIT_SLOTS = 512; // (channel block, K chunk) slots of 16 x 64 f32 in a context's split-K workspace
 
 std::string &last_error();
 int fail(int code, const char *fmt, ...);
