@@ -203,6 +203,11 @@ NNCB_API int nncb_qconv2d_host(nncb_context *ctx, const nncb_conv2d_desc *desc, 
  *   swiglu:      out[m][j] = f16( silu(gate_up[m][j]) * gate_up[m][inter + j] )
  *   embedding:   out[m][:] = table[ids[m]][:] */
 NNCB_API int nncb_gemv_w8a16(nncb_context *ctx, const void *x, const int8_t *w, const void *scale, const void *bias, const void *residual, void *y, int m, int n, int k);
+/* The gate/up MatMul with SwiGLU in its epilogue: the n weight rows come in blocks of 16 = the gate rows of 8
+ * outputs followed by their up rows (scale and bias ordered alike), y is [m][n / 2] and
+ * y[m][8 b + r] = f16( silu(f16(gate)) * f16(up) ) for rows r and r + 8 of block b: bit-identical to
+ * nncb_gemv_w8a16 followed by nncb_swiglu_f16 on the un-interleaved rows, without the [m][n] round trip. */
+NNCB_API int nncb_gemv_w8a16_swiglu(nncb_context *ctx, const void *x, const int8_t *w, const void *scale, const void *bias, void *y, int m, int n, int k);
 NNCB_API int nncb_add_rmsnorm_f16(nncb_context *ctx, void *x, const void *delta, const void *weight, void *h, int rows, int cols, float eps);
 NNCB_API int nncb_rope_kv_append_f16(nncb_context *ctx, const void *qkv, void *q_out, const float *cos_table, const float *sin_table, const int32_t *positions, const int32_t *block_table, void *k_pool, void *v_pool, int batch, int q_heads, int kv_heads, int head_dim, int page_size, int max_pages);
 NNCB_API int nncb_swiglu_f16(nncb_context *ctx, const void *gate_up, void *out, int rows, int inter);

@@ -125,6 +125,7 @@ int paged_attention_launch(nncb_context *ctx, const void *q, const void *k_pool,
                            int max_pages, float scale, int splits, void *scratch);
 
 int gemv_w8a16(nncb_context *, const void *, const int8_t *, const void *, const void *, const void *, void *, int, int, int);
+int gemv_w8a16_swiglu(nncb_context *, const void *, const int8_t *, const void *, const void *, void *, int, int, int);
 int add_rmsnorm_f16(nncb_context *, void *, const void *, const void *, void *, int, int, float);
 int rope_kv_append_f16(nncb_context *, const void *, void *, const float *, const float *, const int32_t *,
                        const int32_t *, void *, void *, int, int, int, int, int, int);
@@ -454,6 +455,13 @@ int nncb_gemv_w8a16(nncb_context *ctx, const void *x, const int8_t *w, const voi
     if (!x || !w || !scale || !y)
         return fail(-EINVAL, "nncb_gemv_w8a16: null pointer");
     return gemv_w8a16(ctx, x, w, scale, bias, residual, y, m, n, k);
+}
+int nncb_gemv_w8a16_swiglu(nncb_context *ctx, const void *x, const int8_t *w, const void *scale, const void *bias, void *y,
+                           int m, int n, int k) {
+    CHECK_CTX(ctx);
+    if (!x || !w || !scale || !y)
+        return fail(-EINVAL, "nncb_gemv_w8a16_swiglu: null pointer");
+    return gemv_w8a16_swiglu(ctx, x, w, scale, bias, y, m, n, k);
 }
 int nncb_add_rmsnorm_f16(nncb_context *ctx, void *x, const void *delta, const void *weight, void *h, int rows, int cols, float eps) {
     CHECK_CTX(ctx);

@@ -46,13 +46,20 @@ __device__ __forceinline__ uint32_t i8x2_to_half2(uint32_t w, int pair) {
     return *reinterpret_cast<const uint32_t *>(&v);
 }
 
+// SwiGLU folded into the MatMul's epilogue (swiglu != 0): the weight rows come in blocks of 16 = the gate
+// rows of 8 outputs followed by their up rows, y has n / 2 columns and
+// y[m][8 * block + r] = f16(silu(f16(gate)) * f16(up)) -- the gate/up activations never go to memory.
+struct GemvFusion {
+    int swiglu;
+};
+
 constexpr int GEMV_KC_MAX = 1280; // largest K chunk of activations held in shared memory (64 x 1280 f16 = 160 KB)
 
 template <int MT, int G> // MT token tiles of 8; G channel groups per CTA (8 or 1)
 __global__ void __launch_bounds__(GEMV_WARPS * 32)
 gemv_w8a16_kernel(const __half *__restrict__ x, const int8_t *__restrict__ w, const __half *__restrict__ scale,
                   const __half *__restrict__ bias, const __half *__restrict__ residual, __half *__restrict__ y, int M,
-                  int N, int K, int KC, float *__restrict__ split_ws, int *__restrict__ split_cnt) {
+                  int N, int K, int KC, float *__restrict__ split_ws, int *__restrict__ split_cnt, const GemvFusion fu) {
     // split_ws != null (G == 1 only): gridDim.y CTAs share a channel block, each taking one K chunk of KC;
     // partial sums meet in split_ws ([block][K chunk][16][64] f32) and the CTA that arrives last (split_cnt,
     // zero between launches) adds them in chunk order, finishes the block and clears the counter.
@@ -188,15 +195,50 @@ gemv_w8a16_kernel(const __half *__restrict__ x, const int8_t *__restrict__ w, co
                 float v = s * __half2float(scale[n]);
                 if (bias)
                     v += __half2float(bias[n]);
+                if (fu.swiglu) {
+                    // rows 0..7 of the block are gates, 8..15 the matching ups: pair them through shared memory
+                    red[0][r][tok] = __half2float(__float2half_rn(v));
+                    continue;
+                }
                 if (residual)
                     v += __half2float(residual[(size_t)tok * N + n]);
                 y[(size_t)tok * N + n] = __float2half_rn(v);
+            }
+            if (fu.swiglu && finish) {
+                __syncthreads();
+                for (int idx = threadIdx.x; idx < MT * 8 * 8; idx += GEMV_WARPS * 32) {
+                    const int tok = idx / 8, r = idx % 8;
+                    if (tok >= M || n0 + r + 8 >= N)
+                        continue;
+                    const float gt = red[0][r][tok], up = red[0][r + 8][tok];
+                    y[(size_t)tok * (N / 2) + blk * 8 + r] = __float2half_rn(gt / (1.0f + expf(-gt)) * up);
+                }
             }
             if (split && finish && threadIdx.x == 0)
                 split_cnt[blk] = 0;
             __syncthreads(); // red is reused by the next block
         } else {
             // this warp's 16 channels x all tokens: accumulator (row = channel g / g + 8, column = token 2t, 2t + 1)
+            if (fu.swiglu) {
+                // accumulator rows g (gate) and g + 8 (up) of this warp's 16-row block belong to one output
+                const int ng = n0 + g, nu = n0 + g + 8;
+                if (nu < N) {
+                    const float sg_ = __half2float(scale[ng]), su = __half2float(scale[nu]);
+                    const float bg = bias ? __half2float(bias[ng]) : 0.f, bu = bias ? __half2float(bias[nu]) : 0.f;
+#pragma unroll
+                    for (int i = 0; i < MT; i++)
+#pragma unroll
+                        for (int e = 0; e < 2; e++) {
+                            const int tok = 8 * i + 2 * t + e;
+                            if (tok >= M)
+                                continue;
+                            const float gt = __half2float(__float2half_rn(acc[i][e] * sg_ + bg));
+                            const float up = __half2float(__float2half_rn(acc[i][2 + e] * su + bu));
+                            y[(size_t)tok * (N / 2) + (n0 >> 1) + g] = __float2half_rn(gt / (1.0f + expf(-gt)) * up);
+                        }
+                }
+                continue;
+            }
 #pragma unroll
             for (int h = 0; h < 2; h++) {
                 const int n = n0 + g + 8 * h;
@@ -220,8 +262,25 @@ gemv_w8a16_kernel(const __half *__restrict__ x, const int8_t *__restrict__ w, co
     }
 }
 
+static int gemv_w8a16_fused(nncb_context *ctx, const void *x, const int8_t *w, const void *scale, const void *bias,
+                            const void *residual, void *y, int M, int N, int K, const GemvFusion &fu);
+
 int gemv_w8a16(nncb_context *ctx, const void *x, const int8_t *w, const void *scale, const void *bias,
                const void *residual, void *y, int M, int N, int K) {
+    GemvFusion fu = {0};
+    return gemv_w8a16_fused(ctx, x, w, scale, bias, residual, y, M, N, K, fu);
+}
+
+int gemv_w8a16_swiglu(nncb_context *ctx, const void *x, const int8_t *w, const void *scale, const void *bias, void *y,
+                      int M, int N, int K) {
+    if (N % 16 != 0)
+        return fail(-EINVAL, "gemv_w8a16_swiglu: gate/up rows come in blocks of 16");
+    GemvFusion fu = {1};
+    return gemv_w8a16_fused(ctx, x, w, scale, bias, nullptr, y, M, N, K, fu);
+}
+
+static int gemv_w8a16_fused(nncb_context *ctx, const void *x, const int8_t *w, const void *scale, const void *bias,
+                            const void *residual, void *y, int M, int N, int K, const GemvFusion &fu) {
     if (M <= 0 || N <= 0 || K <= 0)
         return fail(-EINVAL, "gemv_w8a16: non-positive dimension");
     if (M > 64)
@@ -263,7 +322,7 @@ int gemv_w8a16(nncb_context *ctx, const void *x, const int8_t *w, const void *sc
                                                226 * 1024));                                                          \
             attr_done = true;                                                                                         \
         }                                                                                                             \
-        gemv_w8a16_kernel<MT_, G_><<<grid, GEMV_WARPS * 32, smem, ctx->stream>>>(xs, w, sc, bi, re, ys, M, N, K, KC, ws, cnt);  \
+        gemv_w8a16_kernel<MT_, G_><<<grid, GEMV_WARPS * 32, smem, ctx->stream>>>(xs, w, sc, bi, re, ys, M, N, K, KC, ws, cnt, fu);  \
     } while (0)
     switch (mtt * 2 + (wide ? 1 : 0)) {
     case 2: NNCB_GEMV(1, 1); break;
@@ -282,6 +341,67 @@ int gemv_w8a16(nncb_context *ctx, const void *x, const int8_t *w, const void *sc
 // ---- RMSNorm, optionally fused with the residual add ---------------------------------------------
 //   if delta: x <- f16(x + delta)  (written back);  h = f16( x * rsqrt(mean(x^2) + eps) * w )
 // one CTA of 128 threads per row; f32 statistics.
+// The row stays in registers between the statistics and the scaling (one read of x and delta); rows longer
+// than 128 x 16 elements take the general kernel below.
+__global__ void __launch_bounds__(128)
+add_rmsnorm_row_kernel(__half *__restrict__ x, const __half *__restrict__ delta, const __half *__restrict__ w,
+                       __half *__restrict__ h, int cols, float eps) {
+    __shared__ float part[4];
+    const size_t row = blockIdx.x;
+    uint2 *xr = reinterpret_cast<uint2 *>(x + row * cols);
+    const uint2 *dr = reinterpret_cast<const uint2 *>(delta + row * cols);
+    const int pieces = cols / 4; // 8-byte pieces, at most 4 per thread
+    uint2 v[4];
+    float ss = 0.f;
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+        const int pc = threadIdx.x + 128 * q;
+        v[q] = make_uint2(0, 0);
+        if (pc < pieces) {
+            v[q] = xr[pc];
+            __half2 *hv = reinterpret_cast<__half2 *>(&v[q]);
+            if (delta) {
+                const uint2 d = __ldg(dr + pc);
+                const __half2 *dv = reinterpret_cast<const __half2 *>(&d);
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const float2 a = __half22float2(hv[e]), b2 = __half22float2(dv[e]);
+                    hv[e] = __floats2half2_rn(a.x + b2.x, a.y + b2.y);
+                }
+                xr[pc] = v[q];
+            }
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const float2 a = __half22float2(hv[e]);
+                ss += a.x * a.x + a.y * a.y;
+            }
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1)
+        ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0)
+        part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    const float inv = rsqrtf((part[0] + part[1] + part[2] + part[3]) / (float)cols + eps);
+    uint2 *hr = reinterpret_cast<uint2 *>(h + row * cols);
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+        const int pc = threadIdx.x + 128 * q;
+        if (pc < pieces) {
+            const uint2 gm = __ldg(reinterpret_cast<const uint2 *>(w) + pc);
+            const __half2 *hv = reinterpret_cast<const __half2 *>(&v[q]), *gv = reinterpret_cast<const __half2 *>(&gm);
+            uint2 o2;
+            __half2 *ov = reinterpret_cast<__half2 *>(&o2);
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const float2 a = __half22float2(hv[e]), gg = __half22float2(gv[e]);
+                ov[e] = __floats2half2_rn(a.x * inv * gg.x, a.y * inv * gg.y);
+            }
+            hr[pc] = o2;
+        }
+    }
+}
+
 __global__ void __launch_bounds__(128)
 add_rmsnorm_kernel(__half *__restrict__ x, const __half *__restrict__ delta, const __half *__restrict__ w,
                    __half *__restrict__ h, int cols, float eps) {
@@ -311,8 +431,14 @@ add_rmsnorm_kernel(__half *__restrict__ x, const __half *__restrict__ delta, con
 int add_rmsnorm_f16(nncb_context *ctx, void *x, const void *delta, const void *w, void *h, int rows, int cols, float eps) {
     if (rows <= 0 || cols <= 0)
         return fail(-EINVAL, "rmsnorm: non-positive dimension");
-    add_rmsnorm_kernel<<<rows, 128, 0, ctx->stream>>>((__half *)x, (const __half *)delta, (const __half *)w, (__half *)h,
-                                                       cols, eps);
+    const bool al8 = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(delta) | reinterpret_cast<uintptr_t>(w) |
+                       reinterpret_cast<uintptr_t>(h)) & 7) == 0;
+    if (cols % 4 == 0 && cols <= 2048 && al8)
+        add_rmsnorm_row_kernel<<<rows, 128, 0, ctx->stream>>>((__half *)x, (const __half *)delta, (const __half *)w,
+                                                               (__half *)h, cols, eps);
+    else
+        add_rmsnorm_kernel<<<rows, 128, 0, ctx->stream>>>((__half *)x, (const __half *)delta, (const __half *)w, (__half *)h,
+                                                           cols, eps);
     return after_launch(ctx, "add_rmsnorm");
 }
 

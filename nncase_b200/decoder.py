@@ -101,6 +101,16 @@ def shard_weights(cfg, w, world, rank):
                 lm_head=rows(w["lm_head"], slice(rank * vv, (rank + 1) * vv)))
 
 
+def interleave_gate_up(wq, scale):
+    """[gate rows (inter) | up rows (inter)] -> blocks of 16 rows: the gate rows of 8 outputs, then their up
+    rows -- the order nncb_gemv_w8a16_swiglu expects. inter must be a multiple of 8."""
+    inter = wq.shape[0] // 2
+    assert inter % 8 == 0
+    idx = np.arange(inter).reshape(-1, 8)
+    order = np.concatenate([idx, idx + inter], axis=1).reshape(-1)
+    return np.ascontiguousarray(wq[order]), np.ascontiguousarray(scale[order])
+
+
 class Decoder:
     """One tensor-parallel rank of the decoder (world 1 = the whole model)."""
 
@@ -116,6 +126,7 @@ class Decoder:
         self.hq, self.hkv = cfg.q_heads // world, cfg.kv_heads // world
         self.inter = cfg.inter // world
         for lw in w["layers"]:
+            lw = dict(lw, gate_up=interleave_gate_up(*lw["gate_up"]))  # SwiGLU runs in the gate/up MatMul's epilogue
             self.layers.append(dict(
                 ln1=t(lw["ln1"]), ln2=t(lw["ln2"]), qkv_w=t(lw["qkv"][0]), qkv_s=t(lw["qkv"][1]), qkv_b=t(lw["qkv_bias"]),
                 o_w=t(lw["o"][0]), o_s=t(lw["o"][1]), gu_w=t(lw["gate_up"][0]), gu_s=t(lw["gate_up"][1]),
@@ -131,7 +142,6 @@ class Decoder:
         self.q = torch.empty((B, self.hq * D), **f16)
         self.attn = torch.empty((B, self.hq * D), **f16)
         self.proj = torch.empty((B, H), **f16)
-        self.gu = torch.empty((B, 2 * self.inter), **f16)
         self.act = torch.empty((B, self.inter), **f16)
         self.logits = torch.empty((B, cfg.vocab // world), **f16)
         self.ws = torch.empty(4 << 20, dtype=torch.uint8, device=dev)
@@ -142,6 +152,11 @@ class Decoder:
         lib, h = self.ctx._lib, self.ctx._h
         check(lib.nncb_gemv_w8a16(h, x.data_ptr(), w.data_ptr(), s.data_ptr(), b.data_ptr() if b is not None else None,
                                   None, y.data_ptr(), x.shape[0], w.shape[0], w.shape[1]))
+
+    def _gemv_swiglu(self, x, w, s, y):
+        """y = swiglu(gemv(x)) over interleaved gate/up rows (SwiGLU in the MatMul's epilogue)."""
+        check(self.ctx._lib.nncb_gemv_w8a16_swiglu(self.ctx._h, x.data_ptr(), w.data_ptr(), s.data_ptr(), None, y.data_ptr(),
+                                                   x.shape[0], w.shape[0], w.shape[1]))
 
     def _norm(self, x, delta, w, out):
         check(self.ctx._lib.nncb_add_rmsnorm_f16(self.ctx._h, x.data_ptr(), delta.data_ptr() if delta is not None else None,
@@ -159,8 +174,8 @@ class Decoder:
         B = token_ids.shape[0]
         if B > self.max_batch:
             raise NncbError(-22, "batch larger than planned")
-        x, hh, qkv, q, attn, proj, gu, act = (self.x[:B], self.h[:B], self.qkv[:B], self.q[:B], self.attn[:B],
-                                              self.proj[:B], self.gu[:B], self.act[:B])
+        x, hh, qkv, q, attn, proj, act = (self.x[:B], self.h[:B], self.qkv[:B], self.q[:B], self.attn[:B], self.proj[:B],
+                                          self.act[:B])
         ctx_lens = positions + 1
         check(lib.nncb_embedding_f16(h, self.embed.data_ptr(), token_ids.data_ptr(), x.data_ptr(), B, cfg.hidden, cfg.vocab))
         delta = None
@@ -179,8 +194,7 @@ class Decoder:
             self._gemv(attn, lw["o_w"], lw["o_s"], None, proj)
             self._all_reduce(proj)
             self._norm(x, proj, lw["ln2"], hh)
-            self._gemv(hh, lw["gu_w"], lw["gu_s"], None, gu)
-            check(lib.nncb_swiglu_f16(h, gu.data_ptr(), act.data_ptr(), B, self.inter))
+            self._gemv_swiglu(hh, lw["gu_w"], lw["gu_s"], act)
             self._gemv(act, lw["d_w"], lw["d_s"], None, proj)
             self._all_reduce(proj)
             delta = proj

@@ -93,6 +93,7 @@ SIGNATURES = {
     "nncb_qconv2d_out_shape": (_I, [_VP, C.POINTER(_I), C.POINTER(_I)]),
     "nncb_qconv2d_run": (_I, [_VP, _VP, _VP, _VP, _VP, _VP]),
     "nncb_gemv_w8a16": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I]),
+    "nncb_gemv_w8a16_swiglu": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I]),
     "nncb_add_rmsnorm_f16": (_I, [_VP, _VP, _VP, _VP, _VP, _I, _I, _F]),
     "nncb_rope_kv_append_f16": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I]),
     "nncb_swiglu_f16": (_I, [_VP, _VP, _VP, _I, _I]),

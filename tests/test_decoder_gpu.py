@@ -37,6 +37,32 @@ def test_gemv_w8a16(ctx, m, n, k):
     close(y.cpu().numpy(), OD.gemv_w8a16(x, wq, s))
 
 
+@pytest.mark.parametrize("m,inter,k", [(64, 4864, 896), (64, 2432, 896), (5, 24, 128), (33, 1024, 1280), (64, 64, 4864)])
+def test_gemv_with_swiglu_epilogue(ctx, m, inter, k):
+    """The gate/up MatMul with SwiGLU in its epilogue, on interleaved gate/up rows: bit-identical to the
+    MatMul followed by swiglu (the same f16 gate/up values meet the same f32 formula)."""
+    rng = np.random.default_rng(m + inter + k)
+    x = rng.normal(0, 1, (m, k)).astype(np.float16)
+    wq, s = D.quantize_per_channel_i8(rng.normal(0, 0.02, (2 * inter, k)).astype(np.float32))
+    wi, si = D.interleave_gate_up(wq, s)
+    t = lambda a: torch.from_numpy(a).cuda()
+    xd, wid, sid, wd, sd = t(x), t(wi), t(si), t(wq), t(s)
+    y = torch.empty((m, inter), dtype=torch.float16, device="cuda")
+    L.check(ctx._lib.nncb_gemv_w8a16_swiglu(ctx._h, xd.data_ptr(), wid.data_ptr(), sid.data_ptr(), None, y.data_ptr(), m,
+                                            2 * inter, k))
+    gu = torch.empty((m, 2 * inter), dtype=torch.float16, device="cuda")
+    L.check(ctx._lib.nncb_gemv_w8a16(ctx._h, xd.data_ptr(), wd.data_ptr(), sd.data_ptr(), None, None, gu.data_ptr(), m, 2 * inter, k))
+    act = torch.empty_like(y)
+    L.check(ctx._lib.nncb_swiglu_f16(ctx._h, gu.data_ptr(), act.data_ptr(), m, inter))
+    assert torch.equal(y, act)
+    close(y.cpu().numpy(), OD.swiglu(OD.gemv_w8a16(x, wq, s), inter))
+    # a second call finds the split-K counters cleared by the first (k = 4864 takes the split path)
+    y2 = torch.empty_like(y)
+    L.check(ctx._lib.nncb_gemv_w8a16_swiglu(ctx._h, xd.data_ptr(), wid.data_ptr(), sid.data_ptr(), None, y2.data_ptr(), m,
+                                            2 * inter, k))
+    assert torch.equal(y, y2)
+
+
 def test_gemv_rejects_unsupported(ctx):
     z = torch.zeros(1 << 16, dtype=torch.float16, device="cuda")
     w = torch.zeros(1 << 16, dtype=torch.int8, device="cuda")
