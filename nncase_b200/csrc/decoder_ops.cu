@@ -6,8 +6,8 @@
 // f16 storage between operators.
 //
 // At batch 64 every one of these is tiny next to the KV-cache read of the attention kernel: a
-// layer's weights are 15 MB (2.3 us of HBM time), so the design goal here is few, simple,
-// latency-tolerant launches that capture into one CUDA graph, not peak tensor throughput.
+// layer's weights are 15 MB (2.3 us of HBM time), so the design goal here is few launches that keep
+// many loads in flight and capture into one CUDA graph, not peak tensor throughput.
 #include "internal.cuh"
 #include <cuda_fp16.h>
 
