@@ -28,10 +28,7 @@
 
 namespace nncb {
 
-#ifndef NNCB_PA_WARPS
-#define NNCB_PA_WARPS 4
-#endif
-constexpr int PA_D = 64, PA_PAGE = 16, PA_WARPS = NNCB_PA_WARPS, PA_STAGES = 3, PA_TOK = 32; // tokens per stage
+constexpr int PA_D = 64, PA_PAGE = 16, PA_STAGES = 3, PA_TOK = 32; // tokens per stage
 constexpr int PA_STAGE_BYTES = PA_TOK * PA_D * 2;                                  // K or V of one stage
 
 struct PaArgs {
@@ -74,6 +71,9 @@ __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
 // byte offset of 16-byte chunk `c` (0..7) of token row `r` (0..31) inside a stage tile
 __device__ __forceinline__ uint32_t pa_off(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
 
+// PA_WARPS warps per CTA (4: two CTAs per SM, context splits fill the machine; 8: one CTA per SM takes a
+// whole context -- no partials, no merge launch -- when there are enough (sequence, kv head) pairs).
+template <int PA_WARPS>
 __global__ void __launch_bounds__(PA_WARPS * 32)
 paged_attention_decode_kernel(const PaArgs a) {
     extern __shared__ __align__(128) uint8_t pa_smem_raw[];
@@ -291,11 +291,19 @@ size_t paged_attention_scratch_bytes(int B, int Hq, int splits) {
     return splits <= 1 ? 0 : (size_t)B * Hq * splits * (PA_D + 2) * sizeof(float);
 }
 
+// Eight-warp CTAs (one per SM) once the (sequence, kv head) pairs alone fill half the SMs; four-warp CTAs
+// (two per SM) with context splits below that.
+static int paged_attention_pick_warps(const nncb_context *ctx, int B, int Hkv) {
+    if (const char *e = getenv("NNCB_PA_WARPS")) // tuning aid: force the CTA width (4 or 8)
+        return atoi(e) == 8 ? 8 : 4;
+    return 2 * B * Hkv >= ctx->sm_count ? 8 : 4;
+}
+
 int paged_attention_pick_splits(const nncb_context *ctx, int B, int Hkv, int max_ctx) {
-    // Two CTAs fit an SM (96 KB of shared memory each). Split the context so that the grid fills
-    // those slots in ONE wave -- a second, partly filled wave costs a full pass -- but keep at
-    // least 8 pages (4 units) per CTA.
-    const int per_sm = (int)((227u * 1024u) / ((size_t)PA_WARPS * PA_STAGES * 2 * PA_STAGE_BYTES + 1024));
+    // Split the context so that the grid fills the CTA slots in ONE wave -- a second, partly filled wave
+    // costs a full pass -- but keep at least 8 pages (4 units) per CTA.
+    const int warps = paged_attention_pick_warps(ctx, B, Hkv);
+    const int per_sm = (int)((227u * 1024u) / ((size_t)warps * PA_STAGES * 2 * PA_STAGE_BYTES + 1024));
     const int ctas = B * Hkv, slots = (per_sm > 16 ? 16 : per_sm) * ctx->sm_count;
     int s = slots / ctas;
     const int pages = (max_ctx + PA_PAGE - 1) / PA_PAGE;
@@ -330,14 +338,21 @@ int paged_attention_launch(nncb_context *ctx, const void *q, const void *k_pool,
     a.scale_log2 = scale * 1.4426950408889634f;
     a.part_o = (float *)scratch;
     a.part_ml = a.part_o ? a.part_o + (size_t)B * Hq * splits * PA_D : nullptr;
-    const size_t smem = (size_t)PA_WARPS * PA_STAGES * 2 * PA_STAGE_BYTES; // 96 KB
+    const int warps = paged_attention_pick_warps(ctx, B, Hkv);
+    const size_t smem = (size_t)warps * PA_STAGES * 2 * PA_STAGE_BYTES; // 96 KB or 192 KB
     static bool attr_set = false;
     if (!attr_set) {
-        NNCB_CUDA_TRY(cudaFuncSetAttribute(paged_attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        NNCB_CUDA_TRY(cudaFuncSetAttribute(paged_attention_decode_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           4 * PA_STAGES * 2 * PA_STAGE_BYTES));
+        NNCB_CUDA_TRY(cudaFuncSetAttribute(paged_attention_decode_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           8 * PA_STAGES * 2 * PA_STAGE_BYTES));
         attr_set = true;
     }
     dim3 grid(splits, Hkv, B);
-    paged_attention_decode_kernel<<<grid, PA_WARPS * 32, smem, ctx->stream>>>(a);
+    if (warps == 8)
+        paged_attention_decode_kernel<8><<<grid, 8 * 32, smem, ctx->stream>>>(a);
+    else
+        paged_attention_decode_kernel<4><<<grid, 4 * 32, smem, ctx->stream>>>(a);
     NNCB_TRY(after_launch(ctx, "paged_attention_decode"));
     if (splits > 1) {
         paged_attention_merge_kernel<<<B * Hq, 64, 0, ctx->stream>>>(a.part_o, a.part_ml, a.out, splits);

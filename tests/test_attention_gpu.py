@@ -38,6 +38,22 @@ def test_ragged_contexts(ctx, hq, hkv):
     check(ctx, make_cache(5, len(lens), hq, hkv, lens))
 
 
+@pytest.mark.parametrize("warps", ["4", "8"])
+def test_both_cta_widths(ctx, monkeypatch, warps):
+    """The four-warp (context splits, merge kernel) and the eight-warp (one CTA per sequence and kv head)
+    forms of the kernel on the same ragged batch."""
+    monkeypatch.setenv("NNCB_PA_WARPS", warps)
+    lens = [1, 15, 16, 17, 33, 100, 511, 512, 513, 700, 0, 2048, 31, 32, 1000, 255]
+    check(ctx, make_cache(15, len(lens), 14, 2, lens))
+
+
+def test_many_sequences_take_the_wide_form(ctx):
+    """80 sequences x 2 kv heads fill the SMs without context splits (eight-warp CTAs, no merge)."""
+    rng = np.random.default_rng(16)
+    lens = [int(v) for v in rng.integers(0, 400, 80)]
+    check(ctx, make_cache(16, len(lens), 14, 2, lens))
+
+
 def test_single_token_and_empty(ctx):
     check(ctx, make_cache(6, 3, 14, 2, [0, 1, 1]))
 
