@@ -554,6 +554,7 @@ int nncb_qconv2d_destroy(nncb_qconv2d *cv) {
     cudaSetDevice(cv->device);
     tc_conv_destroy(cv);
     cudaFree(cv->d_w);
+    cudaFree(cv->d_wdw);
     cudaFree(cv->d_wzp);
     cudaFree(cv->d_mult);
     cudaFree(cv->d_bias);
@@ -634,6 +635,8 @@ int nncb_qconv2d_create(nncb_context *ctx, const nncb_conv2d_desc *desc, const v
     }
     if (rc == 0 && cv->path == PATH_TC)
         rc = tc_conv_create(ctx, cv, weights, w_zp);
+    if (rc == 0 && cv->path == PATH_SIMT)
+        rc = simt_conv_prepare(ctx, cv, weights, w_zp);
     if (rc != 0) {
         nncb_qconv2d_destroy(cv);
         return rc;

@@ -53,6 +53,7 @@ struct nncb_qconv2d {
     int path = 0;
     // device copies of the caller's tables
     void *d_w = nullptr;       // OHWI weights as given
+    int16_t *d_wdw = nullptr;  // depthwise only: (w - zw) as int16, [tap][channel]
     int32_t *d_wzp = nullptr;  // per-oc weight zero points (always materialised)
     float *d_mult = nullptr;
     float *d_bias = nullptr;
@@ -64,6 +65,7 @@ struct nncb_qconv2d {
 namespace nncb {
 EpiParams make_epi(const nncb_qconv2d *cv);
 int simt_conv_run(nncb_context *ctx, nncb_qconv2d *cv, const uint8_t *x, const uint8_t *res, void *y, uint8_t *y2);
+int simt_conv_prepare(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, const int32_t *wzp_host);
 // tcgen05 path; tc_conv_supported says whether this shape can use it.
 bool tc_conv_supported(const nncb_conv2d_desc &d, std::string *why);
 int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, const int32_t *wzp_host);

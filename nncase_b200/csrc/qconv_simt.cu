@@ -3,6 +3,7 @@
 // 3-channel stem). One thread per (output pixel, output channel); consecutive threads own
 // consecutive output channels, so activation loads broadcast within a warp and stores coalesce.
 #include "qconv.cuh"
+#include <vector>
 
 namespace nncb {
 
@@ -84,11 +85,86 @@ simt_conv_kernel(SimtGeom g, const uint8_t *__restrict__ x, const void *__restri
     }
 }
 
+// ---- depthwise (groups == c == oc, c % 4 == 0, u8 output) ----------------------------------------
+// A streaming kernel: one thread per (output pixel, four channels); a warp reads 128 contiguous bytes
+// of every tap and writes 128 contiguous bytes. The weights are prepared at plan creation as
+// (w - zw) in int16, tap-major, so that four channels of a tap are one 8-byte load. Padded taps are
+// skipped, which is what the normative formulation says (they contribute (zx - zx) * w = 0).
+__global__ void __launch_bounds__(256)
+dw_conv_kernel(SimtGeom g, const uint8_t *__restrict__ x, const int16_t *__restrict__ wdw, EpiParams p,
+               const uint8_t *__restrict__ res, uint8_t *__restrict__ y, uint8_t *__restrict__ y2) {
+    const int cq = g.c / 4;
+    const size_t total = (size_t)g.n * g.oh * g.ow * cq;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int c0 = (int)(i % cq) * 4;
+        const size_t pix = i / cq;
+        const int ox = (int)(pix % g.ow);
+        const int oy = (int)((pix / g.ow) % g.oh);
+        const int b = (int)(pix / ((size_t)g.ow * g.oh));
+        const int iy0 = oy * g.sh - g.pt, ix0 = ox * g.sw - g.pl;
+        int acc[4] = {0, 0, 0, 0};
+        for (int ky = 0; ky < g.kh; ky++) {
+            const int iy = iy0 + ky * g.dh;
+            if (iy < 0 || iy >= g.h)
+                continue;
+            for (int kx = 0; kx < g.kw; kx++) {
+                const int ix = ix0 + kx * g.dw;
+                if (ix < 0 || ix >= g.w)
+                    continue;
+                const uint32_t xv = __ldg(reinterpret_cast<const uint32_t *>(x + (((size_t)b * g.h + iy) * g.w + ix) * g.c + c0));
+                const uint2 wv = __ldg(reinterpret_cast<const uint2 *>(wdw + (size_t)(ky * g.kw + kx) * g.c + c0));
+                acc[0] += ((int)(xv & 255u) - g.x_zp) * (int)(short)(wv.x & 0xffffu);
+                acc[1] += ((int)((xv >> 8) & 255u) - g.x_zp) * ((int)wv.x >> 16);
+                acc[2] += ((int)((xv >> 16) & 255u) - g.x_zp) * (int)(short)(wv.y & 0xffffu);
+                acc[3] += ((int)(xv >> 24) - g.x_zp) * ((int)wv.y >> 16);
+            }
+        }
+        const float4 mult = __ldg(reinterpret_cast<const float4 *>(p.mult + c0));
+        const float4 bias = __ldg(reinterpret_cast<const float4 *>(p.bias + c0));
+        const size_t o = pix * g.c + c0;
+        const uint32_t rv = p.has_res ? __ldg(reinterpret_cast<const uint32_t *>(res + o)) : 0u;
+        const int q0 = epi_u8(acc[0], mult.x, bias.x, p, (int)(rv & 255u));
+        const int q1 = epi_u8(acc[1], mult.y, bias.y, p, (int)((rv >> 8) & 255u));
+        const int q2 = epi_u8(acc[2], mult.z, bias.z, p, (int)((rv >> 16) & 255u));
+        const int q3 = epi_u8(acc[3], mult.w, bias.w, p, (int)(rv >> 24));
+        *reinterpret_cast<uint32_t *>(y + o) = (uint32_t)q0 | ((uint32_t)q1 << 8) | ((uint32_t)q2 << 16) | ((uint32_t)q3 << 24);
+        if (y2)
+            *reinterpret_cast<uint32_t *>(y2 + o) = (uint32_t)p.y2_lut[q0] | ((uint32_t)p.y2_lut[q1] << 8) |
+                                                    ((uint32_t)p.y2_lut[q2] << 16) | ((uint32_t)p.y2_lut[q3] << 24);
+    }
+}
+
+// (w - zw) as int16, [tap][channel], for dw_conv_kernel; null when the shape is not depthwise.
+int simt_conv_prepare(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, const int32_t *wzp_host) {
+    const nncb_conv2d_desc &d = cv->d;
+    if (!(d.groups == d.c && d.oc == d.c && d.c % 4 == 0 && !d.f32_out))
+        return 0;
+    const int taps = d.kh * d.kw;
+    std::vector<int16_t> t((size_t)taps * d.c);
+    for (int c = 0; c < d.c; c++)
+        for (int k = 0; k < taps; k++) {
+            const int wv = d.w_signed ? (int)reinterpret_cast<const int8_t *>(w_host)[(size_t)c * taps + k]
+                                      : (int)reinterpret_cast<const uint8_t *>(w_host)[(size_t)c * taps + k];
+            t[(size_t)k * d.c + c] = (int16_t)(wv - (wzp_host ? wzp_host[c] : 0));
+        }
+    NNCB_CUDA_TRY(cudaMalloc(&cv->d_wdw, t.size() * sizeof(int16_t)));
+    NNCB_CUDA_TRY(cudaMemcpyAsync(cv->d_wdw, t.data(), t.size() * sizeof(int16_t), cudaMemcpyHostToDevice, ctx->stream));
+    NNCB_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    return 0;
+}
+
 int simt_conv_run(nncb_context *ctx, nncb_qconv2d *cv, const uint8_t *x, const uint8_t *res, void *y, uint8_t *y2) {
     const nncb_conv2d_desc &d = cv->d;
     SimtGeom g{d.n, d.h, d.w, d.c, d.oc, d.kh, d.kw, d.stride_h, d.stride_w, d.pad_t, d.pad_l, d.dil_h,
                d.dil_w, d.groups, cv->oh, cv->ow, d.w_signed, d.x_zp, d.f32_out};
     EpiParams p = make_epi(cv);
+    auto al4 = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 3) == 0; };
+    if (cv->d_wdw && al4(x) && al4(res) && al4(y) && al4(y2)) {
+        const size_t quads = (size_t)d.n * cv->oh * cv->ow * (d.c / 4);
+        const size_t nb = (quads + 255) / 256, capq = (size_t)ctx->sm_count * 32;
+        dw_conv_kernel<<<(int)(nb < capq ? nb : capq), 256, 0, ctx->stream>>>(g, x, cv->d_wdw, p, res, (uint8_t *)y, y2);
+        return after_launch(ctx, "dw_conv");
+    }
     size_t total = (size_t)d.n * cv->oh * cv->ow * d.oc;
     size_t blocks = (total + 255) / 256;
     size_t cap = (size_t)ctx->sm_count * 32;

@@ -233,3 +233,34 @@ def test_tc_conv_kernel_rows_residual_second_output(ctx, qo):
     ctx.check_status()
     assert np.array_equal(got.cpu().numpy(), want)
     assert np.array_equal(got2.cpu().numpy(), want2)
+
+
+DEPTHWISE_CASES = [
+    # n, h, w, c, kh, kw, stride, pad, dil: the streaming depthwise kernel (groups == channels, c % 4 == 0)
+    (2, 28, 28, 96, 3, 3, 1, 1, 1), (1, 56, 56, 160, 3, 3, 2, 1, 1), (3, 9, 11, 32, 3, 3, 1, 1, 2), (1, 14, 14, 960, 3, 3, 1, 1, 1),
+    (2, 7, 7, 4, 5, 5, 1, 2, 1), (1, 112, 112, 32, 3, 3, 2, 0, 1),
+]
+
+
+@pytest.mark.parametrize("cfg", DEPTHWISE_CASES)
+@pytest.mark.parametrize("w_signed", [False, True])
+def test_depthwise_conv(ctx, qo, cfg, w_signed):
+    n, h, w, c, kh, kw, s, p, d = cfg
+    case = make_case(61, n, h, w, c, c, kh, kw, c, w_signed)
+    got, want = run_both(ctx, qo, case, L.PATH_AUTO, (s, s), (p, p, p, p), (d, d), c, (0, 6))
+    assert np.array_equal(got, want)
+
+
+def test_depthwise_conv_residual_and_second_output(ctx, qo):
+    n, h, w, c = 2, 14, 14, 64
+    case = make_case(62, n, h, w, c, c, 3, 3, c)
+    xq, zx, wq, zw, mult, bias, oqp = case
+    res = np.random.default_rng(63).integers(0, 256, (n, h, w, c), dtype=np.uint8)
+    rq, aq, yq2 = QuantParam(117, 0.05), QuantParam(125, 0.06), QuantParam(0, 0.03)
+    y1 = qo.qconv2d_u8(xq, wq, zw, mult, bias, zx, oqp.scale, oqp.zero_point, pad=(1, 1, 1, 1), groups=c)
+    want = qo.qadd_u8(y1, res, oqp.scale, oqp.zero_point, rq.scale, rq.zero_point, aq.scale, aq.zero_point)
+    want2 = qo.requant_u8(want, aq.scale, aq.zero_point, yq2.scale, yq2.zero_point, 0.0, np.inf)
+    got, got2 = ctx.conv2d(torch.from_numpy(xq), wq, zw, mult, bias, zx, oqp, padding=(1, 1, 1, 1), groups=c,
+                           res=torch.from_numpy(res).cuda(), residual=(rq, aq), y2=(yq2, 0.0, float("inf")))
+    ctx.check_status()
+    assert np.array_equal(got.cpu().numpy(), want) and np.array_equal(got2.cpu().numpy(), want2)
