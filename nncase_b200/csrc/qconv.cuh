@@ -54,6 +54,9 @@ struct nncb_qconv2d {
     // device copies of the caller's tables
     void *d_w = nullptr;       // OHWI weights as given
     int16_t *d_wdw = nullptr;  // depthwise only: (w - zw) as int16, [tap][channel]
+    // depthwise only: constants of the division-free exact requantisation (valid when dw_fast)
+    bool dw_fast = false;
+    float dw_rso = 0.f, dw_qlo = 0.f, dw_qhi = 255.f;
     int32_t *d_wzp = nullptr;  // per-oc weight zero points (always materialised)
     float *d_mult = nullptr;
     float *d_bias = nullptr;
@@ -66,6 +69,9 @@ namespace nncb {
 EpiParams make_epi(const nncb_qconv2d *cv);
 int simt_conv_run(nncb_context *ctx, nncb_qconv2d *cv, const uint8_t *x, const uint8_t *res, void *y, uint8_t *y2);
 int simt_conv_prepare(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, const int32_t *wzp_host);
+// RN(1/b) verified in extended precision; *ok = false for scales outside the range the three-operation
+// division is proven for (qconv_tc.cu).
+float rn_reciprocal(float b, bool *ok);
 // tcgen05 path; tc_conv_supported says whether this shape can use it.
 bool tc_conv_supported(const nncb_conv2d_desc &d, std::string *why);
 int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, const int32_t *wzp_host);

@@ -3,6 +3,7 @@
 // 3-channel stem). One thread per (output pixel, output channel); consecutive threads own
 // consecutive output channels, so activation loads broadcast within a warp and stores coalesce.
 #include "qconv.cuh"
+#include <cmath>
 #include <vector>
 
 namespace nncb {
@@ -90,8 +91,14 @@ simt_conv_kernel(SimtGeom g, const uint8_t *__restrict__ x, const void *__restri
 // of every tap and writes 128 contiguous bytes. The weights are prepared at plan creation as
 // (w - zw) in int16, tap-major, so that four channels of a tap are one 8-byte load. Padded taps are
 // skipped, which is what the normative formulation says (they contribute (zx - zx) * w = 0).
+struct DwFast {
+    int on;            // no residual, no activation table: requantise without a division
+    float so, rso, zo; // output scale, its verified reciprocal, zero point
+    float qlo, qhi;    // the fused clamp as quantized bounds
+};
+
 __global__ void __launch_bounds__(256)
-dw_conv_kernel(SimtGeom g, const uint8_t *__restrict__ x, const int16_t *__restrict__ wdw, EpiParams p,
+dw_conv_kernel(SimtGeom g, const uint8_t *__restrict__ x, const int16_t *__restrict__ wdw, EpiParams p, DwFast f,
                const uint8_t *__restrict__ res, uint8_t *__restrict__ y, uint8_t *__restrict__ y2) {
     const int cq = g.c / 4;
     const size_t total = (size_t)g.n * g.oh * g.ow * cq;
@@ -102,17 +109,23 @@ dw_conv_kernel(SimtGeom g, const uint8_t *__restrict__ x, const int16_t *__restr
         const int oy = (int)((pix / g.ow) % g.oh);
         const int b = (int)(pix / ((size_t)g.ow * g.oh));
         const int iy0 = oy * g.sh - g.pt, ix0 = ox * g.sw - g.pl;
+        // valid tap ranges: no bounds test inside the loops
+        int ky0 = 0, ky1 = g.kh, kx0 = 0, kx1 = g.kw;
+        while (ky0 < ky1 && iy0 + ky0 * g.dh < 0)
+            ky0++;
+        while (ky1 > ky0 && iy0 + (ky1 - 1) * g.dh >= g.h)
+            ky1--;
+        while (kx0 < kx1 && ix0 + kx0 * g.dw < 0)
+            kx0++;
+        while (kx1 > kx0 && ix0 + (kx1 - 1) * g.dw >= g.w)
+            kx1--;
         int acc[4] = {0, 0, 0, 0};
-        for (int ky = 0; ky < g.kh; ky++) {
-            const int iy = iy0 + ky * g.dh;
-            if (iy < 0 || iy >= g.h)
-                continue;
-            for (int kx = 0; kx < g.kw; kx++) {
-                const int ix = ix0 + kx * g.dw;
-                if (ix < 0 || ix >= g.w)
-                    continue;
-                const uint32_t xv = __ldg(reinterpret_cast<const uint32_t *>(x + (((size_t)b * g.h + iy) * g.w + ix) * g.c + c0));
-                const uint2 wv = __ldg(reinterpret_cast<const uint2 *>(wdw + (size_t)(ky * g.kw + kx) * g.c + c0));
+        for (int ky = ky0; ky < ky1; ky++) {
+            const uint8_t *xrow = x + (((size_t)b * g.h + iy0 + ky * g.dh) * g.w + ix0) * g.c + c0;
+            const int16_t *wrow = wdw + (size_t)(ky * g.kw) * g.c + c0;
+            for (int kx = kx0; kx < kx1; kx++) {
+                const uint32_t xv = __ldg(reinterpret_cast<const uint32_t *>(xrow + (size_t)kx * g.dw * g.c));
+                const uint2 wv = __ldg(reinterpret_cast<const uint2 *>(wrow + (size_t)kx * g.c));
                 acc[0] += ((int)(xv & 255u) - g.x_zp) * (int)(short)(wv.x & 0xffffu);
                 acc[1] += ((int)((xv >> 8) & 255u) - g.x_zp) * ((int)wv.x >> 16);
                 acc[2] += ((int)((xv >> 16) & 255u) - g.x_zp) * (int)(short)(wv.y & 0xffffu);
@@ -122,15 +135,30 @@ dw_conv_kernel(SimtGeom g, const uint8_t *__restrict__ x, const int16_t *__restr
         const float4 mult = __ldg(reinterpret_cast<const float4 *>(p.mult + c0));
         const float4 bias = __ldg(reinterpret_cast<const float4 *>(p.bias + c0));
         const size_t o = pix * g.c + c0;
-        const uint32_t rv = p.has_res ? __ldg(reinterpret_cast<const uint32_t *>(res + o)) : 0u;
-        const int q0 = epi_u8(acc[0], mult.x, bias.x, p, (int)(rv & 255u));
-        const int q1 = epi_u8(acc[1], mult.y, bias.y, p, (int)((rv >> 8) & 255u));
-        const int q2 = epi_u8(acc[2], mult.z, bias.z, p, (int)((rv >> 16) & 255u));
-        const int q3 = epi_u8(acc[3], mult.w, bias.w, p, (int)(rv >> 24));
-        *reinterpret_cast<uint32_t *>(y + o) = (uint32_t)q0 | ((uint32_t)q1 << 8) | ((uint32_t)q2 << 16) | ((uint32_t)q3 << 24);
+        int q[4];
+        if (f.on) {
+            // the tensor-core kernel's epilogue: v / so as q0 = RN(v r), q = RN(q0 + RN(v - q0 so) r), the
+            // clamp folded into the quantized bounds, + 2^23 to round to nearest-even
+            const float m4[4] = {mult.x, mult.y, mult.z, mult.w}, b4[4] = {bias.x, bias.y, bias.z, bias.w};
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const float v = __fadd_rn(__fmul_rn((float)acc[e], m4[e]), b4[e]);
+                float q0 = __fmul_rn(v, f.rso);
+                q0 = __fmaf_rn(__fmaf_rn(-q0, f.so, v), f.rso, q0);
+                const float t = fminf(fmaxf(__fadd_rn(q0, f.zo), f.qlo), f.qhi);
+                q[e] = (int)(__float_as_uint(__fadd_rn(t, 8388608.0f)) & 255u);
+            }
+        } else {
+            const uint32_t rv = p.has_res ? __ldg(reinterpret_cast<const uint32_t *>(res + o)) : 0u;
+            q[0] = epi_u8(acc[0], mult.x, bias.x, p, (int)(rv & 255u));
+            q[1] = epi_u8(acc[1], mult.y, bias.y, p, (int)((rv >> 8) & 255u));
+            q[2] = epi_u8(acc[2], mult.z, bias.z, p, (int)((rv >> 16) & 255u));
+            q[3] = epi_u8(acc[3], mult.w, bias.w, p, (int)(rv >> 24));
+        }
+        *reinterpret_cast<uint32_t *>(y + o) = (uint32_t)q[0] | ((uint32_t)q[1] << 8) | ((uint32_t)q[2] << 16) | ((uint32_t)q[3] << 24);
         if (y2)
-            *reinterpret_cast<uint32_t *>(y2 + o) = (uint32_t)p.y2_lut[q0] | ((uint32_t)p.y2_lut[q1] << 8) |
-                                                    ((uint32_t)p.y2_lut[q2] << 16) | ((uint32_t)p.y2_lut[q3] << 24);
+            *reinterpret_cast<uint32_t *>(y2 + o) = (uint32_t)p.y2_lut[q[0]] | ((uint32_t)p.y2_lut[q[1]] << 8) |
+                                                    ((uint32_t)p.y2_lut[q[2]] << 16) | ((uint32_t)p.y2_lut[q[3]] << 24);
     }
 }
 
@@ -147,6 +175,18 @@ int simt_conv_prepare(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, c
                                       : (int)reinterpret_cast<const uint8_t *>(w_host)[(size_t)c * taps + k];
             t[(size_t)k * d.c + c] = (int16_t)(wv - (wzp_host ? wzp_host[c] : 0));
         }
+    // constants of the division-free requantisation (no residual, no activation table)
+    bool ok = true;
+    cv->dw_rso = rn_reciprocal(d.out_scale, &ok);
+    auto quant = [&](float v) {
+        if (std::isinf(v))
+            return v < 0 ? 0.f : 255.f;
+        const float tq = v / d.out_scale;
+        const float u = tq + (float)d.out_zp;
+        return std::fmin(std::fmax(rintf(u), 0.f), 255.f);
+    };
+    cv->dw_qlo = quant(d.clamp_lo), cv->dw_qhi = quant(d.clamp_hi);
+    cv->dw_fast = ok && !d.has_residual && cv->d_lut == nullptr && !std::isnan(d.clamp_lo) && !std::isnan(d.clamp_hi);
     NNCB_CUDA_TRY(cudaMalloc(&cv->d_wdw, t.size() * sizeof(int16_t)));
     NNCB_CUDA_TRY(cudaMemcpyAsync(cv->d_wdw, t.data(), t.size() * sizeof(int16_t), cudaMemcpyHostToDevice, ctx->stream));
     NNCB_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
@@ -162,7 +202,8 @@ int simt_conv_run(nncb_context *ctx, nncb_qconv2d *cv, const uint8_t *x, const u
     if (cv->d_wdw && al4(x) && al4(res) && al4(y) && al4(y2)) {
         const size_t quads = (size_t)d.n * cv->oh * cv->ow * (d.c / 4);
         const size_t nb = (quads + 255) / 256, capq = (size_t)ctx->sm_count * 32;
-        dw_conv_kernel<<<(int)(nb < capq ? nb : capq), 256, 0, ctx->stream>>>(g, x, cv->d_wdw, p, res, (uint8_t *)y, y2);
+        DwFast f{cv->dw_fast ? 1 : 0, d.out_scale, cv->dw_rso, (float)d.out_zp, cv->dw_qlo, cv->dw_qhi};
+        dw_conv_kernel<<<(int)(nb < capq ? nb : capq), 256, 0, ctx->stream>>>(g, x, cv->d_wdw, p, f, res, (uint8_t *)y, y2);
         return after_launch(ctx, "dw_conv");
     }
     size_t total = (size_t)d.n * cv->oh * cv->ow * d.oc;

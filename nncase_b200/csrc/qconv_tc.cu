@@ -1132,7 +1132,7 @@ tc_conv_fast_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 // division of the fast epilogue returns the IEEE quotient only with a correctly rounded
 // reciprocal; scales far from 1 (where intermediate products could leave the normal range) are
 // refused, and the generic epilogue takes the layer.
-static float rn_reciprocal(float b, bool *ok) {
+float rn_reciprocal(float b, bool *ok) {
     if (!(b > 1e-18f && b < 1e18f)) {
         *ok = false;
         return 0.f;
