@@ -103,11 +103,21 @@ dw_conv_kernel(SimtGeom g, const uint8_t *__restrict__ x, const int16_t *__restr
     const int cq = g.c / 4;
     const size_t total = (size_t)g.n * g.oh * g.ow * cq;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        const int c0 = (int)(i % cq) * 4;
-        const size_t pix = i / cq;
-        const int ox = (int)(pix % g.ow);
-        const int oy = (int)((pix / g.ow) % g.oh);
-        const int b = (int)(pix / ((size_t)g.ow * g.oh));
+        // 32-bit index arithmetic when the index fits: a 64-bit division costs some seventy instructions
+        int c0, ox, oy, b;
+        size_t pix;
+        if (i <= 0xffffffffull) {
+            const uint32_t ii = (uint32_t)i, px = ii / (uint32_t)cq, row = px / (uint32_t)g.ow;
+            c0 = (int)(ii % (uint32_t)cq) * 4, ox = (int)(px % (uint32_t)g.ow);
+            oy = (int)(row % (uint32_t)g.oh), b = (int)(row / (uint32_t)g.oh);
+            pix = px;
+        } else {
+            c0 = (int)(i % cq) * 4;
+            pix = i / cq;
+            ox = (int)(pix % g.ow);
+            oy = (int)((pix / g.ow) % g.oh);
+            b = (int)(pix / ((size_t)g.ow * g.oh));
+        }
         const int iy0 = oy * g.sh - g.pt, ix0 = ox * g.sw - g.pl;
         // valid tap ranges: no bounds test inside the loops
         int ky0 = 0, ky1 = g.kh, kx0 = 0, kx1 = g.kw;
@@ -162,6 +172,90 @@ dw_conv_kernel(SimtGeom g, const uint8_t *__restrict__ x, const int16_t *__restr
     }
 }
 
+// 3x3, dilation 1, stride S in {1, 2}: one thread computes FOUR horizontally adjacent outputs of four
+// channels from a sliding window of 3 S + 3 input columns per kernel row held in registers, so every input
+// word is loaded and unpacked once per row (instead of once per tap) and every weight once per four outputs.
+template <int S>
+__global__ void __launch_bounds__(256)
+dw3x3_conv_kernel(SimtGeom g, const uint8_t *__restrict__ x, const int16_t *__restrict__ wdw, EpiParams p, DwFast f,
+                  const uint8_t *__restrict__ res, uint8_t *__restrict__ y, uint8_t *__restrict__ y2) {
+    constexpr int NC = 3 * S + 3;
+    // blockIdx.x = output row (image, oy); blockIdx.y * 256 + thread = (group of four outputs, channel quad) in it
+    const uint32_t cq = (uint32_t)g.c / 4u, oxg = ((uint32_t)g.ow + 3u) / 4u;
+    const uint32_t j = blockIdx.y * blockDim.x + threadIdx.x;
+    if (j < oxg * cq) {
+        const int c0 = (int)(j % cq) * 4;
+        const int ox0 = (int)(j / cq) * 4;
+        const int oy = (int)(blockIdx.x % (uint32_t)g.oh), b = (int)(blockIdx.x / (uint32_t)g.oh);
+        const int ix0 = ox0 * S - g.pl, iy0 = oy * S - g.pt;
+        int acc[4][4];
+#pragma unroll
+        for (int t = 0; t < 4; t++)
+            acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0;
+#pragma unroll
+        for (int ky = 0; ky < 3; ky++) {
+            const int iy = iy0 + ky;
+            if (iy < 0 || iy >= g.h)
+                continue; // a padded row contributes (zx - zx) * w = 0
+            const uint8_t *xrow = x + (((size_t)b * g.h + iy) * g.w) * g.c + c0;
+            int xs[NC][4];
+#pragma unroll
+            for (int cidx = 0; cidx < NC; cidx++) {
+                const int ix = ix0 + cidx;
+                const bool valid = ix >= 0 && ix < g.w;
+                const uint32_t v = valid ? __ldg(reinterpret_cast<const uint32_t *>(xrow + (size_t)ix * g.c)) : 0u;
+                xs[cidx][0] = valid ? (int)(v & 255u) - g.x_zp : 0;
+                xs[cidx][1] = valid ? (int)((v >> 8) & 255u) - g.x_zp : 0;
+                xs[cidx][2] = valid ? (int)((v >> 16) & 255u) - g.x_zp : 0;
+                xs[cidx][3] = valid ? (int)(v >> 24) - g.x_zp : 0;
+            }
+#pragma unroll
+            for (int kx = 0; kx < 3; kx++) {
+                const uint2 wv = __ldg(reinterpret_cast<const uint2 *>(wdw + (size_t)(ky * 3 + kx) * g.c + c0));
+                const int w0 = (int)(short)(wv.x & 0xffffu), w1 = (int)wv.x >> 16;
+                const int w2 = (int)(short)(wv.y & 0xffffu), w3 = (int)wv.y >> 16;
+#pragma unroll
+                for (int t = 0; t < 4; t++) {
+                    acc[t][0] += xs[t * S + kx][0] * w0;
+                    acc[t][1] += xs[t * S + kx][1] * w1;
+                    acc[t][2] += xs[t * S + kx][2] * w2;
+                    acc[t][3] += xs[t * S + kx][3] * w3;
+                }
+            }
+        }
+        const float4 mult = __ldg(reinterpret_cast<const float4 *>(p.mult + c0));
+        const float4 bias = __ldg(reinterpret_cast<const float4 *>(p.bias + c0));
+        const float m4[4] = {mult.x, mult.y, mult.z, mult.w}, b4[4] = {bias.x, bias.y, bias.z, bias.w};
+#pragma unroll
+        for (int t = 0; t < 4; t++) {
+            if (ox0 + t >= g.ow)
+                break;
+            const size_t o = ((((size_t)b * g.oh + oy) * g.ow) + ox0 + t) * g.c + c0;
+            int q[4];
+            if (f.on) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float v = __fadd_rn(__fmul_rn((float)acc[t][e], m4[e]), b4[e]);
+                    float q0 = __fmul_rn(v, f.rso);
+                    q0 = __fmaf_rn(__fmaf_rn(-q0, f.so, v), f.rso, q0);
+                    const float tq = fminf(fmaxf(__fadd_rn(q0, f.zo), f.qlo), f.qhi);
+                    q[e] = (int)(__float_as_uint(__fadd_rn(tq, 8388608.0f)) & 255u);
+                }
+            } else {
+                const uint32_t rv = p.has_res ? __ldg(reinterpret_cast<const uint32_t *>(res + o)) : 0u;
+#pragma unroll
+                for (int e = 0; e < 4; e++)
+                    q[e] = epi_u8(acc[t][e], m4[e], b4[e], p, (int)((rv >> (8 * e)) & 255u));
+            }
+            *reinterpret_cast<uint32_t *>(y + o) =
+                (uint32_t)q[0] | ((uint32_t)q[1] << 8) | ((uint32_t)q[2] << 16) | ((uint32_t)q[3] << 24);
+            if (y2)
+                *reinterpret_cast<uint32_t *>(y2 + o) = (uint32_t)p.y2_lut[q[0]] | ((uint32_t)p.y2_lut[q[1]] << 8) |
+                                                        ((uint32_t)p.y2_lut[q[2]] << 16) | ((uint32_t)p.y2_lut[q[3]] << 24);
+        }
+    }
+}
+
 // (w - zw) as int16, [tap][channel], for dw_conv_kernel; null when the shape is not depthwise.
 int simt_conv_prepare(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, const int32_t *wzp_host) {
     const nncb_conv2d_desc &d = cv->d;
@@ -203,6 +297,18 @@ int simt_conv_run(nncb_context *ctx, nncb_qconv2d *cv, const uint8_t *x, const u
         const size_t quads = (size_t)d.n * cv->oh * cv->ow * (d.c / 4);
         const size_t nb = (quads + 255) / 256, capq = (size_t)ctx->sm_count * 32;
         DwFast f{cv->dw_fast ? 1 : 0, d.out_scale, cv->dw_rso, (float)d.out_zp, cv->dw_qlo, cv->dw_qhi};
+        const bool k3 = d.kh == 3 && d.kw == 3 && d.dil_h == 1 && d.dil_w == 1 && d.stride_h == d.stride_w &&
+                        (d.stride_h == 1 || d.stride_h == 2);
+        if (k3) {
+            const int row_items = ((cv->ow + 3) / 4) * (d.c / 4);
+            const int bt = row_items >= 256 ? 256 : (row_items + 31) / 32 * 32;
+            const dim3 grid3((unsigned)(d.n * cv->oh), (unsigned)((row_items + bt - 1) / bt));
+            if (d.stride_h == 1)
+                dw3x3_conv_kernel<1><<<grid3, bt, 0, ctx->stream>>>(g, x, cv->d_wdw, p, f, res, (uint8_t *)y, y2);
+            else
+                dw3x3_conv_kernel<2><<<grid3, bt, 0, ctx->stream>>>(g, x, cv->d_wdw, p, f, res, (uint8_t *)y, y2);
+            return after_launch(ctx, "dw3x3_conv");
+        }
         dw_conv_kernel<<<(int)(nb < capq ? nb : capq), 256, 0, ctx->stream>>>(g, x, cv->d_wdw, p, f, res, (uint8_t *)y, y2);
         return after_launch(ctx, "dw_conv");
     }

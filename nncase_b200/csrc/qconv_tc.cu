@@ -362,7 +362,7 @@ struct FastEpi {
     int corr_pitch;     // bn + 1: distinct border classes fall into distinct banks
     int n_cls;
     int out_sw;         // swizzle span of the staging sub-tiles: 32 or 0
-    int ncg, wcols;     // column groups per tile (4 or 2) and columns per epilogue warp (32 or 16)
+    int ncg, wcols;     // column groups per tile (2 to 4) and columns per epilogue warp (32 or 16)
     float so, rso, zo;  // output scale, its correctly rounded reciprocal, zero point
     float qlo, qhi;     // the fused clamp's bounds after quantization, within [0, 255]
     const float4 *cst;  // [oc_pad] {mult, bias, bits(corr of class 0), bits(-zw)}
@@ -1199,17 +1199,25 @@ int reciprocal_division_selftest(nncb_context *ctx, float scale, unsigned long l
     return rc;
 }
 
-static int pick_bn(int oc, bool xsum) {
-    // N tile: as wide as the layer allows up to 128 (+16 for the row-sum column), multiple of 16.
-    // 128, 64 and 32 are the widths the fast epilogue stages; prefer them when nothing is wasted.
-    (void)xsum;
-    if (oc >= 128)
-        return 128;
-    if (oc % 64 == 0)
-        return 64;
-    if (oc % 32 == 0 && oc <= 96)
-        return 32;
-    return ((oc + 15) / 16) * 16;
+static int pick_bn(int oc, long long K) {
+    // N tile width. 128, 96, 64, 48 and 32 are the widths the fast epilogue stages; a layer whose channel
+    // count is a multiple of 16 takes the one with the least modelled time per 128-pixel tile row. A tile costs
+    // the larger of its epilogue (measured: about 1000 clocks of latency plus 22 per column) and its operand
+    // loads ((128 + bn) K bytes at 40 per clock): 96 columns cover a 96- or 192-channel layer without waste and
+    // in the fewest tiles, 48 a 144-channel one, wide tiles re-read the activations of a deep layer less often.
+    if (oc % 16 != 0)
+        return oc >= 128 ? 128 : ((oc + 15) / 16) * 16;
+    static const int widths[5] = {128, 96, 64, 48, 32};
+    int best = 128;
+    long long best_cost = -1;
+    for (int bn : widths) {
+        const long long tiles = (oc + bn - 1) / bn;
+        const long long epi = 1000 + 22ll * bn, load = (128ll + bn) * K / 40;
+        const long long cost = tiles * (epi > load ? epi : load);
+        if (best_cost < 0 || cost < best_cost)
+            best_cost = cost, best = bn;
+    }
+    return best;
 }
 
 int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, const int32_t *wzp_host) {
@@ -1228,7 +1236,7 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
     for (int i = 0; i < d.oc && wzp_host; i++)
         any_zw |= wzp_host[i] != 0;
     g.has_xsum = any_zw ? 1 : 0;
-    g.bn = pick_bn(d.oc, any_zw);
+    g.bn = pick_bn(d.oc, (long long)d.kh * d.kw * d.c);
     g.bn_mma = g.bn + (any_zw ? 16 : 0);
     g.n_tiles = (d.oc + g.bn - 1) / g.bn;
     g.m_tiles = (g.m_total + 127) / 128;
@@ -1270,7 +1278,7 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
     // memory, mapped tile staged and stored), with the unmapped tile left unstored.
     const bool lut_only = cv->d_lut != nullptr && !d.has_y2 && !d.has_residual;
     const bool fast_shape = !d.f32_out && (cv->d_lut == nullptr || lut_only) && d.oc % 16 == 0 &&
-                            (g.bn == 128 || g.bn == 64 || g.bn == 32);
+                            (g.bn == 128 || g.bn == 96 || g.bn == 64 || g.bn == 48 || g.bn == 32);
     tp->f = new FastEpi();
     FastEpi &fe = *tp->f;
     memset(&fe, 0, sizeof(fe));
@@ -1292,8 +1300,8 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
         fe.off_corr = off;
         extras = off; // the per-class table is appended once the classes are known
         // each epilogue warp stages a 32-row x wcols-byte sub-tile; 32-byte rows are the swizzle span
-        fe.ncg = g.bn >= 64 ? 4 : 2;
-        fe.wcols = g.bn / fe.ncg;
+        fe.wcols = g.bn >= 96 ? 32 : 16;
+        fe.ncg = g.bn / fe.wcols; // 128: 4 x 32, 96: 3 x 32, 64: 4 x 16, 48: 3 x 16, 32: 2 x 16
         fe.out_sw = fe.wcols == 32 ? 32 : 0;
         tp->fast = true;
     }

@@ -209,15 +209,17 @@ int quantize_nchw_to_nhwc_u8(nncb_context *ctx, const float *in, uint8_t *out, i
 template <int CPAD, bool IN_NHWC>
 __global__ void __launch_bounds__(256)
 quantize_nchw_to_s2d_kernel(const float *__restrict__ in, uint8_t *__restrict__ out, int c, int h, int w,
-                            size_t total_cells, float scale, float zp, int pad_t, int pad_b, int pad_l, int pad_r) {
-    // output cells include a border of pad_* cells that hold the zero point in every channel
+                            float scale, float zp, int pad_t, int pad_b, int pad_l, int pad_r) {
+    // output cells include a border of pad_* cells that hold the zero point in every channel;
+    // blockIdx.x = (image, cell row), blockIdx.y * blockDim.x + thread = cell in the row
     const int hc = h / 2 + pad_t + pad_b, wc = w / 2 + pad_l + pad_r;
     const uint32_t zq = (uint32_t)min(max(__float2int_rn(zp), 0), 255);
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total_cells;
-         i += (size_t)gridDim.x * blockDim.x) {
-        const int X = (int)(i % wc) - pad_l;
-        const int Y = (int)((i / wc) % hc) - pad_t;
-        const size_t n = i / ((size_t)wc * hc);
+    const int xc = (int)(blockIdx.y * blockDim.x + threadIdx.x);
+    if (xc < wc) {
+        const int X = xc - pad_l;
+        const int Y = (int)(blockIdx.x % (uint32_t)hc) - pad_t;
+        const size_t n = blockIdx.x / (uint32_t)hc;
+        const size_t i = (size_t)blockIdx.x * wc + xc;
         uint32_t words[CPAD / 4];
 #pragma unroll
         for (int k = 0; k < CPAD / 4; k++)
@@ -262,20 +264,23 @@ int quantize_nchw_to_s2d_u8(nncb_context *ctx, const float *in, uint8_t *out, in
         return fail(-EINVAL, "quantize_nchw_to_s2d_u8: c_pad must be 16 or 32 and hold 4*c channels");
     if ((reinterpret_cast<uintptr_t>(in) & 7) || (reinterpret_cast<uintptr_t>(out) & 15))
         return fail(-EINVAL, "quantize_nchw_to_s2d_u8: pointers must be 8-byte (in) and 16-byte (out) aligned");
-    const size_t total = (size_t)n * (h / 2 + pad_t + pad_b) * (w / 2 + pad_l + pad_r);
-    const int grid = stream_grid(ctx, total, 256);
+    const int hc = h / 2 + pad_t + pad_b, wc = w / 2 + pad_l + pad_r;
+    const int bt = wc >= 256 ? 256 : (wc + 31) / 32 * 32;
+    const dim3 grid((unsigned)((size_t)n * hc), (unsigned)((wc + bt - 1) / bt));
+    if ((size_t)n * hc > 0x7fffffffull)
+        return fail(-EINVAL, "quantize_nchw_to_s2d_u8: too many rows");
     if (c_pad == 32 && in_nhwc)
-        quantize_nchw_to_s2d_kernel<32, true><<<grid, 256, 0, ctx->stream>>>(in, out, c, h, w, total, scale, (float)zp, pad_t, pad_b,
-                                                                              pad_l, pad_r);
+        quantize_nchw_to_s2d_kernel<32, true><<<grid, bt, 0, ctx->stream>>>(in, out, c, h, w, scale, (float)zp, pad_t, pad_b, pad_l,
+                                                                             pad_r);
     else if (c_pad == 32)
-        quantize_nchw_to_s2d_kernel<32, false><<<grid, 256, 0, ctx->stream>>>(in, out, c, h, w, total, scale, (float)zp, pad_t, pad_b,
-                                                                              pad_l, pad_r);
+        quantize_nchw_to_s2d_kernel<32, false><<<grid, bt, 0, ctx->stream>>>(in, out, c, h, w, scale, (float)zp, pad_t, pad_b, pad_l,
+                                                                              pad_r);
     else if (in_nhwc)
-        quantize_nchw_to_s2d_kernel<16, true><<<grid, 256, 0, ctx->stream>>>(in, out, c, h, w, total, scale, (float)zp, pad_t, pad_b,
-                                                                              pad_l, pad_r);
+        quantize_nchw_to_s2d_kernel<16, true><<<grid, bt, 0, ctx->stream>>>(in, out, c, h, w, scale, (float)zp, pad_t, pad_b, pad_l,
+                                                                             pad_r);
     else
-        quantize_nchw_to_s2d_kernel<16, false><<<grid, 256, 0, ctx->stream>>>(in, out, c, h, w, total, scale, (float)zp, pad_t, pad_b,
-                                                                              pad_l, pad_r);
+        quantize_nchw_to_s2d_kernel<16, false><<<grid, bt, 0, ctx->stream>>>(in, out, c, h, w, scale, (float)zp, pad_t, pad_b, pad_l,
+                                                                              pad_r);
     return after_launch(ctx, "quantize_nchw_to_s2d");
 }
 
@@ -427,15 +432,13 @@ int lut_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, size_t n, const uint
 __global__ void __launch_bounds__(256)
 maxpool_vec_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ y, int n, int h, int w, int c, int oh,
                    int ow, int kh, int kw, int sh, int sw, int pt, int pl, uint32_t zp4) {
-    const int cg = c / 16;
-    const size_t total = (size_t)n * oh * ow * cg;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-         i += (size_t)gridDim.x * blockDim.x) {
-        int g = (int)(i % cg);
-        size_t p = i / cg;
-        int ox = (int)(p % ow);
-        int oy = (int)((p / ow) % oh);
-        int b = (int)(p / ((size_t)ow * oh));
+    // blockIdx.x = (image, output row); blockIdx.y * blockDim.x + thread = (output column, channel group)
+    const uint32_t cg = (uint32_t)c / 16u;
+    const uint32_t j = blockIdx.y * blockDim.x + threadIdx.x;
+    if (j < (uint32_t)ow * cg) {
+        const int g = (int)(j % cg), ox = (int)(j / cg);
+        const int oy = (int)(blockIdx.x % (uint32_t)oh), b = (int)(blockIdx.x / (uint32_t)oh);
+        const size_t p = (size_t)blockIdx.x * ow + ox;
         uint4 m = make_uint4(0, 0, 0, 0);
         int cnt = 0;
         for (int ky = 0; ky < kh; ky++) {
@@ -503,8 +506,11 @@ int maxpool_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, int n, int h, in
         return fail(-EINVAL, "maxpool_u8: empty output");
     const int z = zp < 0 ? 0 : (zp > 255 ? 255 : zp);
     if (c % 16 == 0 && aligned16(x, y)) {
-        size_t total = (size_t)n * oh * ow * (c / 16);
-        maxpool_vec_kernel<<<stream_grid(ctx, total, 256), 256, 0, ctx->stream>>>(
+        const int row_items = ow * (c / 16);
+        const int bt = row_items >= 256 ? 256 : (row_items + 31) / 32 * 32;
+        if ((size_t)n * oh > 0x7fffffffull)
+            return fail(-EINVAL, "maxpool_u8: too many rows");
+        maxpool_vec_kernel<<<dim3((unsigned)((size_t)n * oh), (unsigned)((row_items + bt - 1) / bt)), bt, 0, ctx->stream>>>(
             x, y, n, h, w, c, oh, ow, kh, kw, sh, sw, pt, pl, (uint32_t)z * 0x01010101u);
     } else {
         size_t total = (size_t)n * oh * ow * c;
@@ -544,6 +550,16 @@ int global_avgpool_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, int n, in
     return after_launch(ctx, "global_avgpool_u8");
 }
 
+// i / d and i % d; 32-bit arithmetic when i fits (a 64-bit division costs some seventy instructions).
+__device__ __forceinline__ void divmod_fast(size_t i, uint32_t d, size_t &q, uint32_t &r) {
+    if (i <= 0xffffffffull) {
+        const uint32_t ii = (uint32_t)i;
+        q = ii / d, r = ii % d;
+    } else {
+        q = i / d, r = (uint32_t)(i % d);
+    }
+}
+
 // ---- channel-block copy with optional table (concat / split of NHWC tensors) ---------------------
 // dst[p][dst_off + j] = table ? table[src[p][src_off + j]] : src[p][src_off + j],  j < len, p < pixels.
 // Concat requantises every input into the output's quant param (a 256-entry table per input); a
@@ -559,8 +575,9 @@ copy_channels_kernel(const uint8_t *__restrict__ src, int src_c, int src_off, ui
         const int vpp = len / 16; // 16-byte vectors per pixel
         const size_t total = pixels * vpp;
         for (size_t i = tid; i < total; i += nth) {
-            const size_t p = i / vpp;
-            const int v = (int)(i % vpp);
+            size_t p;
+            uint32_t v;
+            divmod_fast(i, (uint32_t)vpp, p, v);
             uint4 in = __ldg(reinterpret_cast<const uint4 *>(src + p * src_c + src_off) + v);
             if (use_table) {
                 uint32_t w[4] = {in.x, in.y, in.z, in.w};
@@ -612,10 +629,11 @@ resize_nearest_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ y, in
     const int per = vec_ok ? c / 16 : c;
     const size_t total = (size_t)n * oh * ow * per;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        const int j = (int)(i % per);
-        const size_t p = i / per;
-        const int ox = (int)(p % ow), oy = (int)((p / ow) % oh);
-        const size_t b = p / ((size_t)ow * oh);
+        size_t p, row, b;
+        uint32_t j, ox, oy;
+        divmod_fast(i, (uint32_t)per, p, j);
+        divmod_fast(p, (uint32_t)ow, row, ox);
+        divmod_fast(row, (uint32_t)oh, b, oy);
         const size_t sp = (b * h + oy / fy) * w + ox / fx;
         if (vec_ok)
             reinterpret_cast<uint4 *>(y + p * c)[j] = __ldg(reinterpret_cast<const uint4 *>(x + sp * c) + j);

@@ -64,6 +64,8 @@ TC_CASES = [
     # n, h, w, c, oc, kh, kw, stride, pad, dil        GEMM mode (1x1, stride 1)
     (1, 1, 128, 128, 64, 1, 1, 1, 0, 1), (1, 1, 200, 64, 48, 1, 1, 1, 0, 1), (2, 14, 14, 256, 128, 1, 1, 1, 0, 1),
     (1, 7, 7, 32, 16, 1, 1, 1, 0, 1), (1, 1, 300, 384, 1000, 1, 1, 1, 0, 1),
+    # channel counts that do not fill the last N tile of the width chosen for them (32, 32, 64, 64 columns)
+    (2, 14, 14, 32, 144, 1, 1, 1, 0, 1), (1, 9, 9, 128, 80, 1, 1, 1, 0, 1), (1, 12, 12, 32, 176, 1, 1, 1, 0, 1), (1, 6, 6, 96, 576, 1, 1, 1, 0, 1),
     # im2col mode
     (1, 56, 56, 64, 64, 3, 3, 1, 1, 1), (2, 14, 14, 128, 256, 3, 3, 1, 1, 1), (1, 28, 28, 64, 128, 3, 3, 2, 1, 1),
     (3, 7, 7, 256, 64, 3, 3, 1, 1, 1), (1, 16, 16, 32, 32, 3, 3, 1, 2, 2), (2, 28, 28, 128, 64, 1, 1, 2, 0, 1),
@@ -108,7 +110,7 @@ def test_conv_rounding_ties(ctx, qo, path):
     assert np.array_equal(got2.cpu().numpy(), want2)
 
 
-@pytest.mark.parametrize("oc", [16, 48, 80, 192, 272])
+@pytest.mark.parametrize("oc", [16, 48, 80, 96, 144, 160, 192, 272])
 def test_tc_conv_channel_tiles(ctx, qo, oc):
     """Output-channel counts that give every staging-tile width (swizzled and not) and a partial
     last N tile."""
@@ -117,8 +119,10 @@ def test_tc_conv_channel_tiles(ctx, qo, oc):
     assert np.array_equal(got, want)
 
 
-def test_tc_conv_residual_and_second_output(ctx, qo):
-    n, h, w, c, oc = 2, 14, 14, 64, 256
+@pytest.mark.parametrize("oc", [256, 96, 144, 64, 32])
+def test_tc_conv_residual_and_second_output(ctx, qo, oc):
+    """Fused add and second output on every staging-tile width (128, 96, 48, 64 and 32 columns)."""
+    n, h, w, c = 2, 14, 14, 64
     case = make_case(41, n, h, w, c, oc, 1, 1)
     xq, zx, wq, zw, mult, bias, oqp = case
     rng = np.random.default_rng(42)
@@ -238,7 +242,8 @@ def test_tc_conv_kernel_rows_residual_second_output(ctx, qo):
 DEPTHWISE_CASES = [
     # n, h, w, c, kh, kw, stride, pad, dil: the streaming depthwise kernel (groups == channels, c % 4 == 0)
     (2, 28, 28, 96, 3, 3, 1, 1, 1), (1, 56, 56, 160, 3, 3, 2, 1, 1), (3, 9, 11, 32, 3, 3, 1, 1, 2), (1, 14, 14, 960, 3, 3, 1, 1, 1),
-    (2, 7, 7, 4, 5, 5, 1, 2, 1), (1, 112, 112, 32, 3, 3, 2, 0, 1),
+    (2, 7, 7, 4, 5, 5, 1, 2, 1), (1, 112, 112, 32, 3, 3, 2, 0, 1), (2, 7, 7, 8, 3, 3, 1, 1, 1), (1, 15, 13, 8, 3, 3, 2, 1, 1),
+    (1, 5, 3, 4, 3, 3, 1, 0, 1), (1, 6, 9, 12, 3, 3, 2, 0, 1),
 ]
 
 
