@@ -28,11 +28,19 @@ simt_conv_kernel(SimtGeom g, const uint8_t *__restrict__ x, const void *__restri
     const size_t total = (size_t)g.n * g.oh * g.ow * g.oc;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (size_t)gridDim.x * blockDim.x) {
-        const int oc = (int)(i % g.oc);
-        const size_t pix = i / g.oc;
-        const int ox = (int)(pix % g.ow);
-        const int oy = (int)((pix / g.ow) % g.oh);
-        const int b = (int)(pix / ((size_t)g.ow * g.oh));
+        // 32-bit index arithmetic when the index fits: a 64-bit division costs some seventy instructions
+        int oc, ox, oy, b;
+        if (i <= 0xffffffffull) {
+            const uint32_t ii = (uint32_t)i, px = ii / (uint32_t)g.oc, row = px / (uint32_t)g.ow;
+            oc = (int)(ii % (uint32_t)g.oc), ox = (int)(px % (uint32_t)g.ow);
+            oy = (int)(row % (uint32_t)g.oh), b = (int)(row / (uint32_t)g.oh);
+        } else {
+            const size_t pix = i / g.oc;
+            oc = (int)(i % g.oc);
+            ox = (int)(pix % g.ow);
+            oy = (int)((pix / g.ow) % g.oh);
+            b = (int)(pix / ((size_t)g.ow * g.oh));
+        }
         const int grp = oc / goc;
         const int zw = w_zp[oc];
         const int iy0 = oy * g.sh - g.pt, ix0 = ox * g.sw - g.pl;
