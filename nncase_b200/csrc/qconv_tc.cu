@@ -38,7 +38,38 @@ namespace nncb {
 // contiguous in memory (kw * c is 32, 64 or 128 bytes): a plain tiled tensor map whose pixel stride
 // is smaller than its row extent delivers the overlapping windows, one K block per kernel row, and
 // the M tile is a bx x by patch of output pixels instead of 128 consecutive ones.
-enum { MODE_GEMM = 0, MODE_IM2COL = 1, MODE_ROWS = 2 };
+// MODE_PATCH: the same convolutions when c == 16 (space-to-depth image stems) and the weights stay resident.
+// The M tile is an 8 x 16 patch of output pixels; ONE load brings its (8 + kw - 1) x (16 + kh - 1) input
+// cells (16 bytes each, a few KB in a few long rows) and the overlapping windows are formed by the MMA's
+// own operand addressing: in the unswizzled K-major layout a core matrix is 8 rows x 16 bytes = 8
+// consecutive cells of a patch row, the next core matrix along K is the same row one cell further (leading
+// offset 16 bytes, they overlap), the next 8 rows are the next patch row (stride offset = its pitch). MODE_ROWS
+// moves kh x 128 short rows per tile for the same data and is bound by rows per clock.
+enum { MODE_GEMM = 0, MODE_IM2COL = 1, MODE_ROWS = 2, MODE_PATCH = 3 };
+
+// Division by a number fixed at plan creation (Granlund and Montgomery's multiply-and-shift): for n < 2^31,
+// n / d == (umulhi(n, mul) + n) >> shift with shift = ceil(log2 d), mul = floor(2^32 (2^shift - d) / d) + 1.
+// An integer division costs the kernel's one-thread roles some hundred dependent cycles and the epilogue
+// warps some 25 issue slots each; the tile loops have several per tile.
+struct FastDiv {
+    uint32_t mul, shift, d;
+};
+static FastDiv make_fastdiv(int d) {
+    FastDiv f;
+    f.d = (uint32_t)(d < 1 ? 1 : d);
+    f.shift = 0;
+    while ((1ull << f.shift) < f.d)
+        f.shift++;
+    f.mul = (uint32_t)((((1ull << f.shift) - f.d) << 32) / f.d) + 1u;
+    return f;
+}
+__device__ __forceinline__ int fdiv(int n, const FastDiv &f) { return (int)((__umulhi((uint32_t)n, f.mul) + (uint32_t)n) >> f.shift); }
+// quotient and remainder
+__device__ __forceinline__ int fdivmod(int n, const FastDiv &f, int &rem) {
+    const int q = fdiv(n, f);
+    rem = n - q * (int)f.d;
+    return q;
+}
 
 struct TcGeom {
     int mode;
@@ -66,6 +97,9 @@ struct TcGeom {
     int kgroup;         // K blocks per pipeline stage (one barrier round trip and one commit for all of them)
     int b_resident;     // the whole weight matrix stays in shared memory (one N tile, small K): loaded once per CTA
     int bx_log2, tiles_x, tiles_y; // MODE_ROWS: patch width 2^bx_log2 (height 128 >> bx_log2), patches per image
+    int patch_w, patch_h;          // MODE_PATCH: input cells per patch row, patch rows
+    int kh, kw_cells;              // MODE_PATCH: kernel rows, cells per kernel row
+    FastDiv fd_m_tiles, fd_ow, fd_oh, fd_tiles_x, fd_tiles_y;
 };
 
 struct FastEpi;
@@ -133,6 +167,15 @@ static bool rows_mode_applies(const nncb_conv2d_desc &d) {
            (rb == 32 || rb == 64 || rb == 128) && d.h >= d.kh && d.w >= d.kw;
 }
 
+static bool patch_mode_applies(const nncb_conv2d_desc &d) {
+    // cells of exactly one core-matrix width, an even number of them per kernel row (one MMA takes two),
+    // one N tile whose weights stay in shared memory, no residual (its buffers and table need the room)
+    if (!rows_mode_applies(d) || d.c != 16 || (d.kw & 1) || d.kh > 8 || d.oc > 128 || d.has_residual)
+        return false;
+    const size_t b_all = (size_t)d.kh * (((size_t)(d.oc + 31) * d.kw * 16 + 1023) & ~(size_t)1023);
+    return b_all <= 48u * 1024u;
+}
+
 bool tc_conv_supported(const nncb_conv2d_desc &d, std::string *why) {
     auto no = [&](const char *m) {
         if (why)
@@ -172,7 +215,16 @@ bool tc_conv_supported(const nncb_conv2d_desc &d, std::string *why) {
 static int make_tmap_a(TcPlan *tp, const nncb_conv2d_desc &d, const void *x) {
     const TcGeom &g = tp->g;
     CUresult r;
-    if (g.mode == MODE_ROWS) {
+    if (g.mode == MODE_PATCH) {
+        // rows of the image as bytes; the box is the patch of input cells under an 8 x 16 output patch
+        cuuint64_t dims[3] = {(cuuint64_t)d.w * 16, (cuuint64_t)d.h, (cuuint64_t)d.n};
+        cuuint64_t strides[2] = {(cuuint64_t)d.w * 16, (cuuint64_t)d.w * 16 * d.h};
+        cuuint32_t box[3] = {(cuuint32_t)g.patch_w * 16, (cuuint32_t)g.patch_h, 1};
+        cuuint32_t estr[3] = {1, 1, 1};
+        r = g_encode_tiled(&tp->tmap_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(x), dims, strides, box,
+                           estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else if (g.mode == MODE_ROWS) {
         // dimension 1 steps one pixel (c bytes) while dimension 0 spans kw pixels: overlapping windows
         cuuint64_t dims[4] = {(cuuint64_t)(d.kw * d.c), (cuuint64_t)g.ow, (cuuint64_t)d.h, (cuuint64_t)d.n};
         cuuint64_t strides[3] = {(cuuint64_t)d.c, (cuuint64_t)d.c * d.w, (cuuint64_t)d.c * d.w * d.h};
@@ -278,6 +330,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
                  ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
                  : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2,
                                             int c3) {
     asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
@@ -290,6 +347,17 @@ __device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const CUtensorM
                  " [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
                  ::"r"(dst), "l"(map), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h)
                  : "memory");
+}
+
+// Unswizzled K-major operand descriptor: core matrices of 8 rows x 16 bytes (128 contiguous bytes), `lbo`
+// bytes from one to the next along K, `sbo` bytes to the next 8 rows.
+__device__ __forceinline__ uint64_t smem_desc_plain(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)(lbo >> 4) << 16;
+    d |= (uint64_t)(sbo >> 4) << 32;
+    d |= (uint64_t)1 << 46; // descriptor version of this architecture
+    return d;               // layout type 0: no swizzle
 }
 
 // K-major shared-memory operand descriptor: rows of `kb` bytes, 8-row swizzle atoms `8*kb`
@@ -363,6 +431,7 @@ struct FastEpi {
     int n_cls;
     int out_sw;         // swizzle span of the staging sub-tiles: 32 or 0
     int ncg, wcols;     // column groups per tile (2 to 4) and columns per epilogue warp (32 or 16)
+    int halves;         // 2: tiles of 8 epilogue warps, the two halves of the warps take alternate tiles; else 1
     float so, rso, zo;  // output scale, its correctly rounded reciprocal, zero point
     float qlo, qhi;     // the fused clamp's bounds after quantization, within [0, 255]
     const float4 *cst;  // [oc_pad] {mult, bias, bits(corr of class 0), bits(-zw)}
@@ -409,7 +478,7 @@ __device__ __forceinline__ StageGeom stage_geom(const TcGeom &g, const uint8_t *
     StageGeom sg;
     // stage ring, 1024-byte aligned (required by the 128-byte swizzle)
     sg.smem_base = (dev::smem_u32(smem_raw) + 1023u) & ~1023u;
-    sg.a_stage_bytes = 128u * g.kb;
+    sg.a_stage_bytes = g.mode == MODE_PATCH ? (((uint32_t)g.patch_w * 16u * g.patch_h + 1023u) & ~1023u) : 128u * g.kb;
     sg.b_stage_bytes = (uint32_t)g.bn_mma * g.kb;
     // keep every stage's A and B tile 1024-byte aligned (a_stage_bytes is a multiple of 1024)
     sg.b_pitch = (sg.b_stage_bytes + 1023u) & ~1023u;
@@ -486,18 +555,40 @@ __device__ __forceinline__ void producer_loop(const TcGeom &g, const StageGeom &
         for (int kbi = 0; kbi < k_blocks; kbi++)
             tma_load_2d(sg.b_resident + kbi * sg.b_pitch, tmap_b, bar_b, kbi * kb, 0);
     }
+    if (g.mode == MODE_PATCH) {
+        // one load per tile: the input cells under the output patch (weights are resident, one N tile)
+        const uint32_t patch_bytes = (uint32_t)g.patch_w * 16u * g.patch_h;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            int txi, tyi;
+            const int r = fdivmod(tile, g.fd_tiles_x, txi);
+            const int img = fdivmod(r, g.fd_tiles_y, tyi);
+            if (!mbar_wait(bar_empty0 + stage * 8, phase ^ 1, &sh.abort_flag, status, ERR_PRODUCER))
+                return;
+            const uint32_t full = bar_full0 + stage * 8;
+            mbar_expect_tx(full, patch_bytes);
+            tma_load_3d(sg.smem_base + stage * sg.stage_pitch, tmap_a, full, (txi * 8) * 16, tyi * 16, img);
+            if (++stage == stages) {
+                stage = 0;
+                phase ^= 1;
+            }
+        }
+        return;
+    }
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-        const int mt = tile % g.m_tiles, nt = tile / g.m_tiles;
+        int mt;
+        const int nt = fdivmod(tile, g.fd_m_tiles, mt);
         const int m0 = mt * 128, n0 = nt * g.bn_mma;
         int cw = 0, chh = 0, cn = 0;
         if (rows) {
-            const int txi = mt % g.tiles_x, r = mt / g.tiles_x;
+            int txi, tyi;
+            const int r = fdivmod(mt, g.fd_tiles_x, txi);
+            cn = fdivmod(r, g.fd_tiles_y, tyi);
             cw = txi << g.bx_log2;
-            chh = (r % g.tiles_y) * (128 >> g.bx_log2);
-            cn = r / g.tiles_y;
+            chh = tyi * (128 >> g.bx_log2);
         } else if (!gemm) {
-            const int q = m0 % g.ow, pp = (m0 / g.ow) % g.oh;
-            cn = m0 / (g.ow * g.oh);
+            int q, pp;
+            const int row_i = fdivmod(m0, g.fd_ow, q);
+            cn = fdivmod(row_i, g.fd_oh, pp);
             cw = q * g.stride_w - g.pad_l;
             chh = pp * g.stride_h - g.pad_t;
         }
@@ -605,6 +696,25 @@ __device__ __forceinline__ void mma_loop(const TcGeom &g, const StageGeom &sg, T
             acc_phase0 ^= 1;
         fence_after_sync();
         const uint32_t tmem_d = tmem_base + buf * g.acc_stride;
+        if (g.mode == MODE_PATCH) {
+            if (!mbar_wait(bar_full0 + stage * 8, phase, &sh.abort_flag, status, ERR_MMA_FULL))
+                return;
+            fence_after_sync();
+            // rows of the tile = (patch row y, x) with x fastest: 8-row groups step one patch row
+            const uint32_t row16 = (uint32_t)g.patch_w; // patch row pitch in 16-byte units
+            uint64_t da = smem_desc_plain(sg.smem_base, 16u, row16 * 16u) + (uint64_t)(stage * pitch16);
+            uint64_t db = desc_bres;
+            for (int ky = 0; ky < g.kh; ky++, da += row16, db += bres_pitch16)
+                for (int j = 0; j < g.kw_cells; j += 2) // one MMA: cells j, j + 1 of the kernel row (K = 32 bytes)
+                    mma_i8(tmem_d, da + (uint64_t)j, db + (uint64_t)j, idesc, (ky | j) != 0);
+            mma_commit(bar_empty0 + stage * 8);
+            if (++stage == stages) {
+                stage = 0;
+                phase ^= 1;
+            }
+            mma_commit(smem_u32(&sh.bar_acc_full[buf]));
+            continue;
+        }
         if (kgroup == 1) {
             for (int kbi = 0; kbi < k_blocks; kbi++) {
                 if (!mbar_wait(bar_full0 + stage * 8, phase, &sh.abort_flag, status, ERR_MMA_FULL))
@@ -670,20 +780,24 @@ __device__ __forceinline__ void epilogue_generic(const TcArgs &a, TcShared &sh, 
     int it = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, it++) {
         const int buf = it & 1;
-        const int mt = tile % g.m_tiles, nt = tile / g.m_tiles;
+        int mt;
+        const int nt = fdivmod(tile, g.fd_m_tiles, mt);
         int m = mt * 128 + row;
         bool row_ok = m < g.m_total;
-        if (g.mode == MODE_ROWS) {
+        if (g.mode == MODE_ROWS || g.mode == MODE_PATCH) {
             // the tile is a patch of output pixels: row -> (patch row, patch column)
-            const int txi = mt % g.tiles_x, r2 = mt / g.tiles_x;
+            int txi, tyi;
+            const int r2 = fdivmod(mt, g.fd_tiles_x, txi);
+            const int img = fdivmod(r2, g.fd_tiles_y, tyi);
             const int ox = (txi << g.bx_log2) + (row & ((1 << g.bx_log2) - 1));
-            const int oy = (r2 % g.tiles_y) * (128 >> g.bx_log2) + (row >> g.bx_log2);
+            const int oy = tyi * (128 >> g.bx_log2) + (row >> g.bx_log2);
             row_ok = ox < g.ow && oy < g.oh;
-            m = ((r2 / g.tiles_y) * g.oh + oy) * g.ow + ox;
+            m = (img * g.oh + oy) * g.ow + ox;
         }
         int cls = 0; // border class of this output pixel
         if (g.mode == MODE_IM2COL && row_ok) {
-            const int ox = m % g.ow, oy = (m / g.ow) % g.oh;
+            int ox, oy;
+            fdivmod(fdivmod(m, g.fd_ow, ox), g.fd_oh, oy);
             cls = (int)a.ycls[oy] * g.n_cls_x + (int)a.xcls[ox];
         }
         const uint32_t ph = buf ? acc_phase1 : acc_phase0;
@@ -878,8 +992,11 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
     const int ew = warp - 2;
     const int et = ew * 32 + lane;   // index among the epilogue threads
     const int lane_group = warp & 3; // TMEM lanes 32*lane_group .. +31 are this warp's
-    const int grp = ew >> 2;         // which group of the tile's columns this warp owns
-    const bool active = grp < f.ncg; // narrow tiles leave the last warps without columns
+    // which group of the tile's columns this warp owns, and (narrow tiles, f.halves == 2) which of the
+    // alternating tiles: while one half of the warps waits for its accumulator, TMEM loads and stores, the
+    // other half requantises the tile before
+    const int grp = (ew >> 2) % f.ncg, half = (ew >> 2) / f.ncg;
+    const bool active = half < f.halves; // some widths leave the last warps without columns
     const int row = lane_group * 32 + lane;
     const int hw = f.wcols;          // bytes per row of this warp's sub-tile (32 rows x hw columns)
     // Every warp stages, stores and prefetches its own 32 x hw sub-tile: no block-wide barrier in
@@ -903,10 +1020,11 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
             c[1] = mt * 128 + lane_group * 32;
             return c[1] < g.m_total;
         }
-        const int txi = mt % g.tiles_x, r2 = mt / g.tiles_x, r0 = lane_group * 32;
+        int txi, tyi;
+        const int r2 = fdivmod(mt, g.fd_tiles_x, txi), r0 = lane_group * 32;
+        c[3] = fdivmod(r2, g.fd_tiles_y, tyi);
         c[1] = (txi << g.bx_log2) + (r0 & ((1 << g.bx_log2) - 1));
-        c[2] = (r2 % g.tiles_y) * (128 >> g.bx_log2) + (r0 >> g.bx_log2);
-        c[3] = r2 / g.tiles_y;
+        c[2] = tyi * (128 >> g.bx_log2) + (r0 >> g.bx_log2);
         return c[1] < g.ow && c[2] < g.oh;
     };
     auto load_sub = [&](uint32_t dst, const CUtensorMap *map, uint32_t bar, const int (&c)[4]) {
@@ -934,11 +1052,14 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
                          : "memory");
     }
     // residual sub-tiles of this warp's next RES_BUFS tiles are always in flight
+    const int tstep = f.halves * (int)gridDim.x; // distance between this warp's tiles
     if (RES && lane == 0 && active) {
-        int t = blockIdx.x;
-        for (int b = 0; b < RES_BUFS && t < total_tiles; b++, t += gridDim.x) {
+        int t = blockIdx.x + half * (int)gridDim.x;
+        for (int b = 0; b < RES_BUFS && t < total_tiles; b++, t += tstep) {
             int c[4];
-            sub_coords(t % g.m_tiles, t / g.m_tiles, c); // a load outside the tensor still completes, with fill
+            int tm;
+            const int tn = fdivmod(t, g.fd_m_tiles, tm);
+            sub_coords(tm, tn, c); // a load outside the tensor still completes, with fill
             mbar_expect_tx(bar_res + b * 8, res_bytes);
             load_sub(s_res + b * f.res_pitch, tmap_res, bar_res + b * 8, c);
         }
@@ -949,7 +1070,8 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
     bool dead = false; // after a failed wait the warp only keeps the block-wide barriers company
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, it++) {
         const int buf = it & 1;
-        const int mt = tile % g.m_tiles, nt = tile / g.m_tiles;
+        int mt;
+        const int nt = fdivmod(tile, g.fd_m_tiles, mt);
         const int m = mt * 128 + row;
         const bool row_ok = m < g.m_total;
         const int oc0 = nt * g.bn;
@@ -972,11 +1094,12 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
             cur_nt = nt;
             epi_bar_sync();
         }
-        if (dead || !active)
+        if (dead || !active || (f.halves == 2 && (it & 1) != half))
             continue;
         int cls = 0;
         if (g.mode == MODE_IM2COL && row_ok) {
-            const int ox = m % g.ow, oy = (m / g.ow) % g.oh;
+            int ox, oy;
+            fdivmod(fdivmod(m, g.fd_ow, ox), g.fd_oh, oy);
             cls = (int)a.ycls[oy] * g.n_cls_x + (int)a.xcls[ox];
         }
         const uint32_t ph = buf ? acc_phase1 : acc_phase0;
@@ -1087,9 +1210,11 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
                     store_sub(tmap_y2, s_y2, c);
             }
             tma_store_commit();
-            const int next = tile + RES_BUFS * (int)gridDim.x;
+            const int next = tile + RES_BUFS * tstep;
             if (RES && next < total_tiles) {
-                sub_coords(next % g.m_tiles, next / g.m_tiles, c);
+                int nm;
+                const int nn = fdivmod(next, g.fd_m_tiles, nm);
+                sub_coords(nm, nn, c);
                 mbar_expect_tx(bar_res + rb * 8, res_bytes);
                 load_sub(s_res_cur, tmap_res, bar_res + rb * 8, c);
             }
@@ -1228,7 +1353,7 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
     TcGeom &g = tp->g;
     const bool gemm = d.kh == 1 && d.kw == 1 && d.stride_h == 1 && d.stride_w == 1 && d.pad_t == 0 && d.pad_b == 0 &&
                       d.pad_l == 0 && d.pad_r == 0;
-    g.mode = gemm ? MODE_GEMM : (rows_mode_applies(d) ? MODE_ROWS : MODE_IM2COL);
+    g.mode = gemm ? MODE_GEMM : (patch_mode_applies(d) ? MODE_PATCH : (rows_mode_applies(d) ? MODE_ROWS : MODE_IM2COL));
     g.oh = cv->oh, g.ow = cv->ow;
     g.m_total = d.n * cv->oh * cv->ow;
     g.oc = d.oc;
@@ -1261,6 +1386,19 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
         g.taps = d.kh;
         g.kw = 1;
     }
+    if (g.mode == MODE_PATCH) {
+        g.bx_log2 = 3; // 8 x 16 output pixels
+        g.tiles_x = (g.ow + 7) / 8, g.tiles_y = (g.oh + 15) / 16;
+        g.m_tiles = d.n * g.tiles_x * g.tiles_y;
+        g.kb = d.kw * d.c; // the weights keep the layout of MODE_ROWS: one K block per kernel row
+        g.c_blocks = 1;
+        g.taps = d.kh;
+        g.kw = 1;
+        g.kh = d.kh, g.kw_cells = d.kw;
+        g.patch_w = 8 + d.kw - 1, g.patch_h = 16 + d.kh - 1;
+    }
+    g.fd_m_tiles = make_fastdiv(g.m_tiles), g.fd_ow = make_fastdiv(g.ow), g.fd_oh = make_fastdiv(g.oh);
+    g.fd_tiles_x = make_fastdiv(g.tiles_x), g.fd_tiles_y = make_fastdiv(g.tiles_y);
     g.stride_h = d.stride_h, g.stride_w = d.stride_w, g.pad_t = d.pad_t, g.pad_l = d.pad_l;
     g.dil_h = d.dil_h, g.dil_w = d.dil_w;
     g.x_zp = d.x_zp;
@@ -1282,12 +1420,17 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
     tp->f = new FastEpi();
     FastEpi &fe = *tp->f;
     memset(&fe, 0, sizeof(fe));
-    const uint32_t a_stage = 128u * g.kb, b_pitch = ((uint32_t)g.bn_mma * g.kb + 1023u) & ~1023u;
+    const uint32_t a_stage = g.mode == MODE_PATCH ? (((uint32_t)g.patch_w * 16u * g.patch_h + 1023u) & ~1023u) : 128u * g.kb;
+    const uint32_t b_pitch = ((uint32_t)g.bn_mma * g.kb + 1023u) & ~1023u;
     const uint32_t budget = 224u * 1024u - 1024u; // dynamic shared memory we may use, minus alignment slack
     uint32_t extras = 0;
     tp->fast = false;
     if (fast_shape) {
-        const uint32_t tile_bytes = (128u * g.bn + 1023u) & ~1023u;
+        // 64- and 32-column tiles: eight warps per tile (four lane quarters x two column groups), the two
+        // halves of the sixteen take alternate tiles; every warp has its own staging sub-tile, so the
+        // staging areas hold two tiles
+        fe.halves = (g.bn == 64 || g.bn == 32) ? 2 : 1;
+        const uint32_t tile_bytes = ((uint32_t)fe.halves * 128u * g.bn + 1023u) & ~1023u;
         uint32_t off = 0;
         fe.off_out = off, off += tile_bytes;
         fe.off_y2 = off, off += (d.has_y2 || lut_only) ? tile_bytes : 0;
@@ -1300,8 +1443,8 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
         fe.off_corr = off;
         extras = off; // the per-class table is appended once the classes are known
         // each epilogue warp stages a 32-row x wcols-byte sub-tile; 32-byte rows are the swizzle span
-        fe.wcols = g.bn >= 96 ? 32 : 16;
-        fe.ncg = g.bn / fe.wcols; // 128: 4 x 32, 96: 3 x 32, 64: 4 x 16, 48: 3 x 16, 32: 2 x 16
+        fe.wcols = g.bn >= 64 ? 32 : 16;
+        fe.ncg = g.bn / fe.wcols; // 128: 4 x 32, 96: 3 x 32, 64: 2 x 32, 48: 3 x 16, 32: 2 x 16
         fe.out_sw = fe.wcols == 32 ? 32 : 0;
         tp->fast = true;
     }
@@ -1493,6 +1636,11 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
     }
     if (g.kgroup == 1)
         g.kgroup = fallback;
+    if (g.mode == MODE_PATCH) {
+        if (!g.b_resident || g.n_tiles != 1)
+            return fail(-ENOSYS, "tcgen05 conv: patch mode without resident weights");
+        g.kgroup = 1; // a stage is one tile's patch
+    }
     const uint32_t per_stage = (uint32_t)g.kgroup * per_kblock;
     int stages = (int)(room / per_stage);
     if (stages > MAX_STAGES)
@@ -1548,7 +1696,7 @@ static int make_tmap_out(CUtensorMap *map, const TcPlan *tp, const void *ptr) {
                                        : (sw == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
                                                    : (sw == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE));
     CUresult r;
-    if (g.mode == MODE_ROWS) {
+    if (g.mode == MODE_ROWS || g.mode == MODE_PATCH) {
         // a warp's 32 rows are sx x sy pixels of the patch
         const int bx = 1 << g.bx_log2, sx = bx < 32 ? bx : 32;
         const int n_img = g.m_total / (g.oh * g.ow);
@@ -1617,7 +1765,7 @@ int tc_conv_run(nncb_context *ctx, nncb_qconv2d *cv, const uint8_t *x, const uin
         const int variant = (res ? 4 : 0) | (y2 ? 2 : 0) | (tp->g.has_xsum ? 1 : 0);
 #define NNCB_LAUNCH_FAST(R, Y, C)                                                                                     \
     do {                                                                                                              \
-        if (tp->g.mode == MODE_ROWS)                                                                                  \
+        if (tp->g.mode == MODE_ROWS || tp->g.mode == MODE_PATCH)                                                      \
             tc_conv_fast_kernel<R, Y, C, true><<<grid, TC_THREADS, tp->smem_bytes, ctx->stream>>>(                    \
                 tp->tmap_a, tp->tmap_b, tp->tmap_y, my2, mres, a);                                                    \
         else                                                                                                          \
