@@ -1008,6 +1008,7 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
     const uint32_t s_lut2 = sg.smem_base + f.off_lut2, s_tab = sg.smem_base + f.off_tab;
     const uint32_t bar_res = smem_u32(&sh.bar_res[ew * RES_BUFS]);
     const bool multi_cls = f.n_cls > 1;
+    const bool sat = f.qlo == 0.f && f.qhi == 255.f; // no activation clamp on the output
     const uint32_t res_bytes = 32u * hw;
     const int col_off = grp * hw;
     constexpr bool rows = ROWS; // the tile is a patch of pixels (MODE_ROWS)
@@ -1130,8 +1131,9 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
         }
         const uint32_t corr_row = s_corr + (uint32_t)(cls * f.corr_pitch) * 4;
         // eight columns at a time: short live ranges keep the 16 epilogue warps within the register file
-        auto chunk = [&](const int (&v)[8], const int cc, auto multi_tag) {
+        auto chunk = [&](const int (&v)[8], const int cc, auto multi_tag, auto sat_tag) {
             constexpr bool MULTI = decltype(multi_tag)::value;
+            constexpr bool SAT = decltype(sat_tag)::value;
             const int c0 = col_off + cc; // column within the tile
             const uint32_t half16 = stage_addr(0, lane, cc >> 4, hw, f.out_sw) + (cc & 8); // offset in a sub-tile
             uint2 rw = make_uint2(0, 0);
@@ -1153,8 +1155,13 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
                 // Quantization is monotone, so the fused clamp on the real value is a clamp of the
                 // quantized value to the quantized bounds; clamping before rounding to an integer is
                 // the same as after, and adding 2^23 rounds to nearest-even like rint.
-                const float t = fminf(fmaxf(__fadd_rn(q0, f.zo), f.qlo), f.qhi);
-                bits[j] = __float_as_uint(__fadd_rn(t, MAGIC)); // 0x4B0000qq: low byte = the quantized value
+                if (SAT) {
+                    // no activation clamp: one saturating round-to-nearest-even conversion is rint + clamp to 0..255
+                    asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(bits[j]) : "f"(__fadd_rn(q0, f.zo)));
+                } else {
+                    const float t = fminf(fmaxf(__fadd_rn(q0, f.zo), f.qlo), f.qhi);
+                    bits[j] = __float_as_uint(__fadd_rn(t, MAGIC)); // 0x4B0000qq: low byte = the quantized value
+                }
                 if (RES) {
                     // dequantize both addends, add, requantise -- as a 64 K-entry table of all byte pairs.
                     // Index (q << 8) | r, with q's low bits folded into the bank bits of r: pixels of one
@@ -1178,24 +1185,26 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
             }
         };
         // the TMEM load of the next eight columns is in flight while the current ones are requantised
-        auto columns = [&](auto multi_tag) {
+        auto columns = [&](auto multi_tag, auto sat_tag) {
             int va[8], vb[8];
             __syncwarp();
             tmem_ld8_issue(tbase + col_off, va);
             for (int cc = 0; cc < hw; cc += 16) { // hw is 16 or 32
                 tmem_ld_wait();
                 tmem_ld8_issue(tbase + col_off + cc + 8, vb);
-                chunk(va, cc, multi_tag);
+                chunk(va, cc, multi_tag, sat_tag);
                 tmem_ld_wait();
                 if (cc + 16 < hw)
                     tmem_ld8_issue(tbase + col_off + cc + 16, va);
-                chunk(vb, cc + 8, multi_tag);
+                chunk(vb, cc + 8, multi_tag, sat_tag);
             }
         };
         if (multi_cls)
-            columns(std::true_type{});
+            columns(std::true_type{}, std::false_type{});
+        else if (sat)
+            columns(std::false_type{}, std::true_type{});
         else
-            columns(std::false_type{});
+            columns(std::false_type{}, std::false_type{});
         // accumulator and residual sub-tile are consumed; staging sub-tiles are written
         fence_before_sync();
         fence_async_smem();
