@@ -105,6 +105,13 @@ struct DwFast {
     float qlo, qhi;    // the fused clamp as quantized bounds
 };
 
+// rint (nearest even) and clamp to 0..255 in one conversion
+__device__ __forceinline__ uint32_t rint_sat_u8(float v) {
+    uint32_t q;
+    asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(q) : "f"(v));
+    return q;
+}
+
 __global__ void __launch_bounds__(256)
 dw_conv_kernel(SimtGeom g, const uint8_t *__restrict__ x, const int16_t *__restrict__ wdw, EpiParams p, DwFast f,
                const uint8_t *__restrict__ res, uint8_t *__restrict__ y, uint8_t *__restrict__ y2) {
@@ -156,7 +163,7 @@ dw_conv_kernel(SimtGeom g, const uint8_t *__restrict__ x, const int16_t *__restr
         int q[4];
         if (f.on) {
             // the tensor-core kernel's epilogue: v / so as q0 = RN(v r), q = RN(q0 + RN(v - q0 so) r), the
-            // clamp folded into the quantized bounds, + 2^23 to round to nearest-even
+            // clamp folded into the quantized bounds, one saturating round-to-nearest-even conversion
             const float m4[4] = {mult.x, mult.y, mult.z, mult.w}, b4[4] = {bias.x, bias.y, bias.z, bias.w};
 #pragma unroll
             for (int e = 0; e < 4; e++) {
@@ -164,7 +171,7 @@ dw_conv_kernel(SimtGeom g, const uint8_t *__restrict__ x, const int16_t *__restr
                 float q0 = __fmul_rn(v, f.rso);
                 q0 = __fmaf_rn(__fmaf_rn(-q0, f.so, v), f.rso, q0);
                 const float t = fminf(fmaxf(__fadd_rn(q0, f.zo), f.qlo), f.qhi);
-                q[e] = (int)(__float_as_uint(__fadd_rn(t, 8388608.0f)) & 255u);
+                q[e] = (int)rint_sat_u8(t);
             }
         } else {
             const uint32_t rv = p.has_res ? __ldg(reinterpret_cast<const uint32_t *>(res + o)) : 0u;
@@ -247,7 +254,7 @@ dw3x3_conv_kernel(SimtGeom g, const uint8_t *__restrict__ x, const int16_t *__re
                     float q0 = __fmul_rn(v, f.rso);
                     q0 = __fmaf_rn(__fmaf_rn(-q0, f.so, v), f.rso, q0);
                     const float tq = fminf(fmaxf(__fadd_rn(q0, f.zo), f.qlo), f.qhi);
-                    q[e] = (int)(__float_as_uint(__fadd_rn(tq, 8388608.0f)) & 255u);
+                    q[e] = (int)rint_sat_u8(tq);
                 }
             } else {
                 const uint32_t rv = p.has_res ? __ldg(reinterpret_cast<const uint32_t *>(res + o)) : 0u;

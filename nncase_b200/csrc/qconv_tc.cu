@@ -459,7 +459,7 @@ constexpr int EPI_WARPS = 16; // four per TMEM lane quadrant: enough warps per s
 constexpr int TC_THREADS = 64 + 32 * EPI_WARPS;
 constexpr int MAX_STAGES = 8;
 constexpr int RES_BUFS = 3; // residual sub-tiles in flight per epilogue warp: the fetch of tile i+3 starts when tile i is done
-constexpr float MAGIC = 8388608.0f; // 2^23: for 0 <= x <= 255, x + MAGIC has bits 0x4B0000qq with qq = rint(x)
+constexpr int ADD_TABLE_BYTES = 256 * 260; // fused residual add: rows of 256 entries, 260 bytes apart
 
 struct TcShared {
     uint64_t bar_full[MAX_STAGES], bar_empty[MAX_STAGES], bar_acc_full[2], bar_acc_empty[2], bar_b, bar_res[EPI_WARPS * RES_BUFS];
@@ -1008,7 +1008,7 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
     const uint32_t s_lut2 = sg.smem_base + f.off_lut2, s_tab = sg.smem_base + f.off_tab;
     const uint32_t bar_res = smem_u32(&sh.bar_res[ew * RES_BUFS]);
     const bool multi_cls = f.n_cls > 1;
-    const bool sat = f.qlo == 0.f && f.qhi == 255.f; // no activation clamp on the output
+    const int clamp_level = f.qhi < 255.f ? 2 : (f.qlo > 0.f ? 1 : 0); // which bounds an activation moved inside 0..255
     const uint32_t res_bytes = 32u * hw;
     const int col_off = grp * hw;
     constexpr bool rows = ROWS; // the tile is a patch of pixels (MODE_ROWS)
@@ -1041,9 +1041,9 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
             tma_store_2d(map, src, c[0], c[1]);
     };
     if (RES) {
-        // the add table: 64 KB, copied once per CTA
+        // the add table (65 KB), copied once per CTA
         const uint4 *src = reinterpret_cast<const uint4 *>(f.add_table);
-        for (int i = et; i < 4096; i += 32 * EPI_WARPS)
+        for (int i = et; i < ADD_TABLE_BYTES / 16; i += 32 * EPI_WARPS)
             sts128(s_tab + i * 16, __ldg(src + i));
     }
     if (Y2) {
@@ -1131,9 +1131,9 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
         }
         const uint32_t corr_row = s_corr + (uint32_t)(cls * f.corr_pitch) * 4;
         // eight columns at a time: short live ranges keep the 16 epilogue warps within the register file
-        auto chunk = [&](const int (&v)[8], const int cc, auto multi_tag, auto sat_tag) {
+        auto chunk = [&](const int (&v)[8], const int cc, auto multi_tag, auto clamp_tag) {
             constexpr bool MULTI = decltype(multi_tag)::value;
-            constexpr bool SAT = decltype(sat_tag)::value;
+            constexpr int CL = decltype(clamp_tag)::value; // 0: no bound inside 0..255, 1: a lower one, 2: both
             const int c0 = col_off + cc; // column within the tile
             const uint32_t half16 = stage_addr(0, lane, cc >> 4, hw, f.out_sw) + (cc & 8); // offset in a sub-tile
             uint2 rw = make_uint2(0, 0);
@@ -1153,22 +1153,21 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
                 float q0 = __fmul_rn(x, f.rso);
                 q0 = __fmaf_rn(__fmaf_rn(-q0, f.so, x), f.rso, q0);
                 // Quantization is monotone, so the fused clamp on the real value is a clamp of the
-                // quantized value to the quantized bounds; clamping before rounding to an integer is
-                // the same as after, and adding 2^23 rounds to nearest-even like rint.
-                if (SAT) {
-                    // no activation clamp: one saturating round-to-nearest-even conversion is rint + clamp to 0..255
-                    asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(bits[j]) : "f"(__fadd_rn(q0, f.zo)));
-                } else {
-                    const float t = fminf(fmaxf(__fadd_rn(q0, f.zo), f.qlo), f.qhi);
-                    bits[j] = __float_as_uint(__fadd_rn(t, MAGIC)); // 0x4B0000qq: low byte = the quantized value
-                }
+                // quantized value to the quantized bounds, and clamping before rounding to an integer is
+                // the same as after. One saturating round-to-nearest-even conversion is rint + clamp to
+                // 0..255; a bound that an activation moved inside that range is applied first.
+                float u = __fadd_rn(q0, f.zo);
+                if (CL >= 1)
+                    u = fmaxf(u, f.qlo);
+                if (CL == 2)
+                    u = fminf(u, f.qhi);
+                asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(bits[j]) : "f"(u));
                 if (RES) {
-                    // dequantize both addends, add, requantise -- as a 64 K-entry table of all byte pairs.
-                    // Index (q << 8) | r, with q's low bits folded into the bank bits of r: pixels of one
-                    // channel have similar q and similar r, which would otherwise share few banks.
-                    uint32_t idx = __byte_perm(rwa[j >> 2], bits[j], 0x6540 | (j & 3));
-                    idx ^= (idx >> 6) & 0x7Cu;
-                    bits[j] = lds8(s_tab + idx);
+                    // dequantize both addends, add, requantise -- as a table of all byte pairs. Rows of 260
+                    // bytes: the bank of entry (q, r) is (q + r / 4) mod 32, so the pixels of one channel,
+                    // which have similar q and similar r, spread over the banks.
+                    const uint32_t r = __byte_perm(rwa[j >> 2], 0u, 0x4440 | (j & 3));
+                    bits[j] = lds8(s_tab + bits[j] * 260u + r);
                 }
             }
             uint2 o;
@@ -1178,33 +1177,45 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
             if (Y2) {
 #pragma unroll
                 for (int j = 0; j < 8; j++)
-                    bits[j] = lds8(s_lut2 + (RES ? bits[j] : (bits[j] & 255u)));
+                    bits[j] = lds8(s_lut2 + bits[j]);
                 o.x = __byte_perm(__byte_perm(bits[0], bits[1], 0x0040), __byte_perm(bits[2], bits[3], 0x0040), 0x5410);
                 o.y = __byte_perm(__byte_perm(bits[4], bits[5], 0x0040), __byte_perm(bits[6], bits[7], 0x0040), 0x5410);
                 sts64(s_y2 + half16, o);
             }
         };
         // the TMEM load of the next eight columns is in flight while the current ones are requantised
-        auto columns = [&](auto multi_tag, auto sat_tag) {
+        auto columns = [&](auto multi_tag, auto clamp_tag) {
             int va[8], vb[8];
             __syncwarp();
             tmem_ld8_issue(tbase + col_off, va);
             for (int cc = 0; cc < hw; cc += 16) { // hw is 16 or 32
                 tmem_ld_wait();
                 tmem_ld8_issue(tbase + col_off + cc + 8, vb);
-                chunk(va, cc, multi_tag, sat_tag);
+                chunk(va, cc, multi_tag, clamp_tag);
                 tmem_ld_wait();
                 if (cc + 16 < hw)
                     tmem_ld8_issue(tbase + col_off + cc + 16, va);
-                chunk(vb, cc + 8, multi_tag, sat_tag);
+                chunk(vb, cc + 8, multi_tag, clamp_tag);
             }
         };
-        if (multi_cls)
-            columns(std::true_type{}, std::false_type{});
-        else if (sat)
-            columns(std::false_type{}, std::true_type{});
-        else
-            columns(std::false_type{}, std::false_type{});
+        using cl0 = std::integral_constant<int, 0>;
+        using cl1 = std::integral_constant<int, 1>;
+        using cl2 = std::integral_constant<int, 2>;
+        if (multi_cls) {
+            if (clamp_level == 0)
+                columns(std::true_type{}, cl0{});
+            else if (clamp_level == 1)
+                columns(std::true_type{}, cl1{});
+            else
+                columns(std::true_type{}, cl2{});
+        } else {
+            if (clamp_level == 0)
+                columns(std::false_type{}, cl0{});
+            else if (clamp_level == 1)
+                columns(std::false_type{}, cl1{});
+            else
+                columns(std::false_type{}, cl2{});
+        }
         // accumulator and residual sub-tile are consumed; staging sub-tiles are written
         fence_before_sync();
         fence_async_smem();
@@ -1448,7 +1459,7 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
         fe.res_pitch = tile_bytes;
         fe.off_cst = off, off += (uint32_t)g.bn * 16;
         fe.off_lut2 = off, off += 256;
-        fe.off_tab = off, off += d.has_residual ? 65536 : 0;
+        fe.off_tab = off, off += d.has_residual ? ADD_TABLE_BYTES : 0;
         fe.off_corr = off;
         extras = off; // the per-class table is appended once the classes are known
         // each epilogue warp stages a 32-row x wcols-byte sub-tile; 32-byte rows are the swizzle span
@@ -1585,7 +1596,7 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
             // every (convolution output byte, residual byte) pair through the unfused chain:
             // dequantize both, add, divide by the output scale, add the zero point, round, clamp
             ok = ok && d.res_zp >= 0 && d.res_zp <= 255;
-            addtab.resize(65536);
+            addtab.assign(ADD_TABLE_BYTES, 0);
             const float so = d.out_scale, zo = (float)d.out_zp, sr = d.res_scale, zr = (float)d.res_zp;
             const float sa = d.add_out_scale, za = (float)d.add_out_zp;
             for (int qa = 0; qa < 256; qa++) {
@@ -1597,7 +1608,7 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
                     const float sum = ya + yb;
                     const float p = sum / sa;
                     const float u = p + za;
-                    addtab[qa * 256 + (r ^ ((qa << 2) & 0x7C))] = (uint8_t)std::fmin(std::fmax(rintf(u), 0.f), 255.f);
+                    addtab[qa * 260 + r] = (uint8_t)std::fmin(std::fmax(rintf(u), 0.f), 255.f);
                 }
             }
         }
