@@ -65,6 +65,31 @@ __device__ __forceinline__ float dequant_dev(float q, float zp, float scale) {
     return __fmul_rn(__fsub_rn(q, zp), scale);
 }
 // kernels::detail::clamp = max(min(v, hi), lo)
+// Two IEEE single-precision operations per instruction (sm_100 f32x2 forms): each half rounds exactly like
+// the scalar operation, and the epilogue, which is bound by instruction issue, spends one slot instead of two.
+// Never feed mul2 straight into add2 (or an fma2 with a factor of one or an addend of -0) where the product has to
+// round on its own: the assembler turns all of these into one fused multiply-add.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t p;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(p) : "f"(lo), "f"(hi));
+    return p;
+}
+__device__ __forceinline__ void unpack2(uint64_t p, float &lo, float &hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(p)); }
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
 __device__ __forceinline__ float clamp_dev(float v, float lo, float hi) {
     float t = v < hi ? v : hi;
     return t > lo ? t : lo;

@@ -112,6 +112,25 @@ __device__ __forceinline__ uint32_t rint_sat_u8(float v) {
     return q;
 }
 
+// The division-free exact requantisation on two accumulators at once (f32x2 instructions): v = acc * mult + bias,
+// v / so as q0 = RN(v r), q = RN(q0 + RN(v - q0 so) r), + zo, the clamp folded into the quantized bounds, one
+// saturating round-to-nearest-even conversion each.
+__device__ __forceinline__ void dw_requant2(int a0, int a1, float m0, float m1, float b0, float b1, const DwFast &f, int &q0o,
+                                            int &q1o) {
+    // the product must round before the bias is added: the assembler contracts a packed multiply and a packed
+    // add into one fused operation even when both carry .rn, so the add is two scalar ones
+    float p0, p1;
+    unpack2(mul2(pack2((float)a0, (float)a1), pack2(m0, m1)), p0, p1);
+    const uint64_t v2 = pack2(__fadd_rn(p0, b0), __fadd_rn(p1, b1));
+    const uint64_t r2 = pack2(f.rso, f.rso);
+    const uint64_t q0 = mul2(v2, r2);
+    const uint64_t q2 = fma2(fma2(q0, pack2(-f.so, -f.so), v2), r2, q0);
+    float u0, u1;
+    unpack2(add2(q2, pack2(f.zo, f.zo)), u0, u1);
+    q0o = (int)rint_sat_u8(fminf(fmaxf(u0, f.qlo), f.qhi));
+    q1o = (int)rint_sat_u8(fminf(fmaxf(u1, f.qlo), f.qhi));
+}
+
 __global__ void __launch_bounds__(256)
 dw_conv_kernel(SimtGeom g, const uint8_t *__restrict__ x, const int16_t *__restrict__ wdw, EpiParams p, DwFast f,
                const uint8_t *__restrict__ res, uint8_t *__restrict__ y, uint8_t *__restrict__ y2) {
@@ -162,17 +181,8 @@ dw_conv_kernel(SimtGeom g, const uint8_t *__restrict__ x, const int16_t *__restr
         const size_t o = pix * g.c + c0;
         int q[4];
         if (f.on) {
-            // the tensor-core kernel's epilogue: v / so as q0 = RN(v r), q = RN(q0 + RN(v - q0 so) r), the
-            // clamp folded into the quantized bounds, one saturating round-to-nearest-even conversion
-            const float m4[4] = {mult.x, mult.y, mult.z, mult.w}, b4[4] = {bias.x, bias.y, bias.z, bias.w};
-#pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const float v = __fadd_rn(__fmul_rn((float)acc[e], m4[e]), b4[e]);
-                float q0 = __fmul_rn(v, f.rso);
-                q0 = __fmaf_rn(__fmaf_rn(-q0, f.so, v), f.rso, q0);
-                const float t = fminf(fmaxf(__fadd_rn(q0, f.zo), f.qlo), f.qhi);
-                q[e] = (int)rint_sat_u8(t);
-            }
+            dw_requant2(acc[0], acc[1], mult.x, mult.y, bias.x, bias.y, f, q[0], q[1]);
+            dw_requant2(acc[2], acc[3], mult.z, mult.w, bias.z, bias.w, f, q[2], q[3]);
         } else {
             const uint32_t rv = p.has_res ? __ldg(reinterpret_cast<const uint32_t *>(res + o)) : 0u;
             q[0] = epi_u8(acc[0], mult.x, bias.x, p, (int)(rv & 255u));
@@ -248,14 +258,8 @@ dw3x3_conv_kernel(SimtGeom g, const uint8_t *__restrict__ x, const int16_t *__re
             const size_t o = ((((size_t)b * g.oh + oy) * g.ow) + ox0 + t) * g.c + c0;
             int q[4];
             if (f.on) {
-#pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    const float v = __fadd_rn(__fmul_rn((float)acc[t][e], m4[e]), b4[e]);
-                    float q0 = __fmul_rn(v, f.rso);
-                    q0 = __fmaf_rn(__fmaf_rn(-q0, f.so, v), f.rso, q0);
-                    const float tq = fminf(fmaxf(__fadd_rn(q0, f.zo), f.qlo), f.qhi);
-                    q[e] = (int)rint_sat_u8(tq);
-                }
+                dw_requant2(acc[t][0], acc[t][1], m4[0], m4[1], b4[0], b4[1], f, q[0], q[1]);
+                dw_requant2(acc[t][2], acc[t][3], m4[2], m4[3], b4[2], b4[3], f, q[2], q[3]);
             } else {
                 const uint32_t rv = p.has_res ? __ldg(reinterpret_cast<const uint32_t *>(res + o)) : 0u;
 #pragma unroll

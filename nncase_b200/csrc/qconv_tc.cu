@@ -952,6 +952,10 @@ __device__ __forceinline__ uint32_t lds8(uint32_t addr) {
     asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
     return v;
 }
+// {a, b} and {c, d} of one 16-byte shared-memory word as two register pairs
+__device__ __forceinline__ void lds128_2x64(uint32_t addr, uint64_t &lo, uint64_t &hi) {
+    asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(lo), "=l"(hi) : "r"(addr));
+}
 __device__ __forceinline__ float4 lds128f(uint32_t addr) {
     float4 v;
     asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
@@ -1079,11 +1083,15 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
         if (nt != cur_nt) {
             // (re)load the per-channel constants of this N tile; happens once or twice per CTA
             epi_bar_sync();
+            // two columns share 32 bytes: {mult0, mult1, bias0, bias1} {corr0, corr1, -zw0, -zw1}, so that
+            // the constants of a column pair arrive as register pairs
             for (int c = et; c < g.bn; c += 32 * EPI_WARPS) {
                 const float4 k = f.cst[oc0 + c];
-                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(s_cst + c * 16), "f"(k.x), "f"(k.y),
-                             "f"(k.z), "f"(k.w)
-                             : "memory");
+                const uint32_t dst = s_cst + (uint32_t)(c >> 1) * 32u + (uint32_t)(c & 1) * 4u;
+                asm volatile("st.shared.f32 [%0], %1;" ::"r"(dst), "f"(k.x) : "memory");
+                asm volatile("st.shared.f32 [%0], %1;" ::"r"(dst + 8), "f"(k.y) : "memory");
+                asm volatile("st.shared.f32 [%0], %1;" ::"r"(dst + 16), "f"(k.z) : "memory");
+                asm volatile("st.shared.f32 [%0], %1;" ::"r"(dst + 24), "f"(k.w) : "memory");
             }
             if (multi_cls)
                 for (int i = et; i < f.n_cls * g.bn; i += 32 * EPI_WARPS) {
@@ -1131,6 +1139,7 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
         }
         const uint32_t corr_row = s_corr + (uint32_t)(cls * f.corr_pitch) * 4;
         // eight columns at a time: short live ranges keep the 16 epilogue warps within the register file
+        const uint64_t rso2 = pack2(f.rso, f.rso), nso2 = pack2(-f.so, -f.so), zo2 = pack2(f.zo, f.zo);
         auto chunk = [&](const int (&v)[8], const int cc, auto multi_tag, auto clamp_tag) {
             constexpr bool MULTI = decltype(multi_tag)::value;
             constexpr int CL = decltype(clamp_tag)::value; // 0: no bound inside 0..255, 1: a lower one, 2: both
@@ -1142,32 +1151,49 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
             const uint32_t rwa[2] = {rw.x, rw.y};
             uint32_t bits[8];
 #pragma unroll
-            for (int j = 0; j < 8; j++) {
-                const float4 k = lds128f(s_cst + (c0 + j) * 16); // {mult, bias, corr, -zw}
-                const int corr = MULTI ? (int)lds32(corr_row + (c0 + j) * 4) : __float_as_int(k.z);
-                int acc = v[j] - corr;
-                if (XSUM)
-                    acc += __float_as_int(k.w) * rsum;
-                const float x = __fadd_rn(__fmul_rn((float)acc, k.x), k.y);
-                // x / so, correctly rounded
-                float q0 = __fmul_rn(x, f.rso);
-                q0 = __fmaf_rn(__fmaf_rn(-q0, f.so, x), f.rso, q0);
+            for (int j = 0; j < 8; j += 2) {
+                uint64_t mult2, bias2, ck_lo, ck_hi;
+                lds128_2x64(s_cst + (c0 + j) * 16, mult2, bias2);      // {mult0, mult1} {bias0, bias1}
+                lds128_2x64(s_cst + (c0 + j) * 16 + 16, ck_lo, ck_hi); // {corr0, corr1} {-zw0, -zw1}
+                int corr0 = (int)(uint32_t)ck_lo, corr1 = (int)(uint32_t)(ck_lo >> 32);
+                if (MULTI) {
+                    corr0 = (int)lds32(corr_row + (c0 + j) * 4);
+                    corr1 = (int)lds32(corr_row + (c0 + j) * 4 + 4);
+                }
+                int acc0 = v[j] - corr0, acc1 = v[j + 1] - corr1;
+                if (XSUM) {
+                    acc0 += (int)(uint32_t)ck_hi * rsum;
+                    acc1 += (int)(uint32_t)(ck_hi >> 32) * rsum;
+                }
+                // x = acc * mult + bias, then x / so correctly rounded: q0 = RN(x r), q = RN(q0 + RN(x - q0 so) r)
+                // the product must round before the bias is added: the assembler contracts a packed multiply and a
+                // packed add into one fused operation even when both carry .rn, so the add is two scalar ones
+                float p0, p1, bias0, bias1;
+                unpack2(mul2(pack2((float)acc0, (float)acc1), mult2), p0, p1);
+                unpack2(bias2, bias0, bias1);
+                const uint64_t x2 = pack2(__fadd_rn(p0, bias0), __fadd_rn(p1, bias1));
+                const uint64_t q0 = mul2(x2, rso2);
+                const uint64_t q2 = fma2(fma2(q0, nso2, x2), rso2, q0);
                 // Quantization is monotone, so the fused clamp on the real value is a clamp of the
                 // quantized value to the quantized bounds, and clamping before rounding to an integer is
                 // the same as after. One saturating round-to-nearest-even conversion is rint + clamp to
                 // 0..255; a bound that an activation moved inside that range is applied first.
-                float u = __fadd_rn(q0, f.zo);
+                float u0, u1;
+                unpack2(add2(q2, zo2), u0, u1);
                 if (CL >= 1)
-                    u = fmaxf(u, f.qlo);
+                    u0 = fmaxf(u0, f.qlo), u1 = fmaxf(u1, f.qlo);
                 if (CL == 2)
-                    u = fminf(u, f.qhi);
-                asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(bits[j]) : "f"(u));
+                    u0 = fminf(u0, f.qhi), u1 = fminf(u1, f.qhi);
+                asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(bits[j]) : "f"(u0));
+                asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(bits[j + 1]) : "f"(u1));
                 if (RES) {
                     // dequantize both addends, add, requantise -- as a table of all byte pairs. Rows of 260
                     // bytes: the bank of entry (q, r) is (q + r / 4) mod 32, so the pixels of one channel,
                     // which have similar q and similar r, spread over the banks.
-                    const uint32_t r = __byte_perm(rwa[j >> 2], 0u, 0x4440 | (j & 3));
-                    bits[j] = lds8(s_tab + bits[j] * 260u + r);
+                    const uint32_t r0 = __byte_perm(rwa[j >> 2], 0u, 0x4440 | (j & 3));
+                    const uint32_t r1 = __byte_perm(rwa[j >> 2], 0u, 0x4440 | ((j + 1) & 3));
+                    bits[j] = lds8(s_tab + bits[j] * 260u + r0);
+                    bits[j + 1] = lds8(s_tab + bits[j + 1] * 260u + r1);
                 }
             }
             uint2 o;
