@@ -2,6 +2,7 @@
 // look-up, pooling. All are bandwidth-bound: 128-bit loads and stores, grid sized as a
 // multiple of the SM count with a grid-stride loop.
 #include "internal.cuh"
+#include "qconv.cuh"
 
 namespace nncb {
 
@@ -206,12 +207,28 @@ int quantize_nchw_to_nhwc_u8(nncb_context *ctx, const float *in, uint8_t *out, i
 // out[n][Y][X][(dy*2+dx)*c + ch] = quantize(in[n][ch][2Y+dy][2X+dx]); channels 4c..c_pad-1 hold the
 // zero point. Turns a stride-2 convolution over few channels (an image stem) into a stride-1
 // convolution over c_pad channels that the tensor-core kernel can take. One thread per cell.
-template <int CPAD, bool IN_NHWC>
+// quantize with the division as q0 = RN(x r), q = RN(q0 + RN(x - q0 s) r) (r = RN(1/s), verified on the host: the
+// correctly rounded quotient) and rint + clamp as one saturating conversion; quotients too large for the
+// sequence to be proven (they saturate anyway, but x r may overflow) and NaN take the division.
+__device__ __forceinline__ uint32_t quant_u8_fast(float x, float s, float r, float zp) {
+    const float q0 = __fmul_rn(x, r);
+    if (!(fabsf(q0) < 1e30f))
+        return (uint32_t)quant_dev(x, s, zp, 0, 255);
+    const float q = __fmaf_rn(__fmaf_rn(-q0, s, x), r, q0);
+    uint32_t o;
+    asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(o) : "f"(__fadd_rn(q, zp)));
+    return o;
+}
+
+// CT: the channel count when it is known at compile time (3: images), else 0 and `c` is used. With CT the
+// twelve loads of a cell are independent and every byte lands in a fixed place of the cell's words.
+template <int CPAD, bool IN_NHWC, int CT>
 __global__ void __launch_bounds__(256)
-quantize_nchw_to_s2d_kernel(const float *__restrict__ in, uint8_t *__restrict__ out, int c, int h, int w,
-                            float scale, float zp, int pad_t, int pad_b, int pad_l, int pad_r) {
+quantize_nchw_to_s2d_kernel(const float *__restrict__ in, uint8_t *__restrict__ out, int c_rt, int h, int w,
+                            float scale, float rscale, float zp, int pad_t, int pad_b, int pad_l, int pad_r) {
     // output cells include a border of pad_* cells that hold the zero point in every channel;
     // blockIdx.x = (image, cell row), blockIdx.y * blockDim.x + thread = cell in the row
+    const int c = CT ? CT : c_rt;
     const int hc = h / 2 + pad_t + pad_b, wc = w / 2 + pad_l + pad_r;
     const uint32_t zq = (uint32_t)min(max(__float2int_rn(zp), 0), 255);
     const int xc = (int)(blockIdx.y * blockDim.x + threadIdx.x);
@@ -225,28 +242,44 @@ quantize_nchw_to_s2d_kernel(const float *__restrict__ in, uint8_t *__restrict__ 
         for (int k = 0; k < CPAD / 4; k++)
             words[k] = zq * 0x01010101u;
         const bool inside = X >= 0 && Y >= 0 && X < w / 2 && Y < h / 2;
-        for (int ch = 0; inside && ch < c; ch++)
+        auto one = [&](int ch, int dy) {
+            float2 v;
+            if (IN_NHWC) {
+                const float *px = in + ((n * h + (2 * Y + dy)) * (size_t)w + 2 * X) * c + ch;
+                v = make_float2(__ldcs(px), __ldcs(px + c));
+            } else {
+                v = __ldcs(reinterpret_cast<const float2 *>(in + ((n * c + ch) * h + (2 * Y + dy)) * (size_t)w + 2 * X));
+            }
+            uint32_t q0, q1;
+            if (rscale != 0.f) {
+                q0 = quant_u8_fast(v.x, scale, rscale, zp), q1 = quant_u8_fast(v.y, scale, rscale, zp);
+            } else {
+                q0 = (uint32_t)quant_dev(v.x, scale, zp, 0, 255), q1 = (uint32_t)quant_dev(v.y, scale, zp, 0, 255);
+            }
+            const int i0 = (dy * 2 + 0) * c + ch, i1 = (dy * 2 + 1) * c + ch;
 #pragma unroll
-            for (int dy = 0; dy < 2; dy++) {
-                float2 v;
-                if (IN_NHWC) {
-                    const float *px = in + ((n * h + (2 * Y + dy)) * (size_t)w + 2 * X) * c + ch;
-                    v = make_float2(__ldcs(px), __ldcs(px + c));
-                } else {
-                    v = __ldcs(reinterpret_cast<const float2 *>(in + ((n * c + ch) * h + (2 * Y + dy)) * (size_t)w + 2 * X));
+            for (int k = 0; k < CPAD / 4; k++) {
+                // constant-indexed update keeps `words` in registers
+                if ((i0 >> 2) == k)
+                    words[k] = (words[k] & ~(0xFFu << (8 * (i0 & 3)))) | (q0 << (8 * (i0 & 3)));
+                if ((i1 >> 2) == k)
+                    words[k] = (words[k] & ~(0xFFu << (8 * (i1 & 3)))) | (q1 << (8 * (i1 & 3)));
+            }
+        };
+        if (inside) {
+            if (CT) {
+#pragma unroll
+                for (int ch = 0; ch < (CT ? CT : 1); ch++) {
+                    one(ch, 0);
+                    one(ch, 1);
                 }
-                const uint32_t q0 = (uint32_t)quant_dev(v.x, scale, zp, 0, 255);
-                const uint32_t q1 = (uint32_t)quant_dev(v.y, scale, zp, 0, 255);
-                const int i0 = (dy * 2 + 0) * c + ch, i1 = (dy * 2 + 1) * c + ch;
-#pragma unroll
-                for (int k = 0; k < CPAD / 4; k++) {
-                    // constant-indexed update keeps `words` in registers
-                    if ((i0 >> 2) == k)
-                        words[k] = (words[k] & ~(0xFFu << (8 * (i0 & 3)))) | (q0 << (8 * (i0 & 3)));
-                    if ((i1 >> 2) == k)
-                        words[k] = (words[k] & ~(0xFFu << (8 * (i1 & 3)))) | (q1 << (8 * (i1 & 3)));
+            } else {
+                for (int ch = 0; ch < c; ch++) {
+                    one(ch, 0);
+                    one(ch, 1);
                 }
             }
+        }
         uint4 *o = reinterpret_cast<uint4 *>(out + i * CPAD);
 #pragma unroll
         for (int k = 0; k < CPAD / 16; k++)
@@ -269,18 +302,34 @@ int quantize_nchw_to_s2d_u8(nncb_context *ctx, const float *in, uint8_t *out, in
     const dim3 grid((unsigned)((size_t)n * hc), (unsigned)((wc + bt - 1) / bt));
     if ((size_t)n * hc > 0x7fffffffull)
         return fail(-EINVAL, "quantize_nchw_to_s2d_u8: too many rows");
-    if (c_pad == 32 && in_nhwc)
-        quantize_nchw_to_s2d_kernel<32, true><<<grid, bt, 0, ctx->stream>>>(in, out, c, h, w, scale, (float)zp, pad_t, pad_b, pad_l,
-                                                                             pad_r);
-    else if (c_pad == 32)
-        quantize_nchw_to_s2d_kernel<32, false><<<grid, bt, 0, ctx->stream>>>(in, out, c, h, w, scale, (float)zp, pad_t, pad_b, pad_l,
-                                                                              pad_r);
-    else if (in_nhwc)
-        quantize_nchw_to_s2d_kernel<16, true><<<grid, bt, 0, ctx->stream>>>(in, out, c, h, w, scale, (float)zp, pad_t, pad_b, pad_l,
-                                                                             pad_r);
-    else
-        quantize_nchw_to_s2d_kernel<16, false><<<grid, bt, 0, ctx->stream>>>(in, out, c, h, w, scale, (float)zp, pad_t, pad_b, pad_l,
-                                                                              pad_r);
+    // the reciprocal of the scale, when it is one the division-free sequence is proven for (else 0: divide)
+    bool r_ok = true;
+    float rscale = rn_reciprocal(scale, &r_ok);
+    if (!r_ok)
+        rscale = 0.f;
+#define NNCB_S2D(CP, NH, CT_)                                                                                          \
+    quantize_nchw_to_s2d_kernel<CP, NH, CT_><<<grid, bt, 0, ctx->stream>>>(in, out, c, h, w, scale, rscale, (float)zp, pad_t, \
+                                                                           pad_b, pad_l, pad_r)
+    if (c == 3) {
+        if (c_pad == 32 && in_nhwc)
+            NNCB_S2D(32, true, 3);
+        else if (c_pad == 32)
+            NNCB_S2D(32, false, 3);
+        else if (in_nhwc)
+            NNCB_S2D(16, true, 3);
+        else
+            NNCB_S2D(16, false, 3);
+    } else {
+        if (c_pad == 32 && in_nhwc)
+            NNCB_S2D(32, true, 0);
+        else if (c_pad == 32)
+            NNCB_S2D(32, false, 0);
+        else if (in_nhwc)
+            NNCB_S2D(16, true, 0);
+        else
+            NNCB_S2D(16, false, 0);
+    }
+#undef NNCB_S2D
     return after_launch(ctx, "quantize_nchw_to_s2d");
 }
 
@@ -467,6 +516,42 @@ maxpool_vec_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ y, int n
     }
 }
 
+// The same with the window size known at compile time: the window's loads are independent and all in flight
+// before the first maximum (the general kernel's loops issue one load at a time).
+template <int KH, int KW>
+__global__ void __launch_bounds__(256)
+maxpool_vec_fixed_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ y, int n, int h, int w, int c, int oh, int ow,
+                         int sh, int sw, int pt, int pl, uint32_t zp4) {
+    const uint32_t cg = (uint32_t)c / 16u;
+    const uint32_t j = blockIdx.y * blockDim.x + threadIdx.x;
+    if (j < (uint32_t)ow * cg) {
+        const int g = (int)(j % cg), ox = (int)(j / cg);
+        const int oy = (int)(blockIdx.x % (uint32_t)oh), b = (int)(blockIdx.x / (uint32_t)oh);
+        const size_t p = (size_t)blockIdx.x * ow + ox;
+        uint4 v[KH * KW];
+        bool all = true;
+#pragma unroll
+        for (int ky = 0; ky < KH; ky++)
+#pragma unroll
+            for (int kx = 0; kx < KW; kx++) {
+                const int iy = oy * sh - pt + ky, ix = ox * sw - pl + kx;
+                const bool valid = iy >= 0 && iy < h && ix >= 0 && ix < w;
+                all = all && valid;
+                v[ky * KW + kx] = valid ? __ldg(reinterpret_cast<const uint4 *>(x + (((size_t)b * h + iy) * w + ix) * c) + g)
+                                        : make_uint4(0, 0, 0, 0);
+            }
+        uint4 m = all ? make_uint4(0, 0, 0, 0) : make_uint4(zp4, zp4, zp4, zp4); // a padded tap holds the zero point
+#pragma unroll
+        for (int t = 0; t < KH * KW; t++) {
+            m.x = __vmaxu4(m.x, v[t].x);
+            m.y = __vmaxu4(m.y, v[t].y);
+            m.z = __vmaxu4(m.z, v[t].z);
+            m.w = __vmaxu4(m.w, v[t].w);
+        }
+        reinterpret_cast<uint4 *>(y + p * c)[g] = m;
+    }
+}
+
 __global__ void __launch_bounds__(256)
 maxpool_scalar_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ y, int n, int h, int w, int c,
                       int oh, int ow, int kh, int kw, int sh, int sw, int pt, int pl, int zp) {
@@ -510,7 +595,21 @@ int maxpool_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, int n, int h, in
         const int bt = row_items >= 256 ? 256 : (row_items + 31) / 32 * 32;
         if ((size_t)n * oh > 0x7fffffffull)
             return fail(-EINVAL, "maxpool_u8: too many rows");
-        maxpool_vec_kernel<<<dim3((unsigned)((size_t)n * oh), (unsigned)((row_items + bt - 1) / bt)), bt, 0, ctx->stream>>>(
+        const dim3 grid((unsigned)((size_t)n * oh), (unsigned)((row_items + bt - 1) / bt));
+        const uint32_t z4 = (uint32_t)z * 0x01010101u;
+        if (kh == 3 && kw == 3) {
+            maxpool_vec_fixed_kernel<3, 3><<<grid, bt, 0, ctx->stream>>>(x, y, n, h, w, c, oh, ow, sh, sw, pt, pl, z4);
+            return after_launch(ctx, "maxpool_u8");
+        }
+        if (kh == 2 && kw == 2) {
+            maxpool_vec_fixed_kernel<2, 2><<<grid, bt, 0, ctx->stream>>>(x, y, n, h, w, c, oh, ow, sh, sw, pt, pl, z4);
+            return after_launch(ctx, "maxpool_u8");
+        }
+        if (kh == 5 && kw == 5) {
+            maxpool_vec_fixed_kernel<5, 5><<<grid, bt, 0, ctx->stream>>>(x, y, n, h, w, c, oh, ow, sh, sw, pt, pl, z4);
+            return after_launch(ctx, "maxpool_u8");
+        }
+        maxpool_vec_kernel<<<grid, bt, 0, ctx->stream>>>(
             x, y, n, h, w, c, oh, ow, kh, kw, sh, sw, pt, pl, (uint32_t)z * 0x01010101u);
     } else {
         size_t total = (size_t)n * oh * ow * c;

@@ -125,7 +125,8 @@ def test_requant_relu(ctx, qo):
 @pytest.mark.parametrize("shape,k,s,pad", [((2, 112, 112, 64), (3, 3), (2, 2), (1, 1, 1, 1)),
                                            ((1, 9, 11, 5), (3, 3), (2, 2), (1, 1, 1, 1)),
                                            ((1, 20, 20, 32), (5, 5), (1, 1), (2, 2, 2, 2)),
-                                           ((1, 8, 8, 16), (2, 2), (2, 2), (0, 0, 0, 0))])
+                                           ((1, 8, 8, 16), (2, 2), (2, 2), (0, 0, 0, 0)),
+                                           ((1, 10, 10, 16), (3, 2), (1, 1), (1, 1, 0, 1))])
 def test_maxpool(ctx, qo, shape, k, s, pad):
     q = np.random.default_rng(8).integers(0, 256, shape, dtype=np.uint8)
     q[0, :3, :3] = np.minimum(q[0, :3, :3], 100)  # corner below the zero point: padding must win
