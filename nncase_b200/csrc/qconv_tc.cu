@@ -1378,6 +1378,11 @@ static int pick_bn(int oc, long long K) {
     // in the fewest tiles, 48 a 144-channel one, wide tiles re-read the activations of a deep layer less often.
     if (oc % 16 != 0)
         return oc >= 128 ? 128 : ((oc + 15) / 16) * 16;
+    if (const char *e = getenv("NNCB_CONV_BN")) { // tuning aid: force the N tile width (128, 96, 64, 48 or 32)
+        const int v = atoi(e);
+        if (v == 128 || v == 96 || v == 64 || v == 48 || v == 32)
+            return v;
+    }
     static const int widths[5] = {128, 96, 64, 48, 32};
     int best = 128;
     long long best_cost = -1;
