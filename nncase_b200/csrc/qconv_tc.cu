@@ -432,6 +432,7 @@ struct FastEpi {
     int out_sw;         // swizzle span of the staging sub-tiles: 32 or 0
     int ncg, wcols;     // column groups per tile (2 to 4) and columns per epilogue warp (32 or 16)
     int halves;         // 2: tiles of 8 epilogue warps, the two halves of the warps take alternate tiles; else 1
+    int fcorr;          // the integer corrections run in float (every intermediate is an integer below 2^24)
     float so, rso, zo;  // output scale, its correctly rounded reciprocal, zero point
     float qlo, qhi;     // the fused clamp's bounds after quantization, within [0, 255]
     const float4 *cst;  // [oc_pad] {mult, bias, bits(corr of class 0), bits(-zw)}
@@ -1090,8 +1091,11 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
                 const uint32_t dst = s_cst + (uint32_t)(c >> 1) * 32u + (uint32_t)(c & 1) * 4u;
                 asm volatile("st.shared.f32 [%0], %1;" ::"r"(dst), "f"(k.x) : "memory");
                 asm volatile("st.shared.f32 [%0], %1;" ::"r"(dst + 8), "f"(k.y) : "memory");
-                asm volatile("st.shared.f32 [%0], %1;" ::"r"(dst + 16), "f"(k.z) : "memory");
-                asm volatile("st.shared.f32 [%0], %1;" ::"r"(dst + 24), "f"(k.w) : "memory");
+                // (float corrections: -corr and -zw as floats instead of integer bits)
+                const float kz = f.fcorr ? -(float)__float_as_int(k.z) : k.z;
+                const float kw_ = f.fcorr ? (float)__float_as_int(k.w) : k.w;
+                asm volatile("st.shared.f32 [%0], %1;" ::"r"(dst + 16), "f"(kz) : "memory");
+                asm volatile("st.shared.f32 [%0], %1;" ::"r"(dst + 24), "f"(kw_) : "memory");
             }
             if (multi_cls)
                 for (int i = et; i < f.n_cls * g.bn; i += 32 * EPI_WARPS) {
@@ -1140,8 +1144,10 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
         const uint32_t corr_row = s_corr + (uint32_t)(cls * f.corr_pitch) * 4;
         // eight columns at a time: short live ranges keep the 16 epilogue warps within the register file
         const uint64_t rso2 = pack2(f.rso, f.rso), nso2 = pack2(-f.so, -f.so), zo2 = pack2(f.zo, f.zo);
-        auto chunk = [&](const int (&v)[8], const int cc, auto multi_tag, auto clamp_tag) {
+        const uint64_t rsumf2 = pack2((float)rsum, (float)rsum);
+        auto chunk = [&](const int (&v)[8], const int cc, auto multi_tag, auto clamp_tag, auto fc_tag) {
             constexpr bool MULTI = decltype(multi_tag)::value;
+            constexpr bool FC = decltype(fc_tag)::value; // corrections in float (never with MULTI)
             constexpr int CL = decltype(clamp_tag)::value; // 0: no bound inside 0..255, 1: a lower one, 2: both
             const int c0 = col_off + cc; // column within the tile
             const uint32_t half16 = stage_addr(0, lane, cc >> 4, hw, f.out_sw) + (cc & 8); // offset in a sub-tile
@@ -1155,21 +1161,31 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
                 uint64_t mult2, bias2, ck_lo, ck_hi;
                 lds128_2x64(s_cst + (c0 + j) * 16, mult2, bias2);      // {mult0, mult1} {bias0, bias1}
                 lds128_2x64(s_cst + (c0 + j) * 16 + 16, ck_lo, ck_hi); // {corr0, corr1} {-zw0, -zw1}
-                int corr0 = (int)(uint32_t)ck_lo, corr1 = (int)(uint32_t)(ck_lo >> 32);
-                if (MULTI) {
-                    corr0 = (int)lds32(corr_row + (c0 + j) * 4);
-                    corr1 = (int)lds32(corr_row + (c0 + j) * 4 + 4);
-                }
-                int acc0 = v[j] - corr0, acc1 = v[j + 1] - corr1;
-                if (XSUM) {
-                    acc0 += (int)(uint32_t)ck_hi * rsum;
-                    acc1 += (int)(uint32_t)(ck_hi >> 32) * rsum;
+                uint64_t accf2;
+                if (FC) {
+                    // acc - corr - zw * rowsum on integers below 2^24 held in floats: exact, and packed
+                    accf2 = pack2((float)v[j], (float)v[j + 1]);
+                    if (XSUM)
+                        accf2 = fma2(ck_hi, rsumf2, accf2);
+                    accf2 = add2(accf2, ck_lo);
+                } else {
+                    int corr0 = (int)(uint32_t)ck_lo, corr1 = (int)(uint32_t)(ck_lo >> 32);
+                    if (MULTI) {
+                        corr0 = (int)lds32(corr_row + (c0 + j) * 4);
+                        corr1 = (int)lds32(corr_row + (c0 + j) * 4 + 4);
+                    }
+                    int acc0 = v[j] - corr0, acc1 = v[j + 1] - corr1;
+                    if (XSUM) {
+                        acc0 += (int)(uint32_t)ck_hi * rsum;
+                        acc1 += (int)(uint32_t)(ck_hi >> 32) * rsum;
+                    }
+                    accf2 = pack2((float)acc0, (float)acc1);
                 }
                 // x = acc * mult + bias, then x / so correctly rounded: q0 = RN(x r), q = RN(q0 + RN(x - q0 so) r)
                 // the product must round before the bias is added: the assembler contracts a packed multiply and a
                 // packed add into one fused operation even when both carry .rn, so the add is two scalar ones
                 float p0, p1, bias0, bias1;
-                unpack2(mul2(pack2((float)acc0, (float)acc1), mult2), p0, p1);
+                unpack2(mul2(accf2, mult2), p0, p1);
                 unpack2(bias2, bias0, bias1);
                 const uint64_t x2 = pack2(__fadd_rn(p0, bias0), __fadd_rn(p1, bias1));
                 const uint64_t q0 = mul2(x2, rso2);
@@ -1210,18 +1226,18 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
             }
         };
         // the TMEM load of the next eight columns is in flight while the current ones are requantised
-        auto columns = [&](auto multi_tag, auto clamp_tag) {
+        auto columns = [&](auto multi_tag, auto clamp_tag, auto fc_tag) {
             int va[8], vb[8];
             __syncwarp();
             tmem_ld8_issue(tbase + col_off, va);
             for (int cc = 0; cc < hw; cc += 16) { // hw is 16 or 32
                 tmem_ld_wait();
                 tmem_ld8_issue(tbase + col_off + cc + 8, vb);
-                chunk(va, cc, multi_tag, clamp_tag);
+                chunk(va, cc, multi_tag, clamp_tag, fc_tag);
                 tmem_ld_wait();
                 if (cc + 16 < hw)
                     tmem_ld8_issue(tbase + col_off + cc + 16, va);
-                chunk(vb, cc + 8, multi_tag, clamp_tag);
+                chunk(vb, cc + 8, multi_tag, clamp_tag, fc_tag);
             }
         };
         using cl0 = std::integral_constant<int, 0>;
@@ -1229,18 +1245,25 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
         using cl2 = std::integral_constant<int, 2>;
         if (multi_cls) {
             if (clamp_level == 0)
-                columns(std::true_type{}, cl0{});
+                columns(std::true_type{}, cl0{}, std::false_type{});
             else if (clamp_level == 1)
-                columns(std::true_type{}, cl1{});
+                columns(std::true_type{}, cl1{}, std::false_type{});
             else
-                columns(std::true_type{}, cl2{});
+                columns(std::true_type{}, cl2{}, std::false_type{});
+        } else if (f.fcorr) {
+            if (clamp_level == 0)
+                columns(std::false_type{}, cl0{}, std::true_type{});
+            else if (clamp_level == 1)
+                columns(std::false_type{}, cl1{}, std::true_type{});
+            else
+                columns(std::false_type{}, cl2{}, std::true_type{});
         } else {
             if (clamp_level == 0)
-                columns(std::false_type{}, cl0{});
+                columns(std::false_type{}, cl0{}, std::false_type{});
             else if (clamp_level == 1)
-                columns(std::false_type{}, cl1{});
+                columns(std::false_type{}, cl1{}, std::false_type{});
             else
-                columns(std::false_type{}, cl2{});
+                columns(std::false_type{}, cl2{}, std::false_type{});
         }
         // accumulator and residual sub-tile are consumed; staging sub-tiles are written
         fence_before_sync();
@@ -1594,6 +1617,9 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
 
     if (tp->fast) {
         fe.n_cls = n_cls;
+        // |sum x w|, |zw rowsum| and |corr| are each at most 255 * 255 * K: with K <= 128 every intermediate of
+        // acc - corr - zw * rowsum stays below 2^24 and float arithmetic on these integers is exact
+        fe.fcorr = (n_cls == 1 && (long long)d.kh * d.kw * d.c <= 128) ? 1 : 0;
         fe.corr_pitch = g.bn + 1;
         if (n_cls > 1)
             extras += (uint32_t)n_cls * fe.corr_pitch * 4;
