@@ -45,6 +45,12 @@ namespace nncb {
 // consecutive cells of a patch row, the next core matrix along K is the same row one cell further (leading
 // offset 16 bytes, they overlap), the next 8 rows are the next patch row (stride offset = its pitch). MODE_ROWS
 // moves kh x 128 short rows per tile for the same data and is bound by rows per clock.
+// The same tile shape serves padded 3 x 3-like stride-1 convolutions over 64 or 128 channels with resident weights
+// (cell = one pixel = one 64- or 128-byte swizzle row): the patch is loaded once per tile with the tensor map's
+// swizzle, out-of-image cells zero-filled, and every tap addresses it through a swizzled descriptor whose start
+// is moved by whole pixels -- the swizzle is a function of the shared-memory address, so a start inside the
+// 8-row pattern and a stride offset that is not a multiple of it read what the load wrote. One ninth of the
+// activation rows of the im2col form, which is bound by rows per clock at these channel counts.
 enum { MODE_GEMM = 0, MODE_IM2COL = 1, MODE_ROWS = 2, MODE_PATCH = 3 };
 
 // Division by a number fixed at plan creation (Granlund and Montgomery's multiply-and-shift): for n < 2^31,
@@ -99,6 +105,7 @@ struct TcGeom {
     int bx_log2, tiles_x, tiles_y; // MODE_ROWS: patch width 2^bx_log2 (height 128 >> bx_log2), patches per image
     int patch_w, patch_h;          // MODE_PATCH: input cells per patch row, patch rows
     int kh, kw_cells;              // MODE_PATCH: kernel rows, cells per kernel row
+    int cell;                      // MODE_PATCH: bytes per cell (16: unswizzled; 64 / 128: one swizzle row per pixel)
     FastDiv fd_m_tiles, fd_ow, fd_oh, fd_tiles_x, fd_tiles_y;
 };
 
@@ -176,6 +183,19 @@ static bool patch_mode_applies(const nncb_conv2d_desc &d) {
     return b_all <= 48u * 1024u;
 }
 
+// the wide-cell form: padded or not, stride 1, dilation 1, c = 64 or 128, one N tile with resident weights
+static bool patch_wide_applies(const nncb_conv2d_desc &d) {
+    if (getenv("NNCB_NO_WIDE_PATCH")) // tuning aid: keep these layers on the im2col form
+        return false;
+    if (d.groups != 1 || d.stride_h != 1 || d.stride_w != 1 || d.dil_h != 1 || d.dil_w != 1 || (d.c != 64 && d.c != 128) ||
+        d.kh < 2 || d.kw < 2 || d.kh > 4 || d.kw > 4 || d.oc > 128 || d.oc % 16 != 0 || d.has_residual || d.f32_out)
+        return false;
+    if (d.pad_t >= d.kh || d.pad_b >= d.kh || d.pad_l >= d.kw || d.pad_r >= d.kw)
+        return false;
+    const size_t b_all = (size_t)d.kh * d.kw * (((size_t)(d.oc + 31) * d.c + 1023) & ~(size_t)1023);
+    return b_all <= 64u * 1024u;
+}
+
 bool tc_conv_supported(const nncb_conv2d_desc &d, std::string *why) {
     auto no = [&](const char *m) {
         if (why)
@@ -215,7 +235,16 @@ bool tc_conv_supported(const nncb_conv2d_desc &d, std::string *why) {
 static int make_tmap_a(TcPlan *tp, const nncb_conv2d_desc &d, const void *x) {
     const TcGeom &g = tp->g;
     CUresult r;
-    if (g.mode == MODE_PATCH) {
+    if (g.mode == MODE_PATCH && g.cell != 16) {
+        // one swizzle row per pixel; the box is the patch of pixels under an 8 x 16 output patch
+        cuuint64_t dims[4] = {(cuuint64_t)d.c, (cuuint64_t)d.w, (cuuint64_t)d.h, (cuuint64_t)d.n};
+        cuuint64_t strides[3] = {(cuuint64_t)d.c, (cuuint64_t)d.c * d.w, (cuuint64_t)d.c * d.w * d.h};
+        cuuint32_t box[4] = {(cuuint32_t)g.cell, (cuuint32_t)g.patch_w, (cuuint32_t)g.patch_h, 1};
+        cuuint32_t estr[4] = {1, 1, 1, 1};
+        r = g_encode_tiled(&tp->tmap_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void *>(x), dims, strides, box,
+                           estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(g.cell), CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else if (g.mode == MODE_PATCH) {
         // rows of the image as bytes; the box is the patch of input cells under an 8 x 16 output patch
         cuuint64_t dims[3] = {(cuuint64_t)d.w * 16, (cuuint64_t)d.h, (cuuint64_t)d.n};
         cuuint64_t strides[2] = {(cuuint64_t)d.w * 16, (cuuint64_t)d.w * 16 * d.h};
@@ -349,6 +378,18 @@ __device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const CUtensorM
                  : "memory");
 }
 
+// Swizzled K-major descriptor with an explicit stride offset (bytes from one 8-row group to the next)
+__device__ __forceinline__ uint64_t smem_desc_sbo(uint32_t addr, int kb, uint32_t sbo) {
+    const uint64_t layout = kb == 128 ? 2 : (kb == 64 ? 4 : 6);
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(sbo >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= layout << 61;
+    return d;
+}
+
 // Unswizzled K-major operand descriptor: core matrices of 8 rows x 16 bytes (128 contiguous bytes), `lbo`
 // bytes from one to the next along K, `sbo` bytes to the next 8 rows.
 __device__ __forceinline__ uint64_t smem_desc_plain(uint32_t addr, uint32_t lbo, uint32_t sbo) {
@@ -479,7 +520,7 @@ __device__ __forceinline__ StageGeom stage_geom(const TcGeom &g, const uint8_t *
     StageGeom sg;
     // stage ring, 1024-byte aligned (required by the 128-byte swizzle)
     sg.smem_base = (dev::smem_u32(smem_raw) + 1023u) & ~1023u;
-    sg.a_stage_bytes = g.mode == MODE_PATCH ? (((uint32_t)g.patch_w * 16u * g.patch_h + 1023u) & ~1023u) : 128u * g.kb;
+    sg.a_stage_bytes = g.mode == MODE_PATCH ? (((uint32_t)g.patch_w * g.cell * g.patch_h + 1023u) & ~1023u) : 128u * g.kb;
     sg.b_stage_bytes = (uint32_t)g.bn_mma * g.kb;
     // keep every stage's A and B tile 1024-byte aligned (a_stage_bytes is a multiple of 1024)
     sg.b_pitch = (sg.b_stage_bytes + 1023u) & ~1023u;
@@ -558,7 +599,8 @@ __device__ __forceinline__ void producer_loop(const TcGeom &g, const StageGeom &
     }
     if (g.mode == MODE_PATCH) {
         // one load per tile: the input cells under the output patch (weights are resident, one N tile)
-        const uint32_t patch_bytes = (uint32_t)g.patch_w * 16u * g.patch_h;
+        const uint32_t patch_bytes = (uint32_t)g.patch_w * g.cell * g.patch_h;
+        const bool wide = g.cell != 16;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             int txi, tyi;
             const int r = fdivmod(tile, g.fd_tiles_x, txi);
@@ -567,7 +609,10 @@ __device__ __forceinline__ void producer_loop(const TcGeom &g, const StageGeom &
                 return;
             const uint32_t full = bar_full0 + stage * 8;
             mbar_expect_tx(full, patch_bytes);
-            tma_load_3d(sg.smem_base + stage * sg.stage_pitch, tmap_a, full, (txi * 8) * 16, tyi * 16, img);
+            if (wide) // pixels as rows; the patch starts pad cells outside the output patch (zero fill outside the image)
+                tma_load_4d(sg.smem_base + stage * sg.stage_pitch, tmap_a, full, 0, txi * 8 - g.pad_l, tyi * 16 - g.pad_t, img);
+            else
+                tma_load_3d(sg.smem_base + stage * sg.stage_pitch, tmap_a, full, (txi * 8) * 16, tyi * 16, img);
             if (++stage == stages) {
                 stage = 0;
                 phase ^= 1;
@@ -702,12 +747,26 @@ __device__ __forceinline__ void mma_loop(const TcGeom &g, const StageGeom &sg, T
                 return;
             fence_after_sync();
             // rows of the tile = (patch row y, x) with x fastest: 8-row groups step one patch row
-            const uint32_t row16 = (uint32_t)g.patch_w; // patch row pitch in 16-byte units
-            uint64_t da = smem_desc_plain(sg.smem_base, 16u, row16 * 16u) + (uint64_t)(stage * pitch16);
-            uint64_t db = desc_bres;
-            for (int ky = 0; ky < g.kh; ky++, da += row16, db += bres_pitch16)
-                for (int j = 0; j < g.kw_cells; j += 2) // one MMA: cells j, j + 1 of the kernel row (K = 32 bytes)
-                    mma_i8(tmem_d, da + (uint64_t)j, db + (uint64_t)j, idesc, (ky | j) != 0);
+            if (g.cell == 16) {
+                const uint32_t row16 = (uint32_t)g.patch_w; // patch row pitch in 16-byte units
+                uint64_t da = smem_desc_plain(sg.smem_base, 16u, row16 * 16u) + (uint64_t)(stage * pitch16);
+                uint64_t db = desc_bres;
+                for (int ky = 0; ky < g.kh; ky++, da += row16, db += bres_pitch16)
+                    for (int j = 0; j < g.kw_cells; j += 2) // one MMA: cells j, j + 1 of the kernel row (K = 32 bytes)
+                        mma_i8(tmem_d, da + (uint64_t)j, db + (uint64_t)j, idesc, (ky | j) != 0);
+            } else {
+                // one pixel = one swizzle row: 8 consecutive pixels of a patch row are an 8-row group, the next
+                // group is the next patch row; a tap moves the start by whole pixels
+                const uint32_t cell16 = (uint32_t)g.cell >> 4, row16 = (uint32_t)g.patch_w * cell16;
+                const uint64_t da0 = smem_desc_sbo(sg.smem_base, g.cell, row16 * 16u) + (uint64_t)(stage * pitch16);
+                uint64_t db = desc_bres;
+                for (int ky = 0; ky < g.kh; ky++)
+                    for (int kx = 0; kx < g.kw_cells; kx++, db += bres_pitch16) {
+                        const uint64_t da = da0 + (uint64_t)((uint32_t)ky * row16 + (uint32_t)kx * cell16);
+                        for (uint32_t i = 0; i < cell16; i += 2) // K = 32 bytes per MMA
+                            mma_i8(tmem_d, da + i, db + i, idesc, (ky | kx | (int)i) != 0);
+                    }
+            }
             mma_commit(bar_empty0 + stage * 8);
             if (++stage == stages) {
                 stage = 0;
@@ -785,6 +844,7 @@ __device__ __forceinline__ void epilogue_generic(const TcArgs &a, TcShared &sh, 
         const int nt = fdivmod(tile, g.fd_m_tiles, mt);
         int m = mt * 128 + row;
         bool row_ok = m < g.m_total;
+        int patch_cls = 0;
         if (g.mode == MODE_ROWS || g.mode == MODE_PATCH) {
             // the tile is a patch of output pixels: row -> (patch row, patch column)
             int txi, tyi;
@@ -794,8 +854,9 @@ __device__ __forceinline__ void epilogue_generic(const TcArgs &a, TcShared &sh, 
             const int oy = tyi * (128 >> g.bx_log2) + (row >> g.bx_log2);
             row_ok = ox < g.ow && oy < g.oh;
             m = (img * g.oh + oy) * g.ow + ox;
+            patch_cls = row_ok ? (int)a.ycls[oy] * g.n_cls_x + (int)a.xcls[ox] : 0; // one class when unpadded
         }
-        int cls = 0; // border class of this output pixel
+        int cls = patch_cls; // border class of this output pixel
         if (g.mode == MODE_IM2COL && row_ok) {
             int ox, oy;
             fdivmod(fdivmod(m, g.fd_ow, ox), g.fd_oh, oy);
@@ -1115,6 +1176,15 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
             fdivmod(fdivmod(m, g.fd_ow, ox), g.fd_oh, oy);
             cls = (int)a.ycls[oy] * g.n_cls_x + (int)a.xcls[ox];
         }
+        if (rows && multi_cls) {
+            // a padded patch-mode layer: the class of this lane's pixel of the patch
+            int txi, tyi;
+            fdivmod(fdivmod(mt, g.fd_tiles_x, txi), g.fd_tiles_y, tyi);
+            const int ox = (txi << g.bx_log2) + (row & ((1 << g.bx_log2) - 1));
+            const int oy = tyi * (128 >> g.bx_log2) + (row >> g.bx_log2);
+            if (ox < g.ow && oy < g.oh)
+                cls = (int)a.ycls[oy] * g.n_cls_x + (int)a.xcls[ox];
+        }
         const uint32_t ph = buf ? acc_phase1 : acc_phase0;
         bool ok = mbar_wait(smem_u32(&sh.bar_acc_full[buf]), ph, &sh.abort_flag, a.status, ERR_EPILOGUE);
         if (RES && ok)
@@ -1427,7 +1497,9 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
     TcGeom &g = tp->g;
     const bool gemm = d.kh == 1 && d.kw == 1 && d.stride_h == 1 && d.stride_w == 1 && d.pad_t == 0 && d.pad_b == 0 &&
                       d.pad_l == 0 && d.pad_r == 0;
-    g.mode = gemm ? MODE_GEMM : (patch_mode_applies(d) ? MODE_PATCH : (rows_mode_applies(d) ? MODE_ROWS : MODE_IM2COL));
+    const bool wide_patch = !gemm && patch_wide_applies(d);
+    g.mode = gemm ? MODE_GEMM
+                  : ((wide_patch || patch_mode_applies(d)) ? MODE_PATCH : (rows_mode_applies(d) ? MODE_ROWS : MODE_IM2COL));
     g.oh = cv->oh, g.ow = cv->ow;
     g.m_total = d.n * cv->oh * cv->ow;
     g.oc = d.oc;
@@ -1464,12 +1536,17 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
         g.bx_log2 = 3; // 8 x 16 output pixels
         g.tiles_x = (g.ow + 7) / 8, g.tiles_y = (g.oh + 15) / 16;
         g.m_tiles = d.n * g.tiles_x * g.tiles_y;
-        g.kb = d.kw * d.c; // the weights keep the layout of MODE_ROWS: one K block per kernel row
-        g.c_blocks = 1;
-        g.taps = d.kh;
-        g.kw = 1;
         g.kh = d.kh, g.kw_cells = d.kw;
         g.patch_w = 8 + d.kw - 1, g.patch_h = 16 + d.kh - 1;
+        if (wide_patch) {
+            g.cell = d.c; // the weights keep the layout of MODE_IM2COL: one K block of c bytes per tap
+        } else {
+            g.cell = 16;
+            g.kb = d.kw * d.c; // the weights keep the layout of MODE_ROWS: one K block per kernel row
+            g.c_blocks = 1;
+            g.taps = d.kh;
+            g.kw = 1;
+        }
     }
     g.fd_m_tiles = make_fastdiv(g.m_tiles), g.fd_ow = make_fastdiv(g.ow), g.fd_oh = make_fastdiv(g.oh);
     g.fd_tiles_x = make_fastdiv(g.tiles_x), g.fd_tiles_y = make_fastdiv(g.tiles_y);
@@ -1494,7 +1571,7 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
     tp->f = new FastEpi();
     FastEpi &fe = *tp->f;
     memset(&fe, 0, sizeof(fe));
-    const uint32_t a_stage = g.mode == MODE_PATCH ? (((uint32_t)g.patch_w * 16u * g.patch_h + 1023u) & ~1023u) : 128u * g.kb;
+    const uint32_t a_stage = g.mode == MODE_PATCH ? (((uint32_t)g.patch_w * g.cell * g.patch_h + 1023u) & ~1023u) : 128u * g.kb;
     const uint32_t b_pitch = ((uint32_t)g.bn_mma * g.kb + 1023u) & ~1023u;
     const uint32_t budget = 224u * 1024u - 1024u; // dynamic shared memory we may use, minus alignment slack
     uint32_t extras = 0;

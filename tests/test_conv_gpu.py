@@ -70,6 +70,10 @@ TC_CASES = [
     (1, 56, 56, 64, 64, 3, 3, 1, 1, 1), (2, 14, 14, 128, 256, 3, 3, 1, 1, 1), (1, 28, 28, 64, 128, 3, 3, 2, 1, 1),
     (3, 7, 7, 256, 64, 3, 3, 1, 1, 1), (1, 16, 16, 32, 32, 3, 3, 1, 2, 2), (2, 28, 28, 128, 64, 1, 1, 2, 0, 1),
     (1, 1, 37, 64, 32, 1, 3, 1, 1, 1), (1, 20, 20, 32, 16, 5, 5, 1, 2, 1),
+    # pixel-patch tiles with one swizzle row per pixel (stride 1, c = 64 or 128, resident weights): padded and
+    # not, patches that overhang the image, 64- and 128-byte rows
+    (2, 20, 23, 64, 32, 3, 3, 1, 1, 1), (1, 9, 9, 64, 48, 2, 2, 1, 0, 1), (1, 12, 10, 128, 32, 2, 2, 1, 1, 1),
+    (1, 30, 17, 64, 64, 3, 3, 1, 1, 1), (3, 8, 16, 64, 96, 3, 3, 1, 1, 1), (1, 33, 9, 64, 16, 4, 4, 1, 2, 1),
 ]
 
 
