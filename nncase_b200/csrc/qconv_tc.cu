@@ -414,10 +414,25 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, int kb) {
     return d;
 }
 
-__device__ __forceinline__ void mma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n}"
-                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum)
+// An operand descriptor as two words: only the low one (start address >> 4 in its low 14 bits) changes from MMA to
+// MMA, and the sums never carry out of that field (the stage ring stays below the field's 256 KB range), so
+// advancing a descriptor is one 32-bit add and the high word is loop-invariant. The MMA loop is one thread's
+// dependent instruction stream and paces the tensor pipe: with 64-bit descriptor arithmetic a K = 32 MMA took
+// about 250 cycles.
+struct Desc {
+    uint32_t lo, hi;
+    __device__ __forceinline__ Desc operator+(uint32_t o) const { return Desc{lo + o, hi}; }
+    __device__ __forceinline__ Desc &operator+=(uint32_t o) {
+        lo += o;
+        return *this;
+    }
+};
+__device__ __forceinline__ Desc make_desc(uint64_t d) { return Desc{(uint32_t)d, (uint32_t)(d >> 32)}; }
+__device__ __forceinline__ void mma_i8(uint32_t tmem_d, Desc a, Desc b, uint32_t idesc, uint32_t accum) {
+    asm volatile("{\n.reg .pred p;\n.reg .b64 da, db;\nsetp.ne.b32 p, %6, 0;\n"
+                 "mov.b64 da, {%1, %2};\nmov.b64 db, {%3, %4};\n"
+                 "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %5, p;\n}"
+                 ::"r"(tmem_d), "r"(a.lo), "r"(a.hi), "r"(b.lo), "r"(b.hi), "r"(idesc), "r"(accum)
                  : "memory");
 }
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
@@ -718,12 +733,12 @@ __device__ __forceinline__ void mma_loop(const TcGeom &g, const StageGeom &sg, T
     int it = 0;
     // descriptors of stage 0; a stage further on adds its byte offset >> 4 to the address field
     // (the ring stays below the field's 256 KB range, so the sum never carries out of it)
-    const uint64_t desc_a0 = smem_desc(sg.smem_base, g.kb), desc_b0 = smem_desc(sg.smem_base + sg.a_stage_bytes, g.kb);
+    const Desc desc_a0 = make_desc(smem_desc(sg.smem_base, g.kb)), desc_b0 = make_desc(smem_desc(sg.smem_base + sg.a_stage_bytes, g.kb));
     const uint32_t pitch16 = sg.stage_pitch >> 4, stages = g.stages, idesc = g.idesc;
     const int kk = g.kb / 32; // 1, 2 or 4 MMAs of K = 32 per K block
     const uint32_t bar_full0 = smem_u32(&sh.bar_full[0]), bar_empty0 = smem_u32(&sh.bar_empty[0]);
     const bool b_res = sg.b_resident != 0;
-    const uint64_t desc_bres = smem_desc(sg.b_resident, g.kb);
+    const Desc desc_bres = make_desc(smem_desc(sg.b_resident, g.kb));
     const uint32_t bres_pitch16 = sg.b_pitch >> 4, kblock_pitch16 = sg.kblock_pitch >> 4;
     const uint32_t b_step16 = b_res ? bres_pitch16 : kblock_pitch16; // from one K block's weights to the next
     const int kgroup = g.kgroup;
@@ -749,23 +764,31 @@ __device__ __forceinline__ void mma_loop(const TcGeom &g, const StageGeom &sg, T
             // rows of the tile = (patch row y, x) with x fastest: 8-row groups step one patch row
             if (g.cell == 16) {
                 const uint32_t row16 = (uint32_t)g.patch_w; // patch row pitch in 16-byte units
-                uint64_t da = smem_desc_plain(sg.smem_base, 16u, row16 * 16u) + (uint64_t)(stage * pitch16);
-                uint64_t db = desc_bres;
+                Desc da = make_desc(smem_desc_plain(sg.smem_base, 16u, row16 * 16u)) + stage * pitch16;
+                Desc db = desc_bres;
                 for (int ky = 0; ky < g.kh; ky++, da += row16, db += bres_pitch16)
                     for (int j = 0; j < g.kw_cells; j += 2) // one MMA: cells j, j + 1 of the kernel row (K = 32 bytes)
-                        mma_i8(tmem_d, da + (uint64_t)j, db + (uint64_t)j, idesc, (ky | j) != 0);
+                        mma_i8(tmem_d, da + (uint32_t)j, db + (uint32_t)j, idesc, (ky | j) != 0);
             } else {
                 // one pixel = one swizzle row: 8 consecutive pixels of a patch row are an 8-row group, the next
                 // group is the next patch row; a tap moves the start by whole pixels
                 const uint32_t cell16 = (uint32_t)g.cell >> 4, row16 = (uint32_t)g.patch_w * cell16;
-                const uint64_t da0 = smem_desc_sbo(sg.smem_base, g.cell, row16 * 16u) + (uint64_t)(stage * pitch16);
-                uint64_t db = desc_bres;
-                for (int ky = 0; ky < g.kh; ky++)
-                    for (int kx = 0; kx < g.kw_cells; kx++, db += bres_pitch16) {
-                        const uint64_t da = da0 + (uint64_t)((uint32_t)ky * row16 + (uint32_t)kx * cell16);
-                        for (uint32_t i = 0; i < cell16; i += 2) // K = 32 bytes per MMA
-                            mma_i8(tmem_d, da + i, db + i, idesc, (ky | kx | (int)i) != 0);
+                const Desc da0 = make_desc(smem_desc_sbo(sg.smem_base, g.cell, row16 * 16u)) + stage * pitch16;
+                // (the shortest instruction stream per MMA: descriptors advance by increments)
+                Desc db = desc_bres, da_row = da0;
+                uint32_t accum = 0;
+                for (int ky = 0; ky < g.kh; ky++, da_row += row16) {
+                    Desc da = da_row;
+                    for (int kx = 0; kx < g.kw_cells; kx++, da += cell16, db += bres_pitch16) {
+                        mma_i8(tmem_d, da, db, idesc, accum); // K = 32 bytes per MMA
+                        mma_i8(tmem_d, da + 2, db + 2, idesc, 1);
+                        if (cell16 > 4) {
+                            mma_i8(tmem_d, da + 4, db + 4, idesc, 1);
+                            mma_i8(tmem_d, da + 6, db + 6, idesc, 1);
+                        }
+                        accum = 1;
                     }
+                }
             }
             mma_commit(bar_empty0 + stage * 8);
             if (++stage == stages) {
@@ -780,8 +803,8 @@ __device__ __forceinline__ void mma_loop(const TcGeom &g, const StageGeom &sg, T
                 if (!mbar_wait(bar_full0 + stage * 8, phase, &sh.abort_flag, status, ERR_MMA_FULL))
                     return;
                 fence_after_sync();
-                const uint64_t da = desc_a0 + (uint64_t)(stage * pitch16);
-                const uint64_t db = b_res ? desc_bres + (uint64_t)(kbi * bres_pitch16) : desc_b0 + (uint64_t)(stage * pitch16);
+                const Desc da = desc_a0 + stage * pitch16;
+                const Desc db = b_res ? desc_bres + (uint32_t)kbi * bres_pitch16 : desc_b0 + stage * pitch16;
                 mma_i8(tmem_d, da, db, idesc, kbi != 0);
                 if (kk > 1)
                     mma_i8(tmem_d, da + 2, db + 2, idesc, 1);
@@ -803,8 +826,8 @@ __device__ __forceinline__ void mma_loop(const TcGeom &g, const StageGeom &sg, T
                 return;
             fence_after_sync();
             const int cnt = min(kgroup, k_blocks - kb0);
-            uint64_t da = desc_a0 + (uint64_t)(stage * pitch16);
-            uint64_t db = b_res ? desc_bres + (uint64_t)(kb0 * bres_pitch16) : desc_b0 + (uint64_t)(stage * pitch16);
+            Desc da = desc_a0 + stage * pitch16;
+            Desc db = b_res ? desc_bres + (uint32_t)kb0 * bres_pitch16 : desc_b0 + stage * pitch16;
             for (int i = 0; i < cnt; i++, da += kblock_pitch16, db += b_step16) {
                 mma_i8(tmem_d, da, db, idesc, (kb0 | i) != 0);
                 if (kk > 1)
