@@ -45,7 +45,7 @@ def peaks():
 # DRAM bytes (read + write) of all convolution launches of one step, from one ncu capture of this
 # workload (dram__bytes_read.sum + dram__bytes_write.sum, summed over the tcgen05 convolution
 # kernels of a step); None until a capture at that size exists. Keyed by (images per GPU, weights).
-MEASURED_DRAM_BYTES_PER_STEP = {(512, "uint8"): 17.158e9}
+MEASURED_DRAM_BYTES_PER_STEP = {(512, "uint8"): 17.181e9}
 
 
 def measured_traffic(batch, w_quant):
