@@ -555,6 +555,8 @@ int nncb_qconv2d_destroy(nncb_qconv2d *cv) {
     tc_conv_destroy(cv);
     cudaFree(cv->d_w);
     cudaFree(cv->d_wdw);
+    cudaFree(cv->d_wdp);
+    cudaFree(cv->d_cdp);
     cudaFree(cv->d_wzp);
     cudaFree(cv->d_mult);
     cudaFree(cv->d_bias);

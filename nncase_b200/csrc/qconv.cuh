@@ -54,6 +54,9 @@ struct nncb_qconv2d {
     // device copies of the caller's tables
     void *d_w = nullptr;       // OHWI weights as given
     int16_t *d_wdw = nullptr;  // depthwise only: (w - zw) as int16, [tap][channel]
+    uint32_t *d_wdp = nullptr; // depthwise 3x3 only: raw weight bytes of a kernel row as dp4a operands, [ky][low / shifted][channel]
+    int32_t *d_cdp = nullptr;  // depthwise 3x3 only: per channel 9 zx zw - zx sum(w)
+    bool dw_has_zw = false;    // some weight zero point is not 0
     // depthwise only: constants of the division-free exact requantisation (valid when dw_fast)
     bool dw_fast = false;
     float dw_rso = 0.f, dw_qlo = 0.f, dw_qhi = 255.f;

@@ -197,6 +197,120 @@ dw_conv_kernel(SimtGeom g, const uint8_t *__restrict__ x, const int16_t *__restr
     }
 }
 
+// requantises and stores the four outputs x four channels a thread of the 3x3 kernels holds
+__device__ __forceinline__ void dw3x3_store(const SimtGeom &g, const EpiParams &p, const DwFast &f, const uint8_t *__restrict__ res,
+                                            uint8_t *__restrict__ y, uint8_t *__restrict__ y2, const int (&acc)[4][4], int b, int oy,
+                                            int ox0, int c0) {
+    const float4 mult = __ldg(reinterpret_cast<const float4 *>(p.mult + c0));
+    const float4 bias = __ldg(reinterpret_cast<const float4 *>(p.bias + c0));
+    const float m4[4] = {mult.x, mult.y, mult.z, mult.w}, b4[4] = {bias.x, bias.y, bias.z, bias.w};
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+        if (ox0 + t >= g.ow)
+            break;
+        const size_t o = ((((size_t)b * g.oh + oy) * g.ow) + ox0 + t) * g.c + c0;
+        int q[4];
+        if (f.on) {
+            dw_requant2(acc[t][0], acc[t][1], m4[0], m4[1], b4[0], b4[1], f, q[0], q[1]);
+            dw_requant2(acc[t][2], acc[t][3], m4[2], m4[3], b4[2], b4[3], f, q[2], q[3]);
+        } else {
+            const uint32_t rv = p.has_res ? __ldg(reinterpret_cast<const uint32_t *>(res + o)) : 0u;
+#pragma unroll
+            for (int e = 0; e < 4; e++)
+                q[e] = epi_u8(acc[t][e], m4[e], b4[e], p, (int)((rv >> (8 * e)) & 255u));
+        }
+        *reinterpret_cast<uint32_t *>(y + o) = (uint32_t)q[0] | ((uint32_t)q[1] << 8) | ((uint32_t)q[2] << 16) | ((uint32_t)q[3] << 24);
+        if (y2)
+            *reinterpret_cast<uint32_t *>(y2 + o) = (uint32_t)p.y2_lut[q[0]] | ((uint32_t)p.y2_lut[q[1]] << 8) |
+                                                    ((uint32_t)p.y2_lut[q[2]] << 16) | ((uint32_t)p.y2_lut[q[3]] << 24);
+    }
+}
+
+// The tap sums as byte dot products. sum (x - zx)(w - zw) = sum x w - zw sum x + (9 zx zw - zx sum w) with padded
+// taps holding zx: per kernel row the six (stride 1) or nine (stride 2) column words of four channels are
+// transposed (eight PRMT per four columns) into words that hold four consecutive columns of ONE channel, and one
+// dp4a against the row's three weight bytes -- in bytes 0..2 for the window that starts at the first column of
+// the word, in bytes 1..3 for the one that starts at the second -- gives a row's share of one output; a second
+// dp4a against ones gives sum x where some weight zero point is not zero. About 25 instructions per output
+// channel against 40 of the multiply-add form.
+template <bool W_SIGNED>
+__device__ __forceinline__ int dot4(uint32_t xbytes, uint32_t wbytes, int acc) {
+    int d;
+    if (W_SIGNED)
+        asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(xbytes), "r"(wbytes), "r"(acc));
+    else
+        asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(xbytes), "r"(wbytes), "r"(acc));
+    return d;
+}
+
+template <int S, bool W_SIGNED, bool HAS_ZW>
+__global__ void __launch_bounds__(256)
+dw3x3_dp_kernel(SimtGeom g, const uint8_t *__restrict__ x, const uint32_t *__restrict__ wdp, const int32_t *__restrict__ cdp,
+                const int32_t *__restrict__ w_zp, EpiParams p, DwFast f, const uint8_t *__restrict__ res,
+                uint8_t *__restrict__ y, uint8_t *__restrict__ y2) {
+    constexpr int NC = 3 * S + 3;
+    const uint32_t cq = (uint32_t)g.c / 4u, oxg = ((uint32_t)g.ow + 3u) / 4u;
+    const uint32_t j = blockIdx.y * blockDim.x + threadIdx.x;
+    if (j < oxg * cq) {
+        const int c0 = (int)(j % cq) * 4;
+        const int ox0 = (int)(j / cq) * 4;
+        const int oy = (int)(blockIdx.x % (uint32_t)g.oh), b = (int)(blockIdx.x / (uint32_t)g.oh);
+        const int ix0 = ox0 * S - g.pl, iy0 = oy * S - g.pt;
+        const uint32_t zxw = (uint32_t)g.x_zp * 0x01010101u; // a padded tap holds the zero point
+        int acc[4][4], sx[4][4];
+#pragma unroll
+        for (int t = 0; t < 4; t++)
+#pragma unroll
+            for (int e = 0; e < 4; e++)
+                acc[t][e] = 0, sx[t][e] = 0;
+#pragma unroll
+        for (int ky = 0; ky < 3; ky++) {
+            const int iy = iy0 + ky;
+            const bool row_ok = iy >= 0 && iy < g.h;
+            const uint8_t *xrow = x + (((size_t)b * g.h + (row_ok ? iy : 0)) * g.w) * g.c + c0;
+            uint32_t col[NC];
+#pragma unroll
+            for (int cidx = 0; cidx < NC; cidx++) {
+                const int ix = ix0 + cidx;
+                const bool valid = row_ok && ix >= 0 && ix < g.w;
+                col[cidx] = valid ? __ldg(reinterpret_cast<const uint32_t *>(xrow + (size_t)ix * g.c)) : zxw;
+            }
+            const uint4 wl = __ldg(reinterpret_cast<const uint4 *>(wdp + (size_t)(ky * 2 + 0) * g.c + c0));
+            const uint4 wh = __ldg(reinterpret_cast<const uint4 *>(wdp + (size_t)(ky * 2 + 1) * g.c + c0));
+            const uint32_t wlo[4] = {wl.x, wl.y, wl.z, wl.w}, whi[4] = {wh.x, wh.y, wh.z, wh.w};
+#pragma unroll
+            for (int t = 0; t < 4; t++) {
+                // the four-column word this output's window lies in, and whether it starts at its second column
+                const int start = S == 1 ? (t / 2) * 2 : (t < 3 ? 2 * t : 5);
+                const bool shifted = S == 1 ? (t & 1) != 0 : t == 3;
+                const uint32_t a = __byte_perm(col[start], col[start + 1], 0x5140), b2 = __byte_perm(col[start + 2], col[start + 3], 0x5140);
+                const uint32_t c = __byte_perm(col[start], col[start + 1], 0x7362), d2 = __byte_perm(col[start + 2], col[start + 3], 0x7362);
+                const uint32_t tr[4] = {__byte_perm(a, b2, 0x5410), __byte_perm(a, b2, 0x7632), __byte_perm(c, d2, 0x5410),
+                                        __byte_perm(c, d2, 0x7632)};
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    acc[t][e] = dot4<W_SIGNED>(tr[e], shifted ? whi[e] : wlo[e], acc[t][e]);
+                    if (HAS_ZW)
+                        sx[t][e] = dot4<false>(tr[e], shifted ? 0x01010100u : 0x00010101u, sx[t][e]);
+                }
+            }
+        }
+        const int4 cd = __ldg(reinterpret_cast<const int4 *>(cdp + c0));
+        const int cds[4] = {cd.x, cd.y, cd.z, cd.w};
+        int zws[4] = {0, 0, 0, 0};
+        if (HAS_ZW) {
+            const int4 z = __ldg(reinterpret_cast<const int4 *>(w_zp + c0));
+            zws[0] = z.x, zws[1] = z.y, zws[2] = z.z, zws[3] = z.w;
+        }
+#pragma unroll
+        for (int t = 0; t < 4; t++)
+#pragma unroll
+            for (int e = 0; e < 4; e++)
+                acc[t][e] += cds[e] - zws[e] * sx[t][e];
+        dw3x3_store(g, p, f, res, y, y2, acc, b, oy, ox0, c0);
+    }
+}
+
 // 3x3, dilation 1, stride S in {1, 2}: one thread computes FOUR horizontally adjacent outputs of four
 // channels from a sliding window of 3 S + 3 input columns per kernel row held in registers, so every input
 // word is loaded and unpacked once per row (instead of once per tap) and every weight once per four outputs.
@@ -248,30 +362,7 @@ dw3x3_conv_kernel(SimtGeom g, const uint8_t *__restrict__ x, const int16_t *__re
                 }
             }
         }
-        const float4 mult = __ldg(reinterpret_cast<const float4 *>(p.mult + c0));
-        const float4 bias = __ldg(reinterpret_cast<const float4 *>(p.bias + c0));
-        const float m4[4] = {mult.x, mult.y, mult.z, mult.w}, b4[4] = {bias.x, bias.y, bias.z, bias.w};
-#pragma unroll
-        for (int t = 0; t < 4; t++) {
-            if (ox0 + t >= g.ow)
-                break;
-            const size_t o = ((((size_t)b * g.oh + oy) * g.ow) + ox0 + t) * g.c + c0;
-            int q[4];
-            if (f.on) {
-                dw_requant2(acc[t][0], acc[t][1], m4[0], m4[1], b4[0], b4[1], f, q[0], q[1]);
-                dw_requant2(acc[t][2], acc[t][3], m4[2], m4[3], b4[2], b4[3], f, q[2], q[3]);
-            } else {
-                const uint32_t rv = p.has_res ? __ldg(reinterpret_cast<const uint32_t *>(res + o)) : 0u;
-#pragma unroll
-                for (int e = 0; e < 4; e++)
-                    q[e] = epi_u8(acc[t][e], m4[e], b4[e], p, (int)((rv >> (8 * e)) & 255u));
-            }
-            *reinterpret_cast<uint32_t *>(y + o) =
-                (uint32_t)q[0] | ((uint32_t)q[1] << 8) | ((uint32_t)q[2] << 16) | ((uint32_t)q[3] << 24);
-            if (y2)
-                *reinterpret_cast<uint32_t *>(y2 + o) = (uint32_t)p.y2_lut[q[0]] | ((uint32_t)p.y2_lut[q[1]] << 8) |
-                                                        ((uint32_t)p.y2_lut[q[2]] << 16) | ((uint32_t)p.y2_lut[q[3]] << 24);
-        }
+        dw3x3_store(g, p, f, res, y, y2, acc, b, oy, ox0, c0);
     }
 }
 
@@ -300,6 +391,33 @@ int simt_conv_prepare(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, c
     };
     cv->dw_qlo = quant(d.clamp_lo), cv->dw_qhi = quant(d.clamp_hi);
     cv->dw_fast = ok && !d.has_residual && cv->d_lut == nullptr && !std::isnan(d.clamp_lo) && !std::isnan(d.clamp_hi);
+    if (d.kh == 3 && d.kw == 3) {
+        // dp4a form: a kernel row's three raw weight bytes in bytes 0..2 (low) and in bytes 1..3 (shifted) of a word,
+        // and the constant part of sum (x - zx)(w - zw) = sum x w - zw sum x - zx sum w + 9 zx zw
+        std::vector<uint32_t> wd((size_t)3 * 2 * d.c);
+        std::vector<int32_t> cd(d.c);
+        for (int c = 0; c < d.c; c++) {
+            int wsum = 0;
+            for (int ky = 0; ky < 3; ky++) {
+                uint32_t lo = 0;
+                for (int kx = 0; kx < 3; kx++) {
+                    const uint8_t b = reinterpret_cast<const uint8_t *>(w_host)[(size_t)c * 9 + ky * 3 + kx];
+                    lo |= (uint32_t)b << (8 * kx);
+                    wsum += d.w_signed ? (int)(int8_t)b : (int)b;
+                }
+                wd[((size_t)ky * 2 + 0) * d.c + c] = lo;
+                wd[((size_t)ky * 2 + 1) * d.c + c] = lo << 8;
+            }
+            const int zw = wzp_host ? wzp_host[c] : 0;
+            cv->dw_has_zw |= zw != 0;
+            cd[c] = 9 * d.x_zp * zw - d.x_zp * wsum;
+        }
+        NNCB_CUDA_TRY(cudaMalloc(&cv->d_wdp, wd.size() * 4));
+        NNCB_CUDA_TRY(cudaMalloc(&cv->d_cdp, cd.size() * 4));
+        NNCB_CUDA_TRY(cudaMemcpyAsync(cv->d_wdp, wd.data(), wd.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+        NNCB_CUDA_TRY(cudaMemcpyAsync(cv->d_cdp, cd.data(), cd.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+        NNCB_CUDA_TRY(cudaStreamSynchronize(ctx->stream)); // the host vectors go out of scope
+    }
     NNCB_CUDA_TRY(cudaMalloc(&cv->d_wdw, t.size() * sizeof(int16_t)));
     NNCB_CUDA_TRY(cudaMemcpyAsync(cv->d_wdw, t.data(), t.size() * sizeof(int16_t), cudaMemcpyHostToDevice, ctx->stream));
     NNCB_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
@@ -322,6 +440,25 @@ int simt_conv_run(nncb_context *ctx, nncb_qconv2d *cv, const uint8_t *x, const u
             const int row_items = ((cv->ow + 3) / 4) * (d.c / 4);
             const int bt = row_items >= 256 ? 256 : (row_items + 31) / 32 * 32;
             const dim3 grid3((unsigned)(d.n * cv->oh), (unsigned)((row_items + bt - 1) / bt));
+            const bool al16 = (reinterpret_cast<uintptr_t>(cv->d_wdp) & 15) == 0;
+            if (cv->d_wdp && cv->d_cdp && al16 && !getenv("NNCB_DW_MAD")) { // (tuning aid: the multiply-add form)
+#define NNCB_DWDP(S_, WS_, ZW_)                                                                                       \
+    dw3x3_dp_kernel<S_, WS_, ZW_><<<grid3, bt, 0, ctx->stream>>>(g, x, cv->d_wdp, cv->d_cdp, cv->d_wzp, p, f, res,   \
+                                                                 (uint8_t *)y, y2)
+                const int v = (d.stride_h == 2 ? 4 : 0) | (d.w_signed ? 2 : 0) | (cv->dw_has_zw ? 1 : 0);
+                switch (v) {
+                case 0: NNCB_DWDP(1, false, false); break;
+                case 1: NNCB_DWDP(1, false, true); break;
+                case 2: NNCB_DWDP(1, true, false); break;
+                case 3: NNCB_DWDP(1, true, true); break;
+                case 4: NNCB_DWDP(2, false, false); break;
+                case 5: NNCB_DWDP(2, false, true); break;
+                case 6: NNCB_DWDP(2, true, false); break;
+                default: NNCB_DWDP(2, true, true); break;
+                }
+#undef NNCB_DWDP
+                return after_launch(ctx, "dw3x3_dp");
+            }
             if (d.stride_h == 1)
                 dw3x3_conv_kernel<1><<<grid3, bt, 0, ctx->stream>>>(g, x, cv->d_wdw, p, f, res, (uint8_t *)y, y2);
             else
