@@ -388,21 +388,32 @@ int nhwc_to_nchw_u8(nncb_context *ctx, const uint8_t *in, uint8_t *out, int n, i
 }
 
 // ---- element-wise add between quantized tensors ------------------------------------------------
+// rso != 0: the division-free form. byte -> float and the zero-point subtraction are one PRMT and one exact add
+// (the bits 0x4B0000qq are the float 2^23 + qq, and (2^23 + qq) - (2^23 + z) = qq - z exactly), the output division
+// is the verified-reciprocal sequence, rint + clamp one saturating conversion.
 __device__ __forceinline__ uint32_t qadd4(uint32_t a, uint32_t b, float sa, float za, float sb, float zb,
-                                          float so, float zo) {
+                                          float so, float zo, float rso) {
     uint32_t r = 0;
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-        float fa = dequant_dev((float)((a >> (8 * i)) & 255), za, sa);
-        float fb = dequant_dev((float)((b >> (8 * i)) & 255), zb, sb);
-        r |= (uint32_t)quant_dev(__fadd_rn(fa, fb), so, zo, 0, 255) << (8 * i);
+        if (rso != 0.f) {
+            const float qa = __uint_as_float(__byte_perm(a, 0x4B000000u, 0x7440 | i)); // 2^23 + byte i of a
+            const float qb = __uint_as_float(__byte_perm(b, 0x4B000000u, 0x7440 | i));
+            const float fa = __fmul_rn(__fsub_rn(qa, __fadd_rn(8388608.0f, za)), sa);
+            const float fb = __fmul_rn(__fsub_rn(qb, __fadd_rn(8388608.0f, zb)), sb);
+            r |= quant_u8_fast(__fadd_rn(fa, fb), so, rso, zo) << (8 * i);
+        } else {
+            float fa = dequant_dev((float)((a >> (8 * i)) & 255), za, sa);
+            float fb = dequant_dev((float)((b >> (8 * i)) & 255), zb, sb);
+            r |= (uint32_t)quant_dev(__fadd_rn(fa, fb), so, zo, 0, 255) << (8 * i);
+        }
     }
     return r;
 }
 
 __global__ void __launch_bounds__(256)
 qadd_kernel(const uint8_t *__restrict__ a, const uint8_t *__restrict__ b, uint8_t *__restrict__ y, size_t n,
-            float sa, float za, float sb, float zb, float so, float zo, bool vec_ok) {
+            float sa, float za, float sb, float zb, float so, float zo, float rso, bool vec_ok) {
     const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t nthreads = (size_t)gridDim.x * blockDim.x;
     const size_t nvec = vec_ok ? n / 16 : 0;
@@ -410,10 +421,10 @@ qadd_kernel(const uint8_t *__restrict__ a, const uint8_t *__restrict__ b, uint8_
         uint4 va = __ldcs(reinterpret_cast<const uint4 *>(a) + v);
         uint4 vb = __ldcs(reinterpret_cast<const uint4 *>(b) + v);
         uint4 r;
-        r.x = qadd4(va.x, vb.x, sa, za, sb, zb, so, zo);
-        r.y = qadd4(va.y, vb.y, sa, za, sb, zb, so, zo);
-        r.z = qadd4(va.z, vb.z, sa, za, sb, zb, so, zo);
-        r.w = qadd4(va.w, vb.w, sa, za, sb, zb, so, zo);
+        r.x = qadd4(va.x, vb.x, sa, za, sb, zb, so, zo, rso);
+        r.y = qadd4(va.y, vb.y, sa, za, sb, zb, so, zo, rso);
+        r.z = qadd4(va.z, vb.z, sa, za, sb, zb, so, zo, rso);
+        r.w = qadd4(va.w, vb.w, sa, za, sb, zb, so, zo, rso);
         __stcs(reinterpret_cast<uint4 *>(y) + v, r);
     }
     for (size_t i = nvec * 16 + tid; i < n; i += nthreads) {
@@ -429,8 +440,13 @@ int qadd_u8(nncb_context *ctx, const uint8_t *a, const uint8_t *b, uint8_t *y, s
     if (!a || !b || !y)
         return fail(-EINVAL, "qadd_u8: null pointer");
     bool v = aligned16(a, b) && aligned16(y, y);
+    // zero points within a byte keep 2^23 + z exact; the reciprocal must be one the sequence is proven for
+    bool r_ok = za >= 0 && za <= 255 && zb >= 0 && zb <= 255;
+    float rso = rn_reciprocal(so, &r_ok);
+    if (!r_ok)
+        rso = 0.f;
     qadd_kernel<<<stream_grid(ctx, (n + 15) / 16, 256), 256, 0, ctx->stream>>>(a, b, y, n, sa, (float)za, sb,
-                                                                                  (float)zb, so, (float)zo, v);
+                                                                                  (float)zb, so, (float)zo, rso, v);
     return after_launch(ctx, "qadd_u8");
 }
 
