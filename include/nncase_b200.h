@@ -44,16 +44,37 @@ typedef enum nncb_dtype { NNCB_I8 = 2, NNCB_I16 = 3, NNCB_U8 = 6, NNCB_F16 = 10,
 
 /* ---- context: device + stream (replaces kernels::kernel_context,
  *      src/Native/include/nncase/kernels/kernel_context.h) ------------------------------ */
-/* stream: the cudaStream_t to launch on; NULL is the CUDA default stream. The caller owns it. */
+/* stream: the cudaStream_t to launch on; NULL is the CUDA default stream. The caller owns it.
+ * Every call that takes a context makes the context's device the calling thread's current CUDA
+ * device (cudaSetDevice) and leaves it so: a caller that works with several devices sets its own
+ * device again afterwards. */
 NNCB_API int nncb_context_create(int device, void *stream, nncb_context **out);
 NNCB_API int nncb_context_destroy(nncb_context *ctx);
 NNCB_API int nncb_context_set_stream(nncb_context *ctx, void *stream);
 NNCB_API void *nncb_context_stream(nncb_context *ctx);
 NNCB_API int nncb_synchronize(nncb_context *ctx);
+/* Per-context options, by name (the role of the reference interpreter's options_dict,
+ * src/Native/src/runtime/interpreter.cpp:29-31). Read when a plan is created or a kernel is launched.
+ *   "wait_limit_us"          kernel-internal waits give up after this long (default 1,000,000)
+ *   "conv.tile_n"            force the N tile of the tensor-core convolution: 128, 96, 64, 48, 32 (0 = choose)
+ *   "conv.wide_patch"        0: keep 64-/128-channel stride-1 convolutions on the im2col form (default 1)
+ *   "depthwise.dot_product"  0: multiply-add form of the 3x3 depthwise kernel (default 1)
+ *   "attention.warps"        force the CTA width of paged attention: 4 or 8 (0 = choose)
+ *   "attention.splits"       force its number of context splits (0 = choose)
+ *   "debug.withhold_load"    1: the tensor-core convolution's loader leaves out one operand load, so that
+ *                            the consumer's wait runs out; exercises the give-up path (see
+ *                            nncb_check_device_status). Results of such a run are undefined.
+ * Unknown names and negative values: -EINVAL. */
+NNCB_API int nncb_context_set_option(nncb_context *ctx, const char *name, int64_t value);
+NNCB_API int nncb_context_get_option(nncb_context *ctx, const char *name, int64_t *value);
 /* Number of kernels this context has launched so far. */
 NNCB_API uint64_t nncb_launch_count(nncb_context *ctx);
-/* Reads and clears the device-side status word kernels set when an internal wait ran out
- * (0 = none). Synchronises the stream. */
+/* Reads and clears the device-side status word (0 = none); synchronises the stream.
+ *   -ETIMEDOUT  a kernel-internal wait ran out (role codes 101-105 of the tensor-core convolution);
+ *               the kernel returned early, its outputs are undefined, the context stays usable
+ *   -ERANGE     a kernel met an index from device memory that it refused to follow: a position,
+ *               context length or page id outside the bounds the call was given (codes 201, 202);
+ *               nothing was read or written through it */
 NNCB_API int nncb_check_device_status(nncb_context *ctx);
 NNCB_API const char *nncb_last_error(void);
 NNCB_API const char *nncb_version(void);
@@ -209,7 +230,10 @@ NNCB_API int nncb_gemv_w8a16(nncb_context *ctx, const void *x, const int8_t *w, 
  * nncb_gemv_w8a16 followed by nncb_swiglu_f16 on the un-interleaved rows, without the [m][n] round trip. */
 NNCB_API int nncb_gemv_w8a16_swiglu(nncb_context *ctx, const void *x, const int8_t *w, const void *scale, const void *bias, void *y, int m, int n, int k);
 NNCB_API int nncb_add_rmsnorm_f16(nncb_context *ctx, void *x, const void *delta, const void *weight, void *h, int rows, int cols, float eps);
-NNCB_API int nncb_rope_kv_append_f16(nncb_context *ctx, const void *qkv, void *q_out, const float *cos_table, const float *sin_table, const int32_t *positions, const int32_t *block_table, void *k_pool, void *v_pool, int batch, int q_heads, int kv_heads, int head_dim, int page_size, int max_pages);
+/* max_pos: rows of the cos/sin tables; num_pages: pages in the pools. A position outside [0, max_pos) or beyond
+ * the block-table row, or a page id outside [0, num_pages), stores nothing for that sequence and sets the
+ * status word (-ERANGE from nncb_check_device_status). */
+NNCB_API int nncb_rope_kv_append_f16(nncb_context *ctx, const void *qkv, void *q_out, const float *cos_table, const float *sin_table, const int32_t *positions, const int32_t *block_table, void *k_pool, void *v_pool, int batch, int q_heads, int kv_heads, int head_dim, int page_size, int max_pages, int max_pos, int num_pages);
 NNCB_API int nncb_swiglu_f16(nncb_context *ctx, const void *gate_up, void *out, int rows, int inter);
 NNCB_API int nncb_embedding_f16(nncb_context *ctx, const void *table, const int32_t *ids, void *out, int rows, int cols, int vocab);
 
@@ -223,9 +247,12 @@ NNCB_API int nncb_embedding_f16(nncb_context *ctx, const void *table, const int3
  *   out [batch][q_heads][head_dim] f16.  Query head h reads kv head h / (q_heads / kv_heads).
  * Built for head_dim 64, page_size 16, q_heads / kv_heads <= 8 (others: -ENOSYS).
  * The context is split across CTAs; partial results go through `workspace` (device memory, size
- * from nncb_paged_attention_workspace_size, may be 0). */
+ * from nncb_paged_attention_workspace_size, may be 0).
+ * num_pages = pages in the pools. Indices read from device memory are bounded: a context length is
+ * clamped to [0, max_pages * page_size], a page id outside [0, num_pages) contributes zeros; either sets
+ * the status word (-ERANGE from nncb_check_device_status). */
 NNCB_API int nncb_paged_attention_workspace_size(nncb_context *ctx, int batch, int q_heads, int kv_heads, int head_dim, int page_size, int max_pages, size_t *bytes);
-NNCB_API int nncb_paged_attention_decode(nncb_context *ctx, const void *q, const void *k_pool, const void *v_pool, const int32_t *block_table, const int32_t *context_lens, void *out, int batch, int q_heads, int kv_heads, int head_dim, int page_size, int max_pages, float scale, void *workspace, size_t workspace_bytes);
+NNCB_API int nncb_paged_attention_decode(nncb_context *ctx, const void *q, const void *k_pool, const void *v_pool, const int32_t *block_table, const int32_t *context_lens, void *out, int batch, int q_heads, int kv_heads, int head_dim, int page_size, int max_pages, int num_pages, float scale, void *workspace, size_t workspace_bytes);
 
 /* Paged-attention decode for callers that must not allocate. (No counterpart in the reference.)
  *
@@ -236,22 +263,32 @@ NNCB_API int nncb_paged_attention_decode(nncb_context *ctx, const void *q, const
  * takes the same inputs and outputs and keeps the split partials in a 768 KiB array that is part of
  * the library image on every GPU that loads it. It calls no cudaMalloc, cudaFree or other allocating
  * routine.
- *  - Limit: batch * q_heads * splits * 264 bytes must fit 768 KiB (the Qwen2-0.5B decode shape,
- *    batch 64 x 14 heads x 3 context splits, uses 693 KiB); larger problems return -E2BIG with a
- *    message that names both sizes.
+ *  - Limit: batch * q_heads * splits * 264 bytes must fit 768 KiB; larger problems return -E2BIG with a
+ *    message that names both sizes. The library splits the context only while (sequence, kv head) pairs
+ *    are too few to fill the GPU, so batch * kv_heads * splits stays near the number of CTA slots: on a
+ *    148-SM part the partials reach about 625 KiB at most. A large batch such as the Qwen2-0.5B decode
+ *    shape (64 sequences x 2 kv heads) runs unsplit and uses none of the array.
  *  - The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that
  *    device current) and remembers it; make that first call before starting any stream capture.
  *  - All calls on a device share the one array. Nothing in it has to be cleared between calls (every
  *    entry that is read is written first by the same call), but two calls that overlap on the GPU
  *    -- different streams, or different contexts -- race on it: serialise them.
  * Results are identical to nncb_paged_attention_decode. */
-NNCB_API int nncb_paged_attention_decode_noalloc(nncb_context *ctx, const void *q, const void *k_pool, const void *v_pool, const int32_t *block_table, const int32_t *context_lens, void *out, int batch, int q_heads, int kv_heads, int head_dim, int page_size, int max_pages, float scale);
+NNCB_API int nncb_paged_attention_decode_noalloc(nncb_context *ctx, const void *q, const void *k_pool, const void *v_pool, const int32_t *block_table, const int32_t *context_lens, void *out, int batch, int q_heads, int kv_heads, int head_dim, int page_size, int max_pages, int num_pages, float scale);
 
 /* Diagnostic: the tensor-core kernel divides by a layer's output scale with a three-operation
  * sequence around a correctly rounded reciprocal. This runs that sequence against the IEEE
  * division for `count` pseudo-random operands on the device and returns how many differ
  * (expected: 0). No counterpart in the reference. */
 NNCB_API int nncb_selftest_reciprocal_division(nncb_context *ctx, float scale, uint64_t count, uint64_t seed, uint64_t *mismatches);
+
+/* Diagnostic: the measured peak of the kind::i8 tensor pipe on this GPU, the denominator of every
+ * "fraction of int8 peak" this library's benchmarks report. One CTA per SM issues `mmas_per_sm`
+ * back-to-back tcgen05.mma (M 128, N 256, K 32; u8 x u8, or u8 x i8 when w_signed) on operand tiles
+ * resident in shared memory; no global-memory traffic, no epilogue. Timed with CUDA events on the context's
+ * stream, `repeats` launches after one warm-up; returns the best and the mean rate in TOP/s (2 operations
+ * per multiply-accumulate). Synchronises. No counterpart in the reference. */
+NNCB_API int nncb_selftest_int8_peak(nncb_context *ctx, uint32_t mmas_per_sm, int repeats, int w_signed, double *best_tops, double *mean_tops);
 
 #ifdef __cplusplus
 }

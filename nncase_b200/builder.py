@@ -290,7 +290,8 @@ def build_program(graph, calib_samples, w_quant_type="uint8", device="cpu"):
             o = dict(op="conv", name=nd["name"], **{"in": nd["in"]}, out=conv_out, w=wq,
                      w_zp=zw if zw.any() else None, mult=mult, bias=bias, stride=tuple(stride),
                      pad=tuple(pad), dil=nd["dil"], groups=groups, clamp=clamp,
-                     res=nd.get("res") if fuse_res else None, y2=nd.get("relu_out"), conv_qp=conv_qp, lut=lut)
+                     res=nd.get("res") if fuse_res else None, y2=nd.get("relu_out"), conv_qp=conv_qp, lut=lut,
+                     w_scale=sw)
             ops.append(o)
             if has_res and not fuse_res:
                 add_tensor(conv_out, oc, oh, ow, qps[nd["out"] + "@conv"])
@@ -322,7 +323,7 @@ def build_program(graph, calib_samples, w_quant_type="uint8", device="cpu"):
             ops.append(dict(op="conv", name=nd["name"], **{"in": nd["in"]}, out=nd["out"], w=wq,
                             w_zp=zw if zw.any() else None, mult=mult, bias=nd["b"].astype(np.float32), stride=(1, 1),
                             pad=(0, 0, 0, 0), dil=(1, 1), groups=1, clamp=(-INF, INF), res=None, y2=None,
-                            conv_qp=None, f32_out=True))
+                            conv_qp=None, f32_out=True, w_scale=sw))
         elif op == "slice":
             c, h, w = shapes[nd["in"]]
             if logical.get(nd["in"], c) != c:

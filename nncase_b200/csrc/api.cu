@@ -122,15 +122,16 @@ int paged_attention_pick_splits(const nncb_context *ctx, int B, int Hkv, int max
 int paged_attention_check(int B, int Hq, int Hkv, int head_dim, int page_size, int max_pages);
 int paged_attention_launch(nncb_context *ctx, const void *q, const void *k_pool, const void *v_pool,
                            const int32_t *block_table, const int32_t *ctx_lens, void *out, int B, int Hq, int Hkv,
-                           int max_pages, float scale, int splits, void *scratch);
+                           int max_pages, int num_pages, float scale, int splits, void *scratch);
 
 int gemv_w8a16(nncb_context *, const void *, const int8_t *, const void *, const void *, const void *, void *, int, int, int);
 int gemv_w8a16_swiglu(nncb_context *, const void *, const int8_t *, const void *, const void *, void *, int, int, int);
 int add_rmsnorm_f16(nncb_context *, void *, const void *, const void *, void *, int, int, float);
 int rope_kv_append_f16(nncb_context *, const void *, void *, const float *, const float *, const int32_t *,
-                       const int32_t *, void *, void *, int, int, int, int, int, int);
+                       const int32_t *, void *, void *, int, int, int, int, int, int, int, int);
 int swiglu_f16(nncb_context *, const void *, void *, int, int);
 int embedding_f16(nncb_context *, const void *, const int32_t *, void *, int, int, int);
+int int8_peak_selftest(nncb_context *ctx, uint32_t mmas_per_sm, int repeats, int w_signed, double *best_tops, double *mean_tops);
 size_t paged_attention_static_capacity();
 int paged_attention_static_scratch(int device, void **ptr);
 
@@ -168,18 +169,68 @@ int nncb_context_create(int device, void *stream, nncb_context **out) {
     NNCB_CUDA_TRY(cudaGetDeviceProperties(&prop, device));
     if (prop.major != 10)
         return fail(-ENOSYS, "device %d is sm_%d%d; this library contains sm_100a code only", device, prop.major, prop.minor);
+    // kernels that need more than 48 KB of dynamic shared memory: the limit is a per-device attribute
+    NNCB_TRY(paged_attention_set_attributes());
+    NNCB_TRY(gemv_set_attributes());
     nncb_context *ctx = new nncb_context();
     ctx->device = device;
     ctx->sm_count = prop.multiProcessorCount;
     ctx->stream = (cudaStream_t)stream; // NULL is the CUDA default stream
-    NNCB_CUDA_TRY(cudaMalloc(&ctx->d_status, sizeof(int)));
-    NNCB_CUDA_TRY(cudaMemset(ctx->d_status, 0, sizeof(int)));
-    {
-        const size_t bytes = (size_t)nncb::GEMV_SPLIT_SLOTS * (16 * 64 * sizeof(float) + sizeof(int));
-        NNCB_CUDA_TRY(cudaMalloc(&ctx->d_gemv_ws, bytes));
-        NNCB_CUDA_TRY(cudaMemset(ctx->d_gemv_ws, 0, bytes));
+    const size_t ws_bytes = (size_t)nncb::GEMV_SPLIT_SLOTS * (16 * 64 * sizeof(float) + sizeof(int));
+    cudaError_t ce = cudaMalloc(&ctx->d_status, sizeof(int));
+    if (ce == cudaSuccess)
+        ce = cudaMemset(ctx->d_status, 0, sizeof(int));
+    if (ce == cudaSuccess)
+        ce = cudaMalloc(&ctx->d_gemv_ws, ws_bytes);
+    if (ce == cudaSuccess)
+        ce = cudaMemset(ctx->d_gemv_ws, 0, ws_bytes);
+    if (ce != cudaSuccess) {
+        cudaFree(ctx->d_status);
+        cudaFree(ctx->d_gemv_ws);
+        delete ctx;
+        cudaGetLastError();
+        return fail(ce == cudaErrorMemoryAllocation ? -ENOMEM : -EIO, "nncb_context_create: %s", cudaGetErrorString(ce));
     }
     *out = ctx;
+    return 0;
+}
+
+// name -> field of nncb_options
+static int *option_slot(nncb_context *ctx, const char *name) {
+    struct { const char *name; int *slot; } table[] = {
+        {"conv.tile_n", &ctx->opt.conv_tile_n},
+        {"conv.wide_patch", &ctx->opt.conv_wide_patch},
+        {"depthwise.dot_product", &ctx->opt.depthwise_dot},
+        {"attention.warps", &ctx->opt.attention_warps},
+        {"attention.splits", &ctx->opt.attention_splits},
+        {"wait_limit_us", reinterpret_cast<int *>(&ctx->opt.wait_limit_us)},
+        {"debug.withhold_load", &ctx->opt.debug_withhold_load},
+    };
+    for (auto &e : table)
+        if (name && strcmp(name, e.name) == 0)
+            return e.slot;
+    return nullptr;
+}
+
+int nncb_context_set_option(nncb_context *ctx, const char *name, int64_t value) {
+    if (!ctx)
+        return fail(-EINVAL, "null context");
+    int *slot = option_slot(ctx, name);
+    if (!slot)
+        return fail(-EINVAL, "unknown option '%s'", name ? name : "(null)");
+    if (value < 0 || value > 0x7fffffff || (slot == reinterpret_cast<int *>(&ctx->opt.wait_limit_us) && value == 0))
+        return fail(-EINVAL, "option '%s': value %lld out of range", name, (long long)value);
+    *slot = (int)value;
+    return 0;
+}
+
+int nncb_context_get_option(nncb_context *ctx, const char *name, int64_t *value) {
+    if (!ctx || !value)
+        return fail(-EINVAL, "null argument");
+    int *slot = option_slot(ctx, name);
+    if (!slot)
+        return fail(-EINVAL, "unknown option '%s'", name ? name : "(null)");
+    *value = *slot;
     return 0;
 }
 
@@ -217,6 +268,8 @@ int nncb_check_device_status(nncb_context *ctx) {
     NNCB_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
     if (st != 0) {
         NNCB_CUDA_TRY(cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream));
+        if (st >= 200)
+            return fail(-ERANGE, "a kernel refused an out-of-range index read from device memory (code %d)", st);
         return fail(-ETIMEDOUT, "a kernel gave up waiting (role code %d) and returned early", st);
     }
     return 0;
@@ -471,12 +524,13 @@ int nncb_add_rmsnorm_f16(nncb_context *ctx, void *x, const void *delta, const vo
 }
 int nncb_rope_kv_append_f16(nncb_context *ctx, const void *qkv, void *q_out, const float *cos_table, const float *sin_table,
                             const int32_t *positions, const int32_t *block_table, void *k_pool, void *v_pool, int batch,
-                            int q_heads, int kv_heads, int head_dim, int page_size, int max_pages) {
+                            int q_heads, int kv_heads, int head_dim, int page_size, int max_pages, int max_pos,
+                            int num_pages) {
     CHECK_CTX(ctx);
     if (!qkv || !q_out || !cos_table || !sin_table || !positions || !block_table || !k_pool || !v_pool)
         return fail(-EINVAL, "nncb_rope_kv_append_f16: null pointer");
     return rope_kv_append_f16(ctx, qkv, q_out, cos_table, sin_table, positions, block_table, k_pool, v_pool, batch, q_heads,
-                              kv_heads, head_dim, page_size, max_pages);
+                              kv_heads, head_dim, page_size, max_pages, max_pos, num_pages);
 }
 int nncb_swiglu_f16(nncb_context *ctx, const void *gate_up, void *out, int rows, int inter) {
     CHECK_CTX(ctx);
@@ -505,8 +559,8 @@ int nncb_paged_attention_workspace_size(nncb_context *ctx, int batch, int q_head
 
 int nncb_paged_attention_decode(nncb_context *ctx, const void *q, const void *k_pool, const void *v_pool,
                                 const int32_t *block_table, const int32_t *context_lens, void *out, int batch,
-                                int q_heads, int kv_heads, int head_dim, int page_size, int max_pages, float scale,
-                                void *workspace, size_t workspace_bytes) {
+                                int q_heads, int kv_heads, int head_dim, int page_size, int max_pages, int num_pages,
+                                float scale, void *workspace, size_t workspace_bytes) {
     CHECK_CTX(ctx);
     if (!q || !k_pool || !v_pool || !block_table || !context_lens || !out)
         return fail(-EINVAL, "nncb_paged_attention_decode: null pointer");
@@ -520,13 +574,13 @@ int nncb_paged_attention_decode(nncb_context *ctx, const void *q, const void *k_
         return fail(-EINVAL, "nncb_paged_attention_decode: workspace of %zu bytes required, %zu given", need,
                     workspace ? workspace_bytes : (size_t)0);
     return paged_attention_launch(ctx, q, k_pool, v_pool, block_table, context_lens, out, batch, q_heads, kv_heads,
-                                  max_pages, scale, splits, workspace);
+                                  max_pages, num_pages, scale, splits, workspace);
 }
 
 int nncb_paged_attention_decode_noalloc(nncb_context *ctx, const void *q, const void *k_pool, const void *v_pool,
                                         const int32_t *block_table, const int32_t *context_lens, void *out, int batch,
                                         int q_heads, int kv_heads, int head_dim, int page_size, int max_pages,
-                                        float scale) {
+                                        int num_pages, float scale) {
     CHECK_CTX(ctx);
     if (!q || !k_pool || !v_pool || !block_table || !context_lens || !out)
         return fail(-EINVAL, "nncb_paged_attention_decode_noalloc: null pointer");
@@ -544,7 +598,15 @@ int nncb_paged_attention_decode_noalloc(nncb_context *ctx, const void *q, const 
     void *scratch = nullptr;
     NNCB_TRY(paged_attention_static_scratch(ctx->device, &scratch));
     return paged_attention_launch(ctx, q, k_pool, v_pool, block_table, context_lens, out, batch, q_heads, kv_heads,
-                                  max_pages, scale, splits, scratch);
+                                  max_pages, num_pages, scale, splits, scratch);
+}
+
+int nncb_selftest_int8_peak(nncb_context *ctx, uint32_t mmas_per_sm, int repeats, int w_signed, double *best_tops,
+                            double *mean_tops) {
+    CHECK_CTX(ctx);
+    if (!best_tops || !mean_tops)
+        return fail(-EINVAL, "nncb_selftest_int8_peak: null out");
+    return int8_peak_selftest(ctx, mmas_per_sm, repeats, w_signed, best_tops, mean_tops);
 }
 
 // ---- quantized conv ------------------------------------------------------------------------

@@ -316,12 +316,6 @@ static int gemv_w8a16_fused(nncb_context *ctx, const void *x, const int8_t *w, c
     }
 #define NNCB_GEMV(MT_, G_)                                                                                            \
     do {                                                                                                              \
-        static bool attr_done = false;                                                                                \
-        if (!attr_done) {                                                                                             \
-            NNCB_CUDA_TRY(cudaFuncSetAttribute(gemv_w8a16_kernel<MT_, G_>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                               226 * 1024));                                                          \
-            attr_done = true;                                                                                         \
-        }                                                                                                             \
         gemv_w8a16_kernel<MT_, G_><<<grid, GEMV_WARPS * 32, smem, ctx->stream>>>(xs, w, sc, bi, re, ys, M, N, K, KC, ws, cnt, fu);  \
     } while (0)
     switch (mtt * 2 + (wide ? 1 : 0)) {
@@ -336,6 +330,21 @@ static int gemv_w8a16_fused(nncb_context *ctx, const void *x, const int8_t *w, c
     }
 #undef NNCB_GEMV
     return after_launch(ctx, "gemv_w8a16");
+}
+
+int gemv_set_attributes() {
+#define NNCB_GEMV_ATTR(MT_, G_)                                                                                       \
+    NNCB_CUDA_TRY(cudaFuncSetAttribute(gemv_w8a16_kernel<MT_, G_>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024))
+    NNCB_GEMV_ATTR(1, 1);
+    NNCB_GEMV_ATTR(1, 8);
+    NNCB_GEMV_ATTR(2, 1);
+    NNCB_GEMV_ATTR(2, 8);
+    NNCB_GEMV_ATTR(4, 1);
+    NNCB_GEMV_ATTR(4, 8);
+    NNCB_GEMV_ATTR(8, 1);
+    NNCB_GEMV_ATTR(8, 8);
+#undef NNCB_GEMV_ATTR
+    return 0;
 }
 
 // ---- RMSNorm, optionally fused with the residual add ---------------------------------------------
@@ -447,14 +456,23 @@ int add_rmsnorm_f16(nncb_context *ctx, void *x, const void *delta, const void *w
 // with i + 32 ("rotate half"): out[i] = x[i] cos - x[i+32] sin, out[i+32] = x[i+32] cos + x[i] sin,
 // cos/sin from a host table [max_pos][32] f32. Rotated q goes to q_out [B][Hq][64] (dense, the layout
 // the attention kernel reads); k (rotated) and v go to page block_table[b][pos / 16], slot pos % 16.
+// Positions and page ids come from device memory the caller filled: a position outside [0, max_pos) or
+// beyond the block-table row, or a page id outside [0, num_pages), stores nothing for that sequence and
+// records ERR_BAD_INDEX in the context's status word (nncb_check_device_status reports it).
+enum { ERR_BAD_INDEX = 201 };
 __global__ void __launch_bounds__(64)
 rope_kv_append_kernel(const __half *__restrict__ qkv, __half *__restrict__ q_out, const float *__restrict__ cos_t,
                       const float *__restrict__ sin_t,
                       const int *__restrict__ positions, const int *__restrict__ block_table, __half *__restrict__ k_pool,
-                      __half *__restrict__ v_pool, int Hq, int Hkv, int max_pages) {
+                      __half *__restrict__ v_pool, int Hq, int Hkv, int max_pages, int max_pos, int num_pages, int *status) {
     const int b = blockIdx.y, head = blockIdx.x; // heads 0..Hq-1: q; Hq..Hq+Hkv-1: k; then v
     const int d = threadIdx.x;                   // 0..63
     const int pos = positions[b];
+    if (pos < 0 || pos >= max_pos || pos / 16 >= max_pages) {
+        if (d == 0)
+            atomicCAS(status, 0, ERR_BAD_INDEX);
+        return;
+    }
     const __half *row = qkv + (size_t)b * (Hq + 2 * Hkv) * 64 + (size_t)head * 64;
     const bool is_v = head >= Hq + Hkv;
     float out;
@@ -473,6 +491,11 @@ rope_kv_append_kernel(const __half *__restrict__ qkv, __half *__restrict__ q_out
     } else {
         const int kvh = is_v ? head - Hq - Hkv : head - Hq;
         const int page = block_table[(size_t)b * max_pages + pos / 16];
+        if (page < 0 || page >= num_pages) {
+            if (d == 0)
+                atomicCAS(status, 0, ERR_BAD_INDEX);
+            return;
+        }
         __half *dst = (is_v ? v_pool : k_pool) + (((size_t)page * Hkv + kvh) * 16 + (pos % 16)) * 64;
         dst[d] = ho;
     }
@@ -480,14 +503,15 @@ rope_kv_append_kernel(const __half *__restrict__ qkv, __half *__restrict__ q_out
 
 int rope_kv_append_f16(nncb_context *ctx, const void *qkv, void *q_out, const float *cos_t, const float *sin_t, const int32_t *positions,
                        const int32_t *block_table, void *k_pool, void *v_pool, int B, int Hq, int Hkv, int head_dim,
-                       int page_size, int max_pages) {
-    if (B <= 0 || Hq <= 0 || Hkv <= 0 || max_pages <= 0)
+                       int page_size, int max_pages, int max_pos, int num_pages) {
+    if (B <= 0 || Hq <= 0 || Hkv <= 0 || max_pages <= 0 || max_pos <= 0 || num_pages <= 0)
         return fail(-EINVAL, "rope_kv_append: non-positive dimension");
     if (head_dim != 64 || page_size != 16)
         return fail(-ENOSYS, "rope_kv_append: only head_dim 64 and 16-token pages are built");
     dim3 grid(Hq + 2 * Hkv, B);
     rope_kv_append_kernel<<<grid, 64, 0, ctx->stream>>>((const __half *)qkv, (__half *)q_out, cos_t, sin_t, positions, block_table,
-                                                       (__half *)k_pool, (__half *)v_pool, Hq, Hkv, max_pages);
+                                                       (__half *)k_pool, (__half *)v_pool, Hq, Hkv, max_pages, max_pos,
+                                                       num_pages, ctx->d_status);
     return after_launch(ctx, "rope_kv_append");
 }
 

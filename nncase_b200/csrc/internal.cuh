@@ -10,7 +10,21 @@
 
 #include "../../include/nncase_b200.h"
 
+// Per-context options (nncb_context_set_option). They stand in for the reference's interpreter
+// options_dict (src/Native/src/runtime/interpreter.cpp:29-31): tuning overrides and the limit of
+// kernel-internal waits. 0 = let the library choose.
+struct nncb_options {
+    int conv_tile_n = 0;        // force the N tile of the tensor-core convolution (128, 96, 64, 48 or 32)
+    int conv_wide_patch = 1;    // 0: keep 64-/128-channel stride-1 layers on the im2col form
+    int depthwise_dot = 1;      // 0: the multiply-add form of the 3x3 depthwise kernel
+    int attention_warps = 0;    // force the CTA width of paged attention (4 or 8)
+    int attention_splits = 0;   // force its number of context splits
+    unsigned wait_limit_us = 1000000; // kernel-internal waits give up after this long
+    int debug_withhold_load = 0; // self-test of the give-up path: the convolution's producer leaves out one load
+};
+
 struct nncb_context {
+    nncb_options opt;
     int device = 0;
     cudaStream_t stream = nullptr;
     uint64_t launches = 0;
@@ -43,6 +57,11 @@ int fail(int code, const char *fmt, ...);
 
 // Checks the launch that was just enqueued and counts it.
 int after_launch(nncb_context *ctx, const char *what);
+
+// Raise the dynamic shared-memory limit of this file's kernels on the CURRENT device (the attribute is per
+// device; called for every context that is created).
+int paged_attention_set_attributes();
+int gemv_set_attributes();
 
 inline int conv_out_size(int in, int k, int stride, int dil, int pad_before, int pad_after) {
     return (in + pad_before + pad_after - ((k - 1) * dil + 1)) / stride + 1;

@@ -23,7 +23,6 @@
 // With `splits` > 1 partial (max, sum, unnormalised output) triples go to a scratch buffer and a
 // second small kernel merges them.
 #include "internal.cuh"
-#include <cstdlib>
 #include <cuda_fp16.h>
 
 namespace nncb {
@@ -38,8 +37,11 @@ struct PaArgs {
     float *part_o;  // [B][Hq][splits][64]
     float *part_ml; // [B][Hq][splits][2]
     int B, Hq, Hkv, max_pages, splits;
+    int num_pages;    // pages in the pools: page ids outside [0, num_pages) are never dereferenced
+    int *status;      // the context's status word
     float scale_log2; // scale * log2(e)
 };
+enum { PA_ERR_BAD_INDEX = 202 };
 
 __device__ __forceinline__ uint32_t pa_smem(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, bool valid) {
@@ -81,7 +83,15 @@ paged_attention_decode_kernel(const PaArgs a) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int group = a.Hq / a.Hkv;
-    const int ctx = a.ctx_lens[b];
+    // Lengths and page ids come from device memory the caller filled. A length is clamped to what the
+    // block-table row can describe; a page id outside the pools reads as zeros (the zero-fill path of
+    // rows beyond the context); both record PA_ERR_BAD_INDEX in the context's status word.
+    int ctx = a.ctx_lens[b];
+    if (ctx < 0 || ctx > a.max_pages * PA_PAGE) {
+        if (threadIdx.x == 0)
+            atomicCAS(a.status, 0, (int)PA_ERR_BAD_INDEX);
+        ctx = ctx < 0 ? 0 : a.max_pages * PA_PAGE;
+    }
     const int n_pages = (ctx + PA_PAGE - 1) / PA_PAGE;
     const int pages_per_split = (n_pages + a.splits - 1) / a.splits;
     const int p_begin = split * pages_per_split;
@@ -117,8 +127,12 @@ paged_attention_decode_kernel(const PaArgs a) {
         for (int j = 0; j < 8; j++) {
             const int r = (lane >> 3) + 4 * j; // token row 0..31
             const int page = page0 + (r >> 4);
-            const bool valid = page < p_end && page * PA_PAGE + (r & 15) < ctx;
-            const int pid = valid ? table[page] : 0;
+            bool valid = page < p_end && page * PA_PAGE + (r & 15) < ctx;
+            int pid = valid ? table[page] : 0;
+            if (pid < 0 || pid >= a.num_pages) {
+                atomicCAS(a.status, 0, (int)PA_ERR_BAD_INDEX);
+                valid = false, pid = 0;
+            }
             const size_t off = (((size_t)pid * a.Hkv + kvh) * PA_PAGE + (r & 15)) * PA_D + c * 8;
             cp_async16(ks + pa_off(r, c), a.k_pool + off, valid);
             cp_async16(vs + pa_off(r, c), a.v_pool + off, valid);
@@ -294,8 +308,8 @@ size_t paged_attention_scratch_bytes(int B, int Hq, int splits) {
 // Eight-warp CTAs (one per SM) once the (sequence, kv head) pairs alone fill half the SMs; four-warp CTAs
 // (two per SM) with context splits below that.
 static int paged_attention_pick_warps(const nncb_context *ctx, int B, int Hkv) {
-    if (const char *e = getenv("NNCB_PA_WARPS")) // tuning aid: force the CTA width (4 or 8)
-        return atoi(e) == 8 ? 8 : 4;
+    if (ctx->opt.attention_warps) // tuning override: force the CTA width (4 or 8)
+        return ctx->opt.attention_warps == 8 ? 8 : 4;
     return 2 * B * Hkv >= ctx->sm_count ? 8 : 4;
 }
 
@@ -312,8 +326,8 @@ int paged_attention_pick_splits(const nncb_context *ctx, int B, int Hkv, int max
         s = cap;
     if (s > 16)
         s = 16;
-    if (const char *e = getenv("NNCB_PA_SPLITS")) // tuning aid: force the split count
-        s = atoi(e);
+    if (ctx->opt.attention_splits) // tuning override: force the split count
+        s = ctx->opt.attention_splits;
     return s < 1 ? 1 : s;
 }
 
@@ -327,11 +341,22 @@ int paged_attention_check(int B, int Hq, int Hkv, int head_dim, int page_size, i
     return 0;
 }
 
+int paged_attention_set_attributes() {
+    NNCB_CUDA_TRY(cudaFuncSetAttribute(paged_attention_decode_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       4 * PA_STAGES * 2 * PA_STAGE_BYTES));
+    NNCB_CUDA_TRY(cudaFuncSetAttribute(paged_attention_decode_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       8 * PA_STAGES * 2 * PA_STAGE_BYTES));
+    return 0;
+}
+
 // Launches on ctx->stream. scratch: at least paged_attention_scratch_bytes(B, Hq, splits) bytes when splits > 1.
 int paged_attention_launch(nncb_context *ctx, const void *q, const void *k_pool, const void *v_pool,
                            const int32_t *block_table, const int32_t *ctx_lens, void *out, int B, int Hq, int Hkv,
-                           int max_pages, float scale, int splits, void *scratch) {
+                           int max_pages, int num_pages, float scale, int splits, void *scratch) {
+    if (num_pages <= 0)
+        return fail(-EINVAL, "paged_attention: num_pages must be positive");
     PaArgs a;
+    a.num_pages = num_pages, a.status = ctx->d_status;
     a.q = (const __half *)q, a.k_pool = (const __half *)k_pool, a.v_pool = (const __half *)v_pool;
     a.block_table = block_table, a.ctx_lens = ctx_lens, a.out = (__half *)out;
     a.B = B, a.Hq = Hq, a.Hkv = Hkv, a.max_pages = max_pages, a.splits = splits;
@@ -340,14 +365,6 @@ int paged_attention_launch(nncb_context *ctx, const void *q, const void *k_pool,
     a.part_ml = a.part_o ? a.part_o + (size_t)B * Hq * splits * PA_D : nullptr;
     const int warps = paged_attention_pick_warps(ctx, B, Hkv);
     const size_t smem = (size_t)warps * PA_STAGES * 2 * PA_STAGE_BYTES; // 96 KB or 192 KB
-    static bool attr_set = false;
-    if (!attr_set) {
-        NNCB_CUDA_TRY(cudaFuncSetAttribute(paged_attention_decode_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           4 * PA_STAGES * 2 * PA_STAGE_BYTES));
-        NNCB_CUDA_TRY(cudaFuncSetAttribute(paged_attention_decode_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           8 * PA_STAGES * 2 * PA_STAGE_BYTES));
-        attr_set = true;
-    }
     dim3 grid(splits, Hkv, B);
     if (warps == 8)
         paged_attention_decode_kernel<8><<<grid, 8 * 32, smem, ctx->stream>>>(a);

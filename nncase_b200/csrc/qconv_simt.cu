@@ -441,7 +441,7 @@ int simt_conv_run(nncb_context *ctx, nncb_qconv2d *cv, const uint8_t *x, const u
             const int bt = row_items >= 256 ? 256 : (row_items + 31) / 32 * 32;
             const dim3 grid3((unsigned)(d.n * cv->oh), (unsigned)((row_items + bt - 1) / bt));
             const bool al16 = (reinterpret_cast<uintptr_t>(cv->d_wdp) & 15) == 0;
-            if (cv->d_wdp && cv->d_cdp && al16 && !getenv("NNCB_DW_MAD")) { // (tuning aid: the multiply-add form)
+            if (cv->d_wdp && cv->d_cdp && al16 && ctx->opt.depthwise_dot) { // (tuning override: 0 takes the multiply-add form)
 #define NNCB_DWDP(S_, WS_, ZW_)                                                                                       \
     dw3x3_dp_kernel<S_, WS_, ZW_><<<grid3, bt, 0, ctx->stream>>>(g, x, cv->d_wdp, cv->d_cdp, cv->d_wzp, p, f, res,   \
                                                                  (uint8_t *)y, y2)

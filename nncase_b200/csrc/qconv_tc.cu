@@ -107,6 +107,8 @@ struct TcGeom {
     int kh, kw_cells;              // MODE_PATCH: kernel rows, cells per kernel row
     int cell;                      // MODE_PATCH: bytes per cell (16: unswizzled; 64 / 128: one swizzle row per pixel)
     FastDiv fd_m_tiles, fd_ow, fd_oh, fd_tiles_x, fd_tiles_y;
+    unsigned wait_limit_us;        // waits give up after this long (context option, set per launch)
+    int withhold;                  // self-test of the give-up path: CTA 0 expects bytes that never arrive
 };
 
 struct FastEpi;
@@ -184,8 +186,8 @@ static bool patch_mode_applies(const nncb_conv2d_desc &d) {
 }
 
 // the wide-cell form: padded or not, stride 1, dilation 1, c = 64 or 128, one N tile with resident weights
-static bool patch_wide_applies(const nncb_conv2d_desc &d) {
-    if (getenv("NNCB_NO_WIDE_PATCH")) // tuning aid: keep these layers on the im2col form
+static bool patch_wide_applies(const nncb_conv2d_desc &d, const nncb_options &opt) {
+    if (!opt.conv_wide_patch) // tuning override: keep these layers on the im2col form
         return false;
     if (d.groups != 1 || d.stride_h != 1 || d.stride_w != 1 || d.dil_h != 1 || d.dil_w != 1 || (d.c != 64 && d.c != 128) ||
         d.kh < 2 || d.kw < 2 || d.kh > 4 || d.kw > 4 || d.oc > 128 || d.oc % 16 != 0 || d.has_residual || d.f32_out)
@@ -323,13 +325,15 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
     return t;
 }
 
-// Bounded wait. Returns false when the block is aborting or the wait ran out (about 1 s);
-// in the latter case it records `code` in the status word and raises the abort flag.
+// Bounded wait. Returns false when the block is aborting or the wait ran out (the context's
+// "wait_limit_us", 1 s unless changed; the limit is the word that follows the abort flag in shared
+// memory); in the latter case it records `code` in the status word and raises the abort flag.
 // The first probe is inlined at the call site: the one-thread producer and MMA loops run one
 // dependent instruction at a time, so a call and a timer read per K block would cost more than
 // the K block's loads and MMAs.
 __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code) {
     const uint64_t t0 = globaltimer_ns();
+    const uint64_t limit_ns = 1000ull * reinterpret_cast<volatile const unsigned *>(abort_flag)[1];
     for (uint32_t it = 1;; it++) {
         if (mbar_try(bar, parity))
             return true;
@@ -339,7 +343,7 @@ __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volat
         if ((it & 63) == 0) {
             if (*abort_flag)
                 return false;
-            if (globaltimer_ns() - t0 > 1000000000ull) {
+            if (globaltimer_ns() - t0 > limit_ns) {
                 atomicCAS(status, 0, code);
                 *abort_flag = 1;
                 __threadfence_block();
@@ -522,6 +526,7 @@ struct TcShared {
     uint64_t bar_full[MAX_STAGES], bar_empty[MAX_STAGES], bar_acc_full[2], bar_acc_empty[2], bar_b, bar_res[EPI_WARPS * RES_BUFS];
     uint32_t tmem_base_slot;
     volatile int abort_flag;
+    unsigned wait_limit_us; // must follow abort_flag: mbar_wait_slow reads it through the flag's address
 };
 
 struct StageGeom {
@@ -549,6 +554,7 @@ __device__ __forceinline__ void tc_setup(const TcGeom &g, TcShared &sh, int warp
     using namespace dev;
     if (threadIdx.x == 0) {
         sh.abort_flag = 0;
+        sh.wait_limit_us = g.wait_limit_us;
         for (int s = 0; s < g.stages; s++) {
             mbar_init(smem_u32(&sh.bar_full[s]), 1);
             mbar_init(smem_u32(&sh.bar_empty[s]), 1);
@@ -605,6 +611,8 @@ __device__ __forceinline__ void producer_loop(const TcGeom &g, const StageGeom &
     const int kgroup = g.kgroup;
     const uint32_t bar_full0 = smem_u32(&sh.bar_full[0]), bar_empty0 = smem_u32(&sh.bar_empty[0]);
     uint32_t stage = 0, phase = 0;
+    if (g.withhold && blockIdx.x == 0) // self-test: 16 bytes that no load delivers keep stage 0 from ever filling
+        asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar_full0), "r"(16u) : "memory");
     if (b_res && (int)blockIdx.x < total_tiles) {
         // the whole weight matrix, once
         const uint32_t bar_b = smem_u32(&sh.bar_b);
@@ -1486,7 +1494,119 @@ int reciprocal_division_selftest(nncb_context *ctx, float scale, unsigned long l
     return rc;
 }
 
-static int pick_bn(int oc, long long K) {
+// ------------------------------------------------------------------------------------------------
+// Peak of the kind::i8 tensor pipe, measured: the denominator of every "fraction of int8 peak".
+// One CTA per SM; one thread issues back-to-back tcgen05.mma kind::i8 of M = 128, N = 256, K = 32 on one
+// resident pair of shared-memory operand tiles (128-byte swizzle, pseudo-random bytes) into two
+// alternating TMEM accumulators. No global-memory traffic, no epilogue: nothing but the tensor pipe can
+// bound it. Every `sync` MMAs the thread commits to an mbarrier and waits (bounded) so that the issue
+// queue stays shallow.
+// ------------------------------------------------------------------------------------------------
+struct PeakShared {
+    uint64_t bar;
+    uint32_t tmem_slot;
+    volatile int abort_flag;
+    unsigned wait_limit_us; // must follow abort_flag (read by mbar_wait_slow through the flag's address)
+};
+
+__global__ void __launch_bounds__(128, 1) int8_peak_kernel(uint32_t mma_groups, uint32_t idesc, int *status, unsigned limit_us) {
+    using namespace dev;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) PeakShared sh;
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t a_tile = base, b_tile = base + 128u * 128u; // A: 128 rows x 128 B, B: 256 rows x 128 B
+    for (uint32_t i = threadIdx.x; i < (128u + 256u) * 128u / 4u; i += blockDim.x) {
+        uint32_t v = (i + 1u) * 2654435761u + blockIdx.x * 40503u;
+        v ^= v >> 15;
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(base + i * 4u), "r"(v) : "memory");
+    }
+    fence_async_smem();
+    if (threadIdx.x == 0) {
+        sh.abort_flag = 0;
+        sh.wait_limit_us = limit_us;
+        mbar_init(smem_u32(&sh.bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    const int warp = threadIdx.x >> 5;
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh.tmem_slot)), "r"(512u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem = sh.tmem_slot;
+    if (threadIdx.x == 32) {
+        const Desc da = make_desc(smem_desc(a_tile, 128)), db = make_desc(smem_desc(b_tile, 128));
+        const uint32_t bar = smem_u32(&sh.bar);
+        uint32_t phase = 0;
+        constexpr uint32_t sync_every = 64; // groups of four MMAs between two commits
+        for (uint32_t g = 0; g < mma_groups; g++) {
+            const uint32_t d = tmem + (g & 1u) * 256u;
+            mma_i8(d, da, db, idesc, g > 1);
+            mma_i8(d, da + 2, db + 2, idesc, 1);
+            mma_i8(d, da + 4, db + 4, idesc, 1);
+            mma_i8(d, da + 6, db + 6, idesc, 1);
+            if ((g + 1) % sync_every == 0 || g + 1 == mma_groups) {
+                mma_commit(bar);
+                if (!mbar_wait(bar, phase, &sh.abort_flag, status, ERR_MMA_ACC))
+                    break;
+                phase ^= 1;
+            }
+        }
+    }
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    if (warp == 0)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+}
+
+// Runs the loop `repeats` times (after one warm-up launch), each timed with CUDA events on the context's
+// stream; returns the best and the mean rate in TOP/s (2 operations per multiply-accumulate).
+int int8_peak_selftest(nncb_context *ctx, uint32_t mmas_per_sm, int repeats, int w_signed, double *best_tops, double *mean_tops) {
+    if (mmas_per_sm < 4 || mmas_per_sm > (1u << 24) || repeats < 1 || repeats > 10000)
+        return fail(-EINVAL, "int8 peak self-test: 4 <= mmas_per_sm <= 2^24, 1 <= repeats <= 10000");
+    const uint32_t groups = mmas_per_sm / 4;
+    const uint32_t idesc = (2u << 4) | ((w_signed ? 1u : 0u) << 10) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+    const size_t smem = (128 + 256) * 128 + 1024;
+    // more than half of an SM's shared memory would not be needed, but exactly one CTA (one 512-column TMEM
+    // allocation) per SM is: ask for it explicitly
+    const size_t smem_one_per_sm = 120 * 1024;
+    NNCB_CUDA_TRY(cudaFuncSetAttribute(int8_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_one_per_sm));
+    (void)smem;
+    cudaEvent_t e0, e1;
+    NNCB_CUDA_TRY(cudaEventCreate(&e0));
+    NNCB_CUDA_TRY(cudaEventCreate(&e1));
+    double best = 0, sum = 0;
+    int rc = 0;
+    for (int r = -1; r < repeats && rc == 0; r++) {
+        cudaEventRecord(e0, ctx->stream);
+        int8_peak_kernel<<<ctx->sm_count, 128, smem_one_per_sm, ctx->stream>>>(groups, idesc, ctx->d_status, ctx->opt.wait_limit_us);
+        rc = after_launch(ctx, "int8_peak");
+        cudaEventRecord(e1, ctx->stream);
+        cudaError_t e = cudaEventSynchronize(e1);
+        if (e != cudaSuccess)
+            rc = fail(-EIO, "int8 peak self-test: %s", cudaGetErrorString(e));
+        float ms = 0;
+        cudaEventElapsedTime(&ms, e0, e1);
+        if (r >= 0 && rc == 0 && ms > 0) {
+            const double tops = (double)ctx->sm_count * groups * 4.0 * 2.0 * 128.0 * 256.0 * 32.0 / (ms * 1e-3) / 1e12;
+            best = tops > best ? tops : best;
+            sum += tops;
+        }
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    if (rc == 0) {
+        *best_tops = best;
+        *mean_tops = sum / repeats;
+    }
+    return rc;
+}
+
+static int pick_bn(int oc, long long K, const nncb_options &opt) {
     // N tile width. 128, 96, 64, 48 and 32 are the widths the fast epilogue stages; a layer whose channel
     // count is a multiple of 16 takes the one with the least modelled time per 128-pixel tile row. A tile costs
     // the larger of its epilogue (measured: about 1000 clocks of latency plus 22 per column) and its operand
@@ -1494,8 +1614,8 @@ static int pick_bn(int oc, long long K) {
     // in the fewest tiles, 48 a 144-channel one, wide tiles re-read the activations of a deep layer less often.
     if (oc % 16 != 0)
         return oc >= 128 ? 128 : ((oc + 15) / 16) * 16;
-    if (const char *e = getenv("NNCB_CONV_BN")) { // tuning aid: force the N tile width (128, 96, 64, 48 or 32)
-        const int v = atoi(e);
+    if (opt.conv_tile_n) { // tuning override: force the N tile width (128, 96, 64, 48 or 32)
+        const int v = opt.conv_tile_n;
         if (v == 128 || v == 96 || v == 64 || v == 48 || v == 32)
             return v;
     }
@@ -1520,7 +1640,7 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
     TcGeom &g = tp->g;
     const bool gemm = d.kh == 1 && d.kw == 1 && d.stride_h == 1 && d.stride_w == 1 && d.pad_t == 0 && d.pad_b == 0 &&
                       d.pad_l == 0 && d.pad_r == 0;
-    const bool wide_patch = !gemm && patch_wide_applies(d);
+    const bool wide_patch = !gemm && patch_wide_applies(d, ctx->opt);
     g.mode = gemm ? MODE_GEMM
                   : ((wide_patch || patch_mode_applies(d)) ? MODE_PATCH : (rows_mode_applies(d) ? MODE_ROWS : MODE_IM2COL));
     g.oh = cv->oh, g.ow = cv->ow;
@@ -1530,7 +1650,7 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
     for (int i = 0; i < d.oc && wzp_host; i++)
         any_zw |= wzp_host[i] != 0;
     g.has_xsum = any_zw ? 1 : 0;
-    g.bn = pick_bn(d.oc, (long long)d.kh * d.kw * d.c);
+    g.bn = pick_bn(d.oc, (long long)d.kh * d.kw * d.c, ctx->opt);
     g.bn_mma = g.bn + (any_zw ? 16 : 0);
     g.n_tiles = (d.oc + g.bn - 1) / g.bn;
     g.m_tiles = (g.m_total + 127) / 128;
@@ -1906,6 +2026,8 @@ int tc_conv_run(nncb_context *ctx, nncb_qconv2d *cv, const uint8_t *x, const uin
         NNCB_TRY(make_tmap_a(tp, cv->d, x));
     TcArgs a;
     a.g = tp->g;
+    a.g.wait_limit_us = ctx->opt.wait_limit_us;
+    a.g.withhold = ctx->opt.debug_withhold_load;
     a.p = make_epi(cv);
     a.f = *tp->f;
     a.corr = tp->d_corr;

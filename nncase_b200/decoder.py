@@ -185,10 +185,11 @@ class Decoder:
             check(lib.nncb_rope_kv_append_f16(h, qkv.data_ptr(), q.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(),
                                               positions.data_ptr(), block_table.data_ptr(), lw["k_pool"].data_ptr(),
                                               lw["v_pool"].data_ptr(), B, self.hq, self.hkv, cfg.head_dim, cfg.page,
-                                              block_table.shape[1]))
+                                              block_table.shape[1], self.cos.shape[0], lw["k_pool"].shape[0]))
             check(lib.nncb_paged_attention_decode(h, q.data_ptr(), lw["k_pool"].data_ptr(), lw["v_pool"].data_ptr(),
                                                   block_table.data_ptr(), ctx_lens.data_ptr(), attn.data_ptr(), B,
                                                   self.hq, self.hkv, cfg.head_dim, cfg.page, block_table.shape[1],
+                                                  lw["k_pool"].shape[0],
                                                   C.c_float(1.0 / np.sqrt(cfg.head_dim)), self.ws.data_ptr(),
                                                   self.ws.numel()))
             self._gemv(attn, lw["o_w"], lw["o_s"], None, proj)

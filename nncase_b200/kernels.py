@@ -81,6 +81,15 @@ class Context:
     def synchronize(self):
         check(self._lib.nncb_synchronize(self._h))
 
+    def set_option(self, name, value):
+        """Per-context option by name (see nncb_context_set_option): wait limit, tuning overrides."""
+        check(self._lib.nncb_context_set_option(self._h, name.encode(), int(value)))
+
+    def get_option(self, name):
+        v = C.c_int64()
+        check(self._lib.nncb_context_get_option(self._h, name.encode(), C.byref(v)))
+        return v.value
+
     def check_status(self):
         check(self._lib.nncb_check_device_status(self._h))
 
@@ -282,7 +291,7 @@ class Context:
         out = torch.empty_like(q)
         check(self._lib.nncb_paged_attention_decode(
             self._h, q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), block_table.data_ptr(),
-            context_lens.data_ptr(), out.data_ptr(), b, hq, hkv, d, page, max_pages, scale,
+            context_lens.data_ptr(), out.data_ptr(), b, hq, hkv, d, page, max_pages, k_pool.shape[0], scale,
             workspace.data_ptr() if workspace is not None else None,
             workspace.numel() if workspace is not None else 0))
         return out

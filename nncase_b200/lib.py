@@ -95,13 +95,16 @@ SIGNATURES = {
     "nncb_gemv_w8a16": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I]),
     "nncb_gemv_w8a16_swiglu": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I]),
     "nncb_add_rmsnorm_f16": (_I, [_VP, _VP, _VP, _VP, _VP, _I, _I, _F]),
-    "nncb_rope_kv_append_f16": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I]),
+    "nncb_rope_kv_append_f16": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _I]),
     "nncb_swiglu_f16": (_I, [_VP, _VP, _VP, _I, _I]),
     "nncb_embedding_f16": (_I, [_VP, _VP, _VP, _VP, _I, _I, _I]),
     "nncb_paged_attention_workspace_size": (_I, [_VP, _I, _I, _I, _I, _I, _I, C.POINTER(_SZ)]),
-    "nncb_paged_attention_decode": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _F, _VP, _SZ]),
-    "nncb_paged_attention_decode_noalloc": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _F]),
+    "nncb_paged_attention_decode": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _F, _VP, _SZ]),
+    "nncb_paged_attention_decode_noalloc": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _F]),
+    "nncb_context_set_option": (_I, [_VP, C.c_char_p, C.c_int64]),
+    "nncb_context_get_option": (_I, [_VP, C.c_char_p, C.POINTER(C.c_int64)]),
     "nncb_selftest_reciprocal_division": (_I, [_VP, _F, C.c_uint64, C.c_uint64, C.POINTER(C.c_uint64)]),
+    "nncb_selftest_int8_peak": (_I, [_VP, C.c_uint32, _I, _I, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "nncb_qconv2d_host": (_I, [_VP, C.POINTER(Conv2dDesc), _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP]),
 }
 

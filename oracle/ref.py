@@ -15,8 +15,16 @@ _PATH = os.path.join(_HERE, "_ref", "libnncase_ref.so")
 _LIB = None
 
 
-def build(ref_root="/root/reference"):
-    if os.path.isdir(ref_root):
+def reference_root():
+    """The nncase checkout to compile from: $NNCASE_REF, else a `reference` directory beside this
+    repository; None when neither exists."""
+    cand = os.environ.get("NNCASE_REF") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    return cand if os.path.isdir(os.path.join(cand, "src", "Native")) else None
+
+
+def build(ref_root=None):
+    ref_root = ref_root or reference_root()
+    if ref_root:
         subprocess.check_call(["make", "-s", "-j8", "-C", _HERE, "ref", "REF=" + ref_root])
 
 

@@ -38,13 +38,16 @@ def test_ragged_contexts(ctx, hq, hkv):
     check(ctx, make_cache(5, len(lens), hq, hkv, lens))
 
 
-@pytest.mark.parametrize("warps", ["4", "8"])
-def test_both_cta_widths(ctx, monkeypatch, warps):
+@pytest.mark.parametrize("warps", [4, 8])
+def test_both_cta_widths(ctx, warps):
     """The four-warp (context splits, merge kernel) and the eight-warp (one CTA per sequence and kv head)
     forms of the kernel on the same ragged batch."""
-    monkeypatch.setenv("NNCB_PA_WARPS", warps)
-    lens = [1, 15, 16, 17, 33, 100, 511, 512, 513, 700, 0, 2048, 31, 32, 1000, 255]
-    check(ctx, make_cache(15, len(lens), 14, 2, lens))
+    ctx.set_option("attention.warps", warps)
+    try:
+        lens = [1, 15, 16, 17, 33, 100, 511, 512, 513, 700, 0, 2048, 31, 32, 1000, 255]
+        check(ctx, make_cache(15, len(lens), 14, 2, lens))
+    finally:
+        ctx.set_option("attention.warps", 0)
 
 
 def test_many_sequences_take_the_wide_form(ctx):

@@ -273,3 +273,77 @@ def test_depthwise_conv_residual_and_second_output(ctx, qo):
                            res=torch.from_numpy(res).cuda(), residual=(rq, aq), y2=(yq2, 0.0, float("inf")))
     ctx.check_status()
     assert np.array_equal(got.cpu().numpy(), want) and np.array_equal(got2.cpu().numpy(), want2)
+
+
+@pytest.mark.parametrize("variant", ["plain", "residual"])
+def test_bounded_wait_gives_up_and_the_context_stays_usable(ctx, qo, variant):
+    """Every wait inside the tensor-core kernel has a time limit. With the limit shortened to 2 ms and the
+    loader of one CTA told to expect bytes that no load delivers ("debug.withhold_load"), that CTA's waits run
+    out: the kernel returns by itself, nncb_check_device_status reports -ETIMEDOUT with a role code once and
+    clears the status word, and the same convolution on the same context is bit-exact afterwards."""
+    n, h, w, c, oc = 2, 28, 28, 64, 256
+    xq, zx, wq, zw, mult, bias, oqp = make_case(77, n, h, w, c, oc, 1, 1)
+    x = torch.from_numpy(xq).cuda()
+    kw, want = {}, qo.qconv2d_u8(xq, wq, zw, mult, bias, zx, oqp.scale, oqp.zero_point)
+    if variant == "residual":
+        rq, aq = QuantParam(117, 0.05), QuantParam(125, 0.06)
+        res = np.random.default_rng(78).integers(0, 256, (n, h, w, oc), dtype=np.uint8)
+        kw = dict(residual=(rq, aq))
+        want = qo.qadd_u8(want, res, oqp.scale, oqp.zero_point, rq.scale, rq.zero_point, aq.scale, aq.zero_point)
+        res_d = torch.from_numpy(res).cuda()
+    plan = ctx.conv2d_plan(tuple(x.shape), wq, zw, mult, bias, zx, oqp, force_path=L.PATH_TC, **kw)
+    run = (lambda: plan(x, res_d)) if variant == "residual" else (lambda: plan(x))
+    assert np.array_equal(run().cpu().numpy(), want)
+    ctx.check_status()
+    ctx.set_option("wait_limit_us", 2000)
+    ctx.set_option("debug.withhold_load", 1)
+    try:
+        run()
+        with pytest.raises(L.NncbError) as e:
+            ctx.check_status()
+    finally:
+        ctx.set_option("debug.withhold_load", 0)
+        ctx.set_option("wait_limit_us", 1000000)
+    assert e.value.code == -110, e.value            # -ETIMEDOUT
+    assert any(f"role code {c_}" in str(e.value) for c_ in (101, 102, 103, 104, 105)), e.value
+    ctx.check_status()                              # the status word was cleared by the read
+    assert np.array_equal(run().cpu().numpy(), want)
+    ctx.check_status()
+    plan.close()
+
+
+def test_options_reject_unknown_names_and_bad_values(ctx):
+    with pytest.raises(L.NncbError) as e:
+        ctx.set_option("no.such.option", 1)
+    assert e.value.code == -22
+    with pytest.raises(L.NncbError):
+        ctx.set_option("wait_limit_us", 0)
+    assert ctx.get_option("wait_limit_us") == 1000000 and ctx.get_option("conv.wide_patch") == 1
+
+
+def test_two_devices_in_one_process():
+    """Kernels that need more than 48 KB of dynamic shared memory raise their limit per device: contexts on
+    two GPUs of one process both run paged attention and the w8a16 MatMul (no peer memory involved)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from nncase_b200.kernels import Context
+    outs = []
+    for dev in (0, 1):
+        with torch.cuda.device(dev):
+            c = Context(dev)
+            g = torch.Generator(device=f"cuda:{dev}").manual_seed(5)
+            k = torch.randn((40, 2, 16, 64), device=f"cuda:{dev}", generator=g, dtype=torch.float16)
+            q = torch.randn((4, 14, 64), device=f"cuda:{dev}", generator=g, dtype=torch.float16)
+            table = torch.arange(40, device=f"cuda:{dev}", dtype=torch.int32).reshape(4, 10)
+            lens = torch.tensor([160, 33, 1, 100], device=f"cuda:{dev}", dtype=torch.int32)
+            out = c.paged_attention_decode(q, k, k, table, lens)
+            xh = torch.randn((8, 4864), device=f"cuda:{dev}", generator=g, dtype=torch.float16)
+            wt = torch.randint(-127, 128, (896, 4864), device=f"cuda:{dev}", generator=g, dtype=torch.int8)
+            sc = torch.full((896,), 0.01, device=f"cuda:{dev}", dtype=torch.float16)
+            y = torch.empty((8, 896), device=f"cuda:{dev}", dtype=torch.float16)
+            L.check(c._lib.nncb_gemv_w8a16(c._h, xh.data_ptr(), wt.data_ptr(), sc.data_ptr(), None, None, y.data_ptr(),
+                                           8, 896, 4864))
+            c.check_status()
+            outs.append((out.cpu(), y.cpu()))
+            c.close()
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])

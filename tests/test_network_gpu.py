@@ -99,3 +99,58 @@ def test_yolov8s_every_tensor(ctx):
     for name, t in zip(program["outputs"], outs):
         assert np.array_equal(t.cpu().numpy(), tens[name])
     fn.close()
+
+
+# ---- the configurations the throughput numbers are quoted on ------------------------------------------
+# Whole batches at the benchmark sizes; images are independent, so the oracle replays a few of them (first,
+# middle, last: large batches take other tile counts, grid-stride trip counts and index ranges than small
+# ones) and every tensor of those images must be bit-identical.
+def _sampled_parity(ctx, program, x, idx):
+    n = x.shape[0]
+    fn = CudaFunction(program, n, ctx)
+    out = fn.invoke(torch.from_numpy(x).to(ctx.device))
+    ctx.check_status()
+    idx = sorted(set(i % n for i in idx))
+    want, tens = oprog.run_program(program, np.ascontiguousarray(x[idx]))
+    sel = torch.tensor(idx, device=ctx.device)
+    checked = 0
+    for name, ref_t in tens.items():
+        got = fn.tensor(name).index_select(0, sel).cpu().numpy()
+        bad = int((got != ref_t).sum())
+        assert bad == 0, f"batch {n}, tensor {name}: {bad} of {ref_t.size} elements differ"
+        checked += 1
+    assert np.array_equal(out.index_select(0, sel).cpu().numpy(), want)
+    fn.close()
+    del fn
+    torch.cuda.empty_cache()
+    return checked
+
+
+@pytest.mark.parametrize("n", [1, 512])
+def test_resnet50v2_benchmark_configuration(ctx, n):
+    """ResNet-50 v2, 16 calibration samples, N = 1 and N = 512 (the benchmarked batch)."""
+    graph = networks.resnet50v2(1003)
+    cal = [np.random.default_rng(3003 + i).normal(0, 1, (1, 3, 224, 224)).astype(np.float32) for i in range(16)]
+    program = builder.build_program(graph, cal, device=ctx.device)
+    x = np.random.default_rng(2003).normal(0, 1, (n, 3, 224, 224)).astype(np.float32)
+    assert _sampled_parity(ctx, program, x, [0, n // 2 - 1, n - 1]) == len(program["tensors"])
+
+
+@pytest.mark.parametrize("n", [1, 256])
+def test_mobilenetv2_benchmark_configuration(ctx, n):
+    """MobileNetV2-1.0, NHWC input uniform[0,1] normalised to mean 0.5 / std 0.5, 16 calibration images."""
+    graph = networks.mobilenetv2(1002)
+    cal = [(np.random.default_rng(3002 + i).uniform(0, 1, (1, 224, 224, 3)).astype(np.float32) - 0.5) / 0.5
+           for i in range(16)]
+    program = builder.build_program(graph, cal, device=ctx.device)
+    x = (np.random.default_rng(2002).uniform(0, 1, (n, 224, 224, 3)).astype(np.float32) - 0.5) / 0.5
+    assert _sampled_parity(ctx, program, x, [0, n // 2 - 1, n - 1]) == len(program["tensors"])
+
+
+def test_yolov8s_benchmark_configuration(ctx):
+    """YOLOv8s at 640 x 640, N = 64, 8 calibration samples; two images through the oracle."""
+    graph = networks.yolov8s(1004, image=640)
+    cal = [np.random.default_rng(3004 + i).uniform(0, 1, (1, 3, 640, 640)).astype(np.float32) for i in range(8)]
+    program = builder.build_program(graph, cal, device=ctx.device)
+    x = np.random.default_rng(2004).uniform(0, 1, (64, 3, 640, 640)).astype(np.float32)
+    assert _sampled_parity(ctx, program, x, [0, 63]) == len(program["tensors"])

@@ -55,6 +55,19 @@ def test_dequantize_u8(ctx, qo, n):
     assert np.array_equal(got, qo.dequantize_u8(q, 0.014035294, 88))
 
 
+def test_dequantize_i16(ctx):
+    """(q - zp) * scale on int16 (reference/dequantize.cpp:29-59 instantiates it for int16 as well); both
+    operations are exact-or-correctly-rounded f32, so numpy float32 arithmetic is the truth."""
+    q = np.random.default_rng(8).integers(-32768, 32768, 70001).astype(np.int16)
+    q[:4] = (-32768, 32767, 0, 7)
+    got = ctx.dequantize(torch.from_numpy(q), QuantParam(7, 0.01)).cpu().numpy()
+    want = (q.astype(np.float32) - np.float32(7)) * np.float32(0.01)
+    assert got.dtype == np.float32 and np.array_equal(got, want)
+    # round trip through quantize is the identity on in-range values
+    back = ctx.quantize(torch.from_numpy(want), QuantParam(7, 0.01), torch.int16).cpu().numpy()
+    assert np.array_equal(back, q)
+
+
 def test_dequantize_i8(ctx, qo):
     q = np.random.default_rng(1).integers(-128, 128, 50001, dtype=np.int8)
     got = ctx.dequantize(torch.from_numpy(q), QuantParam(-3, 0.02)).cpu().numpy()

@@ -37,7 +37,7 @@ def _noalloc(ctx, q, k, v, table, lens):
     out = torch.empty_like(q)
     L.check(ctx._lib.nncb_paged_attention_decode_noalloc(
         ctx._h, q.data_ptr(), k.data_ptr(), v.data_ptr(), table.data_ptr(), lens.data_ptr(), out.data_ptr(), b, hq,
-        k.shape[1], d, k.shape[2], table.shape[1], C.c_float(1.0 / np.sqrt(d))))
+        k.shape[1], d, k.shape[2], table.shape[1], k.shape[0], C.c_float(1.0 / np.sqrt(d))))
     return out
 
 
@@ -53,21 +53,24 @@ def test_noalloc_matches_regular_entry_point_twice(ctx):
         assert float((got - want).abs().max()) <= TOL * rng
 
 
-def test_noalloc_rejects_problems_beyond_the_built_in_scratch(ctx, monkeypatch):
+def test_noalloc_rejects_problems_beyond_the_built_in_scratch(ctx):
     # The one-wave split policy never asks for more than about 625 KiB on a 148-SM part, so the limit is
     # reached through the library's split-count override: 64 x 16 heads x 8 splits x 264 bytes = 2112 KiB.
-    monkeypatch.setenv("NNCB_PA_SPLITS", "8")
-    b, hq, hkv, pages = 64, 16, 2, 128
-    q = torch.zeros((b, hq, 64), dtype=torch.float16, device="cuda")
-    k = torch.zeros((4, hkv, 16, 64), dtype=torch.float16, device="cuda")
-    table = torch.zeros((b, pages), dtype=torch.int32, device="cuda")
-    lens = torch.ones(b, dtype=torch.int32, device="cuda")
-    need = C.c_size_t()
-    L.check(ctx._lib.nncb_paged_attention_workspace_size(ctx._h, b, hq, hkv, 64, 16, pages, C.byref(need)))
-    assert need.value > (768 << 10), "the split policy changed: pick a shape that exceeds the built-in scratch"
-    with pytest.raises(L.NncbError) as e:
-        _noalloc(ctx, q, k, k, table, lens)
-    assert e.value.code == -7 and "786432" in str(e.value)
-    # the regular entry point takes the same problem with a caller-provided workspace
-    out = ctx.paged_attention_decode(q, k, k, table, lens)
-    assert out.shape == q.shape
+    ctx.set_option("attention.splits", 8)
+    try:
+        b, hq, hkv, pages = 64, 16, 2, 128
+        q = torch.zeros((b, hq, 64), dtype=torch.float16, device="cuda")
+        k = torch.zeros((4, hkv, 16, 64), dtype=torch.float16, device="cuda")
+        table = torch.zeros((b, pages), dtype=torch.int32, device="cuda")
+        lens = torch.ones(b, dtype=torch.int32, device="cuda")
+        need = C.c_size_t()
+        L.check(ctx._lib.nncb_paged_attention_workspace_size(ctx._h, b, hq, hkv, 64, 16, pages, C.byref(need)))
+        assert need.value > (768 << 10), "the split policy changed: pick a shape that exceeds the built-in scratch"
+        with pytest.raises(L.NncbError) as e:
+            _noalloc(ctx, q, k, k, table, lens)
+        assert e.value.code == -7 and "786432" in str(e.value)
+        # the regular entry point takes the same problem with a caller-provided workspace
+        out = ctx.paged_attention_decode(q, k, k, table, lens)
+        assert out.shape == q.shape
+    finally:
+        ctx.set_option("attention.splits", 0)
