@@ -2,19 +2,24 @@
 """Benchmark of the quantized-inference hot path: u8/u8 ResNet-50 v2 images/s on B200.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--batch B]
-                  [--w-quant uint8|int8] [--layers]
+                  [--w-quant uint8|int8] [--layers] [--no-secondary]
 
 One step = one forward pass of the whole quantized network over one batch of synthetic images
-per GPU (seeded N(0,1) inputs standing in for ImageNet; random He-normal weights, BN folded).
-For N > 1 launch under torchrun, one rank per GPU; the batch is sharded by images with no
-collective on the data path (weak scaling: every GPU runs `--batch` images).
+(seeded N(0,1) inputs standing in for ImageNet; random He-normal weights, BN folded). The
+configuration the metric is quoted on is a GLOBAL batch of 512 images: on N GPUs (launch under
+torchrun, one rank per GPU) every rank takes 512 / N of them, with no collective on the data path
+(strong scaling). The weak-scaling figure (512 images on every GPU) is reported beside it as
+`weak`.
 
-Prints ONE JSON line (rank 0). `value` is device-resident throughput, `e2e` the same metric
-through the public host-buffer call (pinned f32 input -> H2D -> kernels -> D2H logits, copies
-double-buffered inside the timed region). `--impl reference` times the reference's own CPU
-kernels (dequantize -> conv2d f32 -> quantize, ...) on the host cores on a bounded sample.
+Prints ONE JSON line (rank 0). `value` is device-resident throughput, `e2e` the same metric through
+the public host-buffer call (pinned f32 input -> H2D -> kernels -> D2H logits, every step's copies
+inside the timed region), `parity` the comparison of this very run's tensors with the CPU oracle,
+`secondary` the other paths of the library measured in the same run (paged attention, a decode
+step, the streaming kernels, single-image latency). `--impl reference` times the reference's own
+CPU kernels running the same quantized network on the host cores.
 """
 import argparse
+import ctypes as C
 import json
 import os
 import subprocess
@@ -32,6 +37,13 @@ SEED_W, SEED_X, SEED_CAL = 1000 + CONFIG_ID, 2000 + CONFIG_ID, 3000 + CONFIG_ID
 METRIC = "u8/u8 ResNet-50 images/s"
 UNIT = "images/s"
 
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of the convolution launches of one step PER
+# IMAGE, from a one-pass ncu capture at 128 images (tensors larger than L2, about 2 GB on the device; see
+# profiles/dram_traffic_tc_conv_resnet50v2.md). Traffic grows in proportion to the batch above that size
+# (the full-size capture of the same kernels gave 17.18 GB at 512 images = 33.6 MB per image), so the
+# bench scales this figure by its batch. Keyed by weight type; None = not captured.
+MEASURED_DRAM_BYTES_PER_IMAGE = {"uint8": 17.181e9 / 512}
+
 
 def peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -40,16 +52,6 @@ def peaks():
         return dict(hbm_gbs=d["hbm_gbs"], bf16_burst=d["bf16_tflops"], bf16_sustained=d["bf16_tflops_sustained"],
                     source="measured")
     return dict(hbm_gbs=6650.0, bf16_burst=1590.0, bf16_sustained=1400.0, source="fallback")
-
-
-# DRAM bytes (read + write) of all convolution launches of one step, from one ncu capture of this
-# workload (dram__bytes_read.sum + dram__bytes_write.sum, summed over the tcgen05 convolution
-# kernels of a step); None until a capture at that size exists. Keyed by (images per GPU, weights).
-MEASURED_DRAM_BYTES_PER_STEP = {(512, "uint8"): 17.181e9}
-
-
-def measured_traffic(batch, w_quant):
-    return MEASURED_DRAM_BYTES_PER_STEP.get((batch, w_quant))
 
 
 class ClockSampler:
@@ -93,211 +95,163 @@ class ClockSampler:
                     samples=len(sm))
 
 
-def build_network(batch_for_calib_device, w_quant):
+def build_network(device, w_quant):
     from nncase_b200 import builder, networks
     graph = networks.resnet50v2(SEED_W)
     cal = [np.random.default_rng(SEED_CAL + i).normal(0, 1, (1, 3, 224, 224)).astype(np.float32) for i in range(16)]
-    program = builder.build_program(graph, cal, w_quant, device=batch_for_calib_device)
+    program = builder.build_program(graph, cal, w_quant, device=device)
     macs, per_layer, _ = networks.graph_macs(graph)
     return graph, program, macs, dict(per_layer)
 
 
 # ---------------------------------------------------------------------------------------------
-# reference arm: the reference's own CPU kernels on the host cores
+# CPU arm: the reference's own kernels running the quantized network on the host cores
 # ---------------------------------------------------------------------------------------------
-def cpu_reference_sample(graph, program, macs_total, seconds_target=20.0, threads=None):
-    """Times the reference's CPU implementation of the path on a bounded sample of the workload.
-
-    Sample: one image; the stem, the max-pool, every `stride`-th convolution layer (with its
-    residual add / ReLU requantisation) run through the reference's kernels exactly as its cpu
-    target executes a quantized convolution: dequantize -> conv2d(f32, fused clamp) -> quantize.
-    Layers are independent jobs spread over all host cores (the reference kernel itself is
-    single-threaded). images/s is extrapolated by the sample's share of the network's MACs.
-    """
+def cpu_reference_images(program, images, threads):
+    """Runs `images` synthetic images, one after the other, through the WHOLE quantized network on the
+    reference's own CPU kernels (oracle/_ref: every operator dequantize -> float kernel -> quantize, the
+    way its cpu target executes a quantized graph), each convolution split over `threads` host threads by
+    output channel. Falls back to the integer C port where the reference's library is not available.
+    Returns (images per second, kind, seconds)."""
     from oracle import program as oprog
-    from oracle import qoracle, ref
-    threads = threads or os.cpu_count() or 1
+    from oracle import ref
     x = np.random.default_rng(SEED_X).normal(0, 1, (1, 3, 224, 224)).astype(np.float32)
-    _, tens = oprog.run_program(program, x, threads=threads)  # inputs of every layer, from the oracle
-    convs = [op for op in program["ops"] if op["op"] == "conv" and not op.get("f32_out")]
     use_ref = ref.available()
-    # reference f32 conv runs at ~0.3 GMAC/s per core: choose how many layers fit the time target
-    est_rate = 0.3e9 if use_ref else 3e9
-    layer_macs = []
-    for op in convs:
-        n, oh, ow, oc = tens[op["out"]].shape
-        layer_macs.append(oh * ow * oc * op["w"].shape[1] * op["w"].shape[2] * op["w"].shape[3])
-    budget = est_rate * seconds_target * threads
-    order = np.argsort(layer_macs)[::-1]
-    stride = max(1, int(np.ceil(sum(layer_macs) / budget)))
-    chosen = sorted(order[::stride].tolist())
-    T = program["tensors"]
-
-    job_seconds = []
-
-    def job(i):
-        t_job = time.perf_counter()
-        op = convs[i]
-        xq, xqp, cq = tens[op["in"]], T[op["in"]]["qp"], op["conv_qp"]
-        if use_ref:
-            sw = op["mult"] / np.float32(xqp.scale)
-            ref.qconv2d_composite_u8(xq, op["w"], op["w_zp"], sw, op["bias"], xqp.scale, xqp.zero_point, cq.scale,
-                                     cq.zero_point, op["stride"], op["pad"], op["dil"], op["groups"], op["clamp"])
-        else:
-            qoracle.qconv2d_u8(xq, op["w"], op["w_zp"], op["mult"], op["bias"], xqp.zero_point, cq.scale,
-                               cq.zero_point, op["stride"], op["pad"], op["dil"], op["groups"], op["clamp"])
-        job_seconds.append(time.perf_counter() - t_job)
-
-    if not use_ref:
-        qoracle.lib().qo_set_threads(1)
     t0 = time.perf_counter()
-    from concurrent.futures import ThreadPoolExecutor
-    with ThreadPoolExecutor(threads) as ex:
-        list(ex.map(job, chosen))
+    for _ in range(images):
+        if use_ref:
+            from oracle import ref_program
+            ref_program.run_program(program, x, threads=threads)
+        else:
+            oprog.run_program(program, x, threads=threads)
     dt = time.perf_counter() - t0
-    sample_macs = sum(layer_macs[i] for i in chosen)
-    macs_total = sum(layer_macs)  # same counting as the sample (the FC layer, 0.05 % of the MACs, is left out)
-    # core-seconds the sample took (each layer ran on one core) -> core-seconds per image at
-    # full-network MACs -> images/s with every core busy on its own image
-    core_seconds = sum(job_seconds)
-    img_per_s = threads / (core_seconds * macs_total / sample_macs)
-    return dict(value=img_per_s, unit=UNIT, cores=threads, kind="reference" if use_ref else "port",
-                sample=f"1 image, {len(chosen)} of {len(convs)} conv layers ({sample_macs / macs_total:.1%} of the "
-                       f"network's MACs) through dequantize->conv2d(f32)->quantize, {dt:.1f} s wall, "
-                       f"extrapolated by MACs"), dt
+    return images / dt, ("reference" if use_ref else "port"), dt
+
+
+def cpu_baseline(program, seconds_target, threads=None):
+    threads = threads or os.cpu_count() or 1
+    rate, kind, dt = cpu_reference_images(program, 1, threads)      # also tells how long an image takes
+    n = int(max(1, min(8, seconds_target / max(dt, 1e-3) - 1)))
+    if n >= 1 and dt * (n + 1) <= 2.0 * seconds_target:
+        rate, kind, dt = cpu_reference_images(program, n, threads)
+    else:
+        n = 1
+    return dict(value=rate, unit=UNIT, cores=threads, kind=kind,
+                sample=f"{n} image(s) through all {sum(1 for o in program['ops'] if o['op'] == 'conv')} convolutions and "
+                       f"every other operator of the quantized network on the "
+                       f"{'reference kernels (dequantize -> float kernel -> quantize per operator)' if kind == 'reference' else 'integer C port'}"
+                       f", {dt:.1f} s wall, convolutions split over {threads} threads by output channel")
 
 
 def run_reference(args):
-    import torch
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    graph, program, macs, _ = build_network("cpu", args.w_quant)
-    vals, last = [], None
+    _, program, _, _ = build_network("cpu", args.w_quant)
+    threads = os.cpu_count() or 1
     steps = max(1, args.steps)
-    per_step = max(3.0, min(20.0, 150.0 / (steps + args.warmup)))
-    for i in range(args.warmup + steps):
-        cb, dt = cpu_reference_sample(graph, program, macs, per_step)
+    vals, kind, secs = [], "port", 0.0
+    for i in range(args.warmup + steps):        # one step = one image through the whole network
+        r, kind, dt = cpu_reference_images(program, 1, threads)
         if i >= args.warmup:
-            vals.append(cb["value"])
-            last = cb
-    v = float(np.mean(vals))
-    last["value"] = v
+            vals.append(r)
+            secs += dt
+    v = float(len(vals) / sum(1.0 / r for r in vals))
+    cb = dict(value=v, unit=UNIT, cores=threads, kind=kind,
+              sample=f"{steps} timed steps of one image each through the whole quantized network on the "
+                     f"{'reference kernels' if kind == 'reference' else 'integer C port'}, {secs:.1f} s wall")
     line = dict(metric=METRIC, value=v, unit=UNIT, n_gpus=args.gpus, steps=steps, warmup=args.warmup,
-                ms_per_step=1000.0 * args.batch / v, higher_is_better=True, scaling="weak", vs_baseline=None,
+                ms_per_step=1000.0 / v, higher_is_better=True, scaling="strong", vs_baseline=None,
                 dtype="f32", data="synthetic", impl="reference",
-                config=dict(workload="resnet50v2_u8u8", batch_per_gpu=args.batch, w_quant=args.w_quant),
-                cpu_baseline=last, e2e=dict(value=v, unit=UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+                config=dict(workload="resnet50v2_u8u8", global_batch=args.batch, images_per_step=1,
+                            w_quant=args.w_quant, note="a step is a bounded sample of the workload: one image"),
+                cpu_baseline=cb, e2e=dict(value=v, unit=UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0))
     print(json.dumps(line))
 
 
 # ---------------------------------------------------------------------------------------------
 # our arm
 # ---------------------------------------------------------------------------------------------
-def run_ours(args):
-    import torch
-    import torch.distributed as dist
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py: no CUDA device; the hot path has no CPU fallback")
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    from nncase_b200 import lib as L
-    from nncase_b200.kernels import Context
-    from nncase_b200.runtime import CudaFunction
+def _events(torch):
+    return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
-    dev = torch.device("cuda", local)
-    graph, program, macs, layer_macs = build_network(dev, args.w_quant)
-    ctx = Context(local)
-    fn = CudaFunction(program, args.batch, ctx)
-    B = args.batch
-    g = torch.Generator(device=dev).manual_seed(SEED_X + rank)
-    x = torch.randn((B, 3, 224, 224), device=dev, generator=g)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize(dev)
-
-    # -------- device-resident throughput --------
-    for _ in range(max(3, args.warmup)):
+def time_device(torch, fn, x, steps, barrier):
+    a, b = _events(torch)
+    barrier()
+    a.record()
+    for _ in range(steps):
         fn.invoke(x)
-    ctx.check_status()
-    launches_per_step = fn.launches_per_call
+    b.record()
     barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    l0 = ctx.launches
-    ev0.record()
-    for _ in range(args.steps):
-        fn.invoke(x)
-    ev1.record()
+    return a.elapsed_time(b)
+
+
+def time_e2e(torch, fn, xh, oh, steps, barrier):
+    """K batches through the public host-buffer call (CudaFunction.submit_host / drain): pinned f32 input ->
+    H2D -> kernels -> D2H logits, double-buffered inside the library, every copy inside the timed region."""
+    dev = fn.ctx.device
+    a, b = _events(torch)
     barrier()
-    ms = ev0.elapsed_time(ev1)
-    gpu_launches = ctx.launches - l0
-    ctx.check_status()
-
-    # -------- end to end through the host-buffer call --------
-    xh = [torch.empty((B, 3, 224, 224), dtype=torch.float32).pin_memory() for _ in range(2)]
-    for t in xh:
-        t.copy_(x)
-    oh = [torch.empty((B, 1, 1, 1000), dtype=torch.float32).pin_memory() for _ in range(2)]
-    copy_stream, comp_stream = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-    xd = [torch.empty_like(x) for _ in range(2)]
-    e2e_steps = args.steps
-
-    def e2e_loop(steps):
-        # double buffered: the H2D copy of step i+1 overlaps the kernels of step i; every
-        # step's input copy and result read-back are inside the timed region
-        copied = [torch.cuda.Event() for _ in range(2)]
-        done = [torch.cuda.Event() for _ in range(2)]
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with torch.cuda.stream(copy_stream):
-            start.record()
-            xd[0].copy_(xh[0], non_blocking=True)
-            copied[0].record()
-        for i in range(steps):
-            b = i & 1
-            if i + 1 < steps:
-                with torch.cuda.stream(copy_stream):
-                    if i >= 1:
-                        copy_stream.wait_event(done[b ^ 1])
-                    xd[b ^ 1].copy_(xh[b ^ 1], non_blocking=True)
-                    copied[b ^ 1].record()
-            with torch.cuda.stream(comp_stream):
-                comp_stream.wait_event(copied[b])
-                out = fn.invoke(xd[b])
-                oh[b].copy_(out, non_blocking=True)
-                done[b].record()
-        with torch.cuda.stream(comp_stream):
-            comp_stream.wait_stream(copy_stream)
-            end.record()
-        comp_stream.synchronize()
-        copy_stream.synchronize()
-        return start.elapsed_time(end)
-
-    e2e_loop(3)
+    cur = torch.cuda.current_stream(dev)
+    a.record(cur)
+    p = fn._pipeline()
+    p["copy"].wait_event(a)
+    p["comp"].wait_event(a)
+    for i in range(steps):
+        fn.submit_host(xh[i & 1], oh[i & 1])
+    cur.wait_stream(p["comp"])
+    cur.wait_stream(p["copy"])
+    b.record(cur)
+    fn.drain()
     barrier()
-    e2e_ms = e2e_loop(e2e_steps)
-    barrier()
-    ctx.use_current_stream()
-    clocks = sampler.stop() if rank == 0 else None
+    return a.elapsed_time(b)
 
-    # -------- per-layer timing of the dominant kernel (tcgen05 conv) for the roofline --------
-    tc_ops, tc_ms, tc_bytes, rows = 0.0, 0.0, 0.0, []
-    reps = 5
+
+def time_h2d_only(torch, dev, xh, steps, barrier):
+    """The bare host-to-device copies of the same pinned input buffers, all ranks at once: the ceiling the
+    end-to-end number cannot exceed."""
+    xd = torch.empty(xh[0].shape, dtype=torch.float32, device=dev)
+    a, b = _events(torch)
+    barrier()
+    a.record()
+    for i in range(steps):
+        xd.copy_(xh[i & 1], non_blocking=True)
+    b.record()
+    barrier()
+    return a.elapsed_time(b)
+
+
+def parity_check(torch, fn, program, x, idx):
+    """This run's tensors against the CPU oracle on a few images of the benchmark batch (outside every timed
+    region). Images are independent, so the oracle replays only the chosen ones; every tensor of the
+    program is compared byte for byte (the f32 logits exactly, too)."""
+    from oracle import program as oprog
+    n = x.shape[0]
+    idx = sorted(set(int(i) % n for i in idx))
+    sel = torch.tensor(idx, device=x.device)
+    fn.invoke(x)
+    _, tens = oprog.run_program(program, x.index_select(0, sel).cpu().numpy(), threads=os.cpu_count() or 8)
+    bad, elems = 0, 0
+    for name, ref_t in tens.items():
+        got = fn.tensor(name).index_select(0, sel).cpu().numpy()
+        bad += int((got != ref_t).sum())
+        elems += ref_t.size
+    return dict(images=idx, tensors=len(tens), elements=elems, mismatches=bad,
+                against="oracle/qoracle.c replay of the same program on the same inputs")
+
+
+def conv_rows(torch, fn, layer_macs, B, reps=5):
+    """Live CUDA-event time, operations and algorithmic bytes of every convolution launch of a step."""
+    dev = fn.ctx.device
+    rows = []
     for st in fn.steps:
         if st[0] != "conv":
             continue
         op, plan = st[1], st[2]
         res = fn.buffers[op["res"]] if op.get("res") else None
         y2 = fn.buffers[op["y2"]] if op.get("y2") else None
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a, b = _events(torch)
         plan(fn.buffers[op["in"]], res, fn.buffers[op["out"]], y2)
         torch.cuda.synchronize(dev)
         a.record()
@@ -313,64 +267,263 @@ def run_ours(args):
         nbytes = (fn.buffers[op["in"]].numel() + out_el * (4 if op.get("f32_out") else 1) +
                   (out_el if res is not None else 0) + (out_el if y2 is not None else 0) + op["w"].size)
         rows.append((op["name"], plan.path, t, ops, nbytes))
-        if plan.path == L.PATH_TC:
-            tc_ops += ops
-            tc_ms += t
-            tc_bytes += nbytes
+    return rows
+
+
+def int8_peak(ctx):
+    """The kind::i8 tensor-pipe peak of this GPU, measured now (library self-test): burst = best of ten
+    1 ms launches, sustained = mean of 300 launches back to back (power-capped)."""
+    from nncase_b200 import lib as L
+    best, mean = C.c_double(), C.c_double()
+    L.check(ctx._lib.nncb_selftest_int8_peak(ctx._h, 8192, 10, 0, C.byref(best), C.byref(mean)))
+    burst = best.value
+    L.check(ctx._lib.nncb_selftest_int8_peak(ctx._h, 8192, 300, 0, C.byref(best), C.byref(mean)))
+    return dict(burst=burst, sustained=mean.value)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the hot path has no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from nncase_b200 import lib as L
+    from nncase_b200 import sharding
+    from nncase_b200.kernels import Context
+    from nncase_b200.runtime import CudaFunction
+
+    dev = torch.device("cuda", local)
+    graph, program, macs, layer_macs = build_network(dev, args.w_quant)
+    ctx = Context(local)
+    G = args.batch                                   # global batch of the configuration
+    start, B = sharding.shard_range(G, world, rank)  # this rank's images (strong scaling)
+    if B * world != G:
+        raise SystemExit(f"bench.py: the global batch {G} must divide over {world} ranks")
+    fn = CudaFunction(program, B, ctx)
+    g = torch.Generator(device=dev).manual_seed(SEED_X + rank)
+    x = torch.randn((B, 3, 224, 224), device=dev, generator=g)
+    steps, warm = args.steps, max(3, args.warmup)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    # -------- device-resident throughput --------
+    for _ in range(warm):
+        fn.invoke(x)
+    ctx.check_status()
+    launches_per_step = fn.launches_per_call
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    l0 = ctx.launches
+    ms = time_device(torch, fn, x, steps, barrier)
+    gpu_launches = ctx.launches - l0
     ctx.check_status()
 
+    # -------- end to end through the library's host-buffer call --------
+    xh = [torch.empty((B, 3, 224, 224), dtype=torch.float32).pin_memory() for _ in range(2)]
+    for t in xh:
+        t.copy_(x)
+    oh = [torch.empty((B, 1, 1, 1000), dtype=torch.float32).pin_memory() for _ in range(2)]
+    time_e2e(torch, fn, xh, oh, 3, barrier)
+    e2e_ms = time_e2e(torch, fn, xh, oh, steps, barrier)
+    clocks = sampler.stop() if rank == 0 else None
+    h2d_ms = time_h2d_only(torch, dev, xh, steps, barrier)
+    ctx.check_status()
+
+    # -------- per-layer timing of the dominant kernel (tcgen05 conv) for the roofline --------
+    rows = conv_rows(torch, fn, layer_macs, B)
+    tc = [r for r in rows if r[1] == L.PATH_TC]
+    tc_ms, tc_ops, tc_bytes = sum(r[2] for r in tc), sum(r[3] for r in tc), sum(r[4] for r in tc)
+    ctx.check_status()
+
+    # -------- weak-scaling figure: the full 512 images on every GPU --------
+    weak = None
+    if world > 1:
+        fn_w = CudaFunction(program, G, ctx)
+        xw = torch.randn((G, 3, 224, 224), device=dev, generator=g)
+        for _ in range(3):
+            fn_w.invoke(xw)
+        ms_w = time_device(torch, fn_w, xw, steps, barrier)
+        ms_w = sharding.max_over_ranks([ms_w], dev)[0]
+        weak = dict(value=world * G * steps / (ms_w / 1000.0), unit=UNIT, images_per_gpu=G, ms_per_step=ms_w / steps,
+                    scaling="weak")
+        fn_w.close()
+        del fn_w, xw
+        torch.cuda.empty_cache()
+
     # max over ranks of the device-measured times, sum of the launch counters
-    from nncase_b200 import sharding
-    ms, e2e_ms = sharding.max_over_ranks([ms, e2e_ms], dev)
+    ms, e2e_ms, h2d_ms = sharding.max_over_ranks([ms, e2e_ms, h2d_ms], dev)
     gpu_launches = sharding.sum_over_ranks([gpu_launches], dev)[0]
     if rank != 0:
         if world > 1:
+            dist.barrier()
             dist.destroy_process_group()
         return
 
+    parity = parity_check(torch, fn, program, x, [0, B // 2 - 1, B - 1])
     pk = peaks()
-    value = world * B * args.steps / (ms / 1000.0)
-    e2e_value = world * B * e2e_steps / (e2e_ms / 1000.0)
-    int8_peak = 2.0 * pk["bf16_burst"]  # dense int8 = 2x the measured dense bf16 (int8 itself is not in the peaks file)
+    i8 = int8_peak(ctx)
+    value = G * steps / (ms / 1000.0)
+    e2e_value = G * steps / (e2e_ms / 1000.0)
+    int8_burst = i8["burst"]
     achieved = tc_ops / (tc_ms / 1000.0) / 1e12 if tc_ms > 0 else 0.0
     # The convolution launches of one step move tc_bytes and do tc_ops: their ratio (operations per
     # byte) lies below the ridge point int8 peak / HBM peak, so HBM bandwidth is the roof that bounds
     # the kernel on this workload; the tensor-pipe figures are kept beside it.
     gbs = tc_bytes / (tc_ms / 1000.0) / 1e9 if tc_ms > 0 else 0.0
     intensity = tc_ops / tc_bytes if tc_bytes else 0.0
-    ridge = int8_peak * 1e12 / (pk["hbm_gbs"] * 1e9)
+    ridge = int8_burst * 1e12 / (pk["hbm_gbs"] * 1e9)
     hbm_bound = intensity < ridge
+    per_image = MEASURED_DRAM_BYTES_PER_IMAGE.get(args.w_quant)
     line = dict(
-        metric=METRIC, value=value, unit=UNIT, n_gpus=world, steps=args.steps, warmup=max(3, args.warmup),
-        ms_per_step=ms / args.steps, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="u8",
+        metric=METRIC, value=value, unit=UNIT, n_gpus=world, steps=steps, warmup=warm,
+        ms_per_step=ms / steps, higher_is_better=True, scaling="strong", vs_baseline=None, dtype="u8",
         data="synthetic", impl="ours",
-        config=dict(workload="resnet50v2_u8u8", batch_per_gpu=B, global_batch=B * world, w_quant=args.w_quant,
+        config=dict(workload="resnet50v2_u8u8", global_batch=G, batch_per_gpu=B, w_quant=args.w_quant,
                     input="f32 NCHW [B,3,224,224] N(0,1)", l2="inputs and activations larger than L2 (no flush)",
                     parallelism=f"batch-sharded x{world}, no collective"),
-        e2e=dict(value=e2e_value, unit=UNIT, h2d_bytes_per_step=B * 3 * 224 * 224 * 4, d2h_bytes_per_step=B * 1000 * 4),
+        e2e=dict(value=e2e_value, unit=UNIT, h2d_bytes_per_step=G * 3 * 224 * 224 * 4, d2h_bytes_per_step=G * 1000 * 4,
+                 call="CudaFunction.submit_host / drain (pinned host buffers, two device staging buffers, two streams)",
+                 h2d_ceiling_images_s=G * steps / (h2d_ms / 1000.0),
+                 h2d_gbs_per_gpu=B * 3 * 224 * 224 * 4 * steps / (h2d_ms / 1000.0) / 1e9),
         gpu_launches=gpu_launches, launches_per_step=launches_per_step,
-        clocks=clocks,
+        clocks=clocks, parity=parity,
         roofline=dict(bound="hbm" if hbm_bound else "tensor", kernel="tc_conv_fast_kernel (all convolution launches of a step)",
-                      achieved=gbs if hbm_bound else achieved, peak=pk["hbm_gbs"] if hbm_bound else int8_peak,
+                      achieved=gbs if hbm_bound else achieved, peak=pk["hbm_gbs"] if hbm_bound else int8_burst,
                       unit="GB/s" if hbm_bound else "TFLOP/s",
-                      frac=(gbs / pk["hbm_gbs"]) if hbm_bound else achieved / int8_peak,
-                      traffic=measured_traffic(B, args.w_quant),
+                      frac=(gbs / pk["hbm_gbs"]) if hbm_bound else achieved / int8_burst,
+                      traffic=per_image * B if per_image else None,
+                      traffic_source="ncu dram__bytes_read.sum + dram__bytes_write.sum of the convolution launches, "
+                                     "per image from a capture at a smaller batch, scaled by this batch",
                       algorithmic_bytes_per_step=tc_bytes, ops_per_byte=intensity, ridge_ops_per_byte=ridge,
-                      peak_source=f"{pk['source']} peaks: HBM copy bandwidth; int8 dense taken as 2 x bf16 burst",
-                      tensor=dict(achieved=achieved, peak=int8_peak, unit="TFLOP/s", frac=achieved / int8_peak),
-                      tc_ms_per_step=tc_ms, tc_share_of_step=tc_ms / (ms / args.steps),
-                      whole_step_tops=2.0 * macs * B / (ms / args.steps / 1000.0) / 1e12),
+                      peak_source=f"{pk['source']} HBM copy bandwidth; int8 tensor peak measured in this run "
+                                  f"(nncb_selftest_int8_peak)",
+                      tensor=dict(achieved=achieved, peak=int8_burst, peak_sustained=i8["sustained"], unit="TFLOP/s",
+                                  frac=achieved / int8_burst),
+                      tc_ms_per_step=tc_ms, tc_share_of_step=tc_ms / (ms / steps),
+                      whole_step_tops=2.0 * macs * B / (ms / steps / 1000.0) / 1e12),
     )
+    if weak is not None:
+        line["weak"] = weak
+    if world == 1 and not args.no_secondary:
+        line["secondary"] = secondary(torch, ctx, args, pk)
     if world == 1 and not args.no_cpu_baseline:
-        cb, _ = cpu_reference_sample(graph, program, macs, 15.0)
-        line["cpu_baseline"] = cb
+        line["cpu_baseline"] = cpu_baseline(program, 15.0)
     if args.layers:
         for r in rows:
             print(f"# {r[0]:10s} path={r[1]} {r[2] * 1000:9.1f} us  {r[3] / (r[2] / 1000) / 1e12:8.1f} TOP/s "
                   f"{r[4] / (r[2] / 1000) / 1e9:8.1f} GB/s", file=sys.stderr)
     print(json.dumps(line))
+    sys.stdout.flush()
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------------------------
+# secondary measurements (same run, after the headline): the other paths of the library
+# ---------------------------------------------------------------------------------------------
+def stream_kernels(torch, ctx, pk, reps=10):
+    """Quantize, dequantize, binary add and max-pool at the sizes they have in ResNet-50 at 512 images:
+    achieved HBM GB/s over their algorithmic bytes (inputs + outputs at their stored types)."""
+    from nncase_b200 import lib as L
+    from nncase_b200.kernels import QuantParam
+    dev, lib, h = ctx.device, ctx._lib, ctx._h
+    n_in = 512 * 3 * 224 * 224           # the network input
+    n_act = 512 * 56 * 56 * 256          # a stage-1 block output
+    qp = QuantParam(120, 0.03)
+    xf = torch.randn(n_in, device=dev)
+    xq = torch.empty(n_in, dtype=torch.uint8, device=dev)
+    a = torch.randint(0, 256, (n_act,), dtype=torch.uint8, device=dev)
+    b = torch.randint(0, 256, (n_act,), dtype=torch.uint8, device=dev)
+    y = torch.empty_like(a)
+    yf = torch.empty(n_in, device=dev)
+    pool_in = torch.randint(0, 256, (512, 112, 112, 64), dtype=torch.uint8, device=dev)
+    pool_out = torch.empty((512, 56, 56, 64), dtype=torch.uint8, device=dev)
+    s2d_in = torch.randn((512, 3, 224, 224), device=dev)
+    s2d_out = torch.empty((512, 115, 115, 16), dtype=torch.uint8, device=dev)
+    cases = {
+        "quantize_f32_u8": (lambda: L.check(lib.nncb_quantize(h, xf.data_ptr(), xq.data_ptr(), n_in, qp.scale, qp.zero_point, L.U8)),
+                            5 * n_in),
+        "dequantize_u8_f32": (lambda: L.check(lib.nncb_dequantize(h, xq.data_ptr(), yf.data_ptr(), n_in, qp.scale, qp.zero_point, L.U8)),
+                              5 * n_in),
+        "qadd_u8": (lambda: L.check(lib.nncb_qadd_u8(h, a.data_ptr(), b.data_ptr(), y.data_ptr(), n_act, 0.05, 117, 0.04, 125,
+                                                     0.06, 121)), 3 * n_act),
+        "maxpool_3x3s2_u8": (lambda: L.check(lib.nncb_maxpool_u8(h, pool_in.data_ptr(), pool_out.data_ptr(), 512, 112, 112, 64,
+                                                                 3, 3, 2, 2, 1, 1, 1, 1, 120)),
+                             pool_in.numel() + pool_out.numel()),
+        "quantize_input_stage_s2d": (lambda: L.check(lib.nncb_quantize_to_s2d_padded_u8(
+            h, s2d_in.data_ptr(), 0, s2d_out.data_ptr(), 512, 3, 224, 224, 16, 2, 1, 2, 1, qp.scale, qp.zero_point)),
+            s2d_in.numel() * 4 + s2d_out.numel()),
+    }
+    out = {}
+    for name, (call, nbytes) in cases.items():
+        for _ in range(3):
+            call()
+        e0, e1 = _events(torch)
+        torch.cuda.synchronize(dev)
+        e0.record()
+        for _ in range(reps):
+            call()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        us = e0.elapsed_time(e1) / reps * 1000.0
+        gbs = nbytes / (us * 1e-6) / 1e9
+        out[name] = dict(us=us, algorithmic_bytes=nbytes, gbs=gbs, frac_of_hbm_peak=gbs / pk["hbm_gbs"])
+    ctx.check_status()
+    return out
+
+
+def latency_one_image(torch, ctx, which):
+    """Single-image latency of a whole network replayed as one CUDA graph (capture / replay of CudaFunction)."""
+    from nncase_b200 import builder, networks
+    from nncase_b200.runtime import CudaFunction
+    dev = ctx.device
+    if which == "resnet50v2":
+        graph, shape = networks.resnet50v2(SEED_W), (1, 3, 224, 224)
+        cal = [np.random.default_rng(SEED_CAL + i).normal(0, 1, shape).astype(np.float32) for i in range(16)]
+        x = torch.randn(shape, device=dev)
+    else:
+        graph, shape = networks.mobilenetv2(1002), (1, 224, 224, 3)
+        cal = [(np.random.default_rng(3002 + i).uniform(0, 1, shape).astype(np.float32) - 0.5) / 0.5 for i in range(16)]
+        x = (torch.rand(shape, device=dev) - 0.5) / 0.5
+    program = builder.build_program(graph, cal, device=dev)
+    fn = CudaFunction(program, 1, ctx)
+    fn.capture(x)
+    for _ in range(5):
+        fn.replay()
+    e0, e1 = _events(torch)
+    torch.cuda.synchronize(dev)
+    reps = 50
+    e0.record()
+    for _ in range(reps):
+        fn.replay()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    ctx.check_status()
+    us = e0.elapsed_time(e1) / reps * 1000.0
+    launches = fn.launches_per_call
+    fn.close()
+    return dict(us_per_image=us, images_per_s=1e6 / us, launches=launches, mode="CUDA graph replay, batch 1")
+
+
+def secondary(torch, ctx, args, pk):
+    out = {}
+    out["stream_kernels"] = stream_kernels(torch, ctx, pk)
+    out["paged_attention"] = measure_attention(torch, ctx, pk, steps=20, warmup=3)
+    out["decode"] = measure_decode(torch, ctx, pk, steps=20, warmup=3, world=1, rank=0)
+    out["latency_batch1"] = dict(resnet50v2=latency_one_image(torch, ctx, "resnet50v2"),
+                                 mobilenetv2=latency_one_image(torch, ctx, "mobilenetv2"))
+    torch.cuda.empty_cache()
+    return out
 
 
 def run_layer(args):
@@ -399,7 +552,7 @@ def run_layer(args):
     for _ in range(max(1, args.warmup)):
         plan(fn.buffers[op["in"]], res, fn.buffers[op["out"]], y2)
     torch.cuda.synchronize()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a, b = _events(torch)
     a.record()
     for _ in range(args.steps):
         plan(fn.buffers[op["in"]], res, fn.buffers[op["out"]], y2)
@@ -416,15 +569,12 @@ def run_layer(args):
                           gbs=(in_bytes + out_bytes + op["w"].size) / (ms / 1000) / 1e9)))
 
 
-def run_attention(args):
-    """Secondary measurement: paged-attention decode at the Qwen2-0.5B decode shape (batch 64, context
-    2048, 14 query / 2 kv heads, head_dim 64, 16-token f16 pages, random block-table permutation).
-    One step = the attention of all 24 layers, each over its own KV pool (1.61 GB of K/V per step,
-    larger than L2), reported as achieved HBM GB/s over the K/V bytes referenced."""
-    import torch
-    from nncase_b200.kernels import Context
-    dev = torch.device("cuda", 0)
-    ctx = Context(0)
+def measure_attention(torch, ctx, pk, steps, warmup):
+    """Paged-attention decode at the Qwen2-0.5B decode shape (batch 64, context 2048, 14 query / 2 kv heads,
+    head_dim 64, 16-token f16 pages, random block-table permutation). One step = the attention of all 24
+    layers, each over its own KV pool (1.61 GB of K/V per step, larger than L2), replayed as one CUDA graph;
+    achieved HBM GB/s over the K/V bytes referenced."""
+    dev = ctx.device
     B, Hq, Hkv, D, page, n_ctx, layers = 64, 14, 2, 64, 16, 2048, 24
     pages = B * n_ctx // page
     g = torch.Generator(device=dev).manual_seed(2005)
@@ -433,69 +583,61 @@ def run_attention(args):
     q = torch.randn((B, Hq, D), device=dev, generator=g, dtype=torch.float16)
     table = torch.randperm(pages, device=dev, generator=g).to(torch.int32).reshape(B, n_ctx // page).contiguous()
     lens = torch.full((B,), n_ctx, dtype=torch.int32, device=dev)
-    need = 1 << 22
-    ws = torch.empty(need, dtype=torch.uint8, device=dev)
+    ws = torch.empty(1 << 22, dtype=torch.uint8, device=dev)
 
     def step():
         for k, v in pools:
             ctx.paged_attention_decode(q, k, v, table, lens, workspace=ws)
 
-    for _ in range(max(3, args.warmup)):
+    for _ in range(max(3, warmup)):
         step()
-    torch.cuda.synchronize()
-    # a decode step is launch-bound from Python (24 short kernels): replay it as one CUDA graph
+    torch.cuda.synchronize(dev)
     l0 = ctx.launches
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
     graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
-        ctx.use_current_stream()
-        step()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph):
+            ctx.use_current_stream()
+            step()
     ctx.use_current_stream()
     launches_per_step = ctx.launches - l0
     graph.replay()
-    torch.cuda.synchronize()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(dev)
+    a, b = _events(torch)
     a.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         graph.replay()
     b.record()
-    torch.cuda.synchronize()
+    torch.cuda.synchronize(dev)
     ctx.check_status()
-    ms = a.elapsed_time(b) / args.steps
+    ms = a.elapsed_time(b) / steps
     kv_bytes = layers * B * n_ctx * Hkv * D * 2 * 2
-    pk = peaks()
     gbs = kv_bytes / (ms / 1000) / 1e9
-    print(json.dumps(dict(metric="paged-attention decode HBM GB/s", value=gbs, unit="GB/s", ms_per_step=ms,
-                          steps=args.steps, kv_bytes_per_step=kv_bytes, gpu_launches=launches_per_step * args.steps,
-                          config=dict(workload="qwen2_0.5b_decode_attention", batch=B, context=n_ctx, q_heads=Hq,
-                                      kv_heads=Hkv, head_dim=D, page=page, layers=layers),
-                          roofline=dict(bound="hbm", achieved=gbs, peak=pk["hbm_gbs"], unit="GB/s",
-                                        frac=gbs / pk["hbm_gbs"], peak_source=pk["source"]))))
+    del graph, pools
+    torch.cuda.empty_cache()
+    return dict(metric="paged-attention decode HBM GB/s", value=gbs, unit="GB/s", ms_per_step=ms, steps=steps,
+                kv_bytes_per_step=kv_bytes, launches_per_step=launches_per_step,
+                config=dict(workload="qwen2_0.5b_decode_attention", batch=B, context=n_ctx, q_heads=Hq, kv_heads=Hkv,
+                            head_dim=D, page=page, layers=layers),
+                roofline=dict(bound="hbm", achieved=gbs, peak=pk["hbm_gbs"], unit="GB/s", frac=gbs / pk["hbm_gbs"],
+                              peak_source=pk["source"]))
 
 
-def run_decode(args):
-    """Secondary measurement: one decode step of the Qwen2-0.5B-shaped model (24 layers, hidden 896,
-    14/2 heads, SwiGLU 4864, vocabulary 151936, i8 weights, f16 activations, paged f16 KV cache) at
-    batch 64 and context 2048, tensor parallel over the launched ranks (NCCL all-reduce after the o
-    and down projections). The step is replayed as one CUDA graph. Reports tokens/s and the HBM
-    bytes a step must read (KV pages referenced + weights) over the measured time."""
-    import torch
+def measure_decode(torch, ctx, pk, steps, warmup, world, rank):
+    """One decode step of the Qwen2-0.5B-shaped model (24 layers, hidden 896, 14/2 heads, SwiGLU 4864,
+    vocabulary 151936, i8 weights, f16 activations, paged f16 KV cache) at batch 64 and context 2048, tensor
+    parallel over `world` ranks, replayed as one CUDA graph. Tokens/s and the HBM bytes a step must read
+    (KV pages referenced + weights) over the measured time."""
     import torch.distributed as dist
     from nncase_b200 import decoder as D
     from nncase_b200 import sharding
-    from nncase_b200.kernels import Context
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    dev = ctx.device
     cfg = D.DecoderConfig()
     B, n_ctx = 64, 2048
     weights = D.make_weights(cfg, 1005)
     max_pages = n_ctx // cfg.page + 1
     num_pages = B * max_pages
-    ctx = Context(local)
     dec = D.Decoder(cfg, weights, B, num_pages, ctx=ctx, world=world, rank=rank)
     g = torch.Generator(device=dev).manual_seed(2005)
     for lw in dec.layers:
@@ -504,9 +646,9 @@ def run_decode(args):
     table = torch.randperm(num_pages, device=dev, generator=g).to(torch.int32).reshape(B, max_pages).contiguous()
     ids = torch.randint(0, cfg.vocab, (B,), device=dev, generator=g, dtype=torch.int32)
     pos = torch.full((B,), n_ctx - 1, dtype=torch.int32, device=dev)
-    for _ in range(max(3, args.warmup)):
+    for _ in range(max(3, warmup)):
         dec.step(ids, pos, table)
-    torch.cuda.synchronize()
+    torch.cuda.synchronize(dev)
     l0 = ctx.launches
     side = torch.cuda.Stream(dev)
     side.wait_stream(torch.cuda.current_stream(dev))
@@ -518,39 +660,60 @@ def run_decode(args):
     ctx.use_current_stream()
     launches_per_step = ctx.launches - l0
     graph.replay()
-    torch.cuda.synchronize()
+    torch.cuda.synchronize(dev)
     if world > 1:
         dist.barrier()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a, b = _events(torch)
     a.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         graph.replay()
     b.record()
-    torch.cuda.synchronize()
+    torch.cuda.synchronize(dev)
     if world > 1:
         dist.barrier()
-    ms = sharding.max_over_ranks([a.elapsed_time(b) / args.steps], dev)[0]
+    ms = sharding.max_over_ranks([a.elapsed_time(b) / steps], dev)[0]
     ctx.check_status()
-    if rank == 0:
-        kv = cfg.layers * B * n_ctx * cfg.kv_heads * cfg.head_dim * 2 * 2
-        H, nq, nkv = cfg.hidden, cfg.q_heads * cfg.head_dim, cfg.kv_heads * cfg.head_dim
-        wbytes = cfg.layers * ((nq + 2 * nkv) * H + H * nq + 2 * cfg.inter * H + H * cfg.inter) + cfg.vocab * H
-        pk = peaks()
-        gbs = (kv + wbytes) / world / (ms / 1000) / 1e9  # per GPU: each rank reads its share
-        print(json.dumps(dict(metric="Qwen2-0.5B-shape decode tokens/s", value=B / (ms / 1000), unit="tokens/s",
-                              n_gpus=world, ms_per_step=ms, steps=args.steps, launches_per_step=launches_per_step,
-                              config=dict(workload="qwen2_0.5b_decode", batch=B, context=n_ctx, layers=cfg.layers,
-                                          parallelism=f"tp{world}", weights="i8 per-channel, f16 scales",
-                                          kv="f16, 16-token pages"),
-                              bytes_per_step=dict(kv=kv, weights=wbytes),
-                              roofline=dict(bound="hbm", achieved=gbs, peak=pk["hbm_gbs"], unit="GB/s per GPU",
-                                            frac=gbs / pk["hbm_gbs"], peak_source=pk["source"]))))
-    # A CUDA graph that holds captured NCCL kernels keeps the communicator busy: tearing the process
-    # group down while it is alive can block forever. Drop the graph, drain the device, line the ranks
-    # up and leave without the NCCL teardown.
-    sys.stdout.flush()
+    kv = cfg.layers * B * n_ctx * cfg.kv_heads * cfg.head_dim * 2 * 2
+    H, nq, nkv = cfg.hidden, cfg.q_heads * cfg.head_dim, cfg.kv_heads * cfg.head_dim
+    wbytes = cfg.layers * ((nq + 2 * nkv) * H + H * nq + 2 * cfg.inter * H + H * cfg.inter) + cfg.vocab * H
+    gbs = (kv + wbytes) / world / (ms / 1000) / 1e9  # per GPU: each rank reads its share
+    res = dict(metric="Qwen2-0.5B-shape decode tokens/s", value=B / (ms / 1000), unit="tokens/s", n_gpus=world,
+               ms_per_step=ms, steps=steps, launches_per_step=launches_per_step,
+               config=dict(workload="qwen2_0.5b_decode", batch=B, context=n_ctx, layers=cfg.layers,
+                           parallelism=dec.parallelism, weights="i8 per-channel, f16 scales", kv="f16, 16-token pages"),
+               bytes_per_step=dict(kv=kv, weights=wbytes),
+               roofline=dict(bound="hbm", achieved=gbs, peak=pk["hbm_gbs"], unit="GB/s per GPU", frac=gbs / pk["hbm_gbs"],
+                             peak_source=pk["source"]))
     del graph
-    torch.cuda.synchronize()
+    torch.cuda.synchronize(dev)
+    return res
+
+
+def run_attention(args):
+    import torch
+    from nncase_b200.kernels import Context
+    ctx = Context(0)
+    print(json.dumps(measure_attention(torch, ctx, peaks(), args.steps, args.warmup)))
+
+
+def run_decode(args):
+    import torch
+    import torch.distributed as dist
+    from nncase_b200.kernels import Context
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    ctx = Context(local)
+    res = measure_decode(torch, ctx, peaks(), args.steps, args.warmup, world, rank)
+    if rank == 0:
+        print(json.dumps(res))
+    # A CUDA graph that held captured NCCL kernels kept the communicator busy: the graph is dropped inside
+    # measure_decode, the device drained; line the ranks up and leave without the NCCL teardown.
+    sys.stdout.flush()
     if world > 1:
         dist.barrier()
         torch.cuda.synchronize()
@@ -563,13 +726,14 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=512, help="images per GPU per step")
+    ap.add_argument("--batch", type=int, default=512, help="global batch: images per step over all GPUs")
     ap.add_argument("--w-quant", default="uint8", choices=["uint8", "int8"])
     ap.add_argument("--layers", action="store_true", help="print per-layer timings to stderr")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the secondary measurements (attention, decode, ...)")
     ap.add_argument("--layer", default=None, help="time only this conv layer (profiling aid)")
-    ap.add_argument("--attention", action="store_true", help="secondary metric: paged-attention decode GB/s")
-    ap.add_argument("--decode", action="store_true", help="secondary metric: decoder step tokens/s (tensor parallel under torchrun)")
+    ap.add_argument("--attention", action="store_true", help="only the paged-attention decode measurement")
+    ap.add_argument("--decode", action="store_true", help="only the decoder step (tensor parallel under torchrun)")
     args = ap.parse_args()
     if args.decode:
         run_decode(args)

@@ -331,24 +331,30 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 // The first probe is inlined at the call site: the one-thread producer and MMA loops run one
 // dependent instruction at a time, so a call and a timer read per K block would cost more than
 // the K block's loads and MMAs.
+// try_wait with a suspend-time hint: the thread sleeps in hardware until the phase completes or `ns`
+// nanoseconds have passed, instead of coming back to spend issue slots on another probe
+__device__ __forceinline__ bool mbar_try_suspend(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok)
+                 : "r"(bar), "r"(parity), "r"(ns)
+                 : "memory");
+    return ok != 0;
+}
 __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code) {
     const uint64_t t0 = globaltimer_ns();
     const uint64_t limit_ns = 1000ull * reinterpret_cast<volatile const unsigned *>(abort_flag)[1];
     for (uint32_t it = 1;; it++) {
-        if (mbar_try(bar, parity))
+        // a role that is ahead of the others sleeps on the barrier instead of spending issue slots on probes
+        if (mbar_try_suspend(bar, parity, 20000u))
             return true;
-        // a role that is ahead of the others backs off instead of spending issue slots on probes
-        if (it > 4)
-            __nanosleep(it > 32 ? 256 : 64);
-        if ((it & 63) == 0) {
-            if (*abort_flag)
-                return false;
-            if (globaltimer_ns() - t0 > limit_ns) {
-                atomicCAS(status, 0, code);
-                *abort_flag = 1;
-                __threadfence_block();
-                return false;
-            }
+        if (*abort_flag)
+            return false;
+        if (globaltimer_ns() - t0 > limit_ns) {
+            atomicCAS(status, 0, code);
+            *abort_flag = 1;
+            __threadfence_block();
+            return false;
         }
     }
 }
@@ -1644,6 +1650,7 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
     g.mode = gemm ? MODE_GEMM
                   : ((wide_patch || patch_mode_applies(d)) ? MODE_PATCH : (rows_mode_applies(d) ? MODE_ROWS : MODE_IM2COL));
     g.oh = cv->oh, g.ow = cv->ow;
+    g.wait_limit_us = 1000000, g.withhold = 0;
     g.m_total = d.n * cv->oh * cv->ow;
     g.oc = d.oc;
     bool any_zw = false;

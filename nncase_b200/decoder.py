@@ -116,6 +116,7 @@ class Decoder:
 
     def __init__(self, cfg, weights, max_batch, num_pages, ctx=None, device=0, world=1, rank=0, group=None):
         self.cfg, self.world, self.rank, self.group = cfg, world, rank, group
+        self.parallelism = f"tp{world}"
         self.ctx = ctx or Context(device)
         dev = self.ctx.device
         w = shard_weights(cfg, weights, world, rank)

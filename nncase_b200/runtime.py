@@ -200,6 +200,55 @@ class CudaFunction:
         torch.cuda.current_stream(self.ctx.device).synchronize()
         return res
 
+    # ---- pipelined host-buffer calls -------------------------------------------------------
+    # A caller that feeds batch after batch from host memory does not want invoke_host's
+    # copy-in / run / copy-out / wait per batch: submit_host() queues one batch and returns at once.
+    # Two device staging buffers and two streams overlap the host-to-device copy of batch i+1 with
+    # the kernels of batch i; results land in the caller's host buffer, valid after drain() (or after
+    # the event submit_host returns has completed).
+    def _pipeline(self):
+        if getattr(self, "_pipe", None) is None:
+            dev = self.ctx.device
+            in_t = self.program["tensors"][self.program["input"]]
+            self._pipe = dict(copy=torch.cuda.Stream(dev), comp=torch.cuda.Stream(dev), xd=[None, None],
+                              copied=[torch.cuda.Event(), torch.cuda.Event()],
+                              done=[torch.cuda.Event(), torch.cuda.Event()], n=0)
+        return self._pipe
+
+    def submit_host(self, x_host, out_host):
+        """Queue one batch: x_host (f32, pinned torch tensor of the planned input shape) -> out_host (pinned
+        torch tensor shaped like the program's output). Returns the event that marks out_host valid."""
+        if not (x_host.is_pinned() and out_host.is_pinned()):
+            raise NncbError(-22, "submit_host: both host tensors must be pinned (torch.Tensor.pin_memory)")
+        if x_host.shape[0] != self.batch or x_host.dtype != torch.float32 or not x_host.is_contiguous():
+            raise NncbError(-22, "submit_host: input must be a contiguous f32 tensor of the planned batch")
+        p = self._pipeline()
+        b = p["n"] & 1
+        if p["xd"][b] is None or p["xd"][b].shape != x_host.shape:
+            p["xd"][b] = torch.empty(x_host.shape, dtype=torch.float32, device=self.ctx.device)
+        with torch.cuda.stream(p["copy"]):
+            if p["n"] >= 2:
+                p["copy"].wait_event(p["done"][b])     # the kernels that read this staging buffer two batches ago
+            p["xd"][b].copy_(x_host, non_blocking=True)
+            p["copied"][b].record()
+        with torch.cuda.stream(p["comp"]):
+            p["comp"].wait_event(p["copied"][b])
+            self.ctx.use_current_stream()
+            before = self.ctx.launches
+            out = self._run(p["xd"][b])
+            self.launches_per_call = self.ctx.launches - before
+            out_host.copy_(out, non_blocking=True)
+            p["done"][b].record()
+        p["n"] += 1
+        return p["done"][b]
+
+    def drain(self):
+        """Wait for every batch queued with submit_host; re-binds the context to the caller's stream."""
+        p = self._pipeline()
+        p["comp"].synchronize()
+        p["copy"].synchronize()
+        self.ctx.use_current_stream()
+
     def tensor(self, name):
         return self.buffers[name]
 

@@ -347,3 +347,13 @@ def test_two_devices_in_one_process():
             outs.append((out.cpu(), y.cpu()))
             c.close()
     assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+
+
+def test_int8_peak_selftest_runs(ctx):
+    """The tensor-pipe peak loop returns by itself and reports a plausible rate (a B200 is far above 1 POP/s)."""
+    import ctypes as C
+    best, mean = C.c_double(), C.c_double()
+    for signed in (0, 1):
+        L.check(ctx._lib.nncb_selftest_int8_peak(ctx._h, 4096, 3, signed, C.byref(best), C.byref(mean)))
+        ctx.check_status()
+        assert best.value >= mean.value > 1000.0, (best.value, mean.value)
