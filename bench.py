@@ -689,6 +689,14 @@ def measure_decode(torch, ctx, pk, steps, warmup, world, rank):
     return res
 
 
+def run_streams(args):
+    """Only the streaming kernels (profiling aid): one JSON line with their achieved GB/s."""
+    import torch
+    from nncase_b200.kernels import Context
+    ctx = Context(0)
+    print(json.dumps(stream_kernels(torch, ctx, peaks(), reps=max(1, args.steps))))
+
+
 def run_attention(args):
     import torch
     from nncase_b200.kernels import Context
@@ -734,8 +742,11 @@ def main():
     ap.add_argument("--layer", default=None, help="time only this conv layer (profiling aid)")
     ap.add_argument("--attention", action="store_true", help="only the paged-attention decode measurement")
     ap.add_argument("--decode", action="store_true", help="only the decoder step (tensor parallel under torchrun)")
+    ap.add_argument("--streams", action="store_true", help="only the streaming kernels (quantize, dequantize, add, max-pool, input stage)")
     args = ap.parse_args()
-    if args.decode:
+    if args.streams:
+        run_streams(args)
+    elif args.decode:
         run_decode(args)
     elif args.attention:
         run_attention(args)

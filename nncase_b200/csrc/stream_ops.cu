@@ -3,6 +3,7 @@
 // multiple of the SM count with a grid-stride loop.
 #include "internal.cuh"
 #include "qconv.cuh"
+#include <type_traits>
 
 namespace nncb {
 
@@ -54,29 +55,40 @@ __global__ void __launch_bounds__(256) quantize_kernel(const float *__restrict__
         out[i] = (Q)quant_dev(in[i], scale, zp, qlimits<Q>::lo, qlimits<Q>::hi);
 }
 
+// Four elements per thread per step: consecutive lanes read consecutive 4-byte (8-byte for int16) words and write
+// consecutive float4 -- a warp's store instruction covers 512 contiguous bytes -- with four independent
+// steps in flight per thread (the stream is 80 % writes; the loads of the next steps overlap them).
 template <typename Q>
 __global__ void __launch_bounds__(256) dequantize_kernel(const Q *__restrict__ in, float *__restrict__ out,
                                                          size_t n, float scale, float zp, bool vec_ok) {
     const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t nthreads = (size_t)gridDim.x * blockDim.x;
-    constexpr int PER = 16 / sizeof(Q); // elements per 16-byte load
-    const size_t nvec = vec_ok ? n / PER : 0;
-    for (size_t v = tid; v < nvec; v += nthreads) {
-        uint4 raw = __ldcs(reinterpret_cast<const uint4 *>(in) + v);
-        alignas(16) Q q[PER];
-        *reinterpret_cast<uint4 *>(q) = raw;
-        float4 *o = reinterpret_cast<float4 *>(out + v * PER);
+    const size_t nvec = vec_ok ? n / 4 : 0; // groups of four elements
+    constexpr int UN = 4;
+    using W = typename std::conditional<sizeof(Q) == 1, uint32_t, uint2>::type;
+    auto deq4 = [&](const W &w) {
+        alignas(8) Q q[4];
+        *reinterpret_cast<W *>(q) = w;
+        float4 f;
+        f.x = dequant_dev((float)q[0], zp, scale);
+        f.y = dequant_dev((float)q[1], zp, scale);
+        f.z = dequant_dev((float)q[2], zp, scale);
+        f.w = dequant_dev((float)q[3], zp, scale);
+        return f;
+    };
+    size_t v = tid;
+    for (; v + (UN - 1) * nthreads < nvec; v += UN * nthreads) {
+        W w[UN];
 #pragma unroll
-        for (int i = 0; i < PER / 4; i++) {
-            float4 f;
-            f.x = dequant_dev((float)q[i * 4 + 0], zp, scale);
-            f.y = dequant_dev((float)q[i * 4 + 1], zp, scale);
-            f.z = dequant_dev((float)q[i * 4 + 2], zp, scale);
-            f.w = dequant_dev((float)q[i * 4 + 3], zp, scale);
-            __stcs(o + i, f);
-        }
+        for (int u = 0; u < UN; u++)
+            w[u] = __ldcs(reinterpret_cast<const W *>(in) + v + u * nthreads);
+#pragma unroll
+        for (int u = 0; u < UN; u++)
+            __stcs(reinterpret_cast<float4 *>(out) + v + u * nthreads, deq4(w[u]));
     }
-    for (size_t i = nvec * PER + tid; i < n; i += nthreads)
+    for (; v < nvec; v += nthreads)
+        __stcs(reinterpret_cast<float4 *>(out) + v, deq4(__ldcs(reinterpret_cast<const W *>(in) + v)));
+    for (size_t i = nvec * 4 + tid; i < n; i += nthreads)
         out[i] = dequant_dev((float)in[i], zp, scale);
 }
 
@@ -115,18 +127,16 @@ int dequantize(nncb_context *ctx, const void *in, float *out, size_t n, float sc
         return fail(-EINVAL, "dequantize: null pointer");
     const int threads = 256;
     const bool v = aligned16(in, out);
+    const int grid = stream_grid(ctx, (n + 15) / 16, threads);
     switch (qtype) {
     case NNCB_U8:
-        dequantize_kernel<uint8_t><<<stream_grid(ctx, (n + 15) / 16, threads), threads, 0, ctx->stream>>>(
-            (const uint8_t *)in, out, n, scale, (float)zp, v);
+        dequantize_kernel<uint8_t><<<grid, threads, 0, ctx->stream>>>((const uint8_t *)in, out, n, scale, (float)zp, v);
         break;
     case NNCB_I8:
-        dequantize_kernel<int8_t><<<stream_grid(ctx, (n + 15) / 16, threads), threads, 0, ctx->stream>>>(
-            (const int8_t *)in, out, n, scale, (float)zp, v);
+        dequantize_kernel<int8_t><<<grid, threads, 0, ctx->stream>>>((const int8_t *)in, out, n, scale, (float)zp, v);
         break;
     case NNCB_I16:
-        dequantize_kernel<int16_t><<<stream_grid(ctx, (n + 7) / 8, threads), threads, 0, ctx->stream>>>(
-            (const int16_t *)in, out, n, scale, (float)zp, v);
+        dequantize_kernel<int16_t><<<grid, threads, 0, ctx->stream>>>((const int16_t *)in, out, n, scale, (float)zp, v);
         break;
     default:
         return fail(-ENOSYS, "dequantize: unsupported source type %d", qtype);
@@ -222,21 +232,25 @@ __device__ __forceinline__ uint32_t quant_u8_fast(float x, float s, float r, flo
 
 // CT: the channel count when it is known at compile time (3: images), else 0 and `c` is used. With CT the
 // twelve loads of a cell are independent and every byte lands in a fixed place of the cell's words.
+constexpr uint32_t S2D_ROWS = 1, POOL_ROWS = 1; // cell / output rows per block (more rows per block measured slower)
 template <int CPAD, bool IN_NHWC, int CT>
 __global__ void __launch_bounds__(256)
 quantize_nchw_to_s2d_kernel(const float *__restrict__ in, uint8_t *__restrict__ out, int c_rt, int h, int w,
-                            float scale, float rscale, float zp, int pad_t, int pad_b, int pad_l, int pad_r) {
+                            float scale, float rscale, float zp, int pad_t, int pad_b, int pad_l, int pad_r,
+                            uint32_t total_rows) {
     // output cells include a border of pad_* cells that hold the zero point in every channel;
     // blockIdx.x = (image, cell row), blockIdx.y * blockDim.x + thread = cell in the row
     const int c = CT ? CT : c_rt;
     const int hc = h / 2 + pad_t + pad_b, wc = w / 2 + pad_l + pad_r;
     const uint32_t zq = (uint32_t)min(max(__float2int_rn(zp), 0), 255);
     const int xc = (int)(blockIdx.y * blockDim.x + threadIdx.x);
+    // a block walks S2D_ROWS consecutive cell rows: fewer, longer-lived blocks than one per row
+    for (uint32_t row = blockIdx.x * S2D_ROWS; row < min((blockIdx.x + 1) * S2D_ROWS, total_rows); row++)
     if (xc < wc) {
         const int X = xc - pad_l;
-        const int Y = (int)(blockIdx.x % (uint32_t)hc) - pad_t;
-        const size_t n = blockIdx.x / (uint32_t)hc;
-        const size_t i = (size_t)blockIdx.x * wc + xc;
+        const int Y = (int)(row % (uint32_t)hc) - pad_t;
+        const size_t n = row / (uint32_t)hc;
+        const size_t i = (size_t)row * wc + xc;
         uint32_t words[CPAD / 4];
 #pragma unroll
         for (int k = 0; k < CPAD / 4; k++)
@@ -266,7 +280,44 @@ quantize_nchw_to_s2d_kernel(const float *__restrict__ in, uint8_t *__restrict__ 
                     words[k] = (words[k] & ~(0xFFu << (8 * (i1 & 3)))) | (q1 << (8 * (i1 & 3)));
             }
         };
-        if (inside) {
+        if (inside && CT && !IN_NHWC && rscale != 0.f) {
+            // Straight-line form for a known channel count: all loads first (independent), then the division-free
+            // quantization two values at a time on packed f32x2 operations, bytes assembled with byte permutes.
+            // Inputs are clamped to [xlo, xhi] first: beyond them the result is 0 or 255 either way (the bounds sit
+            // two quantization steps outside the u8 range), NaN takes xlo like the reference's conversion gives 0,
+            // and no product can overflow.
+            const float xlo = scale * (-zp - 2.f), xhi = scale * (257.f - zp);
+            const uint64_t r2 = pack2(rscale, rscale), ns2 = pack2(-scale, -scale), z2 = pack2(zp, zp);
+            const float *base = in + ((n * CT) * h + 2 * Y) * (size_t)w + 2 * X;
+            const uint32_t plane = (uint32_t)h * (uint32_t)w;
+            float2 v[CT ? CT : 1][2];
+#pragma unroll
+            for (int ch = 0; ch < (CT ? CT : 1); ch++)
+#pragma unroll
+                for (int dy = 0; dy < 2; dy++)
+                    v[ch][dy] = __ldcs(reinterpret_cast<const float2 *>(base + ch * plane + dy * (uint32_t)w));
+            uint32_t q[4 * (CT ? CT : 1)]; // byte (dy*2 + dx)*c + ch
+#pragma unroll
+            for (int ch = 0; ch < (CT ? CT : 1); ch++)
+#pragma unroll
+                for (int dy = 0; dy < 2; dy++) {
+                    const float a = fminf(fmaxf(v[ch][dy].x, xlo), xhi), b = fminf(fmaxf(v[ch][dy].y, xlo), xhi);
+                    const uint64_t x2 = pack2(a, b);
+                    const uint64_t q0 = mul2(x2, r2);
+                    float u0, u1;
+                    unpack2(add2(fma2(fma2(q0, ns2, x2), r2, q0), z2), u0, u1);
+                    asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(q[(dy * 2 + 0) * CT + ch]) : "f"(u0));
+                    asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(q[(dy * 2 + 1) * CT + ch]) : "f"(u1));
+                }
+#pragma unroll
+            for (int k = 0; k < CPAD / 4; k++) {
+                uint32_t b[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    b[j] = (4 * k + j) < 4 * CT ? q[(4 * k + j) < 4 * CT ? 4 * k + j : 0] : zq;
+                words[k] = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
+            }
+        } else if (inside) {
             if (CT) {
 #pragma unroll
                 for (int ch = 0; ch < (CT ? CT : 1); ch++) {
@@ -299,9 +350,10 @@ int quantize_nchw_to_s2d_u8(nncb_context *ctx, const float *in, uint8_t *out, in
         return fail(-EINVAL, "quantize_nchw_to_s2d_u8: pointers must be 8-byte (in) and 16-byte (out) aligned");
     const int hc = h / 2 + pad_t + pad_b, wc = w / 2 + pad_l + pad_r;
     const int bt = wc >= 256 ? 256 : (wc + 31) / 32 * 32;
-    const dim3 grid((unsigned)((size_t)n * hc), (unsigned)((wc + bt - 1) / bt));
     if ((size_t)n * hc > 0x7fffffffull)
         return fail(-EINVAL, "quantize_nchw_to_s2d_u8: too many rows");
+    const uint32_t total_rows = (uint32_t)((size_t)n * hc);
+    const dim3 grid((total_rows + S2D_ROWS - 1) / S2D_ROWS, (unsigned)((wc + bt - 1) / bt));
     // the reciprocal of the scale, when it is one the division-free sequence is proven for (else 0: divide)
     bool r_ok = true;
     float rscale = rn_reciprocal(scale, &r_ok);
@@ -309,7 +361,7 @@ int quantize_nchw_to_s2d_u8(nncb_context *ctx, const float *in, uint8_t *out, in
         rscale = 0.f;
 #define NNCB_S2D(CP, NH, CT_)                                                                                          \
     quantize_nchw_to_s2d_kernel<CP, NH, CT_><<<grid, bt, 0, ctx->stream>>>(in, out, c, h, w, scale, rscale, (float)zp, pad_t, \
-                                                                           pad_b, pad_l, pad_r)
+                                                                           pad_b, pad_l, pad_r, total_rows)
     if (c == 3) {
         if (c_pad == 32 && in_nhwc)
             NNCB_S2D(32, true, 3);
@@ -411,21 +463,76 @@ __device__ __forceinline__ uint32_t qadd4(uint32_t a, uint32_t b, float sa, floa
     return r;
 }
 
+// The division-free form on two elements per instruction (f32x2: each half rounds like the scalar operation).
+// Bytes i and i + 1 of a and b -> two output bytes in the low half of the result.
+__device__ __forceinline__ uint32_t qadd2(uint32_t a, uint32_t b, int i, uint64_t nza2, uint64_t sa2, uint64_t nzb2,
+                                          uint64_t sb2, uint64_t rso2, uint64_t nso2, uint64_t zo2) {
+    // 2^23 + byte as float bits; nza2 = -(2^23 + za): the sum is byte - za exactly
+    const uint64_t qa = pack2(__uint_as_float(__byte_perm(a, 0x4B000000u, 0x7440 | i)),
+                              __uint_as_float(__byte_perm(a, 0x4B000000u, 0x7440 | (i + 1))));
+    const uint64_t qb = pack2(__uint_as_float(__byte_perm(b, 0x4B000000u, 0x7440 | i)),
+                              __uint_as_float(__byte_perm(b, 0x4B000000u, 0x7440 | (i + 1))));
+    // fa and fb must each round before they are added: a packed add fed by a packed multiply would be contracted
+    // into one fused multiply-add, so the sum runs as two scalar adds
+    const uint64_t fa = mul2(add2(qa, nza2), sa2), fb = mul2(add2(qb, nzb2), sb2);
+    float fa0, fa1, fb0, fb1;
+    unpack2(fa, fa0, fa1);
+    unpack2(fb, fb0, fb1);
+    const uint64_t x2 = pack2(__fadd_rn(fa0, fb0), __fadd_rn(fa1, fb1));
+    const uint64_t q0 = mul2(x2, rso2);
+    const uint64_t q2 = fma2(fma2(q0, nso2, x2), rso2, q0);
+    float u0, u1;
+    unpack2(add2(q2, zo2), u0, u1);
+    uint32_t r0, r1;
+    asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(r0) : "f"(u0));
+    asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(r1) : "f"(u1));
+    return r0 | (r1 << 8);
+}
+__device__ __forceinline__ uint32_t qadd4p(uint32_t a, uint32_t b, uint64_t nza2, uint64_t sa2, uint64_t nzb2, uint64_t sb2,
+                                           uint64_t rso2, uint64_t nso2, uint64_t zo2) {
+    return qadd2(a, b, 0, nza2, sa2, nzb2, sb2, rso2, nso2, zo2) | (qadd2(a, b, 2, nza2, sa2, nzb2, sb2, rso2, nso2, zo2) << 16);
+}
+
 __global__ void __launch_bounds__(256)
 qadd_kernel(const uint8_t *__restrict__ a, const uint8_t *__restrict__ b, uint8_t *__restrict__ y, size_t n,
             float sa, float za, float sb, float zb, float so, float zo, float rso, bool vec_ok) {
     const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t nthreads = (size_t)gridDim.x * blockDim.x;
     const size_t nvec = vec_ok ? n / 16 : 0;
-    for (size_t v = tid; v < nvec; v += nthreads) {
-        uint4 va = __ldcs(reinterpret_cast<const uint4 *>(a) + v);
-        uint4 vb = __ldcs(reinterpret_cast<const uint4 *>(b) + v);
-        uint4 r;
-        r.x = qadd4(va.x, vb.x, sa, za, sb, zb, so, zo, rso);
-        r.y = qadd4(va.y, vb.y, sa, za, sb, zb, so, zo, rso);
-        r.z = qadd4(va.z, vb.z, sa, za, sb, zb, so, zo, rso);
-        r.w = qadd4(va.w, vb.w, sa, za, sb, zb, so, zo, rso);
-        __stcs(reinterpret_cast<uint4 *>(y) + v, r);
+    if (rso != 0.f) {
+        const float mza = -__fadd_rn(8388608.0f, za), mzb = -__fadd_rn(8388608.0f, zb);
+        const uint64_t nza2 = pack2(mza, mza), nzb2 = pack2(mzb, mzb), sa2 = pack2(sa, sa), sb2 = pack2(sb, sb);
+        const uint64_t rso2 = pack2(rso, rso), nso2 = pack2(-so, -so), zo2 = pack2(zo, zo);
+        auto one = [&](const uint4 &va, const uint4 &vb) {
+            uint4 r;
+            r.x = qadd4p(va.x, vb.x, nza2, sa2, nzb2, sb2, rso2, nso2, zo2);
+            r.y = qadd4p(va.y, vb.y, nza2, sa2, nzb2, sb2, rso2, nso2, zo2);
+            r.z = qadd4p(va.z, vb.z, nza2, sa2, nzb2, sb2, rso2, nso2, zo2);
+            r.w = qadd4p(va.w, vb.w, nza2, sa2, nzb2, sb2, rso2, nso2, zo2);
+            return r;
+        };
+        size_t v = tid;
+        for (; v + nthreads < nvec; v += 2 * nthreads) { // two independent vectors in flight
+            const uint4 a0 = __ldcs(reinterpret_cast<const uint4 *>(a) + v), b0 = __ldcs(reinterpret_cast<const uint4 *>(b) + v);
+            const uint4 a1 = __ldcs(reinterpret_cast<const uint4 *>(a) + v + nthreads);
+            const uint4 b1 = __ldcs(reinterpret_cast<const uint4 *>(b) + v + nthreads);
+            __stcs(reinterpret_cast<uint4 *>(y) + v, one(a0, b0));
+            __stcs(reinterpret_cast<uint4 *>(y) + v + nthreads, one(a1, b1));
+        }
+        for (; v < nvec; v += nthreads)
+            __stcs(reinterpret_cast<uint4 *>(y) + v,
+                   one(__ldcs(reinterpret_cast<const uint4 *>(a) + v), __ldcs(reinterpret_cast<const uint4 *>(b) + v)));
+    } else {
+        for (size_t v = tid; v < nvec; v += nthreads) {
+            uint4 va = __ldcs(reinterpret_cast<const uint4 *>(a) + v);
+            uint4 vb = __ldcs(reinterpret_cast<const uint4 *>(b) + v);
+            uint4 r;
+            r.x = qadd4(va.x, vb.x, sa, za, sb, zb, so, zo, rso);
+            r.y = qadd4(va.y, vb.y, sa, za, sb, zb, so, zo, rso);
+            r.z = qadd4(va.z, vb.z, sa, za, sb, zb, so, zo, rso);
+            r.w = qadd4(va.w, vb.w, sa, za, sb, zb, so, zo, rso);
+            __stcs(reinterpret_cast<uint4 *>(y) + v, r);
+        }
     }
     for (size_t i = nvec * 16 + tid; i < n; i += nthreads) {
         float fa = dequant_dev((float)a[i], za, sa), fb = dequant_dev((float)b[i], zb, sb);
@@ -537,13 +644,15 @@ maxpool_vec_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ y, int n
 template <int KH, int KW>
 __global__ void __launch_bounds__(256)
 maxpool_vec_fixed_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ y, int n, int h, int w, int c, int oh, int ow,
-                         int sh, int sw, int pt, int pl, uint32_t zp4) {
+                         int sh, int sw, int pt, int pl, uint32_t zp4, uint32_t total_rows) {
     const uint32_t cg = (uint32_t)c / 16u;
     const uint32_t j = blockIdx.y * blockDim.x + threadIdx.x;
+    // a block walks POOL_ROWS consecutive output rows: fewer, longer-lived blocks than one per row
+    for (uint32_t row = blockIdx.x * POOL_ROWS; row < min((blockIdx.x + 1) * POOL_ROWS, total_rows); row++)
     if (j < (uint32_t)ow * cg) {
         const int g = (int)(j % cg), ox = (int)(j / cg);
-        const int oy = (int)(blockIdx.x % (uint32_t)oh), b = (int)(blockIdx.x / (uint32_t)oh);
-        const size_t p = (size_t)blockIdx.x * ow + ox;
+        const int oy = (int)(row % (uint32_t)oh), b = (int)(row / (uint32_t)oh);
+        const size_t p = (size_t)row * ow + ox;
         uint4 v[KH * KW];
         bool all = true;
 #pragma unroll
@@ -556,15 +665,31 @@ maxpool_vec_fixed_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ y,
                 v[ky * KW + kx] = valid ? __ldg(reinterpret_cast<const uint4 *>(x + (((size_t)b * h + iy) * w + ix) * c) + g)
                                         : make_uint4(0, 0, 0, 0);
             }
-        uint4 m = all ? make_uint4(0, 0, 0, 0) : make_uint4(zp4, zp4, zp4, zp4); // a padded tap holds the zero point
+        // Byte-wise maximum on the three-input 16-bit-pair maximum of the hardware: every word is split into its
+        // even and its odd bytes (one byte permute each), the taps are reduced three at a time, and the two halves
+        // are interleaved again. The byte-wise __vmaxu4 is a multi-instruction sequence, and with nine taps it made
+        // the kernel issue-bound.
+        const uint32_t zlo = all ? 0u : (zp4 & 0x00FF00FFu); // a padded tap holds the zero point
+        uint32_t mw[4];
 #pragma unroll
-        for (int t = 0; t < KH * KW; t++) {
-            m.x = __vmaxu4(m.x, v[t].x);
-            m.y = __vmaxu4(m.y, v[t].y);
-            m.z = __vmaxu4(m.z, v[t].z);
-            m.w = __vmaxu4(m.w, v[t].w);
+        for (int k = 0; k < 4; k++) {
+            uint32_t lo = zlo, hi = zlo;
+            auto word = [&](int t) { return k == 0 ? v[t].x : (k == 1 ? v[t].y : (k == 2 ? v[t].z : v[t].w)); };
+            int t = 0;
+#pragma unroll
+            for (; t + 1 < KH * KW; t += 2) {
+                const uint32_t a = word(t), b = word(t + 1);
+                lo = __vimax3_u16x2(lo, __byte_perm(a, 0u, 0x4240), __byte_perm(b, 0u, 0x4240));
+                hi = __vimax3_u16x2(hi, __byte_perm(a, 0u, 0x4341), __byte_perm(b, 0u, 0x4341));
+            }
+            if (t < KH * KW) {
+                const uint32_t a = word(t);
+                lo = __vimax3_u16x2(lo, __byte_perm(a, 0u, 0x4240), 0u);
+                hi = __vimax3_u16x2(hi, __byte_perm(a, 0u, 0x4341), 0u);
+            }
+            mw[k] = __byte_perm(lo, hi, 0x6240);
         }
-        reinterpret_cast<uint4 *>(y + p * c)[g] = m;
+        reinterpret_cast<uint4 *>(y + p * c)[g] = make_uint4(mw[0], mw[1], mw[2], mw[3]);
     }
 }
 
@@ -613,16 +738,18 @@ int maxpool_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, int n, int h, in
             return fail(-EINVAL, "maxpool_u8: too many rows");
         const dim3 grid((unsigned)((size_t)n * oh), (unsigned)((row_items + bt - 1) / bt));
         const uint32_t z4 = (uint32_t)z * 0x01010101u;
+        const uint32_t rows = (uint32_t)((size_t)n * oh);
+        const dim3 gridf((rows + POOL_ROWS - 1) / POOL_ROWS, grid.y);
         if (kh == 3 && kw == 3) {
-            maxpool_vec_fixed_kernel<3, 3><<<grid, bt, 0, ctx->stream>>>(x, y, n, h, w, c, oh, ow, sh, sw, pt, pl, z4);
+            maxpool_vec_fixed_kernel<3, 3><<<gridf, bt, 0, ctx->stream>>>(x, y, n, h, w, c, oh, ow, sh, sw, pt, pl, z4, rows);
             return after_launch(ctx, "maxpool_u8");
         }
         if (kh == 2 && kw == 2) {
-            maxpool_vec_fixed_kernel<2, 2><<<grid, bt, 0, ctx->stream>>>(x, y, n, h, w, c, oh, ow, sh, sw, pt, pl, z4);
+            maxpool_vec_fixed_kernel<2, 2><<<gridf, bt, 0, ctx->stream>>>(x, y, n, h, w, c, oh, ow, sh, sw, pt, pl, z4, rows);
             return after_launch(ctx, "maxpool_u8");
         }
         if (kh == 5 && kw == 5) {
-            maxpool_vec_fixed_kernel<5, 5><<<grid, bt, 0, ctx->stream>>>(x, y, n, h, w, c, oh, ow, sh, sw, pt, pl, z4);
+            maxpool_vec_fixed_kernel<5, 5><<<gridf, bt, 0, ctx->stream>>>(x, y, n, h, w, c, oh, ow, sh, sw, pt, pl, z4, rows);
             return after_launch(ctx, "maxpool_u8");
         }
         maxpool_vec_kernel<<<grid, bt, 0, ctx->stream>>>(
