@@ -276,6 +276,36 @@ NNCB_API int nncb_paged_attention_decode(nncb_context *ctx, const void *q, const
  * Results are identical to nncb_paged_attention_decode. */
 NNCB_API int nncb_paged_attention_decode_noalloc(nncb_context *ctx, const void *q, const void *k_pool, const void *v_pool, const int32_t *block_table, const int32_t *context_lens, void *out, int batch, int q_heads, int kv_heads, int head_dim, int page_size, int max_pages, int num_pages, float scale);
 
+/* ---- a whole quantized program: the body of one kmodel function of module kind "cuda" -----------
+ * The native side of the `cuda` module's runtime_function (the reference's contract:
+ * src/Native/include/nncase/runtime/runtime_function.h:59-63 -- initialize_core once, invoke_core per
+ * call; its StackVM counterpart is src/Native/src/runtime/stackvm/runtime_function.run.cpp:34-63).
+ *   nncb_program_create   parses the function's ".desc" section and the module's ".rdata" section (HOST
+ *                         pointers; the formats are written by nncase_b200/kmodel.py and described in
+ *                         INTEGRATION.md), uploads weights, plans every convolution and allocates every
+ *                         tensor for the batch the descriptor names. Malformed input: -EINVAL, never a crash.
+ *   nncb_program_run      enqueues all kernels of one call; x is the f32 input ON THE DEVICE
+ *                         ([n,c,h,w], or [n,h,w,c] when the descriptor says so). Nothing is allocated.
+ *   nncb_program_run_host the same with HOST buffers: input copied in, every output copied out
+ *                         (outs[i] must hold the bytes nncb_program_tensor reports for output i), then
+ *                         synchronised -- the contract of the reference's synchronous functions.
+ *   nncb_program_info / _output / _tensor   shapes, types, quant params and device pointers.
+ *   nncb_program_set_profiling, _profile_text, _profile_ms   per-operator CUDA-event times of the last call,
+ *                         as the two tables of the reference's op_profile::print
+ *                         (src/Native/src/runtime/stackvm/op_profile.cpp:25-111) or as numbers. */
+typedef struct nncb_program nncb_program;
+NNCB_API int nncb_program_create(nncb_context *ctx, const void *desc, size_t desc_bytes, const void *rdata, size_t rdata_bytes, nncb_program **out);
+NNCB_API int nncb_program_destroy(nncb_program *program);
+NNCB_API int nncb_program_run(nncb_context *ctx, nncb_program *program, const float *x);
+NNCB_API int nncb_program_run_host(nncb_context *ctx, nncb_program *program, const float *x_host, void *const *outs_host, int32_t n_outs);
+NNCB_API int nncb_program_info(const nncb_program *program, int32_t *batch, int32_t *in_nhwc, int32_t in_chw[3], int32_t *n_outputs, int32_t *n_ops, int32_t *n_tensors);
+NNCB_API int nncb_program_output(const nncb_program *program, int32_t index, int32_t *tensor);
+NNCB_API int nncb_program_tensor(const nncb_program *program, int32_t tensor, void **dptr, int32_t hwc[3], int32_t *dtype, float *scale, int32_t *zero_point, size_t *bytes);
+NNCB_API int nncb_program_set_profiling(nncb_program *program, int enabled);
+NNCB_API uint64_t nncb_program_launches_per_call(const nncb_program *program);
+NNCB_API int nncb_program_profile_text(const nncb_program *program, char *buf, size_t cap);
+NNCB_API int nncb_program_profile_ms(const nncb_program *program, float *ms, int32_t n);
+
 /* Diagnostic: the tensor-core kernel divides by a layer's output scale with a three-operation
  * sequence around a correctly rounded reciprocal. This runs that sequence against the IEEE
  * division for `count` pseudo-random operands on the device and returns how many differ

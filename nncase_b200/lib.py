@@ -104,6 +104,19 @@ SIGNATURES = {
     "nncb_context_set_option": (_I, [_VP, C.c_char_p, C.c_int64]),
     "nncb_context_get_option": (_I, [_VP, C.c_char_p, C.POINTER(C.c_int64)]),
     "nncb_selftest_reciprocal_division": (_I, [_VP, _F, C.c_uint64, C.c_uint64, C.POINTER(C.c_uint64)]),
+    "nncb_program_create": (_I, [_VP, _VP, _SZ, _VP, _SZ, C.POINTER(_VP)]),
+    "nncb_program_destroy": (_I, [_VP]),
+    "nncb_program_run": (_I, [_VP, _VP, _VP]),
+    "nncb_program_run_host": (_I, [_VP, _VP, _VP, C.POINTER(_VP), _I32]),
+    "nncb_program_info": (_I, [_VP, C.POINTER(_I32), C.POINTER(_I32), C.POINTER(_I32 * 3), C.POINTER(_I32), C.POINTER(_I32),
+                               C.POINTER(_I32)]),
+    "nncb_program_output": (_I, [_VP, _I32, C.POINTER(_I32)]),
+    "nncb_program_tensor": (_I, [_VP, _I32, C.POINTER(_VP), C.POINTER(_I32 * 3), C.POINTER(_I32), C.POINTER(_F),
+                                 C.POINTER(_I32), C.POINTER(_SZ)]),
+    "nncb_program_set_profiling": (_I, [_VP, _I]),
+    "nncb_program_launches_per_call": (C.c_uint64, [_VP]),
+    "nncb_program_profile_text": (_I, [_VP, C.c_char_p, _SZ]),
+    "nncb_program_profile_ms": (_I, [_VP, C.POINTER(_F), _I32]),
     "nncb_selftest_int8_peak": (_I, [_VP, C.c_uint32, _I, _I, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "nncb_qconv2d_host": (_I, [_VP, C.POINTER(Conv2dDesc), _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP]),
 }

@@ -97,3 +97,39 @@ def test_qconv2d_custom_call(harness, qo):
                                  out.ctypes.data_as(C.c_void_p), C.c_size_t(out.size))
     assert rc == 0
     assert np.array_equal(out, want)
+
+
+def test_qconv2d_custom_call_validates_its_tensors(harness):
+    """Tensors reach a custom call from a kmodel: shapes that do not fit the descriptor are refused with
+    invalid_argument before any byte is read through them (host-only checks, no GPU needed)."""
+    from nncase_b200.lib import Conv2dDesc
+    n, h, w, c, oc = 1, 6, 6, 32, 16
+    x = np.zeros((n, h, w, c), np.uint8)
+    zw = np.zeros(oc, np.int32)
+    mult = np.ones(oc, np.float32)
+    bias = np.zeros(oc, np.float32)
+
+    def call(wshape, kdesc=None, res_bytes=None, out_elems=None):
+        d = Conv2dDesc()
+        d.stride_h = d.stride_w = d.dil_h = d.dil_w = d.groups = 1
+        d.out_scale = 0.05
+        for k, v in (kdesc or {}).items():
+            setattr(d, k, v)
+        wq = np.zeros(wshape, np.uint8)
+        out_elems = out_elems or n * h * w * oc
+        out = np.zeros(out_elems, np.uint8)
+        res = np.zeros(res_bytes, np.uint8) if res_bytes else None
+        return harness.harness_qconv2d(C.byref(d), C.c_size_t(C.sizeof(d)), x.ctypes.data_as(C.c_void_p),
+                                       (C.c_size_t * 4)(*x.shape), wq.ctypes.data_as(C.c_void_p),
+                                       (C.c_size_t * 4)(*wshape), 0, zw.ctypes.data_as(C.c_void_p),
+                                       mult.ctypes.data_as(C.c_void_p), bias.ctypes.data_as(C.c_void_p),
+                                       res.ctypes.data_as(C.c_void_p) if res is not None else None,
+                                       out.ctypes.data_as(C.c_void_p), C.c_size_t(res_bytes or out_elems))
+
+    EINVAL = -22
+    assert call((oc, 1, 1, c + 1)) == EINVAL                     # weights' channel count is not c / groups
+    assert call((oc, 9, 9, c)) == EINVAL                         # kernel larger than the (unpadded) input
+    assert call((oc, 1, 1, c), dict(stride_h=0)) == EINVAL       # non-positive stride
+    assert call((oc, 1, 1, c), dict(pad_t=-1)) == EINVAL         # negative padding
+    assert call((oc, 1, 1, c), dict(groups=3)) == EINVAL         # channels not divisible by groups
+    assert call((oc, 1, 1, c), res_bytes=17) == EINVAL           # residual that does not have the output's size
