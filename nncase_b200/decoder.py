@@ -69,36 +69,102 @@ def rope_tables(cfg):
     return np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
 
 
+def shard_plan(cfg, world):
+    """How the model splits over `world` tensor-parallel ranks (Megatron-style: qkv / gate-up by output channel,
+    o / down by input channel, LM head by vocabulary).
+
+    KV heads split when there are enough of them; otherwise several ranks share one KV head (each keeps its
+    own copy of that head's pages) and the query heads of the head's group are dealt to those ranks, the group
+    padded with zero heads to a multiple of the sharing degree -- a zero head has zero q rows and zero o
+    columns, so it adds nothing. The MLP width per rank is rounded up to the MatMul's K granule (64) with zero
+    channels. Qwen2-0.5B (14 q / 2 kv heads, 4864): world 2 -> 7 q + 1 kv per rank; world 4 -> 4 q (one
+    padded per group) + 1 shared kv; world 8 -> 2 q + 1 shared kv, MLP 608 -> 640 per rank."""
+    if world < 1 or cfg.q_heads % cfg.kv_heads:
+        raise NncbError(-22, "bad tensor parallel degree or head counts")
+    group = cfg.q_heads // cfg.kv_heads
+    if cfg.kv_heads % world == 0:
+        rep, hkv, gpad = 1, cfg.kv_heads // world, group
+        hq = hkv * group
+    elif world % cfg.kv_heads == 0:
+        rep, hkv = world // cfg.kv_heads, 1
+        gpad = -(-group // rep) * rep
+        hq = gpad // rep
+    else:
+        raise NncbError(-38, f"tensor parallel degree {world} neither divides nor is a multiple of the {cfg.kv_heads} kv heads")
+    if cfg.vocab % world:
+        raise NncbError(-38, f"tensor parallel degree {world} does not divide the vocabulary")
+    if hq // hkv > 8:
+        raise NncbError(-38, "more than 8 query heads per kv head on a rank")
+    inter = -(-cfg.inter // world)
+    inter_pad = -(-inter // 64) * 64
+    return dict(world=world, group=group, rep=rep, hq=hq, hkv=hkv, gpad=gpad, inter=inter, inter_pad=inter_pad,
+                vocab=cfg.vocab // world)
+
+
+def rank_kv_heads(cfg, world, rank):
+    """Indices of the model's kv heads whose pages rank `rank` keeps."""
+    p = shard_plan(cfg, world)
+    if p["rep"] == 1:
+        return list(range(rank * p["hkv"], (rank + 1) * p["hkv"]))
+    return [rank // p["rep"]]
+
+
 def shard_weights(cfg, w, world, rank):
-    """The slice of every projection that tensor-parallel rank `rank` of `world` owns."""
+    """The slice of every projection that tensor-parallel rank `rank` of `world` owns (see shard_plan)."""
     if world == 1:
         return w
-    if cfg.q_heads % world or cfg.kv_heads % world or cfg.inter % (world * 64) or cfg.vocab % world:
-        raise NncbError(-38, f"tensor parallel degree {world} does not divide the heads / widths of this shape")
+    p = shard_plan(cfg, world)
     D = cfg.head_dim
-    hq, hkv = cfg.q_heads // world, cfg.kv_heads // world
     nq, nkv = cfg.q_heads * D, cfg.kv_heads * D
-    qs = slice(rank * hq * D, (rank + 1) * hq * D)
-    ks = slice(nq + rank * hkv * D, nq + (rank + 1) * hkv * D)
-    vs = slice(nq + nkv + rank * hkv * D, nq + nkv + (rank + 1) * hkv * D)
-    ii = cfg.inter // world
-    gs = slice(rank * ii, (rank + 1) * ii)
-    us = slice(cfg.inter + rank * ii, cfg.inter + (rank + 1) * ii)
-    vv = cfg.vocab // world
+    kv_heads = rank_kv_heads(cfg, world, rank)
+    # query heads of this rank, as indices into the model's heads; None = a zero head that pads the group
+    if p["rep"] == 1:
+        q_heads = list(range(rank * p["hq"], (rank + 1) * p["hq"]))
+    else:
+        j = rank % p["rep"]
+        q_heads = [kv_heads[0] * p["group"] + i if i < p["group"] else None for i in range(j * p["hq"], (j + 1) * p["hq"])]
+    ii, ipad = p["inter"], p["inter_pad"]
+    g0, g1 = rank * ii, min((rank + 1) * ii, cfg.inter)
+    vv = p["vocab"]
 
-    def rows(t, *sl):
-        return np.concatenate([t[0][s] for s in sl]), np.concatenate([t[1][s] for s in sl])
+    def take_rows(t, idx_blocks, bias=None):
+        """Rows of a quantized [N, K] matrix (and of its scales / bias) by blocks of row indices; a None block of
+        length L gives L zero rows."""
+        wq, sc = t
+        ws, ss, bs = [], [], []
+        for blk in idx_blocks:
+            if isinstance(blk, int):
+                ws.append(np.zeros((blk, wq.shape[1]), wq.dtype)), ss.append(np.zeros(blk, sc.dtype))
+                bs.append(np.zeros(blk, np.float16))
+            else:
+                ws.append(wq[blk]), ss.append(sc[blk])
+                if bias is not None:
+                    bs.append(bias[blk])
+        out = (np.ascontiguousarray(np.concatenate(ws)), np.concatenate(ss))
+        return out if bias is None else (out, np.concatenate(bs))
 
-    def cols(t, s):
-        return np.ascontiguousarray(t[0][:, s]), t[1]
+    def take_cols(t, idx_blocks):
+        wq, sc = t
+        cols = [np.zeros((wq.shape[0], blk), wq.dtype) if isinstance(blk, int) else wq[:, blk] for blk in idx_blocks]
+        return np.ascontiguousarray(np.concatenate(cols, axis=1)), sc
 
+    def head_rows(h, base=0):
+        return D if h is None else slice(base + h * D, base + (h + 1) * D)
+
+    q_blocks = [head_rows(h) for h in q_heads]
+    k_blocks = [head_rows(h, nq) for h in kv_heads]
+    v_blocks = [head_rows(h, nq + nkv) for h in kv_heads]
+    pad = ipad - (g1 - g0)
+    gate_blocks = [slice(g0, g1)] + ([pad] if pad else [])
+    up_blocks = [slice(cfg.inter + g0, cfg.inter + g1)] + ([pad] if pad else [])
     layers = []
     for lw in w["layers"]:
-        layers.append(dict(ln1=lw["ln1"], ln2=lw["ln2"], qkv=rows(lw["qkv"], qs, ks, vs),
-                           qkv_bias=np.concatenate([lw["qkv_bias"][s] for s in (qs, ks, vs)]),
-                           o=cols(lw["o"], qs), gate_up=rows(lw["gate_up"], gs, us), down=cols(lw["down"], gs)))
+        qkv, qkv_bias = take_rows(lw["qkv"], q_blocks + k_blocks + v_blocks, lw["qkv_bias"])
+        layers.append(dict(ln1=lw["ln1"], ln2=lw["ln2"], qkv=qkv, qkv_bias=qkv_bias,
+                           o=take_cols(lw["o"], q_blocks), gate_up=take_rows(lw["gate_up"], gate_blocks + up_blocks),
+                           down=take_cols(lw["down"], gate_blocks)))
     return dict(embed=w["embed"], layers=layers, ln_f=w["ln_f"],
-                lm_head=rows(w["lm_head"], slice(rank * vv, (rank + 1) * vv)))
+                lm_head=take_rows(w["lm_head"], [slice(rank * vv, (rank + 1) * vv)]))
 
 
 def interleave_gate_up(wq, scale):
@@ -116,7 +182,6 @@ class Decoder:
 
     def __init__(self, cfg, weights, max_batch, num_pages, ctx=None, device=0, world=1, rank=0, group=None):
         self.cfg, self.world, self.rank, self.group = cfg, world, rank, group
-        self.parallelism = f"tp{world}"
         self.ctx = ctx or Context(device)
         dev = self.ctx.device
         w = shard_weights(cfg, weights, world, rank)
@@ -124,8 +189,11 @@ class Decoder:
         self.embed, self.ln_f = t(w["embed"]), t(w["ln_f"])
         self.lm_w, self.lm_s = t(w["lm_head"][0]), t(w["lm_head"][1])
         self.layers = []
-        self.hq, self.hkv = cfg.q_heads // world, cfg.kv_heads // world
-        self.inter = cfg.inter // world
+        plan = shard_plan(cfg, world)
+        self.hq, self.hkv = plan["hq"], plan["hkv"]
+        self.inter = plan["inter_pad"] if world > 1 else cfg.inter
+        self.parallelism = (f"tp{world}: {self.hq} q + {self.hkv} kv heads, MLP {self.inter} per rank" +
+                            (f", each kv head on {plan['rep']} ranks" if plan["rep"] > 1 else "")) if world > 1 else "tp1"
         for lw in w["layers"]:
             lw = dict(lw, gate_up=interleave_gate_up(*lw["gate_up"]))  # SwiGLU runs in the gate/up MatMul's epilogue
             self.layers.append(dict(

@@ -87,7 +87,10 @@ def tp_step(cfg, sharded, cos, sin, k_pools, v_pools, token_ids, positions, bloc
     (ranks' vocabulary slices concatenated)."""
     world = len(sharded)
     B, D = len(token_ids), cfg.head_dim
-    hq, hkv, inter = cfg.q_heads // world, cfg.kv_heads // world, cfg.inter // world
+    # per-rank sizes from the sharded weights themselves (ranks may carry zero heads / channels as padding)
+    hkv = k_pools[0][0].shape[1]
+    hq = sharded[0]["layers"][0]["qkv"][0].shape[0] // D - 2 * hkv
+    inter = sharded[0]["layers"][0]["gate_up"][0].shape[0] // 2
     x = sharded[0]["embed"][np.clip(token_ids, 0, cfg.vocab - 1)].copy()
     delta = None
     for li in range(cfg.layers):
@@ -115,3 +118,32 @@ def tp_step(cfg, sharded, cos, sin, k_pools, v_pools, token_ids, positions, bloc
         delta = sum(p.astype(f32) for p in parts).astype(f16)
     x, h = add_rmsnorm(x, delta, sharded[0]["ln_f"], cfg.eps)
     return np.concatenate([gemv_w8a16(h, s["lm_head"][0], s["lm_head"][1]) for s in sharded], axis=1)
+
+
+def rank_step(cfg, shard, cos, sin, k_pools, v_pools, token_ids, positions, block_table, all_reduce):
+    """One tensor-parallel rank's decode step: `shard` = this rank's weights, k_pools / v_pools [layer] its local
+    KV pages, `all_reduce(f32 array) -> f32 array` the sum over ranks (a real collective in the multi-process
+    tests). Returns this rank's slice of the logits."""
+    B, D = len(token_ids), cfg.head_dim
+    hkv = k_pools[0].shape[1]
+    hq = shard["layers"][0]["qkv"][0].shape[0] // D - 2 * hkv
+    inter = shard["layers"][0]["gate_up"][0].shape[0] // 2
+    x = shard["embed"][np.clip(token_ids, 0, cfg.vocab - 1)].copy()
+    delta = None
+    for li, lw in enumerate(shard["layers"]):
+        x, h = add_rmsnorm(x, delta, lw["ln1"], cfg.eps)
+        qkv = gemv_w8a16(h, lw["qkv"][0], lw["qkv"][1], lw["qkv_bias"])
+        q = rope(qkv[:, :hq * D].reshape(B, hq, D), cos, sin, positions)
+        k = rope(qkv[:, hq * D:(hq + hkv) * D].reshape(B, hkv, D), cos, sin, positions)
+        v = qkv[:, (hq + hkv) * D:].reshape(B, hkv, D)
+        for b in range(B):
+            page = block_table[b, positions[b] // cfg.page]
+            k_pools[li][page, :, positions[b] % cfg.page] = k[b]
+            v_pools[li][page, :, positions[b] % cfg.page] = v[b]
+        attn = A.paged_attention_decode(q, k_pools[li], v_pools[li], block_table, positions + 1)
+        proj = all_reduce(gemv_w8a16(attn.reshape(B, hq * D), lw["o"][0], lw["o"][1]).astype(f32)).astype(f16)
+        x, h = add_rmsnorm(x, proj, lw["ln2"], cfg.eps)
+        act = swiglu(gemv_w8a16(h, lw["gate_up"][0], lw["gate_up"][1]), inter)
+        delta = all_reduce(gemv_w8a16(act, lw["down"][0], lw["down"][1]).astype(f32)).astype(f16)
+    x, h = add_rmsnorm(x, delta, shard["ln_f"], cfg.eps)
+    return gemv_w8a16(h, shard["lm_head"][0], shard["lm_head"][1])

@@ -1,5 +1,6 @@
-"""Tensor-parallel decode on two GPUs (NCCL all-reduce after the o and down projections) against
-the single-GPU decode of the same model. Skipped when fewer than two GPUs are visible."""
+"""Tensor-parallel decode on two and four GPUs (NCCL all-reduce after the o and down projections) against
+the single-GPU decode of the same model. Four ranks share the two kv heads pairwise and pad the query-head
+groups (see nncase_b200.decoder.shard_plan). Skipped when too few GPUs are visible."""
 import os
 import socket
 
@@ -36,10 +37,10 @@ def _worker(rank, world, port, q):
                rng.normal(0, 1, (num_pages, cfg.kv_heads, 16, 64)).astype(np.float16)) for _ in range(cfg.layers)]
         ctx = Context(rank)
         tp = D.Decoder(cfg, w, B, num_pages, ctx=ctx, world=world, rank=rank)
-        hk = cfg.kv_heads // world
+        heads = D.rank_kv_heads(cfg, world, rank)
         for li in range(cfg.layers):
-            tp.layers[li]["k_pool"].copy_(torch.from_numpy(kv[li][0][:, rank * hk:(rank + 1) * hk]))
-            tp.layers[li]["v_pool"].copy_(torch.from_numpy(kv[li][1][:, rank * hk:(rank + 1) * hk]))
+            tp.layers[li]["k_pool"].copy_(torch.from_numpy(np.ascontiguousarray(kv[li][0][:, heads])))
+            tp.layers[li]["v_pool"].copy_(torch.from_numpy(np.ascontiguousarray(kv[li][1][:, heads])))
         local = tp.step(ids, pos, table)
         parts = [torch.empty_like(local) for _ in range(world)]
         dist.all_gather(parts, local.contiguous())
@@ -57,14 +58,15 @@ def _worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
-def test_tp2_matches_single_gpu():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+@pytest.mark.parametrize("world", [2, 4])
+def test_tp_matches_single_gpu(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
     got, want = q.get(timeout=300)
