@@ -128,6 +128,9 @@ NNCB_API int nncb_nhwc_to_nchw_u8(nncb_context *ctx, const uint8_t *in, uint8_t 
 /* binary add (kernels::stackvm::binary, tensor_ops.cpp:70-89) between quantized tensors:
  *   y = quantize(dequantize(a) + dequantize(b)) */
 NNCB_API int nncb_qadd_u8(nncb_context *ctx, const uint8_t *a, const uint8_t *b, uint8_t *y, size_t n, float sa, int32_t za, float sb, int32_t zb, float so, int32_t zo);
+/* the other binary operators of kernels::stackvm::binary (reference/binary.cpp:28-123), numbered like the reference's
+ * binary_op_t: 0 add, 1 sub, 2 mul, 5 min, 6 max:   y = quantize(op(dequantize(a), dequantize(b))) */
+NNCB_API int nncb_qbinary_u8(nncb_context *ctx, int op, const uint8_t *a, const uint8_t *b, uint8_t *y, size_t n, float sa, int32_t za, float sb, int32_t zb, float so, int32_t zo);
 /* y = quantize(clamp(dequantize(x), lo, hi)) -- clamp/relu/relu6 between quant params
  * (kernels::stackvm::clamp / relu, reference/activation.cpp:32-55). Runs as a 256-entry table. */
 NNCB_API int nncb_requant_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, size_t n, float si, int32_t zi, float so, int32_t zo, float lo, float hi);
@@ -157,6 +160,11 @@ NNCB_API int nncb_lut_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, size_t
 /* reduce_window2d max (tensor_ops.cpp: reduce_window2d, reference/reduce_window.cpp:35-105):
  * windows overlapping the padding also take the real value 0 (the zero point) into the max. */
 NNCB_API int nncb_maxpool_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, int n, int h, int w, int c, int kh, int kw, int stride_h, int stride_w, int pad_t, int pad_b, int pad_l, int pad_r, int32_t zero_point);
+/* reduce_window2d with any reducer of the reference (reduce_op_t: 0 mean, 1 min, 2 max, 3 sum; reference/reduce_window.cpp:
+ * 35-182) between quant params (si, zi) -> (so, zo). Taps outside the image contribute the real value 0. max / min work on
+ * the bytes and requantise; sum and mean accumulate exactly:
+ *   v = (float)(sum_valid q - cnt_valid * zi) * si;  mean: v / (float)(count_include_pad ? kh*kw : cnt_valid);  y = quantize(v) */
+NNCB_API int nncb_reduce_window2d_u8(nncb_context *ctx, int op, const uint8_t *x, uint8_t *y, int n, int h, int w, int c, int kh, int kw, int stride_h, int stride_w, int pad_t, int pad_b, int pad_l, int pad_r, int count_include_pad, float si, int32_t zi, float so, int32_t zo);
 /* reduce_window2d mean over the whole image:
  *   mean = ((float)(sum q - cnt*zi) * si) / (float)cnt ; y = quantize(mean, so, zo) */
 NNCB_API int nncb_global_avgpool_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, int n, int h, int w, int c, float si, int32_t zi, float so, int32_t zo);

@@ -115,6 +115,10 @@ int qadd_u8(nncb_context *, const uint8_t *, const uint8_t *, uint8_t *, size_t,
 int lut_u8(nncb_context *, const uint8_t *, uint8_t *, size_t, const uint8_t *);
 int maxpool_u8(nncb_context *, const uint8_t *, uint8_t *, int, int, int, int, int, int, int, int, int, int, int, int, int32_t);
 int global_avgpool_u8(nncb_context *, const uint8_t *, uint8_t *, int, int, int, int, float, int32_t, float, int32_t);
+int reduce_window2d_u8(nncb_context *, int, const uint8_t *, uint8_t *, int, int, int, int, int, int, int, int, int, int, int, int,
+                       int, float, int32_t, float, int32_t);
+int qbinary_u8(nncb_context *, int, const uint8_t *, const uint8_t *, uint8_t *, size_t, float, int32_t, float, int32_t, float,
+               int32_t);
 int softmax_f32(nncb_context *, const float *, float *, size_t, int, float);
 
 size_t paged_attention_scratch_bytes(int B, int Hq, int splits);
@@ -499,6 +503,21 @@ int nncb_maxpool_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, int n, int 
 int nncb_global_avgpool_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, int n, int h, int w, int c, float si, int32_t zi, float so, int32_t zo) {
     CHECK_CTX(ctx);
     return global_avgpool_u8(ctx, x, y, n, h, w, c, si, zi, so, zo);
+}
+
+int nncb_reduce_window2d_u8(nncb_context *ctx, int op, const uint8_t *x, uint8_t *y, int n, int h, int w, int c, int kh, int kw,
+                            int stride_h, int stride_w, int pad_t, int pad_b, int pad_l, int pad_r, int count_include_pad,
+                            float si, int32_t zi, float so, int32_t zo) {
+    CHECK_CTX(ctx);
+    if (!x || !y)
+        return fail(-EINVAL, "nncb_reduce_window2d_u8: null pointer");
+    return reduce_window2d_u8(ctx, op, x, y, n, h, w, c, kh, kw, stride_h, stride_w, pad_t, pad_b, pad_l, pad_r,
+                              count_include_pad, si, zi, so, zo);
+}
+int nncb_qbinary_u8(nncb_context *ctx, int op, const uint8_t *a, const uint8_t *b, uint8_t *y, size_t n, float sa, int32_t za,
+                    float sb, int32_t zb, float so, int32_t zo) {
+    CHECK_CTX(ctx);
+    return qbinary_u8(ctx, op, a, b, y, n, sa, za, sb, zb, so, zo);
 }
 
 // ---- decode-step operators -----------------------------------------------------------------

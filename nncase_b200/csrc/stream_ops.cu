@@ -933,4 +933,119 @@ int softmax_f32(nncb_context *ctx, const float *in, float *out, size_t rows, int
     return after_launch(ctx, "softmax_f32");
 }
 
+
+// ---- reduce_window2d with any of the reference's four reducers, and the other binary operators -------------
+// General forms (one thread per output element, channels fastest so that a warp's accesses are contiguous); the
+// shapes the benchmark networks use have the specialised kernels above. Arithmetic as stated with the entry
+// points in the public header; the output division is the IEEE one.
+// OP: 0 mean, 1 min, 2 max, 3 sum (reduce_op_t).
+template <int OP>
+__global__ void __launch_bounds__(256)
+reduce_window2d_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ y, int n, int h, int w, int c, int oh, int ow,
+                       int kh, int kw, int sh, int sw, int pt, int pl, int count_include_pad, float si, int zi, float so,
+                       float zo) {
+    const size_t total = (size_t)n * oh * ow * c;
+    const int zq = min(max(zi, 0), 255);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int ch = (int)(i % c);
+        const size_t p = i / c;
+        const int ox = (int)(p % ow), oy = (int)((p / ow) % oh), b = (int)(p / ((size_t)ow * oh));
+        int mx = -1, mn = 256, cnt = 0, sum = 0;
+        for (int ky = 0; ky < kh; ky++) {
+            const int iy = oy * sh - pt + ky;
+            if (iy < 0 || iy >= h)
+                continue;
+            for (int kx = 0; kx < kw; kx++) {
+                const int ix = ox * sw - pl + kx;
+                if (ix < 0 || ix >= w)
+                    continue;
+                const int v = x[(((size_t)b * h + iy) * w + ix) * c + ch];
+                mx = max(mx, v), mn = min(mn, v), sum += v, cnt++;
+            }
+        }
+        float r;
+        if (OP == 1 || OP == 2) {
+            int q = OP == 2 ? mx : mn;
+            if (cnt < kh * kw)
+                q = OP == 2 ? max(q, zq) : min(q, zq); // a tap outside the image holds the real value 0
+            r = dequant_dev((float)q, (float)zi, si);
+        } else {
+            r = __fmul_rn((float)(sum - cnt * zi), si);
+            if (OP == 0)
+                r = __fdiv_rn(r, (float)(count_include_pad ? kh * kw : cnt));
+        }
+        y[i] = (uint8_t)quant_dev(r, so, zo, 0, 255);
+    }
+}
+
+int reduce_window2d_u8(nncb_context *ctx, int op, const uint8_t *x, uint8_t *y, int n, int h, int w, int c, int kh, int kw,
+                       int sh, int sw, int pt, int pb, int pl, int pr, int count_include_pad, float si, int32_t zi, float so,
+                       int32_t zo) {
+    if (n <= 0 || h <= 0 || w <= 0 || c <= 0 || kh <= 0 || kw <= 0 || sh <= 0 || sw <= 0 || pt < 0 || pb < 0 || pl < 0 ||
+        pr < 0)
+        return fail(-EINVAL, "reduce_window2d_u8: bad shape");
+    if (!(si > 0) || !(so > 0))
+        return fail(-EINVAL, "reduce_window2d_u8: scales must be positive");
+    if (pt >= kh || pb >= kh || pl >= kw || pr >= kw)
+        return fail(-EINVAL, "reduce_window2d_u8: padding as large as the window leaves windows without a tap");
+    const int oh = conv_out_size(h, kh, sh, 1, pt, pb), ow = conv_out_size(w, kw, sw, 1, pl, pr);
+    if (oh <= 0 || ow <= 0)
+        return fail(-EINVAL, "reduce_window2d_u8: empty output");
+    const size_t total = (size_t)n * oh * ow * c;
+    const int grid = stream_grid(ctx, total, 256);
+#define NNCB_RW(OP_)                                                                                                  \
+    reduce_window2d_kernel<OP_><<<grid, 256, 0, ctx->stream>>>(x, y, n, h, w, c, oh, ow, kh, kw, sh, sw, pt, pl,      \
+                                                               count_include_pad, si, zi, so, (float)zo)
+    switch (op) {
+    case 0: NNCB_RW(0); break;
+    case 1: NNCB_RW(1); break;
+    case 2: NNCB_RW(2); break;
+    case 3: NNCB_RW(3); break;
+    default: return fail(-ENOSYS, "reduce_window2d_u8: reducer %d (0 mean, 1 min, 2 max, 3 sum)", op);
+    }
+#undef NNCB_RW
+    return after_launch(ctx, "reduce_window2d_u8");
+}
+
+// OP: 1 sub, 2 mul, 5 min, 6 max (binary_op_t; add has its own kernel)
+template <int OP>
+__global__ void __launch_bounds__(256)
+qbinary_kernel(const uint8_t *__restrict__ a, const uint8_t *__restrict__ b, uint8_t *__restrict__ y, size_t n, float sa,
+               float za, float sb, float zb, float so, float zo) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const float fa = dequant_dev((float)a[i], za, sa), fb = dequant_dev((float)b[i], zb, sb);
+        float r;
+        if (OP == 1)
+            r = __fsub_rn(fa, fb);
+        else if (OP == 2)
+            r = __fmul_rn(fa, fb);
+        else if (OP == 5)
+            r = fa < fb ? fa : fb;
+        else
+            r = fa > fb ? fa : fb;
+        y[i] = (uint8_t)quant_dev(r, so, zo, 0, 255);
+    }
+}
+
+int qbinary_u8(nncb_context *ctx, int op, const uint8_t *a, const uint8_t *b, uint8_t *y, size_t n, float sa, int32_t za,
+               float sb, int32_t zb, float so, int32_t zo) {
+    if (op == 0)
+        return qadd_u8(ctx, a, b, y, n, sa, za, sb, zb, so, zo);
+    if (n == 0)
+        return 0;
+    if (!a || !b || !y)
+        return fail(-EINVAL, "qbinary_u8: null pointer");
+    const int grid = stream_grid(ctx, n, 256);
+#define NNCB_QB(OP_) qbinary_kernel<OP_><<<grid, 256, 0, ctx->stream>>>(a, b, y, n, sa, (float)za, sb, (float)zb, so, (float)zo)
+    switch (op) {
+    case 1: NNCB_QB(1); break;
+    case 2: NNCB_QB(2); break;
+    case 5: NNCB_QB(5); break;
+    case 6: NNCB_QB(6); break;
+    default: return fail(-ENOSYS, "qbinary_u8: operator %d (0 add, 1 sub, 2 mul, 5 min, 6 max)", op);
+    }
+#undef NNCB_QB
+    return after_launch(ctx, "qbinary_u8");
+}
+
 } // namespace nncb

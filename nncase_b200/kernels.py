@@ -264,6 +264,32 @@ class Context:
                                         qp.zero_point))
         return y
 
+    REDUCE_OPS = {"mean": 0, "min": 1, "max": 2, "sum": 3}    # reduce_op_t of the reference
+    BINARY_OPS = {"add": 0, "sub": 1, "mul": 2, "min": 5, "max": 6}  # binary_op_t
+
+    def reduce_window2d(self, op, x, qi, qo, filter, stride, padding, count_include_pad=False):
+        """kernels::stackvm::reduce_window2d between quant params: op in mean / min / max / sum; x u8 NHWC;
+        padding = (top, bottom, left, right)."""
+        x = self._cuda(x, torch.uint8)
+        n, h, w, c = x.shape
+        oh = (h + padding[0] + padding[1] - filter[0]) // stride[0] + 1
+        ow = (w + padding[2] + padding[3] - filter[1]) // stride[1] + 1
+        y = torch.empty((n, oh, ow, c), dtype=torch.uint8, device=self.device)
+        check(self._lib.nncb_reduce_window2d_u8(self._h, self.REDUCE_OPS[op], x.data_ptr(), y.data_ptr(), n, h, w, c,
+                                                filter[0], filter[1], stride[0], stride[1], *padding, int(count_include_pad),
+                                                qi.scale, qi.zero_point, qo.scale, qo.zero_point))
+        return y
+
+    def binary(self, op, a, qa, b, qb, qo):
+        """kernels::stackvm::binary between quantized tensors of equal shape: op in add / sub / mul / min / max."""
+        a, b = self._cuda(a, torch.uint8), self._cuda(b, torch.uint8)
+        if a.shape != b.shape:
+            raise NncbError(-22, "binary: shapes differ")
+        y = torch.empty_like(a)
+        check(self._lib.nncb_qbinary_u8(self._h, self.BINARY_OPS[op], a.data_ptr(), b.data_ptr(), y.data_ptr(), a.numel(),
+                                        qa.scale, qa.zero_point, qb.scale, qb.zero_point, qo.scale, qo.zero_point))
+        return y
+
     def global_mean(self, x, qi, qo):
         x = self._cuda(x, torch.uint8)
         n, h, w, c = x.shape
@@ -323,12 +349,15 @@ class Context:
     def mat_mul(self, a, weights_nk, w_zp, mult, bias, a_zp, out_qp, **kw):
         """[M,K] u8 x [N,K] weights -> [M,N]: the 1x1 convolution n=1,h=1,w=M,c=K."""
         a = self._cuda(a, torch.uint8)
-        m, k = a.shape
+        # leading dimensions are batches of rows over the same weights (the broadcast rhs of the reference's
+        # batched mat_mul, reference/matmul.cpp:57-89): they fold into M
+        lead, k = tuple(a.shape[:-1]), a.shape[-1]
+        m = int(np.prod(lead))
         w = np.ascontiguousarray(weights_nk).reshape(weights_nk.shape[0], 1, 1, k)
-        out = self.conv2d(a.view(1, 1, m, k), w, w_zp, mult, bias, a_zp, out_qp, **kw)
+        out = self.conv2d(a.reshape(1, 1, m, k), w, w_zp, mult, bias, a_zp, out_qp, **kw)
         if isinstance(out, tuple):
-            return tuple(o.view(m, -1) for o in out)
-        return out.view(m, -1)
+            return tuple(o.view(*lead, -1) for o in out)
+        return out.view(*lead, -1)
 
     def _cuda(self, t, dtype=None):
         if isinstance(t, np.ndarray):

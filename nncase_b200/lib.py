@@ -86,6 +86,8 @@ SIGNATURES = {
     "nncb_resize_nearest_u8": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _I]),
     "nncb_lut_u8": (_I, [_VP, _VP, _VP, _SZ, _VP]),
     "nncb_maxpool_u8": (_I, [_VP, _VP, _VP] + [_I] * 12 + [_I32]),
+    "nncb_reduce_window2d_u8": (_I, [_VP, _I, _VP, _VP] + [_I] * 13 + [_F, _I32, _F, _I32]),
+    "nncb_qbinary_u8": (_I, [_VP, _I, _VP, _VP, _VP, _SZ, _F, _I32, _F, _I32, _F, _I32]),
     "nncb_global_avgpool_u8": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _F, _I32, _F, _I32]),
     "nncb_qconv2d_create": (_I, [_VP, C.POINTER(Conv2dDesc), _VP, _VP, _VP, _VP, _VP, C.POINTER(_VP)]),
     "nncb_qconv2d_destroy": (_I, [_VP]),

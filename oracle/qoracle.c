@@ -404,6 +404,71 @@ void qo_maxpool_u8(const uint8_t *x, uint8_t *y, int n, int h, int w, int c, int
                 }
 }
 
+
+/* reduce_window2d (kernels::stackvm::reduce_window2d, reference/reduce_window.cpp:35-182) between quantized
+ * tensors, u8 NHWC. op follows reduce_op_t: 0 mean, 1 min, 2 max, 3 sum. A tap outside the image contributes
+ * the real value 0 (:86-90), i.e. the input zero point. max / min are monotone, so they run on the bytes and the
+ * result is requantised from (si, zi) to (so, zo); sum and mean accumulate exactly in integers:
+ *   v = (float)(sum_valid q - cnt_valid * zi) * si;   mean: v / (float)(count_include_pad ? kh*kw : cnt_valid)
+ *   y = quantize(v, so, zo)
+ * (the reference sums the dequantized floats tap by tap; the two agree up to its float summation order). */
+void qo_reduce_window2d_u8(int op, const uint8_t *x, uint8_t *y, int n, int h, int w, int c, int kh, int kw,
+                           int sh, int sw, int pt, int pb, int pl, int pr, int count_include_pad, float si,
+                           int32_t zi, float so, int32_t zo) {
+    const int oh = out_size(h, kh, sh, 1, pt, pb), ow = out_size(w, kw, sw, 1, pl, pr);
+    for (int b = 0; b < n; b++)
+        for (int oy = 0; oy < oh; oy++)
+            for (int ox = 0; ox < ow; ox++)
+                for (int ch = 0; ch < c; ch++) {
+                    int mx = -1, mn = 256, cnt = 0;
+                    int32_t sum = 0;
+                    for (int ky = 0; ky < kh; ky++) {
+                        int iy = oy * sh - pt + ky;
+                        if (iy < 0 || iy >= h)
+                            continue;
+                        for (int kx = 0; kx < kw; kx++) {
+                            int ix = ox * sw - pl + kx;
+                            if (ix < 0 || ix >= w)
+                                continue;
+                            int v = x[(((size_t)b * h + iy) * w + ix) * c + ch];
+                            mx = v > mx ? v : mx;
+                            mn = v < mn ? v : mn;
+                            sum += v;
+                            cnt++;
+                        }
+                    }
+                    float r;
+                    if (op == 1 || op == 2) {
+                        int q = op == 2 ? mx : mn;
+                        if (cnt < kh * kw) {
+                            int z = clampi(zi, 0, 255);
+                            q = op == 2 ? (z > q ? z : q) : (z < q ? z : q);
+                        }
+                        r = ((float)q - (float)zi) * si;
+                    } else {
+                        r = (float)(sum - cnt * zi) * si;
+                        if (op == 0)
+                            r = r / (float)(count_include_pad ? kh * kw : cnt);
+                    }
+                    y[(((size_t)b * oh + oy) * ow + ox) * c + ch] = (uint8_t)quant1(r, so, (float)zo, 0, 255);
+                }
+}
+
+/* Element-wise binary operators between quantized tensors (kernels::stackvm::binary, reference/binary.cpp:28-123):
+ *   y = quantize(op(dequantize(a), dequantize(b)));  op follows binary_op_t: 0 add, 1 sub, 2 mul, 5 min, 6 max. */
+int qo_qbinary_u8(int op, const uint8_t *a, const uint8_t *b, uint8_t *y, size_t n, float sa, int32_t za,
+                  float sb, int32_t zb, float so, int32_t zo) {
+    if (op != 0 && op != 1 && op != 2 && op != 5 && op != 6)
+        return -1;
+    for (size_t i = 0; i < n; i++) {
+        float fa = ((float)a[i] - (float)za) * sa;
+        float fb = ((float)b[i] - (float)zb) * sb;
+        float r = op == 0 ? fa + fb : op == 1 ? fa - fb : op == 2 ? fa * fb : op == 5 ? (fa < fb ? fa : fb) : (fa > fb ? fa : fb);
+        y[i] = (uint8_t)quant1(r, so, (float)zo, 0, 255);
+    }
+    return 0;
+}
+
 /* Global mean over H x W (reduce_window2d mean with the window covering the image,
  * reference/reduce_window.cpp:133-135) on u8 NHWC:
  *   mean = ((float)(sum q - cnt * zi) * si) / (float)cnt ;  yq = quantize(mean).

@@ -148,6 +148,30 @@ def maxpool_u8(x, k, s, pad, zp):
     return y
 
 
+REDUCE_OPS = {"mean": 0, "min": 1, "max": 2, "sum": 3}   # reduce_op_t
+BINARY_OPS = {"add": 0, "sub": 1, "mul": 2, "min": 5, "max": 6}  # binary_op_t
+
+
+def reduce_window2d_u8(op, x, k, s, pad, si, zi, so, zo, count_include_pad=False):
+    x = np.ascontiguousarray(x, np.uint8)
+    n, h, w, c = x.shape
+    oh = out_size(h, k[0], s[0], 1, pad[0], pad[1])
+    ow = out_size(w, k[1], s[1], 1, pad[2], pad[3])
+    y = np.empty((n, oh, ow, c), np.uint8)
+    lib().qo_reduce_window2d_u8(REDUCE_OPS[op], _p(x), _p(y), n, h, w, c, k[0], k[1], s[0], s[1], pad[0], pad[1], pad[2],
+                                pad[3], int(count_include_pad), C.c_float(si), C.c_int32(zi), C.c_float(so), C.c_int32(zo))
+    return y
+
+
+def qbinary_u8(op, a, b, sa, za, sb, zb, so, zo):
+    a = np.ascontiguousarray(a, np.uint8)
+    b = np.ascontiguousarray(b, np.uint8)
+    y = np.empty(a.shape, np.uint8)
+    assert lib().qo_qbinary_u8(BINARY_OPS[op], _p(a), _p(b), _p(y), C.c_size_t(a.size), C.c_float(sa), C.c_int32(za),
+                               C.c_float(sb), C.c_int32(zb), C.c_float(so), C.c_int32(zo)) == 0
+    return y
+
+
 def global_avgpool_u8(x, si, zi, so, zo):
     x = np.ascontiguousarray(x, np.uint8)
     n, h, w, c = x.shape

@@ -357,3 +357,18 @@ def test_int8_peak_selftest_runs(ctx):
         L.check(ctx._lib.nncb_selftest_int8_peak(ctx._h, 4096, 3, signed, C.byref(best), C.byref(mean)))
         ctx.check_status()
         assert best.value >= mean.value > 1000.0, (best.value, mean.value)
+
+
+def test_batched_matmul_with_broadcast_weights(ctx, qo):
+    """[B1, B2, M, K] x [K, N]: leading dimensions are batches of rows over one constant right-hand side, the
+    broadcast case of the reference's mat_mul (reference/matmul.cpp:57-89)."""
+    rng = np.random.default_rng(51)
+    a = rng.integers(0, 256, (2, 3, 40, 64), dtype=np.uint8)
+    wq = rng.integers(0, 256, (48, 64), dtype=np.uint8)
+    zw = rng.integers(100, 150, 48).astype(np.int32)
+    mult = rng.uniform(2e-5, 6e-5, 48).astype(np.float32)
+    bias = rng.normal(0, 0.2, 48).astype(np.float32)
+    oqp = QuantParam(120, 0.02)
+    got = ctx.mat_mul(torch.from_numpy(a), wq, zw, mult, bias, 117, oqp).cpu().numpy()
+    want = qo.qconv2d_u8(a.reshape(1, 1, -1, 64), wq.reshape(48, 1, 1, 64), zw, mult, bias, 117, oqp.scale, oqp.zero_point)
+    assert got.shape == (2, 3, 40, 48) and np.array_equal(got.reshape(-1, 48), want.reshape(-1, 48))

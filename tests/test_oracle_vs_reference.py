@@ -178,3 +178,41 @@ def test_library_activation_tables_match_oracle(qo):
 def test_softmax_vs_reference(qo, ref):
     x = np.random.default_rng(6).normal(0, 3, (37, 1000)).astype(np.float32)
     assert np.array_equal(qo.softmax_f32(x), ref.softmax_f32(x))
+
+
+@pytest.mark.parametrize("op,code", [("mean", 0), ("min", 1), ("max", 2), ("sum", 3)])
+def test_reduce_window2d_vs_reference(qo, ref, op, code):
+    """The quantized reduce_window2d against dequantize -> the reference's reduce_window2d -> quantize, padded and
+    strided, with and without count_include_pad."""
+    import ctypes as C
+    q = np.random.default_rng(41).integers(0, 256, (2, 9, 11, 8), dtype=np.uint8)
+    si, zi, zo = 0.05, 120, 110
+    so = 0.04 * (9 if op == "sum" else 1)
+    xf = ref.dequantize_u8(np.ascontiguousarray(q.transpose(0, 3, 1, 2)), si, zi)
+    init = {"mean": 0.0, "sum": 0.0, "max": float(np.finfo(np.float32).min), "min": float(np.finfo(np.float32).max)}[op]
+    n, c, h, w = xf.shape
+    oh, ow = (h + 2 - 3) // 2 + 1, (w + 2 - 3) // 2 + 1
+    for cip in (False, True):
+        yf = np.empty((n, c, oh, ow), np.float32)
+        S = C.c_size_t
+        assert ref.lib().nncase_ref_reduce_window2d_f32(code, xf.ctypes.data_as(C.c_void_p), C.c_float(init),
+                                                        yf.ctypes.data_as(C.c_void_p), S(n), S(c), S(h), S(w), 3, 3, 2, 2,
+                                                        1, 1, 1, 1, int(cip)) == 0
+        want = ref.quantize_u8(yf, so, zo).transpose(0, 2, 3, 1)
+        got = qo.reduce_window2d_u8(op, q, (3, 3), (2, 2), (1, 1, 1, 1), si, zi, so, zo, cip)
+        d = np.abs(got.astype(int) - want.astype(int))
+        assert d.max() <= 1 and (d != 0).mean() < 0.02  # float summation order of the reference
+
+
+@pytest.mark.parametrize("op,code", [("add", 0), ("sub", 1), ("mul", 2), ("min", 5), ("max", 6)])
+def test_binary_operators_vs_reference(qo, ref, op, code):
+    import ctypes as C
+    rng = np.random.default_rng(42)
+    a = rng.integers(0, 256, 20000, dtype=np.uint8)
+    b = rng.integers(0, 256, 20000, dtype=np.uint8)
+    so = 0.2 if op == "mul" else 0.06
+    fa, fb = ref.dequantize_u8(a, 0.05, 117), ref.dequantize_u8(b, 0.04, 125)
+    yf = np.empty(a.shape, np.float32)
+    assert ref.lib().nncase_ref_binary_f32(code, fa.ctypes.data_as(C.c_void_p), fb.ctypes.data_as(C.c_void_p),
+                                           yf.ctypes.data_as(C.c_void_p), C.c_size_t(a.size)) == 0
+    assert np.array_equal(qo.qbinary_u8(op, a, b, 0.05, 117, 0.04, 125, so, 121), ref.quantize_u8(yf, so, 121))

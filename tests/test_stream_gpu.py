@@ -234,3 +234,34 @@ def test_quantize_to_s2d_padded(ctx, qo, shape, c_pad, pad, nhwc):
     xin = np.ascontiguousarray(x.transpose(0, 2, 3, 1)) if nhwc else x
     got = ctx.quantize_to_s2d_padded(torch.from_numpy(xin), QuantParam(117, 0.021), c_pad, pad, nhwc=nhwc).cpu().numpy()
     assert np.array_equal(got, qo.quantize_nchw_to_s2d_u8(x, 0.021, 117, c_pad, pad))
+
+
+@pytest.mark.parametrize("op", ["mean", "min", "max", "sum"])
+@pytest.mark.parametrize("geom", [((3, 3), (2, 2), (1, 1, 1, 1)), ((2, 2), (2, 2), (0, 0, 0, 0)), ((5, 3), (1, 2), (2, 2, 1, 0)),
+                                  ((7, 7), (1, 1), (0, 0, 0, 0))])
+def test_reduce_window2d_all_reducers(ctx, qo, op, geom):
+    """Windowed mean / min / max / sum (reference/reduce_window.cpp:35-182) on ragged shapes, with and without
+    counting padded taps in the mean."""
+    k, s, pad = geom
+    x = np.random.default_rng(31).integers(0, 256, (2, 13, 10, 24), dtype=np.uint8)
+    qi = QuantParam(120, 0.05)
+    qo_ = QuantParam(90, 0.05 * (k[0] * k[1] if op == "sum" else 1))
+    for cip in (False, True):
+        got = ctx.reduce_window2d(op, torch.from_numpy(x), qi, qo_, k, s, pad, cip).cpu().numpy()
+        want = qo.reduce_window2d_u8(op, x, k, s, pad, qi.scale, qi.zero_point, qo_.scale, qo_.zero_point, cip)
+        assert np.array_equal(got, want)
+    # max with equal quant params is the specialised max-pool
+    if op == "max":
+        assert np.array_equal(ctx.reduce_window2d("max", torch.from_numpy(x), qi, qi, k, s, pad).cpu().numpy(),
+                              qo.maxpool_u8(x, k, s, pad, qi.zero_point))
+
+
+@pytest.mark.parametrize("op", ["add", "sub", "mul", "min", "max"])
+def test_binary_operators(ctx, qo, op):
+    rng = np.random.default_rng(32)
+    a = rng.integers(0, 256, 100003, dtype=np.uint8)
+    b = rng.integers(0, 256, 100003, dtype=np.uint8)
+    qa, qb, qy = QuantParam(117, 0.05), QuantParam(125, 0.04), QuantParam(121, 0.2 if op == "mul" else 0.06)
+    got = ctx.binary(op, torch.from_numpy(a), qa, torch.from_numpy(b), qb, qy).cpu().numpy()
+    want = qo.qbinary_u8(op, a, b, qa.scale, qa.zero_point, qb.scale, qb.zero_point, qy.scale, qy.zero_point)
+    assert np.array_equal(got, want)
