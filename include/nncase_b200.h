@@ -284,6 +284,22 @@ NNCB_API int nncb_paged_attention_decode(nncb_context *ctx, const void *q, const
  * Results are identical to nncb_paged_attention_decode. */
 NNCB_API int nncb_paged_attention_decode_noalloc(nncb_context *ctx, const void *q, const void *k_pool, const void *v_pool, const int32_t *block_table, const int32_t *context_lens, void *out, int batch, int q_heads, int kv_heads, int head_dim, int page_size, int max_pages, int num_pages, float scale);
 
+/* ---- float kernels for calibration ---------------------------------------------------------------
+ * The forward pass the reference's Quantizer runs per calibration sample to collect ranges
+ * (src/Nncase.Quantization/Quantization/Quantizer.cs:389-409) and the range reduction over finite values
+ * (Quantizer.Algorithms.cs:14-30), on the GPU. Semantics of the reference's float kernels: conv2d = bias + sum over
+ * in-image taps, then the fused clamp (reference/convolution.cpp:50-106); max pooling injects the value 0 for taps
+ * outside the image (reference/reduce_window.cpp:86-90); swish in double (kernel_template.h:33-47).
+ * NCHW f32 tensors, OIHW weights, device pointers; bias may be NULL; groups == 1 or depthwise or any divisor. */
+NNCB_API int nncb_conv2d_f32(nncb_context *ctx, const float *x, const float *w, const float *bias, float *y, int n, int c, int h, int wd, int oc, int kh, int kw, int stride_h, int stride_w, int pad_t, int pad_b, int pad_l, int pad_r, int dil_h, int dil_w, int groups, float clamp_lo, float clamp_hi);
+NNCB_API int nncb_clamp_f32(nncb_context *ctx, const float *x, float *y, size_t n, float lo, float hi);
+NNCB_API int nncb_swish_f32(nncb_context *ctx, const float *x, float *y, size_t n);
+NNCB_API int nncb_add_f32(nncb_context *ctx, const float *a, const float *b, float *y, size_t n);
+NNCB_API int nncb_maxpool_f32(nncb_context *ctx, const float *x, float *y, int n, int c, int h, int w, int kh, int kw, int stride_h, int stride_w, int pad_t, int pad_b, int pad_l, int pad_r);
+NNCB_API int nncb_global_mean_f32(nncb_context *ctx, const float *x, float *y, size_t planes, int hw);
+/* min and max over the finite values of x (HOST results; synchronises); (FLT_MAX, -FLT_MAX) when there is none. */
+NNCB_API int nncb_minmax_f32(nncb_context *ctx, const float *x, size_t n, float *min_out, float *max_out);
+
 /* ---- a whole quantized program: the body of one kmodel function of module kind "cuda" -----------
  * The native side of the `cuda` module's runtime_function (the reference's contract:
  * src/Native/include/nncase/runtime/runtime_function.h:59-63 -- initialize_core once, invoke_core per

@@ -9,7 +9,9 @@ This is the host-side stand-in for what the reference does in C# between import 
     (QuantUtility.GetQuantParam, Quantizer.cs:620-661), computed by the library's own host code;
   * lowering of each marked Conv2D / MatMul into the integer kernel call with its fused
     epilogue (what a `cuda` ITarget's RegisterQuantizePass would emit).
-The float forward used for calibration runs on torch (model preparation, not the hot path).
+The float forward used for calibration runs on the library's own float kernels when a CUDA device is given
+(`float_forward_cuda`: nncb_conv2d_f32 and friends, ranges reduced by nncb_minmax_f32) and on torch's CPU
+operators otherwise (model preparation on a machine without a GPU).
 """
 import numpy as np
 import torch
@@ -96,9 +98,154 @@ def float_forward(graph, x, device="cpu", record=None):
     return t[out], t
 
 
+class _FloatCuda:
+    """The float graph on the library's calibration kernels. Tensors are torch CUDA tensors (device memory and
+    views only); every arithmetic operator is a kernel of libnncase_b200.so."""
+
+    def __init__(self, ctx):
+        self.ctx, self.lib, self.h = ctx, ctx._lib, ctx._h
+        self._weights = {}
+
+    def const(self, arr):
+        key = id(arr)
+        if key not in self._weights:
+            self._weights[key] = torch.from_numpy(np.ascontiguousarray(arr, np.float32)).to(self.ctx.device)
+        return self._weights[key]
+
+    def conv(self, x, w, b, stride, pad, dil, groups, lo, hi):
+        n, c, h, wd = x.shape
+        oc, _, kh, kw = w.shape
+        oh = (h + pad[0] + pad[1] - ((kh - 1) * dil[0] + 1)) // stride[0] + 1
+        ow = (wd + pad[2] + pad[3] - ((kw - 1) * dil[1] + 1)) // stride[1] + 1
+        y = torch.empty((n, oc, oh, ow), dtype=torch.float32, device=x.device)
+        L.check(self.lib.nncb_conv2d_f32(self.h, x.data_ptr(), w.data_ptr(), b.data_ptr() if b is not None else None,
+                                         y.data_ptr(), n, c, h, wd, oc, kh, kw, stride[0], stride[1], pad[0], pad[1], pad[2],
+                                         pad[3], dil[0], dil[1], groups, lo, hi))
+        return y
+
+    def clamp(self, x, lo, hi):
+        y = torch.empty_like(x)
+        L.check(self.lib.nncb_clamp_f32(self.h, x.data_ptr(), y.data_ptr(), x.numel(), lo, hi))
+        return y
+
+    def swish(self, x):
+        y = torch.empty_like(x)
+        L.check(self.lib.nncb_swish_f32(self.h, x.data_ptr(), y.data_ptr(), x.numel()))
+        return y
+
+    def add(self, a, b):
+        y = torch.empty_like(a)
+        L.check(self.lib.nncb_add_f32(self.h, a.data_ptr(), b.data_ptr(), y.data_ptr(), a.numel()))
+        return y
+
+    def maxpool(self, x, k, stride, pad):
+        n, c, h, w = x.shape
+        oh = (h + pad[0] + pad[1] - k[0]) // stride[0] + 1
+        ow = (w + pad[2] + pad[3] - k[1]) // stride[1] + 1
+        y = torch.empty((n, c, oh, ow), dtype=torch.float32, device=x.device)
+        L.check(self.lib.nncb_maxpool_f32(self.h, x.data_ptr(), y.data_ptr(), n, c, h, w, k[0], k[1], stride[0], stride[1], *pad))
+        return y
+
+    def global_mean(self, x):
+        n, c, h, w = x.shape
+        y = torch.empty((n, c, 1, 1), dtype=torch.float32, device=x.device)
+        L.check(self.lib.nncb_global_mean_f32(self.h, x.data_ptr(), y.data_ptr(), n * c, h * w))
+        return y
+
+    def minmax(self, x):
+        import ctypes as C
+        x = x.contiguous()
+        mn, mx = C.c_float(), C.c_float()
+        L.check(self.lib.nncb_minmax_f32(self.h, x.data_ptr(), x.numel(), C.byref(mn), C.byref(mx)))
+        return mn.value, mx.value
+
+
+def float_forward_cuda(graph, x, ctx, record=None):
+    """float_forward on the library's own kernels (ctx: nncase_b200.kernels.Context). Slice / Concat / nearest
+    upsampling are data movement and stay tensor views and copies."""
+    k = _FloatCuda(ctx) if not isinstance(ctx, _FloatCuda) else ctx
+    ctx = k.ctx
+    ctx.use_current_stream()
+    t = {}
+    rec = record or (lambda n, v: None)
+    out = None
+    for nd in graph:
+        op = nd["op"]
+        if op == "input":
+            xin = torch.as_tensor(x, dtype=torch.float32).to(ctx.device)
+            if nd.get("layout") == "nhwc":
+                xin = xin.permute(0, 3, 1, 2)
+            t[nd["out"]] = xin.contiguous()
+            rec(nd["out"], t[nd["out"]])
+        elif op == "conv":
+            lo, hi = (-INF, INF) if nd["act"] in (None, "silu") else _ACT_CLAMP[nd["act"]]
+            y = k.conv(t[nd["in"]], k.const(nd["w"]), k.const(nd["b"]), nd["stride"], nd["pad"], nd["dil"], nd["groups"], lo, hi)
+            if nd["act"] == "silu":
+                rec(nd["out"] + "@pre", y)
+                y = k.swish(y)
+            if nd.get("res"):
+                rec(nd["out"] + "@conv", y)
+                y = k.add(y, t[nd["res"]])
+            t[nd["out"]] = y
+            rec(nd["out"], y)
+            if nd.get("relu_out"):
+                t[nd["relu_out"]] = k.clamp(y, 0.0, INF)
+                rec(nd["relu_out"], t[nd["relu_out"]])
+        elif op == "maxpool":
+            t[nd["out"]] = k.maxpool(t[nd["in"]], nd["k"], nd["stride"], nd["pad"])
+            rec(nd["out"], t[nd["out"]])
+        elif op == "relu":
+            t[nd["out"]] = k.clamp(t[nd["in"]], 0.0, INF)
+            rec(nd["out"], t[nd["out"]])
+        elif op == "gap":
+            t[nd["out"]] = k.global_mean(t[nd["in"]])
+            rec(nd["out"], t[nd["out"]])
+        elif op == "fc":
+            xin = t[nd["in"]].reshape(t[nd["in"]].shape[0], -1, 1, 1).contiguous()
+            w = k.const(nd["w"]).reshape(nd["w"].shape[0], -1, 1, 1)
+            t[nd["out"]] = k.conv(xin, w, k.const(nd["b"]), (1, 1), (0, 0, 0, 0), (1, 1), 1, -INF, INF).flatten(1)
+            rec(nd["out"], t[nd["out"]])
+        elif op == "slice":
+            t[nd["out"]] = t[nd["in"]][:, nd["begin"]:nd["end"]].contiguous()
+            rec(nd["out"], t[nd["out"]])
+        elif op == "concat":
+            t[nd["out"]] = torch.cat([t[i] for i in nd["ins"]], 1)
+            rec(nd["out"], t[nd["out"]])
+        elif op == "upsample":
+            t[nd["out"]] = t[nd["in"]].repeat_interleave(nd["factor"], 2).repeat_interleave(nd["factor"], 3).contiguous()
+            rec(nd["out"], t[nd["out"]])
+        elif op == "output":
+            return [t[i] for i in nd["ins"]], t
+        else:
+            raise ValueError(f"unknown node {op}")
+        out = nd["out"]
+    return t[out], t
+
+
+def _is_cuda(device):
+    return str(device).startswith("cuda")
+
+
 def calibrate(graph, samples, device="cpu"):
-    """Union of per-sample (min, max) over finite values for every tensor of the graph."""
+    """Union of per-sample (min, max) over finite values for every tensor of the graph. On a CUDA device the
+    forward pass and the range reduction run on the library's kernels."""
     ranges = {}
+    if _is_cuda(device):
+        dev = torch.device(device)
+        k = _FloatCuda(K.Context(dev.index or 0))
+
+        def rec_cuda(name, v):
+            mn, mx = k.minmax(v)
+            if mn > mx:
+                return  # no finite value
+            ranges[name] = (min(ranges[name][0], mn), max(ranges[name][1], mx)) if name in ranges else (mn, mx)
+
+        with torch.cuda.device(dev):
+            for s in samples:
+                float_forward_cuda(graph, s, k, rec_cuda)
+        k.ctx.synchronize()
+        k.ctx.close()
+        return ranges
 
     def rec(name, v):
         v = v[torch.isfinite(v)]

@@ -106,6 +106,13 @@ SIGNATURES = {
     "nncb_context_set_option": (_I, [_VP, C.c_char_p, C.c_int64]),
     "nncb_context_get_option": (_I, [_VP, C.c_char_p, C.POINTER(C.c_int64)]),
     "nncb_selftest_reciprocal_division": (_I, [_VP, _F, C.c_uint64, C.c_uint64, C.POINTER(C.c_uint64)]),
+    "nncb_conv2d_f32": (_I, [_VP, _VP, _VP, _VP, _VP] + [_I] * 16 + [_F, _F]),
+    "nncb_clamp_f32": (_I, [_VP, _VP, _VP, _SZ, _F, _F]),
+    "nncb_swish_f32": (_I, [_VP, _VP, _VP, _SZ]),
+    "nncb_add_f32": (_I, [_VP, _VP, _VP, _VP, _SZ]),
+    "nncb_maxpool_f32": (_I, [_VP, _VP, _VP] + [_I] * 12),
+    "nncb_global_mean_f32": (_I, [_VP, _VP, _VP, _SZ, _I]),
+    "nncb_minmax_f32": (_I, [_VP, _VP, _SZ, C.POINTER(_F), C.POINTER(_F)]),
     "nncb_program_create": (_I, [_VP, _VP, _SZ, _VP, _SZ, C.POINTER(_VP)]),
     "nncb_program_destroy": (_I, [_VP]),
     "nncb_program_run": (_I, [_VP, _VP, _VP]),
