@@ -37,12 +37,11 @@ SEED_W, SEED_X, SEED_CAL = 1000 + CONFIG_ID, 2000 + CONFIG_ID, 3000 + CONFIG_ID
 METRIC = "u8/u8 ResNet-50 images/s"
 UNIT = "images/s"
 
-# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of the convolution launches of one step PER
-# IMAGE, from a one-pass ncu capture at 128 images (tensors larger than L2, about 2 GB on the device; see
-# profiles/dram_traffic_tc_conv_resnet50v2.md). Traffic grows in proportion to the batch above that size
-# (the full-size capture of the same kernels gave 17.18 GB at 512 images = 33.6 MB per image), so the
-# bench scales this figure by its batch. Keyed by weight type; None = not captured.
-MEASURED_DRAM_BYTES_PER_IMAGE = {"uint8": 17.181e9 / 512}
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum, one-pass ncu captures) of the convolution launches of
+# one step, keyed by (images per GPU, weight type); see profiles/dram_traffic_tc_conv_resnet50v2.md. Traffic
+# does NOT grow in proportion to the batch between these sizes (at 128 images most producer -> consumer tensors
+# never leave the 126 MB L2), so no figure is scaled: other batches report null.
+MEASURED_DRAM_BYTES_PER_STEP = {(512, "uint8"): 17.181e9, (128, "uint8"): 2.861e9}
 
 
 def peaks():
@@ -382,7 +381,7 @@ def run_ours(args):
     intensity = tc_ops / tc_bytes if tc_bytes else 0.0
     ridge = int8_burst * 1e12 / (pk["hbm_gbs"] * 1e9)
     hbm_bound = intensity < ridge
-    per_image = MEASURED_DRAM_BYTES_PER_IMAGE.get(args.w_quant)
+    traffic = MEASURED_DRAM_BYTES_PER_STEP.get((B, args.w_quant))
     line = dict(
         metric=METRIC, value=value, unit=UNIT, n_gpus=world, steps=steps, warmup=warm,
         ms_per_step=ms / steps, higher_is_better=True, scaling="strong", vs_baseline=None, dtype="u8",
@@ -400,9 +399,9 @@ def run_ours(args):
                       achieved=gbs if hbm_bound else achieved, peak=pk["hbm_gbs"] if hbm_bound else int8_burst,
                       unit="GB/s" if hbm_bound else "TFLOP/s",
                       frac=(gbs / pk["hbm_gbs"]) if hbm_bound else achieved / int8_burst,
-                      traffic=per_image * B if per_image else None,
-                      traffic_source="ncu dram__bytes_read.sum + dram__bytes_write.sum of the convolution launches, "
-                                     "per image from a capture at a smaller batch, scaled by this batch",
+                      traffic=traffic,
+                      traffic_source="ncu dram__bytes_read.sum + dram__bytes_write.sum summed over the convolution launches "
+                                     "of one step at this batch (one-pass capture); null where no capture at this batch exists",
                       algorithmic_bytes_per_step=tc_bytes, ops_per_byte=intensity, ridge_ops_per_byte=ridge,
                       peak_source=f"{pk['source']} HBM copy bandwidth; int8 tensor peak measured in this run "
                                   f"(nncb_selftest_int8_peak)",
