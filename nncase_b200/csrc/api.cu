@@ -203,6 +203,8 @@ int nncb_context_create(int device, void *stream, nncb_context **out) {
 static int *option_slot(nncb_context *ctx, const char *name) {
     struct { const char *name; int *slot; } table[] = {
         {"conv.tile_n", &ctx->opt.conv_tile_n},
+        {"conv.mma_issuers", &ctx->opt.conv_mma_issuers},
+        {"conv.load_warps", &ctx->opt.conv_load_warps},
         {"conv.wide_patch", &ctx->opt.conv_wide_patch},
         {"depthwise.dot_product", &ctx->opt.depthwise_dot},
         {"attention.warps", &ctx->opt.attention_warps},

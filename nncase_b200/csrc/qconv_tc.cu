@@ -100,6 +100,8 @@ struct TcGeom {
     uint32_t idesc;
     int f32_out;
     int acc_arrivals;   // epilogue warps that release an accumulator buffer
+    int issuers;        // 2: two warps issue the MMAs, taking the stages of the ring in turn (stages is even then)
+    int load_warps;     // 2: activations and weights are loaded by a warp each
     int kgroup;         // K blocks per pipeline stage (one barrier round trip and one commit for all of them)
     int b_resident;     // the whole weight matrix stays in shared memory (one N tile, small K): loaded once per CTA
     int bx_log2, tiles_x, tiles_y; // MODE_ROWS: patch width 2^bx_log2 (height 128 >> bx_log2), patches per image
@@ -523,13 +525,16 @@ struct TcArgs {
 enum { ERR_PRODUCER = 101, ERR_MMA_FULL = 102, ERR_MMA_ACC = 103, ERR_EPILOGUE = 104, ERR_RESIDUAL = 105 };
 
 constexpr int EPI_WARPS = 16; // four per TMEM lane quadrant: enough warps per scheduler to hide TMEM and shared-memory latency
-constexpr int TC_THREADS = 64 + 32 * EPI_WARPS;
+// warp 0: loads, warp 1: MMAs, warps 2 .. 17: epilogue, warp 18: the second MMA issuer, warp 19: the second
+// load warp (idle in plans that use one of each)
+constexpr int TC_THREADS = 64 + 32 * EPI_WARPS + 64;
+constexpr int WARP_MMA2 = 2 + EPI_WARPS, WARP_LOAD2 = 3 + EPI_WARPS;
 constexpr int MAX_STAGES = 8;
 constexpr int RES_BUFS = 3; // residual sub-tiles in flight per epilogue warp: the fetch of tile i+3 starts when tile i is done
 constexpr int ADD_TABLE_BYTES = 256 * 260; // fused residual add: rows of 256 entries, 260 bytes apart
 
 struct TcShared {
-    uint64_t bar_full[MAX_STAGES], bar_empty[MAX_STAGES], bar_acc_full[2], bar_acc_empty[2], bar_b, bar_res[EPI_WARPS * RES_BUFS];
+    uint64_t bar_full[MAX_STAGES], bar_empty[MAX_STAGES], bar_acc_full[2], bar_acc_empty[2], bar_acc_init[2], bar_b, bar_res[EPI_WARPS * RES_BUFS];
     uint32_t tmem_base_slot;
     volatile int abort_flag;
     unsigned wait_limit_us; // must follow abort_flag: mbar_wait_slow reads it through the flag's address
@@ -562,13 +567,14 @@ __device__ __forceinline__ void tc_setup(const TcGeom &g, TcShared &sh, int warp
         sh.abort_flag = 0;
         sh.wait_limit_us = g.wait_limit_us;
         for (int s = 0; s < g.stages; s++) {
-            mbar_init(smem_u32(&sh.bar_full[s]), 1);
-            mbar_init(smem_u32(&sh.bar_empty[s]), 1);
+            mbar_init(smem_u32(&sh.bar_full[s]), g.load_warps);
+            mbar_init(smem_u32(&sh.bar_empty[s]), g.mode == MODE_PATCH ? g.issuers : 1);
         }
         mbar_init(smem_u32(&sh.bar_b), 1);
         for (int b = 0; b < 2; b++) {
-            mbar_init(smem_u32(&sh.bar_acc_full[b]), 1);
+            mbar_init(smem_u32(&sh.bar_acc_full[b]), g.issuers);
             mbar_init(smem_u32(&sh.bar_acc_empty[b]), g.acc_arrivals);
+            mbar_init(smem_u32(&sh.bar_acc_init[b]), 1);
         }
         for (int w = 0; w < EPI_WARPS * RES_BUFS; w++)
             mbar_init(smem_u32(&sh.bar_res[w]), 1);
@@ -604,8 +610,11 @@ __device__ __forceinline__ void tc_teardown(const TcGeom &g, TcShared &sh, int w
 
 // warp 0, one lane: fills the stage ring with the A (activation) and B (weight) tiles of every
 // K block of every tile this CTA owns.
+// `part`: 0 = this warp loads everything, 1 = the activations only, 2 = the weights only (two load warps: each
+// announces its own bytes on the stage's barrier, which then counts two arrivals)
 __device__ __forceinline__ void producer_loop(const TcGeom &g, const StageGeom &sg, TcShared &sh,
-                                              const CUtensorMap *tmap_a, const CUtensorMap *tmap_b, int *status) {
+                                              const CUtensorMap *tmap_a, const CUtensorMap *tmap_b, int *status,
+                                              const int part) {
     using namespace dev;
     const int k_blocks = g.taps * g.c_blocks;
     const int total_tiles = g.m_tiles * g.n_tiles;
@@ -613,13 +622,14 @@ __device__ __forceinline__ void producer_loop(const TcGeom &g, const StageGeom &
     const int kb = g.kb, c_blocks = g.c_blocks, kw_ = g.kw;
     const uint32_t dil_w = g.dil_w, dil_h = g.dil_h, stages = g.stages;
     const bool b_res = sg.b_resident != 0;
-    const uint32_t kblock_bytes = sg.a_stage_bytes + (b_res ? 0u : sg.b_stage_bytes);
+    const bool load_a = part != 2, load_b = part != 1 && !b_res;
+    const uint32_t kblock_bytes = (load_a ? sg.a_stage_bytes : 0u) + (load_b ? sg.b_stage_bytes : 0u);
     const int kgroup = g.kgroup;
     const uint32_t bar_full0 = smem_u32(&sh.bar_full[0]), bar_empty0 = smem_u32(&sh.bar_empty[0]);
     uint32_t stage = 0, phase = 0;
-    if (g.withhold && blockIdx.x == 0) // self-test: 16 bytes that no load delivers keep stage 0 from ever filling
+    if (g.withhold && blockIdx.x == 0 && load_a) // self-test: 16 bytes that no load delivers keep stage 0 from ever filling
         asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar_full0), "r"(16u) : "memory");
-    if (b_res && (int)blockIdx.x < total_tiles) {
+    if (b_res && (int)blockIdx.x < total_tiles && load_a) {
         // the whole weight matrix, once
         const uint32_t bar_b = smem_u32(&sh.bar_b);
         mbar_expect_tx(bar_b, (uint32_t)k_blocks * sg.b_stage_bytes);
@@ -680,13 +690,15 @@ __device__ __forceinline__ void producer_loop(const TcGeom &g, const StageGeom &
                 const uint32_t full = bar_full0 + stage * 8;
                 const uint32_t sa = sg.smem_base + stage * sg.stage_pitch;
                 mbar_expect_tx(full, kblock_bytes);
-                if (gemm)
-                    tma_load_2d(sa, tmap_a, full, c_off, m0);
-                else if (rows)
-                    tma_load_4d(sa, tmap_a, full, 0, cw, chh + (int)off_h, cn);
-                else
-                    tma_load_im2col_4d(sa, tmap_a, full, c_off, cw, chh, cn, (uint16_t)off_w, (uint16_t)off_h);
-                if (!b_res)
+                if (load_a) {
+                    if (gemm)
+                        tma_load_2d(sa, tmap_a, full, c_off, m0);
+                    else if (rows)
+                        tma_load_4d(sa, tmap_a, full, 0, cw, chh + (int)off_h, cn);
+                    else
+                        tma_load_im2col_4d(sa, tmap_a, full, c_off, cw, chh, cn, (uint16_t)off_w, (uint16_t)off_h);
+                }
+                if (load_b)
                     tma_load_2d(sa + sg.a_stage_bytes, tmap_b, full, k_off, n0);
                 k_off += kb;
                 c_off += kb;
@@ -711,13 +723,15 @@ __device__ __forceinline__ void producer_loop(const TcGeom &g, const StageGeom &
             mbar_expect_tx(full, (uint32_t)cnt * kblock_bytes);
             uint32_t sa = sg.smem_base + stage * sg.stage_pitch;
             for (int i = 0; i < cnt; i++, sa += sg.kblock_pitch) {
-                if (gemm)
-                    tma_load_2d(sa, tmap_a, full, c_off, m0);
-                else if (rows)
-                    tma_load_4d(sa, tmap_a, full, 0, cw, chh + (int)off_h, cn); // kw = 1 here: off_h counts kernel rows
-                else
-                    tma_load_im2col_4d(sa, tmap_a, full, c_off, cw, chh, cn, (uint16_t)off_w, (uint16_t)off_h);
-                if (!b_res)
+                if (load_a) {
+                    if (gemm)
+                        tma_load_2d(sa, tmap_a, full, c_off, m0);
+                    else if (rows)
+                        tma_load_4d(sa, tmap_a, full, 0, cw, chh + (int)off_h, cn); // kw = 1 here: off_h counts kernel rows
+                    else
+                        tma_load_im2col_4d(sa, tmap_a, full, c_off, cw, chh, cn, (uint16_t)off_w, (uint16_t)off_h);
+                }
+                if (load_b)
                     tma_load_2d(sa + sg.a_stage_bytes, tmap_b, full, k_off, n0);
                 k_off += kb;
                 c_off += kb;
@@ -736,14 +750,71 @@ __device__ __forceinline__ void producer_loop(const TcGeom &g, const StageGeom &
     }
 }
 
-// warp 1, one lane: issues the MMAs of every K block into the tile's TMEM accumulator.
+// The MMAs of one tile in patch mode for a filter size known at compile time: straight-line code (in the
+// nested loops over taps each MMA pair cost about 390 cycles of the issuing thread, most of it loop overhead).
+// WIDE: one pixel per swizzle row of `cell16` 16-byte units, a tap is `cell16 / 2` MMAs; else 16-byte cells and
+// one MMA per pair of cells of a kernel row. With DUAL the taps go to the two issuers in turn; issuer 0 owns the
+// first one, which overwrites the accumulator.
+template <int KH, int KWC, bool WIDE, bool DUAL>
+__device__ __forceinline__ bool patch_taps(uint32_t tmem_d, const dev::Desc da0, const dev::Desc db0, const uint32_t row16,
+                                           const uint32_t cell16, const uint32_t bres_pitch16, const uint32_t idesc,
+                                           const uint32_t mi, const uint32_t bar_init, const uint32_t init_parity,
+                                           volatile int *abort_flag, int *status) {
+    using namespace dev;
+    if (DUAL && mi == 1) {
+        if (!mbar_wait(bar_init, init_parity, abort_flag, status, ERR_MMA_ACC))
+            return false;
+        fence_after_sync();
+    }
+    constexpr int PER_ROW = WIDE ? KWC : KWC / 2;
+#pragma unroll
+    for (int ky = 0; ky < KH; ky++) {
+#pragma unroll
+        for (int x = 0; x < PER_ROW; x++) {
+            const int tap = ky * PER_ROW + x;
+            if (DUAL && (uint32_t)(tap & 1) != mi)
+                continue;
+            if (WIDE) {
+                const Desc da = da0 + ((uint32_t)ky * row16 + (uint32_t)x * cell16);
+                const Desc db = db0 + (uint32_t)tap * bres_pitch16;
+                mma_i8(tmem_d, da, db, idesc, tap != 0);
+                mma_i8(tmem_d, da + 2, db + 2, idesc, 1);
+                if (cell16 > 4) {
+                    mma_i8(tmem_d, da + 4, db + 4, idesc, 1);
+                    mma_i8(tmem_d, da + 6, db + 6, idesc, 1);
+                }
+            } else {
+                const Desc da = da0 + ((uint32_t)ky * row16 + (uint32_t)(2 * x));
+                const Desc db = db0 + ((uint32_t)ky * bres_pitch16 + (uint32_t)(2 * x));
+                mma_i8(tmem_d, da, db, idesc, tap != 0);
+            }
+            if (DUAL && tap == 0) {
+                fence_before_sync();
+                mbar_arrive(bar_init);
+            }
+        }
+    }
+    return true;
+}
+
+// One lane of warp 1 (and, with two issuers, of warp 18): issues the MMAs of every K block into the tile's TMEM
+// accumulator. One thread's stream per stage -- barrier probe, fence, descriptor arithmetic, four MMAs, commit,
+// ring bookkeeping, each a dependent instruction or a branch of a lone warp -- takes 600 to 700 cycles, twice what
+// the tensor pipe needs for the stage's MMAs at 144 columns. With DUAL two threads take the stages of the ring in
+// turn: stage index modulo 2, and the plan makes the stage count even, so that a stage always belongs to the same
+// thread and each of its barrier phases is seen in order by one waiter. Both accumulate into the same TMEM
+// accumulator (32-bit integer sums do not depend on the order); the owner of a tile's first stage issues its
+// first MMA, which overwrites the accumulator, and arrives on bar_acc_init; the other waits for that before its
+// first MMA of the tile, with tcgen05 fences on both sides of the barrier. Each commits to the tile's
+// bar_acc_full (count 2) after its last MMA.
+template <bool DUAL>
 __device__ __forceinline__ void mma_loop(const TcGeom &g, const StageGeom &sg, TcShared &sh, uint32_t tmem_base,
-                                         int *status) {
+                                         int *status, const uint32_t mi) {
     using namespace dev;
     const int k_blocks = g.taps * g.c_blocks;
     const int total_tiles = g.m_tiles * g.n_tiles;
     uint32_t stage = 0, phase = 0;
-    uint32_t acc_phase0 = 0, acc_phase1 = 0;
+    uint32_t acc_phase0 = 0, acc_phase1 = 0, init_phase = 0;
     int it = 0;
     // descriptors of stage 0; a stage further on adds its byte offset >> 4 to the address field
     // (the ring stays below the field's 256 KB range, so the sum never carries out of it)
@@ -771,12 +842,26 @@ __device__ __forceinline__ void mma_loop(const TcGeom &g, const StageGeom &sg, T
             acc_phase0 ^= 1;
         fence_after_sync();
         const uint32_t tmem_d = tmem_base + buf * g.acc_stride;
+        bool joined = false; // DUAL: this thread has issued, or waited for, the tile's first MMA
         if (g.mode == MODE_PATCH) {
             if (!mbar_wait(bar_full0 + stage * 8, phase, &sh.abort_flag, status, ERR_MMA_FULL))
                 return;
             fence_after_sync();
             // rows of the tile = (patch row y, x) with x fastest: 8-row groups step one patch row
-            if (g.cell == 16) {
+            const uint32_t bar_init = smem_u32(&sh.bar_acc_init[buf]), init_parity = (init_phase >> buf) & 1;
+            if (g.cell == 16 && g.kh == 4 && g.kw_cells == 4) {
+                const uint32_t row16 = (uint32_t)g.patch_w;
+                const Desc da = make_desc(smem_desc_plain(sg.smem_base, 16u, row16 * 16u)) + stage * pitch16;
+                if (!patch_taps<4, 4, false, DUAL>(tmem_d, da, desc_bres, row16, 1u, bres_pitch16, idesc, mi, bar_init, init_parity,
+                                                   &sh.abort_flag, status))
+                    return;
+            } else if (g.cell != 16 && g.kh == 3 && g.kw_cells == 3) {
+                const uint32_t cell16 = (uint32_t)g.cell >> 4, row16 = (uint32_t)g.patch_w * cell16;
+                const Desc da = make_desc(smem_desc_sbo(sg.smem_base, g.cell, row16 * 16u)) + stage * pitch16;
+                if (!patch_taps<3, 3, true, DUAL>(tmem_d, da, desc_bres, row16, cell16, bres_pitch16, idesc, mi, bar_init, init_parity,
+                                                  &sh.abort_flag, status))
+                    return;
+            } else if (g.cell == 16) {
                 const uint32_t row16 = (uint32_t)g.patch_w; // patch row pitch in 16-byte units
                 Desc da = make_desc(smem_desc_plain(sg.smem_base, 16u, row16 * 16u)) + stage * pitch16;
                 Desc db = desc_bres;
@@ -804,60 +889,91 @@ __device__ __forceinline__ void mma_loop(const TcGeom &g, const StageGeom &sg, T
                     }
                 }
             }
-            mma_commit(bar_empty0 + stage * 8);
+            mma_commit(bar_empty0 + stage * 8); // (with two issuers the stage is free when both have committed)
             if (++stage == stages) {
                 stage = 0;
                 phase ^= 1;
             }
             mma_commit(smem_u32(&sh.bar_acc_full[buf]));
+            init_phase ^= 1u << buf;
             continue;
         }
         if (kgroup == 1) {
             for (int kbi = 0; kbi < k_blocks; kbi++) {
-                if (!mbar_wait(bar_full0 + stage * 8, phase, &sh.abort_flag, status, ERR_MMA_FULL))
-                    return;
-                fence_after_sync();
-                const Desc da = desc_a0 + stage * pitch16;
-                const Desc db = b_res ? desc_bres + (uint32_t)kbi * bres_pitch16 : desc_b0 + stage * pitch16;
-                mma_i8(tmem_d, da, db, idesc, kbi != 0);
-                if (kk > 1)
-                    mma_i8(tmem_d, da + 2, db + 2, idesc, 1);
-                if (kk > 2) {
-                    mma_i8(tmem_d, da + 4, db + 4, idesc, 1);
-                    mma_i8(tmem_d, da + 6, db + 6, idesc, 1);
+                if (!DUAL || (stage & 1u) == mi) {
+                    if (!mbar_wait(bar_full0 + stage * 8, phase, &sh.abort_flag, status, ERR_MMA_FULL))
+                        return;
+                    fence_after_sync();
+                    if (DUAL && !joined) {
+                        if (kbi != 0) {
+                            if (!mbar_wait(smem_u32(&sh.bar_acc_init[buf]), (init_phase >> buf) & 1, &sh.abort_flag, status, ERR_MMA_ACC))
+                                return;
+                            fence_after_sync();
+                        }
+                        joined = true;
+                    }
+                    const Desc da = desc_a0 + stage * pitch16;
+                    const Desc db = b_res ? desc_bres + (uint32_t)kbi * bres_pitch16 : desc_b0 + stage * pitch16;
+                    mma_i8(tmem_d, da, db, idesc, kbi != 0);
+                    if (DUAL && kbi == 0) {
+                        fence_before_sync();
+                        mbar_arrive(smem_u32(&sh.bar_acc_init[buf]));
+                    }
+                    if (kk > 1)
+                        mma_i8(tmem_d, da + 2, db + 2, idesc, 1);
+                    if (kk > 2) {
+                        mma_i8(tmem_d, da + 4, db + 4, idesc, 1);
+                        mma_i8(tmem_d, da + 6, db + 6, idesc, 1);
+                    }
+                    mma_commit(bar_empty0 + stage * 8); // frees the stage when these MMAs retire
                 }
-                mma_commit(bar_empty0 + stage * 8); // frees the stage when these MMAs retire
                 if (++stage == stages) {
                     stage = 0;
                     phase ^= 1;
                 }
             }
             mma_commit(smem_u32(&sh.bar_acc_full[buf]));
+            init_phase ^= 1u << buf;
             continue;
         }
         for (int kb0 = 0; kb0 < k_blocks; kb0 += kgroup) {
-            if (!mbar_wait(bar_full0 + stage * 8, phase, &sh.abort_flag, status, ERR_MMA_FULL))
-                return;
-            fence_after_sync();
-            const int cnt = min(kgroup, k_blocks - kb0);
-            Desc da = desc_a0 + stage * pitch16;
-            Desc db = b_res ? desc_bres + (uint32_t)kb0 * bres_pitch16 : desc_b0 + stage * pitch16;
-            for (int i = 0; i < cnt; i++, da += kblock_pitch16, db += b_step16) {
-                mma_i8(tmem_d, da, db, idesc, (kb0 | i) != 0);
-                if (kk > 1)
-                    mma_i8(tmem_d, da + 2, db + 2, idesc, 1);
-                if (kk > 2) {
-                    mma_i8(tmem_d, da + 4, db + 4, idesc, 1);
-                    mma_i8(tmem_d, da + 6, db + 6, idesc, 1);
+            if (!DUAL || (stage & 1u) == mi) {
+                if (!mbar_wait(bar_full0 + stage * 8, phase, &sh.abort_flag, status, ERR_MMA_FULL))
+                    return;
+                fence_after_sync();
+                if (DUAL && !joined) {
+                    if (kb0 != 0) {
+                        if (!mbar_wait(smem_u32(&sh.bar_acc_init[buf]), (init_phase >> buf) & 1, &sh.abort_flag, status, ERR_MMA_ACC))
+                            return;
+                        fence_after_sync();
+                    }
+                    joined = true;
                 }
+                const int cnt = min(kgroup, k_blocks - kb0);
+                Desc da = desc_a0 + stage * pitch16;
+                Desc db = b_res ? desc_bres + (uint32_t)kb0 * bres_pitch16 : desc_b0 + stage * pitch16;
+                for (int i = 0; i < cnt; i++, da += kblock_pitch16, db += b_step16) {
+                    mma_i8(tmem_d, da, db, idesc, (kb0 | i) != 0);
+                    if (DUAL && (kb0 | i) == 0) {
+                        fence_before_sync();
+                        mbar_arrive(smem_u32(&sh.bar_acc_init[buf]));
+                    }
+                    if (kk > 1)
+                        mma_i8(tmem_d, da + 2, db + 2, idesc, 1);
+                    if (kk > 2) {
+                        mma_i8(tmem_d, da + 4, db + 4, idesc, 1);
+                        mma_i8(tmem_d, da + 6, db + 6, idesc, 1);
+                    }
+                }
+                mma_commit(bar_empty0 + stage * 8); // frees the stage when these MMAs retire
             }
-            mma_commit(bar_empty0 + stage * 8); // frees the stage when these MMAs retire
             if (++stage == stages) {
                 stage = 0;
                 phase ^= 1;
             }
         }
         mma_commit(smem_u32(&sh.bar_acc_full[buf]));
+        init_phase ^= 1u << buf;
     }
 }
 
@@ -993,10 +1109,20 @@ tc_conv_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const uint32_t tmem_base = sh.tmem_base_slot;
     if (warp == 0) {
         if (lane == 0)
-            producer_loop(g, sg, sh, &tmap_a, &tmap_b, a.status);
+            producer_loop(g, sg, sh, &tmap_a, &tmap_b, a.status, g.load_warps == 2 ? 1 : 0);
     } else if (warp == 1) {
-        if (lane == 0)
-            mma_loop(g, sg, sh, tmem_base, a.status);
+        if (lane == 0) {
+            if (g.issuers == 2)
+                mma_loop<true>(g, sg, sh, tmem_base, a.status, 0);
+            else
+                mma_loop<false>(g, sg, sh, tmem_base, a.status, 0);
+        }
+    } else if (warp == WARP_MMA2) {
+        if (lane == 0 && g.issuers == 2)
+            mma_loop<true>(g, sg, sh, tmem_base, a.status, 1);
+    } else if (warp == WARP_LOAD2) {
+        if (lane == 0 && g.load_warps == 2)
+            producer_loop(g, sg, sh, &tmap_a, &tmap_b, a.status, 2);
     } else {
         epilogue_generic(a, sh, tmem_base, warp, lane);
     }
@@ -1416,10 +1542,20 @@ tc_conv_fast_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const uint32_t tmem_base = sh.tmem_base_slot;
     if (warp == 0) {
         if (lane == 0)
-            producer_loop(g, sg, sh, &tmap_a, &tmap_b, a.status);
+            producer_loop(g, sg, sh, &tmap_a, &tmap_b, a.status, g.load_warps == 2 ? 1 : 0);
     } else if (warp == 1) {
-        if (lane == 0)
-            mma_loop(g, sg, sh, tmem_base, a.status);
+        if (lane == 0) {
+            if (g.issuers == 2)
+                mma_loop<true>(g, sg, sh, tmem_base, a.status, 0);
+            else
+                mma_loop<false>(g, sg, sh, tmem_base, a.status, 0);
+        }
+    } else if (warp == WARP_MMA2) {
+        if (lane == 0 && g.issuers == 2)
+            mma_loop<true>(g, sg, sh, tmem_base, a.status, 1);
+    } else if (warp == WARP_LOAD2) {
+        if (lane == 0 && g.load_warps == 2)
+            producer_loop(g, sg, sh, &tmap_a, &tmap_b, a.status, 2);
     } else {
         epilogue_fast<RES, Y2, XSUM, ROWS>(a, sg, sh, tmem_base, &tmap_y, &tmap_y2, &tmap_res, warp, lane);
     }
@@ -1951,6 +2087,22 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
         stages = MAX_STAGES;
     if (stages < 2)
         return fail(-ENOSYS, "tcgen05 conv: tile does not fit shared memory");
+    // Deep K loops are bound by the instruction streams of the one-thread roles, not by the tensor pipe or the
+    // loads: two MMA issuers take the stages in turn (which needs an even stage count), and activations and
+    // weights get a load warp each. A tile of fewer than four stages is over before the second thread pays.
+    const uint32_t stage_groups = (k_blocks + (uint32_t)g.kgroup - 1) / (uint32_t)g.kgroup;
+    const bool deep = g.mode != MODE_PATCH && stage_groups >= 4;
+    const int want_issuers = ctx->opt.conv_mma_issuers ? ctx->opt.conv_mma_issuers : (deep ? 2 : 1);
+    const int want_loaders = ctx->opt.conv_load_warps ? ctx->opt.conv_load_warps : (deep ? 2 : 1);
+    // (patch mode: the taps of a tile are dealt out instead; only the filter sizes with straight-line code)
+    // 18 or 36 MMAs per tile pay for the second issuer; the 8 of a 4 x 4-cell stem do not (measured: 349 us with
+    // one issuer, 377 us with two, ResNet-50 stem at 512 images)
+    const bool patch_dual = g.mode == MODE_PATCH && g.cell != 16 && g.kh == 3 && g.kw_cells == 3;
+    const int want_patch = ctx->opt.conv_mma_issuers ? ctx->opt.conv_mma_issuers : 2;
+    g.issuers = g.mode == MODE_PATCH ? ((patch_dual && want_patch == 2) ? 2 : 1) : (want_issuers == 2 ? 2 : 1);
+    g.load_warps = (want_loaders == 2 && g.mode != MODE_PATCH && !g.b_resident) ? 2 : 1;
+    if (g.issuers == 2 && g.mode != MODE_PATCH)
+        stages &= ~1;
     g.stages = stages;
     g.acc_arrivals = tp->fast ? 4 * fe.ncg : EPI_WARPS;
     const uint32_t ring = (uint32_t)stages * per_stage + (g.b_resident ? b_all : 0u);

@@ -275,13 +275,42 @@ def test_depthwise_conv_residual_and_second_output(ctx, qo):
     assert np.array_equal(got.cpu().numpy(), want) and np.array_equal(got2.cpu().numpy(), want2)
 
 
-@pytest.mark.parametrize("variant", ["plain", "residual"])
+@pytest.mark.parametrize("issuers", [1, 2])
+@pytest.mark.parametrize("loaders", [1, 2])
+@pytest.mark.parametrize("shape", ["im2col_3x3_c256", "gemm_k1024", "patch_3x3_c64", "im2col_odd_kblocks"])
+def test_role_warp_counts_do_not_change_the_result(ctx, qo, shape, issuers, loaders):
+    """Deep K loops run with two MMA-issuing warps (which take the stages of the ring in turn and accumulate into
+    the same TMEM accumulator) and with a load warp each for activations and weights; the wide patch form deals
+    its filter taps out to two issuers. Forced to one or two of each through the context options, the output is
+    the oracle's, byte for byte."""
+    # the 1x1 and the 96-channel case have more tiles than the GPU has SMs (every CTA crosses tile boundaries); the
+    # 96-channel one has an odd number of stages per tile, so the owner of a tile's first stage alternates
+    n, h, w, c, oc, k, pad = {"im2col_3x3_c256": (8, 14, 14, 256, 256, 3, 1), "gemm_k1024": (64, 14, 14, 1024, 256, 1, 0),
+                              "patch_3x3_c64": (8, 56, 56, 64, 64, 3, 1), "im2col_odd_kblocks": (16, 40, 40, 96, 64, 3, 1)}[shape]
+    xq, zx, wq, zw, mult, bias, oqp = make_case(91, n, h, w, c, oc, k, k)
+    want = qo.qconv2d_u8(xq, wq, zw, mult, bias, zx, oqp.scale, oqp.zero_point, pad=(pad,) * 4)
+    ctx.set_option("conv.mma_issuers", issuers)
+    ctx.set_option("conv.load_warps", loaders)
+    try:
+        plan = ctx.conv2d_plan(tuple(xq.shape), wq, zw, mult, bias, zx, oqp, padding=(pad,) * 4, force_path=L.PATH_TC)
+    finally:
+        ctx.set_option("conv.mma_issuers", 0)
+        ctx.set_option("conv.load_warps", 0)
+    x = torch.from_numpy(xq).cuda()
+    for _ in range(3):  # the persistent CTAs take several tiles each: repeat to vary the interleaving of the roles
+        got = plan(x).cpu().numpy()
+        assert np.array_equal(got, want)
+    ctx.check_status()
+    plan.close()
+
+
+@pytest.mark.parametrize("variant", ["plain", "residual", "deep"])
 def test_bounded_wait_gives_up_and_the_context_stays_usable(ctx, qo, variant):
     """Every wait inside the tensor-core kernel has a time limit. With the limit shortened to 2 ms and the
     loader of one CTA told to expect bytes that no load delivers ("debug.withhold_load"), that CTA's waits run
     out: the kernel returns by itself, nncb_check_device_status reports -ETIMEDOUT with a role code once and
     clears the status word, and the same convolution on the same context is bit-exact afterwards."""
-    n, h, w, c, oc = 2, 28, 28, 64, 256
+    n, h, w, c, oc = (2, 14, 14, 1024, 256) if variant == "deep" else (2, 28, 28, 64, 256)  # deep: two issuers, two load warps
     xq, zx, wq, zw, mult, bias, oqp = make_case(77, n, h, w, c, oc, 1, 1)
     x = torch.from_numpy(xq).cuda()
     kw, want = {}, qo.qconv2d_u8(xq, wq, zw, mult, bias, zx, oqp.scale, oqp.zero_point)
