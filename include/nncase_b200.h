@@ -58,7 +58,7 @@ NNCB_API int nncb_synchronize(nncb_context *ctx);
  *   "wait_limit_us"          kernel-internal waits give up after this long (default 1,000,000)
  *   "conv.tile_n"            force the N tile of the tensor-core convolution: 128, 96, 64, 48, 32 (0 = choose)
  *   "conv.mma_issuers"       force the number of warps that issue the convolution's MMAs: 1 or 2 (0 = choose)
- *   "conv.load_warps"        force the number of its load warps: 1, or 2 = activations and weights apart (0 = choose)
+ *   "conv.load_warps"        force its load warps: 1, 2 = one for activations and one for weights, 3 = two that take the stages in turn (0 = choose)
  *   "conv.wide_patch"        0: keep 64-/128-channel stride-1 convolutions on the im2col form (default 1)
  *   "depthwise.dot_product"  0: multiply-add form of the 3x3 depthwise kernel (default 1)
  *   "attention.warps"        force the CTA width of paged attention: 4 or 8 (0 = choose)

@@ -16,7 +16,7 @@
 struct nncb_options {
     int conv_tile_n = 0;        // force the N tile of the tensor-core convolution (128, 96, 64, 48 or 32)
     int conv_mma_issuers = 0;   // force the number of MMA-issuing warps of the tensor-core convolution (1 or 2)
-    int conv_load_warps = 0;    // force the number of its load warps (1, or 2: activations and weights apart)
+    int conv_load_warps = 0;    // force its load warps (1; 2: activations and weights apart; 3: two, stages in turn)
     int conv_wide_patch = 1;    // 0: keep 64-/128-channel stride-1 layers on the im2col form
     int depthwise_dot = 1;      // 0: the multiply-add form of the 3x3 depthwise kernel
     int attention_warps = 0;    // force the CTA width of paged attention (4 or 8)

@@ -101,7 +101,8 @@ struct TcGeom {
     int f32_out;
     int acc_arrivals;   // epilogue warps that release an accumulator buffer
     int issuers;        // 2: two warps issue the MMAs, taking the stages of the ring in turn (stages is even then)
-    int load_warps;     // 2: activations and weights are loaded by a warp each
+    int load_warps;     // 2: two load warps
+    int load_by_stage;  // ... that take the stages of the ring in turn (else: one loads activations, one weights)
     int kgroup;         // K blocks per pipeline stage (one barrier round trip and one commit for all of them)
     int b_resident;     // the whole weight matrix stays in shared memory (one N tile, small K): loaded once per CTA
     int bx_log2, tiles_x, tiles_y; // MODE_ROWS: patch width 2^bx_log2 (height 128 >> bx_log2), patches per image
@@ -567,7 +568,7 @@ __device__ __forceinline__ void tc_setup(const TcGeom &g, TcShared &sh, int warp
         sh.abort_flag = 0;
         sh.wait_limit_us = g.wait_limit_us;
         for (int s = 0; s < g.stages; s++) {
-            mbar_init(smem_u32(&sh.bar_full[s]), g.load_warps);
+            mbar_init(smem_u32(&sh.bar_full[s]), g.load_by_stage ? 1 : g.load_warps);
             mbar_init(smem_u32(&sh.bar_empty[s]), g.mode == MODE_PATCH ? g.issuers : 1);
         }
         mbar_init(smem_u32(&sh.bar_b), 1);
@@ -624,12 +625,14 @@ __device__ __forceinline__ void producer_loop(const TcGeom &g, const StageGeom &
     const bool b_res = sg.b_resident != 0;
     const bool load_a = part != 2, load_b = part != 1 && !b_res;
     const uint32_t kblock_bytes = (load_a ? sg.a_stage_bytes : 0u) + (load_b ? sg.b_stage_bytes : 0u);
+    const bool by_stage = part >= 3;          // parts 3 and 4: the even and the odd stages of the ring, activations and weights
+    const uint32_t my_parity = part == 4 ? 1u : 0u;
     const int kgroup = g.kgroup;
     const uint32_t bar_full0 = smem_u32(&sh.bar_full[0]), bar_empty0 = smem_u32(&sh.bar_empty[0]);
     uint32_t stage = 0, phase = 0;
-    if (g.withhold && blockIdx.x == 0 && load_a) // self-test: 16 bytes that no load delivers keep stage 0 from ever filling
+    if (g.withhold && blockIdx.x == 0 && load_a && part != 4) // self-test: 16 bytes that no load delivers keep stage 0 from ever filling
         asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar_full0), "r"(16u) : "memory");
-    if (b_res && (int)blockIdx.x < total_tiles && load_a) {
+    if (b_res && (int)blockIdx.x < total_tiles && load_a && part != 4) {
         // the whole weight matrix, once
         const uint32_t bar_b = smem_u32(&sh.bar_b);
         mbar_expect_tx(bar_b, (uint32_t)k_blocks * sg.b_stage_bytes);
@@ -685,21 +688,23 @@ __device__ __forceinline__ void producer_loop(const TcGeom &g, const StageGeom &
         if (kgroup == 1) {
             // one K block per stage: the shortest instruction stream per block
             for (int kbi = 0; kbi < k_blocks; kbi++) {
-                if (!mbar_wait(bar_empty0 + stage * 8, phase ^ 1, &sh.abort_flag, status, ERR_PRODUCER))
-                    return;
-                const uint32_t full = bar_full0 + stage * 8;
-                const uint32_t sa = sg.smem_base + stage * sg.stage_pitch;
-                mbar_expect_tx(full, kblock_bytes);
-                if (load_a) {
-                    if (gemm)
-                        tma_load_2d(sa, tmap_a, full, c_off, m0);
-                    else if (rows)
-                        tma_load_4d(sa, tmap_a, full, 0, cw, chh + (int)off_h, cn);
-                    else
-                        tma_load_im2col_4d(sa, tmap_a, full, c_off, cw, chh, cn, (uint16_t)off_w, (uint16_t)off_h);
+                if (!by_stage || (stage & 1u) == my_parity) {
+                    if (!mbar_wait(bar_empty0 + stage * 8, phase ^ 1, &sh.abort_flag, status, ERR_PRODUCER))
+                        return;
+                    const uint32_t full = bar_full0 + stage * 8;
+                    const uint32_t sa = sg.smem_base + stage * sg.stage_pitch;
+                    mbar_expect_tx(full, kblock_bytes);
+                    if (load_a) {
+                        if (gemm)
+                            tma_load_2d(sa, tmap_a, full, c_off, m0);
+                        else if (rows)
+                            tma_load_4d(sa, tmap_a, full, 0, cw, chh + (int)off_h, cn);
+                        else
+                            tma_load_im2col_4d(sa, tmap_a, full, c_off, cw, chh, cn, (uint16_t)off_w, (uint16_t)off_h);
+                    }
+                    if (load_b)
+                        tma_load_2d(sa + sg.a_stage_bytes, tmap_b, full, k_off, n0);
                 }
-                if (load_b)
-                    tma_load_2d(sa + sg.a_stage_bytes, tmap_b, full, k_off, n0);
                 k_off += kb;
                 c_off += kb;
                 if (++cb == c_blocks) {
@@ -716,14 +721,16 @@ __device__ __forceinline__ void producer_loop(const TcGeom &g, const StageGeom &
             continue;
         }
         for (int kb0 = 0; kb0 < k_blocks; kb0 += kgroup) {
-            if (!mbar_wait(bar_empty0 + stage * 8, phase ^ 1, &sh.abort_flag, status, ERR_PRODUCER))
+            const bool mine = !by_stage || (stage & 1u) == my_parity;
+            if (mine && !mbar_wait(bar_empty0 + stage * 8, phase ^ 1, &sh.abort_flag, status, ERR_PRODUCER))
                 return;
             const uint32_t full = bar_full0 + stage * 8;
             const int cnt = min(kgroup, k_blocks - kb0); // K blocks of this stage
-            mbar_expect_tx(full, (uint32_t)cnt * kblock_bytes);
+            if (mine)
+                mbar_expect_tx(full, (uint32_t)cnt * kblock_bytes);
             uint32_t sa = sg.smem_base + stage * sg.stage_pitch;
             for (int i = 0; i < cnt; i++, sa += sg.kblock_pitch) {
-                if (load_a) {
+                if (load_a && mine) {
                     if (gemm)
                         tma_load_2d(sa, tmap_a, full, c_off, m0);
                     else if (rows)
@@ -731,7 +738,7 @@ __device__ __forceinline__ void producer_loop(const TcGeom &g, const StageGeom &
                     else
                         tma_load_im2col_4d(sa, tmap_a, full, c_off, cw, chh, cn, (uint16_t)off_w, (uint16_t)off_h);
                 }
-                if (load_b)
+                if (load_b && mine)
                     tma_load_2d(sa + sg.a_stage_bytes, tmap_b, full, k_off, n0);
                 k_off += kb;
                 c_off += kb;
@@ -801,9 +808,9 @@ __device__ __forceinline__ bool patch_taps(uint32_t tmem_d, const dev::Desc da0,
 // accumulator. One thread's stream per stage -- barrier probe, fence, descriptor arithmetic, four MMAs, commit,
 // ring bookkeeping, each a dependent instruction or a branch of a lone warp -- takes 600 to 700 cycles, twice what
 // the tensor pipe needs for the stage's MMAs at 144 columns. With DUAL two threads take the stages of the ring in
-// turn: stage index modulo 2, and the plan makes the stage count even, so that a stage always belongs to the same
-// thread and each of its barrier phases is seen in order by one waiter. Both accumulate into the same TMEM
-// accumulator (32-bit integer sums do not depend on the order); the owner of a tile's first stage issues its
+// turn: stage index modulo 2 (with an odd stage count one of them takes the last and the first stage of the ring),
+// so that a stage always belongs to the same thread and each of its barrier phases is seen in order by one
+// waiter. Both accumulate into the same TMEM accumulator (32-bit integer sums do not depend on the order); the owner of a tile's first stage issues its
 // first MMA, which overwrites the accumulator, and arrives on bar_acc_init; the other waits for that before its
 // first MMA of the tile, with tcgen05 fences on both sides of the barrier. Each commits to the tile's
 // bar_acc_full (count 2) after its last MMA.
@@ -1109,7 +1116,7 @@ tc_conv_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const uint32_t tmem_base = sh.tmem_base_slot;
     if (warp == 0) {
         if (lane == 0)
-            producer_loop(g, sg, sh, &tmap_a, &tmap_b, a.status, g.load_warps == 2 ? 1 : 0);
+            producer_loop(g, sg, sh, &tmap_a, &tmap_b, a.status, g.load_warps == 2 ? (g.load_by_stage ? 3 : 1) : 0);
     } else if (warp == 1) {
         if (lane == 0) {
             if (g.issuers == 2)
@@ -1122,7 +1129,7 @@ tc_conv_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             mma_loop<true>(g, sg, sh, tmem_base, a.status, 1);
     } else if (warp == WARP_LOAD2) {
         if (lane == 0 && g.load_warps == 2)
-            producer_loop(g, sg, sh, &tmap_a, &tmap_b, a.status, 2);
+            producer_loop(g, sg, sh, &tmap_a, &tmap_b, a.status, g.load_by_stage ? 4 : 2);
     } else {
         epilogue_generic(a, sh, tmem_base, warp, lane);
     }
@@ -1542,7 +1549,7 @@ tc_conv_fast_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const uint32_t tmem_base = sh.tmem_base_slot;
     if (warp == 0) {
         if (lane == 0)
-            producer_loop(g, sg, sh, &tmap_a, &tmap_b, a.status, g.load_warps == 2 ? 1 : 0);
+            producer_loop(g, sg, sh, &tmap_a, &tmap_b, a.status, g.load_warps == 2 ? (g.load_by_stage ? 3 : 1) : 0);
     } else if (warp == 1) {
         if (lane == 0) {
             if (g.issuers == 2)
@@ -1555,7 +1562,7 @@ tc_conv_fast_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             mma_loop<true>(g, sg, sh, tmem_base, a.status, 1);
     } else if (warp == WARP_LOAD2) {
         if (lane == 0 && g.load_warps == 2)
-            producer_loop(g, sg, sh, &tmap_a, &tmap_b, a.status, 2);
+            producer_loop(g, sg, sh, &tmap_a, &tmap_b, a.status, g.load_by_stage ? 4 : 2);
     } else {
         epilogue_fast<RES, Y2, XSUM, ROWS>(a, sg, sh, tmem_base, &tmap_y, &tmap_y2, &tmap_res, warp, lane);
     }
@@ -2087,22 +2094,22 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
         stages = MAX_STAGES;
     if (stages < 2)
         return fail(-ENOSYS, "tcgen05 conv: tile does not fit shared memory");
-    // Deep K loops are bound by the instruction streams of the one-thread roles, not by the tensor pipe or the
-    // loads: two MMA issuers take the stages in turn (which needs an even stage count), and activations and
-    // weights get a load warp each. A tile of fewer than four stages is over before the second thread pays.
+    // Deep K loops are bound by the instruction streams of the one-thread roles and by the latency of the stage
+    // ring, not by the tensor pipe or the load bandwidth: two MMA issuers and two load warps take the stages in
+    // turn. Measured on ResNet-50 at 512 images: tiles of eight or more stages gain (3x3 layers over 256 and 512
+    // channels 72 -> 67 us, 1x1 layers with K = 2048 40 -> 36 us), tiles of four stages lose a few per cent.
     const uint32_t stage_groups = (k_blocks + (uint32_t)g.kgroup - 1) / (uint32_t)g.kgroup;
-    const bool deep = g.mode != MODE_PATCH && stage_groups >= 4;
+    const bool deep = g.mode != MODE_PATCH && stage_groups >= 8;
     const int want_issuers = ctx->opt.conv_mma_issuers ? ctx->opt.conv_mma_issuers : (deep ? 2 : 1);
-    const int want_loaders = ctx->opt.conv_load_warps ? ctx->opt.conv_load_warps : (deep ? 2 : 1);
+    const int want_loaders = ctx->opt.conv_load_warps ? ctx->opt.conv_load_warps : (deep ? 3 : 1);
     // (patch mode: the taps of a tile are dealt out instead; only the filter sizes with straight-line code)
     // 18 or 36 MMAs per tile pay for the second issuer; the 8 of a 4 x 4-cell stem do not (measured: 349 us with
     // one issuer, 377 us with two, ResNet-50 stem at 512 images)
     const bool patch_dual = g.mode == MODE_PATCH && g.cell != 16 && g.kh == 3 && g.kw_cells == 3;
     const int want_patch = ctx->opt.conv_mma_issuers ? ctx->opt.conv_mma_issuers : 2;
     g.issuers = g.mode == MODE_PATCH ? ((patch_dual && want_patch == 2) ? 2 : 1) : (want_issuers == 2 ? 2 : 1);
-    g.load_warps = (want_loaders == 2 && g.mode != MODE_PATCH && !g.b_resident) ? 2 : 1;
-    if (g.issuers == 2 && g.mode != MODE_PATCH)
-        stages &= ~1;
+    g.load_by_stage = want_loaders == 3 && g.mode != MODE_PATCH ? 1 : 0;
+    g.load_warps = (g.load_by_stage || (want_loaders == 2 && g.mode != MODE_PATCH && !g.b_resident)) ? 2 : 1;
     g.stages = stages;
     g.acc_arrivals = tp->fast ? 4 * fe.ncg : EPI_WARPS;
     const uint32_t ring = (uint32_t)stages * per_stage + (g.b_resident ? b_all : 0u);

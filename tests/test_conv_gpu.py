@@ -276,7 +276,7 @@ def test_depthwise_conv_residual_and_second_output(ctx, qo):
 
 
 @pytest.mark.parametrize("issuers", [1, 2])
-@pytest.mark.parametrize("loaders", [1, 2])
+@pytest.mark.parametrize("loaders", [1, 2, 3])
 @pytest.mark.parametrize("shape", ["im2col_3x3_c256", "gemm_k1024", "patch_3x3_c64", "im2col_odd_kblocks"])
 def test_role_warp_counts_do_not_change_the_result(ctx, qo, shape, issuers, loaders):
     """Deep K loops run with two MMA-issuing warps (which take the stages of the ring in turn and accumulate into
