@@ -280,6 +280,20 @@ def int8_peak(ctx):
     return dict(burst=burst, sustained=mean.value)
 
 
+def mma_issue_pace(ctx):
+    """SM cycles per tcgen05.mma kind::i8 (M 128, K 32) when one or two warps issue them back to back on resident
+    operands (library self-test): what bounds a K loop apart from the tensor pipe's own rate."""
+    from nncase_b200 import lib as L
+    out = {}
+    for n in (64, 144, 256):
+        for issuers in (1, 2):
+            c = C.c_double()
+            L.check(ctx._lib.nncb_selftest_mma_issue(ctx._h, n, issuers, 16384, C.byref(c)))
+            out[f"n{n}_issuers{issuers}"] = round(c.value, 1)
+    out["unit"] = "SM cycles per MMA (tensor pipe alone: n / 1.9 at 1965 MHz against the measured int8 peak)"
+    return out
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -407,6 +421,7 @@ def run_ours(args):
                                   f"(nncb_selftest_int8_peak)",
                       tensor=dict(achieved=achieved, peak=int8_burst, peak_sustained=i8["sustained"], unit="TFLOP/s",
                                   frac=achieved / int8_burst),
+                      mma_issue_pace=mma_issue_pace(ctx),
                       tc_ms_per_step=tc_ms, tc_share_of_step=tc_ms / (ms / steps),
                       whole_step_tops=2.0 * macs * B / (ms / steps / 1000.0) / 1e12),
     )

@@ -346,6 +346,14 @@ NNCB_API int nncb_selftest_reciprocal_division(nncb_context *ctx, float scale, u
  * per multiply-accumulate). Synchronises. No counterpart in the reference. */
 NNCB_API int nncb_selftest_int8_peak(nncb_context *ctx, uint32_t mmas_per_sm, int repeats, int w_signed, double *best_tops, double *mean_tops);
 
+/* Diagnostic: the pace at which MMAs can be issued. One CTA per SM; `issuers` warps (1 or 2, one lane each)
+ * issue `mmas_per_issuer` back-to-back tcgen05.mma kind::i8 of M 128, N `n_cols` (16 .. 256, a multiple of 16),
+ * K 32 on operand tiles resident in shared memory, each warp into its own TMEM accumulator, in a loop shaped
+ * like a convolution's K loop (four MMAs and one descriptor step per iteration). Returns the mean over the SMs
+ * of SM cycles per MMA, all issuers' MMAs counted: the floor of a K loop's pace, to set beside the tensor
+ * pipe's own rate (nncb_selftest_int8_peak). Synchronises. No counterpart in the reference. */
+NNCB_API int nncb_selftest_mma_issue(nncb_context *ctx, int n_cols, int issuers, uint32_t mmas_per_issuer, double *cycles_per_mma);
+
 #ifdef __cplusplus
 }
 #endif

@@ -136,6 +136,7 @@ int rope_kv_append_f16(nncb_context *, const void *, void *, const float *, cons
 int swiglu_f16(nncb_context *, const void *, void *, int, int);
 int embedding_f16(nncb_context *, const void *, const int32_t *, void *, int, int, int);
 int int8_peak_selftest(nncb_context *ctx, uint32_t mmas_per_sm, int repeats, int w_signed, double *best_tops, double *mean_tops);
+int mma_issue_selftest(nncb_context *ctx, int n_cols, int issuers, uint32_t mmas_per_issuer, double *cycles_per_mma);
 size_t paged_attention_static_capacity();
 int paged_attention_static_scratch(int device, void **ptr);
 
@@ -628,6 +629,13 @@ int nncb_selftest_int8_peak(nncb_context *ctx, uint32_t mmas_per_sm, int repeats
     if (!best_tops || !mean_tops)
         return fail(-EINVAL, "nncb_selftest_int8_peak: null out");
     return int8_peak_selftest(ctx, mmas_per_sm, repeats, w_signed, best_tops, mean_tops);
+}
+
+int nncb_selftest_mma_issue(nncb_context *ctx, int n_cols, int issuers, uint32_t mmas_per_issuer, double *cycles_per_mma) {
+    CHECK_CTX(ctx);
+    if (!cycles_per_mma)
+        return fail(-EINVAL, "nncb_selftest_mma_issue: null out");
+    return mma_issue_selftest(ctx, n_cols, issuers, mmas_per_issuer, cycles_per_mma);
 }
 
 // ---- quantized conv ------------------------------------------------------------------------

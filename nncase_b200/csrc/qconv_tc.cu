@@ -503,6 +503,7 @@ struct FastEpi {
     int halves;         // 2: tiles of 8 epilogue warps, the two halves of the warps take alternate tiles; else 1
     int fcorr;          // the integer corrections run in float (every intermediate is an integer below 2^24)
     float so, rso, zo;  // output scale, its correctly rounded reciprocal, zero point
+    float one;          // 1.0f, as a kernel argument: a value the assembler cannot fold (see the bias add)
     float qlo, qhi;     // the fused clamp's bounds after quantization, within [0, 255]
     const float4 *cst;  // [oc_pad] {mult, bias, bits(corr of class 0), bits(-zw)}
     const uint8_t *add_table; // [256][256] quantized sum of (convolution output, residual), or null
@@ -1384,6 +1385,7 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
         const uint32_t corr_row = s_corr + (uint32_t)(cls * f.corr_pitch) * 4;
         // eight columns at a time: short live ranges keep the 16 epilogue warps within the register file
         const uint64_t rso2 = pack2(f.rso, f.rso), nso2 = pack2(-f.so, -f.so), zo2 = pack2(f.zo, f.zo);
+        const uint64_t one2 = pack2(f.one, f.one);
         const uint64_t rsumf2 = pack2((float)rsum, (float)rsum);
         auto chunk = [&](const int (&v)[8], const int cc, auto multi_tag, auto clamp_tag, auto fc_tag) {
             constexpr bool MULTI = decltype(multi_tag)::value;
@@ -1423,11 +1425,9 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
                 }
                 // x = acc * mult + bias, then x / so correctly rounded: q0 = RN(x r), q = RN(q0 + RN(x - q0 so) r)
                 // the product must round before the bias is added: the assembler contracts a packed multiply and a
-                // packed add into one fused operation even when both carry .rn, so the add is two scalar ones
-                float p0, p1, bias0, bias1;
-                unpack2(mul2(accf2, mult2), p0, p1);
-                unpack2(bias2, bias0, bias1);
-                const uint64_t x2 = pack2(__fadd_rn(p0, bias0), __fadd_rn(p1, bias1));
+                // packed add into one fused operation even when both carry .rn. So the add is a fused multiply-add
+                // by one, RN(p * 1 + bias) = RN(p + bias), with the one a kernel argument that cannot be folded away.
+                const uint64_t x2 = fma2(mul2(accf2, mult2), one2, bias2);
                 const uint64_t q0 = mul2(x2, rso2);
                 const uint64_t q2 = fma2(fma2(q0, nso2, x2), rso2, q0);
                 // Quantization is monotone, so the fused clamp on the real value is a clamp of the
@@ -1755,6 +1755,114 @@ int int8_peak_selftest(nncb_context *ctx, uint32_t mmas_per_sm, int repeats, int
     return rc;
 }
 
+// ------------------------------------------------------------------------------------------------
+// Pace of MMA issue, measured: cycles per tcgen05.mma kind::i8 (M = 128, K = 32) of `n_cols` columns when one
+// or two warps (one lane each) issue them back to back on operand tiles resident in shared memory, each warp into
+// its own TMEM accumulator, four MMAs and one descriptor step per loop iteration. It is the floor of a
+// convolution's K loop: measured, one issuer keeps the pipe's own pace from 144 columns up (72 cycles per MMA at
+// n = 144, 128 at n = 256, i.e. n / 1.9 at 1.965 GHz) and takes 57 cycles at 64 columns, where two issuers reach
+// the 48 cycles at which shared memory delivers the operands ((128 + n) / 4). What a real K loop adds per stage --
+// a barrier probe, a fence, a commit, ring bookkeeping, each some tens of cycles in a lone thread's dependent
+// stream -- is what separates it from these figures.
+// ------------------------------------------------------------------------------------------------
+struct IssueShared {
+    uint64_t bar[2];
+    uint32_t tmem_slot;
+    volatile int abort_flag;
+    unsigned wait_limit_us; // must follow abort_flag (read by mbar_wait_slow through the flag's address)
+};
+
+__global__ void __launch_bounds__(128, 1) mma_issue_kernel(uint32_t groups, uint32_t idesc, int issuers, unsigned long long *cycles,
+                                                           int *status, unsigned limit_us) {
+    using namespace dev;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) IssueShared sh;
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t a_tile = base, b_tile = base + 48u * 1024u; // three A stages of 16 KB, B: 256 rows x 128 B
+    for (uint32_t i = threadIdx.x; i < 80u * 1024u / 4u; i += blockDim.x) {
+        uint32_t v = (i + 1u) * 2654435761u + blockIdx.x * 40503u;
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(base + i * 4u), "r"(v ^ (v >> 15)) : "memory");
+    }
+    fence_async_smem();
+    if (threadIdx.x == 0) {
+        sh.abort_flag = 0;
+        sh.wait_limit_us = limit_us;
+        mbar_init(smem_u32(&sh.bar[0]), 1);
+        mbar_init(smem_u32(&sh.bar[1]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh.tmem_slot)), "r"(512u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem = sh.tmem_slot;
+    if (lane == 0 && warp >= 1 && warp <= issuers) {
+        const Desc da0 = make_desc(smem_desc(a_tile, 128)), db = make_desc(smem_desc(b_tile, 128));
+        const uint32_t bar = smem_u32(&sh.bar[warp - 1]), d = tmem + (uint32_t)(warp - 1) * 256u;
+        uint32_t st = 0;
+        const long long t0 = clock64();
+        for (uint32_t g = 0; g < groups; g++) {
+            const Desc da = da0 + st * 1024u; // a K block of another stage each time, as in a K loop
+            mma_i8(d, da, db, idesc, g != 0);
+            mma_i8(d, da + 2, db + 2, idesc, 1);
+            mma_i8(d, da + 4, db + 4, idesc, 1);
+            mma_i8(d, da + 6, db + 6, idesc, 1);
+            if (++st == 3)
+                st = 0;
+        }
+        mma_commit(bar);
+        mbar_wait(bar, 0, &sh.abort_flag, status, ERR_MMA_ACC);
+        const long long t1 = clock64();
+        if (warp == 1)
+            cycles[blockIdx.x] = (unsigned long long)(t1 - t0);
+    }
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    if (warp == 0)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+}
+
+// One launch after one warm-up; returns the mean over the SMs of cycles per MMA (all issuers' MMAs counted).
+int mma_issue_selftest(nncb_context *ctx, int n_cols, int issuers, uint32_t mmas_per_issuer, double *cycles_per_mma) {
+    if (n_cols < 16 || n_cols > 256 || n_cols % 16 != 0 || issuers < 1 || issuers > 2 || mmas_per_issuer < 4 ||
+        mmas_per_issuer > (1u << 22))
+        return fail(-EINVAL, "mma issue self-test: 16 <= n_cols <= 256 in steps of 16, issuers 1 or 2, 4 <= mmas <= 2^22");
+    const uint32_t groups = mmas_per_issuer / 4;
+    const uint32_t idesc = (2u << 4) | ((uint32_t)(n_cols >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+    const size_t smem_one_per_sm = 120 * 1024; // more than half of an SM's shared memory: one CTA, one TMEM allocation per SM
+    NNCB_CUDA_TRY(cudaFuncSetAttribute(mma_issue_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_one_per_sm));
+    unsigned long long *d_cyc = nullptr;
+    NNCB_CUDA_TRY(cudaMalloc(&d_cyc, sizeof(unsigned long long) * ctx->sm_count));
+    int rc = 0;
+    for (int r = 0; r < 2 && rc == 0; r++) {
+        mma_issue_kernel<<<ctx->sm_count, 128, smem_one_per_sm, ctx->stream>>>(groups, idesc, issuers, d_cyc, ctx->d_status,
+                                                                               ctx->opt.wait_limit_us);
+        rc = after_launch(ctx, "mma_issue");
+    }
+    std::vector<unsigned long long> h(ctx->sm_count);
+    if (rc == 0) {
+        cudaError_t e = cudaMemcpyAsync(h.data(), d_cyc, sizeof(unsigned long long) * ctx->sm_count, cudaMemcpyDeviceToHost, ctx->stream);
+        if (e == cudaSuccess)
+            e = cudaStreamSynchronize(ctx->stream);
+        if (e != cudaSuccess)
+            rc = fail(-EIO, "mma issue self-test: %s", cudaGetErrorString(e));
+    }
+    cudaFree(d_cyc);
+    if (rc == 0) {
+        double sum = 0;
+        for (unsigned long long c : h)
+            sum += (double)c;
+        *cycles_per_mma = sum / ctx->sm_count / ((double)groups * 4.0 * issuers);
+    }
+    return rc;
+}
+
 static int pick_bn(int oc, long long K, const nncb_options &opt) {
     // N tile width. 128, 96, 64, 48 and 32 are the widths the fast epilogue stages; a layer whose channel
     // count is a multiple of 16 takes the one with the least modelled time per 128-pixel tile row. A tile costs
@@ -2009,6 +2117,7 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
         bool ok = true;
         fe.so = d.out_scale, fe.zo = (float)d.out_zp;
         fe.rso = rn_reciprocal(d.out_scale, &ok);
+        fe.one = 1.0f;
         // quantized clamp bounds: q(clamp(v, lo, hi)) == clamp(q(v), q(lo), q(hi)) for the monotone q
         auto quant = [&](float v) {
             if (std::isinf(v))

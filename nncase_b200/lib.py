@@ -127,6 +127,7 @@ SIGNATURES = {
     "nncb_program_profile_text": (_I, [_VP, C.c_char_p, _SZ]),
     "nncb_program_profile_ms": (_I, [_VP, C.POINTER(_F), _I32]),
     "nncb_selftest_int8_peak": (_I, [_VP, C.c_uint32, _I, _I, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
+    "nncb_selftest_mma_issue": (_I, [_VP, _I, _I, C.c_uint32, C.POINTER(C.c_double)]),
     "nncb_qconv2d_host": (_I, [_VP, C.POINTER(Conv2dDesc), _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP]),
 }
 

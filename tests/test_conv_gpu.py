@@ -388,6 +388,23 @@ def test_int8_peak_selftest_runs(ctx):
         assert best.value >= mean.value > 1000.0, (best.value, mean.value)
 
 
+def test_mma_issue_selftest(ctx):
+    """The issue-pace loop returns by itself; two issuing warps are not slower than one at a 64-column tile, and no
+    configuration beats the pace of the tensor pipe itself (n / 2 cycles per MMA is below what any B200 clock allows)."""
+    import ctypes as C
+    with pytest.raises(L.NncbError):
+        L.check(ctx._lib.nncb_selftest_mma_issue(ctx._h, 100, 1, 4096, C.byref(C.c_double())))
+    got = {}
+    for n in (64, 144, 256):
+        for issuers in (1, 2):
+            c = C.c_double()
+            L.check(ctx._lib.nncb_selftest_mma_issue(ctx._h, n, issuers, 8192, C.byref(c)))
+            ctx.check_status()
+            got[n, issuers] = c.value
+            assert c.value > n / 2.0, (n, issuers, c.value)
+    assert got[64, 2] <= got[64, 1] * 1.05, got
+
+
 def test_batched_matmul_with_broadcast_weights(ctx, qo):
     """[B1, B2, M, K] x [K, N]: leading dimensions are batches of rows over one constant right-hand side, the
     broadcast case of the reference's mat_mul (reference/matmul.cpp:57-89)."""
