@@ -35,6 +35,7 @@ class CudaFunction:
         in_t = program["tensors"][program["input"]]
         self.in_qp = in_t["qp"]
         self._graph = None
+        self.pipeline_graphs = True   # submit_host replays one captured graph per staging buffer
         self._static_in = None
         self.launches_per_call = None
 
@@ -212,7 +213,7 @@ class CudaFunction:
             in_t = self.program["tensors"][self.program["input"]]
             self._pipe = dict(copy=torch.cuda.Stream(dev), comp=torch.cuda.Stream(dev), xd=[None, None],
                               copied=[torch.cuda.Event(), torch.cuda.Event()],
-                              done=[torch.cuda.Event(), torch.cuda.Event()], n=0)
+                              done=[torch.cuda.Event(), torch.cuda.Event()], n=0, graphs=[None, None], uses=[0, 0])
         return self._pipe
 
     def submit_host(self, x_host, out_host):
@@ -226,6 +227,7 @@ class CudaFunction:
         b = p["n"] & 1
         if p["xd"][b] is None or p["xd"][b].shape != x_host.shape:
             p["xd"][b] = torch.empty(x_host.shape, dtype=torch.float32, device=self.ctx.device)
+            p["graphs"][b], p["uses"][b] = None, 0
         with torch.cuda.stream(p["copy"]):
             if p["n"] >= 2:
                 p["copy"].wait_event(p["done"][b])     # the kernels that read this staging buffer two batches ago
@@ -234,11 +236,25 @@ class CudaFunction:
         with torch.cuda.stream(p["comp"]):
             p["comp"].wait_event(p["copied"][b])
             self.ctx.use_current_stream()
-            before = self.ctx.launches
-            out = self._run(p["xd"][b])
-            self.launches_per_call = self.ctx.launches - before
+            if p["graphs"][b] is not None:
+                p["graphs"][b].replay()              # the kernels of one call, reading this staging buffer
+                out = self.buffers[self.program["output"]]
+            else:
+                before = self.ctx.launches
+                out = self._run(p["xd"][b])
+                self.launches_per_call = self.ctx.launches - before
             out_host.copy_(out, non_blocking=True)
             p["done"][b].record()
+        p["uses"][b] += 1
+        if p["graphs"][b] is None and p["uses"][b] == 1 and self.pipeline_graphs:
+            # the first batch through a staging buffer has run eagerly (plans and tensor maps are warm): capture the
+            # launch list once per buffer; later batches replay it (one graph launch instead of one call per operator)
+            p["comp"].synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=p["comp"], capture_error_mode="thread_local"):
+                self.ctx.use_current_stream()
+                self._run(p["xd"][b])
+            p["graphs"][b] = g
         p["n"] += 1
         return p["done"][b]
 
@@ -257,6 +273,9 @@ class CudaFunction:
         return [self.buffers[n] for n in self.program.get("outputs", [self.program["output"]])]
 
     def close(self):
+        if getattr(self, "_pipe", None) is not None:
+            self.drain()
+            self._pipe["graphs"] = [None, None]
         for p in self.plans:
             p.close()
         self.plans = []

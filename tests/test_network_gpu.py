@@ -154,3 +154,30 @@ def test_yolov8s_benchmark_configuration(ctx):
     program = builder.build_program(graph, cal, device=ctx.device)
     x = np.random.default_rng(2004).uniform(0, 1, (64, 3, 640, 640)).astype(np.float32)
     assert _sampled_parity(ctx, program, x, [0, 63]) == len(program["tensors"])
+
+
+def test_pipelined_host_calls_match_single_calls(ctx):
+    """CudaFunction.submit_host / drain (the call the end-to-end benchmark number goes through): seven batches with
+    different inputs, queued back to back from pinned host buffers through the two staging buffers and the captured
+    graphs, give byte for byte what invoke() gives on each batch; results land in the caller's host buffers."""
+    graph = networks.resnet50v2(1003)
+    cal = [np.random.default_rng(3003 + i).normal(0, 1, (1, 3, 224, 224)).astype(np.float32) for i in range(2)]
+    program = builder.build_program(graph, cal)
+    n, batches = 4, 7
+    fn = CudaFunction(program, n, ctx)
+    rng = np.random.default_rng(2011)
+    xs = [torch.from_numpy(rng.normal(0, 1, (n, 3, 224, 224)).astype(np.float32)).pin_memory() for _ in range(batches)]
+    want = [fn.invoke(x.cuda()).cpu().clone() for x in xs]
+    assert not torch.equal(want[0], want[1])
+    outs = [torch.zeros(want[0].shape, dtype=want[0].dtype).pin_memory() for _ in range(batches)]
+    with pytest.raises(L.NncbError):
+        fn.submit_host(xs[0].clone(), outs[0])       # not pinned
+    for x, o in zip(xs, outs):
+        fn.submit_host(x, o)
+    fn.drain()
+    ctx.check_status()
+    for i in range(batches):
+        assert torch.equal(outs[i], want[i]), i
+    # a single call afterwards still works on the caller's stream
+    assert torch.equal(fn.invoke(xs[2].cuda()).cpu(), want[2])
+    fn.close()
