@@ -583,13 +583,13 @@ def run_layer(args):
                           gbs=(in_bytes + out_bytes + op["w"].size) / (ms / 1000) / 1e9)))
 
 
-def measure_attention(torch, ctx, pk, steps, warmup):
+def measure_attention(torch, ctx, pk, steps, warmup, batch=64):
     """Paged-attention decode at the Qwen2-0.5B decode shape (batch 64, context 2048, 14 query / 2 kv heads,
     head_dim 64, 16-token f16 pages, random block-table permutation). One step = the attention of all 24
     layers, each over its own KV pool (1.61 GB of K/V per step, larger than L2), replayed as one CUDA graph;
     achieved HBM GB/s over the K/V bytes referenced."""
     dev = ctx.device
-    B, Hq, Hkv, D, page, n_ctx, layers = 64, 14, 2, 64, 16, 2048, 24
+    B, Hq, Hkv, D, page, n_ctx, layers = batch, 14, 2, 64, 16, 2048, 24
     pages = B * n_ctx // page
     g = torch.Generator(device=dev).manual_seed(2005)
     pools = [(torch.randn((pages, Hkv, page, D), device=dev, generator=g, dtype=torch.float16),
@@ -715,7 +715,7 @@ def run_attention(args):
     import torch
     from nncase_b200.kernels import Context
     ctx = Context(0)
-    print(json.dumps(measure_attention(torch, ctx, peaks(), args.steps, args.warmup)))
+    print(json.dumps(measure_attention(torch, ctx, peaks(), args.steps, args.warmup, args.attention_batch)))
 
 
 def run_decode(args):
@@ -755,6 +755,7 @@ def main():
     ap.add_argument("--no-secondary", action="store_true", help="skip the secondary measurements (attention, decode, ...)")
     ap.add_argument("--layer", default=None, help="time only this conv layer (profiling aid)")
     ap.add_argument("--attention", action="store_true", help="only the paged-attention decode measurement")
+    ap.add_argument("--attention-batch", type=int, default=64, help="sequences of the --attention measurement (74 = one (sequence, kv head) pair per SM of a 148-SM part)")
     ap.add_argument("--decode", action="store_true", help="only the decoder step (tensor parallel under torchrun)")
     ap.add_argument("--streams", action="store_true", help="only the streaming kernels (quantize, dequantize, add, max-pool, input stage)")
     args = ap.parse_args()
