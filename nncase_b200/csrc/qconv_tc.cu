@@ -763,8 +763,8 @@ __device__ __forceinline__ void producer_loop(const TcGeom &g, const StageGeom &
 // WIDE: one pixel per swizzle row of `cell16` 16-byte units, a tap is `cell16 / 2` MMAs; else 16-byte cells and
 // one MMA per pair of cells of a kernel row. With DUAL the taps go to the two issuers in turn; issuer 0 owns the
 // first one, which overwrites the accumulator.
-template <int KH, int KWC, bool WIDE, bool DUAL>
-__device__ __forceinline__ bool patch_taps(uint32_t tmem_d, const dev::Desc da0, const dev::Desc db0, const uint32_t row16,
+template <int KH, int KWC, bool WIDE>
+__device__ __forceinline__ bool patch_taps(const bool DUAL, uint32_t tmem_d, const dev::Desc da0, const dev::Desc db0, const uint32_t row16,
                                            const uint32_t cell16, const uint32_t bres_pitch16, const uint32_t idesc,
                                            const uint32_t mi, const uint32_t bar_init, const uint32_t init_parity,
                                            volatile int *abort_flag, int *status) {
@@ -808,16 +808,16 @@ __device__ __forceinline__ bool patch_taps(uint32_t tmem_d, const dev::Desc da0,
 // One lane of warp 1 (and, with two issuers, of warp 18): issues the MMAs of every K block into the tile's TMEM
 // accumulator. One thread's stream per stage -- barrier probe, fence, descriptor arithmetic, four MMAs, commit,
 // ring bookkeeping, each a dependent instruction or a branch of a lone warp -- takes 600 to 700 cycles, twice what
-// the tensor pipe needs for the stage's MMAs at 144 columns. With DUAL two threads take the stages of the ring in
+// the tensor pipe needs for the stage's MMAs at 144 columns. With DUAL (a run-time flag: one copy of the loop keeps
+// the kernels' code, which every launch has to fetch, short) two threads take the stages of the ring in
 // turn: stage index modulo 2 (with an odd stage count one of them takes the last and the first stage of the ring),
 // so that a stage always belongs to the same thread and each of its barrier phases is seen in order by one
 // waiter. Both accumulate into the same TMEM accumulator (32-bit integer sums do not depend on the order); the owner of a tile's first stage issues its
 // first MMA, which overwrites the accumulator, and arrives on bar_acc_init; the other waits for that before its
 // first MMA of the tile, with tcgen05 fences on both sides of the barrier. Each commits to the tile's
 // bar_acc_full (count 2) after its last MMA.
-template <bool DUAL>
 __device__ __forceinline__ void mma_loop(const TcGeom &g, const StageGeom &sg, TcShared &sh, uint32_t tmem_base,
-                                         int *status, const uint32_t mi) {
+                                         int *status, const bool DUAL, const uint32_t mi) {
     using namespace dev;
     const int k_blocks = g.taps * g.c_blocks;
     const int total_tiles = g.m_tiles * g.n_tiles;
@@ -860,13 +860,13 @@ __device__ __forceinline__ void mma_loop(const TcGeom &g, const StageGeom &sg, T
             if (g.cell == 16 && g.kh == 4 && g.kw_cells == 4) {
                 const uint32_t row16 = (uint32_t)g.patch_w;
                 const Desc da = make_desc(smem_desc_plain(sg.smem_base, 16u, row16 * 16u)) + stage * pitch16;
-                if (!patch_taps<4, 4, false, DUAL>(tmem_d, da, desc_bres, row16, 1u, bres_pitch16, idesc, mi, bar_init, init_parity,
+                if (!patch_taps<4, 4, false>(DUAL, tmem_d, da, desc_bres, row16, 1u, bres_pitch16, idesc, mi, bar_init, init_parity,
                                                    &sh.abort_flag, status))
                     return;
             } else if (g.cell != 16 && g.kh == 3 && g.kw_cells == 3) {
                 const uint32_t cell16 = (uint32_t)g.cell >> 4, row16 = (uint32_t)g.patch_w * cell16;
                 const Desc da = make_desc(smem_desc_sbo(sg.smem_base, g.cell, row16 * 16u)) + stage * pitch16;
-                if (!patch_taps<3, 3, true, DUAL>(tmem_d, da, desc_bres, row16, cell16, bres_pitch16, idesc, mi, bar_init, init_parity,
+                if (!patch_taps<3, 3, true>(DUAL, tmem_d, da, desc_bres, row16, cell16, bres_pitch16, idesc, mi, bar_init, init_parity,
                                                   &sh.abort_flag, status))
                     return;
             } else if (g.cell == 16) {
@@ -1119,15 +1119,11 @@ tc_conv_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (lane == 0)
             producer_loop(g, sg, sh, &tmap_a, &tmap_b, a.status, g.load_warps == 2 ? (g.load_by_stage ? 3 : 1) : 0);
     } else if (warp == 1) {
-        if (lane == 0) {
-            if (g.issuers == 2)
-                mma_loop<true>(g, sg, sh, tmem_base, a.status, 0);
-            else
-                mma_loop<false>(g, sg, sh, tmem_base, a.status, 0);
-        }
+        if (lane == 0)
+            mma_loop(g, sg, sh, tmem_base, a.status, g.issuers == 2, 0);
     } else if (warp == WARP_MMA2) {
         if (lane == 0 && g.issuers == 2)
-            mma_loop<true>(g, sg, sh, tmem_base, a.status, 1);
+            mma_loop(g, sg, sh, tmem_base, a.status, true, 1);
     } else if (warp == WARP_LOAD2) {
         if (lane == 0 && g.load_warps == 2)
             producer_loop(g, sg, sh, &tmap_a, &tmap_b, a.status, g.load_by_stage ? 4 : 2);
@@ -1551,15 +1547,11 @@ tc_conv_fast_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (lane == 0)
             producer_loop(g, sg, sh, &tmap_a, &tmap_b, a.status, g.load_warps == 2 ? (g.load_by_stage ? 3 : 1) : 0);
     } else if (warp == 1) {
-        if (lane == 0) {
-            if (g.issuers == 2)
-                mma_loop<true>(g, sg, sh, tmem_base, a.status, 0);
-            else
-                mma_loop<false>(g, sg, sh, tmem_base, a.status, 0);
-        }
+        if (lane == 0)
+            mma_loop(g, sg, sh, tmem_base, a.status, g.issuers == 2, 0);
     } else if (warp == WARP_MMA2) {
         if (lane == 0 && g.issuers == 2)
-            mma_loop<true>(g, sg, sh, tmem_base, a.status, 1);
+            mma_loop(g, sg, sh, tmem_base, a.status, true, 1);
     } else if (warp == WARP_LOAD2) {
         if (lane == 0 && g.load_warps == 2)
             producer_loop(g, sg, sh, &tmap_a, &tmap_b, a.status, g.load_by_stage ? 4 : 2);
@@ -2317,6 +2309,9 @@ int tc_conv_run(nncb_context *ctx, nncb_qconv2d *cv, const uint8_t *x, const uin
     a.status = ctx->d_status;
     const int tiles = tp->g.m_tiles * tp->g.n_tiles;
     const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+    // the two further role warps exist only in plans that use them: every warp of the block meets the set-up and
+    // tear-down barriers, and short launches (single images, narrow layers) feel two idle warps
+    const int threads = (tp->g.issuers == 2 || tp->g.load_warps == 2) ? TC_THREADS : TC_THREADS - 64;
     auto al16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
     if (tp->fast && al16(y) && al16(y2) && al16(res)) {
         if (tp->f->lut_only) {
@@ -2340,10 +2335,10 @@ int tc_conv_run(nncb_context *ctx, nncb_qconv2d *cv, const uint8_t *x, const uin
 #define NNCB_LAUNCH_FAST(R, Y, C)                                                                                     \
     do {                                                                                                              \
         if (tp->g.mode == MODE_ROWS || tp->g.mode == MODE_PATCH)                                                      \
-            tc_conv_fast_kernel<R, Y, C, true><<<grid, TC_THREADS, tp->smem_bytes, ctx->stream>>>(                    \
+            tc_conv_fast_kernel<R, Y, C, true><<<grid, threads, tp->smem_bytes, ctx->stream>>>(                       \
                 tp->tmap_a, tp->tmap_b, tp->tmap_y, my2, mres, a);                                                    \
         else                                                                                                          \
-            tc_conv_fast_kernel<R, Y, C, false><<<grid, TC_THREADS, tp->smem_bytes, ctx->stream>>>(                   \
+            tc_conv_fast_kernel<R, Y, C, false><<<grid, threads, tp->smem_bytes, ctx->stream>>>(                      \
                 tp->tmap_a, tp->tmap_b, tp->tmap_y, my2, mres, a);                                                    \
     } while (0)
         switch (variant) {
@@ -2359,7 +2354,7 @@ int tc_conv_run(nncb_context *ctx, nncb_qconv2d *cv, const uint8_t *x, const uin
 #undef NNCB_LAUNCH_FAST
         return after_launch(ctx, "tc_conv_fast");
     }
-    tc_conv_kernel<<<grid, TC_THREADS, tp->smem_bytes, ctx->stream>>>(tp->tmap_a, tp->tmap_b, a);
+    tc_conv_kernel<<<grid, threads, tp->smem_bytes, ctx->stream>>>(tp->tmap_a, tp->tmap_b, a);
     return after_launch(ctx, "tc_conv");
 }
 
