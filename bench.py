@@ -176,11 +176,17 @@ def _events(torch):
 
 
 def time_device(torch, fn, x, steps, barrier):
+    """K steps with the input resident in HBM. The step's launch list is captured once (CudaFunction.capture) and
+    replayed: the same kernels on the same buffers, without the host's per-launch cost between them (2 % of a
+    512-image step, 8 % of a 64-image one)."""
+    fn.capture(x)
+    for _ in range(2):
+        fn.replay()
     a, b = _events(torch)
     barrier()
     a.record()
     for _ in range(steps):
-        fn.invoke(x)
+        fn.replay()
     b.record()
     barrier()
     return a.elapsed_time(b)
@@ -335,9 +341,8 @@ def run_ours(args):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    l0 = ctx.launches
     ms = time_device(torch, fn, x, steps, barrier)
-    gpu_launches = ctx.launches - l0
+    gpu_launches = launches_per_step * steps   # kernels of this library run by the replays inside the timed region
     ctx.check_status()
 
     # -------- end to end through the library's host-buffer call --------
@@ -402,6 +407,7 @@ def run_ours(args):
         data="synthetic", impl="ours",
         config=dict(workload="resnet50v2_u8u8", global_batch=G, batch_per_gpu=B, w_quant=args.w_quant,
                     input="f32 NCHW [B,3,224,224] N(0,1)", l2="inputs and activations larger than L2 (no flush)",
+                    launch="the step's launch list captured once and replayed as a CUDA graph (value and e2e)",
                     parallelism=f"batch-sharded x{world}, no collective"),
         e2e=dict(value=e2e_value, unit=UNIT, h2d_bytes_per_step=G * 3 * 224 * 224 * 4, d2h_bytes_per_step=G * 1000 * 4,
                  call="CudaFunction.submit_host / drain (pinned host buffers, two device staging buffers, two streams)",

@@ -175,7 +175,8 @@ class CudaFunction:
         self.invoke(self._static_in)  # warm-up outside capture (tensor maps, lazy init)
         torch.cuda.synchronize(self.ctx.device)
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
+        # thread-local capture: another thread of the process (a collective library's watchdog) may call the runtime
+        with torch.cuda.graph(g, capture_error_mode="thread_local"):
             self.ctx.use_current_stream()
             self._run(self._static_in)
         self.ctx.use_current_stream()
