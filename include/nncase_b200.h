@@ -55,6 +55,8 @@ NNCB_API void *nncb_context_stream(nncb_context *ctx);
 NNCB_API int nncb_synchronize(nncb_context *ctx);
 /* Per-context options, by name (the role of the reference interpreter's options_dict,
  * src/Native/src/runtime/interpreter.cpp:29-31). Read when a plan is created or a kernel is launched.
+ *   "launch.overlap"         1: tensor-core convolutions are launched as programmatic dependents of the kernel before them in
+ *                            the stream (their set-up overlaps its last tiles); 0: plain launches
  *   "wait_limit_us"          kernel-internal waits give up after this long (default 1,000,000)
  *   "conv.tile_n"            force the N tile of the tensor-core convolution: 128, 96, 64, 48, 32 (0 = choose)
  *   "conv.mma_issuers"       force the number of warps that issue the convolution's MMAs: 1 or 2 (0 = choose)

@@ -210,6 +210,7 @@ static int *option_slot(nncb_context *ctx, const char *name) {
         {"depthwise.dot_product", &ctx->opt.depthwise_dot},
         {"attention.warps", &ctx->opt.attention_warps},
         {"attention.splits", &ctx->opt.attention_splits},
+        {"launch.overlap", &ctx->opt.launch_overlap},
         {"wait_limit_us", reinterpret_cast<int *>(&ctx->opt.wait_limit_us)},
         {"debug.withhold_load", &ctx->opt.debug_withhold_load},
     };

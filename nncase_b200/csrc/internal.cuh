@@ -22,6 +22,7 @@ struct nncb_options {
     int attention_warps = 0;    // force the CTA width of paged attention (4 or 8)
     int attention_splits = 0;   // force its number of context splits
     unsigned wait_limit_us = 1000000; // kernel-internal waits give up after this long
+    int launch_overlap = 1;     // tensor-core convolutions are launched as programmatic dependents of their predecessor
     int debug_withhold_load = 0; // self-test of the give-up path: the convolution's producer leaves out one load
 };
 
@@ -59,6 +60,30 @@ int fail(int code, const char *fmt, ...);
 
 // Checks the launch that was just enqueued and counts it.
 int after_launch(nncb_context *ctx, const char *what);
+
+// ---- programmatic dependent launch ------------------------------------------------------------------
+// A kernel launched with the programmatic-serialization attribute may become resident while its predecessor in
+// the stream still runs (on SMs the predecessor has left): its set-up -- barriers, TMEM allocation, tables and
+// constants that no kernel writes -- overlaps the predecessor's last tiles and the launch latency. It must call
+// grid_dependency_wait() before it touches memory that an earlier kernel wrote or reads; the wait returns when
+// the predecessor grid has completed and its writes are visible (launched without the attribute, at once). A
+// kernel lets its own dependent in with grid_dependency_release(); without that call the dependent starts when
+// the kernel ends, as in a plain launch.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_dependent(nncb_context *ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                           Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->opt.launch_overlap ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 // Raise the dynamic shared-memory limit of this file's kernels on the CURRENT device (the attribute is per
 // device; called for every context that is created).

@@ -640,6 +640,7 @@ __device__ __forceinline__ void producer_loop(const TcGeom &g, const StageGeom &
         for (int kbi = 0; kbi < k_blocks; kbi++)
             tma_load_2d(sg.b_resident + kbi * sg.b_pitch, tmap_b, bar_b, kbi * kb, 0);
     }
+    grid_dependency_wait(); // activations are the previous kernel's output (the weights above are nobody's)
     if (g.mode == MODE_PATCH) {
         // one load per tile: the input cells under the output patch (weights are resident, one N tile)
         const uint32_t patch_bytes = (uint32_t)g.patch_w * g.cell * g.patch_h;
@@ -1113,6 +1114,7 @@ tc_conv_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const TcGeom &g = a.g;
     const StageGeom sg = stage_geom(g, smem_raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    grid_dependency_release(); // the next kernel of the stream may take the SMs this one leaves
     tc_setup(g, sh, warp);
     const uint32_t tmem_base = sh.tmem_base_slot;
     if (warp == 0) {
@@ -1288,6 +1290,7 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
     // residual sub-tiles of this warp's next RES_BUFS tiles are always in flight
     const int tstep = f.halves * (int)gridDim.x; // distance between this warp's tiles
     if (RES && lane == 0 && active) {
+        grid_dependency_wait(); // the residual is an earlier kernel's output
         int t = blockIdx.x + half * (int)gridDim.x;
         for (int b = 0; b < RES_BUFS && t < total_tiles; b++, t += tstep) {
             int c[4];
@@ -1541,6 +1544,7 @@ tc_conv_fast_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const TcGeom &g = a.g;
     const StageGeom sg = stage_geom(g, smem_raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    grid_dependency_release(); // the next kernel of the stream may take the SMs this one leaves
     tc_setup(g, sh, warp);
     const uint32_t tmem_base = sh.tmem_base_slot;
     if (warp == 0) {
@@ -2335,11 +2339,11 @@ int tc_conv_run(nncb_context *ctx, nncb_qconv2d *cv, const uint8_t *x, const uin
 #define NNCB_LAUNCH_FAST(R, Y, C)                                                                                     \
     do {                                                                                                              \
         if (tp->g.mode == MODE_ROWS || tp->g.mode == MODE_PATCH)                                                      \
-            tc_conv_fast_kernel<R, Y, C, true><<<grid, threads, tp->smem_bytes, ctx->stream>>>(                       \
-                tp->tmap_a, tp->tmap_b, tp->tmap_y, my2, mres, a);                                                    \
+            launch_dependent(ctx, tc_conv_fast_kernel<R, Y, C, true>, dim3(grid), dim3(threads), tp->smem_bytes,        \
+                             tp->tmap_a, tp->tmap_b, tp->tmap_y, my2, mres, a);                                       \
         else                                                                                                          \
-            tc_conv_fast_kernel<R, Y, C, false><<<grid, threads, tp->smem_bytes, ctx->stream>>>(                      \
-                tp->tmap_a, tp->tmap_b, tp->tmap_y, my2, mres, a);                                                    \
+            launch_dependent(ctx, tc_conv_fast_kernel<R, Y, C, false>, dim3(grid), dim3(threads), tp->smem_bytes,       \
+                             tp->tmap_a, tp->tmap_b, tp->tmap_y, my2, mres, a);                                       \
     } while (0)
         switch (variant) {
         case 0: NNCB_LAUNCH_FAST(false, false, false); break;
@@ -2354,7 +2358,7 @@ int tc_conv_run(nncb_context *ctx, nncb_qconv2d *cv, const uint8_t *x, const uin
 #undef NNCB_LAUNCH_FAST
         return after_launch(ctx, "tc_conv_fast");
     }
-    tc_conv_kernel<<<grid, threads, tp->smem_bytes, ctx->stream>>>(tp->tmap_a, tp->tmap_b, a);
+    launch_dependent(ctx, tc_conv_kernel, dim3(grid), dim3(threads), tp->smem_bytes, tp->tmap_a, tp->tmap_b, a);
     return after_launch(ctx, "tc_conv");
 }
 

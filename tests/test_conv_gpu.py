@@ -304,6 +304,43 @@ def test_role_warp_counts_do_not_change_the_result(ctx, qo, shape, issuers, load
     plan.close()
 
 
+@pytest.mark.parametrize("overlap", [0, 1])
+def test_chained_convolutions_with_and_without_launch_overlap(ctx, qo, overlap):
+    """Convolutions are launched as programmatic dependents of the kernel before them: a kernel may become resident
+    while its predecessor still runs and waits (griddepcontrol.wait) before it reads what the predecessor wrote. A
+    chain of three layers, each reading the previous one's output (the third also as its residual), run twenty times
+    back to back, gives the oracle's bytes with the overlap on and off."""
+    n, h, w, c = 4, 28, 28, 128
+    rng = np.random.default_rng(123)
+    xq = rng.integers(0, 256, (n, h, w, c), dtype=np.uint8)
+    cases = [make_case(200 + i, n, h, w, c, c, k, k) for i, k in enumerate((1, 3, 1))]
+    rq, aq = QuantParam(117, 0.05), QuantParam(125, 0.06)
+    ctx.set_option("launch.overlap", overlap)
+    try:
+        plans, want, cur, zx = [], [], xq, cases[0][1]
+        for i, (_, _, wq, zw, mult, bias, oqp) in enumerate(cases):
+            pad = 1 if wq.shape[1] == 3 else 0
+            kw = dict(residual=(rq, aq)) if i == 2 else {}
+            plans.append(ctx.conv2d_plan(cur.shape, wq, zw, mult, bias, zx, oqp, padding=(pad,) * 4, force_path=L.PATH_TC, **kw))
+            y = qo.qconv2d_u8(cur, wq, zw, mult, bias, zx, oqp.scale, oqp.zero_point, pad=(pad,) * 4)
+            if i == 2:
+                y = qo.qadd_u8(y, want[0], oqp.scale, oqp.zero_point, rq.scale, rq.zero_point, aq.scale, aq.zero_point)
+            want.append(y)
+            cur, zx = y, oqp.zero_point
+        x = torch.from_numpy(xq).cuda()
+        for _ in range(20):
+            y0 = plans[0](x)
+            y1 = plans[1](y0)
+            y2 = plans[2](y1, y0)
+        assert np.array_equal(y0.cpu().numpy(), want[0]) and np.array_equal(y1.cpu().numpy(), want[1])
+        assert np.array_equal(y2.cpu().numpy(), want[2])
+        ctx.check_status()
+        for p_ in plans:
+            p_.close()
+    finally:
+        ctx.set_option("launch.overlap", 1)
+
+
 @pytest.mark.parametrize("variant", ["plain", "residual", "deep"])
 def test_bounded_wait_gives_up_and_the_context_stays_usable(ctx, qo, variant):
     """Every wait inside the tensor-core kernel has a time limit. With the limit shortened to 2 ms and the
