@@ -189,9 +189,14 @@ int nncb_context_create(int device, void *stream, nncb_context **out) {
         ce = cudaMalloc(&ctx->d_gemv_ws, ws_bytes);
     if (ce == cudaSuccess)
         ce = cudaMemset(ctx->d_gemv_ws, 0, ws_bytes);
+    if (ce == cudaSuccess)
+        ce = cudaMalloc(&ctx->d_gemm_ws, nncb::gemm_w8a16_tc_workspace_bytes());
+    if (ce == cudaSuccess)
+        ce = cudaMemset(ctx->d_gemm_ws, 0, nncb::gemm_w8a16_tc_workspace_bytes());
     if (ce != cudaSuccess) {
         cudaFree(ctx->d_status);
         cudaFree(ctx->d_gemv_ws);
+        cudaFree(ctx->d_gemm_ws);
         delete ctx;
         cudaGetLastError();
         return fail(ce == cudaErrorMemoryAllocation ? -ENOMEM : -EIO, "nncb_context_create: %s", cudaGetErrorString(ce));
@@ -211,6 +216,7 @@ static int *option_slot(nncb_context *ctx, const char *name) {
         {"attention.warps", &ctx->opt.attention_warps},
         {"attention.splits", &ctx->opt.attention_splits},
         {"launch.overlap", &ctx->opt.launch_overlap},
+        {"matmul.tensor_core", &ctx->opt.matmul_tensor_core},
         {"wait_limit_us", reinterpret_cast<int *>(&ctx->opt.wait_limit_us)},
         {"debug.withhold_load", &ctx->opt.debug_withhold_load},
     };
@@ -249,6 +255,7 @@ int nncb_context_destroy(nncb_context *ctx) {
     cudaStreamSynchronize(ctx->stream);
     cudaFree(ctx->d_status);
     cudaFree(ctx->d_gemv_ws);
+    cudaFree(ctx->d_gemm_ws);
     delete ctx;
     return 0;
 }

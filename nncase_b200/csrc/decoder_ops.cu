@@ -289,6 +289,8 @@ static int gemv_w8a16_fused(nncb_context *ctx, const void *x, const int8_t *w, c
         return fail(-ENOSYS, "gemv_w8a16: K must be a multiple of 64");
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15)
         return fail(-EINVAL, "gemv_w8a16: x and w must be 16-byte aligned");
+    if (ctx->opt.matmul_tensor_core && gemm_w8a16_tc_applies(ctx, M, N, K))
+        return gemm_w8a16_tc(ctx, x, w, scale, bias, residual, y, M, N, K, fu.swiglu);
     const __half *xs = (const __half *)x, *sc = (const __half *)scale, *bi = (const __half *)bias,
                  *re = (const __half *)residual;
     __half *ys = (__half *)y;

@@ -22,6 +22,7 @@ struct nncb_options {
     int attention_warps = 0;    // force the CTA width of paged attention (4 or 8)
     int attention_splits = 0;   // force its number of context splits
     unsigned wait_limit_us = 1000000; // kernel-internal waits give up after this long
+    int matmul_tensor_core = 1; // w8a16 MatMul on tcgen05: 0 never, 1 for matrices of 2 M weights or more, 2 wherever it fits
     int launch_overlap = 1;     // tensor-core convolutions are launched as programmatic dependents of their predecessor
     int debug_withhold_load = 0; // self-test of the give-up path: the convolution's producer leaves out one load
 };
@@ -33,6 +34,7 @@ struct nncb_context {
     uint64_t launches = 0;
     int sm_count = 148;
     int *d_status = nullptr;  // device word: 0 ok, else code of the first bounded wait that gave up
+    float *d_gemm_ws = nullptr; // split-K meeting place of the tensor-core w8a16 MatMul: partials + one counter per channel tile, counters zero between launches
     float *d_gemv_ws = nullptr; // split-K meeting place of gemv_w8a16: GEMV_SPLIT_SLOTS x 16 x 64 f32 + one counter per slot, counters zero between launches
 };
 
@@ -60,6 +62,10 @@ int fail(int code, const char *fmt, ...);
 
 // Checks the launch that was just enqueued and counts it.
 int after_launch(nncb_context *ctx, const char *what);
+bool gemm_w8a16_tc_applies(const nncb_context *ctx, int M, int N, int K);
+int gemm_w8a16_tc(nncb_context *ctx, const void *x, const int8_t *w, const void *scale, const void *bias, const void *residual,
+                  void *y, int M, int N, int K, int swiglu);
+size_t gemm_w8a16_tc_workspace_bytes();
 
 // ---- programmatic dependent launch ------------------------------------------------------------------
 // A kernel launched with the programmatic-serialization attribute may become resident while its predecessor in

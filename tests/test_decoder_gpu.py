@@ -20,8 +20,17 @@ def close(got, want, tol=1e-3):
     assert err <= tol * rng, f"max abs err {err} vs range {rng}"
 
 
-@pytest.mark.parametrize("m,n,k", [(64, 1152, 896), (64, 896, 4864), (5, 1000, 128), (1, 16, 64), (33, 9728, 896)])
-def test_gemv_w8a16(ctx, m, n, k):
+@pytest.fixture(params=[0, 2], ids=["mma_sync", "tcgen05"])
+def matmul_form(ctx, request):
+    """Both forms of the w8a16 MatMul: CUDA-core-fed mma.sync, and tcgen05 with the accumulator in TMEM (forced for
+    every shape that fits; by default it takes matrices of 2 M weights or more)."""
+    ctx.set_option("matmul.tensor_core", request.param)
+    yield request.param
+    ctx.set_option("matmul.tensor_core", 1)
+
+
+@pytest.mark.parametrize("m,n,k", [(64, 1152, 896), (64, 896, 4864), (5, 1000, 128), (1, 16, 64), (33, 9728, 896), (64, 4224, 896)])
+def test_gemv_w8a16(ctx, matmul_form, m, n, k):
     rng = np.random.default_rng(m + n)
     x = rng.normal(0, 1, (m, k)).astype(np.float16)
     wq, s = D.quantize_per_channel_i8(rng.normal(0, 0.02, (n, k)).astype(np.float32))
@@ -38,7 +47,7 @@ def test_gemv_w8a16(ctx, m, n, k):
 
 
 @pytest.mark.parametrize("m,inter,k", [(64, 4864, 896), (64, 2432, 896), (5, 24, 128), (33, 1024, 1280), (64, 64, 4864)])
-def test_gemv_with_swiglu_epilogue(ctx, m, inter, k):
+def test_gemv_with_swiglu_epilogue(ctx, matmul_form, m, inter, k):
     """The gate/up MatMul with SwiGLU in its epilogue, on interleaved gate/up rows: bit-identical to the
     MatMul followed by swiglu (the same f16 gate/up values meet the same f32 formula)."""
     rng = np.random.default_rng(m + inter + k)
