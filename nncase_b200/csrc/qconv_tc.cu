@@ -9,10 +9,13 @@
 //   rows per N tile.
 //
 //   One persistent CTA per SM, warp-specialised:
-//     warp 0      TMA producer   (one lane) fills a ring of shared-memory stages
-//     warp 1      MMA issuer     (one lane) tcgen05.mma into one of two TMEM accumulators
-//     warps 2..5  epilogue       tcgen05.ld the finished accumulator, requantise, store u8
-//   so the epilogue of tile i overlaps the main loop of tile i+1.
+//     warp 0       TMA producer   (one lane) fills a ring of shared-memory stages
+//     warp 1       MMA issuer     (one lane) tcgen05.mma into one of two TMEM accumulators
+//     warps 2..17  epilogue       tcgen05.ld the finished accumulator, requantise, store u8 (TMA stores)
+//     warps 18, 19 a second MMA issuer and a second load warp, in plans with deep K loops
+//   so the epilogue of tile i overlaps the main loop of tile i+1. Launched as a programmatic dependent of the
+//   kernel before it in the stream: set-up runs during that kernel's last tiles, the first load of
+//   activations (and of the residual) waits for its completion.
 //
 //   Zero points. The MMA accumulates raw sum(xq*wq); TMA fills padding with 0 (not with the
 //   zero point), so with "valid" = taps inside the image
