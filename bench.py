@@ -535,11 +535,65 @@ def latency_one_image(torch, ctx, which):
     return dict(us_per_image=us, images_per_s=1e6 / us, launches=launches, mode="CUDA graph replay, batch 1")
 
 
+def measure_matmuls(torch, ctx, pk, reps=100):
+    """The five w8a16 MatMuls of a Qwen2-0.5B-shaped decode step at 64 tokens, each replayed `reps` times in one CUDA
+    graph (weights warm in L2 except the LM head, which is larger than L2): microseconds per call, weight GB/s, and the
+    form that ran (tcgen05 for matrices of 2 M weights or more, mma.sync below)."""
+    from nncase_b200 import lib as L
+    dev = ctx.device
+    lib, h = ctx._lib, ctx._h
+    out = {}
+    shapes = [("qkv", 1152, 896, False, reps), ("o", 896, 896, False, reps), ("down", 896, 4864, False, reps),
+              ("gate_up_swiglu", 9728, 896, True, reps), ("lm_head", 151936, 896, False, max(4, reps // 5))]
+    M = 64
+    g = torch.Generator(device=dev).manual_seed(2007)
+    for name, N, K, swiglu, n_rep in shapes:
+        x = torch.randn((M, K), dtype=torch.float16, device=dev, generator=g)
+        w = torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev, generator=g)
+        sc = torch.rand((N,), dtype=torch.float16, device=dev, generator=g) * 0.01
+        y = torch.empty((M, N // 2 if swiglu else N), dtype=torch.float16, device=dev)
+
+        def call():
+            if swiglu:
+                L.check(lib.nncb_gemv_w8a16_swiglu(h, x.data_ptr(), w.data_ptr(), sc.data_ptr(), None, y.data_ptr(), M, N, K))
+            else:
+                L.check(lib.nncb_gemv_w8a16(h, x.data_ptr(), w.data_ptr(), sc.data_ptr(), None, None, y.data_ptr(), M, N, K))
+
+        ctx.use_current_stream()
+        for _ in range(3):
+            call()
+        torch.cuda.synchronize(dev)
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                ctx.use_current_stream()
+                for _ in range(n_rep):
+                    call()
+        ctx.use_current_stream()
+        graph.replay()
+        torch.cuda.synchronize(dev)
+        a, b = _events(torch)
+        a.record()
+        graph.replay()
+        b.record()
+        torch.cuda.synchronize(dev)
+        us = a.elapsed_time(b) / n_rep * 1e3
+        out[name] = dict(n=N, k=K, us=round(us, 2), weight_gbs=round(N * K / us / 1e3, 1),
+                         form="tcgen05" if N * K >= (1 << 21) else "mma.sync")
+        del graph
+    ctx.check_status()
+    out["tokens"] = M
+    return out
+
+
 def secondary(torch, ctx, args, pk):
     out = {}
     out["stream_kernels"] = stream_kernels(torch, ctx, pk)
     out["paged_attention"] = measure_attention(torch, ctx, pk, steps=20, warmup=3)
     out["decode"] = measure_decode(torch, ctx, pk, steps=20, warmup=3, world=1, rank=0)
+    out["decode_matmuls"] = measure_matmuls(torch, ctx, pk)
     out["latency_batch1"] = dict(resnet50v2=latency_one_image(torch, ctx, "resnet50v2"),
                                  mobilenetv2=latency_one_image(torch, ctx, "mobilenetv2"))
     torch.cuda.empty_cache()
@@ -760,6 +814,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true", help="skip the secondary measurements (attention, decode, ...)")
     ap.add_argument("--layer", default=None, help="time only this conv layer (profiling aid)")
+    ap.add_argument("--matmuls", action="store_true", help="only the w8a16 MatMuls of a decode step (64 tokens)")
     ap.add_argument("--attention", action="store_true", help="only the paged-attention decode measurement")
     ap.add_argument("--attention-batch", type=int, default=64, help="sequences of the --attention measurement (74 = one (sequence, kv head) pair per SM of a 148-SM part)")
     ap.add_argument("--decode", action="store_true", help="only the decoder step (tensor parallel under torchrun)")
@@ -769,6 +824,10 @@ def main():
         run_streams(args)
     elif args.decode:
         run_decode(args)
+    elif args.matmuls:
+        import torch
+        from nncase_b200.kernels import Context
+        print(json.dumps(measure_matmuls(torch, Context(0), peaks(), reps=max(4, args.steps))))
     elif args.attention:
         run_attention(args)
     elif args.layer:
