@@ -22,7 +22,9 @@
 // conversion 53 us, no MMAs 52 us, neither 46 us, and without the epilogue's 2-byte stores 36 us: the tile-per-CTA
 // form re-reads the 112 KB of activations once per channel tile (as many bytes as the weights) and stores its
 // output in 64-byte pieces; a persistent CTA with resident activations and a staged, 16-byte-per-thread store is
-// the next step.
+// the next step. Also measured and not kept: a load ring of six slots with two converted tiles, one CTA per SM
+// (gate/up 13 us, LM head 82 us: nothing hides a CTA's fill and drain any more), and two MMA-issuing threads with an
+// accumulator each, added in the epilogue (no change: the issuing thread is not what paces a K block here).
 #include "tc_dev.cuh"
 #include <cuda_fp16.h>
 
