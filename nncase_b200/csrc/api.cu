@@ -177,6 +177,7 @@ int nncb_context_create(int device, void *stream, nncb_context **out) {
     // kernels that need more than 48 KB of dynamic shared memory: the limit is a per-device attribute
     NNCB_TRY(paged_attention_set_attributes());
     NNCB_TRY(gemv_set_attributes());
+    NNCB_TRY(nncb::gemm_w8a16_tc_set_attributes());
     nncb_context *ctx = new nncb_context();
     ctx->device = device;
     ctx->sm_count = prop.multiProcessorCount;

@@ -326,14 +326,16 @@ int gemm_w8a16_tc(nncb_context *ctx, const void *x, const int8_t *w, const void 
         a.splits = 1, a.kb_per_split = a.k_blocks;
     a.idesc = (1u << 4) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24); // f16 x f16 -> f32, N 64, M 128
     a.limit_us = ctx->opt.wait_limit_us;
-    static bool attr_set[64] = {};
-    if (ctx->device >= 0 && ctx->device < 64 && !attr_set[ctx->device]) {
-        NNCB_CUDA_TRY(cudaFuncSetAttribute(gemm_w8a16_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GT_SMEM));
-        attr_set[ctx->device] = true;
-    }
     dim3 grid(tiles, a.splits, 1);
     gemm_w8a16_tc_kernel<<<grid, GT_THREADS, GT_SMEM, ctx->stream>>>(tw, tx, a);
     return after_launch(ctx, "gemm_w8a16_tc");
+}
+
+// The dynamic shared-memory limit is a per-device attribute of the kernel: set for the current device when a context
+// is created on it.
+int gemm_w8a16_tc_set_attributes() {
+    NNCB_CUDA_TRY(cudaFuncSetAttribute(gemm_w8a16_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GT_SMEM));
+    return 0;
 }
 
 size_t gemm_w8a16_tc_workspace_bytes() { return (size_t)GT_MAX_SLOTS * 64 * 128 * sizeof(float) + 4096 * sizeof(int); }

@@ -66,6 +66,7 @@ bool gemm_w8a16_tc_applies(const nncb_context *ctx, int M, int N, int K);
 int gemm_w8a16_tc(nncb_context *ctx, const void *x, const int8_t *w, const void *scale, const void *bias, const void *residual,
                   void *y, int M, int N, int K, int swiglu);
 size_t gemm_w8a16_tc_workspace_bytes();
+int gemm_w8a16_tc_set_attributes();
 
 // ---- programmatic dependent launch ------------------------------------------------------------------
 // A kernel launched with the programmatic-serialization attribute may become resident while its predecessor in
