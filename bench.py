@@ -256,15 +256,17 @@ def conv_rows(torch, fn, layer_macs, B, reps=5):
         op, plan = st[1], st[2]
         res = fn.buffers[op["res"]] if op.get("res") else None
         y2 = fn.buffers[op["y2"]] if op.get("y2") else None
-        a, b = _events(torch)
         plan(fn.buffers[op["in"]], res, fn.buffers[op["out"]], y2)
         torch.cuda.synchronize(dev)
-        a.record()
-        for _ in range(reps):
-            plan(fn.buffers[op["in"]], res, fn.buffers[op["out"]], y2)
-        b.record()
-        torch.cuda.synchronize(dev)
-        t = a.elapsed_time(b) / reps
+        t = None
+        for _ in range(2):  # two rounds, the quieter one counts (a host hiccup between launches shows up as GPU idle time)
+            a, b = _events(torch)
+            a.record()
+            for _ in range(reps):
+                plan(fn.buffers[op["in"]], res, fn.buffers[op["out"]], y2)
+            b.record()
+            torch.cuda.synchronize(dev)
+            t = a.elapsed_time(b) / reps if t is None else min(t, a.elapsed_time(b) / reps)
         ops = 2.0 * layer_macs[op["name"]] * B
         # algorithmic bytes of the launch: activations in, every tensor written or added, weights once
         n_, oh_, ow_, oc_ = plan.out_shape

@@ -607,6 +607,7 @@ __device__ __forceinline__ void mma_loop(const TcGeom &g, const StageGeom &sg, T
     const int k_blocks = g.taps * g.c_blocks;
     const int total_tiles = g.m_tiles * g.n_tiles;
     uint32_t stage = 0, phase = 0;
+    grid_dependency_wait(); // every bounded wait below starts its clock after the predecessor kernel has completed
     uint32_t acc_phase0 = 0, acc_phase1 = 0, init_phase = 0;
     int it = 0;
     // descriptors of stage 0; a stage further on adds its byte offset >> 4 to the address field
@@ -782,6 +783,7 @@ __device__ __forceinline__ void epilogue_generic(const TcArgs &a, TcShared &sh, 
     const int lane_group = warp & 3; // TMEM lanes 32*lane_group .. +31 are this warp's
     const int grp = ew >> 2;         // the warps of a lane group take 16-column chunks in turn
     const int row = lane_group * 32 + lane;
+    grid_dependency_wait(); // every bounded wait below starts its clock after the predecessor kernel has completed
     uint32_t acc_phase0 = 0, acc_phase1 = 0;
     int it = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, it++) {
@@ -1085,6 +1087,7 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
             load_sub(s_res + b * f.res_pitch, tmap_res, bar_res + b * 8, c);
         }
     }
+    grid_dependency_wait(); // every bounded wait below starts its clock after the predecessor kernel has completed
     uint32_t acc_phase0 = 0, acc_phase1 = 0, res_phase = 0; // res_phase: one parity bit per buffer
     int rb = 0;                                             // residual buffer of the current tile
     int it = 0, cur_nt = -1;
