@@ -190,14 +190,9 @@ int nncb_context_create(int device, void *stream, nncb_context **out) {
         ce = cudaMalloc(&ctx->d_gemv_ws, ws_bytes);
     if (ce == cudaSuccess)
         ce = cudaMemset(ctx->d_gemv_ws, 0, ws_bytes);
-    if (ce == cudaSuccess)
-        ce = cudaMalloc(&ctx->d_gemm_ws, nncb::gemm_w8a16_tc_workspace_bytes());
-    if (ce == cudaSuccess)
-        ce = cudaMemset(ctx->d_gemm_ws, 0, nncb::gemm_w8a16_tc_workspace_bytes());
     if (ce != cudaSuccess) {
         cudaFree(ctx->d_status);
         cudaFree(ctx->d_gemv_ws);
-        cudaFree(ctx->d_gemm_ws);
         delete ctx;
         cudaGetLastError();
         return fail(ce == cudaErrorMemoryAllocation ? -ENOMEM : -EIO, "nncb_context_create: %s", cudaGetErrorString(ce));
@@ -256,7 +251,6 @@ int nncb_context_destroy(nncb_context *ctx) {
     cudaStreamSynchronize(ctx->stream);
     cudaFree(ctx->d_status);
     cudaFree(ctx->d_gemv_ws);
-    cudaFree(ctx->d_gemm_ws);
     delete ctx;
     return 0;
 }

@@ -13,18 +13,28 @@
 //   * eight warps turn the weight bytes into the f16 A operand [128][64] in 128-byte-swizzled shared memory
 //     (exact: (b ^ 0x80) | 0x6400 is the half 1152 + b), one such tile per ring slot;
 //   * one thread issues the four MMAs of the block and commits once, which frees the slot.
-// After the last block the eight warps read the accumulator (lane = channel, 32 token columns each) and finish.
-// Few output channels (qkv, o, down projections: 7 to 9 channel tiles) leave most SMs idle, so K is split over
-// CTAs; their f32 partials meet in a per-context workspace and the CTA that arrives last at a tile adds them in
-// split order (deterministic) and finishes. Every wait is bounded; no multicast.
-// Measured at 64 tokens against the mma.sync form: down projection (896 x 4864) 19.2 -> 14.5 us, LM head
-// (151936 x 896) 73 -> 56 us, gate/up with SwiGLU (9728 x 896) 14.3 -> 15 us. What-if builds of the LM head: no
-// conversion 53 us, no MMAs 52 us, neither 46 us, and without the epilogue's 2-byte stores 36 us: the tile-per-CTA
-// form re-reads the 112 KB of activations once per channel tile (as many bytes as the weights) and stores its
-// output in 64-byte pieces; a persistent CTA with resident activations and a staged, 16-byte-per-thread store is
-// the next step. Also measured and not kept: a load ring of six slots with two converted tiles, one CTA per SM
-// (gate/up 13 us, LM head 82 us: nothing hides a CTA's fill and drain any more), and two MMA-issuing threads with an
-// accumulator each, added in the epilogue (no change: the issuing thread is not what paces a K block here).
+// A ring stage holds one or two such K blocks; the two groups of four conversion warps take the stages in turn.
+// After the last stage the eight warps read the accumulator (lane = channel, 32 token columns each) and finish.
+// Two shapes of launch:
+//   * many channel tiles (an LM head): two CTAs per SM, three one-block stages each, the whole K in one CTA, the
+//     result finished from registers;
+//   * few channel tiles (the projections of a layer: 7 to 76): K is split over the 2, 4 or 8 CTAs of a thread-block
+//     cluster. Every CTA leaves its f32 partial [64 tokens][128 channels] in its own shared memory (the ring is idle
+//     by then); after a cluster barrier CTA r finishes token rows 64 r / S .. of the tile, adding the S partials in
+//     rank order (deterministic) through distributed shared memory; a second barrier keeps every partial alive
+//     until its readers are done. With at most 74 tiles one CTA per SM runs five two-block stages (all the loads
+//     of a split in flight at once), otherwise the two-CTA form.
+// The load thread sends the first ring-full of loads before the block's first barrier. Every wait is bounded (the
+// cluster barriers wait for CTAs whose own waits are bounded); no multicast.
+// Measured at 64 tokens, back to back with L2-resident weights (CUDA-core form -> this kernel): qkv projection
+// (1152 x 896) 6.9 -> 5.7 us, o (896 x 896) 6.9 -> 5.7, down (896 x 4864) 19.2 -> 9.0, gate/up with SwiGLU
+// (9728 x 896) 14.3 -> 10.1, LM head (151936 x 896) 73 -> 55.6 us. An earlier form met the K splits in a global
+// workspace, the last CTA of a tile adding the partials: that CTA's serial finish took 3 us (6 us with SwiGLU) of a
+// 15 us launch, which is what the cluster form removes. What-if builds of the LM head: no conversion 53 us, no
+// MMAs 52 us, neither 46 us, without the epilogue's stores 36 us. Also measured and not kept: a persistent CTA per
+// SM with the activations resident and a staged, 16-byte-per-thread store (LM head 58 us, gate/up 15 us: no
+// change), a load ring of six slots with one CTA per SM for the LM head (82 us: nothing hides a CTA's fill and
+// drain), and two MMA-issuing threads with an accumulator each (no change).
 #include "tc_dev.cuh"
 #include <cuda_fp16.h>
 
@@ -32,20 +42,19 @@ namespace nncb {
 
 namespace {
 
-constexpr int GT_STAGES = 3;                   // ring slots: i8 weights 8 KB + f16 activations 8 KB (TMA) and the converted
-                                               // f16 weight tile 16 KB of the same K block; two CTAs fit an SM
 constexpr int GT_CONV_WARPS = 8;               // conversion warps = epilogue warps (two per TMEM lane quarter: 32 token columns each)
 constexpr int GT_THREADS = 32 * (2 + GT_CONV_WARPS);
+// One K block of 64: i8 weights [128][64] 8 KB + f16 activations [64][64] 8 KB (TMA) and the converted f16 weight tile 16 KB.
 constexpr uint32_t GT_W8_BYTES = 128 * 64, GT_X_BYTES = 64 * 128, GT_A16_BYTES = 128 * 128;
-constexpr uint32_t GT_STAGE_BYTES = GT_W8_BYTES + GT_X_BYTES;
-constexpr size_t GT_SMEM = GT_STAGES * (GT_STAGE_BYTES + GT_A16_BYTES) + 1024;
-constexpr int GT_MAX_SLOTS = 256;              // (channel tile, K split) pairs with a partial in the workspace
+constexpr uint32_t GT_BLOCK_BYTES = GT_W8_BYTES + GT_X_BYTES;
+constexpr int GT_MAX_LS = 8;
+// A ring stage holds KS K blocks; LS load stages and AS stages of converted tiles.
+constexpr size_t gt_smem_bytes(int ks, int ls, int as) { return (size_t)ks * (ls * GT_BLOCK_BYTES + as * GT_A16_BYTES) + 1024; }
 enum { GT_ERR_LOAD = 301, GT_ERR_CONVERT = 302, GT_ERR_MMA = 303, GT_ERR_EPILOGUE = 304 };
 
 struct GtShared {
-    uint64_t full[GT_STAGES], a_full[GT_STAGES], freed[GT_STAGES], acc_full;
+    uint64_t full[GT_MAX_LS], a_full[GT_MAX_LS], freed[GT_MAX_LS], acc_full;
     uint32_t tmem_slot;
-    int last;                // split K: this CTA is the last to arrive at its channel tile
     volatile int abort_flag;
     unsigned wait_limit_us;  // must follow abort_flag (mbar_wait_slow reads it through the flag's address)
 };
@@ -53,10 +62,9 @@ struct GtShared {
 struct GtArgs {
     const __half *scale, *bias, *residual;
     __half *y;
-    float *ws;               // [slots][64][128] f32 partials
-    int *cnt;                // [channel tiles], zero between launches
     int *status;
-    int M, N, K, k_blocks, kb_per_split, splits, swiglu;
+    int M, N, K, k_blocks, kb_per_split, swiglu;
+    int cluster;             // > 1: K is split over the CTAs of a cluster (2, 4 or 8), one channel tile per cluster
     uint32_t idesc;
     unsigned limit_us;
 };
@@ -88,31 +96,62 @@ __device__ __forceinline__ uint32_t i8x2_to_half2(uint32_t w, int pair) {
     const __half2 v = __hsub2(*reinterpret_cast<const __half2 *>(&h), __half2half2(__ushort_as_half(0x6480)));
     return *reinterpret_cast<const uint32_t *>(&v);
 }
-__device__ __forceinline__ void conv_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(32 * GT_CONV_WARPS) : "memory"); }
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+// the address, in the cluster's shared window, of this CTA's shared-memory location `addr` in CTA `rank`
+__device__ __forceinline__ uint32_t peer_smem(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ float2 ld_cluster_f32x2(uint32_t addr) {
+    float2 v;
+    asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr) : "memory");
+    return v;
+}
 
-__global__ void __launch_bounds__(GT_THREADS, 2)
+template <int KS, int LS, int AS, int CTAS>
+__global__ void __launch_bounds__(GT_THREADS, CTAS)
 gemm_w8a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const GtArgs a) {
     using namespace dev;
+    static_assert(LS <= GT_MAX_LS && AS <= LS, "ring sizes");
+    constexpr uint32_t STAGE_BYTES = KS * GT_BLOCK_BYTES, A16_STAGE_BYTES = KS * GT_A16_BYTES;
     extern __shared__ uint8_t gt_smem[];
     __shared__ __align__(8) GtShared sh;
     const uint32_t base = (smem_u32(gt_smem) + 1023u) & ~1023u;
-    const uint32_t a16_base = base + GT_STAGES * GT_STAGE_BYTES;
+    const uint32_t a16_base = base + LS * STAGE_BYTES;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile = blockIdx.x, split = blockIdx.y;
+    const int tile = blockIdx.x, split = blockIdx.y; // with a cluster, blockIdx.y is the rank in it (cluster 1 x S x 1, grid y = S)
     const int kb0 = split * a.kb_per_split;
-    const int kb1 = min(a.k_blocks, kb0 + a.kb_per_split);
-    const int n_blocks = kb1 - kb0; // >= 1 by construction of the grid
+    const int n_blocks = max(min(a.k_blocks, kb0 + a.kb_per_split) - kb0, 0); // 0: a cluster rank past the last K block adds zeros
+    const int n_stages = (n_blocks + KS - 1) / KS;
+    // the load thread: K blocks of stage st into ring slot s
+    auto load_stage = [&](int st, int s) {
+        const int nsub = min(KS, n_blocks - st * KS);
+        const uint32_t full = smem_u32(&sh.full[s]), dst = base + s * STAGE_BYTES;
+        mbar_expect_tx(full, nsub * GT_BLOCK_BYTES);
+        for (int u = 0; u < nsub; u++) {
+            const int kx = (kb0 + st * KS + u) * 64;
+            tma_load_2d(dst + u * GT_BLOCK_BYTES, &tmap_w, full, kx, tile * 128);           // weights [128 channels][64 k] i8
+            tma_load_2d(dst + u * GT_BLOCK_BYTES + GT_W8_BYTES, &tmap_x, full, kx, 0);      // activations [64 tokens][64 k] f16
+        }
+    };
     if (threadIdx.x == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_x) : "memory");
         sh.abort_flag = 0;
         sh.wait_limit_us = a.limit_us;
-        sh.last = 0;
-        for (int s = 0; s < GT_STAGES; s++) {
+        for (int s = 0; s < LS; s++) {
             mbar_init(smem_u32(&sh.full[s]), 1);
-            mbar_init(smem_u32(&sh.a_full[s]), GT_CONV_WARPS);
-            mbar_init(smem_u32(&sh.freed[s]), 1); // one commit frees the slot for the load warp and the conversion warps
+            mbar_init(smem_u32(&sh.freed[s]), 1); // one commit frees a stage's load slot and its converted tiles
         }
+        for (int s = 0; s < AS; s++)
+            mbar_init(smem_u32(&sh.a_full[s]), GT_CONV_WARPS / 2);
         mbar_init(smem_u32(&sh.acc_full), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // the first ring-full of loads leaves before the block meets: nothing else has touched these slots
+        for (int st = 0; st < LS && st < n_stages; st++)
+            load_stage(st, st);
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh.tmem_slot)), "r"(64u)
@@ -124,140 +163,243 @@ gemm_w8a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     fence_after_sync();
     const uint32_t tmem = sh.tmem_slot;
 
+    // what the finishing threads need from global memory is fetched before the K loop's waits
+    const int ct = threadIdx.x - 64; // 0 .. 255 among the conversion / epilogue threads
+    bool ok = true;
     if (warp == 0) {
         if (lane == 0) {
-            for (int i = 0; i < n_blocks; i++) {
-                const int s = i % GT_STAGES;
-                if (!mbar_wait(smem_u32(&sh.freed[s]), ((i / GT_STAGES) & 1) ^ 1, &sh.abort_flag, a.status, GT_ERR_LOAD))
+            for (int st = LS; st < n_stages; st++) {
+                const int s = st % LS;
+                if (!mbar_wait(smem_u32(&sh.freed[s]), ((st / LS) & 1) ^ 1, &sh.abort_flag, a.status, GT_ERR_LOAD))
                     break;
-                const uint32_t full = smem_u32(&sh.full[s]), dst = base + s * GT_STAGE_BYTES;
-                mbar_expect_tx(full, GT_STAGE_BYTES);
-                tma_load_2d(dst, &tmap_w, full, (kb0 + i) * 64, tile * 128);           // weights [128 channels][64 k] i8
-                tma_load_2d(dst + GT_W8_BYTES, &tmap_x, full, (kb0 + i) * 64, 0);      // activations [64 tokens][64 k] f16
+                load_stage(st, s);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            bool ok = true;
-            for (int i = 0; i < n_blocks && ok; i++) {
-                const int s = i % GT_STAGES;
-                ok = mbar_wait(smem_u32(&sh.a_full[s]), (i / GT_STAGES) & 1, &sh.abort_flag, a.status, GT_ERR_MMA) &&
-                     mbar_wait(smem_u32(&sh.full[s]), (i / GT_STAGES) & 1, &sh.abort_flag, a.status, GT_ERR_MMA);
+            for (int st = 0; st < n_stages && ok; st++) {
+                const int s = st % LS, sa = st % AS;
+                ok = mbar_wait(smem_u32(&sh.a_full[sa]), (st / AS) & 1, &sh.abort_flag, a.status, GT_ERR_MMA) &&
+                     mbar_wait(smem_u32(&sh.full[s]), (st / LS) & 1, &sh.abort_flag, a.status, GT_ERR_MMA);
                 if (!ok)
                     break;
                 fence_after_sync();
-                const Desc da = make_desc(smem_desc(a16_base + s * GT_A16_BYTES, 128));
-                const Desc db = make_desc(smem_desc(base + s * GT_STAGE_BYTES + GT_W8_BYTES, 128));
-                mma_f16(tmem, da, db, a.idesc, i != 0);
-                mma_f16(tmem, da + 2, db + 2, a.idesc, 1);
-                mma_f16(tmem, da + 4, db + 4, a.idesc, 1);
-                mma_f16(tmem, da + 6, db + 6, a.idesc, 1);
-                mma_commit(smem_u32(&sh.freed[s])); // the activations, the weight bytes and the converted tile of this slot
+                const int nsub = min(KS, n_blocks - st * KS);
+                for (int u = 0; u < nsub; u++) {
+                    const Desc da = make_desc(smem_desc(a16_base + sa * A16_STAGE_BYTES + u * GT_A16_BYTES, 128));
+                    const Desc db = make_desc(smem_desc(base + s * STAGE_BYTES + u * GT_BLOCK_BYTES + GT_W8_BYTES, 128));
+                    mma_f16(tmem, da, db, a.idesc, (st | u) != 0);
+                    mma_f16(tmem, da + 2, db + 2, a.idesc, 1);
+                    mma_f16(tmem, da + 4, db + 4, a.idesc, 1);
+                    mma_f16(tmem, da + 6, db + 6, a.idesc, 1);
+                }
+                mma_commit(smem_u32(&sh.freed[s])); // the activations, the weight bytes and the converted tiles of this stage
             }
-            if (ok)
+            if (ok && n_stages > 0)
                 mma_commit(smem_u32(&sh.acc_full));
         }
     } else {
-        // ---- conversion, then the epilogue ----
-        const int ct = threadIdx.x - 64; // 0 .. 255
-        bool ok = true;
-        for (int i = 0; i < n_blocks && ok; i++) {
-            const int s = i % GT_STAGES;
-            ok = mbar_wait(smem_u32(&sh.full[s]), (i / GT_STAGES) & 1, &sh.abort_flag, a.status, GT_ERR_CONVERT) &&
-                 mbar_wait(smem_u32(&sh.freed[s]), ((i / GT_STAGES) & 1) ^ 1, &sh.abort_flag, a.status, GT_ERR_CONVERT);
+        // ---- conversion: the two groups of four warps take the stages in turn, so that one group's waits and
+        // fences overlap the other's loads and stores ----
+        const int cgrp = (warp - 2) >> 2, cgt = ct & 127;
+        for (int st = cgrp; st < n_stages && ok; st += 2) {
+            const int s = st % LS, sa = st % AS;
+            ok = mbar_wait(smem_u32(&sh.full[s]), (st / LS) & 1, &sh.abort_flag, a.status, GT_ERR_CONVERT);
+            // the slot of the converted tiles is free once the MMAs of stage st - AS have completed: that stage's
+            // commit on its load slot. That barrier is at most one phase ahead: the MMAs go in stage order, so no
+            // later stage of the slot completes before stage st has been converted.
+            if (ok && st >= AS)
+                ok = mbar_wait(smem_u32(&sh.freed[(st - AS) % LS]), ((st - AS) / LS) & 1, &sh.abort_flag, a.status, GT_ERR_CONVERT);
             if (!ok)
                 break;
-            const uint32_t src = base + s * GT_STAGE_BYTES, dst = a16_base + s * GT_A16_BYTES;
+            const int nsub = min(KS, n_blocks - st * KS);
+            for (int u = 0; u < nsub; u++) {
+                const uint32_t src = base + s * STAGE_BYTES + u * GT_BLOCK_BYTES, dst = a16_base + sa * A16_STAGE_BYTES + u * GT_A16_BYTES;
 #pragma unroll
-            for (int q0 = 0; q0 < 512 / (32 * GT_CONV_WARPS); q0++) {
-                const int q = ct + q0 * 32 * GT_CONV_WARPS; // 16-byte chunk of the i8 tile: row q / 4, bytes 16 (q % 4) ..
-                const int row = q >> 2, c16 = q & 3;
-                uint32_t w0, w1, w2, w3;
-                asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3) : "r"(src + q * 16));
-                const uint32_t d0 = dst + row * 128 + (((2 * c16) ^ (row & 7)) << 4);
-                const uint32_t d1 = dst + row * 128 + (((2 * c16 + 1) ^ (row & 7)) << 4);
-                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(d0), "r"(i8x2_to_half2(w0, 0)), "r"(i8x2_to_half2(w0, 1)),
-                             "r"(i8x2_to_half2(w1, 0)), "r"(i8x2_to_half2(w1, 1))
-                             : "memory");
-                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(d1), "r"(i8x2_to_half2(w2, 0)), "r"(i8x2_to_half2(w2, 1)),
-                             "r"(i8x2_to_half2(w3, 0)), "r"(i8x2_to_half2(w3, 1))
-                             : "memory");
+                for (int q0 = 0; q0 < 4; q0++) {
+                    const int q = cgt + q0 * 128; // 16-byte chunk of the i8 tile: row q / 4, bytes 16 (q % 4) ..
+                    const int row = q >> 2, c16 = q & 3;
+                    uint32_t w0, w1, w2, w3;
+                    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3) : "r"(src + q * 16));
+                    const uint32_t d0 = dst + row * 128 + (((2 * c16) ^ (row & 7)) << 4);
+                    const uint32_t d1 = dst + row * 128 + (((2 * c16 + 1) ^ (row & 7)) << 4);
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(d0), "r"(i8x2_to_half2(w0, 0)), "r"(i8x2_to_half2(w0, 1)),
+                                 "r"(i8x2_to_half2(w1, 0)), "r"(i8x2_to_half2(w1, 1))
+                                 : "memory");
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(d1), "r"(i8x2_to_half2(w2, 0)), "r"(i8x2_to_half2(w2, 1)),
+                                 "r"(i8x2_to_half2(w3, 0)), "r"(i8x2_to_half2(w3, 1))
+                                 : "memory");
+                }
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // the MMA reads this tile through the async proxy
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // the MMA reads these tiles through the async proxy
             __syncwarp();
             if (lane == 0)
-                mbar_arrive(smem_u32(&sh.a_full[s]));
+                mbar_arrive(smem_u32(&sh.a_full[sa]));
         }
-        if (ok)
-            ok = mbar_wait(smem_u32(&sh.acc_full), 0, &sh.abort_flag, a.status, GT_ERR_EPILOGUE);
-        if (ok) {
-            fence_after_sync();
-            const int quarter = warp & 3;                 // TMEM lanes 32 quarter .. + 31 are this warp's
-            const int t0 = ((warp - 2) >> 2) * 32;        // ... and token columns t0 .. t0 + 31
-            const int ch = quarter * 32 + lane;           // channel within the tile
-            const int n = tile * 128 + ch;
+        // ---- the accumulator: lane = channel of the tile, 32 token columns per warp ----
+        const int quarter = warp & 3;          // TMEM lanes 32 quarter .. + 31 are this warp's
+        const int t0 = ((warp - 2) >> 2) * 32; // ... and token columns t0 .. t0 + 31
+        const int ch = quarter * 32 + lane;
+        const int n = tile * 128 + ch;
+        if (a.cluster == 1) {
+            // the whole K in this CTA: finish from registers
+            const bool valid = n < a.N;
+            const float sc = valid ? __half2float(a.scale[n]) : 0.f, bi = (valid && a.bias) ? __half2float(a.bias[n]) : 0.f;
+            if (ok)
+                ok = mbar_wait(smem_u32(&sh.acc_full), 0, &sh.abort_flag, a.status, GT_ERR_EPILOGUE);
+            if (ok) {
+                fence_after_sync();
+                float v[32];
+                tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + t0, v);
+                if (!a.swiglu && valid) {
+#pragma unroll
+                    for (int t = 0; t < 32; t++) {
+                        if (t0 + t >= a.M)
+                            break;
+                        float r = v[t] * sc + bi;
+                        if (a.residual)
+                            r += __half2float(a.residual[(size_t)(t0 + t) * a.N + n]);
+                        a.y[(size_t)(t0 + t) * a.N + n] = __float2half_rn(r);
+                    }
+                }
+                if (a.swiglu) {
+                    // lanes 0-7 / 16-23 hold gate rows, lanes 8-15 / 24-31 the matching up rows (blocks of 16 rows)
+                    const int out_col = (n >> 4) * 8 + (lane & 7);
+#pragma unroll
+                    for (int t = 0; t < 32; t++) {
+                        if (t0 + t >= a.M)
+                            break;
+                        const float mineh = __half2float(__float2half_rn(v[t] * sc + bi));
+                        const float up = __shfl_down_sync(0xffffffffu, mineh, 8);
+                        if (valid && (lane & 8) == 0 && n + 8 < a.N)
+                            a.y[(size_t)(t0 + t) * (a.N / 2) + out_col] = __float2half_rn(mineh / (1.0f + expf(-mineh)) * up);
+                    }
+                }
+            }
+        } else {
+            // K split over the cluster: this CTA's f32 partial [64 tokens][128 channels] goes to its own shared
+            // memory (the ring is idle once the accumulator is complete) and is added up after the cluster barrier
+            if (ok && n_stages > 0)
+                ok = mbar_wait(smem_u32(&sh.acc_full), 0, &sh.abort_flag, a.status, GT_ERR_EPILOGUE);
             float v[32];
-            tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + t0, v);
-            bool finish = true;
-            if (a.splits > 1) {
-                // partial sums meet in the workspace; the CTA that arrives last at this tile adds them in split order
-                float *mine = a.ws + ((size_t)(tile * a.splits + split) * 64 + t0) * 128;
+            if (ok && n_stages > 0) {
+                fence_after_sync();
+                tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + t0, v);
+            } else {
 #pragma unroll
                 for (int t = 0; t < 32; t++)
-                    mine[t * 128 + ch] = v[t];
-                __threadfence();
-                conv_bar_sync();
-                if (ct == 0)
-                    sh.last = atomicAdd(&a.cnt[tile], 1) == a.splits - 1;
-                conv_bar_sync();
-                finish = sh.last != 0;
-                if (finish) {
-                    __threadfence();
-#pragma unroll
-                    for (int t = 0; t < 32; t++)
-                        v[t] = 0.f;
-                    for (int sp = 0; sp < a.splits; sp++) {
-                        const float *p = a.ws + ((size_t)(tile * a.splits + sp) * 64 + t0) * 128 + ch;
-                        float u[32];
-#pragma unroll
-                        for (int t = 0; t < 32; t++)
-                            u[t] = __ldcg(p + t * 128);
-#pragma unroll
-                        for (int t = 0; t < 32; t++)
-                            v[t] += u[t];
-                    }
-                    if (ct == 0)
-                        a.cnt[tile] = 0;
-                }
+                    v[t] = 0.f;
             }
-            if (finish && !a.swiglu && n < a.N) {
-                const float sc = __half2float(a.scale[n]), bi = a.bias ? __half2float(a.bias[n]) : 0.f;
 #pragma unroll
-                for (int t = 0; t < 32; t++) {
-                    if (t0 + t >= a.M)
-                        break;
-                    float r = v[t] * sc + bi;
-                    if (a.residual)
-                        r += __half2float(a.residual[(size_t)(t0 + t) * a.N + n]);
-                    a.y[(size_t)(t0 + t) * a.N + n] = __float2half_rn(r);
-                }
-            }
-            if (finish && a.swiglu) {
-                // lanes 0-7 / 16-23 hold gate rows, lanes 8-15 / 24-31 the matching up rows (blocks of 16 rows)
-                const bool valid = n < a.N;
-                const float sc = valid ? __half2float(a.scale[n]) : 0.f, bi = (valid && a.bias) ? __half2float(a.bias[n]) : 0.f;
-                const int out_col = (n >> 4) * 8 + (lane & 7);
-#pragma unroll
-                for (int t = 0; t < 32; t++) {
-                    if (t0 + t >= a.M)
-                        break;
-                    const float mineh = __half2float(__float2half_rn(v[t] * sc + bi));
-                    const float up = __shfl_down_sync(0xffffffffu, mineh, 8);
-                    if (valid && (lane & 8) == 0 && n + 8 < a.N)
-                        a.y[(size_t)(t0 + t) * (a.N / 2) + out_col] = __float2half_rn(mineh / (1.0f + expf(-mineh)) * up);
-                }
-            }
+            for (int t = 0; t < 32; t++)
+                asm volatile("st.shared.f32 [%0], %1;" ::"r"(base + (uint32_t)((t0 + t) * 128 + ch) * 4u), "f"(v[t]) : "memory");
         }
+    }
+    if (a.cluster > 1) {
+        __syncwarp(); // the role threads rejoin their warps before the warp-aligned cluster barrier
+        cluster_arrive();
+        // Token rows 64 / S * rank .. of the tile are this CTA's to finish: the S partials are added in rank order.
+        // A thread fetches eight (row, rank) pairs at a time from the peers' shared memory, then finishes those rows.
+        const int S = a.cluster, lg = 31 - __clz(S), rows = 64 >> lg, row0 = split * rows;
+        const int RB = 8 >> lg; // rows per batch of eight fetches
+        if (warp >= 2 && !a.swiglu) {
+            // a thread owns two neighbouring channels, 64 threads a token row
+            const int c2 = ct & 63, n = tile * 128 + 2 * c2;
+            const bool v0 = n < a.N, v1 = n + 1 < a.N, pair = v1 && (a.N & 1) == 0;
+            const float sc0 = v0 ? __half2float(a.scale[n]) : 0.f, sc1 = v1 ? __half2float(a.scale[n + 1]) : 0.f;
+            const float bi0 = (v0 && a.bias) ? __half2float(a.bias[n]) : 0.f, bi1 = (v1 && a.bias) ? __half2float(a.bias[n + 1]) : 0.f;
+            const uint32_t own = base + (uint32_t)(2 * c2) * 4u;
+            cluster_wait(); // every partial of the cluster is written
+            for (int k0 = 0; k0 < (16 >> lg); k0 += RB) { // this thread's rows: row0 + (ct >> 6) + 4 k
+                float2 res[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const int t = row0 + (ct >> 6) + 4 * (k0 + j);
+                    res[j] = make_float2(0.f, 0.f);
+                    if (a.residual && j < RB && t < a.M) {
+                        const size_t o = (size_t)t * a.N + n;
+                        if (pair)
+                            res[j] = __half22float2(*reinterpret_cast<const __half2 *>(a.residual + o));
+                        else {
+                            res[j].x = v0 ? __half2float(a.residual[o]) : 0.f;
+                            res[j].y = v1 ? __half2float(a.residual[o + 1]) : 0.f;
+                        }
+                    }
+                }
+                float2 u[8];
+#pragma unroll
+                for (int q = 0; q < 8; q++) {
+                    const int t = row0 + (ct >> 6) + 4 * (k0 + (q >> lg));
+                    u[q] = ld_cluster_f32x2(peer_smem(own, (uint32_t)(q & (S - 1))) + (uint32_t)t * 512u);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const int t = row0 + (ct >> 6) + 4 * (k0 + j);
+                    if (j >= RB || t >= a.M)
+                        continue;
+                    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+                    for (int q = 0; q < 8; q++)
+                        if ((q >> lg) == j)
+                            s0 += u[q].x, s1 += u[q].y;
+                    float r0 = s0 * sc0 + bi0, r1 = s1 * sc1 + bi1;
+                    if (a.residual)
+                        r0 += res[j].x, r1 += res[j].y;
+                    const size_t o = (size_t)t * a.N + n;
+                    if (pair)
+                        *reinterpret_cast<__half2 *>(a.y + o) = __halves2half2(__float2half_rn(r0), __float2half_rn(r1));
+                    else {
+                        if (v0)
+                            a.y[o] = __float2half_rn(r0);
+                        if (v1)
+                            a.y[o + 1] = __float2half_rn(r1);
+                    }
+                }
+            }
+        } else if (warp >= 2) {
+            // a thread owns outputs 2 o2, 2 o2 + 1 of the tile's 64 (gate rows at channel 16 b + j, their up rows 8
+            // further), 32 threads a token row; its rows are row0 + (ct >> 5) + 8 j
+            const int o2 = ct & 31, cg = ((2 * o2) >> 3) * 16 + ((2 * o2) & 7), n = tile * 128 + cg;
+            const bool valid = n + 9 < a.N;
+            float sc[4], bi[4];
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const int nn = n + (q & 1) + (q >> 1) * 8;
+                sc[q] = valid ? __half2float(a.scale[nn]) : 0.f;
+                bi[q] = (valid && a.bias) ? __half2float(a.bias[nn]) : 0.f;
+            }
+            const uint32_t own = base + (uint32_t)cg * 4u;
+            cluster_wait();
+            float2 ug[8], uu[8];
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+                const int t = row0 + (ct >> 5) + 8 * (q >> lg);
+                const uint32_t src = peer_smem(own, (uint32_t)(q & (S - 1))) + (uint32_t)t * 512u;
+                ug[q] = ld_cluster_f32x2(src), uu[q] = ld_cluster_f32x2(src + 32u);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int t = row0 + (ct >> 5) + 8 * j;
+                if (j >= RB || t >= a.M)
+                    continue;
+                float g0 = 0.f, g1 = 0.f, u0 = 0.f, u1 = 0.f;
+#pragma unroll
+                for (int q = 0; q < 8; q++)
+                    if ((q >> lg) == j)
+                        g0 += ug[q].x, g1 += ug[q].y, u0 += uu[q].x, u1 += uu[q].y;
+                const float gh0 = __half2float(__float2half_rn(g0 * sc[0] + bi[0])), gh1 = __half2float(__float2half_rn(g1 * sc[1] + bi[1]));
+                const float uh0 = __half2float(__float2half_rn(u0 * sc[2] + bi[2])), uh1 = __half2float(__float2half_rn(u1 * sc[3] + bi[3]));
+                if (valid)
+                    *reinterpret_cast<__half2 *>(a.y + (size_t)t * (a.N / 2) + tile * 64 + 2 * o2) =
+                        __halves2half2(__float2half_rn(gh0 / (1.0f + expf(-gh0)) * uh0), __float2half_rn(gh1 / (1.0f + expf(-gh1)) * uh1));
+            }
+        } else {
+            cluster_wait();
+        }
+        // no CTA leaves while a peer may still read its partial
+        __syncwarp();
+        cluster_arrive();
+        cluster_wait();
     }
     fence_before_sync();
     __syncthreads();
@@ -268,13 +410,18 @@ gemm_w8a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
 
 } // namespace
 
-// Matrices of less than 2 M weights (the qkv and o projections of a 0.5 B model) stay on the mma.sync form: a
-// launch's fixed costs (set-up, first loads, the partials' round trip) outweigh what the tensor pipe saves there
-// (measured at 64 tokens: 6.9 us against 10.8 us). Option matmul.tensor_core = 2 takes every shape that fits.
+#define GT_WIDE 1, 3, 3, 2
+#define GT_DEEP 2, 5, 2, 1
+constexpr size_t GT_SMEM_WIDE = gt_smem_bytes(1, 3, 3), GT_SMEM_DEEP = gt_smem_bytes(2, 5, 2);
+
+// Where this form is the faster one (measured on the projections of a 0.5 B model and its LM head): more than 32
+// tokens -- below that the CUDA-core form streams the weights in 3 to 6 us a projection, less than this kernel's
+// set-up, first loads and cluster barriers cost (5 us) -- and at least half a million weights. Option
+// matmul.tensor_core = 2 takes every shape that fits.
 bool gemm_w8a16_tc_applies(const nncb_context *ctx, int M, int N, int K) {
-    if (ctx->d_gemm_ws == nullptr || M < 1 || M > 64 || K % 64 != 0 || K < 64 || N < 16)
+    if (M < 1 || M > 64 || K % 64 != 0 || K < 64 || N < 16)
         return false;
-    return ctx->opt.matmul_tensor_core >= 2 || (long long)N * K >= (1ll << 21);
+    return ctx->opt.matmul_tensor_core >= 2 || (M > 32 && (long long)N * K >= (1ll << 19));
 }
 
 // Launches the tensor-core form (the caller has checked gemm_w8a16_tc_applies and the pointer alignment).
@@ -304,40 +451,45 @@ int gemm_w8a16_tc(nncb_context *ctx, const void *x, const int8_t *w, const void 
     }
     GtArgs a;
     a.scale = (const __half *)scale, a.bias = (const __half *)bias, a.residual = (const __half *)residual, a.y = (__half *)y;
-    a.ws = ctx->d_gemm_ws;
-    a.cnt = reinterpret_cast<int *>(ctx->d_gemm_ws + (size_t)GT_MAX_SLOTS * 64 * 128);
     a.status = ctx->d_status;
     a.M = M, a.N = N, a.K = K, a.k_blocks = K / 64, a.swiglu = swiglu;
     const int tiles = (N + 127) / 128;
-    // K split: only where the channel tiles alone leave most SMs idle, and never more partials than the workspace holds
-    int splits = 1;
-    if (tiles < ctx->sm_count) {
-        splits = (2 * ctx->sm_count) / tiles; // two CTAs fit an SM
-        if (splits > 4)
-            splits = 4; // the last CTA of a tile reads every partial: 32 KB each
-        if (splits > a.k_blocks)
-            splits = a.k_blocks;
-        while (splits > 1 && tiles * splits > GT_MAX_SLOTS)
-            splits--;
-    }
-    a.kb_per_split = (a.k_blocks + splits - 1) / splits;
-    a.splits = (a.k_blocks + a.kb_per_split - 1) / a.kb_per_split; // no empty split
-    if (tiles > GT_MAX_SLOTS && a.splits > 1)
-        a.splits = 1, a.kb_per_split = a.k_blocks;
+    // Many channel tiles (an LM head): two CTAs per SM, a short ring each, the whole K in one CTA. Few (the
+    // projections of a layer): one CTA per SM with a long ring of two-block stages, and K split over the CTAs of a
+    // cluster of 2, 4 or 8 as far as the SMs go.
+    const bool deep = 2 * tiles <= ctx->sm_count;
+    int cluster = 1;
+    for (int c = 8; c > 1; c >>= 1)
+        if (tiles * c <= (deep ? 1 : 2) * ctx->sm_count && c <= a.k_blocks) {
+            cluster = c;
+            break;
+        }
+    a.cluster = cluster;
+    a.kb_per_split = (a.k_blocks + cluster - 1) / cluster;
     a.idesc = (1u << 4) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24); // f16 x f16 -> f32, N 64, M 128
     a.limit_us = ctx->opt.wait_limit_us;
-    dim3 grid(tiles, a.splits, 1);
-    gemm_w8a16_tc_kernel<<<grid, GT_THREADS, GT_SMEM, ctx->stream>>>(tw, tx, a);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(tiles, cluster, 1);
+    cfg.blockDim = dim3(GT_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = deep ? GT_SMEM_DEEP : GT_SMEM_WIDE;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1, attr[0].val.clusterDim.y = cluster, attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr, cfg.numAttrs = 1;
+    if (deep)
+        NNCB_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_w8a16_tc_kernel<GT_DEEP>, tw, tx, a));
+    else
+        NNCB_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_w8a16_tc_kernel<GT_WIDE>, tw, tx, a));
     return after_launch(ctx, "gemm_w8a16_tc");
 }
 
 // The dynamic shared-memory limit is a per-device attribute of the kernel: set for the current device when a context
 // is created on it.
 int gemm_w8a16_tc_set_attributes() {
-    NNCB_CUDA_TRY(cudaFuncSetAttribute(gemm_w8a16_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GT_SMEM));
+    NNCB_CUDA_TRY(cudaFuncSetAttribute(gemm_w8a16_tc_kernel<GT_WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GT_SMEM_WIDE));
+    NNCB_CUDA_TRY(cudaFuncSetAttribute(gemm_w8a16_tc_kernel<GT_DEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GT_SMEM_DEEP));
     return 0;
 }
-
-size_t gemm_w8a16_tc_workspace_bytes() { return (size_t)GT_MAX_SLOTS * 64 * 128 * sizeof(float) + 4096 * sizeof(int); }
 
 } // namespace nncb

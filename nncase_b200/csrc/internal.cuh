@@ -34,7 +34,6 @@ struct nncb_context {
     uint64_t launches = 0;
     int sm_count = 148;
     int *d_status = nullptr;  // device word: 0 ok, else code of the first bounded wait that gave up
-    float *d_gemm_ws = nullptr; // split-K meeting place of the tensor-core w8a16 MatMul: partials + one counter per channel tile, counters zero between launches
     float *d_gemv_ws = nullptr; // split-K meeting place of gemv_w8a16: GEMV_SPLIT_SLOTS x 16 x 64 f32 + one counter per slot, counters zero between launches
 };
 
@@ -65,7 +64,6 @@ int after_launch(nncb_context *ctx, const char *what);
 bool gemm_w8a16_tc_applies(const nncb_context *ctx, int M, int N, int K);
 int gemm_w8a16_tc(nncb_context *ctx, const void *x, const int8_t *w, const void *scale, const void *bias, const void *residual,
                   void *y, int M, int N, int K, int swiglu);
-size_t gemm_w8a16_tc_workspace_bytes();
 int gemm_w8a16_tc_set_attributes();
 
 // ---- programmatic dependent launch ------------------------------------------------------------------

@@ -23,7 +23,9 @@ def close(got, want, tol=1e-3):
 @pytest.fixture(params=[0, 2], ids=["mma_sync", "tcgen05"])
 def matmul_form(ctx, request):
     """Both forms of the w8a16 MatMul: CUDA-core-fed mma.sync, and tcgen05 with the accumulator in TMEM (forced for
-    every shape that fits; by default it takes matrices of 2 M weights or more)."""
+    every shape that fits; by default it takes more than 32 tokens on matrices of half a million weights or more). The
+    shapes below cover both launch forms, K split over clusters of 2, 4 and 8 CTAs, a cluster rank without K blocks,
+    ragged token and channel counts."""
     ctx.set_option("matmul.tensor_core", request.param)
     yield request.param
     ctx.set_option("matmul.tensor_core", 1)
@@ -65,7 +67,7 @@ def test_gemv_with_swiglu_epilogue(ctx, matmul_form, m, inter, k):
     L.check(ctx._lib.nncb_swiglu_f16(ctx._h, gu.data_ptr(), act.data_ptr(), m, inter))
     assert torch.equal(y, act)
     close(y.cpu().numpy(), OD.swiglu(OD.gemv_w8a16(x, wq, s), inter))
-    # a second call finds the split-K counters cleared by the first (k = 4864 takes the split path)
+    # a second call gives the same bits (k = 4864 is split over a cluster)
     y2 = torch.empty_like(y)
     L.check(ctx._lib.nncb_gemv_w8a16_swiglu(ctx._h, xd.data_ptr(), wid.data_ptr(), sid.data_ptr(), None, y2.data_ptr(), m,
                                             2 * inter, k))
