@@ -358,6 +358,7 @@ __global__ void __launch_bounds__(128)
 add_rmsnorm_row_kernel(__half *__restrict__ x, const __half *__restrict__ delta, const __half *__restrict__ w,
                        __half *__restrict__ h, int cols, float eps) {
     __shared__ float part[4];
+    grid_dependency_release(); // a MatMul that follows sets itself up and fetches its weights meanwhile
     const size_t row = blockIdx.x;
     uint2 *xr = reinterpret_cast<uint2 *>(x + row * cols);
     const uint2 *dr = reinterpret_cast<const uint2 *>(delta + row * cols);
@@ -417,6 +418,7 @@ __global__ void __launch_bounds__(128)
 add_rmsnorm_kernel(__half *__restrict__ x, const __half *__restrict__ delta, const __half *__restrict__ w,
                    __half *__restrict__ h, int cols, float eps) {
     __shared__ float part[4];
+    grid_dependency_release();
     const size_t row = blockIdx.x;
     __half *xr = x + row * cols;
     float ss = 0.f;

@@ -125,17 +125,21 @@ gemm_w8a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     const int kb0 = split * a.kb_per_split;
     const int n_blocks = max(min(a.k_blocks, kb0 + a.kb_per_split) - kb0, 0); // 0: a cluster rank past the last K block adds zeros
     const int n_stages = (n_blocks + KS - 1) / KS;
-    // the load thread: K blocks of stage st into ring slot s
-    auto load_stage = [&](int st, int s) {
+    // the load thread: K blocks of stage st into ring slot s (part 1: the weights, 2: the activations, 3: both)
+    auto load_stage = [&](int st, int s, int part) {
         const int nsub = min(KS, n_blocks - st * KS);
         const uint32_t full = smem_u32(&sh.full[s]), dst = base + s * STAGE_BYTES;
-        mbar_expect_tx(full, nsub * GT_BLOCK_BYTES);
+        if (part & 1)
+            mbar_expect_tx(full, nsub * GT_BLOCK_BYTES);
         for (int u = 0; u < nsub; u++) {
             const int kx = (kb0 + st * KS + u) * 64;
-            tma_load_2d(dst + u * GT_BLOCK_BYTES, &tmap_w, full, kx, tile * 128);           // weights [128 channels][64 k] i8
-            tma_load_2d(dst + u * GT_BLOCK_BYTES + GT_W8_BYTES, &tmap_x, full, kx, 0);      // activations [64 tokens][64 k] f16
+            if (part & 1)
+                tma_load_2d(dst + u * GT_BLOCK_BYTES, &tmap_w, full, kx, tile * 128);           // weights [128 channels][64 k] i8
+            if (part & 2)
+                tma_load_2d(dst + u * GT_BLOCK_BYTES + GT_W8_BYTES, &tmap_x, full, kx, 0);      // activations [64 tokens][64 k] f16
         }
     };
+    grid_dependency_release(); // the next kernel of the stream may set itself up while this one runs
     if (threadIdx.x == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_w) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_x) : "memory");
@@ -149,9 +153,10 @@ gemm_w8a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
             mbar_init(smem_u32(&sh.a_full[s]), GT_CONV_WARPS / 2);
         mbar_init(smem_u32(&sh.acc_full), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        // the first ring-full of loads leaves before the block meets: nothing else has touched these slots
+        // the weights of the first ring-full leave at once: nothing else has touched these slots, and the weights
+        // are nobody's output
         for (int st = 0; st < LS && st < n_stages; st++)
-            load_stage(st, st);
+            load_stage(st, st, 1);
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh.tmem_slot)), "r"(64u)
@@ -162,8 +167,14 @@ gemm_w8a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     __syncthreads();
     fence_after_sync();
     const uint32_t tmem = sh.tmem_slot;
+    // Launched as a programmatic dependent, the kernel has come this far beside the kernel before it in the stream;
+    // its activations and residual are that kernel's (or an earlier one's) output, and every bounded wait below
+    // starts its clock here.
+    grid_dependency_wait();
+    if (threadIdx.x == 0)
+        for (int st = 0; st < LS && st < n_stages; st++)
+            load_stage(st, st, 2);
 
-    // what the finishing threads need from global memory is fetched before the K loop's waits
     const int ct = threadIdx.x - 64; // 0 .. 255 among the conversion / epilogue threads
     bool ok = true;
     if (warp == 0) {
@@ -172,7 +183,7 @@ gemm_w8a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
                 const int s = st % LS;
                 if (!mbar_wait(smem_u32(&sh.freed[s]), ((st / LS) & 1) ^ 1, &sh.abort_flag, a.status, GT_ERR_LOAD))
                     break;
-                load_stage(st, s);
+                load_stage(st, s, 3);
             }
         }
     } else if (warp == 1) {
@@ -473,10 +484,12 @@ int gemm_w8a16_tc(nncb_context *ctx, const void *x, const int8_t *w, const void 
     cfg.blockDim = dim3(GT_THREADS, 1, 1);
     cfg.dynamicSmemBytes = deep ? GT_SMEM_DEEP : GT_SMEM_WIDE;
     cfg.stream = ctx->stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1, attr[0].val.clusterDim.y = cluster, attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr, cfg.numAttrs = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr, cfg.numAttrs = ctx->opt.launch_overlap ? 2 : 1;
     if (deep)
         NNCB_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_w8a16_tc_kernel<GT_DEEP>, tw, tx, a));
     else

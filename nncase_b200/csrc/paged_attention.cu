@@ -79,6 +79,7 @@ template <int PA_WARPS>
 __global__ void __launch_bounds__(PA_WARPS * 32)
 paged_attention_decode_kernel(const PaArgs a) {
     extern __shared__ __align__(128) uint8_t pa_smem_raw[];
+    grid_dependency_release(); // the output projection that follows sets itself up and fetches its weights meanwhile
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -286,6 +287,7 @@ paged_attention_decode_kernel(const PaArgs a) {
 __global__ void __launch_bounds__(64)
 paged_attention_merge_kernel(const float *__restrict__ part_o, const float *__restrict__ part_ml, __half *__restrict__ out,
                              int splits) {
+    grid_dependency_release();
     const size_t bh = blockIdx.x;
     const int d = threadIdx.x;
     float M = -INFINITY;
