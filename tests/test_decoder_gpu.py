@@ -74,6 +74,40 @@ def test_gemv_with_swiglu_epilogue(ctx, matmul_form, m, inter, k):
     assert torch.equal(y, y2)
 
 
+def test_matmul_chain_with_and_without_launch_overlap(ctx):
+    """RMSNorm -> gate/up MatMul with SwiGLU -> down MatMul with residual, 64 tokens: the tensor-core MatMuls are
+    launched as programmatic dependents of the kernel before them (their set-up and first weight loads run beside
+    it); the chain gives the same bits with plain launches."""
+    rng = np.random.default_rng(11)
+    m, d, inter = 64, 896, 4864
+    x = rng.normal(0, 1, (m, d)).astype(np.float16)
+    g = rng.normal(1, 0.1, d).astype(np.float16)
+    wgu0, sgu0 = D.quantize_per_channel_i8(rng.normal(0, 0.02, (2 * inter, d)).astype(np.float32))
+    wgu, sgu = D.interleave_gate_up(wgu0, sgu0)
+    wdn, sdn = D.quantize_per_channel_i8(rng.normal(0, 0.02, (d, inter)).astype(np.float32))
+    t = lambda a: torch.from_numpy(a).cuda()
+    gd, wgud, sgud, wdnd, sdnd = t(g), t(wgu), t(sgu), t(wdn), t(sdn)
+    outs = []
+    for overlap in (1, 0, 1):
+        ctx.set_option("launch.overlap", overlap)
+        xd = t(x)
+        h = torch.empty_like(xd)
+        act = torch.empty((m, inter), dtype=torch.float16, device="cuda")
+        y = torch.empty_like(xd)
+        for _ in range(3):  # back to back: each launch finds the one before still running
+            L.check(ctx._lib.nncb_add_rmsnorm_f16(ctx._h, xd.data_ptr(), None, gd.data_ptr(), h.data_ptr(), m, d, 1e-6))
+            L.check(ctx._lib.nncb_gemv_w8a16_swiglu(ctx._h, h.data_ptr(), wgud.data_ptr(), sgud.data_ptr(), None, act.data_ptr(),
+                                                    m, 2 * inter, d))
+            L.check(ctx._lib.nncb_gemv_w8a16(ctx._h, act.data_ptr(), wdnd.data_ptr(), sdnd.data_ptr(), None, xd.data_ptr(),
+                                             y.data_ptr(), m, d, inter))
+        ctx.synchronize()
+        outs.append(y.cpu())
+    ctx.set_option("launch.overlap", 1)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    _, hh = OD.add_rmsnorm(x, None, g, 1e-6)
+    close(outs[0].numpy(), OD.gemv_w8a16(OD.swiglu(OD.gemv_w8a16(hh, wgu0, sgu0), inter), wdn, sdn, None, x))
+
+
 def test_gemv_rejects_unsupported(ctx):
     z = torch.zeros(1 << 16, dtype=torch.float16, device="cuda")
     w = torch.zeros(1 << 16, dtype=torch.int8, device="cuda")
