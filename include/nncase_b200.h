@@ -268,6 +268,15 @@ NNCB_API int nncb_embedding_f16(nncb_context *ctx, const void *table, const int3
 NNCB_API int nncb_paged_attention_workspace_size(nncb_context *ctx, int batch, int q_heads, int kv_heads, int head_dim, int page_size, int max_pages, size_t *bytes);
 NNCB_API int nncb_paged_attention_decode(nncb_context *ctx, const void *q, const void *k_pool, const void *v_pool, const int32_t *block_table, const int32_t *context_lens, void *out, int batch, int q_heads, int kv_heads, int head_dim, int page_size, int max_pages, int num_pages, float scale, void *workspace, size_t workspace_bytes);
 
+/* The same with the step's rotary embedding and KV append inside (one launch instead of nncb_rope_kv_append_f16 +
+ * nncb_paged_attention_decode, bit-identical results): qkv [batch][(q_heads + 2 kv_heads) * 64] f16 holds the
+ * unrotated q, k and v heads of the new token of every sequence, positions [batch] int32 its position
+ * (context_lens[b] must be positions[b] + 1 or more), cos / sin tables [max_pos][32] f32. Each CTA rotates the q
+ * heads it reads; the CTA whose part of the context holds page positions[b] / 16 writes the rotated k and the v
+ * into that page before it loads it. A position outside [0, max_pos), beyond the block-table row or not covered
+ * by the context length appends nothing and sets the status word. */
+NNCB_API int nncb_paged_attention_decode_rope(nncb_context *ctx, const void *qkv, const float *cos_table, const float *sin_table, const int32_t *positions, void *k_pool, void *v_pool, const int32_t *block_table, const int32_t *context_lens, void *out, int batch, int q_heads, int kv_heads, int head_dim, int page_size, int max_pages, int max_pos, int num_pages, float scale, void *workspace, size_t workspace_bytes);
+
 /* Paged-attention decode for callers that must not allocate. (No counterpart in the reference.)
  *
  * Some hosts of this library hand out all device memory up front and forbid the allocator

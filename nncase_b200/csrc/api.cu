@@ -126,7 +126,7 @@ int paged_attention_pick_splits(const nncb_context *ctx, int B, int Hkv, int max
 int paged_attention_check(int B, int Hq, int Hkv, int head_dim, int page_size, int max_pages);
 int paged_attention_launch(nncb_context *ctx, const void *q, const void *k_pool, const void *v_pool,
                            const int32_t *block_table, const int32_t *ctx_lens, void *out, int B, int Hq, int Hkv,
-                           int max_pages, int num_pages, float scale, int splits, void *scratch);
+                           int max_pages, int num_pages, float scale, int splits, void *scratch, const PaRope *rope = nullptr);
 
 int gemv_w8a16(nncb_context *, const void *, const int8_t *, const void *, const void *, const void *, void *, int, int, int);
 int gemv_w8a16_swiglu(nncb_context *, const void *, const int8_t *, const void *, const void *, void *, int, int, int);
@@ -600,6 +600,31 @@ int nncb_paged_attention_decode(nncb_context *ctx, const void *q, const void *k_
                     workspace ? workspace_bytes : (size_t)0);
     return paged_attention_launch(ctx, q, k_pool, v_pool, block_table, context_lens, out, batch, q_heads, kv_heads,
                                   max_pages, num_pages, scale, splits, workspace);
+}
+
+int nncb_paged_attention_decode_rope(nncb_context *ctx, const void *qkv, const float *cos_table, const float *sin_table,
+                                     const int32_t *positions, void *k_pool, void *v_pool, const int32_t *block_table,
+                                     const int32_t *context_lens, void *out, int batch, int q_heads, int kv_heads,
+                                     int head_dim, int page_size, int max_pages, int max_pos, int num_pages, float scale,
+                                     void *workspace, size_t workspace_bytes) {
+    CHECK_CTX(ctx);
+    if (!qkv || !cos_table || !sin_table || !positions || !k_pool || !v_pool || !block_table || !context_lens || !out)
+        return fail(-EINVAL, "nncb_paged_attention_decode_rope: null pointer");
+    if (max_pos <= 0)
+        return fail(-EINVAL, "nncb_paged_attention_decode_rope: max_pos must be positive");
+    NNCB_TRY(paged_attention_check(batch, q_heads, kv_heads, head_dim, page_size, max_pages));
+    if ((reinterpret_cast<uintptr_t>(k_pool) | reinterpret_cast<uintptr_t>(v_pool) | reinterpret_cast<uintptr_t>(qkv) |
+         reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(workspace) | reinterpret_cast<uintptr_t>(cos_table) |
+         reinterpret_cast<uintptr_t>(sin_table)) & 15)
+        return fail(-EINVAL, "nncb_paged_attention_decode_rope: pointers must be 16-byte aligned");
+    const int splits = paged_attention_pick_splits(ctx, batch, kv_heads, max_pages * page_size);
+    const size_t need = paged_attention_scratch_bytes(batch, q_heads, splits);
+    if (need > 0 && (!workspace || workspace_bytes < need))
+        return fail(-EINVAL, "nncb_paged_attention_decode_rope: workspace of %zu bytes required, %zu given", need,
+                    workspace ? workspace_bytes : (size_t)0);
+    PaRope rope = {qkv, cos_table, sin_table, positions, max_pos};
+    return paged_attention_launch(ctx, nullptr, k_pool, v_pool, block_table, context_lens, out, batch, q_heads, kv_heads,
+                                  max_pages, num_pages, scale, splits, workspace, &rope);
 }
 
 int nncb_paged_attention_decode_noalloc(nncb_context *ctx, const void *q, const void *k_pool, const void *v_pool,

@@ -93,6 +93,14 @@ static inline cudaError_t launch_dependent(nncb_context *ctx, void (*kernel)(KAr
 // Raise the dynamic shared-memory limit of this file's kernels on the CURRENT device (the attribute is per
 // device; called for every context that is created).
 int paged_attention_set_attributes();
+// This step's unrotated qkv rows with the rotary tables and positions: the attention kernel then rotates q, and
+// rotates and appends the new token's k / v, itself.
+struct PaRope {
+    const void *qkv;
+    const float *cos_t, *sin_t;
+    const int32_t *positions;
+    int max_pos;
+};
 int gemv_set_attributes();
 
 inline int conv_out_size(int in, int k, int stride, int dil, int pad_before, int pad_after) {

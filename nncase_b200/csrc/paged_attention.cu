@@ -22,6 +22,12 @@
 // low f16 part so that P carries 22 bits.
 // With `splits` > 1 partial (max, sum, unnormalised output) triples go to a scratch buffer and a
 // second small kernel merges them.
+// The ROPE form of the kernel takes the step's unrotated qkv rows instead of q: it rotates the q heads it reads and
+// the new token's k ("rotate half", the arithmetic of rope_kv_append_kernel), writes k and v to their page, and --
+// when the tile that holds the new token has landed in shared memory -- puts them into the token's row of the tile,
+// so the pool write needs no ordering against the loads of the same launch. Its arguments travel in a kernel
+// parameter of their own: with them inside PaArgs the compiler gave the plain form 103 registers instead of 128
+// and the plain kernel lost 5 % (4.27 against 4.51 TB/s).
 #include "internal.cuh"
 #include <cuda_fp16.h>
 
@@ -40,6 +46,16 @@ struct PaArgs {
     int num_pages;    // pages in the pools: page ids outside [0, num_pages) are never dereferenced
     int *status;      // the context's status word
     float scale_log2; // scale * log2(e)
+};
+// Fused rotary embedding and append (the ROPE form of the kernel; PaArgs::q is then unused): qkv
+// [B][(Hq + 2 Hkv) * 64] holds this step's unrotated q heads, k heads, v heads; cos_t / sin_t [max_pos][32] f32;
+// positions [B].
+struct PaRopeArgs {
+    const __half *qkv;
+    const float *cos_t, *sin_t;
+    const int *positions;
+    __half *k_pool_w, *v_pool_w;
+    int max_pos;
 };
 enum { PA_ERR_BAD_INDEX = 202 };
 
@@ -75,9 +91,9 @@ __device__ __forceinline__ uint32_t pa_off(int r, int c) { return (uint32_t)(r *
 
 // PA_WARPS warps per CTA (4: two CTAs per SM, context splits fill the machine; 8: one CTA per SM takes a
 // whole context -- no partials, no merge launch -- when there are enough (sequence, kv head) pairs).
-template <int PA_WARPS>
+template <int PA_WARPS, bool ROPE>
 __global__ void __launch_bounds__(PA_WARPS * 32)
-paged_attention_decode_kernel(const PaArgs a) {
+paged_attention_decode_kernel(const PaArgs a, const PaRopeArgs ra) {
     extern __shared__ __align__(128) uint8_t pa_smem_raw[];
     grid_dependency_release(); // the output projection that follows sets itself up and fetches its weights meanwhile
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
@@ -105,7 +121,7 @@ paged_attention_decode_kernel(const PaArgs a) {
 
     // Q as the A operand (rows = heads of the group, rows >= group are zero)
     uint32_t qa[4][2];
-    {
+    if (!ROPE) {
         const bool hv = g < group;
         const __half *qrow = a.q + ((size_t)b * a.Hq + kvh * group + (hv ? g : 0)) * PA_D;
 #pragma unroll
@@ -153,6 +169,73 @@ paged_attention_decode_kernel(const PaArgs a) {
         else
             asm volatile("cp.async.commit_group;" ::: "memory");
     }
+    // Fused rotary embedding and append: this step's q, k, v arrive unrotated. Rotation pairs dimension i with
+    // i + 32 ("rotate half"): out[i] = x[i] cos - x[i+32] sin, out[i+32] = x[i+32] cos + x[i] sin, rounded to f16 --
+    // the same arithmetic, in the same order, as rope_kv_append_kernel (csrc/decoder_ops.cu). It runs here, behind
+    // the first page loads, so that its chain of dependent reads hides in their flight.
+    int new_u = -1, new_row = 0;  // the warp's unit that holds the new token, and the token's row in it
+    uint32_t new_k = 0u, new_v = 0u; // dims 2 lane, 2 lane + 1 of the new token's rotated k and its v
+    if (ROPE) {
+        int pos = ra.positions[b];
+        const bool pos_ok = pos >= 0 && pos < ra.max_pos && pos / PA_PAGE < a.max_pages;
+        if (!pos_ok) {
+            if (threadIdx.x == 0)
+                atomicCAS(a.status, 0, (int)PA_ERR_BAD_INDEX);
+            pos = 0;
+        }
+        const size_t row_stride = (size_t)(a.Hq + 2 * a.Hkv) * PA_D;
+        const float *cs = ra.cos_t + (size_t)pos * 32, *sn = ra.sin_t + (size_t)pos * 32;
+        {
+            const bool hv = g < group;
+            const __half *qrow = ra.qkv + (size_t)b * row_stride + (size_t)(kvh * group + (hv ? g : 0)) * PA_D;
+            // this lane's dims: 16 ks + 8 j + 2 t + e; the partner of ks < 2 is ks + 2 of the same (j, e)
+#pragma unroll
+            for (int kl = 0; kl < 2; kl++) {
+#pragma unroll
+                for (int j = 0; j < 2; j++) {
+                    const int i = kl * 16 + 8 * j + 2 * t; // index into the cos / sin row (even)
+                    const float2 lo = __half22float2(*reinterpret_cast<const __half2 *>(qrow + i));
+                    const float2 hi = __half22float2(*reinterpret_cast<const __half2 *>(qrow + i + 32));
+                    const float2 c = *reinterpret_cast<const float2 *>(cs + i), sv = *reinterpret_cast<const float2 *>(sn + i);
+                    const float l0 = lo.x * c.x - hi.x * sv.x, l1 = lo.y * c.y - hi.y * sv.y;
+                    const float h0 = hi.x * c.x + lo.x * sv.x, h1 = hi.y * c.y + lo.y * sv.y;
+                    qa[kl][j] = hv ? pack_half2(l0, l1) : 0u;
+                    qa[kl + 2][j] = hv ? pack_half2(h0, h1) : 0u;
+                }
+            }
+        }
+        // The new token's k (rotated) and v belong in page block_table[b][pos / 16], slot pos % 16. The warp whose
+        // unit holds that page writes them to the pool and keeps them: when the unit's tile has landed it puts them
+        // into the token's row of the tile itself, so the pool write needs no ordering against this launch's loads.
+        const int new_page = pos / PA_PAGE;
+        if (pos_ok && new_page >= p_begin && new_page < p_end) {
+            const int uu = (new_page - p_begin) >> 1;
+            if (uu % PA_WARPS == warp) {
+                const int d = 2 * lane, i = d & 31;
+                const __half *krow = ra.qkv + (size_t)b * row_stride + (size_t)(a.Hq + kvh) * PA_D;
+                const __half *vrow = krow + (size_t)a.Hkv * PA_D;
+                const float2 x = __half22float2(*reinterpret_cast<const __half2 *>(krow + d));
+                const float2 other = __half22float2(*reinterpret_cast<const __half2 *>(krow + (d < 32 ? d + 32 : d - 32)));
+                const float2 c = *reinterpret_cast<const float2 *>(cs + i), sv = *reinterpret_cast<const float2 *>(sn + i);
+                const float o0 = d < 32 ? x.x * c.x - other.x * sv.x : x.x * c.x + other.x * sv.x;
+                const float o1 = d < 32 ? x.y * c.y - other.y * sv.y : x.y * c.y + other.y * sv.y;
+                new_k = pack_half2(o0, o1);
+                new_v = *reinterpret_cast<const uint32_t *>(vrow + d);
+                const int pid = table[new_page];
+                if (pid < 0 || pid >= a.num_pages) {
+                    atomicCAS(a.status, 0, (int)PA_ERR_BAD_INDEX); // reads as zeros below, like any bad page
+                } else {
+                    const size_t off = (((size_t)pid * a.Hkv + kvh) * PA_PAGE + (pos % PA_PAGE)) * PA_D + d;
+                    *reinterpret_cast<uint32_t *>(ra.k_pool_w + off) = new_k;
+                    *reinterpret_cast<uint32_t *>(ra.v_pool_w + off) = new_v;
+                    new_u = uu / PA_WARPS;
+                    new_row = pos - (p_begin + 2 * uu) * PA_PAGE;
+                }
+            }
+        } else if (pos_ok && split == 0 && threadIdx.x == 0 && new_page >= n_pages) {
+            atomicCAS(a.status, 0, (int)PA_ERR_BAD_INDEX); // the context length does not cover the new token
+        }
+    }
     for (int u = 0; u < my_units; u++) {
         if (u + PA_STAGES - 1 < my_units)
             issue(u + PA_STAGES - 1, (u + PA_STAGES - 1) % PA_STAGES);
@@ -163,6 +246,13 @@ paged_attention_decode_kernel(const PaArgs a) {
         const int stage = u % PA_STAGES;
         const uint32_t ks = ring_s + stage * 2 * PA_STAGE_BYTES, vs = ks + PA_STAGE_BYTES;
         const int tok0 = (p_begin + 2 * (warp + PA_WARPS * u)) * PA_PAGE; // first token of this unit
+        if (ROPE && u == new_u) {
+            // the new token's row of the tile: what the pool holds from now on, whatever the load saw
+            const uint32_t off = pa_off(new_row, lane >> 2) + (uint32_t)(lane & 3) * 4u;
+            asm volatile("st.shared.u32 [%0], %1;" ::"r"(ks + off), "r"(new_k) : "memory");
+            asm volatile("st.shared.u32 [%0], %1;" ::"r"(vs + off), "r"(new_v) : "memory");
+            __syncwarp();
+        }
         const int tok_end = min(ctx, p_end * PA_PAGE);                    // tokens beyond belong to nobody or to the next split
 
         // ---- S^T = Q K^T : 4 n-tiles of 8 tokens, 4 k-steps of 16 dims ----
@@ -344,9 +434,13 @@ int paged_attention_check(int B, int Hq, int Hkv, int head_dim, int page_size, i
 }
 
 int paged_attention_set_attributes() {
-    NNCB_CUDA_TRY(cudaFuncSetAttribute(paged_attention_decode_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    NNCB_CUDA_TRY(cudaFuncSetAttribute(paged_attention_decode_kernel<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        4 * PA_STAGES * 2 * PA_STAGE_BYTES));
-    NNCB_CUDA_TRY(cudaFuncSetAttribute(paged_attention_decode_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    NNCB_CUDA_TRY(cudaFuncSetAttribute(paged_attention_decode_kernel<8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       8 * PA_STAGES * 2 * PA_STAGE_BYTES));
+    NNCB_CUDA_TRY(cudaFuncSetAttribute(paged_attention_decode_kernel<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       4 * PA_STAGES * 2 * PA_STAGE_BYTES));
+    NNCB_CUDA_TRY(cudaFuncSetAttribute(paged_attention_decode_kernel<8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        8 * PA_STAGES * 2 * PA_STAGE_BYTES));
     return 0;
 }
@@ -354,10 +448,16 @@ int paged_attention_set_attributes() {
 // Launches on ctx->stream. scratch: at least paged_attention_scratch_bytes(B, Hq, splits) bytes when splits > 1.
 int paged_attention_launch(nncb_context *ctx, const void *q, const void *k_pool, const void *v_pool,
                            const int32_t *block_table, const int32_t *ctx_lens, void *out, int B, int Hq, int Hkv,
-                           int max_pages, int num_pages, float scale, int splits, void *scratch) {
+                           int max_pages, int num_pages, float scale, int splits, void *scratch, const PaRope *rope) {
     if (num_pages <= 0)
         return fail(-EINVAL, "paged_attention: num_pages must be positive");
     PaArgs a;
+    PaRopeArgs ra = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0};
+    if (rope) {
+        ra.qkv = (const __half *)rope->qkv, ra.cos_t = rope->cos_t, ra.sin_t = rope->sin_t, ra.positions = rope->positions;
+        ra.k_pool_w = (__half *)const_cast<void *>(k_pool), ra.v_pool_w = (__half *)const_cast<void *>(v_pool);
+        ra.max_pos = rope->max_pos;
+    }
     a.num_pages = num_pages, a.status = ctx->d_status;
     a.q = (const __half *)q, a.k_pool = (const __half *)k_pool, a.v_pool = (const __half *)v_pool;
     a.block_table = block_table, a.ctx_lens = ctx_lens, a.out = (__half *)out;
@@ -368,10 +468,14 @@ int paged_attention_launch(nncb_context *ctx, const void *q, const void *k_pool,
     const int warps = paged_attention_pick_warps(ctx, B, Hkv);
     const size_t smem = (size_t)warps * PA_STAGES * 2 * PA_STAGE_BYTES; // 96 KB or 192 KB
     dim3 grid(splits, Hkv, B);
-    if (warps == 8)
-        paged_attention_decode_kernel<8><<<grid, 8 * 32, smem, ctx->stream>>>(a);
+    if (warps == 8 && rope)
+        paged_attention_decode_kernel<8, true><<<grid, 8 * 32, smem, ctx->stream>>>(a, ra);
+    else if (warps == 8)
+        paged_attention_decode_kernel<8, false><<<grid, 8 * 32, smem, ctx->stream>>>(a, ra);
+    else if (rope)
+        paged_attention_decode_kernel<4, true><<<grid, 4 * 32, smem, ctx->stream>>>(a, ra);
     else
-        paged_attention_decode_kernel<4><<<grid, 4 * 32, smem, ctx->stream>>>(a);
+        paged_attention_decode_kernel<4, false><<<grid, 4 * 32, smem, ctx->stream>>>(a, ra);
     NNCB_TRY(after_launch(ctx, "paged_attention_decode"));
     if (splits > 1) {
         paged_attention_merge_kernel<<<B * Hq, 64, 0, ctx->stream>>>(a.part_o, a.part_ml, a.out, splits);

@@ -180,8 +180,9 @@ def interleave_gate_up(wq, scale):
 class Decoder:
     """One tensor-parallel rank of the decoder (world 1 = the whole model)."""
 
-    def __init__(self, cfg, weights, max_batch, num_pages, ctx=None, device=0, world=1, rank=0, group=None):
+    def __init__(self, cfg, weights, max_batch, num_pages, ctx=None, device=0, world=1, rank=0, group=None, fused_rope=True):
         self.cfg, self.world, self.rank, self.group = cfg, world, rank, group
+        self.fused_rope = fused_rope  # rotary embedding and KV append inside the attention launch (one launch fewer per layer)
         self.ctx = ctx or Context(device)
         dev = self.ctx.device
         w = shard_weights(cfg, weights, world, rank)
@@ -251,16 +252,26 @@ class Decoder:
         for lw in self.layers:
             self._norm(x, delta, lw["ln1"], hh)
             self._gemv(hh, lw["qkv_w"], lw["qkv_s"], lw["qkv_b"], qkv)
-            check(lib.nncb_rope_kv_append_f16(h, qkv.data_ptr(), q.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(),
-                                              positions.data_ptr(), block_table.data_ptr(), lw["k_pool"].data_ptr(),
-                                              lw["v_pool"].data_ptr(), B, self.hq, self.hkv, cfg.head_dim, cfg.page,
-                                              block_table.shape[1], self.cos.shape[0], lw["k_pool"].shape[0]))
-            check(lib.nncb_paged_attention_decode(h, q.data_ptr(), lw["k_pool"].data_ptr(), lw["v_pool"].data_ptr(),
-                                                  block_table.data_ptr(), ctx_lens.data_ptr(), attn.data_ptr(), B,
-                                                  self.hq, self.hkv, cfg.head_dim, cfg.page, block_table.shape[1],
-                                                  lw["k_pool"].shape[0],
-                                                  C.c_float(1.0 / np.sqrt(cfg.head_dim)), self.ws.data_ptr(),
-                                                  self.ws.numel()))
+            if self.fused_rope:
+                # rotary embedding and KV append inside the attention launch
+                check(lib.nncb_paged_attention_decode_rope(h, qkv.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(),
+                                                           positions.data_ptr(), lw["k_pool"].data_ptr(), lw["v_pool"].data_ptr(),
+                                                           block_table.data_ptr(), ctx_lens.data_ptr(), attn.data_ptr(), B,
+                                                           self.hq, self.hkv, cfg.head_dim, cfg.page, block_table.shape[1],
+                                                           self.cos.shape[0], lw["k_pool"].shape[0],
+                                                           C.c_float(1.0 / np.sqrt(cfg.head_dim)), self.ws.data_ptr(),
+                                                           self.ws.numel()))
+            else:
+                check(lib.nncb_rope_kv_append_f16(h, qkv.data_ptr(), q.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(),
+                                                  positions.data_ptr(), block_table.data_ptr(), lw["k_pool"].data_ptr(),
+                                                  lw["v_pool"].data_ptr(), B, self.hq, self.hkv, cfg.head_dim, cfg.page,
+                                                  block_table.shape[1], self.cos.shape[0], lw["k_pool"].shape[0]))
+                check(lib.nncb_paged_attention_decode(h, q.data_ptr(), lw["k_pool"].data_ptr(), lw["v_pool"].data_ptr(),
+                                                      block_table.data_ptr(), ctx_lens.data_ptr(), attn.data_ptr(), B,
+                                                      self.hq, self.hkv, cfg.head_dim, cfg.page, block_table.shape[1],
+                                                      lw["k_pool"].shape[0],
+                                                      C.c_float(1.0 / np.sqrt(cfg.head_dim)), self.ws.data_ptr(),
+                                                      self.ws.numel()))
             self._gemv(attn, lw["o_w"], lw["o_s"], None, proj)
             self._all_reduce(proj)
             self._norm(x, proj, lw["ln2"], hh)

@@ -102,6 +102,8 @@ SIGNATURES = {
     "nncb_embedding_f16": (_I, [_VP, _VP, _VP, _VP, _I, _I, _I]),
     "nncb_paged_attention_workspace_size": (_I, [_VP, _I, _I, _I, _I, _I, _I, C.POINTER(_SZ)]),
     "nncb_paged_attention_decode": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _F, _VP, _SZ]),
+    "nncb_paged_attention_decode_rope": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _I, _F, _VP,
+                                              _SZ]),
     "nncb_paged_attention_decode_noalloc": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _F]),
     "nncb_context_set_option": (_I, [_VP, C.c_char_p, C.c_int64]),
     "nncb_context_get_option": (_I, [_VP, C.c_char_p, C.POINTER(C.c_int64)]),

@@ -94,3 +94,86 @@ def test_unsupported_shapes_are_rejected(ctx):
     with pytest.raises(NncbError) as e:
         ctx.paged_attention_decode(q, k, k, torch.zeros((1, 2), dtype=torch.int32), torch.ones(1, dtype=torch.int32))
     assert e.value.code == -38
+
+
+@pytest.mark.parametrize("positions", [
+    [0, 14, 15, 16, 17, 100, 511, 512, 2047],                 # few sequences: context splits and the merge kernel
+    None,                                                     # 80 sequences: one CTA per sequence and kv head
+])
+def test_rope_and_append_inside_the_attention_launch(ctx, positions):
+    """nncb_paged_attention_decode_rope against nncb_rope_kv_append_f16 followed by nncb_paged_attention_decode on
+    the same inputs: the output and both pools must come out bit-identical (first token, page boundaries, last
+    position of the block table)."""
+    import ctypes as C
+
+    from nncase_b200 import lib as L
+    rng = np.random.default_rng(23)
+    if positions is None:
+        positions = [int(v) for v in rng.integers(0, 400, 80)]
+    hq, hkv, d = 14, 2, 64
+    b = len(positions)
+    lens = [p + 1 for p in positions]
+    _, k_pool, v_pool, table, lens_np = make_cache(23, b, hq, hkv, lens)
+    max_pos = 2048
+    qkv = rng.normal(0, 1, (b, (hq + 2 * hkv) * d)).astype(np.float16)
+    inv = 1.0 / (10000.0 ** (np.arange(32, dtype=np.float64) / 32.0))
+    ang = np.arange(max_pos, dtype=np.float64)[:, None] * inv[None, :]
+    cos, sin = np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    qkv_d, cos_d, sin_d, pos_d, tab_d, len_d = t(qkv), t(cos), t(sin), t(np.asarray(positions, np.int32)), t(table), t(lens_np)
+    lib, h = ctx._lib, ctx._h
+    need = C.c_size_t()
+    L.check(lib.nncb_paged_attention_workspace_size(h, b, hq, hkv, d, 16, table.shape[1], C.byref(need)))
+    ws = torch.empty(max(need.value, 16), dtype=torch.uint8, device="cuda")
+    scale = C.c_float(0.125)
+    # two launches
+    k1, v1 = t(k_pool), t(v_pool)
+    q1 = torch.empty((b, hq, d), dtype=torch.float16, device="cuda")
+    out1 = torch.empty_like(q1)
+    L.check(lib.nncb_rope_kv_append_f16(h, qkv_d.data_ptr(), q1.data_ptr(), cos_d.data_ptr(), sin_d.data_ptr(), pos_d.data_ptr(),
+                                        tab_d.data_ptr(), k1.data_ptr(), v1.data_ptr(), b, hq, hkv, d, 16, table.shape[1], max_pos,
+                                        k1.shape[0]))
+    L.check(lib.nncb_paged_attention_decode(h, q1.data_ptr(), k1.data_ptr(), v1.data_ptr(), tab_d.data_ptr(), len_d.data_ptr(),
+                                            out1.data_ptr(), b, hq, hkv, d, 16, table.shape[1], k1.shape[0], scale, ws.data_ptr(),
+                                            ws.numel()))
+    # one launch
+    k2, v2 = t(k_pool), t(v_pool)
+    out2 = torch.empty_like(q1)
+    L.check(lib.nncb_paged_attention_decode_rope(h, qkv_d.data_ptr(), cos_d.data_ptr(), sin_d.data_ptr(), pos_d.data_ptr(),
+                                                 k2.data_ptr(), v2.data_ptr(), tab_d.data_ptr(), len_d.data_ptr(), out2.data_ptr(),
+                                                 b, hq, hkv, d, 16, table.shape[1], max_pos, k2.shape[0], scale, ws.data_ptr(),
+                                                 ws.numel()))
+    ctx.synchronize()
+    assert torch.equal(k1, k2) and torch.equal(v1, v2)
+    assert not torch.equal(k1, t(k_pool))  # the append happened
+    assert torch.equal(out1, out2)
+    ctx.check_status()
+
+
+def test_rope_inside_attention_flags_a_position_outside_the_context(ctx):
+    """A position the context length does not cover, or outside the rotary table, appends nothing and sets the
+    status word; the launch itself completes."""
+    import ctypes as C
+
+    from nncase_b200 import lib as L
+    from nncase_b200.lib import NncbError
+    hq, hkv, d = 14, 2, 64
+    for positions, lens in (([40, 5], [41, 3]), ([5000, 3], [17, 4])):
+        b = 2
+        _, k_pool, v_pool, table, lens_np = make_cache(29, b, hq, hkv, [64, 64])
+        lens_np = np.asarray(lens, np.int32)
+        t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+        qkv = t(np.ones((b, (hq + 2 * hkv) * d), np.float16))
+        cos, sin = t(np.ones((64, 32), np.float32)), t(np.zeros((64, 32), np.float32))
+        k2, v2, out = t(k_pool), t(v_pool), torch.empty((b, hq, d), dtype=torch.float16, device="cuda")
+        lib, h = ctx._lib, ctx._h
+        need = C.c_size_t()
+        L.check(lib.nncb_paged_attention_workspace_size(h, b, hq, hkv, d, 16, table.shape[1], C.byref(need)))
+        ws = torch.empty(max(need.value, 16), dtype=torch.uint8, device="cuda")
+        L.check(lib.nncb_paged_attention_decode_rope(h, qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                                                     t(np.asarray(positions, np.int32)).data_ptr(), k2.data_ptr(), v2.data_ptr(),
+                                                     t(table).data_ptr(), t(lens_np).data_ptr(), out.data_ptr(), b, hq, hkv, d, 16,
+                                                     table.shape[1], 64, k2.shape[0], C.c_float(0.125), ws.data_ptr(), ws.numel()))
+        ctx.synchronize()
+        with pytest.raises(NncbError):
+            ctx.check_status()
