@@ -700,7 +700,7 @@ def measure_attention(torch, ctx, pk, steps, warmup, batch=64):
                               peak_source=pk["source"]))
 
 
-def measure_decode(torch, ctx, pk, steps, warmup, world, rank, fused_rope=True):
+def measure_decode(torch, ctx, pk, steps, warmup, world, rank, fused_rope=True, peer_reduce=True):
     """One decode step of the Qwen2-0.5B-shaped model (24 layers, hidden 896, 14/2 heads, SwiGLU 4864,
     vocabulary 151936, i8 weights, f16 activations, paged f16 KV cache) at batch 64 and context 2048, tensor
     parallel over `world` ranks, replayed as one CUDA graph. Tokens/s and the HBM bytes a step must read
@@ -714,7 +714,7 @@ def measure_decode(torch, ctx, pk, steps, warmup, world, rank, fused_rope=True):
     weights = D.make_weights(cfg, 1005)
     max_pages = n_ctx // cfg.page + 1
     num_pages = B * max_pages
-    dec = D.Decoder(cfg, weights, B, num_pages, ctx=ctx, world=world, rank=rank, fused_rope=fused_rope)
+    dec = D.Decoder(cfg, weights, B, num_pages, ctx=ctx, world=world, rank=rank, fused_rope=fused_rope, peer_reduce=peer_reduce)
     g = torch.Generator(device=dev).manual_seed(2005)
     for lw in dec.layers:
         lw["k_pool"].normal_(generator=g)
@@ -792,7 +792,7 @@ def run_decode(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     ctx = Context(local)
-    res = measure_decode(torch, ctx, peaks(), args.steps, args.warmup, world, rank, fused_rope=not args.separate_rope)
+    res = measure_decode(torch, ctx, peaks(), args.steps, args.warmup, world, rank, fused_rope=not args.separate_rope, peer_reduce=not args.nccl_reduce)
     if rank == 0:
         print(json.dumps(res))
     # A CUDA graph that held captured NCCL kernels kept the communicator busy: the graph is dropped inside
@@ -822,6 +822,8 @@ def main():
     ap.add_argument("--decode", action="store_true", help="only the decoder step (tensor parallel under torchrun)")
     ap.add_argument("--separate-rope", action="store_true",
                     help="with --decode: rotary embedding and KV append as a launch of their own instead of inside the attention launch")
+    ap.add_argument("--nccl-reduce", action="store_true",
+                    help="with --decode under torchrun: NCCL all-reduce + norm kernel instead of the kernel over peer memory")
     ap.add_argument("--streams", action="store_true", help="only the streaming kernels (quantize, dequantize, add, max-pool, input stage)")
     args = ap.parse_args()
     if args.streams:

@@ -60,6 +60,7 @@ NNCB_API int nncb_synchronize(nncb_context *ctx);
  *   "matmul.tensor_core"     1: nncb_gemv_w8a16 / _swiglu run on the tcgen05 form for more than 32 tokens on matrices of half a
  *                            million weights or more (K a multiple of 64); 2: for every shape that fits; 0: mma.sync form always
  *   "wait_limit_us"          kernel-internal waits give up after this long (default 1,000,000)
+ *   "peer_wait_limit_us"     waits for another rank's flag (nncb_peer_allreduce_add_rmsnorm_f16) give up after this long (default 30,000,000)
  *   "conv.tile_n"            force the N tile of the tensor-core convolution: 128, 96, 64, 48, 32 (0 = choose)
  *   "conv.mma_issuers"       force the number of warps that issue the convolution's MMAs: 1 or 2 (0 = choose)
  *   "conv.load_warps"        force its load warps: 1, 2 = one for activations and one for weights, 3 = two that take the stages in turn (0 = choose)
@@ -250,6 +251,28 @@ NNCB_API int nncb_add_rmsnorm_f16(nncb_context *ctx, void *x, const void *delta,
 NNCB_API int nncb_rope_kv_append_f16(nncb_context *ctx, const void *qkv, void *q_out, const float *cos_table, const float *sin_table, const int32_t *positions, const int32_t *block_table, void *k_pool, void *v_pool, int batch, int q_heads, int kv_heads, int head_dim, int page_size, int max_pages, int max_pos, int num_pages);
 NNCB_API int nncb_swiglu_f16(nncb_context *ctx, const void *gate_up, void *out, int rows, int inter);
 NNCB_API int nncb_embedding_f16(nncb_context *ctx, const void *table, const int32_t *ids, void *out, int rows, int cols, int vocab);
+
+/* ---- tensor-parallel decode: the all-reduce after a row-split projection, over peer memory ----------------
+ * One process per GPU. Every rank allocates, with nncb_malloc, a buffer for its partial results and a flag block of
+ * 128 zeroed bytes, exports both (nncb_ipc_export gives the 64-byte CUDA IPC handle to send to the other ranks) and
+ * maps the other ranks' (nncb_ipc_import; nncb_ipc_close before the owner frees). (No counterpart in the
+ * reference, whose runtime is single-device.)
+ * nncb_peer_allreduce_add_rmsnorm_f16 is the exchange and what follows it in a decoder block, in one launch:
+ *   delta = f16( sum over ranks r = 0 .. world-1, in that order, of partials[r] in f32 );
+ *   x <- f16(x + delta) in place;  h = f16(x * rsqrt(mean(x^2) + eps) * weight)          (as nncb_add_rmsnorm_f16)
+ * partials[r] / flags[r]: host arrays of `world` device pointers (rank r's partial [rows][cols] f16 and flag block;
+ * the own entries are local memory). Launch it after the MatMul that wrote partials[rank], on the same stream, on
+ * every rank with the same slot (0 or 1: two consecutive exchanges must use different slots and different partial
+ * buffers -- a rank may be one exchange ahead of a peer that still reads). The kernel tells the peers that this rank's
+ * partial is ready, waits until every peer has said the same (option "peer_wait_limit_us", default 30 s; a wait that
+ * runs out sets the status word, -ETIMEDOUT from nncb_check_device_status, reads no peer, and later launches
+ * on the context do not wait again until the status has been read), then reads the peers' rows over NVLink with
+ * plain loads. No multicast, no NCCL; works inside a captured CUDA graph (sequence numbers live in the flag blocks).
+ * world 2..8; cols a multiple of 4, at most 2048. */
+NNCB_API int nncb_ipc_export(nncb_context *ctx, const void *dptr, void *handle, size_t handle_bytes);
+NNCB_API int nncb_ipc_import(nncb_context *ctx, const void *handle, size_t handle_bytes, void **dptr);
+NNCB_API int nncb_ipc_close(nncb_context *ctx, void *dptr);
+NNCB_API int nncb_peer_allreduce_add_rmsnorm_f16(nncb_context *ctx, void *x, const void *const *partials, void *const *flags, int world, int rank, int slot, const void *weight, void *h, int rows, int cols, float eps);
 
 /* ---- paged-attention decode ---------------------------------------------------------------
  * The reference has no attention, KV-cache or softmax-over-pages operator (its native op list is

@@ -134,6 +134,8 @@ int add_rmsnorm_f16(nncb_context *, void *, const void *, const void *, void *, 
 int rope_kv_append_f16(nncb_context *, const void *, void *, const float *, const float *, const int32_t *,
                        const int32_t *, void *, void *, int, int, int, int, int, int, int, int);
 int swiglu_f16(nncb_context *, const void *, void *, int, int);
+int peer_allreduce_add_rmsnorm_f16(nncb_context *, void *, const void *const *, void *const *, int, int, int, const void *, void *, int,
+                                   int, float);
 int embedding_f16(nncb_context *, const void *, const int32_t *, void *, int, int, int);
 int int8_peak_selftest(nncb_context *ctx, uint32_t mmas_per_sm, int repeats, int w_signed, double *best_tops, double *mean_tops);
 int mma_issue_selftest(nncb_context *ctx, int n_cols, int issuers, uint32_t mmas_per_issuer, double *cycles_per_mma);
@@ -214,6 +216,7 @@ static int *option_slot(nncb_context *ctx, const char *name) {
         {"launch.overlap", &ctx->opt.launch_overlap},
         {"matmul.tensor_core", &ctx->opt.matmul_tensor_core},
         {"wait_limit_us", reinterpret_cast<int *>(&ctx->opt.wait_limit_us)},
+        {"peer_wait_limit_us", reinterpret_cast<int *>(&ctx->opt.peer_wait_limit_us)},
         {"debug.withhold_load", &ctx->opt.debug_withhold_load},
     };
     for (auto &e : table)
@@ -278,7 +281,7 @@ int nncb_check_device_status(nncb_context *ctx) {
     NNCB_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
     if (st != 0) {
         NNCB_CUDA_TRY(cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream));
-        if (st >= 200)
+        if (st >= 200 && st < 300)
             return fail(-ERANGE, "a kernel refused an out-of-range index read from device memory (code %d)", st);
         return fail(-ETIMEDOUT, "a kernel gave up waiting (role code %d) and returned early", st);
     }
@@ -649,6 +652,43 @@ int nncb_paged_attention_decode_noalloc(nncb_context *ctx, const void *q, const 
     NNCB_TRY(paged_attention_static_scratch(ctx->device, &scratch));
     return paged_attention_launch(ctx, q, k_pool, v_pool, block_table, context_lens, out, batch, q_heads, kv_heads,
                                   max_pages, num_pages, scale, splits, scratch);
+}
+
+int nncb_ipc_export(nncb_context *ctx, const void *dptr, void *handle, size_t handle_bytes) {
+    CHECK_CTX(ctx);
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    if (!dptr || !handle || handle_bytes < sizeof(cudaIpcMemHandle_t))
+        return fail(-EINVAL, "nncb_ipc_export: needs a device pointer and 64 bytes for the handle");
+    cudaIpcMemHandle_t hd;
+    NNCB_CUDA_TRY(cudaIpcGetMemHandle(&hd, const_cast<void *>(dptr)));
+    memcpy(handle, &hd, sizeof(hd));
+    return 0;
+}
+
+int nncb_ipc_import(nncb_context *ctx, const void *handle, size_t handle_bytes, void **dptr) {
+    CHECK_CTX(ctx);
+    if (!handle || handle_bytes < sizeof(cudaIpcMemHandle_t) || !dptr)
+        return fail(-EINVAL, "nncb_ipc_import: needs a 64-byte handle and an out pointer");
+    cudaIpcMemHandle_t hd;
+    memcpy(&hd, handle, sizeof(hd));
+    NNCB_CUDA_TRY(cudaIpcOpenMemHandle(dptr, hd, cudaIpcMemLazyEnablePeerAccess));
+    return 0;
+}
+
+int nncb_ipc_close(nncb_context *ctx, void *dptr) {
+    CHECK_CTX(ctx);
+    if (!dptr)
+        return 0;
+    NNCB_CUDA_TRY(cudaIpcCloseMemHandle(dptr));
+    return 0;
+}
+
+int nncb_peer_allreduce_add_rmsnorm_f16(nncb_context *ctx, void *x, const void *const *partials, void *const *flags, int world,
+                                        int rank, int slot, const void *weight, void *h, int rows, int cols, float eps) {
+    CHECK_CTX(ctx);
+    if (!x || !partials || !flags || !weight || !h)
+        return fail(-EINVAL, "nncb_peer_allreduce_add_rmsnorm_f16: null pointer");
+    return peer_allreduce_add_rmsnorm_f16(ctx, x, partials, flags, world, rank, slot, weight, h, rows, cols, eps);
 }
 
 int nncb_selftest_int8_peak(nncb_context *ctx, uint32_t mmas_per_sm, int repeats, int w_signed, double *best_tops,

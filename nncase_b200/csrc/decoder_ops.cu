@@ -358,6 +358,7 @@ __global__ void __launch_bounds__(128)
 add_rmsnorm_row_kernel(__half *__restrict__ x, const __half *__restrict__ delta, const __half *__restrict__ w,
                        __half *__restrict__ h, int cols, float eps) {
     __shared__ float part[4];
+    grid_dependency_wait();    // launched as a programmatic dependent: x and delta are earlier kernels' output
     grid_dependency_release(); // a MatMul that follows sets itself up and fetches its weights meanwhile
     const size_t row = blockIdx.x;
     uint2 *xr = reinterpret_cast<uint2 *>(x + row * cols);
@@ -447,12 +448,171 @@ int add_rmsnorm_f16(nncb_context *ctx, void *x, const void *delta, const void *w
     const bool al8 = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(delta) | reinterpret_cast<uintptr_t>(w) |
                        reinterpret_cast<uintptr_t>(h)) & 7) == 0;
     if (cols % 4 == 0 && cols <= 2048 && al8)
-        add_rmsnorm_row_kernel<<<rows, 128, 0, ctx->stream>>>((__half *)x, (const __half *)delta, (const __half *)w,
-                                                               (__half *)h, cols, eps);
+        NNCB_CUDA_TRY(launch_dependent(ctx, add_rmsnorm_row_kernel, dim3(rows), dim3(128), 0, (__half *)x, (const __half *)delta,
+                                       (const __half *)w, (__half *)h, cols, eps));
     else
         add_rmsnorm_kernel<<<rows, 128, 0, ctx->stream>>>((__half *)x, (const __half *)delta, (const __half *)w, (__half *)h,
                                                            cols, eps);
     return after_launch(ctx, "add_rmsnorm");
+}
+
+// ---- all-reduce over peer memory, fused with the residual add and RMSNorm -------------------------
+// Tensor-parallel ranks (one process per GPU) each hold a partial [rows][cols] f16 of a row-split projection in a
+// buffer the other ranks have mapped (CUDA IPC). This kernel is the whole exchange:
+//   delta = f16( sum over ranks, in rank order, of the partials in f32 )      -- every rank adds in the same order
+//   x <- f16(x + delta);  h = f16( x * rsqrt(mean(x^2) + eps) * w )            -- as add_rmsnorm_row_kernel
+// It starts after this rank's MatMul (stream order), so block 0 first tells every peer that this rank's partial of
+// sequence number `seq` is complete (a release store into the peer's flag block); every block then waits -- bounded --
+// until its own flag block shows `seq` from every peer, and reads the peers' rows with L2-coherent loads over NVLink.
+// Flag block of a rank (32 unsigned, zeroed once): flag[slot][source rank] at 8 * slot + source, the sequence number
+// of the rank's last finished launch per slot at 16 + slot, its count of finished blocks at 18 + slot. Two slots
+// alternate (o projection, down projection): a rank can reach its next write of a slot only after every peer has
+// finished reading the previous contents (the peers' flags for the launch in between are sent after those reads).
+enum { ERR_PEER_WAIT = 401 };
+struct PeerArgs {
+    const __half *part[8]; // rank r's partial (own: local memory; others: peer mappings)
+    unsigned *flags[8];    // rank r's flag block
+    int world, rank, slot;
+    unsigned limit_us;
+};
+__global__ void __launch_bounds__(128)
+peer_allreduce_add_rmsnorm_kernel(__half *__restrict__ x, const PeerArgs pa, const __half *__restrict__ w, __half *__restrict__ h,
+                                  int cols, float eps, int *status) {
+    __shared__ float part[4];
+    __shared__ int s_ok;
+    grid_dependency_wait();    // launched as a programmatic dependent of the MatMul that writes this rank's partial
+    grid_dependency_release();
+    unsigned *mine = pa.flags[pa.rank];
+    if (threadIdx.x == 0) {
+        const unsigned seq = *reinterpret_cast<volatile unsigned *>(mine + 16 + pa.slot) + 1u;
+        if (blockIdx.x == 0) {
+            __threadfence_system();
+            for (int p = 0; p < pa.world; p++)
+                if (p != pa.rank)
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pa.flags[p] + 8 * pa.slot + pa.rank), "r"(seq) : "memory");
+        }
+        // an earlier give-up on this context is not waited for again
+        bool ok = *reinterpret_cast<volatile int *>(status) == 0;
+        unsigned long long t0 = 0;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+        for (int p = 0; p < pa.world && ok; p++) {
+            if (p == pa.rank)
+                continue;
+            const unsigned *f = mine + 8 * pa.slot + p;
+            for (unsigned spin = 0;; spin++) {
+                unsigned v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+                if ((int)(v - seq) >= 0)
+                    break;
+                if ((spin & 63u) == 63u) {
+                    unsigned long long t1;
+                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+                    if (t1 - t0 > (unsigned long long)pa.limit_us * 1000ull) {
+                        atomicCAS(status, 0, (int)ERR_PEER_WAIT);
+                        ok = false;
+                        break;
+                    }
+                }
+            }
+        }
+        s_ok = ok ? 1 : 0;
+        part[0] = __uint_as_float(seq);
+    }
+    __syncthreads();
+    const bool ok = s_ok != 0;
+    const unsigned seq = __float_as_uint(part[0]);
+    __syncthreads();
+    const size_t row = blockIdx.x;
+    uint2 *xr = reinterpret_cast<uint2 *>(x + row * cols);
+    const int pieces = cols / 4; // 8-byte pieces, at most 4 per thread
+    uint2 v[4];
+    float ss = 0.f;
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+        const int pc = threadIdx.x + 128 * q;
+        v[q] = make_uint2(0, 0);
+        if (pc < pieces) {
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int p = 0; p < pa.world; p++) {
+                if (!ok && p != pa.rank)
+                    continue; // a peer that never answered is not read
+                const uint2 d = __ldcg(reinterpret_cast<const uint2 *>(pa.part[p] + row * cols) + pc);
+                const __half2 *dv = reinterpret_cast<const __half2 *>(&d);
+                const float2 a0 = __half22float2(dv[0]), a1 = __half22float2(dv[1]);
+                acc[0] += a0.x, acc[1] += a0.y, acc[2] += a1.x, acc[3] += a1.y;
+            }
+            v[q] = xr[pc];
+            __half2 *hv = reinterpret_cast<__half2 *>(&v[q]);
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const float2 a = __half22float2(hv[e]);
+                const float2 b2 = __half22float2(__floats2half2_rn(acc[2 * e], acc[2 * e + 1])); // the all-reduced f16 value
+                hv[e] = __floats2half2_rn(a.x + b2.x, a.y + b2.y);
+            }
+            xr[pc] = v[q];
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const float2 a = __half22float2(hv[e]);
+                ss += a.x * a.x + a.y * a.y;
+            }
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1)
+        ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0)
+        part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    const float inv = rsqrtf((part[0] + part[1] + part[2] + part[3]) / (float)cols + eps);
+    uint2 *hr = reinterpret_cast<uint2 *>(h + row * cols);
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+        const int pc = threadIdx.x + 128 * q;
+        if (pc < pieces) {
+            const uint2 gm = __ldg(reinterpret_cast<const uint2 *>(w) + pc);
+            const __half2 *hv = reinterpret_cast<const __half2 *>(&v[q]), *gv = reinterpret_cast<const __half2 *>(&gm);
+            uint2 o2;
+            __half2 *ov = reinterpret_cast<__half2 *>(&o2);
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const float2 a = __half22float2(hv[e]), gg = __half22float2(gv[e]);
+                ov[e] = __floats2half2_rn(a.x * inv * gg.x, a.y * inv * gg.y);
+            }
+            hr[pc] = o2;
+        }
+    }
+    // the last block to finish publishes the sequence number for the next launch on this slot
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(mine + 18 + pa.slot, 1u) == gridDim.x - 1) {
+            mine[18 + pa.slot] = 0u;
+            *reinterpret_cast<volatile unsigned *>(mine + 16 + pa.slot) = seq;
+        }
+    }
+}
+
+int peer_allreduce_add_rmsnorm_f16(nncb_context *ctx, void *x, const void *const *partials, void *const *flags, int world, int rank,
+                                   int slot, const void *w, void *h, int rows, int cols, float eps) {
+    if (rows <= 0 || cols <= 0)
+        return fail(-EINVAL, "peer_allreduce_add_rmsnorm: non-positive dimension");
+    if (world < 2 || world > 8 || rank < 0 || rank >= world || slot < 0 || slot > 1)
+        return fail(-EINVAL, "peer_allreduce_add_rmsnorm: world must be 2..8, rank inside it, slot 0 or 1");
+    if (cols % 4 != 0 || cols > 2048)
+        return fail(-ENOSYS, "peer_allreduce_add_rmsnorm: rows of up to 2048 elements, a multiple of 4, are built");
+    PeerArgs pa;
+    uintptr_t bits = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(h);
+    for (int p = 0; p < 8; p++) {
+        pa.part[p] = p < world ? (const __half *)partials[p] : nullptr;
+        pa.flags[p] = p < world ? (unsigned *)flags[p] : nullptr;
+        if (p < world && (!partials[p] || !flags[p]))
+            return fail(-EINVAL, "peer_allreduce_add_rmsnorm: null buffer for rank %d", p);
+        bits |= reinterpret_cast<uintptr_t>(pa.part[p]);
+    }
+    if (bits & 7)
+        return fail(-EINVAL, "peer_allreduce_add_rmsnorm: pointers must be 8-byte aligned");
+    pa.world = world, pa.rank = rank, pa.slot = slot, pa.limit_us = ctx->opt.peer_wait_limit_us;
+    NNCB_CUDA_TRY(launch_dependent(ctx, peer_allreduce_add_rmsnorm_kernel, dim3(rows), dim3(128), 0, (__half *)x, pa, (const __half *)w,
+                                   (__half *)h, cols, eps, ctx->d_status));
+    return after_launch(ctx, "peer_allreduce_add_rmsnorm");
 }
 
 // ---- rotary embedding of q and k, and append of k, v to the paged cache --------------------------

@@ -22,6 +22,7 @@ struct nncb_options {
     int attention_warps = 0;    // force the CTA width of paged attention (4 or 8)
     int attention_splits = 0;   // force its number of context splits
     unsigned wait_limit_us = 1000000; // kernel-internal waits give up after this long
+    unsigned peer_wait_limit_us = 30000000; // ... and waits for another rank's flag (ranks start their steps at different times) after this long
     int matmul_tensor_core = 1; // w8a16 MatMul on tcgen05: 0 never, 1 for matrices of 2 M weights or more, 2 wherever it fits
     int launch_overlap = 1;     // tensor-core convolutions are launched as programmatic dependents of their predecessor
     int debug_withhold_load = 0; // self-test of the give-up path: the convolution's producer leaves out one load

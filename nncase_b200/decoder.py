@@ -180,7 +180,8 @@ def interleave_gate_up(wq, scale):
 class Decoder:
     """One tensor-parallel rank of the decoder (world 1 = the whole model)."""
 
-    def __init__(self, cfg, weights, max_batch, num_pages, ctx=None, device=0, world=1, rank=0, group=None, fused_rope=True):
+    def __init__(self, cfg, weights, max_batch, num_pages, ctx=None, device=0, world=1, rank=0, group=None, fused_rope=True,
+                 peer_reduce=True):
         self.cfg, self.world, self.rank, self.group = cfg, world, rank, group
         self.fused_rope = fused_rope  # rotary embedding and KV append inside the attention launch (one launch fewer per layer)
         self.ctx = ctx or Context(device)
@@ -216,12 +217,62 @@ class Decoder:
         self.logits = torch.empty((B, cfg.vocab // world), **f16)
         self.ws = torch.empty(4 << 20, dtype=torch.uint8, device=dev)
         self.max_batch = B
+        # the all-reduce after the o and down projections: one kernel over peer memory (with the residual add and the
+        # RMSNorm that follow it), or NCCL followed by the norm kernel
+        self.peer = None
+        if world > 1 and peer_reduce:
+            self._setup_peer()
+
+    def _setup_peer(self):
+        """Allocates this rank's two partial buffers ([max_batch, hidden] f16 each: o projection, down projection) and
+        its flag block, exchanges their CUDA IPC handles with the other ranks and maps theirs."""
+        lib, h = self.ctx._lib, self.ctx._h
+        part_bytes = self.max_batch * self.cfg.hidden * 2
+        part_bytes = (part_bytes + 255) // 256 * 256
+        total = 2 * part_bytes + 256
+        base = C.c_void_p()
+        check(lib.nncb_malloc(h, total, C.byref(base)))
+        check(lib.nncb_memset(h, base, 0, total))
+        self.ctx.synchronize()
+        handle = C.create_string_buffer(64)
+        check(lib.nncb_ipc_export(h, base, handle, 64))
+        handles = [None] * self.world
+        dist.all_gather_object(handles, handle.raw, group=self.group)
+        bases = []
+        for r in range(self.world):
+            if r == self.rank:
+                bases.append(base.value)
+            else:
+                p = C.c_void_p()
+                check(lib.nncb_ipc_import(h, handles[r], 64, C.byref(p)))
+                bases.append(p.value)
+        dist.barrier(group=self.group)  # every block of flags is zeroed and mapped before the first step
+        arr = C.c_void_p * self.world
+        self.peer = dict(
+            base=base, bases=bases, part_bytes=part_bytes,
+            parts=[arr(*[b + s * part_bytes for b in bases]) for s in (0, 1)],
+            flags=arr(*[b + 2 * part_bytes for b in bases]),
+            own=[base.value + s * part_bytes for s in (0, 1)])
+
+    def close(self):
+        """Unmaps the other ranks' buffers and frees this rank's (after a barrier: nobody reads them any more)."""
+        if self.peer is not None:
+            lib, h = self.ctx._lib, self.ctx._h
+            self.ctx.synchronize()
+            dist.barrier(group=self.group)
+            for r, b in enumerate(self.peer["bases"]):
+                if r != self.rank:
+                    check(lib.nncb_ipc_close(h, C.c_void_p(b)))
+            dist.barrier(group=self.group)
+            check(lib.nncb_free(h, self.peer["base"]))
+            self.peer = None
 
     # thin wrappers over the C ABI (device pointers of preallocated tensors)
     def _gemv(self, x, w, s, b, y):
+        """y: a tensor, or the device address of this rank's partial buffer."""
         lib, h = self.ctx._lib, self.ctx._h
         check(lib.nncb_gemv_w8a16(h, x.data_ptr(), w.data_ptr(), s.data_ptr(), b.data_ptr() if b is not None else None,
-                                  None, y.data_ptr(), x.shape[0], w.shape[0], w.shape[1]))
+                                  None, y if isinstance(y, int) else y.data_ptr(), x.shape[0], w.shape[0], w.shape[1]))
 
     def _gemv_swiglu(self, x, w, s, y):
         """y = swiglu(gemv(x)) over interleaved gate/up rows (SwiGLU in the MatMul's epilogue)."""
@@ -236,6 +287,13 @@ class Decoder:
         if self.world > 1:
             dist.all_reduce(t, group=self.group)
 
+    def _reduce_norm(self, x, slot, w, out):
+        """x += all-reduce of the ranks' partials of `slot`; out = RMSNorm(x): one launch over peer memory."""
+        pr = self.peer
+        check(self.ctx._lib.nncb_peer_allreduce_add_rmsnorm_f16(self.ctx._h, x.data_ptr(), pr["parts"][slot], pr["flags"], self.world,
+                                                                self.rank, slot, w.data_ptr(), out.data_ptr(), x.shape[0],
+                                                                x.shape[1], self.cfg.eps))
+
     def step(self, token_ids, positions, block_table):
         """token_ids, positions [B] int32 (position = number of tokens already cached), block_table
         [B, max_pages] int32 (device tensors). Appends this token's K/V and returns this rank's slice of
@@ -249,8 +307,12 @@ class Decoder:
         ctx_lens = positions + 1
         check(lib.nncb_embedding_f16(h, self.embed.data_ptr(), token_ids.data_ptr(), x.data_ptr(), B, cfg.hidden, cfg.vocab))
         delta = None
+        peer = self.peer is not None
         for lw in self.layers:
-            self._norm(x, delta, lw["ln1"], hh)
+            if peer and delta is not None:
+                self._reduce_norm(x, 1, lw["ln1"], hh)  # the down projection's partials of the layer before
+            else:
+                self._norm(x, delta, lw["ln1"], hh)
             self._gemv(hh, lw["qkv_w"], lw["qkv_s"], lw["qkv_b"], qkv)
             if self.fused_rope:
                 # rotary embedding and KV append inside the attention launch
@@ -272,13 +334,23 @@ class Decoder:
                                                       lw["k_pool"].shape[0],
                                                       C.c_float(1.0 / np.sqrt(cfg.head_dim)), self.ws.data_ptr(),
                                                       self.ws.numel()))
-            self._gemv(attn, lw["o_w"], lw["o_s"], None, proj)
-            self._all_reduce(proj)
-            self._norm(x, proj, lw["ln2"], hh)
+            if peer:
+                self._gemv(attn, lw["o_w"], lw["o_s"], None, self.peer["own"][0])
+                self._reduce_norm(x, 0, lw["ln2"], hh)
+            else:
+                self._gemv(attn, lw["o_w"], lw["o_s"], None, proj)
+                self._all_reduce(proj)
+                self._norm(x, proj, lw["ln2"], hh)
             self._gemv_swiglu(hh, lw["gu_w"], lw["gu_s"], act)
-            self._gemv(act, lw["d_w"], lw["d_s"], None, proj)
-            self._all_reduce(proj)
+            if peer:
+                self._gemv(act, lw["d_w"], lw["d_s"], None, self.peer["own"][1])
+            else:
+                self._gemv(act, lw["d_w"], lw["d_s"], None, proj)
+                self._all_reduce(proj)
             delta = proj
-        self._norm(x, delta, self.ln_f, hh)
+        if peer and delta is not None:
+            self._reduce_norm(x, 1, self.ln_f, hh)
+        else:
+            self._norm(x, delta, self.ln_f, hh)
         self._gemv(hh, self.lm_w, self.lm_s, None, self.logits[:B])
         return self.logits[:B]

@@ -99,6 +99,10 @@ SIGNATURES = {
     "nncb_add_rmsnorm_f16": (_I, [_VP, _VP, _VP, _VP, _VP, _I, _I, _F]),
     "nncb_rope_kv_append_f16": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _I]),
     "nncb_swiglu_f16": (_I, [_VP, _VP, _VP, _I, _I]),
+    "nncb_ipc_export": (_I, [_VP, _VP, _VP, _SZ]),
+    "nncb_ipc_import": (_I, [_VP, _VP, _SZ, C.POINTER(_VP)]),
+    "nncb_ipc_close": (_I, [_VP, _VP]),
+    "nncb_peer_allreduce_add_rmsnorm_f16": (_I, [_VP, _VP, C.POINTER(_VP), C.POINTER(_VP), _I, _I, _I, _VP, _VP, _I, _I, _F]),
     "nncb_embedding_f16": (_I, [_VP, _VP, _VP, _VP, _I, _I, _I]),
     "nncb_paged_attention_workspace_size": (_I, [_VP, _I, _I, _I, _I, _I, _I, C.POINTER(_SZ)]),
     "nncb_paged_attention_decode": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _F, _VP, _SZ]),

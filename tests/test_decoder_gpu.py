@@ -108,6 +108,73 @@ def test_matmul_chain_with_and_without_launch_overlap(ctx):
     close(outs[0].numpy(), OD.gemv_w8a16(OD.swiglu(OD.gemv_w8a16(hh, wgu0, sgu0), inter), wdn, sdn, None, x))
 
 
+def _peer_case(ctx, world, rank, rows, cols, seed):
+    """Buffers of a fake tensor-parallel group inside one process: every 'rank' is a local buffer."""
+    rng = np.random.default_rng(seed)
+    parts = [rng.normal(0, 1, (rows, cols)).astype(np.float16) for _ in range(world)]
+    x = rng.normal(0, 1, (rows, cols)).astype(np.float16)
+    g = rng.normal(1, 0.1, cols).astype(np.float16)
+    t = lambda a: torch.from_numpy(a).cuda()
+    parts_d = [t(p) for p in parts]
+    flags_d = [torch.zeros(32, dtype=torch.int32, device="cuda") for _ in range(world)]
+    arr = C.c_void_p * world
+    return dict(parts=parts, x=x, g=g, parts_d=parts_d, flags_d=flags_d, xd=t(x), gd=t(g), h=torch.empty((rows, cols), dtype=torch.float16, device="cuda"),
+                parts_arr=arr(*[p.data_ptr() for p in parts_d]), flags_arr=arr(*[f.data_ptr() for f in flags_d]), world=world, rank=rank)
+
+
+def _peer_call(ctx, c, slot):
+    return ctx._lib.nncb_peer_allreduce_add_rmsnorm_f16(ctx._h, c["xd"].data_ptr(), c["parts_arr"], c["flags_arr"], c["world"], c["rank"],
+                                                        slot, c["gd"].data_ptr(), c["h"].data_ptr(), c["x"].shape[0], c["x"].shape[1],
+                                                        1e-6)
+
+
+@pytest.mark.parametrize("world,rank", [(2, 0), (4, 2), (8, 7)])
+def test_peer_allreduce_add_rmsnorm_with_flags_already_set(ctx, world, rank):
+    """The exchange kernel of tensor-parallel decode on one GPU: the other ranks' partials are local buffers and their
+    'ready' flags for the first two sequence numbers are set by the host beforehand, so nothing waits. The result is
+    the rank-ordered f32 sum rounded to f16, added to x, then RMSNorm; the second launch on the slot uses sequence
+    number 2 and the kernel has told every peer (flag blocks of the other ranks) about both."""
+    c = _peer_case(ctx, world, rank, 7, 896, 40 + world)
+    own_flags = np.zeros(32, np.int32)
+    own_flags[8 * 1:8 * 1 + world] = 2  # slot 1: every peer is already at sequence number 2
+    c["flags_d"][rank].copy_(torch.from_numpy(own_flags))
+    x = c["x"]
+    for launch in (1, 2):
+        L.check(_peer_call(ctx, c, 1))
+        ctx.synchronize()
+        delta = sum(p.astype(np.float32) for p in c["parts"]).astype(np.float16)
+        x, want_h = OD.add_rmsnorm(x, delta, c["g"], 1e-6)
+        assert np.array_equal(c["xd"].cpu().numpy(), x)
+        close(c["h"].cpu().numpy(), want_h)
+        for p in range(world):
+            f = c["flags_d"][p].cpu().numpy()
+            if p != rank:
+                assert f[8 * 1 + rank] == launch  # told by this rank
+        mine = c["flags_d"][rank].cpu().numpy()
+        assert mine[16 + 1] == launch and mine[18 + 1] == 0
+    ctx.check_status()
+
+
+def test_peer_allreduce_wait_runs_out(ctx):
+    """A peer that never reports: the wait gives up after the limit, the launch returns, the status word says so once,
+    later launches on the context do not wait again until the status has been read, and the context still works."""
+    c = _peer_case(ctx, 2, 0, 4, 896, 77)
+    ctx.set_option("peer_wait_limit_us", 2000)
+    try:
+        L.check(_peer_call(ctx, c, 0))
+        L.check(_peer_call(ctx, c, 0))
+        ctx.synchronize()
+        with pytest.raises(L.NncbError) as e:
+            ctx.check_status()
+        assert e.value.code == -110  # -ETIMEDOUT
+        ctx.check_status()
+    finally:
+        ctx.set_option("peer_wait_limit_us", 30000000)
+    y = torch.empty((4, 896), dtype=torch.float16, device="cuda")
+    L.check(ctx._lib.nncb_add_rmsnorm_f16(ctx._h, c["xd"].data_ptr(), None, c["gd"].data_ptr(), y.data_ptr(), 4, 896, 1e-6))
+    ctx.check_status()
+
+
 def test_gemv_rejects_unsupported(ctx):
     z = torch.zeros(1 << 16, dtype=torch.float16, device="cuda")
     w = torch.zeros(1 << 16, dtype=torch.int8, device="cuda")

@@ -1,5 +1,7 @@
-"""Tensor-parallel decode on two and four GPUs (NCCL all-reduce after the o and down projections) against
-the single-GPU decode of the same model. Four ranks share the two kv heads pairwise and pad the query-head
+"""Tensor-parallel decode on two and four GPUs against the single-GPU decode of the same model, with both forms of
+the all-reduce after the o and down projections: the kernel over peer memory that also does the residual add and the
+RMSNorm (plain peer loads, bounded flag waits; eager and replayed as a CUDA graph), and NCCL followed by the norm
+kernel. Four ranks share the two kv heads pairwise and pad the query-head
 groups (see nncase_b200.decoder.shard_plan). Skipped when too few GPUs are visible."""
 import os
 import socket
@@ -17,7 +19,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, q):
+def _worker(rank, world, port, q, peer_reduce):
     import torch.distributed as dist
     from nncase_b200 import decoder as D
     from nncase_b200.kernels import Context
@@ -36,12 +38,29 @@ def _worker(rank, world, port, q):
         kv = [(rng.normal(0, 1, (num_pages, cfg.kv_heads, 16, 64)).astype(np.float16),
                rng.normal(0, 1, (num_pages, cfg.kv_heads, 16, 64)).astype(np.float16)) for _ in range(cfg.layers)]
         ctx = Context(rank)
-        tp = D.Decoder(cfg, w, B, num_pages, ctx=ctx, world=world, rank=rank)
+        tp = D.Decoder(cfg, w, B, num_pages, ctx=ctx, world=world, rank=rank, peer_reduce=peer_reduce)
         heads = D.rank_kv_heads(cfg, world, rank)
         for li in range(cfg.layers):
             tp.layers[li]["k_pool"].copy_(torch.from_numpy(np.ascontiguousarray(kv[li][0][:, heads])))
             tp.layers[li]["v_pool"].copy_(torch.from_numpy(np.ascontiguousarray(kv[li][1][:, heads])))
-        local = tp.step(ids, pos, table)
+        local = tp.step(ids, pos, table).clone()
+        if peer_reduce:
+            # the same step again (it rewrites the same KV slots), replayed from a CUDA graph: the sequence numbers of
+            # the exchange live in device memory, so a replay needs no new arguments
+            ctx.synchronize()
+            dist.barrier()
+            side = torch.cuda.Stream(rank)
+            side.wait_stream(torch.cuda.current_stream(rank))
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                    ctx.use_current_stream()
+                    out = tp.step(ids, pos, table)
+            ctx.use_current_stream()
+            for _ in range(3):
+                graph.replay()
+            torch.cuda.synchronize(rank)
+            assert torch.equal(out, local)
         parts = [torch.empty_like(local) for _ in range(world)]
         dist.all_gather(parts, local.contiguous())
         got = torch.cat(parts, 1).float().cpu().numpy()
@@ -54,19 +73,21 @@ def _worker(rank, world, port, q):
             want = single.step(ids, pos, table).float().cpu().numpy()
             q.put((got, want))
         dist.barrier()
+        tp.close()
     finally:
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("peer_reduce", [True, False])
 @pytest.mark.parametrize("world", [2, 4])
-def test_tp_matches_single_gpu(world):
+def test_tp_matches_single_gpu(world, peer_reduce):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, peer_reduce)) for r in range(world)]
     for p in procs:
         p.start()
     got, want = q.get(timeout=300)
