@@ -176,6 +176,9 @@ paged_attention_decode_kernel(const PaArgs a, const PaRopeArgs ra) {
     int new_u = -1, new_row = 0;  // the warp's unit that holds the new token, and the token's row in it
     uint32_t new_k = 0u, new_v = 0u; // dims 2 lane, 2 lane + 1 of the new token's rotated k and its v
     if (ROPE) {
+        // Launched as a programmatic dependent of the qkv MatMul: the page loads above read nothing that kernel
+        // writes and are in flight while it finishes; its output is first touched here.
+        grid_dependency_wait();
         int pos = ra.positions[b];
         const bool pos_ok = pos >= 0 && pos < ra.max_pos && pos / PA_PAGE < a.max_pages;
         if (!pos_ok) {
@@ -469,11 +472,11 @@ int paged_attention_launch(nncb_context *ctx, const void *q, const void *k_pool,
     const size_t smem = (size_t)warps * PA_STAGES * 2 * PA_STAGE_BYTES; // 96 KB or 192 KB
     dim3 grid(splits, Hkv, B);
     if (warps == 8 && rope)
-        paged_attention_decode_kernel<8, true><<<grid, 8 * 32, smem, ctx->stream>>>(a, ra);
+        NNCB_CUDA_TRY(launch_dependent(ctx, paged_attention_decode_kernel<8, true>, grid, dim3(8 * 32), smem, a, ra));
     else if (warps == 8)
         paged_attention_decode_kernel<8, false><<<grid, 8 * 32, smem, ctx->stream>>>(a, ra);
     else if (rope)
-        paged_attention_decode_kernel<4, true><<<grid, 4 * 32, smem, ctx->stream>>>(a, ra);
+        NNCB_CUDA_TRY(launch_dependent(ctx, paged_attention_decode_kernel<4, true>, grid, dim3(4 * 32), smem, a, ra));
     else
         paged_attention_decode_kernel<4, false><<<grid, 4 * 32, smem, ctx->stream>>>(a, ra);
     NNCB_TRY(after_launch(ctx, "paged_attention_decode"));
