@@ -24,6 +24,7 @@ __global__ void __launch_bounds__(256)
 simt_conv_kernel(SimtGeom g, const uint8_t *__restrict__ x, const void *__restrict__ w,
                  const int32_t *__restrict__ w_zp, EpiParams p, const uint8_t *__restrict__ res,
                  void *__restrict__ y, uint8_t *__restrict__ y2) {
+    grid_dependency_release(); // a tensor-core convolution that follows sets itself up meanwhile
     const int gic = g.c / g.groups, goc = g.oc / g.groups;
     const size_t total = (size_t)g.n * g.oh * g.ow * g.oc;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -134,6 +135,7 @@ __device__ __forceinline__ void dw_requant2(int a0, int a1, float m0, float m1, 
 __global__ void __launch_bounds__(256)
 dw_conv_kernel(SimtGeom g, const uint8_t *__restrict__ x, const int16_t *__restrict__ wdw, EpiParams p, DwFast f,
                const uint8_t *__restrict__ res, uint8_t *__restrict__ y, uint8_t *__restrict__ y2) {
+    grid_dependency_release(); // a tensor-core convolution that follows sets itself up meanwhile
     const int cq = g.c / 4;
     const size_t total = (size_t)g.n * g.oh * g.ow * cq;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
@@ -248,6 +250,7 @@ __global__ void __launch_bounds__(256)
 dw3x3_dp_kernel(SimtGeom g, const uint8_t *__restrict__ x, const uint32_t *__restrict__ wdp, const int32_t *__restrict__ cdp,
                 const int32_t *__restrict__ w_zp, EpiParams p, DwFast f, const uint8_t *__restrict__ res,
                 uint8_t *__restrict__ y, uint8_t *__restrict__ y2) {
+    grid_dependency_release(); // a tensor-core convolution that follows sets itself up meanwhile
     constexpr int NC = 3 * S + 3;
     const uint32_t cq = (uint32_t)g.c / 4u, oxg = ((uint32_t)g.ow + 3u) / 4u;
     const uint32_t j = blockIdx.y * blockDim.x + threadIdx.x;
@@ -318,6 +321,7 @@ template <int S>
 __global__ void __launch_bounds__(256)
 dw3x3_conv_kernel(SimtGeom g, const uint8_t *__restrict__ x, const int16_t *__restrict__ wdw, EpiParams p, DwFast f,
                   const uint8_t *__restrict__ res, uint8_t *__restrict__ y, uint8_t *__restrict__ y2) {
+    grid_dependency_release(); // a tensor-core convolution that follows sets itself up meanwhile
     constexpr int NC = 3 * S + 3;
     // blockIdx.x = output row (image, oy); blockIdx.y * 256 + thread = (group of four outputs, channel quad) in it
     const uint32_t cq = (uint32_t)g.c / 4u, oxg = ((uint32_t)g.ow + 3u) / 4u;

@@ -181,6 +181,7 @@ nchw_to_nhwc_kernel(const void *__restrict__ in_, uint8_t *__restrict__ out, int
 __global__ void __launch_bounds__(256)
 quantize_nchw_to_nhwc4_kernel(const float *__restrict__ in, uint32_t *__restrict__ out, int c, size_t hw,
                               size_t total_pix, float scale, float zp) {
+    grid_dependency_release(); // a tensor-core convolution that follows sets itself up meanwhile
     const uint32_t zq = (uint32_t)min(max(__float2int_rn(zp), 0), 255);
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total_pix;
          i += (size_t)gridDim.x * blockDim.x) {
@@ -238,6 +239,7 @@ __global__ void __launch_bounds__(256)
 quantize_nchw_to_s2d_kernel(const float *__restrict__ in, uint8_t *__restrict__ out, int c_rt, int h, int w,
                             float scale, float rscale, float zp, int pad_t, int pad_b, int pad_l, int pad_r,
                             uint32_t total_rows) {
+    grid_dependency_release(); // a tensor-core convolution that follows sets itself up meanwhile
     // output cells include a border of pad_* cells that hold the zero point in every channel;
     // blockIdx.x = (image, cell row), blockIdx.y * blockDim.x + thread = cell in the row
     const int c = CT ? CT : c_rt;
@@ -496,6 +498,7 @@ __device__ __forceinline__ uint32_t qadd4p(uint32_t a, uint32_t b, uint64_t nza2
 __global__ void __launch_bounds__(256)
 qadd_kernel(const uint8_t *__restrict__ a, const uint8_t *__restrict__ b, uint8_t *__restrict__ y, size_t n,
             float sa, float za, float sb, float zb, float so, float zo, float rso, bool vec_ok) {
+    grid_dependency_release(); // a tensor-core convolution that follows sets itself up meanwhile
     const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t nthreads = (size_t)gridDim.x * blockDim.x;
     const size_t nvec = vec_ok ? n / 16 : 0;
@@ -604,6 +607,7 @@ int lut_u8(nncb_context *ctx, const uint8_t *x, uint8_t *y, size_t n, const uint
 __global__ void __launch_bounds__(256)
 maxpool_vec_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ y, int n, int h, int w, int c, int oh,
                    int ow, int kh, int kw, int sh, int sw, int pt, int pl, uint32_t zp4) {
+    grid_dependency_release(); // a tensor-core convolution that follows sets itself up meanwhile
     // blockIdx.x = (image, output row); blockIdx.y * blockDim.x + thread = (output column, channel group)
     const uint32_t cg = (uint32_t)c / 16u;
     const uint32_t j = blockIdx.y * blockDim.x + threadIdx.x;
@@ -645,6 +649,7 @@ template <int KH, int KW>
 __global__ void __launch_bounds__(256)
 maxpool_vec_fixed_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ y, int n, int h, int w, int c, int oh, int ow,
                          int sh, int sw, int pt, int pl, uint32_t zp4, uint32_t total_rows) {
+    grid_dependency_release(); // a tensor-core convolution that follows sets itself up meanwhile
     const uint32_t cg = (uint32_t)c / 16u;
     const uint32_t j = blockIdx.y * blockDim.x + threadIdx.x;
     // a block walks POOL_ROWS consecutive output rows: fewer, longer-lived blocks than one per row
