@@ -540,7 +540,7 @@ def latency_one_image(torch, ctx, which):
 def measure_matmuls(torch, ctx, pk, reps=100):
     """The five w8a16 MatMuls of a Qwen2-0.5B-shaped decode step at 64 tokens, each replayed `reps` times in one CUDA
     graph (weights warm in L2 except the LM head, which is larger than L2): microseconds per call, weight GB/s, and the
-    form that ran (tcgen05 for more than 32 tokens on matrices of half a million weights or more, mma.sync otherwise)."""
+    form that ran (tcgen05 for more than 32 tokens on matrices of 128 K weights or more, mma.sync otherwise)."""
     from nncase_b200 import lib as L
     dev = ctx.device
     lib, h = ctx._lib, ctx._h
@@ -583,7 +583,7 @@ def measure_matmuls(torch, ctx, pk, reps=100):
         torch.cuda.synchronize(dev)
         us = a.elapsed_time(b) / n_rep * 1e3
         out[name] = dict(n=N, k=K, us=round(us, 2), weight_gbs=round(N * K / us / 1e3, 1),
-                         form="tcgen05" if M > 32 and N * K >= (1 << 19) else "mma.sync")
+                         form="tcgen05" if M > 32 and N * K >= (1 << 17) else "mma.sync")
         del graph
     ctx.check_status()
     out["tokens"] = M

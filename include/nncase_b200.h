@@ -57,8 +57,8 @@ NNCB_API int nncb_synchronize(nncb_context *ctx);
  * src/Native/src/runtime/interpreter.cpp:29-31). Read when a plan is created or a kernel is launched.
  *   "launch.overlap"         1: tensor-core convolutions are launched as programmatic dependents of the kernel before them in
  *                            the stream (their set-up overlaps its last tiles); 0: plain launches
- *   "matmul.tensor_core"     1: nncb_gemv_w8a16 / _swiglu run on the tcgen05 form for more than 32 tokens on matrices of half a
- *                            million weights or more (K a multiple of 64); 2: for every shape that fits; 0: mma.sync form always
+ *   "matmul.tensor_core"     1: nncb_gemv_w8a16 / _swiglu run on the tcgen05 form for more than 32 tokens on matrices of 128 K
+ *                            weights or more (K a multiple of 64); 2: for every shape that fits; 0: mma.sync form always
  *   "wait_limit_us"          kernel-internal waits give up after this long (default 1,000,000)
  *   "peer_wait_limit_us"     waits for another rank's flag (nncb_peer_allreduce_add_rmsnorm_f16) give up after this long (default 30,000,000)
  *   "conv.tile_n"            force the N tile of the tensor-core convolution: 128, 96, 64, 48, 32 (0 = choose)

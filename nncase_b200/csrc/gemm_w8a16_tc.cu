@@ -427,12 +427,13 @@ constexpr size_t GT_SMEM_WIDE = gt_smem_bytes(1, 3, 3), GT_SMEM_DEEP = gt_smem_b
 
 // Where this form is the faster one (measured on the projections of a 0.5 B model and its LM head): more than 32
 // tokens -- below that the CUDA-core form streams the weights in 3 to 6 us a projection, less than this kernel's
-// set-up, first loads and cluster barriers cost (5 us) -- and at least half a million weights. Option
-// matmul.tensor_core = 2 takes every shape that fits.
+// set-up, first loads and cluster barriers cost (5 us) -- and at least 128 K weights (measured down to 896 x 256,
+// the per-rank projections of eight-way tensor parallelism: 4.6 against 4.7 us; 576 x 896: 4.8 against 6.9 us).
+// Option matmul.tensor_core = 2 takes every shape that fits.
 bool gemm_w8a16_tc_applies(const nncb_context *ctx, int M, int N, int K) {
     if (M < 1 || M > 64 || K % 64 != 0 || K < 64 || N < 16)
         return false;
-    return ctx->opt.matmul_tensor_core >= 2 || (M > 32 && (long long)N * K >= (1ll << 19));
+    return ctx->opt.matmul_tensor_core >= 2 || (M > 32 && (long long)N * K >= (1ll << 17));
 }
 
 // Launches the tensor-core form (the caller has checked gemm_w8a16_tc_applies and the pointer alignment).

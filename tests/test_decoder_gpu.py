@@ -23,7 +23,7 @@ def close(got, want, tol=1e-3):
 @pytest.fixture(params=[0, 2], ids=["mma_sync", "tcgen05"])
 def matmul_form(ctx, request):
     """Both forms of the w8a16 MatMul: CUDA-core-fed mma.sync, and tcgen05 with the accumulator in TMEM (forced for
-    every shape that fits; by default it takes more than 32 tokens on matrices of half a million weights or more). The
+    every shape that fits; by default it takes more than 32 tokens on matrices of 128 K weights or more). The
     shapes below cover both launch forms, K split over clusters of 2, 4 and 8 CTAs, a cluster rank without K blocks,
     ragged token and channel counts."""
     ctx.set_option("matmul.tensor_core", request.param)
