@@ -33,7 +33,10 @@
 // 15 us launch, which is what the cluster form removes. What-if builds of the LM head: no conversion 53 us, no
 // MMAs 52 us, neither 46 us, without the epilogue's stores 36 us. Also measured and not kept: a persistent CTA per
 // SM with the activations resident and a staged, 16-byte-per-thread store (LM head 58 us, gate/up 15 us: no
-// change), a load ring of six slots with one CTA per SM for the LM head (82 us: nothing hides a CTA's fill and
+// change), the K-split partials pushed into the finishing CTA's shared memory with remote stores so that one
+// cluster barrier is enough (qkv 5.5 us, down 7.8 us: no change), the first activation loads sent by the MMA thread
+// and the peers' partials fetched in one batch of 16 (no change; the LM head loses 4 us when its first loads wait
+// for the block's first barrier), a load ring of six slots with one CTA per SM for the LM head (82 us: nothing hides a CTA's fill and
 // drain), and two MMA-issuing threads with an accumulator each (no change).
 #include "tc_dev.cuh"
 #include <cuda_fp16.h>
