@@ -65,6 +65,8 @@ NNCB_API int nncb_synchronize(nncb_context *ctx);
  *   "conv.mma_issuers"       force the number of warps that issue the convolution's MMAs: 1 or 2 (0 = choose)
  *   "conv.load_warps"        force its load warps: 1, 2 = one for activations and one for weights, 3 = two that take the stages in turn (0 = choose)
  *   "conv.wide_patch"        0: keep 64-/128-channel stride-1 convolutions on the im2col form (default 1)
+ *   "conv.add_table"         the fused residual add of the tensor-core convolution: 2 = the unfused float chain on packed arithmetic
+ *                            instead of the look-up in a table of all byte pairs (default 0; same bits, measured slower)
  *   "depthwise.dot_product"  0: multiply-add form of the 3x3 depthwise kernel (default 1)
  *   "attention.warps"        force the CTA width of paged attention: 4 or 8 (0 = choose)
  *   "attention.splits"       force its number of context splits (0 = choose)

@@ -210,6 +210,7 @@ static int *option_slot(nncb_context *ctx, const char *name) {
         {"conv.mma_issuers", &ctx->opt.conv_mma_issuers},
         {"conv.load_warps", &ctx->opt.conv_load_warps},
         {"conv.wide_patch", &ctx->opt.conv_wide_patch},
+        {"conv.add_table", &ctx->opt.conv_add_table},
         {"depthwise.dot_product", &ctx->opt.depthwise_dot},
         {"attention.warps", &ctx->opt.attention_warps},
         {"attention.splits", &ctx->opt.attention_splits},

@@ -18,6 +18,7 @@ struct nncb_options {
     int conv_mma_issuers = 0;   // force the number of MMA-issuing warps of the tensor-core convolution (1 or 2)
     int conv_load_warps = 0;    // force its load warps (1; 2: activations and weights apart; 3: two, stages in turn)
     int conv_wide_patch = 1;    // 0: keep 64-/128-channel stride-1 layers on the im2col form
+    int conv_add_table = 0;     // fused residual add of the tensor-core convolution: 2: the float chain on packed arithmetic instead of the byte-pair table (same bits, measured slower)
     int depthwise_dot = 1;      // 0: the multiply-add form of the 3x3 depthwise kernel
     int attention_warps = 0;    // force the CTA width of paged attention (4 or 8)
     int attention_splits = 0;   // force its number of context splits

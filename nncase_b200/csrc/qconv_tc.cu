@@ -291,6 +291,10 @@ struct FastEpi {
     float qlo, qhi;     // the fused clamp's bounds after quantization, within [0, 255]
     const float4 *cst;  // [oc_pad] {mult, bias, bits(corr of class 0), bits(-zw)}
     const uint8_t *add_table; // [256][256] quantized sum of (convolution output, residual), or null
+    // the same chain in arithmetic (add_math): -(residual zero point), residual scale, the add's output scale as
+    // correctly rounded reciprocal and negated, its zero point
+    int add_math;
+    float add_nzr, add_sr, add_rsa, add_nsa, add_za;
 };
 
 struct TcArgs {
@@ -1002,7 +1006,8 @@ __device__ __forceinline__ uint32_t stage_addr(uint32_t base, int row, int chunk
 }
 } // namespace dev
 
-template <bool RES, bool Y2, bool XSUM, bool ROWS>
+// RES: 0 no residual, 1 fused add through the byte-pair table, 2 fused add as the float chain itself
+template <int RES, bool Y2, bool XSUM, bool ROWS>
 __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &sg, TcShared &sh, uint32_t tmem_base,
                                               const CUtensorMap *tmap_y, const CUtensorMap *tmap_y2,
                                               const CUtensorMap *tmap_res, int warp, int lane) {
@@ -1061,7 +1066,7 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
         else
             tma_store_2d(map, src, c[0], c[1]);
     };
-    if (RES) {
+    if (RES == 1) {
         // the add table (65 KB), copied once per CTA
         const uint4 *src = reinterpret_cast<const uint4 *>(f.add_table);
         for (int i = et; i < ADD_TABLE_BYTES / 16; i += 32 * EPI_WARPS)
@@ -1173,6 +1178,9 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
         const uint64_t rso2 = pack2(f.rso, f.rso), nso2 = pack2(-f.so, -f.so), zo2 = pack2(f.zo, f.zo);
         const uint64_t one2 = pack2(f.one, f.one);
         const uint64_t rsumf2 = pack2((float)rsum, (float)rsum);
+        const uint64_t add_nzo2 = pack2(-f.zo, -f.zo), add_so2 = pack2(f.so, f.so), add_nzr2 = pack2(f.add_nzr, f.add_nzr);
+        const uint64_t add_sr2 = pack2(f.add_sr, f.add_sr), add_rsa2 = pack2(f.add_rsa, f.add_rsa);
+        const uint64_t add_nsa2 = pack2(f.add_nsa, f.add_nsa), add_za2 = pack2(f.add_za, f.add_za);
         auto chunk = [&](const int (&v)[8], const int cc, auto multi_tag, auto clamp_tag, auto fc_tag) {
             constexpr bool MULTI = decltype(multi_tag)::value;
             constexpr bool FC = decltype(fc_tag)::value; // corrections in float (never with MULTI)
@@ -1228,7 +1236,23 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
                     u0 = fminf(u0, f.qhi), u1 = fminf(u1, f.qhi);
                 asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(bits[j]) : "f"(u0));
                 asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(bits[j + 1]) : "f"(u1));
-                if (RES) {
+                if (RES == 2) {
+                    // dequantize both addends, add, requantise: the unfused chain itself, two outputs at a time.
+                    // (q - zo) so and (r - zr) sr are rounded products; their sum is a fused multiply-add by one
+                    // (see the bias add above); the division is the three-operation exact quotient.
+                    const uint32_t r0 = __byte_perm(rwa[j >> 2], 0u, 0x4440 | (j & 3));
+                    const uint32_t r1 = __byte_perm(rwa[j >> 2], 0u, 0x4440 | ((j + 1) & 3));
+                    const uint64_t ya = mul2(add2(pack2((float)bits[j], (float)bits[j + 1]), add_nzo2), add_so2);
+                    const uint64_t yb = mul2(add2(pack2((float)r0, (float)r1), add_nzr2), add_sr2);
+                    const uint64_t sum = fma2(ya, one2, yb);
+                    const uint64_t p0 = mul2(sum, add_rsa2);
+                    const uint64_t p2 = fma2(fma2(p0, add_nsa2, sum), add_rsa2, p0);
+                    float w0, w1;
+                    unpack2(add2(p2, add_za2), w0, w1);
+                    asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(bits[j]) : "f"(w0));
+                    asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(bits[j + 1]) : "f"(w1));
+                }
+                if (RES == 1) {
                     // dequantize both addends, add, requantise -- as a table of all byte pairs. Rows of 260
                     // bytes: the bank of entry (q, r) is (q + r / 4) mod 32, so the pixels of one channel,
                     // which have similar q and similar r, spread over the banks.
@@ -1321,7 +1345,7 @@ __device__ __forceinline__ void epilogue_fast(const TcArgs &a, const StageGeom &
         tma_store_wait_all();
 }
 
-template <bool RES, bool Y2, bool XSUM, bool ROWS>
+template <int RES, bool Y2, bool XSUM, bool ROWS>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 tc_conv_fast_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_y, const __grid_constant__ CUtensorMap tmap_y2,
@@ -1774,7 +1798,16 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
         fe.res_pitch = tile_bytes;
         fe.off_cst = off, off += (uint32_t)g.bn * 16;
         fe.off_lut2 = off, off += 256;
-        fe.off_tab = off, off += d.has_residual ? ADD_TABLE_BYTES : 0;
+        // The fused residual add: a look-up in a table of all byte pairs (65 KB of shared memory, one load per
+        // output), or -- option conv.add_table = 2 -- the float chain itself on packed arithmetic (about six more
+        // instructions per output, no table, room for four pipeline stages instead of two on a 128 x 144 tile with
+        // several K blocks). Measured on the 16 such layers of ResNet-50 at 512 images, table -> arithmetic: 56 x 56
+        // 434 -> 538 us, 28 x 28 233 -> 271, 14 x 14 (K 256) 137 -> 148, 7 x 7 (K 512) 91.5 -> 92.6; 3.33 -> 3.91 ms
+        // in all. The table stays the default everywhere: the epilogue's instruction issue, not the table's
+        // look-ups or the depth of the ring, is what these layers wait for.
+        if (d.has_residual)
+            fe.add_math = ctx->opt.conv_add_table == 2 ? 1 : 0;
+        fe.off_tab = off, off += (d.has_residual && !fe.add_math) ? ADD_TABLE_BYTES : 0;
         fe.off_corr = off;
         extras = off; // the per-class table is appended once the classes are known
         // each epilogue warp stages a 32-row x wcols-byte sub-tile; 32-byte rows are the swizzle span
@@ -1918,6 +1951,11 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
             addtab.assign(ADD_TABLE_BYTES, 0);
             const float so = d.out_scale, zo = (float)d.out_zp, sr = d.res_scale, zr = (float)d.res_zp;
             const float sa = d.add_out_scale, za = (float)d.add_out_zp;
+            fe.add_nzr = -zr, fe.add_sr = sr, fe.add_za = za, fe.add_nsa = -sa;
+            bool ok_sa = true;
+            fe.add_rsa = rn_reciprocal(sa, &ok_sa);
+            if (!ok_sa && fe.add_math)
+                return fail(-ENOSYS, "tcgen05 conv: the fused add's output scale is outside the range of the exact division");
             for (int qa = 0; qa < 256; qa++) {
                 const float da = (float)qa - zo;
                 const float ya = da * so;
@@ -1937,7 +1975,7 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
             NNCB_CUDA_TRY(cudaMalloc(&tp->d_cst, cst.size() * sizeof(float4)));
             NNCB_CUDA_TRY(cudaMemcpyAsync(tp->d_cst, cst.data(), cst.size() * sizeof(float4), cudaMemcpyHostToDevice, ctx->stream));
             fe.cst = tp->d_cst;
-            if (!addtab.empty()) {
+            if (!addtab.empty() && !fe.add_math) {
                 NNCB_CUDA_TRY(cudaMalloc(&tp->d_addtab, addtab.size()));
                 NNCB_CUDA_TRY(cudaMemcpyAsync(tp->d_addtab, addtab.data(), addtab.size(), cudaMemcpyHostToDevice, ctx->stream));
                 fe.add_table = tp->d_addtab;
@@ -2017,10 +2055,11 @@ int tc_conv_create(nncb_context *ctx, nncb_qconv2d *cv, const void *w_host, cons
     // plan can ask for.
     const int lim = 226 * 1024;
     NNCB_CUDA_TRY(cudaFuncSetAttribute(tc_conv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
-    const void *fast_kernels[16] = {
+    const void *fast_kernels[24] = {
 #define NNCB_K(R, Y, X) (const void *)tc_conv_fast_kernel<R, Y, X, false>, (const void *)tc_conv_fast_kernel<R, Y, X, true>
-        NNCB_K(false, false, false), NNCB_K(false, false, true), NNCB_K(false, true, false), NNCB_K(false, true, true),
-        NNCB_K(true, false, false),  NNCB_K(true, false, true),  NNCB_K(true, true, false),  NNCB_K(true, true, true)
+        NNCB_K(0, false, false), NNCB_K(0, false, true), NNCB_K(0, true, false), NNCB_K(0, true, true),
+        NNCB_K(1, false, false), NNCB_K(1, false, true), NNCB_K(1, true, false), NNCB_K(1, true, true),
+        NNCB_K(2, false, false), NNCB_K(2, false, true), NNCB_K(2, true, false), NNCB_K(2, true, true)
 #undef NNCB_K
     };
     for (const void *k : fast_kernels)
@@ -2122,7 +2161,7 @@ int tc_conv_run(nncb_context *ctx, nncb_qconv2d *cv, const uint8_t *x, const uin
             tp->res_ptr = res;
         }
         const CUtensorMap &my2 = y2 ? tp->tmap_y2 : tp->tmap_y, &mres = res ? tp->tmap_res : tp->tmap_y;
-        const int variant = (res ? 4 : 0) | (y2 ? 2 : 0) | (tp->g.has_xsum ? 1 : 0);
+        const int variant = (res ? (tp->f->add_math ? 8 : 4) : 0) | (y2 ? 2 : 0) | (tp->g.has_xsum ? 1 : 0);
 #define NNCB_LAUNCH_FAST(R, Y, C)                                                                                     \
     do {                                                                                                              \
         if (tp->g.mode == MODE_ROWS || tp->g.mode == MODE_PATCH)                                                      \
@@ -2133,14 +2172,18 @@ int tc_conv_run(nncb_context *ctx, nncb_qconv2d *cv, const uint8_t *x, const uin
                              tp->tmap_a, tp->tmap_b, tp->tmap_y, my2, mres, a);                                       \
     } while (0)
         switch (variant) {
-        case 0: NNCB_LAUNCH_FAST(false, false, false); break;
-        case 1: NNCB_LAUNCH_FAST(false, false, true); break;
-        case 2: NNCB_LAUNCH_FAST(false, true, false); break;
-        case 3: NNCB_LAUNCH_FAST(false, true, true); break;
-        case 4: NNCB_LAUNCH_FAST(true, false, false); break;
-        case 5: NNCB_LAUNCH_FAST(true, false, true); break;
-        case 6: NNCB_LAUNCH_FAST(true, true, false); break;
-        default: NNCB_LAUNCH_FAST(true, true, true); break;
+        case 0: NNCB_LAUNCH_FAST(0, false, false); break;
+        case 1: NNCB_LAUNCH_FAST(0, false, true); break;
+        case 2: NNCB_LAUNCH_FAST(0, true, false); break;
+        case 3: NNCB_LAUNCH_FAST(0, true, true); break;
+        case 4: NNCB_LAUNCH_FAST(1, false, false); break;
+        case 5: NNCB_LAUNCH_FAST(1, false, true); break;
+        case 6: NNCB_LAUNCH_FAST(1, true, false); break;
+        case 7: NNCB_LAUNCH_FAST(1, true, true); break;
+        case 8: NNCB_LAUNCH_FAST(2, false, false); break;
+        case 9: NNCB_LAUNCH_FAST(2, false, true); break;
+        case 10: NNCB_LAUNCH_FAST(2, true, false); break;
+        default: NNCB_LAUNCH_FAST(2, true, true); break;
         }
 #undef NNCB_LAUNCH_FAST
         return after_launch(ctx, "tc_conv_fast");

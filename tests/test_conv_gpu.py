@@ -143,6 +143,35 @@ def test_tc_conv_residual_and_second_output(ctx, qo, oc):
         assert np.array_equal(got2.cpu().numpy(), want2)
 
 
+@pytest.mark.parametrize("add_form", [0, 2])
+@pytest.mark.parametrize("c,oc", [(64, 256), (512, 96), (256, 64), (512, 2048)])
+def test_tc_conv_fused_add_table_and_arithmetic(ctx, qo, add_form, c, oc):
+    """The fused residual add of the tensor-core convolution in its two forms -- a look-up in the table of all byte
+    pairs (the default), and the unfused float chain itself on packed arithmetic (option conv.add_table = 2, which leaves
+    the table's 65 KB to the pipeline stages): the same bits as the operator chain conv -> add (-> requantized second output), over every residual byte and a spread of convolution outputs."""
+    n, h, w = 2, 14, 14
+    case = make_case(300 + c + oc, n, h, w, c, oc, 1, 1)
+    xq, zx, wq, zw, mult, bias, oqp = case
+    rng = np.random.default_rng(43)
+    res = rng.integers(0, 256, (n, h, w, oc), dtype=np.uint8)
+    rq, aq, yq2 = QuantParam(117, 0.05), QuantParam(125, 0.06), QuantParam(0, 0.03)
+    y1 = qo.qconv2d_u8(xq, wq, zw, mult, bias, zx, oqp.scale, oqp.zero_point)
+    want = qo.qadd_u8(y1, res, oqp.scale, oqp.zero_point, rq.scale, rq.zero_point, aq.scale, aq.zero_point)
+    want2 = qo.requant_u8(want, aq.scale, aq.zero_point, yq2.scale, yq2.zero_point, 0.0, np.inf)
+    ctx.set_option("conv.add_table", add_form)
+    try:
+        got, got2 = ctx.conv2d(torch.from_numpy(xq), wq, zw, mult, bias, zx, oqp, res=torch.from_numpy(res).cuda(),
+                               residual=(rq, aq), y2=(yq2, 0.0, float("inf")), force_path=L.PATH_TC)
+        ctx.check_status()
+        assert np.array_equal(got.cpu().numpy(), want)
+        assert np.array_equal(got2.cpu().numpy(), want2)
+        got = ctx.conv2d(torch.from_numpy(xq), wq, zw, mult, bias, zx, oqp, res=torch.from_numpy(res).cuda(),
+                         residual=(rq, aq), force_path=L.PATH_TC)
+        assert np.array_equal(got.cpu().numpy(), want)
+    finally:
+        ctx.set_option("conv.add_table", 0)
+
+
 def test_tc_matmul_f32_logits(ctx, qo):
     """FC layer: [M,K] x [N,K] with real-valued f32 output (classifier logits)."""
     m, k, n = 70, 2048, 1000
