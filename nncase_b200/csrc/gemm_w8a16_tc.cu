@@ -16,8 +16,8 @@
 // A ring stage holds one or two such K blocks; the two groups of four conversion warps take the stages in turn.
 // After the last stage the eight warps read the accumulator (lane = channel, 32 token columns each) and finish.
 // Two shapes of launch:
-//   * many channel tiles (an LM head): two CTAs per SM, three one-block stages each, the whole K in one CTA, the
-//     result finished from registers;
+//   * many channel tiles (an LM head): two CTAs per SM, four one-block load stages and two stages of converted
+//     tiles each (three and three: LM head 54 -> 52 us), the whole K in one CTA, the result finished from registers;
 //   * few channel tiles (the projections of a layer: 7 to 76): K is split over the 2, 4 or 8 CTAs of a thread-block
 //     cluster. Every CTA leaves its f32 partial [64 tokens][128 channels] in its own shared memory (the ring is idle
 //     by then); after a cluster barrier CTA r finishes token rows 64 r / S .. of the tile, adding the S partials in
@@ -424,9 +424,9 @@ gemm_w8a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
 
 } // namespace
 
-#define GT_WIDE 1, 3, 3, 2
+#define GT_WIDE 1, 4, 2, 2
 #define GT_DEEP 2, 5, 2, 1
-constexpr size_t GT_SMEM_WIDE = gt_smem_bytes(1, 3, 3), GT_SMEM_DEEP = gt_smem_bytes(2, 5, 2);
+constexpr size_t GT_SMEM_WIDE = gt_smem_bytes(1, 4, 2), GT_SMEM_DEEP = gt_smem_bytes(2, 5, 2);
 
 // Where this form is the faster one (measured on the projections of a 0.5 B model and its LM head): more than 32
 // tokens -- below that the CUDA-core form streams the weights in 3 to 6 us a projection, less than this kernel's
