@@ -222,6 +222,9 @@ class Decoder:
         self.peer = None
         if world > 1 and peer_reduce:
             self._setup_peer()
+        if world > 1:
+            self.parallelism += (", all-reduce as one kernel over peer memory with the residual add and RMSNorm" if self.peer
+                                 else ", NCCL all-reduce")
 
     def _setup_peer(self):
         """Allocates this rank's two partial buffers ([max_batch, hidden] f16 each: o projection, down projection) and
@@ -238,14 +241,30 @@ class Decoder:
         check(lib.nncb_ipc_export(h, base, handle, 64))
         handles = [None] * self.world
         dist.all_gather_object(handles, handle.raw, group=self.group)
-        bases = []
+        bases, failed = [], None
         for r in range(self.world):
             if r == self.rank:
                 bases.append(base.value)
-            else:
-                p = C.c_void_p()
+                continue
+            p = C.c_void_p()
+            try:
                 check(lib.nncb_ipc_import(h, handles[r], 64, C.byref(p)))
-                bases.append(p.value)
+            except NncbError as e:  # no peer access between these two GPUs, or IPC closed to this process
+                failed = e
+                p = C.c_void_p(0)
+            bases.append(p.value or 0)
+        # every rank takes the same path: if one mapping failed anywhere, all fall back to NCCL's all-reduce
+        okay = torch.tensor([0 if failed else 1], dtype=torch.int32, device=self.ctx.device)
+        dist.all_reduce(okay, op=dist.ReduceOp.MIN, group=self.group)
+        if int(okay.item()) == 0:
+            for r, b in enumerate(bases):
+                if r != self.rank and b:
+                    lib.nncb_ipc_close(h, C.c_void_p(b))
+            dist.barrier(group=self.group)
+            check(lib.nncb_free(h, base))
+            import warnings
+            warnings.warn(f"tensor-parallel decode: peer memory could not be mapped ({failed}); using NCCL all-reduce")
+            return
         dist.barrier(group=self.group)  # every block of flags is zeroed and mapped before the first step
         arr = C.c_void_p * self.world
         self.peer = dict(
