@@ -257,8 +257,9 @@ NNCB_API int nncb_embedding_f16(nncb_context *ctx, const void *table, const int3
 /* ---- tensor-parallel decode: the all-reduce after a row-split projection, over peer memory ----------------
  * One process per GPU. Every rank allocates, with nncb_malloc, a buffer for its partial results and a flag block of
  * 128 zeroed bytes, exports both (nncb_ipc_export gives the 64-byte CUDA IPC handle to send to the other ranks) and
- * maps the other ranks' (nncb_ipc_import; nncb_ipc_close before the owner frees). (No counterpart in the
- * reference, whose runtime is single-device.)
+ * maps the other ranks' (nncb_ipc_import, in another process than the one that exported: CUDA IPC does not open a
+ * process's own handles; nncb_ipc_close before the owner frees). One allocation may hold the partial buffers of both
+ * slots and the flag block. (No counterpart in the reference, whose runtime is single-device.)
  * nncb_peer_allreduce_add_rmsnorm_f16 is the exchange and what follows it in a decoder block, in one launch:
  *   delta = f16( sum over ranks r = 0 .. world-1, in that order, of partials[r] in f32 );
  *   x <- f16(x + delta) in place;  h = f16(x * rsqrt(mean(x^2) + eps) * weight)          (as nncb_add_rmsnorm_f16)
