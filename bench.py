@@ -792,7 +792,14 @@ def run_decode(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     ctx = Context(local)
+    options = {}
+    for item in args.option:
+        name, _, value = item.partition("=")
+        ctx.set_option(name, int(value))
+        options[name] = int(value)
     res = measure_decode(torch, ctx, peaks(), args.steps, args.warmup, world, rank, fused_rope=not args.separate_rope, peer_reduce=not args.nccl_reduce)
+    if options:
+        res["config"]["options"] = options
     if rank == 0:
         print(json.dumps(res))
     # A CUDA graph that held captured NCCL kernels kept the communicator busy: the graph is dropped inside
@@ -824,6 +831,8 @@ def main():
                     help="with --decode: rotary embedding and KV append as a launch of their own instead of inside the attention launch")
     ap.add_argument("--nccl-reduce", action="store_true",
                     help="with --decode under torchrun: NCCL all-reduce + norm kernel instead of the kernel over peer memory")
+    ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
+                    help="with --decode: set a context option first (launch.overlap=0, matmul.tensor_core=0, ...); repeatable")
     ap.add_argument("--streams", action="store_true", help="only the streaming kernels (quantize, dequantize, add, max-pool, input stage)")
     args = ap.parse_args()
     if args.streams:
