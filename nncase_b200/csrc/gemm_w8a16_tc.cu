@@ -37,7 +37,8 @@
 // cluster barrier is enough (qkv 5.5 us, down 7.8 us: no change), the first activation loads sent by the MMA thread
 // and the peers' partials fetched in one batch of 16 (no change; the LM head loses 4 us when its first loads wait
 // for the block's first barrier), gate/up on three CTAs per SM with two load stages and K split four ways (11.0
-// against 9.2 us), a load ring of six slots with one CTA per SM for the LM head (82 us: nothing hides a CTA's fill and
+// against 9.2 us), the unsplit form's tile stored through shared memory, 16 bytes per thread (LM head 56 against
+// 51 us), a load ring of six slots with one CTA per SM for the LM head (82 us: nothing hides a CTA's fill and
 // drain), and two MMA-issuing threads with an accumulator each (no change).
 #include "tc_dev.cuh"
 #include <cuda_fp16.h>

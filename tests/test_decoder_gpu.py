@@ -31,7 +31,8 @@ def matmul_form(ctx, request):
     ctx.set_option("matmul.tensor_core", 1)
 
 
-@pytest.mark.parametrize("m,n,k", [(64, 1152, 896), (64, 896, 4864), (5, 1000, 128), (1, 16, 64), (33, 9728, 896), (64, 4224, 896)])
+@pytest.mark.parametrize("m,n,k", [(64, 1152, 896), (64, 896, 4864), (5, 1000, 128), (1, 16, 64), (33, 9728, 896), (64, 4224, 896),
+                                   (64, 19208, 128), (37, 19204, 192)])
 def test_gemv_w8a16(ctx, matmul_form, m, n, k):
     rng = np.random.default_rng(m + n)
     x = rng.normal(0, 1, (m, k)).astype(np.float16)
